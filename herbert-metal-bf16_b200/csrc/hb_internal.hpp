@@ -1,0 +1,83 @@
+// Internal C++ side of the C ABI declared in include/hb200.h: the context, the
+// kernel objects behind hb_kernel handles, error plumbing and launch helpers.
+#pragma once
+
+#include <cstdint>
+#include <cstdio>
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "../../include/hb200.h"
+
+struct hb_kernel {
+    std::string name;
+    int kind = 0;  // HB_KIND_*
+    int nargs = 0;
+    virtual ~hb_kernel() = default;
+    // Validates the bound ranges for `m` rows and enqueues the kernel on ctx->stream.
+    virtual int launch(hb_ctx* ctx, const hb_range* args, int nargs, uint32_t m) = 0;
+};
+
+typedef CUresult (*hb_encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                       const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                       CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+struct hb_ctx {
+    int device = 0;
+    int sm_count = 0;
+    size_t smem_optin = 0;
+    std::string device_name;
+    cudaStream_t stream = nullptr;
+    bool own_stream = false;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    uint32_t* status_dev = nullptr;  // 8 words, see tc05.cuh
+    std::string err;
+    std::vector<void*> allocs;
+    size_t allocated = 0;
+    size_t alloc_limit = 0;  // 0 = none; a test hook to provoke HB_OOM without exhausting a GPU
+    hb_encode_tiled_fn encode = nullptr;
+    std::map<std::string, std::unique_ptr<hb_kernel>> kernels;  // by name: one object per distinct kernel
+    uint64_t launches = 0;  // kernels enqueued through this context
+};
+
+namespace hb {
+
+int fail(hb_ctx* ctx, int code, const std::string& msg);
+int cuda_fail(hb_ctx* ctx, cudaError_t e, const char* what);
+#define HB_CUDA(ctx, call)                                        \
+    do {                                                          \
+        cudaError_t e__ = (call);                                 \
+        if (e__ != cudaSuccess) return hb::cuda_fail(ctx, e__, #call); \
+    } while (0)
+
+// A 2-D bf16 row-major tensor [rows][cols] as a TMA descriptor with a box of
+// box_rows x 64 elements in the 128-byte swizzle. Rows or columns past the
+// extents read as zero.
+int make_tmap_bf16(hb_ctx* ctx, CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint32_t box_rows);
+
+// Reads the device status words; turns a kernel-side failure into an error.
+int check_status(hb_ctx* ctx);
+
+inline bool range_ok(const hb_range& r, size_t need) { return r.ptr != nullptr && r.size >= need; }
+
+// Factories (one translation unit per kernel family).
+int make_gemm(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out);
+int make_matvec(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out);
+int make_swiglu_rows(hb_ctx* ctx, uint32_t n, hb_kernel** out);
+int make_route(hb_ctx* ctx, uint32_t experts, uint32_t top_k, hb_kernel** out);
+int make_moe_sort(hb_ctx* ctx, uint32_t experts, uint32_t top_k, uint32_t rows_max, uint32_t bm, hb_kernel** out);
+int make_moe_gather(hb_ctx* ctx, uint32_t h, uint32_t top_k, hb_kernel** out);
+int make_moe_combine(hb_ctx* ctx, uint32_t d, uint32_t top_k, uint32_t f32_sum, hb_kernel** out);
+
+// Registers `k` under its name (or returns the existing object of that name).
+hb_kernel* intern(hb_ctx* ctx, std::unique_ptr<hb_kernel> k);
+hb_kernel* find(hb_ctx* ctx, const std::string& name);
+
+const char* out_tag(uint32_t out);
+
+}  // namespace hb

@@ -1,0 +1,426 @@
+// The small kernels around the GEMMs: SwiGLU over rows, the MoE route (softmax + top-k),
+// the stable expert sort with its tile table, the row gather and the weighted combine.
+// All are memory- or latency-bound CUDA-core kernels; results are bit-exact restatements
+// of the reference's arithmetic (citations per kernel).
+#include <algorithm>
+
+#include "hb_internal.hpp"
+#include "tc05.cuh"
+
+namespace hb {
+
+// ------------------------------------------------------------- swiglu_rows
+// h[r][c] = bf16(g*sigmoid(g)*u), g = gu[r][c], u = gu[r][n + c]
+// (reference src/metal/prefill.rs:2790-2818; src/metal/qwen_kernels.rs:2087 over expert rows).
+__global__ void swiglu_rows_kernel(const uint16_t* __restrict__ gu, uint16_t* __restrict__ h, uint32_t m, uint32_t n, uint32_t vec) {
+    if (vec) {
+        const uint32_t n8 = n / 8;
+        const size_t total = (size_t)m * n8;
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+            const uint32_t r = (uint32_t)(i / n8), c = (uint32_t)(i % n8);
+            const uint4 g = *reinterpret_cast<const uint4*>(gu + (size_t)r * 2 * n + c * 8);
+            const uint4 u = *reinterpret_cast<const uint4*>(gu + (size_t)r * 2 * n + n + c * 8);
+            const uint32_t gw[4] = {g.x, g.y, g.z, g.w}, uw[4] = {u.x, u.y, u.z, u.w};
+            uint32_t o[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t lo = swiglu_bf16(bf16_to_f32(gw[j] & 0xffffu), bf16_to_f32(uw[j] & 0xffffu));
+                const uint32_t hi = swiglu_bf16(bf16_to_f32(gw[j] >> 16), bf16_to_f32(uw[j] >> 16));
+                o[j] = lo | (hi << 16);
+            }
+            *reinterpret_cast<uint4*>(h + (size_t)r * n + c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    } else {
+        const size_t total = (size_t)m * n;
+        for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+            const uint32_t r = (uint32_t)(i / n), c = (uint32_t)(i % n);
+            h[i] = (uint16_t)swiglu_bf16(bf16_to_f32(gu[(size_t)r * 2 * n + c]), bf16_to_f32(gu[(size_t)r * 2 * n + n + c]));
+        }
+    }
+}
+
+// ------------------------------------------------------------------- route
+// One block of `experts` threads per row (reference src/metal/qwen_kernels.rs:1802-1878):
+// softmax of the bf16 scores in f32 (max, exp, sum = 32-lane butterfly sums folded warp by
+// warp in order, divide), top_k rounds of "largest value, lowest index on a tie", weights
+// p/sum(p_top) with the sum taken best-first, rounded to bf16, written in increasing expert order.
+template <int MAXK>
+__global__ void route_topk_kernel(const uint16_t* __restrict__ scores, uint32_t* __restrict__ route, uint32_t experts, uint32_t top_k) {
+    __shared__ float red_v[33];
+    __shared__ uint32_t red_i[33];
+    __shared__ float vals[MAXK];
+    __shared__ uint32_t chosen[MAXK];
+    const uint32_t e = threadIdx.x, lane = e & 31, warp = e >> 5, warps = experts >> 5;
+    const uint32_t row = blockIdx.x;
+    const float s = bf16_to_f32(scores[(size_t)row * experts + e]);
+    // max
+    float mx = s;
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
+    if (lane == 0) red_v[warp] = mx;
+    __syncthreads();
+    if (e == 0) {
+        float a = red_v[0];
+        for (uint32_t j = 1; j < warps; ++j) a = fmaxf(a, red_v[j]);
+        red_v[32] = a;
+    }
+    __syncthreads();
+    mx = red_v[32];
+    __syncthreads();
+    const float ex = exp_f32(__fsub_rn(s, mx));
+    float sum = ex;
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, off));
+    if (lane == 0) red_v[warp] = sum;
+    __syncthreads();
+    if (e == 0) {
+        float a = red_v[0];
+        for (uint32_t j = 1; j < warps; ++j) a = __fadd_rn(a, red_v[j]);
+        red_v[32] = a;
+    }
+    __syncthreads();
+    sum = red_v[32];
+    __syncthreads();
+    float p = __fdiv_rn(ex, sum);
+    for (uint32_t t = 0; t < top_k; ++t) {
+        float bv = p;
+        uint32_t bi = e;
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
+            const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, off);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        }
+        if (lane == 0) { red_v[warp] = bv; red_i[warp] = bi; }
+        __syncthreads();
+        if (e == 0) {
+            float a = red_v[0];
+            uint32_t ai = red_i[0];
+            for (uint32_t j = 1; j < warps; ++j)
+                if (red_v[j] > a) { a = red_v[j]; ai = red_i[j]; }  // warps are in index order: strict > keeps the lowest index
+            vals[t] = a;
+            chosen[t] = ai;
+        }
+        __syncthreads();
+        if (chosen[t] == e) p = -1.0f;
+        __syncthreads();
+    }
+    if (e < top_k) {
+        float total = 0.0f;
+        for (uint32_t j = 0; j < top_k; ++j) total = __fadd_rn(total, vals[j]);
+        const float w = round_bf16(__fdiv_rn(vals[e], total));
+        uint32_t rank = 0;
+        for (uint32_t j = 0; j < top_k; ++j)
+            if (j != e && chosen[j] < chosen[e]) rank++;
+        uint32_t* r = route + (size_t)row * 2 * top_k;
+        r[rank] = chosen[e];
+        r[top_k + rank] = __float_as_uint(w);
+    }
+}
+
+// ---------------------------------------------------------------- moe_sort
+// Stable counting sort of the (row, slot) pairs by expert and the expert-tile table
+// (reference src/metal/prefill.rs:1303-1442): list[p] = pair index, experts ascending, pairs
+// ascending inside an expert; tiles[0] = count, tile t = (expert, first sorted row, rows <= bm).
+// One block of 1024 threads: warp w owns a contiguous segment of pairs and walks it 32 at a
+// time in order; __match_any_sync ranks equal experts inside a step, per-warp per-expert
+// counters in shared memory carry the rank across steps and warps. No atomics: the result is
+// the same list on every run.
+constexpr int SORT_THREADS = 1024;
+constexpr int SORT_WARPS = SORT_THREADS / 32;
+
+__global__ void __launch_bounds__(SORT_THREADS) moe_sort_kernel(const uint32_t* __restrict__ route, uint32_t* __restrict__ list,
+                                                                uint32_t* __restrict__ tiles, uint32_t rows, uint32_t experts, uint32_t top_k, uint32_t bm) {
+    extern __shared__ uint32_t sm[];
+    uint32_t* cnt = sm;                          // [SORT_WARPS][experts]: pairs of expert e in warp w's segment, then running base
+    uint32_t* off = sm + SORT_WARPS * experts;   // [experts]: first sorted row of expert e
+    uint32_t* tstart = off + experts;            // [experts]: first tile of expert e
+    uint32_t* scan = tstart + experts;           // [2][experts] scratch
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t pairs = rows * top_k;
+    const uint32_t seg = ((pairs + SORT_WARPS - 1) / SORT_WARPS + 31) / 32 * 32;
+    const uint32_t s0 = min(pairs, warp * seg), s1 = min(pairs, s0 + seg);
+    for (uint32_t i = tid; i < SORT_WARPS * experts; i += SORT_THREADS) cnt[i] = 0;
+    __syncthreads();
+    auto expert_of = [&](uint32_t i) { return route[(size_t)(i / top_k) * 2 * top_k + (i % top_k)]; };
+    // pass 1: per-warp histograms
+    for (uint32_t b = s0; b < s1; b += 32) {
+        const uint32_t i = b + lane;
+        const bool in = i < s1;
+        const uint32_t x = in ? expert_of(i) : 0xffffffffu;
+        const uint32_t peers = __match_any_sync(0xffffffffu, x);
+        if (in && (peers & ((1u << lane) - 1)) == 0) cnt[warp * experts + x] += __popc(peers);
+        __syncwarp();
+    }
+    __syncthreads();
+    // per expert: exclusive scan over the warps, total count
+    uint32_t total_e = 0;
+    if (tid < experts) {
+        for (uint32_t w = 0; w < SORT_WARPS; ++w) {
+            const uint32_t c = cnt[w * experts + tid];
+            cnt[w * experts + tid] = total_e;
+            total_e += c;
+        }
+    }
+    // exclusive scans over the experts of (count) and (tiles per expert), Hillis-Steele on two arrays
+    const uint32_t ntile_e = (total_e + bm - 1) / bm;
+    uint32_t a = total_e, t = ntile_e;
+    uint32_t* sa = scan;
+    uint32_t* st = scan + experts;
+    if (tid < experts) { sa[tid] = a; st[tid] = t; }
+    __syncthreads();
+    for (uint32_t d = 1; d < experts; d <<= 1) {
+        uint32_t va = 0, vt = 0;
+        if (tid < experts && tid >= d) { va = sa[tid - d]; vt = st[tid - d]; }
+        __syncthreads();
+        if (tid < experts) { a += va; t += vt; sa[tid] = a; st[tid] = t; }
+        __syncthreads();
+    }
+    if (tid < experts) {
+        const uint32_t start = a - total_e, tfirst = t - ntile_e;
+        off[tid] = start;
+        tstart[tid] = tfirst;
+        for (uint32_t j = 0, ti = tfirst; j < total_e; j += bm, ++ti) {
+            tiles[1 + 3 * ti] = tid;
+            tiles[2 + 3 * ti] = start + j;
+            tiles[3 + 3 * ti] = min(bm, total_e - j);
+        }
+        if (tid == experts - 1) tiles[0] = t;
+    }
+    __syncthreads();
+    // pass 2: placement
+    for (uint32_t b = s0; b < s1; b += 32) {
+        const uint32_t i = b + lane;
+        const bool in = i < s1;
+        const uint32_t x = in ? expert_of(i) : 0xffffffffu;
+        const uint32_t peers = __match_any_sync(0xffffffffu, x);
+        const uint32_t before = __popc(peers & ((1u << lane) - 1));
+        uint32_t base = 0;
+        if (in) base = off[x] + cnt[warp * experts + x];
+        __syncwarp();
+        if (in) {
+            list[base + before] = i;
+            if (before == 0) cnt[warp * experts + x] += __popc(peers);
+        }
+        __syncwarp();
+    }
+}
+
+// -------------------------------------------------------------- moe_gather
+// XS[p] = X[list[p] / top_k] (reference src/metal/prefill.rs:579).
+__global__ void moe_gather_kernel(const uint4* __restrict__ x, const uint32_t* __restrict__ list, uint4* __restrict__ xs, uint32_t pairs, uint32_t h8, uint32_t top_k) {
+    const size_t total = (size_t)pairs * h8;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t p = (uint32_t)(i / h8), c = (uint32_t)(i % h8);
+        xs[i] = x[(size_t)(list[p] / top_k) * h8 + c];
+    }
+}
+
+// ------------------------------------------------------------- moe_combine
+// out[r][i] over the slots in route order: acc = bf16(acc + bf16(y*w)) (reference
+// src/metal/qwen_kernels.rs:2119-2161), or with F32SUM an f32 FMA chain rounded once.
+template <bool F32SUM>
+__global__ void moe_combine_kernel(const uint16_t* __restrict__ y, const uint32_t* __restrict__ route, uint16_t* __restrict__ out, uint32_t rows, uint32_t d,
+                                   uint32_t top_k) {
+    const uint32_t d8 = d / 8;
+    const size_t total = (size_t)rows * d8;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t row = (uint32_t)(i / d8), c = (uint32_t)(i % d8);
+        float acc[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+        for (uint32_t s = 0; s < top_k; ++s) {
+            const uint4 v = *reinterpret_cast<const uint4*>(y + ((size_t)row * top_k + s) * d + c * 8);
+            const float w = __uint_as_float(route[(size_t)row * 2 * top_k + top_k + s]);
+            const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float lo = bf16_to_f32(vw[j] & 0xffffu), hi = bf16_to_f32(vw[j] >> 16);
+                if (F32SUM) {
+                    acc[2 * j] = __fmaf_rn(lo, w, acc[2 * j]);
+                    acc[2 * j + 1] = __fmaf_rn(hi, w, acc[2 * j + 1]);
+                } else {
+                    acc[2 * j] = round_bf16(__fadd_rn(acc[2 * j], round_bf16(__fmul_rn(lo, w))));
+                    acc[2 * j + 1] = round_bf16(__fadd_rn(acc[2 * j + 1], round_bf16(__fmul_rn(hi, w))));
+                }
+            }
+        }
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] = f32_to_bf16(acc[2 * j]) | (f32_to_bf16(acc[2 * j + 1]) << 16);
+        *reinterpret_cast<uint4*>(out + (size_t)row * d + c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+}
+
+// ------------------------------------------------------------------ host side
+
+namespace {
+
+inline uint32_t grid_for(hb_ctx* ctx, size_t items, int threads) {
+    size_t blocks = (items + threads - 1) / threads;
+    return (uint32_t)std::max<size_t>(1, std::min<size_t>(blocks, (size_t)ctx->sm_count * 16));
+}
+
+struct SwigluRows : hb_kernel {
+    uint32_t n = 0;
+    int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
+        if (na != 2) return fail(ctx, HB_INVALID, name + ": bindings are gate_up, h");
+        if (m == 0) return fail(ctx, HB_INVALID, name + ": m = 0");
+        if (!range_ok(a[0], (size_t)m * 2 * n * 2) || !range_ok(a[1], (size_t)m * n * 2)) return fail(ctx, HB_INVALID, name + ": a bound range is too small");
+        const uint32_t vec = (n % 8 == 0 && ((reinterpret_cast<uintptr_t>(a[0].ptr) | reinterpret_cast<uintptr_t>(a[1].ptr)) & 15u) == 0) ? 1u : 0u;
+        const size_t items = vec ? (size_t)m * (n / 8) : (size_t)m * n;
+        swiglu_rows_kernel<<<grid_for(ctx, items, 256), 256, 0, ctx->stream>>>(static_cast<const uint16_t*>(a[0].ptr), static_cast<uint16_t*>(a[1].ptr), m, n, vec);
+        HB_CUDA(ctx, cudaGetLastError());
+        ctx->launches++;
+        return HB_OK;
+    }
+};
+
+struct Route : hb_kernel {
+    uint32_t experts = 0, top_k = 0;
+    int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
+        if (na != 2) return fail(ctx, HB_INVALID, name + ": bindings are scores, route");
+        if (m == 0) return fail(ctx, HB_INVALID, name + ": m = 0");
+        if (!range_ok(a[0], (size_t)m * experts * 2) || !range_ok(a[1], (size_t)m * 2 * top_k * 4)) return fail(ctx, HB_INVALID, name + ": a bound range is too small");
+        route_topk_kernel<64><<<m, experts, 0, ctx->stream>>>(static_cast<const uint16_t*>(a[0].ptr), static_cast<uint32_t*>(a[1].ptr), experts, top_k);
+        HB_CUDA(ctx, cudaGetLastError());
+        ctx->launches++;
+        return HB_OK;
+    }
+};
+
+struct MoeSort : hb_kernel {
+    uint32_t experts = 0, top_k = 0, rows_max = 0, bm = 0;
+    size_t smem = 0;
+    int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
+        if (na != 3) return fail(ctx, HB_INVALID, name + ": bindings are route, list, tiles");
+        if (m == 0 || m > rows_max) return fail(ctx, HB_INVALID, name + ": m outside 1.." + std::to_string(rows_max));
+        const size_t tiles_words = 1 + 3 * (size_t)hb_moe_tiles(m, top_k, experts, bm);
+        if (!range_ok(a[0], (size_t)m * 2 * top_k * 4) || !range_ok(a[1], (size_t)m * top_k * 4) || !range_ok(a[2], tiles_words * 4))
+            return fail(ctx, HB_INVALID, name + ": a bound range is too small");
+        moe_sort_kernel<<<1, SORT_THREADS, smem, ctx->stream>>>(static_cast<const uint32_t*>(a[0].ptr), static_cast<uint32_t*>(a[1].ptr), static_cast<uint32_t*>(a[2].ptr), m,
+                                                               experts, top_k, bm);
+        HB_CUDA(ctx, cudaGetLastError());
+        ctx->launches++;
+        return HB_OK;
+    }
+};
+
+struct MoeGather : hb_kernel {
+    uint32_t h = 0, top_k = 0;
+    int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
+        if (na != 3) return fail(ctx, HB_INVALID, name + ": bindings are X, list, XS");
+        if (m == 0) return fail(ctx, HB_INVALID, name + ": m = 0");
+        const uint32_t pairs = m * top_k;
+        if (!range_ok(a[0], (size_t)m * h * 2) || !range_ok(a[1], (size_t)pairs * 4) || !range_ok(a[2], (size_t)pairs * h * 2))
+            return fail(ctx, HB_INVALID, name + ": a bound range is too small");
+        if ((reinterpret_cast<uintptr_t>(a[0].ptr) | reinterpret_cast<uintptr_t>(a[2].ptr)) & 15u) return fail(ctx, HB_INVALID, name + ": X and XS must be 16-byte aligned");
+        moe_gather_kernel<<<grid_for(ctx, (size_t)pairs * (h / 8), 256), 256, 0, ctx->stream>>>(static_cast<const uint4*>(a[0].ptr), static_cast<const uint32_t*>(a[1].ptr),
+                                                                                                 static_cast<uint4*>(a[2].ptr), pairs, h / 8, top_k);
+        HB_CUDA(ctx, cudaGetLastError());
+        ctx->launches++;
+        return HB_OK;
+    }
+};
+
+struct MoeCombine : hb_kernel {
+    uint32_t d = 0, top_k = 0, f32_sum = 0;
+    int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
+        if (na != 3) return fail(ctx, HB_INVALID, name + ": bindings are y, route, out");
+        if (m == 0) return fail(ctx, HB_INVALID, name + ": m = 0");
+        if (!range_ok(a[0], (size_t)m * top_k * d * 2) || !range_ok(a[1], (size_t)m * 2 * top_k * 4) || !range_ok(a[2], (size_t)m * d * 2))
+            return fail(ctx, HB_INVALID, name + ": a bound range is too small");
+        if ((reinterpret_cast<uintptr_t>(a[0].ptr) | reinterpret_cast<uintptr_t>(a[2].ptr)) & 15u) return fail(ctx, HB_INVALID, name + ": y and out must be 16-byte aligned");
+        const uint32_t grid = grid_for(ctx, (size_t)m * (d / 8), 256);
+        if (f32_sum)
+            moe_combine_kernel<true><<<grid, 256, 0, ctx->stream>>>(static_cast<const uint16_t*>(a[0].ptr), static_cast<const uint32_t*>(a[1].ptr), static_cast<uint16_t*>(a[2].ptr), m, d, top_k);
+        else
+            moe_combine_kernel<false><<<grid, 256, 0, ctx->stream>>>(static_cast<const uint16_t*>(a[0].ptr), static_cast<const uint32_t*>(a[1].ptr), static_cast<uint16_t*>(a[2].ptr), m, d, top_k);
+        HB_CUDA(ctx, cudaGetLastError());
+        ctx->launches++;
+        return HB_OK;
+    }
+};
+
+}  // namespace
+
+int make_swiglu_rows(hb_ctx* ctx, uint32_t n, hb_kernel** out) {
+    *out = nullptr;
+    if (n == 0) return fail(ctx, HB_INVALID, "swiglu_rows: n = 0");
+    auto k = std::make_unique<SwigluRows>();
+    k->n = n;
+    k->kind = 3;
+    k->nargs = 2;
+    k->name = "swiglu_rows_" + std::to_string(n);
+    *out = intern(ctx, std::move(k));
+    return HB_OK;
+}
+
+int make_route(hb_ctx* ctx, uint32_t experts, uint32_t top_k, hb_kernel** out) {
+    *out = nullptr;
+    // the reference's own bound: experts a multiple of the simdgroup, <= 1024 (qwen_kernels.rs:1803)
+    if (experts == 0 || experts % 32 != 0 || experts > 1024 || top_k < 1 || top_k > experts || top_k > 64)
+        return fail(ctx, HB_UNSUPPORTED, "route: experts a multiple of 32 up to 1024, 1 <= top_k <= min(experts, 64)");
+    auto k = std::make_unique<Route>();
+    k->experts = experts;
+    k->top_k = top_k;
+    k->kind = 4;
+    k->nargs = 2;
+    k->name = "route_qwen_" + std::to_string(experts) + "_k" + std::to_string(top_k);
+    *out = intern(ctx, std::move(k));
+    return HB_OK;
+}
+
+int make_moe_sort(hb_ctx* ctx, uint32_t experts, uint32_t top_k, uint32_t rows_max, uint32_t bm, hb_kernel** out) {
+    *out = nullptr;
+    if (experts == 0 || experts > 1024 || top_k == 0 || rows_max == 0) return fail(ctx, HB_UNSUPPORTED, "moe_sort: 1..1024 experts, top_k and rows_max positive");
+    if (bm != 16 && bm != 32 && bm != 64) return fail(ctx, HB_UNSUPPORTED, "moe_sort: tile rows 16, 32 or 64");
+    auto k = std::make_unique<MoeSort>();
+    k->experts = experts;
+    k->top_k = top_k;
+    k->rows_max = rows_max;
+    k->bm = bm;
+    k->smem = ((size_t)SORT_WARPS * experts + 4 * (size_t)experts) * sizeof(uint32_t);
+    k->kind = 5;
+    k->nargs = 3;
+    k->name = "moe_sort_" + std::to_string(experts) + "_k" + std::to_string(top_k) + "_r" + std::to_string(rows_max) + "_m" + std::to_string(bm);
+    if (hb_kernel* have = find(ctx, k->name)) {
+        *out = have;
+        return HB_OK;
+    }
+    if (k->smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(moe_sort_kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)k->smem);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(moe_sort)");
+    }
+    *out = intern(ctx, std::move(k));
+    return HB_OK;
+}
+
+int make_moe_gather(hb_ctx* ctx, uint32_t h, uint32_t top_k, hb_kernel** out) {
+    *out = nullptr;
+    if (h == 0 || h % 8 != 0 || top_k == 0) return fail(ctx, HB_UNSUPPORTED, "moe_gather: h a positive multiple of 8, top_k positive");
+    auto k = std::make_unique<MoeGather>();
+    k->h = h;
+    k->top_k = top_k;
+    k->kind = 6;
+    k->nargs = 3;
+    k->name = "moe_gather_" + std::to_string(h) + "_k" + std::to_string(top_k);
+    *out = intern(ctx, std::move(k));
+    return HB_OK;
+}
+
+int make_moe_combine(hb_ctx* ctx, uint32_t d, uint32_t top_k, uint32_t f32_sum, hb_kernel** out) {
+    *out = nullptr;
+    if (d == 0 || d % 8 != 0 || top_k == 0) return fail(ctx, HB_UNSUPPORTED, "moe_combine: d a positive multiple of 8, top_k positive");
+    auto k = std::make_unique<MoeCombine>();
+    k->d = d;
+    k->top_k = top_k;
+    k->f32_sum = f32_sum;
+    k->kind = 7;
+    k->nargs = 3;
+    k->name = "moe_combine_" + std::to_string(d) + "_k" + std::to_string(top_k) + (f32_sum ? "_f32" : "");
+    *out = intern(ctx, std::move(k));
+    return HB_OK;
+}
+
+}  // namespace hb

@@ -1,0 +1,241 @@
+/*
+ * hb200 - C ABI of the B200 implementation of herbert-metal-bf16's bf16
+ * matrix-multiply path (prefill GEMM, decode matvec, MoE grouped GEMM) and of
+ * the load-time loop that chooses among kernel candidates.
+ *
+ * The reference engine has no FFI for this path: its seam is the internal
+ * Rust API between the engine (src/metal/qwen.rs) and the kernel emitter plus
+ * device layer (src/msl, src/metal/gpu.rs). Each entry point below names the
+ * reference item it stands for (path:line inside the reference project).
+ *
+ * Conventions: every function returns an hb_status (0 = ok) and never aborts
+ * or throws across the boundary (reference: Result<T, HerbertError>,
+ * src/core/error.rs:9-27). hb_last_error() gives the message of the last
+ * failure on a context. A context is not thread-safe: one context, one host
+ * thread, one CUDA stream (reference: one engine, one queue,
+ * src/metal/gpu.rs:59-74). Buffers are device memory; the reference's
+ * host-visible shared buffers become explicit hb_upload/hb_download copies.
+ * All matrices are row-major; bf16 values are passed as uint16_t bits.
+ */
+#ifndef HB200_H
+#define HB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct hb_ctx hb_ctx;
+typedef struct hb_kernel hb_kernel;
+
+typedef enum {
+    HB_OK = 0,
+    HB_INVALID = 1,     /* bad argument, range too small, misaligned pointer */
+    HB_UNSUPPORTED = 2, /* a kernel that cannot be built for this shape/tile: the caller skips the candidate
+                           (reference: Gpu::pipeline -> Err, "not built", src/metal/qwen.rs:2266) */
+    HB_BACKEND = 3,     /* CUDA failure (reference: HerbertError::Backend, src/core/error.rs:19) */
+    HB_OOM = 4,
+    HB_KERNEL = 5       /* a kernel reported a failed bounded wait through the status buffer */
+} hb_status;
+
+/* Epilogue of a projection (reference: enum Out, src/metal/kernels.rs:30-42). */
+typedef enum {
+    HB_OUT_BF16 = 0,     /* y = bf16(acc) */
+    HB_OUT_F32 = 1,      /* y = acc */
+    HB_OUT_RESIDUAL = 2, /* y = bf16(f32(y) + f32(bf16(acc))) */
+    HB_OUT_SWIGLU = 3    /* W = [gate | up] rows; y[.., n/2] = bf16(g*sigmoid(g)*u), g and u rounded to bf16 first */
+} hb_out;
+
+/* Which rows a GEMM reads and writes (reference: enum MmaRows, src/metal/prefill.rs:317-328). */
+typedef enum {
+    HB_ROWS_DENSE = 0,
+    HB_ROWS_GATHER = 1, /* expert tiles: sorted row p reads X[list[p] / top_k], writes Y[p] */
+    HB_ROWS_SCATTER = 2, /* expert tiles: sorted row p reads X[p], writes Y[list[p]] */
+    HB_ROWS_SORTED = 3   /* expert tiles over rows gathered beforehand (moe_gather): reads X[p], writes Y[p]
+                            (reference: the expert branch of gemm_mm2d_rows, src/metal/prefill.rs:534-552) */
+} hb_rows_mode;
+
+/* A range of device memory (reference: Range{buf, offset, size}, src/metal/gpu.rs:32-47). */
+typedef struct {
+    void* ptr;
+    size_t size;
+} hb_range;
+
+/* One recorded launch (reference: Op{pipe, ranges, groups}, src/metal/qwen.rs:650). The grid is derived
+ * from `m`, the row count the reference keeps in state[STATE_ROWS] (src/metal/kernels.rs:10-15). */
+typedef struct {
+    const hb_kernel* kernel;
+    const hb_range* args;
+    int nargs;
+    uint32_t m;
+} hb_op;
+
+/* ---- device and buffers ------------------------------------------------ */
+
+/* Gpu::open, src/metal/gpu.rs:70. Fails with HB_BACKEND when no sm_100 device is present:
+ * there is no CPU fallback. */
+int hb_open(int device, hb_ctx** out);
+/* Buffers and kernels of the context are freed here (the reference never frees, gpu.rs:62). */
+int hb_close(hb_ctx* ctx);
+/* Message of the last failure; ctx may be NULL for a failed hb_open. */
+const char* hb_last_error(const hb_ctx* ctx);
+/* Gpu::summary, src/metal/gpu.rs:81. */
+int hb_describe(hb_ctx* ctx, char* buf, size_t len);
+/* Use an existing CUDA stream (cudaStream_t) for every later launch and copy; NULL restores the
+ * context's own stream. For callers that order these kernels with their own collectives. */
+int hb_set_stream(hb_ctx* ctx, void* cuda_stream);
+/* Gpu::alloc, src/metal/gpu.rs:92-123: zero-initialised, 256-byte aligned, owned by the context. */
+int hb_alloc(hb_ctx* ctx, size_t bytes, void** dptr);
+/* Test hook: hb_alloc fails with HB_OOM once the context holds more than `bytes` (0 = no limit). */
+int hb_set_alloc_limit(hb_ctx* ctx, size_t bytes);
+/* The reference writes and reads its shared buffers through raw pointers while the GPU is idle
+ * (src/metal/qwen.rs:2764); here these are stream-ordered copies followed by a synchronisation. */
+int hb_upload(hb_ctx* ctx, void* dst_device, const void* src_host, size_t bytes);
+int hb_download(hb_ctx* ctx, void* dst_host, const void* src_device, size_t bytes);
+int hb_memset(hb_ctx* ctx, void* dst_device, int value, size_t bytes);
+/* Waits for the stream and checks the kernels' status words (command-buffer status, gpu.rs:215-218). */
+int hb_sync(hb_ctx* ctx);
+/* Number of kernels this context has enqueued so far. */
+uint64_t hb_launch_count(const hb_ctx* ctx);
+
+/* ---- kernels ------------------------------------------------------------ */
+
+/* Prefill GEMM Y[m][n] = out(X[m][k] . W[n][k]^T), bf16 inputs, f32 accumulation on the tensor cores.
+ * Stands for the emitters gemm_mma_rows / gemm_mm2d / gemm_nax_swiglu and the expert-tile forms
+ * (src/metal/prefill.rs:838,852-1301,442-567,755-822; rows modes :317-328,889-941,1206-1209).
+ * Bindings: DENSE  W, X, Y             (reference order state, W, X, Y; prefill.rs:416-417)
+ *           GATHER / SCATTER / SORTED  W, X, Y, list, tiles   (prefill.rs:836-837)
+ * For GATHER/SCATTER `n` is the rows of ONE expert in W ([experts*n][k]) and `m` is the number of token rows
+ * of the block; the tile table tells the kernel how many sorted rows there are. */
+typedef struct {
+    uint32_t k, n;
+    uint32_t out;       /* hb_out */
+    uint32_t rows_mode; /* hb_rows_mode */
+    uint32_t top_k;     /* GATHER: slots per token row */
+    uint32_t experts;   /* GATHER/SCATTER */
+    uint32_t bm;        /* GATHER/SCATTER: rows of an expert tile, 16/32/64 (moe.tile) */
+    uint32_t tile_n;    /* DENSE: accumulator columns per tile, 64/128/256 (0 = default 256) */
+    uint32_t stages;    /* shared-memory pipeline depth, 0 = as many as fit */
+    uint32_t cta_pair;  /* DENSE: 1 = two CTAs share a 256-row tile (tcgen05 cta_group::2) */
+    uint32_t m_first;   /* tile order: 1 = walk the row tiles of a column tile first (gemm.mfirst, prefill.rs:26-42) */
+    uint32_t rows_max;  /* largest m this kernel will be launched with (sizes the tile table in expert modes) */
+} hb_gemm_desc;
+int hb_gemm_get(hb_ctx* ctx, const hb_gemm_desc* desc, hb_kernel** out);
+
+/* Decode matvec y[r][n] = out(W[n][k] . x[r][k]) for m = 1..8 activation rows, an HBM-streaming kernel on the
+ * CUDA cores: 128-bit loads, f32 FMA chains, warp-shuffle sums. Stands for matvec / matvec_split
+ * (src/metal/kernels.rs:146-214,502-981). Bindings: W, x, y (kernels.rs:145). The reference is m = 1 only;
+ * rows 2..8 apply the same per-row contract. */
+typedef struct {
+    uint32_t k, n;
+    uint32_t out;           /* BF16, F32, RESIDUAL, SWIGLU (y of n/2, kernels.rs:934-944) */
+    uint32_t rows_max;      /* 1..8 activation rows */
+    uint32_t rows_per_warp; /* W rows one warp reduces: 1, 2, 4 or 8 (the reference's `rows`) */
+    uint32_t split;         /* K split across the warps of a block: 1, 2 or 4 (mv.split) */
+    uint32_t persist;       /* 1 = a fixed grid that loops over the row groups (mv.persist) */
+} hb_matvec_desc;
+int hb_matvec_get(hb_ctx* ctx, const hb_matvec_desc* desc, hb_kernel** out);
+
+/* h = bf16(g*sigmoid(g)*u) over rows of [gate(n) | up(n)]: swiglu_rows, src/metal/prefill.rs:2790-2818 (and
+ * swiglu_slots over sorted expert rows, src/metal/qwen_kernels.rs:2087). Bindings: gate_up, h. */
+int hb_swiglu_get(hb_ctx* ctx, uint32_t n, hb_kernel** out);
+/* route_qwen, src/metal/qwen_kernels.rs:1802-1878. Bindings: scores (bf16 [m][experts]),
+ * route (u32 [m][2*top_k]: experts ascending, then the f32 bits of their bf16 weights). */
+int hb_route_get(hb_ctx* ctx, uint32_t experts, uint32_t top_k, hb_kernel** out);
+/* moe_sort, src/metal/prefill.rs:1315-1442: stable counting sort of the (row, slot) pairs by expert and the
+ * expert-tile table. Bindings: route, list (u32 [m*top_k]), tiles (u32 [1 + 3*hb_moe_tiles()]). */
+int hb_moe_sort_get(hb_ctx* ctx, uint32_t experts, uint32_t top_k, uint32_t rows_max, uint32_t bm, hb_kernel** out);
+/* moe_tiles, src/metal/prefill.rs:832: upper bound of the number of expert tiles. */
+uint32_t hb_moe_tiles(uint32_t rows_max, uint32_t top_k, uint32_t experts, uint32_t bm);
+/* moe_gather, src/metal/prefill.rs:579: XS[p] = X[list[p] / top_k]. Bindings: X, list, XS. m = token rows. */
+int hb_moe_gather_get(hb_ctx* ctx, uint32_t h, uint32_t top_k, hb_kernel** out);
+/* moe_combine, src/metal/qwen_kernels.rs:2119-2161: acc = bf16(acc + bf16(y*w)) over the slots in route order.
+ * f32_sum = 1 is the variant that keeps the sum in f32 and rounds once. Bindings: y ([m][top_k][d]), route, out. */
+int hb_moe_combine_get(hb_ctx* ctx, uint32_t d, uint32_t top_k, uint32_t f32_sum, hb_kernel** out);
+
+/* Emitted.name, src/msl/mod.rs:1461: deterministic, encodes the description. */
+const char* hb_kernel_name(const hb_kernel* k);
+/* Gpu::dispatch, src/metal/gpu.rs:166: enqueue on the context's stream. Any 1 <= m <= rows_max. */
+int hb_launch(hb_ctx* ctx, const hb_kernel* k, const hb_range* args, int nargs, uint32_t m);
+/* Runs the sequence once (asynchronously). */
+int hb_run(hb_ctx* ctx, const hb_op* ops, int nops);
+/* time_ops, src/metal/qwen.rs:2593: `reps` runs of the sequence, GPU seconds measured with events on the
+ * stream (reference: Done.gpu of the command buffer, src/metal/gpu.rs:209-221). Synchronises. */
+int hb_time(hb_ctx* ctx, const hb_op* ops, int nops, int reps, double* gpu_seconds);
+
+/* ---- the load-time selection loop (host library) ------------------------- */
+
+/* Tune, src/metal/qwen.rs:62-397. Keys on this path are acted on (gemm.auto gemm.mma gemm.tn gemm.mform
+ * gemm.mfirst gemm.half gemm.simt prefill.block moe.grouped moe.tile pf.fswi mv.auto mv.split mv.persist
+ * mv.cold dec.fswi); every other key of the reference is parsed, validated as a u32 and stored. */
+typedef struct hb_tune hb_tune;
+int hb_tune_new(hb_tune** out);
+void hb_tune_free(hb_tune* t);
+/* Tune::apply, qwen.rs:296-389: "key=value[,key=value]"; unknown key, non-u32 value or a value out of range
+ * returns HB_INVALID with the reference's message in err. */
+int hb_tune_apply(hb_tune* t, const char* list, char* err, size_t errlen);
+int hb_tune_get(const hb_tune* t, const char* key, uint32_t* value);
+/* Tune::summary, qwen.rs:391-396 (the keys of this path, in the reference's order). */
+int hb_tune_summary(const hb_tune* t, char* buf, size_t len);
+/* 1 when GEMM candidates are timed at load: gemm.auto != 0 and none of gemm.mma/gemm.tn/gemm.mform given
+ * (qwen.rs:902,2229). */
+int hb_tune_gemm_timed(const hb_tune* t);
+
+typedef struct hb_selector hb_selector;
+int hb_selector_new(hb_ctx* ctx, const hb_tune* tune, hb_selector** out);
+void hb_selector_free(hb_selector* s);
+/* The "[autotune] ..." lines produced so far (also written to stderr), newline separated. */
+const char* hb_selector_log(const hb_selector* s);
+/* Row buckets of the prefill GEMMs: 64, 128, .. < block, then block (qwen.rs:1049-1052). Returns the count. */
+int hb_selector_buckets(const hb_selector* s, uint32_t* buckets, int cap);
+/* autotune_inputs / fill_random16, qwen.rs:2605-2626: fills a device range with xorshift32 bf16 in [-1, 1). */
+int hb_fill_random16(hb_ctx* ctx, hb_range dst, uint32_t seed);
+/* QwenEngine::gemm, qwen.rs:2200-2315: the kernel for (k, n, out) at m rows. With timing on, candidates are
+ * built, checked against the first one (check_candidates, qwen.rs:2497-2543: full and partial block from a
+ * zeroed output, rejected when max|diff| > max|ref|/64), timed (pick_flagged, qwen.rs:2547-2573: 5 interleaved
+ * rounds, median) and the pick cached under "{k}x{n} {Out}, {m} rows". With timing off the tune keys name it. */
+int hb_select_gemm(hb_selector* s, uint32_t k, uint32_t n, uint32_t out, hb_range w, hb_range x, hb_range y, uint32_t m,
+                   const hb_kernel** picked);
+/* gate_up_pipes, qwen.rs:2148-2191: [gate|up] GEMM + swiglu_rows ("apart") against the fused epilogue,
+ * per pf.fswi (0 apart, 1 fused, 2 timed). ops_out receives 1 or 2 ops bound to the given ranges;
+ * gu is the [m][2*inter] intermediate of the apart form. */
+int hb_select_gate_up(hb_selector* s, uint32_t k, uint32_t inter, hb_range w, hb_range x, hb_range gu, hb_range h, uint32_t m,
+                      const hb_kernel** kernels_out, int* nkernels);
+/* mv_full, qwen.rs:1311-1505: the matvec form for (k, n, out) at `rows` activation rows. `w_copies` same-shaped
+ * matrices are walked in turn so that weights come from memory, not cache (mv.cold, qwen.rs:248-251,1177). */
+int hb_select_matvec(hb_selector* s, uint32_t k, uint32_t n, uint32_t out, uint32_t rows, const hb_range* w_copies, int ncopies,
+                     hb_range x, hb_range y, const hb_kernel** picked);
+/* expert_pipes, qwen.rs:2326-2386: for bm in {16, 32, 64} (moe.tile only, if given) the sort and the two expert
+ * GEMMs are timed on a real route (the caller has run the router on its block); per tile size the fastest
+ * checked gate/up form is kept, then the tile whose sort + gate/up + down time is least.
+ * Gate/up forms: "fused" (GATHER GEMM with the SwiGLU epilogue, X -> EHB), "apart" (GATHER GEMM to EGU, then
+ * swiglu over the sorted rows; needs egu), "gather+fused" (moe_gather to XS, then the SORTED GEMM with the
+ * SwiGLU epilogue; needs xs). egu and xs may be empty ranges: their forms are then left out. */
+typedef struct {
+    uint32_t experts, top_k, h, mi, m;
+    hb_range route, list, tiles, x, wgu, wdown, ehb, ey;
+    hb_range egu; /* optional: bf16 [m*top_k][2*mi] */
+    hb_range xs;  /* optional: bf16 [m*top_k][h] */
+} hb_expert_io;
+typedef struct {
+    uint32_t bm;
+    const hb_kernel* sort;    /* bindings route, list, tiles */
+    const hb_kernel* gather;  /* NULL, or moe_gather: X, list, XS */
+    const hb_kernel* gate_up; /* W, X (or XS), EHB (or EGU), list, tiles */
+    const hb_kernel* swiglu;  /* NULL, or swiglu over sorted rows: EGU, EHB; launched with m*top_k rows */
+    const hb_kernel* down;    /* W, EHB, EY, list, tiles */
+} hb_expert_pick;
+int hb_select_experts(hb_selector* s, const hb_expert_io* io, hb_expert_pick* pick);
+/* Test hook for the correctness gate: while enabled, hb_select_gemm adds a candidate named "wrong" that runs
+ * the first candidate and then scales the output by 1.25 (builds, runs, plausible magnitudes, incorrect). The
+ * 1/64 rule must reject it and log it (the reference's incident: README.md:65-73). */
+int hb_selector_inject_wrong(hb_selector* s, int enable);
+/* check_candidates' rule alone, on host arrays (bf16 bits or f32): returns HB_OK and sets *eligible. */
+int hb_check_rule(const void* reference, const void* got, size_t count, int f32_out, int* eligible, float* err, float* scale);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
