@@ -1,0 +1,433 @@
+"""Benchmark of the bf16 matrix-multiply hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One JSON line on stdout. A step is one pass of the 9B-class layer GEMM set at M = 2048 rows
+(BASELINE config 3: qkv 4096->6144, o_proj 4096->4096 + residual, fused gate/up 4096->2x12288 with
+SiLU*mul, down 12288->4096 + residual) through the C ABI of libhb200.so, kernels chosen by the
+load-time selection loop. `value` is TFLOP/s over all ranks with inputs resident in HBM, timed with
+CUDA events on the launching stream; `e2e` is the same step with the block's activations copied in
+from pinned host memory and the result copied back inside the timed region. The decode matvec
+(config 2), the 27B-class tensor-parallel FFN (config 4) and the MoE block (config 5) are measured
+beside it and reported under "extra". Inputs are seeded synthetic tensors of the reference's shapes
+(no checkpoints exist here): X ~ N(0,1), W ~ N(0,1/sqrt(K)), bf16.
+
+--impl reference times the CPU restatement of the same contract (oracle/, OpenMP on every host
+core) on a bounded row sample of the same workload: the reference's own kernels exist only as
+Metal shaders and cannot run here.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+HIDDEN, INTER, ROWS = 4096, 12288, 2048
+# (name, K, N, out) of the layer's four projections; out: 0 Bf16, 2 Residual, 3 Swiglu
+LAYER = [("qkv", HIDDEN, 6144, 0), ("o_proj", HIDDEN, HIDDEN, 2), ("gate_up", HIDDEN, 2 * INTER, 3), ("down", INTER, HIDDEN, 2)]
+STEP_FLOP = sum(2.0 * ROWS * k * n for _, k, n, _ in LAYER)
+
+
+def peaks():
+    p = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            d = json.load(open(path))
+            p.update({k: float(d[k]) for k in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained") if k in d})
+            p["source"] = "measured"
+        except Exception:
+            pass
+    return p
+
+
+class ClockSampler(threading.Thread):
+    """SM clock and throttle reasons read through NVML while the timed loops run (read-only)."""
+
+    def __init__(self, index: int):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self.active = threading.Event()
+        self.stop = threading.Event()
+        self.ok = False
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM)
+            self.ok = True
+        except Exception as e:  # no NVML: the clocks key says so
+            self.err = str(e)
+
+    def run(self):
+        if not self.ok:
+            return
+        nv = self.nv
+        names = {
+            getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+            getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+            getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+        }
+        while not self.stop.is_set():
+            if self.active.is_set():
+                try:
+                    self.samples.append(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM))
+                    try:
+                        r = nv.nvmlDeviceGetCurrentClocksEventReasons(self.h)
+                    except Exception:
+                        r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                    for bit, name in names.items():
+                        if r & bit:
+                            self.reasons.add(name)
+                except Exception:
+                    pass
+            time.sleep(0.002)
+
+    def summary(self):
+        if not self.ok:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "note": "NVML unavailable: " + getattr(self, "err", "")}
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def run_reference(args):
+    """The CPU arm: the contract restated in C (oracle/), all host threads, a row sample of the workload."""
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    import numpy as np
+
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from oracle_lib import Oracle
+
+    o = Oracle(native=True)
+    rows = 64
+    rng = np.random.default_rng(0)
+
+    def bf16(a):
+        b = a.astype(np.float32).view(np.uint32)
+        return ((b + 0x7FFF + ((b >> 16) & 1)) >> 16).astype(np.uint16)
+
+    ws = [bf16(rng.standard_normal((n, k), dtype=np.float32) * k**-0.5) for _, k, n, _ in LAYER]
+    xs = [bf16(rng.standard_normal((rows, k), dtype=np.float32)) for _, k, _, _ in LAYER]
+    y0 = bf16(rng.standard_normal((rows, HIDDEN), dtype=np.float32))
+
+    def step():
+        for (name, k, n, out), w, x in zip(LAYER, ws, xs):
+            o.gemm_f32(x, w, out, y0 if out == 2 else None)
+
+    # size the sample so that steps + warmup stay within about two minutes
+    t0 = time.perf_counter()
+    step()
+    one = time.perf_counter() - t0
+    budget = 120.0 / max(1, args.steps + args.warmup)
+    while rows < ROWS and one * 2 < budget and one * 2 < 8.0:
+        rows *= 2
+        one *= 2
+    xs = [bf16(rng.standard_normal((rows, k), dtype=np.float32)) for _, k, _, _ in LAYER]
+    y0 = bf16(rng.standard_normal((rows, HIDDEN), dtype=np.float32))
+    for _ in range(args.warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        step()
+    dt = (time.perf_counter() - t0) / args.steps
+    flop = STEP_FLOP * rows / ROWS
+    value = flop / dt / 1e12
+    sample = f"{rows} of {ROWS} rows of every GEMM of the layer set (same K and N), f32 accumulate, one RNE"
+    line = {
+        "impl": "reference", "metric": "bf16 prefill GEMM TFLOP/s/GPU", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": "9B-class layer GEMM set, M=2048 (CPU arm: row sample)", "rows": ROWS, "hidden": HIDDEN, "intermediate": INTER,
+                   "note": "the reference's kernels are Metal shaders and cannot run here; this is the CPU restatement of its contract"},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": o.threads(), "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extra", action="store_true", help="skip the matvec / MoE / tensor-parallel sections")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+        return
+
+    import numpy as np
+    import torch
+
+    from __graft_entry__ import load_package
+
+    hb = load_package()
+    rank, world, local = dist_env()
+    if world > 1:
+        import torch.distributed as dist
+
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    dev = torch.device("cuda", local)
+    torch.cuda.set_device(dev)
+    ctx = hb.Context(local)
+    pk = peaks()
+    sampler = ClockSampler(local)
+    sampler.start()
+
+    def wrap(t):
+        return ctx.wrap(t.data_ptr(), t.numel() * t.element_size())
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(sec):
+        if world == 1:
+            return sec
+        t = torch.tensor([sec], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- the layer GEMM set: weights and activations resident in HBM (386 MB of weights per step: larger than L2)
+    g = torch.Generator(device=dev)
+    g.manual_seed(0x9E3779B9 + rank)
+    weights = [(torch.randn(n, k, device=dev, generator=g) * k**-0.5).bfloat16() for _, k, n, _ in LAYER]
+    x = torch.randn(ROWS, HIDDEN, device=dev, generator=g).bfloat16()
+    qkv = torch.zeros(ROWS, 6144, device=dev, dtype=torch.bfloat16)
+    resid = torch.randn(ROWS, HIDDEN, device=dev, generator=g).bfloat16()
+    hmid = torch.zeros(ROWS, INTER, device=dev, dtype=torch.bfloat16)
+    gu_scratch = torch.zeros(ROWS, 2 * INTER, device=dev, dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+
+    tune = hb.Tune("")
+    sel = hb.Selector(ctx, tune)
+    t_sel = time.perf_counter()
+    k_qkv = sel.gemm(HIDDEN, 6144, 0, wrap(weights[0]), wrap(x), wrap(qkv), ROWS)
+    k_o = sel.gemm(HIDDEN, HIDDEN, 2, wrap(weights[1]), wrap(x), wrap(resid), ROWS)
+    k_gu = sel.gate_up(HIDDEN, INTER, wrap(weights[2]), wrap(x), wrap(gu_scratch), wrap(hmid), ROWS)
+    k_down = sel.gemm(INTER, HIDDEN, 2, wrap(weights[3]), wrap(hmid), wrap(resid), ROWS)
+    t_sel = time.perf_counter() - t_sel
+    ops = [(k_qkv, ROWS, wrap(weights[0]), wrap(x), wrap(qkv)), (k_o, ROWS, wrap(weights[1]), wrap(x), wrap(resid))]
+    if len(k_gu) == 2:
+        ops += [(k_gu[0], ROWS, wrap(weights[2]), wrap(x), wrap(gu_scratch)), (k_gu[1], ROWS, wrap(gu_scratch), wrap(hmid))]
+    else:
+        ops += [(k_gu[0], ROWS, wrap(weights[2]), wrap(x), wrap(hmid))]
+    ops += [(k_down, ROWS, wrap(weights[3]), wrap(hmid), wrap(resid))]
+    picks = {"qkv": k_qkv.name, "o_proj": k_o.name, "gate_up": "+".join(k.name for k in k_gu), "down": k_down.name}
+
+    ctx.time(ops, args.warmup)
+    barrier()
+    sampler.active.set()
+    launches0 = ctx.launch_count()
+    sec = ctx.time(ops, args.steps)  # CUDA events on the launching stream around the K steps
+    launches = ctx.launch_count() - launches0
+    barrier()
+    sec = max_over_ranks(sec)
+    ms_per_step = sec / args.steps * 1e3
+    value = STEP_FLOP * world / (sec / args.steps) / 1e12
+
+    # ---- end to end: activations in from pinned host memory, result back out, every step
+    x_host = torch.empty(ROWS, HIDDEN, dtype=torch.bfloat16).pin_memory()
+    x_host.copy_(x.cpu())
+    y_host = torch.empty(ROWS, HIDDEN, dtype=torch.bfloat16).pin_memory()
+    d_x, d_resid = wrap(x), wrap(resid)
+    L = hb.lib()
+
+    def e2e_step():
+        ctx._check(L.hb_upload(ctx.h, d_x.ptr, x_host.data_ptr(), ROWS * HIDDEN * 2))
+        ctx.run(ops)
+        ctx._check(L.hb_download(ctx.h, y_host.data_ptr(), d_resid.ptr, ROWS * HIDDEN * 2))
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    n_e2e = max(3, min(args.steps, 50))
+    t0 = time.perf_counter()
+    for _ in range(n_e2e):
+        e2e_step()
+    torch.cuda.synchronize()
+    e2e_sec = max_over_ranks((time.perf_counter() - t0) / n_e2e)
+    sampler.active.clear()
+    barrier()
+    e2e = {"value": STEP_FLOP * world / e2e_sec / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": ROWS * HIDDEN * 2, "d2h_bytes_per_step": ROWS * HIDDEN * 2,
+           "ms_per_step": e2e_sec * 1e3, "steps": n_e2e}
+
+    per_gpu_tflops = value / world
+    roofline = {
+        "bound": "tensor", "achieved": per_gpu_tflops, "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": per_gpu_tflops / pk["bf16_tflops"],
+        "traffic": TRAFFIC_BYTES_PER_LAUNCH, "kernel": "gemm_bf16_tn_kernel", "peak_source": pk["source"] + " (burst cuBLAS bf16)",
+        "frac_of_sustained_peak": per_gpu_tflops / pk["bf16_tflops_sustained"], "frac_of_nominal_2250": per_gpu_tflops / 2250.0,
+        "algorithmic_flop_per_launch": STEP_FLOP / 4, "launches_per_step": len(ops),
+    }
+
+    extra = {"selection_seconds": t_sel, "picks": picks}
+    if not args.no_extra:
+        try:
+            extra.update(bench_extra(hb, ctx, sel, torch, dev, wrap, pk, rank, world, barrier, max_over_ranks))
+        except Exception as e:  # the headline stands on its own
+            extra["error"] = repr(e)
+
+    cpu = None
+    if rank == 0 and world == 1:
+        cpu = cpu_baseline()
+
+    sampler.stop.set()
+    if rank == 0:
+        line = {
+            "metric": "bf16 prefill GEMM TFLOP/s/GPU", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "9B-class layer GEMM set, M=2048: qkv 4096->6144, o 4096->4096 +residual, gate/up 4096->2x12288 SiLU*mul, down 12288->4096 +residual",
+                       "rows": ROWS, "hidden": HIDDEN, "intermediate": INTER, "parallelism": f"replicas x{world}" if world > 1 else "1 GPU",
+                       "l2": "386 MB of weights per step: inputs larger than L2"},
+            "e2e": e2e, "gpu_launches": launches, "clocks": sampler.summary(), "roofline": roofline, "cpu_baseline": cpu, "extra": extra,
+        }
+        print(json.dumps(line))
+    sel.close()
+    ctx.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the GEMM kernel, averaged over the four launches of a
+# step, from the ncu capture summarised in profiles/ (None until that capture exists).
+TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def bench_extra(hb, ctx, sel, torch, dev, wrap, pk, rank, world, barrier, max_over_ranks):
+    """Decode matvec (config 2) and the MoE block (config 5) on every rank's own GPU."""
+    out = {}
+    g = torch.Generator(device=dev)
+    g.manual_seed(1234 + rank)
+    # -- matvec: K=4096, N=12288, M in {1,4,8}; four weight copies walked in turn so that W streams from HBM
+    k, n = 4096, 12288
+    copies = [(torch.randn(n, k, device=dev, generator=g) * k**-0.5).bfloat16() for _ in range(4)]
+    xs = torch.randn(8, k, device=dev, generator=g).bfloat16()
+    y = torch.zeros(8, n, device=dev, dtype=torch.bfloat16)
+    mv = {}
+    for m in (1, 4, 8):
+        kern = sel.matvec(k, n, 0, m, [wrap(c) for c in copies], wrap(xs), wrap(y))
+        ops = [(kern, m, wrap(c), wrap(xs), wrap(y)) for c in copies]
+        ctx.time(ops, 5)
+        barrier()
+        sec = max_over_ranks(ctx.time(ops, 50) / (50 * len(copies)))
+        bytes_ = 2.0 * (n * k + m * k + m * n)
+        mv[f"m{m}"] = {"us": sec * 1e6, "gbs": bytes_ / sec / 1e9, "frac_hbm": bytes_ / sec / 1e9 / pk["hbm_gbs"], "form": kern.name}
+    out["matvec_4096x12288"] = mv
+    del copies
+    # the LM-head-like matrix is larger than L2 on its own
+    n2 = 151936
+    w2 = (torch.randn(n2, k, device=dev, generator=g) * k**-0.5).bfloat16()
+    y2 = torch.zeros(8, n2, device=dev, dtype=torch.bfloat16)
+    mv2 = {}
+    for m in (1, 4, 8):
+        kern = sel.matvec(k, n2, 0, m, [wrap(w2)], wrap(xs), wrap(y2))
+        ops = [(kern, m, wrap(w2), wrap(xs), wrap(y2))]
+        ctx.time(ops, 3)
+        barrier()
+        sec = max_over_ranks(ctx.time(ops, 20) / 20)
+        bytes_ = 2.0 * (n2 * k + m * k + m * n2)
+        mv2[f"m{m}"] = {"us": sec * 1e6, "gbs": bytes_ / sec / 1e9, "frac_hbm": bytes_ / sec / 1e9 / pk["hbm_gbs"], "form": kern.name}
+    out["matvec_4096x151936"] = mv2
+    del w2, y2
+    # -- MoE block (config 5): 2048 tokens, hidden 2048, 256 experts, top-8, expert intermediate 512
+    m, h, mi, E, top_k = 2048, 2048, 512, 256, 8
+    pairs = m * top_k
+    x = torch.randn(m, h, device=dev, generator=g).bfloat16()
+    wgu = (torch.randn(E * 2 * mi, h, device=dev, generator=g) * h**-0.5).bfloat16()
+    wd = (torch.randn(E * h, mi, device=dev, generator=g) * mi**-0.5).bfloat16()
+    scores = torch.randn(m, E, device=dev, generator=g).bfloat16()
+    route = torch.zeros(m, 2 * top_k, device=dev, dtype=torch.int32)
+    lst = torch.zeros(pairs, device=dev, dtype=torch.int32)
+    tiles = torch.zeros(1 + 3 * hb.lib().hb_moe_tiles(m, top_k, E, 16), device=dev, dtype=torch.int32)
+    ehb = torch.zeros(pairs, mi, device=dev, dtype=torch.bfloat16)
+    ey = torch.zeros(pairs, h, device=dev, dtype=torch.bfloat16)
+    egu = torch.zeros(pairs, 2 * mi, device=dev, dtype=torch.bfloat16)
+    xsb = torch.zeros(pairs, h, device=dev, dtype=torch.bfloat16)
+    outb = torch.zeros(m, h, device=dev, dtype=torch.bfloat16)
+    k_route = ctx.route(E, top_k)
+    k_route(m, wrap(scores), wrap(route))
+    ctx.sync()
+    pick = sel.experts(E, top_k, h, mi, m, wrap(route), wrap(lst), wrap(tiles), wrap(x), wrap(wgu), wrap(wd), wrap(ehb), wrap(ey), wrap(egu), wrap(xsb))
+    ops = [(k_route, m, wrap(scores), wrap(route)), (pick["sort"], m, wrap(route), wrap(lst), wrap(tiles))]
+    if pick["gather"]:
+        ops += [(pick["gather"], m, wrap(x), wrap(lst), wrap(xsb)), (pick["gate_up"], m, wrap(wgu), wrap(xsb), wrap(ehb), wrap(lst), wrap(tiles))]
+    elif pick["swiglu"]:
+        ops += [(pick["gate_up"], m, wrap(wgu), wrap(x), wrap(egu), wrap(lst), wrap(tiles)), (pick["swiglu"], pairs, wrap(egu), wrap(ehb))]
+    else:
+        ops += [(pick["gate_up"], m, wrap(wgu), wrap(x), wrap(ehb), wrap(lst), wrap(tiles))]
+    ops += [(pick["down"], m, wrap(wd), wrap(ehb), wrap(ey), wrap(lst), wrap(tiles)), (ctx.moe_combine(h, top_k), m, wrap(ey), wrap(route), wrap(outb))]
+    ctx.time(ops, 3)
+    barrier()
+    sec = max_over_ranks(ctx.time(ops, 20) / 20)
+    wbytes = 2.0 * E * (2 * mi * h + h * mi)
+    flop = 2.0 * pairs * (2 * mi) * h + 2.0 * pairs * h * mi
+    per_kernel = {}
+    for op in ops:
+        per_kernel[op[0].name] = ctx.time([op], 20) / 20 * 1e6
+    out["moe_2048tok_256e_top8"] = {"us": sec * 1e6, "tile_rows": pick["bm"], "weight_gbs": wbytes / sec / 1e9, "frac_hbm": wbytes / sec / 1e9 / pk["hbm_gbs"],
+                                    "tflops": flop / sec / 1e12, "us_per_kernel": per_kernel}
+    return out
+
+
+def cpu_baseline():
+    """The oracle's f32-accumulate contract kernel on the host cores, on a bounded sample: BASELINE config 1
+    (M=512, K=1024, N=4096) repeated, and one matvec pass; about 10-20 s in all."""
+    import numpy as np
+
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    from oracle_lib import Oracle
+
+    o = Oracle(native=True)
+    rng = np.random.default_rng(0)
+
+    def bf16(a):
+        b = a.astype(np.float32).view(np.uint32)
+        return ((b + 0x7FFF + ((b >> 16) & 1)) >> 16).astype(np.uint16)
+
+    rows = 128
+    ws = [bf16(rng.standard_normal((n, k), dtype=np.float32) * k**-0.5) for _, k, n, _ in LAYER]
+    xs = [bf16(rng.standard_normal((rows, k), dtype=np.float32)) for _, k, _, _ in LAYER]
+    y0 = bf16(rng.standard_normal((rows, HIDDEN), dtype=np.float32))
+
+    def step():
+        for (name, k, n, out), w, x in zip(LAYER, ws, xs):
+            o.gemm_f32(x, w, out, y0 if out == 2 else None)
+
+    step()
+    t0 = time.perf_counter()
+    reps = 0
+    while time.perf_counter() - t0 < 10.0 and reps < 50:
+        step()
+        reps += 1
+    dt = (time.perf_counter() - t0) / reps
+    value = STEP_FLOP * rows / ROWS / dt / 1e12
+    return {"value": value, "unit": "TFLOP/s", "cores": o.threads(), "kind": "port",
+            "sample": f"{rows} of {ROWS} rows of every GEMM of the layer set, {reps} passes, f32 accumulate + one RNE (oracle/hb_oracle.c, OpenMP)"}
+
+
+if __name__ == "__main__":
+    main()

@@ -162,56 +162,58 @@ void hbo_gemm_f64(const uint16_t* x, const uint16_t* w, void* y, int m, int n, i
     hbo_gemm_f64_rows(x, w, y, NULL, m, n, k, out);
 }
 
-/* f32-accumulate contract kernel: operands widened once, 4x4 register block,
- * the k loop left to the compiler's vectoriser (partial sums per SIMD lane,
- * folded at the end: an accumulation order, as every GPU kernel has its own). */
+/* f32-accumulate contract kernel (the timed CPU baseline): X widened once, four W rows widened
+ * per step into a thread-local buffer and reused over every X row, 4x4 register block, the k loop
+ * left to the compiler's vectoriser (partial sums per SIMD lane, folded at the end: an
+ * accumulation order, as every GPU kernel has its own). */
 static void widen(const uint16_t* s, float* d, size_t count) {
-#pragma omp parallel for schedule(static)
     for (size_t i = 0; i < count; ++i) d[i] = hbo_bf16_to_f32(s[i]);
 }
 
 void hbo_gemm_f32(const uint16_t* x, const uint16_t* w, void* y, int m, int n, int k, int out) {
     float* xf = (float*)malloc((size_t)m * k * sizeof(float));
-    float* wf = (float*)malloc((size_t)n * k * sizeof(float));
-    widen(x, xf, (size_t)m * k);
-    widen(w, wf, (size_t)n * k);
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < m; ++r) widen(x + (size_t)r * k, xf + (size_t)r * k, (size_t)k);
     int nout = out == HBO_OUT_SWIGLU ? n / 2 : n;
     float* acc_all = NULL;
     if (out == HBO_OUT_SWIGLU) acc_all = (float*)malloc((size_t)m * n * sizeof(float));
     int nb = (n + 3) / 4;
-#pragma omp parallel for schedule(dynamic, 8)
-    for (int cb = 0; cb < nb; ++cb) {
-        int c0 = cb * 4;
-        int cn = n - c0 < 4 ? n - c0 : 4;
-        const float* w0 = wf + (size_t)c0 * k;
-        const float* w1 = wf + (size_t)(c0 + (cn > 1 ? 1 : 0)) * k;
-        const float* w2 = wf + (size_t)(c0 + (cn > 2 ? 2 : 0)) * k;
-        const float* w3 = wf + (size_t)(c0 + (cn > 3 ? 3 : 0)) * k;
-        for (int r0 = 0; r0 < m; r0 += 4) {
-            int rn = m - r0 < 4 ? m - r0 : 4;
-            const float* x0 = xf + (size_t)r0 * k;
-            const float* x1 = xf + (size_t)(r0 + (rn > 1 ? 1 : 0)) * k;
-            const float* x2 = xf + (size_t)(r0 + (rn > 2 ? 2 : 0)) * k;
-            const float* x3 = xf + (size_t)(r0 + (rn > 3 ? 3 : 0)) * k;
-            float a00 = 0, a01 = 0, a02 = 0, a03 = 0, a10 = 0, a11 = 0, a12 = 0, a13 = 0;
-            float a20 = 0, a21 = 0, a22 = 0, a23 = 0, a30 = 0, a31 = 0, a32 = 0, a33 = 0;
+#pragma omp parallel
+    {
+        float* wf = (float*)malloc((size_t)4 * k * sizeof(float));
+#pragma omp for schedule(dynamic, 8)
+        for (int cb = 0; cb < nb; ++cb) {
+            int c0 = cb * 4;
+            int cn = n - c0 < 4 ? n - c0 : 4;
+            for (int j = 0; j < 4; ++j) widen(w + (size_t)(c0 + (j < cn ? j : 0)) * k, wf + (size_t)j * k, (size_t)k);
+            const float *w0 = wf, *w1 = wf + k, *w2 = wf + 2 * (size_t)k, *w3 = wf + 3 * (size_t)k;
+            for (int r0 = 0; r0 < m; r0 += 4) {
+                int rn = m - r0 < 4 ? m - r0 : 4;
+                const float* x0 = xf + (size_t)r0 * k;
+                const float* x1 = xf + (size_t)(r0 + (rn > 1 ? 1 : 0)) * k;
+                const float* x2 = xf + (size_t)(r0 + (rn > 2 ? 2 : 0)) * k;
+                const float* x3 = xf + (size_t)(r0 + (rn > 3 ? 3 : 0)) * k;
+                float a00 = 0, a01 = 0, a02 = 0, a03 = 0, a10 = 0, a11 = 0, a12 = 0, a13 = 0;
+                float a20 = 0, a21 = 0, a22 = 0, a23 = 0, a30 = 0, a31 = 0, a32 = 0, a33 = 0;
 #pragma omp simd reduction(+ : a00, a01, a02, a03, a10, a11, a12, a13, a20, a21, a22, a23, a30, a31, a32, a33)
-            for (int i = 0; i < k; ++i) {
-                float b0 = w0[i], b1 = w1[i], b2 = w2[i], b3 = w3[i];
-                float v0 = x0[i], v1 = x1[i], v2 = x2[i], v3 = x3[i];
-                a00 += v0 * b0; a01 += v0 * b1; a02 += v0 * b2; a03 += v0 * b3;
-                a10 += v1 * b0; a11 += v1 * b1; a12 += v1 * b2; a13 += v1 * b3;
-                a20 += v2 * b0; a21 += v2 * b1; a22 += v2 * b2; a23 += v2 * b3;
-                a30 += v3 * b0; a31 += v3 * b1; a32 += v3 * b2; a33 += v3 * b3;
-            }
-            float a[4][4] = {{a00, a01, a02, a03}, {a10, a11, a12, a13}, {a20, a21, a22, a23}, {a30, a31, a32, a33}};
-            for (int i = 0; i < rn; ++i)
-                for (int j = 0; j < cn; ++j) {
-                    size_t at = (size_t)(r0 + i) * n + (c0 + j);
-                    if (out == HBO_OUT_SWIGLU) acc_all[at] = a[i][j];
-                    else store_out(y, at, a[i][j], out);
+                for (int i = 0; i < k; ++i) {
+                    float b0 = w0[i], b1 = w1[i], b2 = w2[i], b3 = w3[i];
+                    float v0 = x0[i], v1 = x1[i], v2 = x2[i], v3 = x3[i];
+                    a00 += v0 * b0; a01 += v0 * b1; a02 += v0 * b2; a03 += v0 * b3;
+                    a10 += v1 * b0; a11 += v1 * b1; a12 += v1 * b2; a13 += v1 * b3;
+                    a20 += v2 * b0; a21 += v2 * b1; a22 += v2 * b2; a23 += v2 * b3;
+                    a30 += v3 * b0; a31 += v3 * b1; a32 += v3 * b2; a33 += v3 * b3;
                 }
+                float a[4][4] = {{a00, a01, a02, a03}, {a10, a11, a12, a13}, {a20, a21, a22, a23}, {a30, a31, a32, a33}};
+                for (int i = 0; i < rn; ++i)
+                    for (int j = 0; j < cn; ++j) {
+                        size_t at = (size_t)(r0 + i) * n + (c0 + j);
+                        if (out == HBO_OUT_SWIGLU) acc_all[at] = a[i][j];
+                        else store_out(y, at, a[i][j], out);
+                    }
+            }
         }
+        free(wf);
     }
     if (out == HBO_OUT_SWIGLU) {
 #pragma omp parallel for schedule(static)
@@ -224,7 +226,6 @@ void hbo_gemm_f32(const uint16_t* x, const uint16_t* w, void* y, int m, int n, i
         free(acc_all);
     }
     free(xf);
-    free(wf);
 }
 
 /* kernels.rs:146-214 with a 32-lane simdgroup: lane l takes chunks l, l+32, ..

@@ -1,0 +1,340 @@
+"""Generates tests/golden/golden.npz: known-answer vectors for the matrix-multiply path.
+
+The reference (herbert-metal-bf16) holds no fixture for this path and its kernels cannot run off
+an Apple GPU, so these vectors come from an INDEPENDENT restatement of its rules in numpy /
+pure Python (this file), written from the reference source:
+  * round to nearest even f32 -> bf16        src/core/bf16.rs:13-23
+  * epilogues Bf16 / F32 / Residual / Swiglu  src/metal/kernels.rs:30-42,217-234; prefill.rs:2790-2818
+  * route (softmax, top-k, renormalise)       src/metal/qwen_kernels.rs:1802-1878
+  * sort and tile table                       src/metal/prefill.rs:1303-1442
+  * combine                                   src/metal/qwen_kernels.rs:2119-2161
+  * check rule                                src/metal/qwen.rs:2519-2531
+  * input generators                          src/metal/qwen.rs:2613-2626; src/bin/herbert-metal-probe.rs:435-462
+The C oracle (oracle/hb_oracle.c) is tested against this file's output; the two share no code.
+
+    python tests/golden/make_golden.py
+"""
+import os
+import struct
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def f32_bits(x):
+    return struct.unpack("<I", struct.pack("<f", float(x)))[0]
+
+
+def bits_f32(b):
+    return struct.unpack("<f", struct.pack("<I", b & 0xFFFFFFFF))[0]
+
+
+def rne_bf16(x):
+    """bits>>16, +1 when the round bit is set and (sticky != 0 or the kept lsb is 1)."""
+    bits = f32_bits(np.float32(x))
+    lsb, rnd, sticky = (bits >> 16) & 1, (bits >> 15) & 1, bits & 0x7FFF
+    r = bits >> 16
+    if rnd == 1 and (sticky != 0 or lsb == 1):
+        r += 1
+    return r & 0xFFFF
+
+
+def widen(h):
+    return np.float32(bits_f32(int(h) << 16))
+
+
+def rne_bf16_array(a):
+    return np.array([rne_bf16(v) for v in np.asarray(a, dtype=np.float32).ravel()], dtype=np.uint16).reshape(np.shape(a))
+
+
+def widen_array(a):
+    return (np.asarray(a, dtype=np.uint16).astype(np.uint32) << 16).view(np.float32)
+
+
+def exp_f32(x):
+    """The contract's exp: a fixed sequence of f32 operations (see oracle/hb_oracle.h)."""
+    f = np.float32
+    x = f(x)
+    if x > f(88.72283):
+        return f(np.inf)
+    if x < f(-103.98):
+        return f(0.0)
+
+    def fma(a, b, c):  # exact product and sum in float64 (24x24-bit product fits), one rounding to f32
+        # a*b is exact in f64; adding c may round in f64 before the f32 rounding: use integers of the
+        # exact rational instead.
+        from fractions import Fraction
+
+        v = Fraction(float(a)) * Fraction(float(b)) + Fraction(float(c))
+        return round_fraction_f32(v)
+
+    n = f(np.rint(f(x * f(1.44269504088896341))))
+    r = fma(n, f(-0.693359375), x)
+    r = fma(n, f(2.12194440e-4), r)
+    p = f(1.9875691500e-4)
+    for c in (1.3981999507e-3, 8.3334519073e-3, 4.1665795894e-2, 1.6666665459e-1, 5.0000001201e-1):
+        p = fma(p, r, f(c))
+    r2 = f(r * r)
+    p = fma(p, r2, r)
+    p = f(p + f(1.0))
+    k = int(n)
+    k1 = int(k / 2)  # C division truncates toward zero
+    k2 = k - k1
+    return f(f(p * f(2.0 ** k1)) * f(2.0 ** k2))
+
+
+def round_fraction_f32(v):
+    """A Fraction rounded to nearest-even f32 (normal range)."""
+    from fractions import Fraction
+
+    if v == 0:
+        return np.float32(0.0)
+    sign = -1 if v < 0 else 1
+    v = abs(v)
+    e = 0
+    while v >= 2:
+        v /= 2
+        e += 1
+    while v < 1:
+        v *= 2
+        e -= 1
+    scaled = v * (1 << 23)
+    q = int(scaled)
+    rem = scaled - q
+    if rem > Fraction(1, 2) or (rem == Fraction(1, 2) and (q & 1)):
+        q += 1
+    return np.float32(sign * q * 2.0 ** (e - 23))
+
+
+def sigmoid_f32(x):
+    f = np.float32
+    e = exp_f32(f(-x))
+    return f(f(1.0) / f(f(1.0) + e))
+
+
+def swiglu(gh, uh):
+    f = np.float32
+    g, u = widen(gh), widen(uh)
+    return rne_bf16(f(f(g * sigmoid_f32(g)) * u))
+
+
+def xorshift16(count, seed):
+    out = []
+    for _ in range(count):
+        seed ^= (seed << 13) & 0xFFFFFFFF
+        seed ^= seed >> 17
+        seed ^= (seed << 5) & 0xFFFFFFFF
+        out.append(rne_bf16(np.float32(np.float32(seed >> 8) / np.float32(1 << 23)) - np.float32(1.0)))
+    return np.array(out, dtype=np.uint16)
+
+
+def random16(count, seed):
+    out, s = [], seed
+    for _ in range(count):
+        s = (s * 6364136223846793005 + 1442695040888963407) & 0xFFFFFFFFFFFFFFFF
+        r = s >> 32
+        sign = r >> 31
+        e = 9 + ((r >> 24) & 7) % 6
+        out.append((sign << 15) | ((e + 112) << 7) | (r & 0x7F))
+    return np.array(out, dtype=np.uint16)
+
+
+def splitmix64(z):
+    z = (z + 0x9E3779B97F4A7C15) & 0xFFFFFFFFFFFFFFFF
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & 0xFFFFFFFFFFFFFFFF
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & 0xFFFFFFFFFFFFFFFF
+    return z ^ (z >> 31)
+
+
+def fill_normal(count, seed, tensor_id, sigma):
+    out = []
+    for i in range(count):
+        base = (seed ^ (tensor_id << 40) ^ i) & 0xFFFFFFFFFFFFFFFF
+        total = 0
+        for j in range(3):
+            u = splitmix64((base * 3 + j) & 0xFFFFFFFFFFFFFFFF)
+            total += (u & 0xFFFF) + ((u >> 16) & 0xFFFF) + ((u >> 32) & 0xFFFF) + ((u >> 48) & 0xFFFF)
+        z = (total - 393210.0) / 65536.0
+        out.append(rne_bf16(np.float32(z * sigma)))
+    return np.array(out, dtype=np.uint16)
+
+
+def gemm_f64(x, w, out, y0=None):
+    """Exact dot products (float64 of small-K bf16 inputs is exact enough to be order-free), one rounding."""
+    from fractions import Fraction
+
+    xf, wf = widen_array(x).astype(np.float64), widen_array(w).astype(np.float64)
+    m, n = x.shape[0], w.shape[0]
+    acc = [[sum(Fraction(a) * Fraction(b) for a, b in zip(xf[r], wf[c])) for c in range(n)] for r in range(m)]
+
+    def to_bf16(v):  # a Fraction rounded once to bf16 (8 significant bits)
+        if v == 0:
+            return 0
+        sign = 0x8000 if v < 0 else 0
+        v = abs(v)
+        e = 0
+        while v >= 2:
+            v /= 2
+            e += 1
+        while v < 1:
+            v *= 2
+            e -= 1
+        scaled = v * 128
+        q = int(scaled)
+        rem = scaled - q
+        if rem > Fraction(1, 2) or (rem == Fraction(1, 2) and (q & 1)):
+            q += 1
+        if q == 256:
+            q, e = 128, e + 1
+        return sign | ((e + 127) << 7) | (q - 128)
+
+    if out == "f32":
+        return np.array([[round_fraction_f32(v) for v in row] for row in acc], dtype=np.float32)
+    b = np.array([[to_bf16(v) for v in row] for row in acc], dtype=np.uint16)
+    if out == "bf16":
+        return b
+    if out == "residual":
+        return rne_bf16_array(widen_array(y0) + widen_array(b))
+    if out == "swiglu":
+        half = n // 2
+        return np.array([[swiglu(b[r, c], b[r, half + c]) for c in range(half)] for r in range(m)], dtype=np.uint16)
+    raise ValueError(out)
+
+
+def butterfly_sum(v):
+    a = [np.float32(t) for t in v]
+    for off in (16, 8, 4, 2, 1):
+        a = [np.float32(a[i] + a[i ^ off]) for i in range(32)]
+    return a[0]
+
+
+def route_topk(scores, top_k):
+    f = np.float32
+    rows, experts = scores.shape
+    out = np.zeros((rows, 2 * top_k), dtype=np.uint32)
+    for r in range(rows):
+        s = [widen(h) for h in scores[r]]
+        mx = max(s)
+        ex = [exp_f32(f(v - mx)) for v in s]
+        total = butterfly_sum(ex[0:32])
+        for g in range(1, experts // 32):
+            total = f(total + butterfly_sum(ex[32 * g : 32 * g + 32]))
+        p = [f(e / total) for e in ex]
+        chosen, vals = [], []
+        for _ in range(top_k):
+            best, idx = f(-2.0), 0
+            for e in range(experts):
+                if p[e] > best:
+                    best, idx = p[e], e
+            p[idx] = f(-1.0)
+            chosen.append(idx)
+            vals.append(best)
+        tot = f(0.0)
+        for v in vals:
+            tot = f(tot + v)
+        for i in range(top_k):
+            w = widen(rne_bf16(f(vals[i] / tot)))
+            rank = sum(1 for j in range(top_k) if j != i and chosen[j] < chosen[i])
+            out[r, rank] = chosen[i]
+            out[r, top_k + rank] = f32_bits(w)
+    return out
+
+
+def moe_sort(route, experts, top_k, bm):
+    rows = route.shape[0]
+    pairs = [(int(route[i // top_k, i % top_k]), i) for i in range(rows * top_k)]
+    lst, tiles = [], []
+    for e in range(experts):
+        mine = [i for (x, i) in pairs if x == e]
+        start = len(lst)
+        for j in range(0, len(mine), bm):
+            tiles.append((e, start + j, min(bm, len(mine) - j)))
+        lst.extend(mine)
+    table = [len(tiles)] + [v for t in tiles for v in t]
+    return np.array(lst, dtype=np.uint32), np.array(table, dtype=np.uint32)
+
+
+def moe_combine(ey, route, top_k):
+    f = np.float32
+    rows, d = route.shape[0], ey.shape[1]
+    out = np.zeros((rows, d), dtype=np.uint16)
+    for r in range(rows):
+        for i in range(d):
+            acc = f(0.0)
+            for s in range(top_k):
+                y = widen(ey[r * top_k + s, i])
+                w = f(bits_f32(int(route[r, top_k + s])))
+                c = widen(rne_bf16(f(y * w)))
+                acc = widen(rne_bf16(f(acc + c)))
+            out[r, i] = rne_bf16(acc)
+    return out
+
+
+def main():
+    g = {}
+    # RNE known answers: (f32 bits, bf16 bits) - ties to even, carries, signed zero, subnormal, infinity.
+    rne_in = [0x3F800000, 0x3F808000, 0x3F818000, 0x3F808001, 0x3F807FFF, 0x3FFF8000, 0x7F7F8000, 0x00000000, 0x80000000,
+              0x00008000, 0x00018000, 0x7F800000, 0xFF800000, 0x3F7FFFFF, 0xC0490FDB, 0x477FE000, 0x33800000]
+    g["rne_in"] = np.array(rne_in, dtype=np.uint32)
+    g["rne_out"] = np.array([rne_bf16(bits_f32(b)) for b in rne_in], dtype=np.uint16)
+    assert list(g["rne_out"][:7]) == [0x3F80, 0x3F80, 0x3F82, 0x3F81, 0x3F80, 0x4000, 0x7F80]
+    # exp and SwiGLU
+    xs = np.array([-20.0, -5.5, -1.0, -0.3465, 0.0, 1e-3, 0.5, 1.0, 3.25, 10.0, 44.4, 88.0, -87.0, -100.0], dtype=np.float32)
+    g["exp_in"] = xs
+    g["exp_out"] = np.array([exp_f32(v) for v in xs], dtype=np.float32)
+    gh = fill_normal(64, 11, 1, 2.0)
+    uh = fill_normal(64, 11, 2, 1.5)
+    g["swiglu_g"], g["swiglu_u"] = gh, uh
+    g["swiglu_out"] = np.array([swiglu(a, b) for a, b in zip(gh, uh)], dtype=np.uint16)
+    # generators
+    g["xorshift16_9e3779b9"] = xorshift16(64, 0x9E3779B9)
+    g["random16_1"] = random16(64, 1)
+    g["normal_x"] = fill_normal(96, 0x9E3779B9, 1, 1.0)
+    g["normal_w"] = fill_normal(96, 0x2545F491, 2, 1.0 / 32.0)
+    # a small GEMM in the four output modes (exact rational dot products)
+    m, n, k = 5, 12, 40
+    x = fill_normal(m * k, 0x9E3779B9, 1, 1.0).reshape(m, k)
+    w = fill_normal(n * k, 0x2545F491, 2, k ** -0.5).reshape(n, k)
+    y0 = fill_normal(m * n, 0x85EBCA6B, 5, 1.0).reshape(m, n)
+    g["gemm_x"], g["gemm_w"], g["gemm_y0"] = x, w, y0
+    g["gemm_bf16"] = gemm_f64(x, w, "bf16")
+    g["gemm_f32"] = gemm_f64(x, w, "f32")
+    g["gemm_residual"] = gemm_f64(x, w, "residual", y0)
+    g["gemm_swiglu"] = gemm_f64(x, w, "swiglu")
+    # MoE: route, sort (three tile sizes), combine
+    rows, experts, top_k, d = 6, 64, 4, 16
+    scores = fill_normal(rows * experts, 0xC2B2AE35, 3, 1.0).reshape(rows, experts)
+    scores[1, 5] = scores[1, 9]  # exact ties: the lowest index must win
+    scores[1, 40] = scores[1, 9]
+    route = route_topk(scores, top_k)
+    g["route_scores"], g["route_out"] = scores, route
+    for bm in (16, 32, 64):
+        # a skewed route so that one expert spans several tiles
+        skew = route.copy()
+        lst, table = moe_sort(skew, experts, top_k, bm)
+        g[f"sort_list_{bm}"], g[f"sort_tiles_{bm}"] = lst, table
+    big = np.zeros((40, 2 * 2), dtype=np.uint32)  # 40 rows, top_k 2: expert 3 gets every row, expert 0 or 7 the other slot
+    for r in range(40):
+        big[r, 0], big[r, 1] = (0, 3) if r % 3 else (3, 7)
+    g["sort_big_route"] = big
+    for bm in (16, 32, 64):
+        lst, table = moe_sort(big, 8, 2, bm)
+        g[f"sort_big_list_{bm}"], g[f"sort_big_tiles_{bm}"] = lst, table
+    ey = fill_normal(rows * top_k * d, 0x85EBCA6B, 9, 1.0).reshape(rows * top_k, d)
+    g["combine_ey"] = ey
+    g["combine_out"] = moe_combine(ey, route, top_k)
+    # check rule
+    ref = widen_array(fill_normal(256, 5, 1, 1.0)).astype(np.float32)
+    scale = np.abs(ref).max()
+    ok = ref.copy()
+    ok[17] += scale / 64.0 * 0.99
+    bad = ref.copy()
+    bad[17] += scale / 64.0 * 1.02
+    g["check_ref"], g["check_ok"], g["check_bad"] = ref, ok, bad
+    np.savez_compressed(os.path.join(HERE, "golden.npz"), **g)
+    print("wrote", os.path.join(HERE, "golden.npz"), "with", len(g), "arrays")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,77 @@
+"""Parity of the decode matvec (M = 1..8) with the f64-accumulated oracle, through the C ABI."""
+import numpy as np
+import pytest
+
+from gpu_util import gemm_inputs, out_buffer, within_contract
+from oracle_lib import OUT_BF16, OUT_F32, OUT_RESIDUAL, OUT_SWIGLU
+
+pytestmark = pytest.mark.gpu
+
+
+def run(ctx, oracle, m, k, n, out, **form):
+    x, w, y0 = gemm_inputs(oracle, m, k, n)
+    d_x, d_w = ctx.to_device(x), ctx.to_device(w)
+    d_y, dtype, shape = out_buffer(ctx, out, m, n, y0)
+    kern = ctx.matvec(k, n, out, rows_max=m, **form)
+    kern(m, d_w, d_x, d_y)
+    ctx.sync()
+    return kern, oracle.gemm_f64(x, w, out, y0), d_y.download(dtype, shape)
+
+
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 5, 8])
+@pytest.mark.parametrize("out", [OUT_BF16, OUT_F32, OUT_RESIDUAL, OUT_SWIGLU])
+def test_every_form(ctx, oracle, m, out):
+    k, n = 1024, 328  # n is a multiple of no row group, so the last group is ragged
+    for rpw in (1, 2, 4, 8):
+        for split in (1, 2, 4):
+            for persist in (0, 1):
+                if out == OUT_SWIGLU and rpw == 1:
+                    continue
+                kern, want, got = run(ctx, oracle, m, k, n, out, rows_per_warp=rpw, split=split, persist=persist)
+                within_contract(oracle, want, got, f"{kern.name} m={m}")
+
+
+def test_m1_equals_reference_lane_order_closely(ctx, oracle):
+    # M = 1 against the reference's own order of operations (32 lanes striding K by chunks of 8,
+    # butterfly sum): the same sums up to the association of the lane fold
+    k, n = 4096, 512
+    x, w, _ = gemm_inputs(oracle, 1, k, n)
+    d_x, d_w, d_y = ctx.to_device(x), ctx.to_device(w), ctx.alloc(n * 2)
+    ctx.matvec(k, n, OUT_BF16, rows_max=1, rows_per_warp=1)(1, d_w, d_x, d_y)
+    ctx.sync()
+    got = d_y.download(np.uint16, (n,))
+    assert np.array_equal(got, oracle.matvec_ref_order(x, w))  # same lane striding, same butterfly: same bits
+
+
+@pytest.mark.parametrize("m", [1, 4, 8])
+def test_config2_shapes(ctx, oracle, m):
+    # BASELINE config 2: K=4096, N=12288 (and the LM-head-like N=151936 on a row sample of W)
+    k, n = 4096, 12288
+    kern, want, got = run(ctx, oracle, m, k, n, OUT_BF16, rows_per_warp=4)
+    within_contract(oracle, want, got, f"{kern.name} m={m}")
+
+
+def test_lm_head_shape(ctx, oracle):
+    k, n, m = 4096, 151936, 4
+    x = oracle.normal((m, k), 1, 1, 1.0)
+    w = oracle.normal((n, k), 2, 2, k**-0.5)
+    d_x, d_w, d_y = ctx.to_device(x), ctx.to_device(w), ctx.alloc(m * n * 2)
+    kern = ctx.matvec(k, n, OUT_BF16, rows_max=m, rows_per_warp=4)
+    kern(m, d_w, d_x, d_y)
+    ctx.sync()
+    got = d_y.download(np.uint16, (m, n))
+    cols = np.concatenate([np.arange(0, 4096), np.arange(n - 4096, n), np.random.default_rng(0).integers(0, n, 8192)])
+    want = oracle.gemm_f64(x, np.ascontiguousarray(w[cols]))
+    within_contract(oracle, want, np.ascontiguousarray(got[:, cols]), kern.name)
+
+
+def test_k_multiple_of_8_only_and_unsupported(ctx, oracle, hb200):
+    kern, want, got = run(ctx, oracle, 2, 72, 40, OUT_BF16, rows_per_warp=2, split=2)
+    within_contract(oracle, want, got, kern.name)
+    with pytest.raises(hb200.HbError) as e:
+        ctx.matvec(100, 64)  # K = 100 is not a multiple of 8 (reference: kernels.rs:147)
+    assert e.value.status == hb200.UNSUPPORTED
+    with pytest.raises(hb200.HbError):
+        ctx.matvec(64, 64, rows_max=9)
+    with pytest.raises(hb200.HbError):
+        ctx.matvec(64, 64, OUT_SWIGLU, rows_per_warp=1)
