@@ -171,10 +171,16 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the matvec / MoE / tensor-parallel sections")
+    ap.add_argument("--tune", default="", help="engine tune keys, e.g. gemm.auto=0 to skip the load-time timing")
+    ap.add_argument("--case", default="", choices=["", "gate_up", "down", "matvec", "matvec8", "moe"],
+                    help="run one small case of one kernel a few times and exit (the command profiled under ncu)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)
+        return
+    if args.case:
+        run_case(args)
         return
 
     import numpy as np
@@ -223,7 +229,7 @@ def main():
     gu_scratch = torch.zeros(ROWS, 2 * INTER, device=dev, dtype=torch.bfloat16)
     torch.cuda.synchronize()
 
-    tune = hb.Tune("")
+    tune = hb.Tune(args.tune)
     sel = hb.Selector(ctx, tune)
     t_sel = time.perf_counter()
     k_qkv = sel.gemm(HIDDEN, 6144, 0, wrap(weights[0]), wrap(x), wrap(qkv), ROWS)
@@ -310,6 +316,70 @@ def main():
     ctx.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_case(args):
+    """One kernel on one case, a handful of launches, a few hundred MB to 1.3 GB on the device (operands larger
+    than L2): the command an ncu capture runs. Prints the case's CUDA-event time."""
+    import torch
+
+    from __graft_entry__ import load_package
+
+    hb = load_package()
+    dev = torch.device("cuda", 0)
+    ctx = hb.Context(0)
+    g = torch.Generator(device=dev)
+    g.manual_seed(7)
+
+    def wrap(t):
+        return ctx.wrap(t.data_ptr(), t.numel() * t.element_size())
+
+    def rnd(*shape, scale=1.0):
+        return (torch.randn(*shape, device=dev, generator=g) * scale).bfloat16()
+
+    reps = 5
+    if args.case in ("gate_up", "down"):
+        k, n, out = (HIDDEN, 2 * INTER, 3) if args.case == "gate_up" else (INTER, HIDDEN, 2)
+        w, x = rnd(n, k, scale=k**-0.5), rnd(ROWS, k)
+        y = rnd(ROWS, n // 2 if out == 3 else n)
+        torch.cuda.synchronize()
+        kern = ctx.gemm(k, n, out, rows_max=ROWS)
+        ops = [(kern, ROWS, wrap(w), wrap(x), wrap(y))]
+        work = {"flop": 2.0 * ROWS * k * n}
+    elif args.case in ("matvec", "matvec8"):
+        m = 1 if args.case == "matvec" else 8
+        k, n = 4096, 151936
+        w, x = rnd(n, k, scale=k**-0.5), rnd(8, k)
+        y = torch.zeros(8, n, device=dev, dtype=torch.bfloat16)
+        torch.cuda.synchronize()
+        kern = ctx.matvec(k, n, 0, rows_max=m, rows_per_warp=2 if m == 1 else 4, split=2 if m == 1 else 1)
+        ops = [(kern, m, wrap(w), wrap(x), wrap(y))]
+        work = {"bytes": 2.0 * (n * k + m * k + m * n)}
+    else:
+        m, h, mi, E, top_k, bm = 2048, 2048, 512, 256, 8, 64
+        pairs = m * top_k
+        x, wgu, wd = rnd(m, h), rnd(E * 2 * mi, h, scale=h**-0.5), rnd(E * h, mi, scale=mi**-0.5)
+        scores = rnd(m, E)
+        route = torch.zeros(m, 2 * top_k, device=dev, dtype=torch.int32)
+        lst = torch.zeros(pairs, device=dev, dtype=torch.int32)
+        tiles = torch.zeros(1 + 3 * hb.lib().hb_moe_tiles(m, top_k, E, bm), device=dev, dtype=torch.int32)
+        ehb, ey, out = rnd(pairs, mi), rnd(pairs, h), rnd(m, h)
+        torch.cuda.synchronize()
+        kw = dict(rows_max=m, top_k=top_k, experts=E, bm=bm)
+        ops = [(ctx.route(E, top_k), m, wrap(scores), wrap(route)), (ctx.moe_sort(E, top_k, m, bm), m, wrap(route), wrap(lst), wrap(tiles)),
+               (ctx.gemm(h, 2 * mi, 3, rows_mode=hb.ROWS_GATHER, **kw), m, wrap(wgu), wrap(x), wrap(ehb), wrap(lst), wrap(tiles)),
+               (ctx.gemm(mi, h, 0, rows_mode=hb.ROWS_SCATTER, **kw), m, wrap(wd), wrap(ehb), wrap(ey), wrap(lst), wrap(tiles)),
+               (ctx.moe_combine(h, top_k), m, wrap(ey), wrap(route), wrap(out))]
+        work = {"bytes": 2.0 * E * 3 * mi * h}
+    ctx.time(ops, 2)
+    sec = ctx.time(ops, reps) / reps
+    line = {"case": args.case, "kernels": [o[0].name for o in ops], "us": sec * 1e6}
+    if "flop" in work:
+        line["tflops"] = work["flop"] / sec / 1e12
+    else:
+        line["gbs"] = work["bytes"] / sec / 1e9
+    print(json.dumps(line))
+    ctx.close()
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the GEMM kernel, averaged over the four launches of a
