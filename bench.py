@@ -296,6 +296,10 @@ def main():
             extra.update(bench_extra(hb, ctx, sel, torch, dev, wrap, pk, rank, world, barrier, max_over_ranks))
         except Exception as e:  # the headline stands on its own
             extra["error"] = repr(e)
+        try:
+            extra.update(bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks))
+        except Exception as e:
+            extra["sharded_error"] = repr(e)
 
     cpu = None
     if rank == 0 and world == 1:
@@ -460,6 +464,72 @@ def bench_extra(hb, ctx, sel, torch, dev, wrap, pk, rank, world, barrier, max_ov
         per_kernel[op[0].name] = ctx.time([op], 20) / 20 * 1e6
     out["moe_2048tok_256e_top8"] = {"us": sec * 1e6, "tile_rows": pick["bm"], "weight_gbs": wbytes / sec / 1e9, "frac_hbm": wbytes / sec / 1e9 / pk["hbm_gbs"],
                                     "tflops": flop / sec / 1e12, "us_per_kernel": per_kernel}
+    return out
+
+
+def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks):
+    """The two configurations that shard (strong scaling, total work fixed): the 27B-class FFN tensor-parallel
+    over `world` ranks (config 4) and the MoE block expert-parallel (config 5). At world = 1 the same code runs
+    without an exchange."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("hb200_dist", os.path.join(ROOT, "herbert-metal-bf16_b200", "dist.py"))
+    D = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(D)
+    out = {}
+    stream = torch.cuda.Stream(dev)
+    ctx.sync()
+    ctx.set_stream(stream.cuda_stream)
+    try:
+        with torch.cuda.stream(stream):
+            be = D.GpuBackend(hb, ctx, rows_max=2048)
+            g = torch.Generator(device=dev)
+            g.manual_seed(99)  # x, y and the router scores are the same on every rank
+            gl = torch.Generator(device=dev)
+            gl.manual_seed(1000 + rank)
+
+            def timed(fn, warm, reps):
+                for _ in range(warm):
+                    fn()
+                barrier()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for _ in range(reps):
+                    fn()
+                e1.record(stream)
+                e1.synchronize()
+                barrier()
+                return max_over_ranks(e0.elapsed_time(e1) * 1e-3 / reps)
+
+            # -- config 4: hidden 5120, intermediate 17408, M = 2048
+            m, h, inter = 2048, 5120, 17408
+            if inter % world == 0:
+                ip = inter // world
+                x = torch.randn(m, h, device=dev, generator=g).bfloat16()
+                y = torch.randn(m, h, device=dev, generator=g).bfloat16()
+                wgu_l = (torch.randn(2 * ip, h, device=dev, generator=gl) * h**-0.5).bfloat16()
+                wd_l = (torch.randn(h, ip, device=dev, generator=gl) * inter**-0.5).bfloat16()
+                sec = timed(lambda: D.tp_ffn(be, x, wgu_l, wd_l, y), 3, 10)
+                flop = 2.0 * m * (2 * inter) * h + 2.0 * m * h * inter
+                out["tp_ffn_27b_m2048"] = {"n_gpus": world, "us": sec * 1e6, "tflops_total": flop / sec / 1e12, "tflops_per_gpu": flop / sec / 1e12 / world,
+                                           "frac_of_measured_peak_per_gpu": flop / sec / 1e12 / world / pk["bf16_tflops"],
+                                           "allreduce_bytes": m * h * 4 if world > 1 else 0, "scaling": "strong"}
+                del wgu_l, wd_l
+            # -- config 5: 2048 tokens, hidden 2048, 256 experts, top-8, expert intermediate 512
+            m, h, mi, E, top_k, bm = 2048, 2048, 512, 256, 8, 64
+            if m % world == 0 and E % world == 0:
+                rl, epr = m // world, E // world
+                xs = torch.randn(m, h, device=dev, generator=g).bfloat16()[rank * rl : (rank + 1) * rl].contiguous()
+                sc = torch.randn(m, E, device=dev, generator=g).bfloat16()[rank * rl : (rank + 1) * rl].contiguous()
+                wgu_l = (torch.randn(epr * 2 * mi, h, device=dev, generator=gl) * h**-0.5).bfloat16()
+                wd_l = (torch.randn(epr * h, mi, device=dev, generator=gl) * mi**-0.5).bfloat16()
+                sec = timed(lambda: D.ep_moe(be, xs, sc, wgu_l, wd_l, E, top_k, mi, bm), 3, 10)
+                wbytes = 2.0 * E * 3 * mi * h
+                out["moe_ep_2048tok"] = {"n_gpus": world, "us": sec * 1e6, "weight_gbs_total": wbytes / sec / 1e9, "tokens_per_s": m / sec, "scaling": "strong",
+                                         "tile_rows": bm}
+    finally:
+        stream.synchronize()
+        ctx.set_stream(None)
     return out
 
 

@@ -44,68 +44,68 @@ __global__ void swiglu_rows_kernel(const uint16_t* __restrict__ gu, uint16_t* __
 // softmax of the bf16 scores in f32 (max, exp, sum = 32-lane butterfly sums folded warp by
 // warp in order, divide), top_k rounds of "largest value, lowest index on a tie", weights
 // p/sum(p_top) with the sum taken best-first, rounded to bf16, written in increasing expert order.
+// One warp per row: lane l holds experts l, 32 + l, 64 + l, ... so the butterfly over element g of every lane is
+// the 32-lane sum of experts [32g, 32g + 32) - the same partial sums, folded in the same order, as a block of
+// `experts` threads would make.
+constexpr int ROUTE_WARPS = 8;
 template <int MAXK>
-__global__ void route_topk_kernel(const uint16_t* __restrict__ scores, uint32_t* __restrict__ route, uint32_t experts, uint32_t top_k) {
-    __shared__ float red_v[33];
-    __shared__ uint32_t red_i[33];
-    __shared__ float vals[MAXK];
-    __shared__ uint32_t chosen[MAXK];
-    const uint32_t e = threadIdx.x, lane = e & 31, warp = e >> 5, warps = experts >> 5;
-    const uint32_t row = blockIdx.x;
-    const float s = bf16_to_f32(scores[(size_t)row * experts + e]);
-    // max
-    float mx = s;
+__global__ void __launch_bounds__(ROUTE_WARPS * 32) route_topk_kernel(const uint16_t* __restrict__ scores, uint32_t* __restrict__ route, uint32_t rows,
+                                                                      uint32_t experts, uint32_t top_k) {
+    __shared__ float vals_s[ROUTE_WARPS][MAXK];
+    __shared__ uint32_t chosen_s[ROUTE_WARPS][MAXK];
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t row = blockIdx.x * ROUTE_WARPS + warp;
+    if (row >= rows) return;
+    const uint32_t npl = experts >> 5;  // values per lane, <= 32
+    float* vals = vals_s[warp];
+    uint32_t* chosen = chosen_s[warp];
+    float p[32];
+    float mx = -3.4e38f;
+#pragma unroll
+    for (int g = 0; g < 32; ++g) {
+        p[g] = 0.f;
+        if ((uint32_t)g < npl) {
+            p[g] = bf16_to_f32(scores[(size_t)row * experts + 32 * g + lane]);
+            mx = fmaxf(mx, p[g]);
+        }
+    }
 #pragma unroll
     for (int off = 16; off >= 1; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
-    if (lane == 0) red_v[warp] = mx;
-    __syncthreads();
-    if (e == 0) {
-        float a = red_v[0];
-        for (uint32_t j = 1; j < warps; ++j) a = fmaxf(a, red_v[j]);
-        red_v[32] = a;
-    }
-    __syncthreads();
-    mx = red_v[32];
-    __syncthreads();
-    const float ex = exp_f32(__fsub_rn(s, mx));
-    float sum = ex;
+    float sum = 0.f;
 #pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) sum = __fadd_rn(sum, __shfl_xor_sync(0xffffffffu, sum, off));
-    if (lane == 0) red_v[warp] = sum;
-    __syncthreads();
-    if (e == 0) {
-        float a = red_v[0];
-        for (uint32_t j = 1; j < warps; ++j) a = __fadd_rn(a, red_v[j]);
-        red_v[32] = a;
+    for (int g = 0; g < 32; ++g) {
+        if ((uint32_t)g < npl) {
+            p[g] = exp_f32(__fsub_rn(p[g], mx));
+            float part = p[g];
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) part = __fadd_rn(part, __shfl_xor_sync(0xffffffffu, part, off));
+            sum = g == 0 ? part : __fadd_rn(sum, part);
+        }
     }
-    __syncthreads();
-    sum = red_v[32];
-    __syncthreads();
-    float p = __fdiv_rn(ex, sum);
+#pragma unroll
+    for (int g = 0; g < 32; ++g)
+        if ((uint32_t)g < npl) p[g] = __fdiv_rn(p[g], sum);
     for (uint32_t t = 0; t < top_k; ++t) {
-        float bv = p;
-        uint32_t bi = e;
+        float bv = p[0];
+        uint32_t bi = lane;
+#pragma unroll
+        for (int g = 1; g < 32; ++g)
+            if ((uint32_t)g < npl && p[g] > bv) { bv = p[g]; bi = 32 * g + lane; }  // strict >: the lowest index of a lane's ties
 #pragma unroll
         for (int off = 16; off >= 1; off >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, bv, off);
             const uint32_t oi = __shfl_xor_sync(0xffffffffu, bi, off);
             if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
         }
-        if (lane == 0) { red_v[warp] = bv; red_i[warp] = bi; }
-        __syncthreads();
-        if (e == 0) {
-            float a = red_v[0];
-            uint32_t ai = red_i[0];
-            for (uint32_t j = 1; j < warps; ++j)
-                if (red_v[j] > a) { a = red_v[j]; ai = red_i[j]; }  // warps are in index order: strict > keeps the lowest index
-            vals[t] = a;
-            chosen[t] = ai;
+        if (lane == 0) { vals[t] = bv; chosen[t] = bi; }
+        if ((bi & 31u) == lane) {
+#pragma unroll
+            for (int g = 0; g < 32; ++g)
+                if ((uint32_t)g == (bi >> 5)) p[g] = -1.0f;
         }
-        __syncthreads();
-        if (chosen[t] == e) p = -1.0f;
-        __syncthreads();
     }
-    if (e < top_k) {
+    __syncwarp();
+    for (uint32_t e = lane; e < top_k; e += 32) {
         float total = 0.0f;
         for (uint32_t j = 0; j < top_k; ++j) total = __fadd_rn(total, vals[j]);
         const float w = round_bf16(__fdiv_rn(vals[e], total));
@@ -130,19 +130,24 @@ constexpr int SORT_THREADS = 1024;
 constexpr int SORT_WARPS = SORT_THREADS / 32;
 
 __global__ void __launch_bounds__(SORT_THREADS) moe_sort_kernel(const uint32_t* __restrict__ route, uint32_t* __restrict__ list,
-                                                                uint32_t* __restrict__ tiles, uint32_t rows, uint32_t experts, uint32_t top_k, uint32_t bm) {
+                                                                uint32_t* __restrict__ tiles, uint32_t rows, uint32_t experts, uint32_t top_k, uint32_t bm, uint32_t staged) {
     extern __shared__ uint32_t sm[];
     uint32_t* cnt = sm;                          // [SORT_WARPS][experts]: pairs of expert e in warp w's segment, then running base
     uint32_t* off = sm + SORT_WARPS * experts;   // [experts]: first sorted row of expert e
     uint32_t* tstart = off + experts;            // [experts]: first tile of expert e
     uint32_t* scan = tstart + experts;           // [2][experts] scratch
+    uint16_t* ex16 = reinterpret_cast<uint16_t*>(scan + 2 * experts);  // [pairs] when `staged`
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t pairs = rows * top_k;
     const uint32_t seg = ((pairs + SORT_WARPS - 1) / SORT_WARPS + 31) / 32 * 32;
     const uint32_t s0 = min(pairs, warp * seg), s1 = min(pairs, s0 + seg);
     for (uint32_t i = tid; i < SORT_WARPS * experts; i += SORT_THREADS) cnt[i] = 0;
+    // The ordered passes below are chains of dependent steps; with the experts staged here first (all loads in
+    // flight at once) they touch shared memory only.
+    if (staged)
+        for (uint32_t i = tid; i < pairs; i += SORT_THREADS) ex16[i] = (uint16_t)route[(size_t)(i / top_k) * 2 * top_k + (i % top_k)];
     __syncthreads();
-    auto expert_of = [&](uint32_t i) { return route[(size_t)(i / top_k) * 2 * top_k + (i % top_k)]; };
+    auto expert_of = [&](uint32_t i) -> uint32_t { return staged ? (uint32_t)ex16[i] : route[(size_t)(i / top_k) * 2 * top_k + (i % top_k)]; };
     // pass 1: per-warp histograms
     for (uint32_t b = s0; b < s1; b += 32) {
         const uint32_t i = b + lane;
@@ -282,7 +287,8 @@ struct Route : hb_kernel {
         if (na != 2) return fail(ctx, HB_INVALID, name + ": bindings are scores, route");
         if (m == 0) return fail(ctx, HB_INVALID, name + ": m = 0");
         if (!range_ok(a[0], (size_t)m * experts * 2) || !range_ok(a[1], (size_t)m * 2 * top_k * 4)) return fail(ctx, HB_INVALID, name + ": a bound range is too small");
-        route_topk_kernel<64><<<m, experts, 0, ctx->stream>>>(static_cast<const uint16_t*>(a[0].ptr), static_cast<uint32_t*>(a[1].ptr), experts, top_k);
+        route_topk_kernel<64><<<(m + ROUTE_WARPS - 1) / ROUTE_WARPS, ROUTE_WARPS * 32, 0, ctx->stream>>>(static_cast<const uint16_t*>(a[0].ptr), static_cast<uint32_t*>(a[1].ptr), m,
+                                                                                                    experts, top_k);
         HB_CUDA(ctx, cudaGetLastError());
         ctx->launches++;
         return HB_OK;
@@ -290,7 +296,7 @@ struct Route : hb_kernel {
 };
 
 struct MoeSort : hb_kernel {
-    uint32_t experts = 0, top_k = 0, rows_max = 0, bm = 0;
+    uint32_t experts = 0, top_k = 0, rows_max = 0, bm = 0, staged = 0;
     size_t smem = 0;
     int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
         if (na != 3) return fail(ctx, HB_INVALID, name + ": bindings are route, list, tiles");
@@ -299,7 +305,7 @@ struct MoeSort : hb_kernel {
         if (!range_ok(a[0], (size_t)m * 2 * top_k * 4) || !range_ok(a[1], (size_t)m * top_k * 4) || !range_ok(a[2], tiles_words * 4))
             return fail(ctx, HB_INVALID, name + ": a bound range is too small");
         moe_sort_kernel<<<1, SORT_THREADS, smem, ctx->stream>>>(static_cast<const uint32_t*>(a[0].ptr), static_cast<uint32_t*>(a[1].ptr), static_cast<uint32_t*>(a[2].ptr), m,
-                                                               experts, top_k, bm);
+                                                               experts, top_k, bm, staged);
         HB_CUDA(ctx, cudaGetLastError());
         ctx->launches++;
         return HB_OK;
@@ -381,6 +387,11 @@ int make_moe_sort(hb_ctx* ctx, uint32_t experts, uint32_t top_k, uint32_t rows_m
     k->rows_max = rows_max;
     k->bm = bm;
     k->smem = ((size_t)SORT_WARPS * experts + 4 * (size_t)experts) * sizeof(uint32_t);
+    const size_t stage_bytes = ((size_t)rows_max * top_k * 2 + 15) / 16 * 16;
+    if (k->smem + stage_bytes <= 200 * 1024) {  // the experts of every pair fit beside the counters
+        k->staged = 1;
+        k->smem += stage_bytes;
+    }
     k->kind = 5;
     k->nargs = 3;
     k->name = "moe_sort_" + std::to_string(experts) + "_k" + std::to_string(top_k) + "_r" + std::to_string(rows_max) + "_m" + std::to_string(bm);
@@ -388,8 +399,8 @@ int make_moe_sort(hb_ctx* ctx, uint32_t experts, uint32_t top_k, uint32_t rows_m
         *out = have;
         return HB_OK;
     }
-    if (k->smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(moe_sort_kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)k->smem);
+    {
+        cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(moe_sort_kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin);  // the limit is per function, not per kernel object: always the most
         if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(moe_sort)");
     }
     *out = intern(ctx, std::move(k));

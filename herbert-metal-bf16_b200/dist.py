@@ -1,0 +1,210 @@
+"""Sharding of the two configurations of the path that partition across the GPUs of one box.
+
+The reference engine is single-GPU; these are the partitionings BASELINE.json asks for:
+
+* 27B-class FFN, tensor parallel: gate/up column-parallel (a rank owns a slice of gate rows AND the matching up
+  rows, so the SwiGLU epilogue stays local), down row-parallel with f32 partial products, one all-reduce (sum)
+  before the single rounding and the residual add.
+* MoE block, expert parallel: experts partitioned contiguously, token rows data-parallel; the token rows of every
+  routed (row, slot) pair travel to the rank that owns the pair's expert (all-to-all), are sorted and multiplied
+  there, and the expert outputs travel back (all-to-all) to be combined in slot order at home.
+
+One process per GPU; the plumbing is torch.distributed (NCCL on GPUs; the same code runs on gloo with CPU tensors
+for the host-logic tests). Every kernel reads and writes only its own GPU's memory: remote rows land in local
+buffers through the collective before any kernel touches them.
+
+The arithmetic is behind a small backend object so that the sharding and exchange logic here is the same code in
+production (GpuBackend: the CUDA kernels through the C ABI) and in the CPU tests (a backend the tests supply).
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+OUT_BF16, OUT_F32, OUT_RESIDUAL, OUT_SWIGLU = range(4)
+
+
+# --------------------------------------------------------------------------- tensor-parallel FFN
+
+def shard_gate_up(wgu: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    """[gate(inter) | up(inter)] rows -> this rank's [gate slice | up slice] (column-parallel)."""
+    inter = wgu.shape[0] // 2
+    assert inter % world == 0, "intermediate size must divide by the number of ranks"
+    ip = inter // world
+    return torch.cat([wgu[rank * ip : (rank + 1) * ip], wgu[inter + rank * ip : inter + (rank + 1) * ip]], dim=0).contiguous()
+
+
+def shard_down(wd: torch.Tensor, rank: int, world: int) -> torch.Tensor:
+    """Wdown [h][inter] -> this rank's K slice as its own contiguous [h][inter/world] matrix (row-parallel)."""
+    inter = wd.shape[1]
+    assert inter % world == 0
+    ip = inter // world
+    return wd[:, rank * ip : (rank + 1) * ip].contiguous()
+
+
+def tp_ffn(backend, x, wgu_local, wd_local, y, group=None):
+    """y = bf16(y + bf16(sum over ranks of H_r . Wd_r^T)), H_r = swiglu(x . Wgu_r^T). x is replicated."""
+    h_local = backend.gemm(x, wgu_local, OUT_SWIGLU)
+    acc = backend.gemm(h_local, wd_local, OUT_F32)
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(acc, op=dist.ReduceOp.SUM, group=group)
+    backend.epilogue(acc, y, OUT_RESIDUAL)
+    return y
+
+
+# --------------------------------------------------------------------------- expert-parallel MoE
+
+def exchange_rows(send: torch.Tensor, send_counts, recv_counts, group=None) -> torch.Tensor:
+    """Variable all-to-all of rows: chunk d of `send` (send_counts[d] rows) goes to rank d; the result holds the
+    chunks received from ranks 0..P-1 in rank order."""
+    world = dist.get_world_size(group)
+    if send.dtype == torch.bfloat16 and dist.get_backend(group) != "nccl":
+        return exchange_rows(send.view(torch.int16), send_counts, recv_counts, group).view(torch.bfloat16)
+    recv = send.new_empty((int(sum(recv_counts)),) + tuple(send.shape[1:]))
+    if dist.get_backend(group) == "nccl":
+        dist.all_to_all_single(recv, send, output_split_sizes=[int(c) for c in recv_counts], input_split_sizes=[int(c) for c in send_counts], group=group)
+        return recv
+    # gloo has no all-to-all: pairwise sends in a fixed schedule
+    rank = dist.get_rank(group)
+    s_off = [0]
+    r_off = [0]
+    for d in range(world):
+        s_off.append(s_off[-1] + int(send_counts[d]))
+        r_off.append(r_off[-1] + int(recv_counts[d]))
+    recv[r_off[rank] : r_off[rank + 1]] = send[s_off[rank] : s_off[rank + 1]]
+    ops = []
+    for d in range(world):
+        if d == rank:
+            continue
+        if send_counts[d]:
+            ops.append(dist.P2POp(dist.isend, send[s_off[d] : s_off[d + 1]].contiguous(), d, group))
+        if recv_counts[d]:
+            ops.append(dist.P2POp(dist.irecv, recv[r_off[d] : r_off[d + 1]], d, group))
+    if ops:
+        for w in dist.batch_isend_irecv(ops):
+            w.wait()
+    return recv
+
+
+def exchange_counts(send_counts: torch.Tensor, group=None) -> torch.Tensor:
+    """Every rank tells every other how many rows it will send it (a small all-gather)."""
+    world = dist.get_world_size(group)
+    allc = [torch.empty_like(send_counts) for _ in range(world)]
+    dist.all_gather(allc, send_counts, group=group)
+    rank = dist.get_rank(group)
+    return torch.stack([c[rank] for c in allc])
+
+
+def ep_moe(backend, x_local, scores_local, wgu_local, wd_local, experts: int, top_k: int, mi: int, bm: int, group=None, debug=None):
+    """The sparse block for this rank's token rows. wgu_local / wd_local hold this rank's experts
+    [rank*E/P, (rank+1)*E/P). Returns out_local [rows_local][h]."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    assert experts % world == 0
+    epr = experts // world
+    rows, h = x_local.shape
+    route = backend.route(scores_local, top_k)  # [rows][2*top_k]: experts ascending, then weight bits
+    # destination rank of every (row, slot) pair; pairs grouped by destination in pair order = a stable counting
+    # sort with the destination as the "expert" (the same sort kernel)
+    dest = route.clone()
+    dest[:, :top_k] = torch.div(route[:, :top_k], epr, rounding_mode="floor")
+    send_order, _ = backend.sort(dest, world, top_k, 16)  # list of local pair ids
+    send_counts = torch.bincount(dest[:, :top_k].reshape(-1).long(), minlength=world).to(torch.int64)
+    if world > 1:
+        recv_counts = exchange_counts(send_counts, group)
+    else:
+        recv_counts = send_counts.clone()
+    send_counts_l, recv_counts_l = send_counts.tolist(), recv_counts.tolist()
+    # rows and their (local) expert ids, packed in send order
+    send_rows = backend.gather(x_local, send_order, top_k)  # [pairs][h]: X[pair // top_k]
+    pair_expert = route[:, :top_k].reshape(-1)
+    send_expert = (pair_expert[send_order.long()] % epr).to(torch.int32).reshape(-1, 1).contiguous()
+    if world > 1:
+        recv_rows = exchange_rows(send_rows, send_counts_l, recv_counts_l, group)
+        recv_expert = exchange_rows(send_expert, send_counts_l, recv_counts_l, group)
+    else:
+        recv_rows, recv_expert = send_rows, send_expert
+    n_recv = recv_rows.shape[0]
+    if n_recv:
+        # every received pair is a one-slot row of a local route: [expert | weight unused]
+        local_route = torch.zeros((n_recv, 2), dtype=route.dtype, device=route.device)
+        local_route[:, 0] = recv_expert.reshape(-1).to(route.dtype)
+        lst, tiles = backend.sort(local_route, epr, 1, bm)
+        ey_recv = backend.expert_ffn(recv_rows, wgu_local, wd_local, lst, tiles, epr, mi, h, bm)  # rows in receive order
+    else:
+        lst = torch.zeros(0, dtype=route.dtype, device=route.device)
+        ey_recv = recv_rows.new_zeros((0, h))
+    if debug is not None:
+        debug.update(route=route, send_order=send_order, recv_expert=recv_expert, local_list=lst, send_counts=send_counts_l, recv_counts=recv_counts_l)
+    if world > 1:
+        ey_back = exchange_rows(ey_recv, recv_counts_l, send_counts_l, group)  # in this rank's send order
+    else:
+        ey_back = ey_recv
+    # EY[pair] = ey_back[position of pair in the send order]
+    inv = torch.empty_like(send_order)
+    inv[send_order.long()] = torch.arange(send_order.numel(), dtype=send_order.dtype, device=send_order.device)
+    ey = backend.gather(ey_back, inv, 1)  # [pairs][h] indexed by pair = row*top_k + slot
+    return backend.combine(ey, route, top_k)
+
+
+# --------------------------------------------------------------------------- the CUDA backend
+
+class GpuBackend:
+    """The backend that runs the CUDA kernels of libhb200.so on torch CUDA tensors (device memory and stream
+    plumbing only). `hb` is the loaded binding module, `ctx` its Context bound to torch's current stream."""
+
+    def __init__(self, hb, ctx, rows_max: int = 2048):
+        self.hb, self.ctx, self.rows_max = hb, ctx, rows_max
+
+    def _w(self, t):
+        assert t.is_cuda and t.is_contiguous()
+        return self.ctx.wrap(t.data_ptr(), max(t.numel() * t.element_size(), 1))
+
+    def gemm(self, x, w, out, y=None):
+        m, k = x.shape
+        n = w.shape[0]
+        if y is None:
+            y = torch.empty((m, n // 2 if out == OUT_SWIGLU else n), device=x.device, dtype=torch.float32 if out == OUT_F32 else torch.bfloat16)
+        self.ctx.gemm(k, n, out, rows_max=max(m, self.rows_max))(m, self._w(w), self._w(x), self._w(y))
+        return y
+
+    def epilogue(self, acc, y, out):
+        m, n = acc.shape
+        self.ctx.epilogue(n, out)(m, self._w(acc), self._w(y))
+        return y
+
+    def route(self, scores, top_k):
+        m, e = scores.shape
+        route = torch.empty((m, 2 * top_k), device=scores.device, dtype=torch.int32)
+        self.ctx.route(e, top_k)(m, self._w(scores), self._w(route))
+        return route
+
+    def sort(self, route, experts, top_k, bm):
+        m = route.shape[0]
+        lst = torch.empty(m * top_k, device=route.device, dtype=torch.int32)
+        tiles = torch.zeros(1 + 3 * self.hb.lib().hb_moe_tiles(m, top_k, experts, bm), device=route.device, dtype=torch.int32)
+        rows_max = 1 << max(m - 1, 0).bit_length()  # kernels are named by their capacity: round it up so few are made
+        self.ctx.moe_sort(experts, top_k, rows_max, bm)(m, self._w(route.contiguous()), self._w(lst), self._w(tiles))
+        return lst, tiles
+
+    def gather(self, x, lst, top_k):
+        pairs, h = lst.numel(), x.shape[1]
+        xs = torch.empty((pairs, h), device=x.device, dtype=x.dtype)
+        if pairs:
+            self.ctx.moe_gather(h, top_k)(pairs // top_k, self._w(x), self._w(lst), self._w(xs))
+        return xs
+
+    def expert_ffn(self, rows, wgu, wd, lst, tiles, experts, mi, h, bm):
+        n = rows.shape[0]
+        kw = dict(rows_max=max(n, self.rows_max), top_k=1, experts=experts, bm=bm)
+        ehb = torch.empty((n, mi), device=rows.device, dtype=torch.bfloat16)
+        ey = torch.empty((n, h), device=rows.device, dtype=torch.bfloat16)
+        self.ctx.gemm(h, 2 * mi, OUT_SWIGLU, rows_mode=self.hb.ROWS_GATHER, **kw)(n, self._w(wgu), self._w(rows), self._w(ehb), self._w(lst), self._w(tiles))
+        self.ctx.gemm(mi, h, OUT_BF16, rows_mode=self.hb.ROWS_SCATTER, **kw)(n, self._w(wd), self._w(ehb), self._w(ey), self._w(lst), self._w(tiles))
+        return ey
+
+    def combine(self, ey, route, top_k):
+        m, h = route.shape[0], ey.shape[1]
+        out = torch.empty((m, h), device=ey.device, dtype=torch.bfloat16)
+        self.ctx.moe_combine(h, top_k)(m, self._w(ey), self._w(route), self._w(out))
+        return out

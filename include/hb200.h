@@ -154,6 +154,10 @@ int hb_moe_gather_get(hb_ctx* ctx, uint32_t h, uint32_t top_k, hb_kernel** out);
 /* moe_combine, src/metal/qwen_kernels.rs:2119-2161: acc = bf16(acc + bf16(y*w)) over the slots in route order.
  * f32_sum = 1 is the variant that keeps the sum in f32 and rounds once. Bindings: y ([m][top_k][d]), route, out. */
 int hb_moe_combine_get(hb_ctx* ctx, uint32_t d, uint32_t top_k, uint32_t f32_sum, hb_kernel** out);
+/* The output mode (BF16 or RESIDUAL: store, src/metal/kernels.rs:217-234) applied to an f32 accumulator array
+ * [m][n] that was completed outside a GEMM: a row-parallel projection sums f32 partial products across GPUs
+ * (hb_gemm_get with HB_OUT_F32 on each, then an all-reduce) and rounds once afterwards. Bindings: acc, y. */
+int hb_epilogue_get(hb_ctx* ctx, uint32_t n, uint32_t out, hb_kernel** res);
 
 /* Emitted.name, src/msl/mod.rs:1461: deterministic, encodes the description. */
 const char* hb_kernel_name(const hb_kernel* k);
