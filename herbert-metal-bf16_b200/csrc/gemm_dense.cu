@@ -373,7 +373,7 @@ int make_gemm(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
         *out = have;
         return HB_OK;
     }
-    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin);  // the limit is per function, not per kernel object: always the most
+    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin - 1024);  // (static shared memory counts too) the limit is per function, not per kernel object: always the most
     if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(max dynamic shared memory)");
     *out = intern(ctx, std::move(k));
     return HB_OK;

@@ -1,5 +1,5 @@
 // The small kernels around the GEMMs: SwiGLU over rows, the MoE route (softmax + top-k),
-// the stable expert sort with its tile table, the row gather and the weighted combine.
+// the row gather and the weighted combine.
 // All are memory- or latency-bound CUDA-core kernels; results are bit-exact restatements
 // of the reference's arithmetic (citations per kernel).
 #include <algorithm>
@@ -48,7 +48,7 @@ __global__ void swiglu_rows_kernel(const uint16_t* __restrict__ gu, uint16_t* __
 // the 32-lane sum of experts [32g, 32g + 32) - the same partial sums, folded in the same order, as a block of
 // `experts` threads would make.
 constexpr int ROUTE_WARPS = 8;
-template <int MAXK>
+template <int MAXK, int NPL>  // NPL: values per lane = experts / 32 rounded up to a power of two
 __global__ void __launch_bounds__(ROUTE_WARPS * 32) route_topk_kernel(const uint16_t* __restrict__ scores, uint32_t* __restrict__ route, uint32_t rows,
                                                                       uint32_t experts, uint32_t top_k) {
     __shared__ float vals_s[ROUTE_WARPS][MAXK];
@@ -56,13 +56,13 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) route_topk_kernel(const uint
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t row = blockIdx.x * ROUTE_WARPS + warp;
     if (row >= rows) return;
-    const uint32_t npl = experts >> 5;  // values per lane, <= 32
+    const uint32_t npl = experts >> 5;  // values per lane in use, <= NPL
     float* vals = vals_s[warp];
     uint32_t* chosen = chosen_s[warp];
-    float p[32];
+    float p[NPL];
     float mx = -3.4e38f;
 #pragma unroll
-    for (int g = 0; g < 32; ++g) {
+    for (int g = 0; g < NPL; ++g) {
         p[g] = 0.f;
         if ((uint32_t)g < npl) {
             p[g] = bf16_to_f32(scores[(size_t)row * experts + 32 * g + lane]);
@@ -73,7 +73,7 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) route_topk_kernel(const uint
     for (int off = 16; off >= 1; off >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, off));
     float sum = 0.f;
 #pragma unroll
-    for (int g = 0; g < 32; ++g) {
+    for (int g = 0; g < NPL; ++g) {
         if ((uint32_t)g < npl) {
             p[g] = exp_f32(__fsub_rn(p[g], mx));
             float part = p[g];
@@ -83,13 +83,13 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) route_topk_kernel(const uint
         }
     }
 #pragma unroll
-    for (int g = 0; g < 32; ++g)
+    for (int g = 0; g < NPL; ++g)
         if ((uint32_t)g < npl) p[g] = __fdiv_rn(p[g], sum);
     for (uint32_t t = 0; t < top_k; ++t) {
         float bv = p[0];
         uint32_t bi = lane;
 #pragma unroll
-        for (int g = 1; g < 32; ++g)
+        for (int g = 1; g < NPL; ++g)
             if ((uint32_t)g < npl && p[g] > bv) { bv = p[g]; bi = 32 * g + lane; }  // strict >: the lowest index of a lane's ties
 #pragma unroll
         for (int off = 16; off >= 1; off >>= 1) {
@@ -100,7 +100,7 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) route_topk_kernel(const uint
         if (lane == 0) { vals[t] = bv; chosen[t] = bi; }
         if ((bi & 31u) == lane) {
 #pragma unroll
-            for (int g = 0; g < 32; ++g)
+            for (int g = 0; g < NPL; ++g)
                 if ((uint32_t)g == (bi >> 5)) p[g] = -1.0f;
         }
     }
@@ -115,99 +115,6 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) route_topk_kernel(const uint
         uint32_t* r = route + (size_t)row * 2 * top_k;
         r[rank] = chosen[e];
         r[top_k + rank] = __float_as_uint(w);
-    }
-}
-
-// ---------------------------------------------------------------- moe_sort
-// Stable counting sort of the (row, slot) pairs by expert and the expert-tile table
-// (reference src/metal/prefill.rs:1303-1442): list[p] = pair index, experts ascending, pairs
-// ascending inside an expert; tiles[0] = count, tile t = (expert, first sorted row, rows <= bm).
-// One block of 1024 threads: warp w owns a contiguous segment of pairs and walks it 32 at a
-// time in order; __match_any_sync ranks equal experts inside a step, per-warp per-expert
-// counters in shared memory carry the rank across steps and warps. No atomics: the result is
-// the same list on every run.
-constexpr int SORT_THREADS = 1024;
-constexpr int SORT_WARPS = SORT_THREADS / 32;
-
-__global__ void __launch_bounds__(SORT_THREADS) moe_sort_kernel(const uint32_t* __restrict__ route, uint32_t* __restrict__ list,
-                                                                uint32_t* __restrict__ tiles, uint32_t rows, uint32_t experts, uint32_t top_k, uint32_t bm, uint32_t staged) {
-    extern __shared__ uint32_t sm[];
-    uint32_t* cnt = sm;                          // [SORT_WARPS][experts]: pairs of expert e in warp w's segment, then running base
-    uint32_t* off = sm + SORT_WARPS * experts;   // [experts]: first sorted row of expert e
-    uint32_t* tstart = off + experts;            // [experts]: first tile of expert e
-    uint32_t* scan = tstart + experts;           // [2][experts] scratch
-    uint16_t* ex16 = reinterpret_cast<uint16_t*>(scan + 2 * experts);  // [pairs] when `staged`
-    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const uint32_t pairs = rows * top_k;
-    const uint32_t seg = ((pairs + SORT_WARPS - 1) / SORT_WARPS + 31) / 32 * 32;
-    const uint32_t s0 = min(pairs, warp * seg), s1 = min(pairs, s0 + seg);
-    for (uint32_t i = tid; i < SORT_WARPS * experts; i += SORT_THREADS) cnt[i] = 0;
-    // The ordered passes below are chains of dependent steps; with the experts staged here first (all loads in
-    // flight at once) they touch shared memory only.
-    if (staged)
-        for (uint32_t i = tid; i < pairs; i += SORT_THREADS) ex16[i] = (uint16_t)route[(size_t)(i / top_k) * 2 * top_k + (i % top_k)];
-    __syncthreads();
-    auto expert_of = [&](uint32_t i) -> uint32_t { return staged ? (uint32_t)ex16[i] : route[(size_t)(i / top_k) * 2 * top_k + (i % top_k)]; };
-    // pass 1: per-warp histograms
-    for (uint32_t b = s0; b < s1; b += 32) {
-        const uint32_t i = b + lane;
-        const bool in = i < s1;
-        const uint32_t x = in ? expert_of(i) : 0xffffffffu;
-        const uint32_t peers = __match_any_sync(0xffffffffu, x);
-        if (in && (peers & ((1u << lane) - 1)) == 0) cnt[warp * experts + x] += __popc(peers);
-        __syncwarp();
-    }
-    __syncthreads();
-    // per expert: exclusive scan over the warps, total count
-    uint32_t total_e = 0;
-    if (tid < experts) {
-        for (uint32_t w = 0; w < SORT_WARPS; ++w) {
-            const uint32_t c = cnt[w * experts + tid];
-            cnt[w * experts + tid] = total_e;
-            total_e += c;
-        }
-    }
-    // exclusive scans over the experts of (count) and (tiles per expert), Hillis-Steele on two arrays
-    const uint32_t ntile_e = (total_e + bm - 1) / bm;
-    uint32_t a = total_e, t = ntile_e;
-    uint32_t* sa = scan;
-    uint32_t* st = scan + experts;
-    if (tid < experts) { sa[tid] = a; st[tid] = t; }
-    __syncthreads();
-    for (uint32_t d = 1; d < experts; d <<= 1) {
-        uint32_t va = 0, vt = 0;
-        if (tid < experts && tid >= d) { va = sa[tid - d]; vt = st[tid - d]; }
-        __syncthreads();
-        if (tid < experts) { a += va; t += vt; sa[tid] = a; st[tid] = t; }
-        __syncthreads();
-    }
-    if (tid < experts) {
-        const uint32_t start = a - total_e, tfirst = t - ntile_e;
-        off[tid] = start;
-        tstart[tid] = tfirst;
-        for (uint32_t j = 0, ti = tfirst; j < total_e; j += bm, ++ti) {
-            tiles[1 + 3 * ti] = tid;
-            tiles[2 + 3 * ti] = start + j;
-            tiles[3 + 3 * ti] = min(bm, total_e - j);
-        }
-        if (tid == experts - 1) tiles[0] = t;
-    }
-    __syncthreads();
-    // pass 2: placement
-    for (uint32_t b = s0; b < s1; b += 32) {
-        const uint32_t i = b + lane;
-        const bool in = i < s1;
-        const uint32_t x = in ? expert_of(i) : 0xffffffffu;
-        const uint32_t peers = __match_any_sync(0xffffffffu, x);
-        const uint32_t before = __popc(peers & ((1u << lane) - 1));
-        uint32_t base = 0;
-        if (in) base = off[x] + cnt[warp * experts + x];
-        __syncwarp();
-        if (in) {
-            list[base + before] = i;
-            if (before == 0) cnt[warp * experts + x] += __popc(peers);
-        }
-        __syncwarp();
     }
 }
 
@@ -287,25 +194,15 @@ struct Route : hb_kernel {
         if (na != 2) return fail(ctx, HB_INVALID, name + ": bindings are scores, route");
         if (m == 0) return fail(ctx, HB_INVALID, name + ": m = 0");
         if (!range_ok(a[0], (size_t)m * experts * 2) || !range_ok(a[1], (size_t)m * 2 * top_k * 4)) return fail(ctx, HB_INVALID, name + ": a bound range is too small");
-        route_topk_kernel<64><<<(m + ROUTE_WARPS - 1) / ROUTE_WARPS, ROUTE_WARPS * 32, 0, ctx->stream>>>(static_cast<const uint16_t*>(a[0].ptr), static_cast<uint32_t*>(a[1].ptr), m,
-                                                                                                    experts, top_k);
-        HB_CUDA(ctx, cudaGetLastError());
-        ctx->launches++;
-        return HB_OK;
-    }
-};
-
-struct MoeSort : hb_kernel {
-    uint32_t experts = 0, top_k = 0, rows_max = 0, bm = 0, staged = 0;
-    size_t smem = 0;
-    int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
-        if (na != 3) return fail(ctx, HB_INVALID, name + ": bindings are route, list, tiles");
-        if (m == 0 || m > rows_max) return fail(ctx, HB_INVALID, name + ": m outside 1.." + std::to_string(rows_max));
-        const size_t tiles_words = 1 + 3 * (size_t)hb_moe_tiles(m, top_k, experts, bm);
-        if (!range_ok(a[0], (size_t)m * 2 * top_k * 4) || !range_ok(a[1], (size_t)m * top_k * 4) || !range_ok(a[2], tiles_words * 4))
-            return fail(ctx, HB_INVALID, name + ": a bound range is too small");
-        moe_sort_kernel<<<1, SORT_THREADS, smem, ctx->stream>>>(static_cast<const uint32_t*>(a[0].ptr), static_cast<uint32_t*>(a[1].ptr), static_cast<uint32_t*>(a[2].ptr), m,
-                                                               experts, top_k, bm, staged);
+        const uint32_t grid = (m + ROUTE_WARPS - 1) / ROUTE_WARPS, npl = experts / 32;
+        const uint16_t* sc = static_cast<const uint16_t*>(a[0].ptr);
+        uint32_t* rt = static_cast<uint32_t*>(a[1].ptr);
+        if (npl <= 1) route_topk_kernel<64, 1><<<grid, ROUTE_WARPS * 32, 0, ctx->stream>>>(sc, rt, m, experts, top_k);
+        else if (npl <= 2) route_topk_kernel<64, 2><<<grid, ROUTE_WARPS * 32, 0, ctx->stream>>>(sc, rt, m, experts, top_k);
+        else if (npl <= 4) route_topk_kernel<64, 4><<<grid, ROUTE_WARPS * 32, 0, ctx->stream>>>(sc, rt, m, experts, top_k);
+        else if (npl <= 8) route_topk_kernel<64, 8><<<grid, ROUTE_WARPS * 32, 0, ctx->stream>>>(sc, rt, m, experts, top_k);
+        else if (npl <= 16) route_topk_kernel<64, 16><<<grid, ROUTE_WARPS * 32, 0, ctx->stream>>>(sc, rt, m, experts, top_k);
+        else route_topk_kernel<64, 32><<<grid, ROUTE_WARPS * 32, 0, ctx->stream>>>(sc, rt, m, experts, top_k);
         HB_CUDA(ctx, cudaGetLastError());
         ctx->launches++;
         return HB_OK;
@@ -373,36 +270,6 @@ int make_route(hb_ctx* ctx, uint32_t experts, uint32_t top_k, hb_kernel** out) {
     k->kind = 4;
     k->nargs = 2;
     k->name = "route_qwen_" + std::to_string(experts) + "_k" + std::to_string(top_k);
-    *out = intern(ctx, std::move(k));
-    return HB_OK;
-}
-
-int make_moe_sort(hb_ctx* ctx, uint32_t experts, uint32_t top_k, uint32_t rows_max, uint32_t bm, hb_kernel** out) {
-    *out = nullptr;
-    if (experts == 0 || experts > 1024 || top_k == 0 || rows_max == 0) return fail(ctx, HB_UNSUPPORTED, "moe_sort: 1..1024 experts, top_k and rows_max positive");
-    if (bm != 16 && bm != 32 && bm != 64) return fail(ctx, HB_UNSUPPORTED, "moe_sort: tile rows 16, 32 or 64");
-    auto k = std::make_unique<MoeSort>();
-    k->experts = experts;
-    k->top_k = top_k;
-    k->rows_max = rows_max;
-    k->bm = bm;
-    k->smem = ((size_t)SORT_WARPS * experts + 4 * (size_t)experts) * sizeof(uint32_t);
-    const size_t stage_bytes = ((size_t)rows_max * top_k * 2 + 15) / 16 * 16;
-    if (k->smem + stage_bytes <= 200 * 1024) {  // the experts of every pair fit beside the counters
-        k->staged = 1;
-        k->smem += stage_bytes;
-    }
-    k->kind = 5;
-    k->nargs = 3;
-    k->name = "moe_sort_" + std::to_string(experts) + "_k" + std::to_string(top_k) + "_r" + std::to_string(rows_max) + "_m" + std::to_string(bm);
-    if (hb_kernel* have = find(ctx, k->name)) {
-        *out = have;
-        return HB_OK;
-    }
-    {
-        cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(moe_sort_kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin);  // the limit is per function, not per kernel object: always the most
-        if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(moe_sort)");
-    }
     *out = intern(ctx, std::move(k));
     return HB_OK;
 }

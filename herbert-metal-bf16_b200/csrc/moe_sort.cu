@@ -1,0 +1,238 @@
+// moe_sort: stable counting sort of the routed (row, slot) pairs by expert, and the expert-tile table
+// (reference src/metal/prefill.rs:1303-1442): list[p] = pair index (row*top_k + slot), experts ascending, pairs
+// ascending inside an expert; tiles[0] = number of tiles, tile t = (expert, first sorted row, rows <= bm).
+//
+// One block of 1024 threads, no data-dependent ordering between threads, the same list on every run.
+// Fast path (a route names an expert at most once per row, which a top-k route always does): one bitmask of
+// rows per expert built with shared-memory atomicOr (the result does not depend on the order of the ORs), a
+// prefix of popcounts per mask word, and every pair places itself at
+//   first row of its expert + popcount of the expert's mask below its row.
+// General path (an expert repeated inside a row, or masks too large for shared memory): every warp owns a
+// contiguous segment of pairs and walks it 32 at a time in order; __match_any_sync ranks equal experts inside a
+// step and per-warp per-expert counters carry the rank across steps and warps.
+#include <algorithm>
+
+#include "hb_internal.hpp"
+#include "tc05.cuh"
+
+namespace hb {
+
+constexpr int SORT_THREADS = 1024;
+constexpr int SORT_WARPS = SORT_THREADS / 32;
+
+struct SortParams {
+    const uint32_t* route;
+    uint32_t* list;
+    uint32_t* tiles;
+    uint32_t rows, experts, top_k, bm;
+    uint32_t staged;    // the experts of all pairs fit in shared memory as 16-bit values
+    uint32_t use_masks; // the per-expert row masks fit in shared memory
+    uint32_t words;     // stride of an expert's mask in words: ceil(rows_max / 32) made odd
+};
+
+__global__ void __launch_bounds__(SORT_THREADS) moe_sort_kernel(const SortParams p) {
+    extern __shared__ uint32_t sm[];
+    const uint32_t experts = p.experts, top_k = p.top_k, bm = p.bm;
+    uint32_t* off = sm;                   // [experts] first sorted row of expert e
+    uint32_t* tot = off + experts;        // [experts] pairs of expert e
+    uint32_t* scan = tot + experts;       // [2][experts] scratch
+    uint32_t* flag = scan + 2 * experts;  // [4]
+    uint32_t* big = flag + 4;             // masks + prefixes, or the per-warp counters
+    uint32_t* mask = big;                                     // [experts][words]
+    uint32_t* pre = big + (p.use_masks ? experts * p.words : 0);  // [experts][words]
+    uint32_t* cnt = big;                                      // [SORT_WARPS][experts] (general path)
+    const size_t big_words = p.use_masks ? 2 * (size_t)experts * p.words : (size_t)SORT_WARPS * experts;
+    const size_t counter_words = (size_t)SORT_WARPS * experts;
+    uint16_t* ex16 = reinterpret_cast<uint16_t*>(big + (big_words > counter_words ? big_words : counter_words));
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t pairs = p.rows * top_k;
+    const uint32_t words = (p.rows + 31) / 32;  // words in use this launch (<= p.words)
+
+    auto expert_global = [&](uint32_t i) { return p.route[(size_t)(i / top_k) * 2 * top_k + (i % top_k)]; };
+    if (tid == 0) flag[0] = 0;
+    if (p.staged)
+        for (uint32_t i = tid; i < pairs; i += SORT_THREADS) ex16[i] = (uint16_t)expert_global(i);
+    auto expert_of = [&](uint32_t i) -> uint32_t { return p.staged ? (uint32_t)ex16[i] : expert_global(i); };
+
+    bool fast = p.use_masks != 0;
+    if (fast) {
+        for (uint32_t i = tid; i < experts * p.words; i += SORT_THREADS) mask[i] = 0;
+        __syncthreads();
+        for (uint32_t i = tid; i < pairs; i += SORT_THREADS) {
+            const uint32_t e = expert_of(i), r = i / top_k, bit = 1u << (r & 31);
+            if (atomicOr(&mask[e * p.words + (r >> 5)], bit) & bit) flag[0] = 1;  // the expert twice in one row
+        }
+        __syncthreads();
+        fast = flag[0] == 0;
+    } else {
+        __syncthreads();
+    }
+
+    uint32_t total_e = 0;
+    if (fast) {
+        // per expert: exclusive prefix of the popcounts of its mask words (a warp per expert, lanes over words)
+        for (uint32_t e = warp; e < experts; e += SORT_WARPS) {
+            uint32_t carry = 0;
+            for (uint32_t w0 = 0; w0 < words; w0 += 32) {
+                const uint32_t w = w0 + lane;
+                const uint32_t c = w < words ? __popc(mask[e * p.words + w]) : 0;
+                uint32_t incl = c;
+#pragma unroll
+                for (int d = 1; d < 32; d <<= 1) {
+                    const uint32_t v = __shfl_up_sync(0xffffffffu, incl, d);
+                    if (lane >= (uint32_t)d) incl += v;
+                }
+                if (w < words) pre[e * p.words + w] = carry + incl - c;
+                carry += __shfl_sync(0xffffffffu, incl, 31);
+            }
+            if (lane == 0) tot[e] = carry;
+        }
+        __syncthreads();
+        if (tid < experts) total_e = tot[tid];
+    } else {
+        // general path, pass 1: per-warp histograms over contiguous segments
+        for (uint32_t i = tid; i < SORT_WARPS * experts; i += SORT_THREADS) cnt[i] = 0;
+        __syncthreads();
+        const uint32_t seg = ((pairs + SORT_WARPS - 1) / SORT_WARPS + 31) / 32 * 32;
+        const uint32_t s0 = min(pairs, warp * seg), s1 = min(pairs, s0 + seg);
+        for (uint32_t b = s0; b < s1; b += 32) {
+            const uint32_t i = b + lane;
+            const bool in = i < s1;
+            const uint32_t x = in ? expert_of(i) : 0xffffffffu;
+            const uint32_t peers = __match_any_sync(0xffffffffu, x);
+            if (in && (peers & ((1u << lane) - 1)) == 0) cnt[warp * experts + x] += __popc(peers);
+            __syncwarp();
+        }
+        __syncthreads();
+        if (tid < experts) {
+            for (uint32_t w = 0; w < SORT_WARPS; ++w) {  // exclusive scan over the warps
+                const uint32_t c = cnt[w * experts + tid];
+                cnt[w * experts + tid] = total_e;
+                total_e += c;
+            }
+        }
+    }
+
+    // exclusive scans over the experts of (pairs) and (tiles per expert); the tile table
+    const uint32_t ntile_e = (total_e + bm - 1) / bm;
+    uint32_t a = total_e, t = ntile_e;
+    uint32_t* sa = scan;
+    uint32_t* st = scan + experts;
+    if (tid < experts) { sa[tid] = a; st[tid] = t; }
+    __syncthreads();
+    for (uint32_t d = 1; d < experts; d <<= 1) {
+        uint32_t va = 0, vt = 0;
+        if (tid < experts && tid >= d) { va = sa[tid - d]; vt = st[tid - d]; }
+        __syncthreads();
+        if (tid < experts) { a += va; t += vt; sa[tid] = a; st[tid] = t; }
+        __syncthreads();
+    }
+    if (tid < experts) {
+        const uint32_t start = a - total_e, tfirst = t - ntile_e;
+        off[tid] = start;
+        for (uint32_t j = 0, ti = tfirst; j < total_e; j += bm, ++ti) {
+            p.tiles[1 + 3 * ti] = tid;
+            p.tiles[2 + 3 * ti] = start + j;
+            p.tiles[3 + 3 * ti] = min(bm, total_e - j);
+        }
+        if (tid == experts - 1) p.tiles[0] = t;
+    }
+    __syncthreads();
+
+    if (fast) {
+        for (uint32_t i = tid; i < pairs; i += SORT_THREADS) {
+            const uint32_t e = expert_of(i), r = i / top_k;
+            const uint32_t at = e * p.words + (r >> 5);
+            p.list[off[e] + pre[at] + __popc(mask[at] & ((1u << (r & 31)) - 1u))] = i;
+        }
+    } else {
+        const uint32_t seg = ((pairs + SORT_WARPS - 1) / SORT_WARPS + 31) / 32 * 32;
+        const uint32_t s0 = min(pairs, warp * seg), s1 = min(pairs, s0 + seg);
+        for (uint32_t b = s0; b < s1; b += 32) {
+            const uint32_t i = b + lane;
+            const bool in = i < s1;
+            const uint32_t x = in ? expert_of(i) : 0xffffffffu;
+            const uint32_t peers = __match_any_sync(0xffffffffu, x);
+            const uint32_t before = __popc(peers & ((1u << lane) - 1));
+            uint32_t base = 0;
+            if (in) base = off[x] + cnt[warp * experts + x];
+            __syncwarp();
+            if (in) {
+                p.list[base + before] = i;
+                if (before == 0) cnt[warp * experts + x] += __popc(peers);
+            }
+            __syncwarp();
+        }
+    }
+}
+
+namespace {
+
+struct MoeSort : hb_kernel {
+    uint32_t experts = 0, top_k = 0, rows_max = 0, bm = 0, staged = 0, use_masks = 0, words = 0;
+    size_t smem = 0;
+    int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
+        if (na != 3) return fail(ctx, HB_INVALID, name + ": bindings are route, list, tiles");
+        if (m == 0 || m > rows_max) return fail(ctx, HB_INVALID, name + ": m outside 1.." + std::to_string(rows_max));
+        const size_t tiles_words = 1 + 3 * (size_t)hb_moe_tiles(m, top_k, experts, bm);
+        if (!range_ok(a[0], (size_t)m * 2 * top_k * 4) || !range_ok(a[1], (size_t)m * top_k * 4) || !range_ok(a[2], tiles_words * 4))
+            return fail(ctx, HB_INVALID, name + ": a bound range is too small");
+        SortParams p{};
+        p.route = static_cast<const uint32_t*>(a[0].ptr);
+        p.list = static_cast<uint32_t*>(a[1].ptr);
+        p.tiles = static_cast<uint32_t*>(a[2].ptr);
+        p.rows = m;
+        p.experts = experts;
+        p.top_k = top_k;
+        p.bm = bm;
+        p.staged = staged;
+        p.use_masks = use_masks;
+        p.words = words;
+        moe_sort_kernel<<<1, SORT_THREADS, smem, ctx->stream>>>(p);
+        HB_CUDA(ctx, cudaGetLastError());
+        ctx->launches++;
+        return HB_OK;
+    }
+};
+
+}  // namespace
+
+int make_moe_sort(hb_ctx* ctx, uint32_t experts, uint32_t top_k, uint32_t rows_max, uint32_t bm, hb_kernel** out) {
+    *out = nullptr;
+    if (experts == 0 || experts > 1024 || top_k == 0 || rows_max == 0) return fail(ctx, HB_UNSUPPORTED, "moe_sort: 1..1024 experts, top_k and rows_max positive");
+    if (bm != 16 && bm != 32 && bm != 64) return fail(ctx, HB_UNSUPPORTED, "moe_sort: tile rows 16, 32 or 64");
+    auto k = std::make_unique<MoeSort>();
+    k->experts = experts;
+    k->top_k = top_k;
+    k->rows_max = rows_max;
+    k->bm = bm;
+    k->kind = 5;
+    k->nargs = 3;
+    k->name = "moe_sort_" + std::to_string(experts) + "_k" + std::to_string(top_k) + "_r" + std::to_string(rows_max) + "_m" + std::to_string(bm);
+    if (hb_kernel* have = find(ctx, k->name)) {
+        *out = have;
+        return HB_OK;
+    }
+    const size_t limit = 200 * 1024;
+    const size_t fixed = (4 * (size_t)experts + 4) * 4;
+    const size_t counters = (size_t)SORT_WARPS * experts * 4;
+    k->words = ((rows_max + 31) / 32) | 1u;  // odd stride: the same word of different experts falls in different banks
+    const size_t masks = 2 * (size_t)experts * k->words * 4;
+    size_t big = counters;
+    if (fixed + std::max(masks, counters) <= limit) {
+        k->use_masks = 1;
+        big = std::max(masks, counters);  // the general path stays available inside the same launch
+    }
+    const size_t stage = ((size_t)rows_max * top_k * 2 + 15) / 16 * 16;
+    k->smem = fixed + big;
+    if (k->smem + stage <= limit) {
+        k->staged = 1;
+        k->smem += stage;
+    }
+    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(moe_sort_kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin - 1024);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(moe_sort)");
+    *out = intern(ctx, std::move(k));
+    return HB_OK;
+}
+
+}  // namespace hb

@@ -477,8 +477,9 @@ int hb_select_matvec(hb_selector* s, uint32_t k, uint32_t n, uint32_t out, uint3
     try {
         const hb_tune& t = s->tune;
         int r;
-        auto get = [&](uint32_t rpw, uint32_t split, uint32_t persist, hb_kernel** kern) {
+        auto get = [&](uint32_t rpw, uint32_t split, uint32_t persist, hb_kernel** kern, uint32_t xs = 0) {
             hb_matvec_desc d{};
+            d.x_stationary = xs;
             d.k = k;
             d.n = n;
             d.out = out;
@@ -525,6 +526,15 @@ int hb_select_matvec(hb_selector* s, uint32_t k, uint32_t n, uint32_t out, uint3
                     for (int i = 0; i < copies; ++i) add_op(c, kern, {w_copies[i], x, y});
                     cands.push_back(std::move(c));
                 }
+        // with several activation rows: the forms that keep the activations widened in registers
+        if (rows > 1)
+            for (uint32_t rpw : {2u, 4u}) {
+                if (get(rpw, 1, 1, &kern, 1) != HB_OK) continue;
+                Cand c;
+                c.name = "x" + std::to_string(rpw);
+                for (int i = 0; i < copies; ++i) add_op(c, kern, {w_copies[i], x, y});
+                cands.push_back(std::move(c));
+            }
         if (cands.empty()) return hb::fail(ctx, HB_UNSUPPORTED, "matvec " + key + ": no form could be built");
         std::vector<char> eligible(cands.size(), 1);
         size_t best;

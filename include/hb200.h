@@ -135,6 +135,9 @@ typedef struct {
     uint32_t rows_per_warp; /* W rows one warp reduces: 1, 2, 4 or 8 (the reference's `rows`) */
     uint32_t split;         /* K split across the warps of a block: 1, 2 or 4 (mv.split) */
     uint32_t persist;       /* 1 = a fixed grid that loops over the row groups (mv.persist) */
+    uint32_t x_stationary;  /* 1 = for 2..8 activation rows: K is split across the threads of a persistent block and
+                               each thread keeps its slice of the activations widened in registers; rows_per_warp
+                               (2 or 4) is then the W rows reduced per step; needs K * rows <= 32768 */
 } hb_matvec_desc;
 int hb_matvec_get(hb_ctx* ctx, const hb_matvec_desc* desc, hb_kernel** out);
 

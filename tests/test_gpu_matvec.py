@@ -31,6 +31,20 @@ def test_every_form(ctx, oracle, m, out):
                 within_contract(oracle, want, got, f"{kern.name} m={m}")
 
 
+@pytest.mark.parametrize("m", [2, 3, 4, 7, 8])
+@pytest.mark.parametrize("out", [OUT_BF16, OUT_F32, OUT_RESIDUAL, OUT_SWIGLU])
+def test_activation_stationary_forms(ctx, oracle, hb200, m, out):
+    # K split across the threads of a block, activations widened once in registers
+    for k, n in ((1024, 330), (4096, 512), (72, 40), (2560, 96)):
+        for rpw in (2, 4):
+            kern, want, got = run(ctx, oracle, m, k, n, out, rows_per_warp=rpw, x_stationary=1)
+            assert f"_x{rpw}" in kern.name
+            within_contract(oracle, want, got, f"{kern.name} m={m}")
+    with pytest.raises(hb200.HbError) as e:
+        ctx.matvec(12288, 64, rows_max=8, x_stationary=1)  # K * rows beyond what the registers hold
+    assert e.value.status == hb200.UNSUPPORTED
+
+
 def test_m1_equals_reference_lane_order_closely(ctx, oracle):
     # M = 1 against the reference's own order of operations (32 lanes striding K by chunks of 8,
     # butterfly sum): the same sums up to the association of the lane fold

@@ -57,6 +57,20 @@ def test_sort_skewed_and_empty_experts(ctx, hb200, oracle):
         assert np.array_equal(lst, want_l) and np.array_equal(tiles[: 1 + 3 * n], want_t[: 1 + 3 * n])
 
 
+def test_sort_expert_repeated_within_a_row(ctx, hb200, oracle):
+    # not a top-k route (the destination-rank sort of the expert-parallel path looks like this): the kernel's
+    # general path must give the same stable order
+    rng = np.random.default_rng(3)
+    rows, experts, top_k = 700, 8, 8
+    route = np.zeros((rows, 2 * top_k), dtype=np.uint32)
+    route[:, :top_k] = np.sort(rng.integers(0, experts, size=(rows, top_k)), axis=1)
+    for bm in (16, 64):
+        _, _, lst, tiles = sort_on_gpu(ctx, hb200, route, experts, top_k, bm)
+        want_l, want_t = oracle.moe_sort(route, experts, top_k, bm)
+        n = int(want_t[0])
+        assert np.array_equal(lst, want_l) and np.array_equal(tiles[: 1 + 3 * n], want_t[: 1 + 3 * n])
+
+
 def test_sort_same_list_every_run(ctx, hb200, oracle):
     route = oracle.route_topk(oracle.normal((2048, 256), 7, 3, 1.0), 8)
     first = sort_on_gpu(ctx, hb200, route, 256, 8, 16)[2]
