@@ -312,6 +312,8 @@ struct ExpertGemm : hb_kernel {
 
 }  // namespace
 
+int make_gemm_expert_runs(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out);
+
 int make_gemm_experts(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
     *out = nullptr;
     if (d->k == 0 || d->n == 0 || d->rows_max == 0 || d->experts == 0 || d->top_k == 0)
@@ -321,6 +323,7 @@ int make_gemm_experts(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
     const bool fused = d->out == HB_OUT_SWIGLU;
     if (d->out != HB_OUT_BF16 && !fused) return fail(ctx, HB_UNSUPPORTED, "expert gemm: output bf16, or the fused SwiGLU of the [gate | up] rows");
     if (fused && d->n % 2 != 0) return fail(ctx, HB_INVALID, "expert gemm: the SwiGLU form needs an even n");
+    if (d->merge_runs) return make_gemm_expert_runs(ctx, d, out);
     ex_fn fn = nullptr;
     switch (d->bm) {
         case 16: fn = ex_pick<16>(d->rows_mode, fused); break;

@@ -196,7 +196,7 @@ class GpuBackend:
 
     def expert_ffn(self, rows, wgu, wd, lst, tiles, experts, mi, h, bm):
         n = rows.shape[0]
-        kw = dict(rows_max=max(n, self.rows_max), top_k=1, experts=experts, bm=bm)
+        kw = dict(rows_max=max(n, self.rows_max), top_k=1, experts=experts, bm=bm, merge_runs=1)
         ehb = torch.empty((n, mi), device=rows.device, dtype=torch.bfloat16)
         ey = torch.empty((n, h), device=rows.device, dtype=torch.bfloat16)
         self.ctx.gemm(h, 2 * mi, OUT_SWIGLU, rows_mode=self.hb.ROWS_GATHER, **kw)(n, self._w(wgu), self._w(rows), self._w(ehb), self._w(lst), self._w(tiles))

@@ -557,8 +557,9 @@ int hb_select_experts(hb_selector* s, const hb_expert_io* io, hb_expert_pick* pi
         std::vector<uint32_t> bms;
         if (t.moe_tile_set || !t.gemm_timed()) bms = {t.get("moe.tile")};  // qwen.rs:2352
         else bms = {16, 32, 64};
-        auto expert_gemm = [&](uint32_t k, uint32_t n, uint32_t out, uint32_t mode, uint32_t bm, hb_kernel** kern) {
+        auto expert_gemm = [&](uint32_t k, uint32_t n, uint32_t out, uint32_t mode, uint32_t bm, hb_kernel** kern, uint32_t merge = 0) {
             hb_gemm_desc d{};
+            d.merge_runs = merge;
             d.k = k;
             d.n = n;
             d.out = out;
@@ -623,6 +624,20 @@ int hb_select_experts(hb_selector* s, const hb_expert_io* io, hb_expert_pick* pi
                 add_op(c, sorted, {io->wgu, io->xs, io->ehb, io->list, io->tiles});
                 gu.push_back(std::move(c));
             }
+            hb_kernel *fused_m = nullptr, *sorted_m = nullptr, *down_m = nullptr;
+            if (expert_gemm(io->h, 2 * io->mi, HB_OUT_SWIGLU, HB_ROWS_GATHER, bm, &fused_m, 1) == HB_OK) {
+                Cand c;
+                c.name = "fused+runs";
+                add_op(c, fused_m, {io->wgu, io->x, io->ehb, io->list, io->tiles});
+                gu.push_back(std::move(c));
+            }
+            if (io->xs.ptr && gather && expert_gemm(io->h, 2 * io->mi, HB_OUT_SWIGLU, HB_ROWS_SORTED, bm, &sorted_m, 1) == HB_OK) {
+                Cand c;
+                c.name = "gather+fused+runs";
+                add_op(c, gather, {io->x, io->list, io->xs});
+                add_op(c, sorted_m, {io->wgu, io->xs, io->ehb, io->list, io->tiles});
+                gu.push_back(std::move(c));
+            }
             std::vector<char> el(gu.size(), 1);
             // The partial-block pass of the check needs a route of that many rows: only the full block is sorted
             // here, so candidates are compared at m rows (rows past the sorted pairs are never written).
@@ -661,7 +676,32 @@ int hb_select_experts(hb_selector* s, const hb_expert_io* io, hb_expert_pick* pi
             cd.name = "scatter";
             add_op(cd, down, {io->wdown, io->ehb, io->ey, io->list, io->tiles});
             dn.push_back(std::move(cd));
-            std::vector<char> eld = {1};
+            if (expert_gemm(io->mi, io->h, HB_OUT_BF16, HB_ROWS_SCATTER, bm, &down_m, 1) == HB_OK) {
+                Cand c;
+                c.name = "scatter+runs";
+                add_op(c, down_m, {io->wdown, io->ehb, io->ey, io->list, io->tiles});
+                dn.push_back(std::move(c));
+            }
+            std::vector<char> eld(dn.size(), 1);
+            {   // the merged form against the per-tile form, on the EHB just made
+                const size_t bytes = (size_t)pairs * io->h * 2;
+                std::vector<uint8_t> ref(bytes), got(bytes);
+                double tt;
+                if ((r = hb_memset(ctx, io->ey.ptr, 0, bytes)) != HB_OK) return r;
+                if ((r = time_ops(s, dn[0], m, 1, &tt)) != HB_OK) return r;
+                if ((r = hb_download(ctx, ref.data(), io->ey.ptr, bytes)) != HB_OK) return r;
+                for (size_t i = 1; i < dn.size(); ++i) {
+                    if ((r = hb_memset(ctx, io->ey.ptr, 0, bytes)) != HB_OK) return r;
+                    if ((r = time_ops(s, dn[i], m, 1, &tt)) != HB_OK) return r;
+                    if ((r = hb_download(ctx, got.data(), io->ey.ptr, bytes)) != HB_OK) return r;
+                    float err, scale;
+                    if (!rule_1_64(ref.data(), got.data(), bytes / 2, false, &err, &scale)) {
+                        eld[i] = 0;
+                        say(s, "[autotune] experts down " + tag + ": wrong against " + dn[0].name + ", never picked: " + dn[i].name + " (" + std::to_string(m) +
+                                   " rows: max err " + fmt_e3(err) + " of " + fmt_e3(scale) + ")");
+                    }
+                }
+            }
             size_t bd;
             if ((r = pick_flagged(s, "experts down " + tag, dn, eld, m, &bd, &t_down)) != HB_OK) return r;
             const double total = t_sort + t_gu + t_down;
@@ -670,10 +710,11 @@ int hb_select_experts(hb_selector* s, const hb_expert_io* io, hb_expert_pick* pi
                 best_total = total;
                 pick->bm = bm;
                 pick->sort = sort;
-                pick->gather = gu[bgu].name == "gather+fused" ? gather : nullptr;
-                pick->gate_up = gu[bgu].name == "fused" ? fused : gu[bgu].name == "apart" ? apart : sorted;
-                pick->swiglu = gu[bgu].name == "apart" ? swi : nullptr;
-                pick->down = down;
+                const std::string& gn = gu[bgu].name;
+                pick->gather = gn.rfind("gather+", 0) == 0 ? gather : nullptr;
+                pick->gate_up = gn == "fused" ? fused : gn == "apart" ? apart : gn == "gather+fused" ? sorted : gn == "fused+runs" ? fused_m : sorted_m;
+                pick->swiglu = gn == "apart" ? swi : nullptr;
+                pick->down = dn[bd].name == "scatter" ? down : down_m;
             }
         }
         char buf[160];

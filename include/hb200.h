@@ -121,6 +121,8 @@ typedef struct {
     uint32_t cta_pair;  /* DENSE: 1 = two CTAs share a 256-row tile (tcgen05 cta_group::2) */
     uint32_t m_first;   /* tile order: 1 = walk the row tiles of a column tile first (gemm.mfirst, prefill.rs:26-42) */
     uint32_t rows_max;  /* largest m this kernel will be launched with (sizes the tile table in expert modes) */
+    uint32_t merge_runs; /* expert modes: 1 = the consecutive tiles of one expert are merged into work items of up to
+                            128 rows, so that an expert's weights are read once whatever the tile size */
 } hb_gemm_desc;
 int hb_gemm_get(hb_ctx* ctx, const hb_gemm_desc* desc, hb_kernel** out);
 

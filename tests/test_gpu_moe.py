@@ -105,7 +105,7 @@ def test_gather_and_swiglu_slots_bit_exact(ctx, oracle):
     assert np.array_equal(d_h.download(np.uint16, (rows * top_k, 96)), oracle.swiglu_slots(egu))
 
 
-def moe_layer(ctx, hb200, oracle, m, h, mi, experts, top_k, bm, fused=True, pre_gather=False):
+def moe_layer(ctx, hb200, oracle, m, h, mi, experts, top_k, bm, fused=True, pre_gather=False, merge_runs=0):
     """The whole sparse block on the GPU and in the oracle; returns both sets of intermediates."""
     x = oracle.normal((m, h), SEED_X, 1, 1.0)
     wgu = oracle.normal((experts * 2 * mi, h), SEED_W, 2, h**-0.5)
@@ -126,7 +126,7 @@ def moe_layer(ctx, hb200, oracle, m, h, mi, experts, top_k, bm, fused=True, pre_
     d_egu, d_ehb, d_ey, d_out, d_xs = ctx.alloc(pairs * 2 * mi * 2), ctx.alloc(pairs * mi * 2), ctx.alloc(pairs * h * 2), ctx.alloc(m * h * 2), ctx.alloc(pairs * h * 2)
     ctx.route(experts, top_k)(m, d_s, d_route)
     ctx.moe_sort(experts, top_k, m, bm)(m, d_route, d_list, d_tiles)
-    kw = dict(rows_max=m, top_k=top_k, experts=experts, bm=bm)
+    kw = dict(rows_max=m, top_k=top_k, experts=experts, bm=bm, merge_runs=merge_runs)
     if pre_gather:
         ctx.moe_gather(h, top_k)(m, d_x, d_list, d_xs)
         ctx.gemm(h, 2 * mi, hb200.OUT_SWIGLU, rows_mode=hb200.ROWS_SORTED, **kw)(m, d_wgu, d_xs, d_ehb, d_list, d_tiles)
@@ -154,18 +154,27 @@ def moe_layer(ctx, hb200, oracle, m, h, mi, experts, top_k, bm, fused=True, pre_
     return g_out
 
 
+@pytest.mark.parametrize("merge_runs", [0, 1])
 @pytest.mark.parametrize("bm", [16, 32, 64])
 @pytest.mark.parametrize("form", ["fused", "apart", "gather+fused"])
-def test_moe_layer_small(ctx, hb200, oracle, bm, form):
-    moe_layer(ctx, hb200, oracle, 100, 256, 192, 32, 8, bm, fused=form == "fused", pre_gather=form == "gather+fused")
+def test_moe_layer_small(ctx, hb200, oracle, bm, form, merge_runs):
+    moe_layer(ctx, hb200, oracle, 100, 256, 192, 32, 8, bm, fused=form == "fused", pre_gather=form == "gather+fused", merge_runs=merge_runs)
+
+
+@pytest.mark.parametrize("bm", [16, 64])
+def test_moe_layer_long_runs_merged(ctx, hb200, oracle, bm):
+    # 600 tokens, 32 experts, top-16: 300 rows per expert, so an expert's run spans three 128-row work items
+    moe_layer(ctx, hb200, oracle, 600, 128, 160, 32, 16, bm, merge_runs=1)
 
 
 def test_moe_layer_forms_agree_bitwise(ctx, hb200, oracle):
-    outs = [moe_layer(ctx, hb200, oracle, 64, 128, 128, 32, 4, bm, fused=f, pre_gather=g) for bm in (16, 64) for f, g in ((True, False), (False, False), (True, True))]
+    outs = [moe_layer(ctx, hb200, oracle, 64, 128, 128, 32, 4, bm, fused=f, pre_gather=g, merge_runs=r) for bm in (16, 64) for f, g in ((True, False), (False, False), (True, True))
+            for r in (0, 1)]
     for o in outs[1:]:
         assert np.array_equal(outs[0], o)
 
 
-def test_config5_full_size(ctx, hb200, oracle):
+@pytest.mark.parametrize("merge_runs", [0, 1])
+def test_config5_full_size(ctx, hb200, oracle, merge_runs):
     # hidden 2048, 256 experts, top-8, expert intermediate 512, 2048 tokens
-    moe_layer(ctx, hb200, oracle, 2048, 2048, 512, 256, 8, 16)
+    moe_layer(ctx, hb200, oracle, 2048, 2048, 512, 256, 8, 16, merge_runs=merge_runs)
