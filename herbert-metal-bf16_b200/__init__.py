@@ -41,7 +41,7 @@ class Op(C.Structure):
 
 
 class GemmDesc(C.Structure):
-    _fields_ = [(n, C.c_uint32) for n in ("k", "n", "out", "rows_mode", "top_k", "experts", "bm", "tile_n", "stages", "cta_pair", "m_first", "rows_max", "merge_runs")]
+    _fields_ = [(n, C.c_uint32) for n in ("k", "n", "out", "rows_mode", "top_k", "experts", "bm", "tile_n", "stages", "cta_pair", "m_first", "rows_max", "stream_k", "merge_runs")]
 
 
 class MatvecDesc(C.Structure):
@@ -248,8 +248,8 @@ class Context:
         self._check(fn(self.h, *args, C.byref(k)))
         return Kernel(self, k.value)
 
-    def gemm(self, k, n, out=OUT_BF16, rows_max=2048, tile_n=0, stages=0, cta_pair=0, m_first=1, rows_mode=ROWS_DENSE, top_k=0, experts=0, bm=0, merge_runs=0) -> Kernel:
-        d = GemmDesc(k, n, out, rows_mode, top_k, experts, bm, tile_n, stages, cta_pair, m_first, rows_max, merge_runs)
+    def gemm(self, k, n, out=OUT_BF16, rows_max=2048, tile_n=0, stages=0, cta_pair=0, m_first=1, rows_mode=ROWS_DENSE, top_k=0, experts=0, bm=0, merge_runs=0, stream_k=0) -> Kernel:
+        d = GemmDesc(k, n, out, rows_mode, top_k, experts, bm, tile_n, stages, cta_pair, m_first, rows_max, stream_k, merge_runs)
         return self._get(lib().hb_gemm_get, C.byref(d))
 
     def matvec(self, k, n, out=OUT_BF16, rows_max=1, rows_per_warp=2, split=1, persist=0, x_stationary=0) -> Kernel:

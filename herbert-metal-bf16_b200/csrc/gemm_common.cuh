@@ -1,0 +1,97 @@
+// Shared by the dense prefill GEMM kernels: launch parameters, tile constants, barrier block and the
+// epilogue that applies the output mode to 32 consecutive accumulator columns of one row
+// (reference src/metal/kernels.rs:217-234, src/metal/prefill.rs:1200-1230).
+#pragma once
+
+#include "hb_internal.hpp"
+#include "tc05.cuh"
+
+namespace hb {
+
+struct GemmParams {
+    void* y;
+    uint32_t m, n_w;      // rows of X, rows of W
+    uint32_t n_out;       // columns (and row stride) of Y
+    uint32_t k_blocks;    // ceil(k / 64)
+    uint32_t tiles_m, tiles_n, num_tiles;
+    uint32_t stages;
+    uint32_t m_first;
+    uint32_t vec_ok;      // Y rows allow 16-byte accesses
+    uint32_t* status;
+};
+
+constexpr int BM = 128;
+constexpr int BK = 64;
+constexpr int A_BYTES = BM * BK * 2;
+constexpr int MAX_STAGES = 10;
+constexpr int GEMM_THREADS = 192;
+
+struct __align__(8) GemmBarriers {
+    uint64_t full[MAX_STAGES];
+    uint64_t empty[MAX_STAGES];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+    uint32_t abort;
+};
+
+// Stores 32 consecutive outputs of one row. v[] are the f32 accumulators (or for SWIGLU the
+// gate accumulators, u[] the up ones).
+template <int OUT>
+__device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t row, uint32_t col0, const uint32_t (&v)[32], const uint32_t (&u)[32]) {
+    if (row >= p.m || col0 >= p.n_out) return;
+    const uint32_t ncols = min(32u, p.n_out - col0);
+    if constexpr (OUT == HB_OUT_F32) {
+        float* y = reinterpret_cast<float*>(p.y) + (size_t)row * p.n_out + col0;
+        if (ncols == 32 && p.vec_ok) {
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+                reinterpret_cast<uint4*>(y)[i] = make_uint4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        } else {
+            for (uint32_t i = 0; i < ncols; ++i) y[i] = __uint_as_float(v[i]);
+        }
+    } else {
+        uint16_t* y = reinterpret_cast<uint16_t*>(p.y) + (size_t)row * p.n_out + col0;
+        uint32_t o[32];
+        if constexpr (OUT == HB_OUT_BF16) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = f32_to_bf16(__uint_as_float(v[i]));
+        } else if constexpr (OUT == HB_OUT_SWIGLU) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                o[i] = swiglu_bf16(round_bf16(__uint_as_float(v[i])), round_bf16(__uint_as_float(u[i])));
+        } else {  // RESIDUAL: y = bf16(f32(y_old) + f32(bf16(acc)))
+            uint32_t old[32];
+            if (ncols == 32 && p.vec_ok) {
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    uint4 q = reinterpret_cast<const uint4*>(y)[i];
+                    uint32_t w[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        old[8 * i + 2 * j] = w[j] & 0xffffu;
+                        old[8 * i + 2 * j + 1] = w[j] >> 16;
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) old[i] = (uint32_t)i < ncols ? y[i] : 0u;
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                o[i] = f32_to_bf16(__fadd_rn(bf16_to_f32(old[i]), round_bf16(__uint_as_float(v[i]))));
+        }
+        if (ncols == 32 && p.vec_ok) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+                reinterpret_cast<uint4*>(y)[i] = make_uint4(o[8 * i] | (o[8 * i + 1] << 16), o[8 * i + 2] | (o[8 * i + 3] << 16),
+                                                            o[8 * i + 4] | (o[8 * i + 5] << 16), o[8 * i + 6] | (o[8 * i + 7] << 16));
+        } else {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+                if ((uint32_t)i < ncols) y[i] = (uint16_t)o[i];
+        }
+    }
+}
+
+}  // namespace hb

@@ -43,6 +43,10 @@ struct hb_ctx {
     hb_encode_tiled_fn encode = nullptr;
     std::map<std::string, std::unique_ptr<hb_kernel>> kernels;  // by name: one object per distinct kernel
     uint64_t launches = 0;  // kernels enqueued through this context
+    // scratch of the stream-K GEMM: f32 partial tiles [sm_count][128][256] and their flags, made on first use
+    float* sk_scratch = nullptr;
+    uint32_t* sk_flags = nullptr;
+    uint32_t sk_epoch = 0;
 };
 
 namespace hb {

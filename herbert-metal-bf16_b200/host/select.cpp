@@ -236,8 +236,9 @@ int pick_flagged(hb_selector* s, const std::string& what, const std::vector<Cand
 uint32_t tile_n_of_tn(uint32_t tn) { return tn >= 64 ? 256 : tn == 32 ? 128 : 64; }
 
 int get_dense(hb_selector* s, uint32_t k, uint32_t n, uint32_t out, uint32_t tile_n, uint32_t stages, uint32_t m_first, uint32_t pair, uint32_t rows_max,
-              hb_kernel** kern) {
+              hb_kernel** kern, uint32_t stream_k = 0) {
     hb_gemm_desc d{};
+    d.stream_k = stream_k;
     d.k = k;
     d.n = n;
     d.out = out;
@@ -252,12 +253,13 @@ int get_dense(hb_selector* s, uint32_t k, uint32_t n, uint32_t out, uint32_t til
 
 struct DenseForm {
     const char* name;
-    uint32_t tile_n, pair, flip;
+    uint32_t tile_n, pair, flip, stream_k;
 };
 // The first one is the production reference every other candidate is checked against (the role of
 // "mma" in the reference's list, qwen.rs:2248).
 const DenseForm kDenseForms[] = {
-    {"t128x256", 256, 0, 0}, {"t128x128", 128, 0, 0}, {"t128x64", 64, 0, 0}, {"t128x256n", 256, 0, 1}, {"t128x128n", 128, 0, 1}, {"pair256x256", 256, 1, 0},
+    {"t128x256", 256, 0, 0, 0}, {"t128x128", 128, 0, 0, 0}, {"t128x64", 64, 0, 0, 0},   {"t128x256n", 256, 0, 1, 0}, {"t128x128n", 128, 0, 1, 0},
+    {"sk128x256", 256, 0, 0, 1}, {"sk128x128", 128, 0, 0, 1}, {"sk128x64", 64, 0, 0, 1}, {"pair256x256", 256, 1, 0, 0},
 };
 
 }  // namespace
@@ -359,7 +361,7 @@ int hb_select_gemm(hb_selector* s, uint32_t k, uint32_t n, uint32_t out, hb_rang
         std::vector<Cand> cands;
         std::vector<char> eligible;
         for (const auto& f : kDenseForms) {
-            r = get_dense(s, k, n, out, f.tile_n, 0, f.flip ? 1u - mf : mf, f.pair, rows_max, &kern);
+            r = get_dense(s, k, n, out, f.tile_n, 0, f.flip ? 1u - mf : mf, f.pair, rows_max, &kern, f.stream_k);
             if (r != HB_OK) {
                 if (cands.empty()) return r;  // the production kernel itself does not build: an error, not a skipped candidate
                 say(s, "[autotune] gemm " + key + ": " + f.name + " not built (" + hb_last_error(ctx) + ")");
@@ -441,10 +443,11 @@ int hb_select_gate_up(hb_selector* s, uint32_t k, uint32_t inter, hb_range w, hb
                 add_op(c0, ap[1], {gu, h});
                 cands.push_back(std::move(c0));
                 eligible.push_back(1);
-                for (uint32_t tn : {256u, 128u, 64u}) {
+                for (uint32_t form = 0; form < 6; ++form) {
+                    const uint32_t tn = 256u >> (form % 3), sk = form / 3;
                     hb_kernel* f = nullptr;
-                    const std::string name = "fused128x" + std::to_string(tn);
-                    if (get_dense(s, k, 2 * inter, HB_OUT_SWIGLU, tn, 0, mf, 0, rows_max, &f) != HB_OK) {
+                    const std::string name = std::string(sk ? "fusedsk128x" : "fused128x") + std::to_string(tn);
+                    if (get_dense(s, k, 2 * inter, HB_OUT_SWIGLU, tn, 0, mf, 0, rows_max, &f, sk) != HB_OK) {
                         say(s, "[autotune] gate_up " + key + ": " + name + " not built (" + hb_last_error(ctx) + ")");
                         continue;
                     }

@@ -121,6 +121,10 @@ typedef struct {
     uint32_t cta_pair;  /* DENSE: 1 = two CTAs share a 256-row tile (tcgen05 cta_group::2) */
     uint32_t m_first;   /* tile order: 1 = walk the row tiles of a column tile first (gemm.mfirst, prefill.rs:26-42) */
     uint32_t rows_max;  /* largest m this kernel will be launched with (sizes the tile table in expert modes) */
+    uint32_t stream_k;  /* DENSE: 1 = the (tile, k-block) units are divided evenly among the CTAs of a persistent grid;
+                           a tile cut by a boundary is completed through f32 partial tiles in scratch memory owned by
+                           the context (allocated at the first such hb_gemm_get). Removes the idle tail when the tile
+                           count is not a multiple of the SM count, and splits K for short row buckets. */
     uint32_t merge_runs; /* expert modes: 1 = the consecutive tiles of one expert are merged into work items of up to
                             128 rows, so that an expert's weights are read once whatever the tile size */
 } hb_gemm_desc;

@@ -39,6 +39,35 @@ def test_k_and_n_tails(ctx, oracle, k, n):
         within_contract(oracle, oracle.gemm_f64(x, w, out, y0), got, kern.name)
 
 
+@pytest.mark.parametrize("out", MODES)
+@pytest.mark.parametrize("m,k,n,tile_n", [(200, 320, 520, 64), (64, 4096, 768, 256), (1, 2048, 264, 128), (683, 1024, 1024, 256), (300, 8192, 256, 128), (129, 72, 40, 64)])
+def test_stream_k_forms(ctx, oracle, out, m, k, n, tile_n):
+    # tiles cut across CTAs and completed through the scratch partials: two-way cuts (many tiles) and
+    # many-way K splits (fewer tiles than SMs), ragged extents, every output mode
+    kern, (x, w, y0), got = run_gemm(ctx, oracle, m, k, n, out, tile_n=tile_n, stream_k=1)
+    assert kern.name.startswith("gemm_sk_")
+    within_contract(oracle, oracle.gemm_f64(x, w, out, y0), got, kern.name)
+
+
+def test_stream_k_repeated_launches_and_config1(ctx, oracle):
+    # launches are told apart by an epoch: the same kernel object run many times back to back stays right
+    m, k, n = 512, 1024, 4096
+    x, w, y0 = gemm_inputs(oracle, m, k, n)
+    d_x, d_w, d_y = ctx.to_device(x), ctx.to_device(w), ctx.alloc(m * n * 2)
+    kern = ctx.gemm(k, n, OUT_BF16, rows_max=m, stream_k=1)
+    want = oracle.gemm_f64(x, w)
+    for _ in range(20):
+        kern(m, d_w, d_x, d_y)
+    ctx.sync()
+    within_contract(oracle, want, d_y.download(np.uint16, (m, n)), kern.name)
+    first = d_y.download(np.uint16, (m, n))
+    for _ in range(3):
+        d_y.zero()
+        kern(m, d_w, d_x, d_y)
+        ctx.sync()
+        assert np.array_equal(first, d_y.download(np.uint16, (m, n)))  # a fixed summation order: the same bits every run
+
+
 def test_config1_dense_gemm(ctx, oracle):
     # BASELINE config 1: M=512, K=1024, N=4096
     for m_first in (1, 0):
