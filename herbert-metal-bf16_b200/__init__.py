@@ -102,6 +102,7 @@ def lib() -> C.CDLL:
         "hb_moe_gather_get": (ci, [vp, u32, u32, pvp]),
         "hb_moe_combine_get": (ci, [vp, u32, u32, u32, pvp]),
         "hb_epilogue_get": (ci, [vp, u32, u32, pvp]),
+        "hb_gemm_static_scratch": (ci, [vp, u32, u32, u32, u32, Range, Range, Range]),
         "hb_kernel_name": (C.c_char_p, [vp]),
         "hb_launch": (ci, [vp, vp, C.POINTER(Range), ci, u32]),
         "hb_run": (ci, [vp, C.POINTER(Op), ci]),
@@ -135,7 +136,7 @@ def lib() -> C.CDLL:
 EXPORTS = [
     "hb_open", "hb_close", "hb_last_error", "hb_describe", "hb_set_stream", "hb_alloc", "hb_set_alloc_limit", "hb_upload",
     "hb_download", "hb_memset", "hb_sync", "hb_launch_count", "hb_gemm_get", "hb_matvec_get", "hb_swiglu_get", "hb_route_get",
-    "hb_moe_sort_get", "hb_moe_tiles", "hb_moe_gather_get", "hb_moe_combine_get", "hb_epilogue_get", "hb_kernel_name", "hb_launch", "hb_run", "hb_time",
+    "hb_moe_sort_get", "hb_moe_tiles", "hb_moe_gather_get", "hb_moe_combine_get", "hb_epilogue_get", "hb_gemm_static_scratch", "hb_kernel_name", "hb_launch", "hb_run", "hb_time",
     "hb_tune_new", "hb_tune_free", "hb_tune_apply", "hb_tune_get", "hb_tune_summary", "hb_tune_gemm_timed", "hb_selector_new",
     "hb_selector_free", "hb_selector_log", "hb_selector_buckets", "hb_fill_random16", "hb_select_gemm", "hb_select_gate_up",
     "hb_select_matvec", "hb_select_experts", "hb_selector_inject_wrong", "hb_check_rule",

@@ -497,3 +497,93 @@ int make_gemm_streamk(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
 
 }  // namespace hb
 
+// ------------------------------------------------------------------ the entry point that allocates nothing
+//
+// hb_gemm_static_scratch runs the stream-K GEMM (128x64 tiles) with its partial-tile scratch in the two arrays
+// below instead of memory obtained from the allocator. Every GPU that loads this library holds them (5.0 MiB)
+// until the process exits.
+
+namespace hb {
+constexpr uint32_t STATIC_SLOTS = HB_STATIC_SCRATCH_SLOTS;  // CTAs the static scratch can serve
+constexpr uint32_t STATIC_BN = 64;
+}  // namespace hb
+
+static __device__ __align__(256) float g_static_partials[hb::STATIC_SLOTS * hb::BM * hb::STATIC_BN];
+static __device__ __align__(256) uint32_t g_static_flags[hb::STATIC_SLOTS * 4];
+
+namespace {
+constexpr int MAX_DEVICES = 64;
+// Per device: the device addresses of the arrays (their names are host-side stand-ins, not addresses a kernel
+// could use) and the epoch that tells this device's launches apart.
+float* s_partials[MAX_DEVICES];
+uint32_t* s_flags[MAX_DEVICES];
+uint32_t s_epoch[MAX_DEVICES];
+bool s_ready[MAX_DEVICES];
+}  // namespace
+
+extern "C" int hb_gemm_static_scratch(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t out, uint32_t m, hb_range w, hb_range x, hb_range y) {
+    using namespace hb;
+    if (!ctx) return HB_INVALID;
+    if (k == 0 || n == 0 || m == 0) return fail(ctx, HB_INVALID, "hb_gemm_static_scratch: k, n and m must be positive");
+    if (k % 8 != 0) return fail(ctx, HB_UNSUPPORTED, "hb_gemm_static_scratch: k must be a multiple of 8");
+    if (out > HB_OUT_SWIGLU || (out == HB_OUT_SWIGLU && n % 2 != 0)) return fail(ctx, HB_INVALID, "hb_gemm_static_scratch: bad output mode");
+    if (m > HB_STATIC_SCRATCH_MAX_ROWS || k > HB_STATIC_SCRATCH_MAX_K || n > HB_STATIC_SCRATCH_MAX_N)
+        return fail(ctx, HB_UNSUPPORTED, "hb_gemm_static_scratch: at most 2048 rows, k <= 65536 and n <= 262144 (larger products need hb_gemm_get, which allocates)");
+    if (ctx->device < 0 || ctx->device >= MAX_DEVICES) return fail(ctx, HB_UNSUPPORTED, "hb_gemm_static_scratch: device index out of range");
+    const uint32_t n_out = out == HB_OUT_SWIGLU ? n / 2 : n;
+    if (!range_ok(w, (size_t)n * k * 2) || !range_ok(x, (size_t)m * k * 2) || !range_ok(y, (size_t)m * n_out * (out == HB_OUT_F32 ? 4 : 2)))
+        return fail(ctx, HB_INVALID, "hb_gemm_static_scratch: a range is too small");
+    sk_fn fn = sk_pick_out<STATIC_BN>(out);
+    const int dev = ctx->device;
+    HB_CUDA(ctx, cudaSetDevice(dev));
+    if (!s_ready[dev]) {
+        // Set-up, once per device, with that device current: ask the runtime where the arrays live on it.
+        float* pp = nullptr;
+        uint32_t* fp = nullptr;
+        HB_CUDA(ctx, cudaGetSymbolAddress(reinterpret_cast<void**>(&pp), g_static_partials));
+        HB_CUDA(ctx, cudaGetSymbolAddress(reinterpret_cast<void**>(&fp), g_static_flags));
+        for (uint32_t o = HB_OUT_BF16; o <= HB_OUT_SWIGLU; ++o)
+            HB_CUDA(ctx, cudaFuncSetAttribute(reinterpret_cast<const void*>(sk_pick_out<STATIC_BN>(o)), cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                              (int)ctx->smem_optin - 1024));
+        // The flags keep whatever the last call left; launches are told apart by the epoch, and the arrays start
+        // zeroed when the module loads, so epochs begin at 1 and nothing needs clearing.
+        s_partials[dev] = pp;
+        s_flags[dev] = fp;
+        s_epoch[dev] = 0;
+        s_ready[dev] = true;
+    }
+    CUtensorMap tm_x, tm_w;
+    int r = make_tmap_bf16(ctx, &tm_w, w.ptr, n, k, STATIC_BN / 2);
+    if (r != HB_OK) return r;
+    if ((r = make_tmap_bf16(ctx, &tm_x, x.ptr, m, k, BM)) != HB_OK) return r;
+    const size_t stage_bytes = A_BYTES + (size_t)STATIC_BN * BK * 2;
+    const size_t budget = std::min<size_t>(ctx->smem_optin, 227 * 1024) - 2048;
+    const uint32_t stages = (uint32_t)std::min<size_t>(budget / stage_bytes, MAX_STAGES);
+    StreamKParams sp{};
+    GemmParams& p = sp.g;
+    p.y = y.ptr;
+    p.m = m;
+    p.n_w = n;
+    p.n_out = n_out;
+    p.k_blocks = (k + BK - 1) / BK;
+    p.tiles_m = (m + BM - 1) / BM;
+    const uint32_t cols_per_tile = out == HB_OUT_SWIGLU ? STATIC_BN / 2 : STATIC_BN;
+    p.tiles_n = (n_out + cols_per_tile - 1) / cols_per_tile;
+    p.num_tiles = p.tiles_m * p.tiles_n;
+    p.stages = stages;
+    p.m_first = 1;
+    const uint32_t elem = out == HB_OUT_F32 ? 4 : 2;
+    p.vec_ok = ((reinterpret_cast<uintptr_t>(y.ptr) & 15u) == 0 && ((size_t)n_out * elem) % 16 == 0) ? 1u : 0u;
+    p.status = ctx->status_dev;
+    const uint64_t units = (uint64_t)p.num_tiles * p.k_blocks;
+    if (units > 0xffffffffull) return fail(ctx, HB_UNSUPPORTED, "hb_gemm_static_scratch: too many (tile, k-block) units");
+    sp.total_units = (uint32_t)units;
+    sp.scratch = s_partials[dev];
+    sp.flags = s_flags[dev];
+    sp.epoch = ++s_epoch[dev];
+    const uint32_t grid = (uint32_t)std::min<uint64_t>(units, std::min<uint64_t>((uint64_t)ctx->sm_count, STATIC_SLOTS));
+    fn<<<grid, GEMM_THREADS, stages * stage_bytes + 1024, ctx->stream>>>(tm_x, tm_w, sp);
+    HB_CUDA(ctx, cudaGetLastError());
+    ctx->launches++;
+    return HB_OK;
+}

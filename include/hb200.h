@@ -168,6 +168,32 @@ int hb_moe_combine_get(hb_ctx* ctx, uint32_t d, uint32_t top_k, uint32_t f32_sum
  * (hb_gemm_get with HB_OUT_F32 on each, then an all-reduce) and rounds once afterwards. Bindings: acc, y. */
 int hb_epilogue_get(hb_ctx* ctx, uint32_t n, uint32_t out, hb_kernel** res);
 
+/* The GEMM for callers that must not allocate device memory. (No counterpart in the reference: its buffers all
+ * come from Gpu::alloc at load.)
+ *
+ * Some hosts of this library cannot call cudaMalloc where they call the GEMM: code running inside a region where
+ * the allocator is off limits (a latency-critical serving loop that forbids any call that may synchronise the
+ * device or take the allocator's lock), a plugin handed a fixed memory budget by its host engine, or a process
+ * whose device memory is fully claimed by another allocator. hb_gemm_get with stream_k = 1 allocates its
+ * partial-tile scratch from the context on first use; this entry point runs the same stream-K kernel (128x64
+ * tiles, output modes BF16 / F32 / RESIDUAL / SWIGLU) with the scratch in a fixed array inside the library
+ * instead, and calls no cudaMalloc, cudaFree or other allocating routine. The caller passes W, X and Y as for
+ * hb_launch (W [n][k], X [m][k], Y [m][n] or [m][n/2]); the launch goes on the context's stream.
+ *
+ * Limits: the array serves HB_STATIC_SCRATCH_SLOTS CTAs (a GPU with more SMs runs that many CTAs) and costs
+ * 5.0 MiB of device memory on every GPU that loads the library, until the process exits. Products beyond
+ * HB_STATIC_SCRATCH_MAX_ROWS rows, HB_STATIC_SCRATCH_MAX_K or HB_STATIC_SCRATCH_MAX_N are refused with
+ * HB_UNSUPPORTED: use hb_gemm_get for those.
+ * The first call on a device looks up the array's device address (cudaGetSymbolAddress) and raises the kernel's
+ * shared-memory limit; make that first call before any stream capture begins.
+ * All calls on a device share the one array: two calls whose kernels overlap on the GPU (different streams or
+ * contexts) race on it. Calls on one stream are ordered and safe; nothing needs clearing between them. */
+#define HB_STATIC_SCRATCH_SLOTS 160u
+#define HB_STATIC_SCRATCH_MAX_ROWS 2048u
+#define HB_STATIC_SCRATCH_MAX_K 65536u
+#define HB_STATIC_SCRATCH_MAX_N 262144u
+int hb_gemm_static_scratch(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t out, uint32_t m, hb_range w, hb_range x, hb_range y);
+
 /* Emitted.name, src/msl/mod.rs:1461: deterministic, encodes the description. */
 const char* hb_kernel_name(const hb_kernel* k);
 /* Gpu::dispatch, src/metal/gpu.rs:166: enqueue on the context's stream. Any 1 <= m <= rows_max. */
