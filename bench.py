@@ -161,10 +161,25 @@ def run_reference(args):
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line))
+    emit(line)
+
+
+# The one JSON line goes to the process's real stdout; everything else that writes to file descriptor 1 (NCCL prints its
+# version banner there) is sent to stderr, so that stdout holds exactly the line.
+_REAL_STDOUT = None
+
+
+def emit(line: dict) -> None:
+    out = _REAL_STDOUT or sys.stdout
+    out.write(json.dumps(line) + "\n")
+    out.flush()
 
 
 def main():
+    global _REAL_STDOUT
+    sys.stdout.flush()
+    _REAL_STDOUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
@@ -315,7 +330,7 @@ def main():
                        "l2": "386 MB of weights per step: inputs larger than L2"},
             "e2e": e2e, "gpu_launches": launches, "clocks": sampler.summary(), "roofline": roofline, "cpu_baseline": cpu, "extra": extra,
         }
-        print(json.dumps(line))
+        emit(line)
     sel.close()
     ctx.close()
     if world > 1:
@@ -356,7 +371,7 @@ def run_case(args):
         w, x = rnd(n, k, scale=k**-0.5), rnd(8, k)
         y = torch.zeros(8, n, device=dev, dtype=torch.bfloat16)
         torch.cuda.synchronize()
-        kern = ctx.matvec(k, n, 0, rows_max=m, rows_per_warp=2 if m == 1 else 4, split=2 if m == 1 else 1)
+        kern = ctx.matvec(k, n, 0, rows_max=m, rows_per_warp=2 if m == 1 else 4, split=2 if m == 1 else 1, x_stationary=0 if m == 1 else 1)
         ops = [(kern, m, wrap(w), wrap(x), wrap(y))]
         work = {"bytes": 2.0 * (n * k + m * k + m * n)}
     else:
@@ -382,7 +397,7 @@ def run_case(args):
         line["tflops"] = work["flop"] / sec / 1e12
     else:
         line["gbs"] = work["bytes"] / sec / 1e9
-    print(json.dumps(line))
+    emit(line)
     ctx.close()
 
 

@@ -121,10 +121,13 @@ __device__ __forceinline__ void build_runs(const RunParams& p, uint32_t ntiles, 
     __syncthreads();
 }
 
-template <int SRC, int DST, bool FUSED>
+// ACCS: 1 = one block of 128 features per work item; 2 with FUSED = the gate block and its up block (SwiGLU);
+// 2 without FUSED = two neighbouring feature blocks sharing the token operand (halves its traffic from L2).
+template <int SRC, int DST, bool FUSED, int ACCS>
 __global__ void __launch_bounds__(RN_THREADS, 1)
 gemm_expert_runs_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x64, const __grid_constant__ CUtensorMap tm_x128, const RunParams p) {
-    constexpr int NACC = FUSED ? 2 : 1;
+    constexpr int NACC = ACCS;
+    constexpr uint32_t FEAT_PER_ITEM = (ACCS == 2 && !FUSED) ? 256u : 128u;
     constexpr int A_STAGE = NACC * RN_A_BYTES;
     constexpr int STAGE_BYTES = A_STAGE + RN_B_BYTES;
     constexpr uint32_t ACC_COLS = NACC * RN_NMAX;  // 128 or 256 columns per accumulator set
@@ -176,8 +179,8 @@ gemm_expert_runs_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_c
             for (uint32_t w = blockIdx.x; ok && w < work_total; w += gridDim.x) {
                 const uint32_t r = w / p.n_blocks, nb = w % p.n_blocks;
                 const uint32_t expert = runs[3 * r], start = runs[3 * r + 1], rows = runs[3 * r + 2];
-                const int row_w0 = (int)(expert * p.n + nb * 128);
-                const int row_w1 = (int)(expert * p.n + p.n_feat + nb * 128);
+                const int row_w0 = (int)(expert * p.n + nb * FEAT_PER_ITEM);
+                const int row_w1 = FUSED ? (int)(expert * p.n + p.n_feat + nb * 128) : row_w0 + 128;
                 const bool small = rows <= 64;
                 const uint32_t b_bytes = small ? 64 * 128 : 128 * 128;
                 for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
@@ -190,7 +193,7 @@ gemm_expert_runs_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_c
                     const uint32_t dst = smem_base + s * STAGE_BYTES;
                     mbar_arrive_expect_tx(full, SRC == RSRC_SORTED ? A_STAGE + b_bytes : A_STAGE);
                     tma_load_2d(dst, &tm_w, full, (int)(kb * 64), row_w0);
-                    if (FUSED) tma_load_2d(dst + RN_A_BYTES, &tm_w, full, (int)(kb * 64), row_w1);
+                    if (NACC == 2) tma_load_2d(dst + RN_A_BYTES, &tm_w, full, (int)(kb * 64), row_w1);
                     if (SRC == RSRC_SORTED) tma_load_2d(dst + A_STAGE, small ? &tm_x64 : &tm_x128, full, (int)(kb * 64), (int)start);
                     if (++s == S) { s = 0; ph ^= 1u; }
                 }
@@ -226,7 +229,7 @@ gemm_expert_runs_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_c
                     for (uint32_t k4 = 0; k4 < 4; ++k4) {
                         const uint32_t accumulate = (kb | k4) != 0 ? 1u : 0u;
                         umma_bf16(d_tmem, a_desc + 2 * k4, b_desc + 2 * k4, idesc, accumulate);
-                        if (FUSED) umma_bf16(d_tmem + RN_NMAX, umma_desc_sw128(a_addr + RN_A_BYTES) + 2 * k4, b_desc + 2 * k4, idesc, accumulate);
+                        if (NACC == 2) umma_bf16(d_tmem + RN_NMAX, umma_desc_sw128(a_addr + RN_A_BYTES) + 2 * k4, b_desc + 2 * k4, idesc, accumulate);
                     }
                     umma_commit(smem_u32(&bars.empty[s]));
                     if (++s == S) { s = 0; ph ^= 1u; }
@@ -251,13 +254,13 @@ gemm_expert_runs_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_c
                 break;
             }
             tc_fence_after();
-            const uint32_t feat = nb * 128 + q * 32 + lane;
+            const uint32_t feat = nb * FEAT_PER_ITEM + q * 32 + lane;
             const uint32_t t_addr = tmem_base + ((q * 32u) << 16) + acc * ACC_COLS;
             uint16_t* y = reinterpret_cast<uint16_t*>(p.y) + feat;
             for (uint32_t c = 0; c * 32 < rows; ++c) {
                 uint32_t g[32], u[32];
                 tmem_ld_32x32(t_addr + c * 32, g);
-                if (FUSED) tmem_ld_32x32(t_addr + RN_NMAX + c * 32, u);
+                if (NACC == 2) tmem_ld_32x32(t_addr + RN_NMAX + c * 32, u);
                 tmem_ld_wait();
                 if (feat < p.n_feat) {
 #pragma unroll
@@ -269,6 +272,13 @@ gemm_expert_runs_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_c
                             else o = f32_to_bf16(__uint_as_float(g[j]));
                             y[(size_t)orow[row] * p.n_feat] = (uint16_t)o;
                         }
+                    }
+                }
+                if (NACC == 2 && !FUSED && feat + 128 < p.n_feat) {  // the second feature block of the pair
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const uint32_t row = c * 32 + j;
+                        if (row < rows) y[(size_t)orow[row] * p.n_feat + 128] = (uint16_t)f32_to_bf16(__uint_as_float(u[j]));
                     }
                 }
             }
@@ -329,17 +339,23 @@ namespace {
 
 typedef void (*run_fn)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const RunParams);
 
-run_fn run_pick(uint32_t rows_mode, bool fused) {
-    if (rows_mode == HB_ROWS_GATHER) return fused ? gemm_expert_runs_kernel<RSRC_GATHER, RDST_SORTED, true> : gemm_expert_runs_kernel<RSRC_GATHER, RDST_SORTED, false>;
-    if (rows_mode == HB_ROWS_SORTED) return fused ? gemm_expert_runs_kernel<RSRC_SORTED, RDST_SORTED, true> : gemm_expert_runs_kernel<RSRC_SORTED, RDST_SORTED, false>;
-    if (rows_mode == HB_ROWS_SCATTER) return fused ? nullptr : gemm_expert_runs_kernel<RSRC_SORTED, RDST_SCATTER, false>;
+// Unfused forms take two feature blocks per work item when the expert has at least 256 features.
+run_fn run_pick(uint32_t rows_mode, bool fused, bool pair) {
+    if (rows_mode == HB_ROWS_GATHER)
+        return fused ? gemm_expert_runs_kernel<RSRC_GATHER, RDST_SORTED, true, 2>
+                     : pair ? gemm_expert_runs_kernel<RSRC_GATHER, RDST_SORTED, false, 2> : gemm_expert_runs_kernel<RSRC_GATHER, RDST_SORTED, false, 1>;
+    if (rows_mode == HB_ROWS_SORTED)
+        return fused ? gemm_expert_runs_kernel<RSRC_SORTED, RDST_SORTED, true, 2>
+                     : pair ? gemm_expert_runs_kernel<RSRC_SORTED, RDST_SORTED, false, 2> : gemm_expert_runs_kernel<RSRC_SORTED, RDST_SORTED, false, 1>;
+    if (rows_mode == HB_ROWS_SCATTER)
+        return fused ? nullptr : pair ? gemm_expert_runs_kernel<RSRC_SORTED, RDST_SCATTER, false, 2> : gemm_expert_runs_kernel<RSRC_SORTED, RDST_SCATTER, false, 1>;
     return nullptr;
 }
 
 struct ExpertRunsGemm : hb_kernel {
     hb_gemm_desc d{};
     run_fn fn = nullptr;
-    bool fused = false;
+    bool fused = false, pair = false;
     uint32_t stages = 0;
     size_t smem = 0;
     const void* last_w = nullptr;
@@ -377,7 +393,7 @@ struct ExpertRunsGemm : hb_kernel {
         p.k_blocks = (d.k + 63) / 64;
         p.n = d.n;
         p.n_feat = n_feat;
-        p.n_blocks = (n_feat + 127) / 128;
+        p.n_blocks = pair ? (n_feat + 255) / 256 : (n_feat + 127) / 128;
         p.k = d.k;
         p.top_k = d.top_k;
         p.stages = stages;
@@ -397,9 +413,10 @@ int make_gemm_expert_runs(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
     *out = nullptr;
     const bool fused = d->out == HB_OUT_SWIGLU;
     if (d->experts > RN_MAX_EXPERTS) return fail(ctx, HB_UNSUPPORTED, "expert gemm (merged runs): at most 1024 experts");
-    run_fn fn = run_pick(d->rows_mode, fused);
+    const bool pair = !fused && d->n >= 256;
+    run_fn fn = run_pick(d->rows_mode, fused, pair);
     if (!fn) return fail(ctx, HB_UNSUPPORTED, "expert gemm: this rows mode / output combination is not built");
-    const size_t stage_bytes = (fused ? 2 : 1) * (size_t)RN_A_BYTES + RN_B_BYTES;
+    const size_t stage_bytes = (fused || pair ? 2 : 1) * (size_t)RN_A_BYTES + RN_B_BYTES;
     const size_t static_smem = sizeof(RunBarriers) + (2 * RN_MAX_EXPERTS + 3 * RN_MAX_RUNS + RN_THREADS + 4 * RN_NMAX) * 4;
     const size_t budget = std::min<size_t>(ctx->smem_optin, 227 * 1024) - 2048 - static_smem;
     const uint32_t max_stages = (uint32_t)std::min<size_t>(budget / stage_bytes, RN_MAX_STAGES);
@@ -409,6 +426,7 @@ int make_gemm_expert_runs(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
     k->d = *d;
     k->fn = fn;
     k->fused = fused;
+    k->pair = pair;
     k->stages = stages;
     k->smem = stages * stage_bytes + 1024;
     k->kind = 8;

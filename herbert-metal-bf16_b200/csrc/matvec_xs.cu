@@ -39,6 +39,31 @@ __device__ __forceinline__ void widen8(const uint4& v, float (&f)[8]) {
     f[6] = __uint_as_float(v.w << 16); f[7] = __uint_as_float(v.w & 0xffff0000u);
 }
 
+// Two f32 in one 64-bit register, and the packed fused multiply-add of sm_100 (two FMAs per instruction): the
+// accumulators are kept as (sum over even elements, sum over odd elements) and folded once at the end.
+__device__ __forceinline__ uint64_t pack2(uint32_t lo, uint32_t hi) {
+    uint64_t d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+    return d;
+}
+__device__ __forceinline__ uint64_t ffma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ float fold2(uint64_t v) {
+    uint32_t lo, hi;
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(lo), "=r"(hi) : "l"(v));
+    return __fadd_rn(__uint_as_float(lo), __uint_as_float(hi));
+}
+// The four (even, odd) pairs of a 16-byte chunk of bf16, widened.
+__device__ __forceinline__ void widen_pairs(const uint4& v, uint64_t (&p)[4]) {
+    p[0] = pack2(v.x << 16, v.x & 0xffff0000u);
+    p[1] = pack2(v.y << 16, v.y & 0xffff0000u);
+    p[2] = pack2(v.z << 16, v.z & 0xffff0000u);
+    p[3] = pack2(v.w << 16, v.w & 0xffff0000u);
+}
+
 // Sums V values per lane across the 32 lanes. On return v[g] (g < max(V/32, 1)) of lane l holds the warp sum of
 // value index g*32 + l (V >= 32) or l >> (5 - log2 V) (V < 32, every lane of a run of 32/V lanes the same sum).
 template <int V>
@@ -89,7 +114,7 @@ __global__ void __launch_bounds__(XS_THREADS, 1) matvec_xs_kernel(const MatvecXs
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
 
     // this thread's slice of the activations, widened once
-    float xf[M][CPT][8];
+    uint64_t xf[M][CPT][4];
 #pragma unroll
     for (int j = 0; j < CPT; ++j) {
         const uint32_t c = tid + j * XS_THREADS;
@@ -97,7 +122,7 @@ __global__ void __launch_bounds__(XS_THREADS, 1) matvec_xs_kernel(const MatvecXs
         for (int i = 0; i < M; ++i) {
             uint4 v = make_uint4(0, 0, 0, 0);
             if (c < p.k8 && (uint32_t)i < p.m) v = __ldg(p.x + (size_t)i * p.k8 + c);
-            widen8(v, xf[i][j]);
+            widen_pairs(v, xf[i][j]);
         }
     }
 
@@ -125,20 +150,23 @@ __global__ void __launch_bounds__(XS_THREADS, 1) matvec_xs_kernel(const MatvecXs
     for (uint32_t g = blockIdx.x; g < p.groups; g += gridDim.x) {
         const uint32_t next = g + gridDim.x;
         if (next < p.groups) load_group(next, wn);
-        float acc[V];
+        uint64_t acc2[V];
 #pragma unroll
-        for (int i = 0; i < V; ++i) acc[i] = 0.f;
+        for (int i = 0; i < V; ++i) acc2[i] = 0ull;
 #pragma unroll
         for (int r = 0; r < R; ++r)
 #pragma unroll
             for (int j = 0; j < CPT; ++j) {
-                float wf[8];
-                widen8(wv[r][j], wf);
+                uint64_t wp[4];
+                widen_pairs(wv[r][j], wp);
 #pragma unroll
                 for (int i = 0; i < M; ++i)
 #pragma unroll
-                    for (int e = 0; e < 8; ++e) acc[r * M + i] = __fmaf_rn(wf[e], xf[i][j][e], acc[r * M + i]);
+                    for (int e = 0; e < 4; ++e) acc2[r * M + i] = ffma2(wp[e], xf[i][j][e], acc2[r * M + i]);
             }
+        float acc[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) acc[i] = fold2(acc2[i]);
         warp_transpose_sum<V>(acc, lane);
         if constexpr (V >= 32) {
 #pragma unroll

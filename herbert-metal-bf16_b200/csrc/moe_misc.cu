@@ -141,19 +141,32 @@ __global__ void moe_combine_kernel(const uint16_t* __restrict__ y, const uint32_
         float acc[8];
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] = 0.f;
-        for (uint32_t s = 0; s < top_k; ++s) {
-            const uint4 v = *reinterpret_cast<const uint4*>(y + ((size_t)row * top_k + s) * d + c * 8);
-            const float w = __uint_as_float(route[(size_t)row * 2 * top_k + top_k + s]);
-            const uint32_t vw[4] = {v.x, v.y, v.z, v.w};
+        // slots in batches of eight: all of a batch's loads are issued before the first is used (the slot chain
+        // itself is sequential by contract, the loads need not be)
+        for (uint32_t s0 = 0; s0 < top_k; s0 += 8) {
+            uint4 v[8];
+            float w[8];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const float lo = bf16_to_f32(vw[j] & 0xffffu), hi = bf16_to_f32(vw[j] >> 16);
-                if (F32SUM) {
-                    acc[2 * j] = __fmaf_rn(lo, w, acc[2 * j]);
-                    acc[2 * j + 1] = __fmaf_rn(hi, w, acc[2 * j + 1]);
-                } else {
-                    acc[2 * j] = round_bf16(__fadd_rn(acc[2 * j], round_bf16(__fmul_rn(lo, w))));
-                    acc[2 * j + 1] = round_bf16(__fadd_rn(acc[2 * j + 1], round_bf16(__fmul_rn(hi, w))));
+            for (int b = 0; b < 8; ++b) {
+                const uint32_t s = min(s0 + b, top_k - 1);
+                v[b] = __ldcs(reinterpret_cast<const uint4*>(y + ((size_t)row * top_k + s) * d + c * 8));
+                w[b] = __uint_as_float(route[(size_t)row * 2 * top_k + top_k + s]);
+            }
+#pragma unroll
+            for (int b = 0; b < 8; ++b) {
+                if (s0 + b < top_k) {
+                    const uint32_t vw[4] = {v[b].x, v[b].y, v[b].z, v[b].w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float lo = bf16_to_f32(vw[j] & 0xffffu), hi = bf16_to_f32(vw[j] >> 16);
+                        if (F32SUM) {
+                            acc[2 * j] = __fmaf_rn(lo, w[b], acc[2 * j]);
+                            acc[2 * j + 1] = __fmaf_rn(hi, w[b], acc[2 * j + 1]);
+                        } else {
+                            acc[2 * j] = round_bf16(__fadd_rn(acc[2 * j], round_bf16(__fmul_rn(lo, w[b]))));
+                            acc[2 * j + 1] = round_bf16(__fadd_rn(acc[2 * j + 1], round_bf16(__fmul_rn(hi, w[b]))));
+                        }
+                    }
                 }
             }
         }
