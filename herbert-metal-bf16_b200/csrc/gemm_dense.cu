@@ -245,6 +245,7 @@ struct DenseGemm : hb_kernel {
 
 int make_gemm_experts(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out);
 int make_gemm_streamk(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out);
+int make_gemm_pair(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out);
 
 int make_gemm(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
     *out = nullptr;
@@ -253,7 +254,7 @@ int make_gemm(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
     if (d->k % 8 != 0) return fail(ctx, HB_UNSUPPORTED, "gemm: k must be a multiple of 8 (16-byte rows for TMA)");
     if (d->out > HB_OUT_SWIGLU) return fail(ctx, HB_INVALID, "gemm: unknown output mode");
     if (d->out == HB_OUT_SWIGLU && d->n % 2 != 0) return fail(ctx, HB_INVALID, "gemm: the SwiGLU form needs an even n ([gate | up])");
-    if (d->cta_pair) return fail(ctx, HB_UNSUPPORTED, "gemm: the CTA-pair form is not built");
+    if (d->cta_pair) return make_gemm_pair(ctx, d, out);
     if (d->stream_k) return make_gemm_streamk(ctx, d, out);
     const uint32_t bn = d->tile_n ? d->tile_n : 256;
     gemm_fn fn = nullptr;

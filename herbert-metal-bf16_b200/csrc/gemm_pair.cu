@@ -1,0 +1,331 @@
+// Prefill GEMM, CTA-pair form (hb_gemm_desc.cta_pair = 1): a cluster of two CTAs computes one 256 x 256 tile
+// with tcgen05.mma.cta_group::2.
+//
+// Why: with one CTA per 128 x 256 tile a pipeline stage is 48 KB (128 rows of X + 256 rows of W) and only four
+// fit in shared memory; the measured time still falls 6-10 % from three to four stages, i.e. the kernel is
+// short of bytes in flight. In a pair each CTA stages 128 rows of X (its half of the tile's rows) and 128 rows
+// of W (its half of the tile's columns): 32 KB per stage, seven stages, and every W row is read from shared
+// memory by one CTA only. The MMA is issued by the leader CTA (cluster rank 0) and reads both CTAs' shared
+// memory; each CTA's tensor memory receives its own 128 rows of the 256 x 256 accumulator and its own four
+// epilogue warps write them out.
+//
+// No TMA multicast anywhere: each CTA loads its own halves with an ordinary tiled load whose completion is
+// counted on the LEADER's stage barrier (cp.async.bulk.tensor with .cta_group::2 may signal the peer's
+// mbarrier). The leader's tcgen05.commit arrives on both CTAs' barriers (commit with .multicast::cluster).
+// SwiGLU: CTA 0 stages the gate rows, CTA 1 the matching up rows, so accumulator columns [0,128) are gate and
+// [128,256) up, as in the single-CTA kernel.
+// Every wait is bounded; both CTAs always reach the closing cluster barrier and free their tensor memory.
+#include <algorithm>
+#include <cstring>
+
+#include "gemm_common.cuh"
+
+namespace hb {
+
+constexpr int PAIR_BN = 256;
+constexpr int PAIR_B_BYTES = 128 * BK * 2;            // this CTA's half of the W tile
+constexpr int PAIR_STAGE_BYTES = A_BYTES + PAIR_B_BYTES;  // 32 KiB
+
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrival on a barrier that may live in the peer CTA (a shared::cluster address).
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Tiled load into this CTA's shared memory, bytes counted on a barrier of either CTA of the pair. Not a multicast.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* d, uint32_t bar_cluster_addr, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst), "l"((uint64_t)d), "r"(bar_cluster_addr), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t cols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() { asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// One arrival on the barrier at this offset in BOTH CTAs once the MMAs issued so far are done.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"(mask) : "memory");
+}
+
+template <int OUT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, const GemmParams p) {
+    constexpr uint32_t TMEM_COLS = 2 * PAIR_BN;  // two accumulators of 256 columns (this CTA's 128 rows of each)
+    constexpr uint32_t IDESC = umma_idesc_bf16(256, PAIR_BN);
+    constexpr int HALF = PAIR_BN / 2;
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ GemmBarriers bars;
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t S = p.stages;
+    const uint32_t rank = cluster_rank();
+    const uint32_t pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < S; ++s) {
+            mbar_init(smem_u32(&bars.full[s]), 1);   // used in the leader: its producer's expect_tx arrival
+            mbar_init(smem_u32(&bars.empty[s]), 1);  // the leader's commit, in both CTAs
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&bars.tmem_full[a]), 1);   // the leader's commit, in both CTAs
+            mbar_init(smem_u32(&bars.tmem_empty[a]), 8);  // used in the leader: four epilogue warps of each CTA
+        }
+        fence_mbar_init();
+        fence_proxy_async();
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(smem_u32(&bars.tmem_base), TMEM_COLS);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    cluster_sync_all();  // both CTAs' barriers exist before anything signals them
+    tc_fence_after();
+    const uint32_t tmem_base = bars.tmem_base;
+    // tiles: 256 rows x (256 columns, or 128 SwiGLU outputs)
+    const uint32_t tiles_m = (p.m + 255u) / 256u;
+    const uint32_t tiles_n = p.tiles_n;
+    const uint32_t num_tiles = tiles_m * tiles_n;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------- producer (one per CTA)
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_x);
+            tma_prefetch_desc(&tm_w);
+            uint32_t s = 0, ph = 0;
+            bool ok = true;
+            for (uint32_t tile = pair; ok && tile < num_tiles; tile += npairs) {
+                const uint32_t tm = p.m_first ? tile % tiles_m : tile / tiles_n;
+                const uint32_t tn = p.m_first ? tile / tiles_m : tile % tiles_n;
+                const int row_x = (int)(tm * 256 + rank * 128);
+                int row_w;
+                if constexpr (OUT == HB_OUT_SWIGLU) row_w = (int)(rank * p.n_out + tn * HALF);  // rank 0: gate rows, rank 1: up rows
+                else row_w = (int)(tn * PAIR_BN + rank * HALF);
+                for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait(smem_u32(&bars.empty[s]), ph ^ 1u)) {
+                        report(p.status, ST_WAIT_TIMEOUT, WHERE_EMPTY, s);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t full_leader = map_to_cta(smem_u32(&bars.full[s]), 0);
+                    const uint32_t a_dst = smem_base + s * PAIR_STAGE_BYTES;
+                    if (rank == 0) mbar_arrive_expect_tx(smem_u32(&bars.full[s]), 2 * PAIR_STAGE_BYTES);  // both CTAs' bytes
+                    tma_load_2d_pair(a_dst, &tm_x, full_leader, (int)(kb * BK), row_x);
+                    tma_load_2d_pair(a_dst + A_BYTES, &tm_w, full_leader, (int)(kb * BK), row_w);
+                    if (++s == S) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // --------------------------------------------------------- MMA issuer (leader CTA only)
+        if (lane == 0 && rank == 0) {
+            uint32_t s = 0, ph = 0, it = 0;
+            bool ok = true;
+            for (uint32_t tile = pair; ok && tile < num_tiles; tile += npairs, ++it) {
+                const uint32_t acc = it & 1u, acc_ph = (it >> 1) & 1u;
+                if (!mbar_wait(smem_u32(&bars.tmem_empty[acc]), acc_ph ^ 1u)) {
+                    report(p.status, ST_WAIT_TIMEOUT, WHERE_TMEM_EMPTY, acc);
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * PAIR_BN;
+                for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+                    if (!mbar_wait(smem_u32(&bars.full[s]), ph)) {
+                        report(p.status, ST_WAIT_TIMEOUT, WHERE_FULL, s);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t a_addr = smem_base + s * PAIR_STAGE_BYTES;
+                    const uint64_t a_desc = umma_desc_sw128(a_addr);
+                    const uint64_t b_desc = umma_desc_sw128(a_addr + A_BYTES);
+#pragma unroll
+                    for (uint32_t k4 = 0; k4 < BK / 16; ++k4)
+                        umma_bf16_pair(d_tmem, a_desc + 2 * k4, b_desc + 2 * k4, IDESC, (kb | k4) != 0 ? 1u : 0u);
+                    umma_commit_pair(smem_u32(&bars.empty[s]));
+                    if (++s == S) { s = 0; ph ^= 1u; }
+                }
+                if (ok) umma_commit_pair(smem_u32(&bars.tmem_full[acc]));
+            }
+        }
+    } else {
+        // ------------------------------------------------------------ epilogue (both CTAs: their own 128 rows)
+        const uint32_t q = (uint32_t)warp & 3u;
+        uint32_t it = 0;
+        for (uint32_t tile = pair; tile < num_tiles; tile += npairs, ++it) {
+            const uint32_t tm = p.m_first ? tile % tiles_m : tile / tiles_n;
+            const uint32_t tn = p.m_first ? tile / tiles_m : tile % tiles_n;
+            const uint32_t acc = it & 1u, acc_ph = (it >> 1) & 1u;
+            const bool got = mbar_wait(smem_u32(&bars.tmem_full[acc]), acc_ph);
+            if (!__all_sync(0xffffffffu, got)) {
+                if (lane == 0) report(p.status, ST_WAIT_TIMEOUT, WHERE_TMEM_FULL, acc);
+                break;
+            }
+            tc_fence_after();
+            const uint32_t row = tm * 256 + rank * 128 + q * 32 + lane;
+            const uint32_t t_addr = tmem_base + ((q * 32u) << 16) + acc * PAIR_BN;
+            if constexpr (OUT == HB_OUT_SWIGLU) {
+#pragma unroll 1
+                for (int c = 0; c < HALF / 32; ++c) {
+                    uint32_t g[32], u[32];
+                    tmem_ld_32x32(t_addr + c * 32, g);
+                    tmem_ld_32x32(t_addr + HALF + c * 32, u);
+                    tmem_ld_wait();
+                    store_chunk<OUT>(p, row, tn * HALF + c * 32, g, u);
+                }
+            } else {
+#pragma unroll 1
+                for (int c = 0; c < PAIR_BN / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(t_addr + c * 32, v);
+                    tmem_ld_wait();
+                    store_chunk<OUT>(p, row, tn * PAIR_BN + c * 32, v, v);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&bars.tmem_empty[acc]), 0));
+        }
+    }
+
+    tc_fence_before();
+    cluster_sync_all();  // nobody signals the peer's barriers or reads its shared memory after this
+    tc_fence_after();
+    if (warp == 1) tmem_dealloc_pair(tmem_base, TMEM_COLS);
+}
+
+// ------------------------------------------------------------------ host side
+
+namespace {
+
+typedef void (*pair_fn)(const CUtensorMap, const CUtensorMap, const GemmParams);
+
+pair_fn pair_pick(uint32_t out) {
+    switch (out) {
+        case HB_OUT_BF16: return gemm_bf16_tn_pair_kernel<HB_OUT_BF16>;
+        case HB_OUT_F32: return gemm_bf16_tn_pair_kernel<HB_OUT_F32>;
+        case HB_OUT_RESIDUAL: return gemm_bf16_tn_pair_kernel<HB_OUT_RESIDUAL>;
+        case HB_OUT_SWIGLU: return gemm_bf16_tn_pair_kernel<HB_OUT_SWIGLU>;
+    }
+    return nullptr;
+}
+
+struct PairGemm : hb_kernel {
+    hb_gemm_desc d{};
+    pair_fn fn = nullptr;
+    uint32_t stages = 0;
+    size_t smem = 0;
+    const void* last_w = nullptr;
+    const void* last_x = nullptr;
+    uint32_t last_m = 0;
+    CUtensorMap tm_x{}, tm_w{};
+
+    int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
+        if (na != 3) return fail(ctx, HB_INVALID, name + ": bindings are W, X, Y");
+        if (m == 0 || m > d.rows_max) return fail(ctx, HB_INVALID, name + ": m = " + std::to_string(m) + " outside 1.." + std::to_string(d.rows_max));
+        const uint32_t n_out = d.out == HB_OUT_SWIGLU ? d.n / 2 : d.n;
+        const size_t ybytes = (size_t)m * n_out * (d.out == HB_OUT_F32 ? 4 : 2);
+        if (!range_ok(a[0], (size_t)d.n * d.k * 2) || !range_ok(a[1], (size_t)m * d.k * 2) || !range_ok(a[2], ybytes))
+            return fail(ctx, HB_INVALID, name + ": a bound range is too small for " + std::to_string(m) + " rows");
+        if (a[0].ptr != last_w || a[1].ptr != last_x || m != last_m) {
+            int r = make_tmap_bf16(ctx, &tm_w, a[0].ptr, d.n, d.k, 128);
+            if (r != HB_OK) return r;
+            r = make_tmap_bf16(ctx, &tm_x, a[1].ptr, m, d.k, 128);
+            if (r != HB_OK) return r;
+            last_w = a[0].ptr;
+            last_x = a[1].ptr;
+            last_m = m;
+        }
+        GemmParams p{};
+        p.y = a[2].ptr;
+        p.m = m;
+        p.n_w = d.n;
+        p.n_out = n_out;
+        p.k_blocks = (d.k + BK - 1) / BK;
+        p.tiles_m = (m + 255) / 256;
+        const uint32_t cols_per_tile = d.out == HB_OUT_SWIGLU ? PAIR_BN / 2 : PAIR_BN;
+        p.tiles_n = (n_out + cols_per_tile - 1) / cols_per_tile;
+        p.num_tiles = p.tiles_m * p.tiles_n;
+        p.stages = stages;
+        p.m_first = d.m_first;
+        const uint32_t elem = d.out == HB_OUT_F32 ? 4 : 2;
+        p.vec_ok = ((reinterpret_cast<uintptr_t>(a[2].ptr) & 15u) == 0 && ((size_t)n_out * elem) % 16 == 0) ? 1u : 0u;
+        p.status = ctx->status_dev;
+        const uint32_t pairs = std::min<uint32_t>(p.num_tiles, (uint32_t)ctx->sm_count / 2);
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = dim3(2 * pairs);
+        cfg.blockDim = dim3(GEMM_THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = ctx->stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        HB_CUDA(ctx, cudaLaunchKernelEx(&cfg, fn, tm_x, tm_w, p));
+        ctx->launches++;
+        return HB_OK;
+    }
+};
+
+}  // namespace
+
+int make_gemm_pair(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
+    *out = nullptr;
+    if (d->tile_n != 0 && d->tile_n != 256) return fail(ctx, HB_UNSUPPORTED, "gemm: the CTA-pair form has 256 x 256 tiles only");
+    pair_fn fn = pair_pick(d->out);
+    const size_t budget = std::min<size_t>(ctx->smem_optin, 227 * 1024) - 2048;
+    const uint32_t max_stages = (uint32_t)std::min<size_t>(budget / PAIR_STAGE_BYTES, MAX_STAGES);
+    const uint32_t stages = d->stages ? d->stages : max_stages;
+    if (stages < 2 || stages > max_stages) return fail(ctx, HB_UNSUPPORTED, "gemm: stage count does not fit");
+    auto k = std::make_unique<PairGemm>();
+    k->d = *d;
+    k->d.tile_n = 256;
+    k->fn = fn;
+    k->stages = stages;
+    k->smem = (size_t)stages * PAIR_STAGE_BYTES + 1024;
+    k->kind = 1;
+    k->nargs = 3;
+    char nm[160];
+    snprintf(nm, sizeof nm, "gemm_pair_%ux%u_%s%s_t256x256_s%u", d->k, d->n, out_tag(d->out), d->m_first ? "_mf" : "", stages);
+    k->name = nm;
+    if (hb_kernel* have = find(ctx, k->name)) {
+        auto* g = static_cast<PairGemm*>(have);
+        g->d.rows_max = std::max(g->d.rows_max, d->rows_max);
+        *out = have;
+        return HB_OK;
+    }
+    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin - 1024);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(max dynamic shared memory)");
+    *out = intern(ctx, std::move(k));
+    return HB_OK;
+}
+
+}  // namespace hb

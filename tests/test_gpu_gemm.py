@@ -68,6 +68,26 @@ def test_stream_k_repeated_launches_and_config1(ctx, oracle):
         assert np.array_equal(first, d_y.download(np.uint16, (m, n)))  # a fixed summation order: the same bits every run
 
 
+@pytest.mark.parametrize("out", MODES)
+@pytest.mark.parametrize("m,k,n", [(300, 320, 520), (256, 64, 256), (1, 64, 72), (683, 1024, 1000), (2048, 4096, 1024), (257, 72, 40)])
+def test_cta_pair_form(ctx, oracle, out, m, k, n):
+    # two CTAs of a cluster share a 256 x 256 tile (tcgen05 cta_group::2): rows and columns that fill only one CTA's
+    # half, ragged extents, every output mode
+    if out == OUT_SWIGLU and n % 2:
+        pytest.skip("odd n")
+    kern, (x, w, y0), got = run_gemm(ctx, oracle, m, k, n, out, cta_pair=1)
+    assert kern.name.startswith("gemm_pair_")
+    within_contract(oracle, oracle.gemm_f64(x, w, out, y0), got, kern.name)
+
+
+def test_cta_pair_matches_single_cta_bits(ctx, oracle):
+    # the pair changes who stages what, not the order of the K loop: same bits as the 128 x 256 kernel
+    m, k, n = 512, 2048, 768
+    a = run_gemm(ctx, oracle, m, k, n, OUT_BF16, cta_pair=1)[2]
+    b = run_gemm(ctx, oracle, m, k, n, OUT_BF16, tile_n=256)[2]
+    assert np.array_equal(a, b)
+
+
 def test_config1_dense_gemm(ctx, oracle):
     # BASELINE config 1: M=512, K=1024, N=4096
     for m_first in (1, 0):
