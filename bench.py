@@ -187,7 +187,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the matvec / MoE / tensor-parallel sections")
     ap.add_argument("--tune", default="", help="engine tune keys, e.g. gemm.auto=0 to skip the load-time timing")
-    ap.add_argument("--case", default="", choices=["", "gate_up", "down", "matvec", "matvec8", "moe"],
+    ap.add_argument("--form", default="", choices=["", "pair", "sk"], help="with --case gate_up/down: the GEMM form")
+    ap.add_argument("--case", default="", choices=["", "layer", "gate_up", "down", "matvec", "matvec8", "moe"],
                     help="run one small case of one kernel a few times and exit (the command profiled under ncu)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -271,38 +272,72 @@ def main():
     ms_per_step = sec / args.steps * 1e3
     value = STEP_FLOP * world / (sec / args.steps) / 1e12
 
-    # ---- end to end: activations in from pinned host memory, result back out, every step
+    # ---- end to end: activations in from page-locked host memory, result back out, every step.
+    # Serial: upload, kernels, download, one after the other. Streamed: the same three per step through the
+    # library's copy lanes with two sets of device buffers, so the copies of one step run under the kernels
+    # of its neighbours; the host reads step i's result before it enqueues step i + 2.
     x_host = torch.empty(ROWS, HIDDEN, dtype=torch.bfloat16).pin_memory()
     x_host.copy_(x.cpu())
     y_host = torch.empty(ROWS, HIDDEN, dtype=torch.bfloat16).pin_memory()
     d_x, d_resid = wrap(x), wrap(resid)
     L = hb.lib()
+    io_bytes = ROWS * HIDDEN * 2
 
-    def e2e_step():
-        ctx._check(L.hb_upload(ctx.h, d_x.ptr, x_host.data_ptr(), ROWS * HIDDEN * 2))
+    def serial_step():
+        ctx._check(L.hb_upload(ctx.h, d_x.ptr, x_host.data_ptr(), io_bytes))
         ctx.run(ops)
-        ctx._check(L.hb_download(ctx.h, y_host.data_ptr(), d_resid.ptr, ROWS * HIDDEN * 2))
+        ctx._check(L.hb_download(ctx.h, y_host.data_ptr(), d_resid.ptr, io_bytes))
 
     for _ in range(3):
-        e2e_step()
+        serial_step()
     barrier()
     n_e2e = max(3, min(args.steps, 50))
     t0 = time.perf_counter()
     for _ in range(n_e2e):
-        e2e_step()
+        serial_step()
     torch.cuda.synchronize()
-    e2e_sec = max_over_ranks((time.perf_counter() - t0) / n_e2e)
+    serial_sec = max_over_ranks((time.perf_counter() - t0) / n_e2e)
+
+    x2 = x.clone()
+    resid2 = resid.clone()
+    ops2 = [(k, m, *[wrap(x2) if r.ptr == d_x.ptr else wrap(resid2) if r.ptr == d_resid.ptr else r for r in rs]) for (k, m, *rs) in ops]
+    xh = ctx.host_array((2, ROWS, HIDDEN))
+    yh = ctx.host_array((2, ROWS, HIDDEN))
+    xh[:] = x_host.view(torch.uint16).numpy()
+    blocks = hb.StreamedBlocks(ctx, [(ops, d_x, d_resid), (ops2, wrap(x2), wrap(resid2))])
+    n_str = max(4, args.steps)
+
+    def streamed(n):
+        for i in range(n):
+            if i >= 2:
+                blocks.wait(i - 2)  # the host has step i-2's result before its buffers are used again
+            blocks.step(i, xh[i % 2], yh[i % 2])
+        blocks.wait(n - 2)
+        blocks.wait(n - 1)
+
+    streamed(4)
+    ctx.sync()
+    barrier()
+    t0 = time.perf_counter()
+    streamed(n_str)
+    str_sec = max_over_ranks((time.perf_counter() - t0) / n_str)
+    ctx.sync()
+    blocks.close()
     sampler.active.clear()
     barrier()
-    e2e = {"value": STEP_FLOP * world / e2e_sec / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": ROWS * HIDDEN * 2, "d2h_bytes_per_step": ROWS * HIDDEN * 2,
-           "ms_per_step": e2e_sec * 1e3, "steps": n_e2e}
+    e2e = {"value": STEP_FLOP * world / str_sec / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes,
+           "ms_per_step": str_sec * 1e3, "steps": n_str, "mode": "streamed: copy lanes, 2 buffer sets, host reads every result",
+           "serial": {"value": STEP_FLOP * world / serial_sec / 1e12, "ms_per_step": serial_sec * 1e3, "steps": n_e2e}}
 
     per_gpu_tflops = value / world
     roofline = {
         "bound": "tensor", "achieved": per_gpu_tflops, "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": per_gpu_tflops / pk["bf16_tflops"],
-        "traffic": TRAFFIC_BYTES_PER_LAUNCH, "kernel": "gemm_bf16_tn_kernel", "peak_source": pk["source"] + " (burst cuBLAS bf16)",
+        "traffic": TRAFFIC_BYTES_PER_LAUNCH if all(v.startswith("gemm_pair_") for v in picks.values()) else None,
+        "kernel": "gemm_bf16_tn_pair_kernel" if all(v.startswith("gemm_pair_") for v in picks.values()) else "gemm_bf16_tn_kernel / gemm_bf16_tn_pair_kernel", "peak_source": pk["source"] + " (burst cuBLAS bf16)",
         "frac_of_sustained_peak": per_gpu_tflops / pk["bf16_tflops_sustained"], "frac_of_nominal_2250": per_gpu_tflops / 2250.0,
         "algorithmic_flop_per_launch": STEP_FLOP / 4, "launches_per_step": len(ops),
+        # operands once: 2(MK + NK + M N_out) bytes, plus the residual read where there is one, averaged over the four
+        "algorithmic_bytes_per_launch": sum(2.0 * (ROWS * k + n * k + ROWS * (n // 2 if o == 3 else n) * (2 if o == 2 else 1)) for _, k, n, o in LAYER) / 4,
     }
 
     extra = {"selection_seconds": t_sel, "picks": picks}
@@ -362,9 +397,20 @@ def run_case(args):
         w, x = rnd(n, k, scale=k**-0.5), rnd(ROWS, k)
         y = rnd(ROWS, n // 2 if out == 3 else n)
         torch.cuda.synchronize()
-        kern = ctx.gemm(k, n, out, rows_max=ROWS)
+        form = {"": {}, "pair": {"cta_pair": 1}, "sk": {"stream_k": 1}}[args.form]
+        kern = ctx.gemm(k, n, out, rows_max=ROWS, **form)
         ops = [(kern, ROWS, wrap(w), wrap(x), wrap(y))]
         work = {"flop": 2.0 * ROWS * k * n}
+    elif args.case == "layer":
+        # the bench's step in its picked forms: the four GEMMs of one layer on the CTA-pair kernel
+        ws = [rnd(n, k, scale=k**-0.5) for _, k, n, _ in LAYER]
+        x, hmid = rnd(ROWS, HIDDEN), rnd(ROWS, INTER)
+        qkv, resid = rnd(ROWS, 6144), rnd(ROWS, HIDDEN)
+        torch.cuda.synchronize()
+        ks = [ctx.gemm(k, n, out, rows_max=ROWS, cta_pair=1) for _, k, n, out in LAYER]
+        ops = [(ks[0], ROWS, wrap(ws[0]), wrap(x), wrap(qkv)), (ks[1], ROWS, wrap(ws[1]), wrap(x), wrap(resid)),
+               (ks[2], ROWS, wrap(ws[2]), wrap(x), wrap(hmid)), (ks[3], ROWS, wrap(ws[3]), wrap(hmid), wrap(resid))]
+        work = {"flop": STEP_FLOP}
     elif args.case in ("matvec", "matvec8"):
         m = 1 if args.case == "matvec" else 8
         k, n = 4096, 151936
@@ -386,8 +432,8 @@ def run_case(args):
         torch.cuda.synchronize()
         kw = dict(rows_max=m, top_k=top_k, experts=E, bm=bm)
         ops = [(ctx.route(E, top_k), m, wrap(scores), wrap(route)), (ctx.moe_sort(E, top_k, m, bm), m, wrap(route), wrap(lst), wrap(tiles)),
-               (ctx.gemm(h, 2 * mi, 3, rows_mode=hb.ROWS_GATHER, **kw), m, wrap(wgu), wrap(x), wrap(ehb), wrap(lst), wrap(tiles)),
-               (ctx.gemm(mi, h, 0, rows_mode=hb.ROWS_SCATTER, **kw), m, wrap(wd), wrap(ehb), wrap(ey), wrap(lst), wrap(tiles)),
+               (ctx.gemm(h, 2 * mi, 3, rows_mode=hb.ROWS_GATHER, merge_runs=1, **kw), m, wrap(wgu), wrap(x), wrap(ehb), wrap(lst), wrap(tiles)),
+               (ctx.gemm(mi, h, 0, rows_mode=hb.ROWS_SCATTER, merge_runs=1, **kw), m, wrap(wd), wrap(ehb), wrap(ey), wrap(lst), wrap(tiles)),
                (ctx.moe_combine(h, top_k), m, wrap(ey), wrap(route), wrap(out))]
         work = {"bytes": 2.0 * E * 3 * mi * h}
     ctx.time(ops, 2)
@@ -401,9 +447,9 @@ def run_case(args):
     ctx.close()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the GEMM kernel, averaged over the four launches of a
-# step, from the ncu capture summarised in profiles/ (None until that capture exists).
-TRAFFIC_BYTES_PER_LAUNCH = None
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the CTA-pair GEMM kernel, averaged over the four launches
+# of a step (72.3, 70.0, 257.8 and 236.4 MB), from the ncu capture summarised in profiles/.
+TRAFFIC_BYTES_PER_LAUNCH = 159.1e6
 
 
 def bench_extra(hb, ctx, sel, torch, dev, wrap, pk, rank, world, barrier, max_over_ranks):

@@ -93,6 +93,15 @@ def lib() -> C.CDLL:
         "hb_memset": (ci, [vp, vp, ci, sz]),
         "hb_sync": (ci, [vp]),
         "hb_launch_count": (C.c_uint64, [vp]),
+        "hb_event_new": (ci, [vp, pvp]),
+        "hb_event_free": (ci, [vp, vp]),
+        "hb_lane_record": (ci, [vp, ci, vp]),
+        "hb_lane_wait": (ci, [vp, ci, vp]),
+        "hb_event_sync": (ci, [vp, vp]),
+        "hb_upload_async": (ci, [vp, vp, vp, sz]),
+        "hb_download_async": (ci, [vp, vp, vp, sz]),
+        "hb_host_alloc": (ci, [vp, sz, pvp]),
+        "hb_host_free": (ci, [vp, vp]),
         "hb_gemm_get": (ci, [vp, C.POINTER(GemmDesc), pvp]),
         "hb_matvec_get": (ci, [vp, C.POINTER(MatvecDesc), pvp]),
         "hb_swiglu_get": (ci, [vp, u32, pvp]),
@@ -135,12 +144,79 @@ def lib() -> C.CDLL:
 
 EXPORTS = [
     "hb_open", "hb_close", "hb_last_error", "hb_describe", "hb_set_stream", "hb_alloc", "hb_set_alloc_limit", "hb_upload",
-    "hb_download", "hb_memset", "hb_sync", "hb_launch_count", "hb_gemm_get", "hb_matvec_get", "hb_swiglu_get", "hb_route_get",
+    "hb_download", "hb_memset", "hb_sync", "hb_launch_count", "hb_event_new", "hb_event_free", "hb_lane_record", "hb_lane_wait", "hb_event_sync",
+    "hb_upload_async", "hb_download_async", "hb_host_alloc", "hb_host_free", "hb_gemm_get", "hb_matvec_get", "hb_swiglu_get", "hb_route_get",
     "hb_moe_sort_get", "hb_moe_tiles", "hb_moe_gather_get", "hb_moe_combine_get", "hb_epilogue_get", "hb_gemm_static_scratch", "hb_kernel_name", "hb_launch", "hb_run", "hb_time",
     "hb_tune_new", "hb_tune_free", "hb_tune_apply", "hb_tune_get", "hb_tune_summary", "hb_tune_gemm_timed", "hb_selector_new",
     "hb_selector_free", "hb_selector_log", "hb_selector_buckets", "hb_fill_random16", "hb_select_gemm", "hb_select_gate_up",
     "hb_select_matvec", "hb_select_experts", "hb_selector_inject_wrong", "hb_check_rule",
 ]
+
+
+LANE_KERNELS, LANE_UPLOAD, LANE_DOWNLOAD = 0, 1, 2
+
+
+class Event:
+    """A mark in a lane of a Context: record it on one lane, make another lane (or the host) wait for it."""
+
+    def __init__(self, ctx: "Context", h):
+        self.ctx, self.h = ctx, h
+
+    def record(self, lane: int) -> "Event":
+        self.ctx._check(lib().hb_lane_record(self.ctx.h, lane, self.h))
+        return self
+
+    def wait(self, lane: int) -> None:
+        self.ctx._check(lib().hb_lane_wait(self.ctx.h, lane, self.h))
+
+    def sync(self) -> None:
+        self.ctx._check(lib().hb_event_sync(self.ctx.h, self.h))
+
+    def free(self) -> None:
+        if self.h:
+            lib().hb_event_free(self.ctx.h, self.h)
+            self.h = None
+
+
+class StreamedBlocks:
+    """Runs the same kernels over a stream of host blocks, the copies of one block under the kernels of another.
+
+    `sets` is a list (two or more) of (ops, device_in, device_out): the same kernels bound to separate device
+    buffers. step(i, host_in, host_out) enqueues upload -> kernels -> download of block i on buffer set
+    i % len(sets) and returns without waiting; the upload waits for the kernels that last read that set's input,
+    the kernels wait for the upload and for the download that last read that set's output. wait(i) blocks the
+    host until block i's result is in host_out.
+    """
+
+    def __init__(self, ctx: "Context", sets):
+        assert len(sets) >= 2
+        self.ctx, self.sets = ctx, sets
+        self.prepared = [ctx.make_ops(ops) + (len(ops),) for ops, _, _ in sets]  # the hb_op arrays, built once
+        self.up = [ctx.event() for _ in sets]
+        self.done = [ctx.event() for _ in sets]
+        self.down = [ctx.event() for _ in sets]
+
+    def step(self, i: int, host_in: np.ndarray, host_out: np.ndarray) -> None:
+        s = i % len(self.sets)
+        ops, d_in, d_out = self.sets[s]
+        self.done[s].wait(LANE_UPLOAD)      # the kernels that read this input two blocks ago
+        self.ctx.upload_async(d_in, host_in)
+        self.up[s].record(LANE_UPLOAD)
+        self.up[s].wait(LANE_KERNELS)
+        self.down[s].wait(LANE_KERNELS)     # the download that read this output two blocks ago
+        arr, _keep, nops = self.prepared[s]
+        self.ctx._check(lib().hb_run(self.ctx.h, arr, nops))
+        self.done[s].record(LANE_KERNELS)
+        self.done[s].wait(LANE_DOWNLOAD)
+        self.ctx.download_async(host_out, d_out)
+        self.down[s].record(LANE_DOWNLOAD)
+
+    def wait(self, i: int) -> None:
+        self.down[i % len(self.sets)].sync()
+
+    def close(self) -> None:
+        for e in self.up + self.done + self.down:
+            e.free()
 
 
 class Buffer:
@@ -242,6 +318,28 @@ class Context:
 
     def launch_count(self) -> int:
         return int(lib().hb_launch_count(self.h))
+
+    # ---- copy lanes (kernels 0, upload 1, download 2): in-order queues tied together by events
+    def event(self) -> "Event":
+        e = C.c_void_p()
+        self._check(lib().hb_event_new(self.h, C.byref(e)))
+        return Event(self, e)
+
+    def host_array(self, shape, dtype=np.uint16) -> np.ndarray:
+        """Page-locked host memory as a numpy array; it lives as long as the context."""
+        n = int(np.prod(shape)) * np.dtype(dtype).itemsize
+        p = C.c_void_p()
+        self._check(lib().hb_host_alloc(self.h, n, C.byref(p)))
+        raw = (C.c_uint8 * n).from_address(p.value)
+        return np.frombuffer(raw, dtype=dtype).reshape(shape)
+
+    def upload_async(self, dst: Buffer, src: np.ndarray) -> None:
+        assert src.flags.c_contiguous and src.nbytes <= dst.size
+        self._check(lib().hb_upload_async(self.h, dst.ptr, src.ctypes.data, src.nbytes))
+
+    def download_async(self, dst: np.ndarray, src: Buffer) -> None:
+        assert dst.flags.c_contiguous and dst.nbytes <= src.size
+        self._check(lib().hb_download_async(self.h, dst.ctypes.data, src.ptr, dst.nbytes))
 
     # ---- kernels
     def _get(self, fn, *args) -> Kernel:

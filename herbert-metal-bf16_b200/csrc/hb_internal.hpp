@@ -35,6 +35,8 @@ struct hb_ctx {
     cudaStream_t stream = nullptr;
     bool own_stream = false;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    cudaStream_t copy_lane[2] = {nullptr, nullptr};  // upload, download: made on first use
+    std::vector<void*> host_allocs;
     uint32_t* status_dev = nullptr;  // 8 words, see tc05.cuh
     std::string err;
     std::vector<void*> allocs;

@@ -132,6 +132,12 @@ int hb_close(hb_ctx* ctx) {
     cudaFree(ctx->status_dev);
     cudaEventDestroy(ctx->ev0);
     cudaEventDestroy(ctx->ev1);
+    for (cudaStream_t& c : ctx->copy_lane)
+        if (c) {
+            cudaStreamSynchronize(c);
+            cudaStreamDestroy(c);
+        }
+    for (void* p : ctx->host_allocs) cudaFreeHost(p);
     if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
     return HB_OK;
@@ -199,6 +205,111 @@ int hb_download(hb_ctx* ctx, void* dst, const void* src, size_t bytes) {
     HB_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
     HB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return hb::check_status(ctx);
+}
+
+// ---- copy lanes -------------------------------------------------------------------------------
+struct hb_event {
+    cudaEvent_t ev = nullptr;
+};
+
+namespace {
+int lane_stream(hb_ctx* ctx, int lane, cudaStream_t* out) {
+    if (lane == HB_LANE_KERNELS) {
+        *out = ctx->stream;
+        return HB_OK;
+    }
+    if (lane != HB_LANE_UPLOAD && lane != HB_LANE_DOWNLOAD) return fail(ctx, HB_INVALID, "no such lane");
+    cudaStream_t& c = ctx->copy_lane[lane - 1];
+    if (!c) HB_CUDA(ctx, cudaStreamCreateWithFlags(&c, cudaStreamNonBlocking));
+    *out = c;
+    return HB_OK;
+}
+}  // namespace
+
+int hb_event_new(hb_ctx* ctx, hb_event** out) {
+    if (!ctx || !out) return fail(ctx, HB_INVALID, "hb_event_new: bad argument");
+    auto* e = new hb_event;
+    cudaError_t st = cudaEventCreateWithFlags(&e->ev, cudaEventDisableTiming);
+    if (st != cudaSuccess) {
+        delete e;
+        return hb::cuda_fail(ctx, st, "cudaEventCreateWithFlags");
+    }
+    *out = e;
+    return HB_OK;
+}
+
+int hb_event_free(hb_ctx* ctx, hb_event* ev) {
+    if (!ev) return HB_OK;
+    cudaEventDestroy(ev->ev);
+    delete ev;
+    (void)ctx;
+    return HB_OK;
+}
+
+int hb_lane_record(hb_ctx* ctx, int lane, hb_event* ev) {
+    if (!ctx || !ev) return fail(ctx, HB_INVALID, "hb_lane_record: bad argument");
+    cudaStream_t s;
+    int r = lane_stream(ctx, lane, &s);
+    if (r != HB_OK) return r;
+    HB_CUDA(ctx, cudaEventRecord(ev->ev, s));
+    return HB_OK;
+}
+
+int hb_lane_wait(hb_ctx* ctx, int lane, const hb_event* ev) {
+    if (!ctx || !ev) return fail(ctx, HB_INVALID, "hb_lane_wait: bad argument");
+    cudaStream_t s;
+    int r = lane_stream(ctx, lane, &s);
+    if (r != HB_OK) return r;
+    HB_CUDA(ctx, cudaStreamWaitEvent(s, ev->ev, 0));
+    return HB_OK;
+}
+
+int hb_event_sync(hb_ctx* ctx, const hb_event* ev) {
+    if (!ctx || !ev) return fail(ctx, HB_INVALID, "hb_event_sync: bad argument");
+    HB_CUDA(ctx, cudaEventSynchronize(ev->ev));
+    return HB_OK;
+}
+
+int hb_upload_async(hb_ctx* ctx, void* dst, const void* src, size_t bytes) {
+    if (!ctx || !dst || !src) return fail(ctx, HB_INVALID, "hb_upload_async: bad argument");
+    cudaStream_t s;
+    int r = lane_stream(ctx, HB_LANE_UPLOAD, &s);
+    if (r != HB_OK) return r;
+    HB_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, s));
+    return HB_OK;
+}
+
+int hb_download_async(hb_ctx* ctx, void* dst, const void* src, size_t bytes) {
+    if (!ctx || !dst || !src) return fail(ctx, HB_INVALID, "hb_download_async: bad argument");
+    cudaStream_t s;
+    int r = lane_stream(ctx, HB_LANE_DOWNLOAD, &s);
+    if (r != HB_OK) return r;
+    HB_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, s));
+    return HB_OK;
+}
+
+int hb_host_alloc(hb_ctx* ctx, size_t bytes, void** host_ptr) {
+    if (!ctx || !host_ptr || bytes == 0) return fail(ctx, HB_INVALID, "hb_host_alloc: bad argument");
+    void* p = nullptr;
+    cudaError_t st = cudaHostAlloc(&p, bytes, cudaHostAllocDefault);
+    if (st != cudaSuccess) {
+        cudaGetLastError();
+        return fail(ctx, HB_OOM, std::string("hb_host_alloc: ") + cudaGetErrorString(st));
+    }
+    ctx->host_allocs.push_back(p);
+    *host_ptr = p;
+    return HB_OK;
+}
+
+int hb_host_free(hb_ctx* ctx, void* host_ptr) {
+    if (!ctx || !host_ptr) return HB_OK;
+    for (size_t i = 0; i < ctx->host_allocs.size(); ++i)
+        if (ctx->host_allocs[i] == host_ptr) {
+            ctx->host_allocs.erase(ctx->host_allocs.begin() + i);
+            HB_CUDA(ctx, cudaFreeHost(host_ptr));
+            return HB_OK;
+        }
+    return fail(ctx, HB_INVALID, "hb_host_free: not a pointer of hb_host_alloc");
 }
 
 int hb_memset(hb_ctx* ctx, void* dst, int value, size_t bytes) {

@@ -425,7 +425,7 @@ int hb_select_gate_up(hb_selector* s, uint32_t k, uint32_t inter, hb_range w, hb
             if ((r = apart(&ks)) != HB_OK) return r;
         } else if (fswi == 1 || !t.gemm_timed()) {
             hb_kernel* f = nullptr;
-            if ((r = get_dense(s, k, 2 * inter, HB_OUT_SWIGLU, 256, 0, mf, 0, rows_max, &f)) != HB_OK) return r;
+            if ((r = get_dense(s, k, 2 * inter, HB_OUT_SWIGLU, 256, 0, mf, t.get("gemm.mma") == 3 ? 1u : 0u, rows_max, &f)) != HB_OK) return r;
             ks = {f};
         } else {
             const std::string key = std::to_string(k) + "x" + std::to_string(2 * inter) + ", " + std::to_string(m) + " rows";
@@ -443,11 +443,12 @@ int hb_select_gate_up(hb_selector* s, uint32_t k, uint32_t inter, hb_range w, hb
                 add_op(c0, ap[1], {gu, h});
                 cands.push_back(std::move(c0));
                 eligible.push_back(1);
-                for (uint32_t form = 0; form < 6; ++form) {
-                    const uint32_t tn = 256u >> (form % 3), sk = form / 3;
+                for (uint32_t form = 0; form < 7; ++form) {
+                    const uint32_t pair = form == 6 ? 1u : 0u;
+                    const uint32_t tn = pair ? 256u : 256u >> (form % 3), sk = pair ? 0u : form / 3;
                     hb_kernel* f = nullptr;
-                    const std::string name = std::string(sk ? "fusedsk128x" : "fused128x") + std::to_string(tn);
-                    if (get_dense(s, k, 2 * inter, HB_OUT_SWIGLU, tn, 0, mf, 0, rows_max, &f, sk) != HB_OK) {
+                    const std::string name = pair ? std::string("fusedpair256x256") : std::string(sk ? "fusedsk128x" : "fused128x") + std::to_string(tn);
+                    if (get_dense(s, k, 2 * inter, HB_OUT_SWIGLU, tn, 0, mf, pair, rows_max, &f, sk) != HB_OK) {
                         say(s, "[autotune] gate_up " + key + ": " + name + " not built (" + hb_last_error(ctx) + ")");
                         continue;
                     }

@@ -100,6 +100,28 @@ int hb_sync(hb_ctx* ctx);
 /* Number of kernels this context has enqueued so far. */
 uint64_t hb_launch_count(const hb_ctx* ctx);
 
+/* ---- copy lanes ---------------------------------------------------------
+ * The reference's buffers are shared between CPU and GPU (src/metal/gpu.rs:92-110), so its engine
+ * never copies activations. On a discrete GPU a prompt block crosses PCIe both ways; these calls let
+ * the engine overlap the copies of one block with the kernels of another. A context has three lanes,
+ * each an in-order queue: the kernels' lane (hb_launch, hb_run, hb_memset and the synchronous copies
+ * above), an upload lane and a download lane. Nothing orders one lane against another except events:
+ * hb_lane_record marks the work a lane holds so far, hb_lane_wait makes a lane's later work wait for
+ * a mark on the device (the host does not block), hb_event_sync makes the host wait. Waiting for an
+ * event that was never recorded returns at once. Host memory of the asynchronous copies must come
+ * from hb_host_alloc (page-locked); with pageable memory the copies still happen but do not overlap. */
+typedef struct hb_event hb_event;
+enum { HB_LANE_KERNELS = 0, HB_LANE_UPLOAD = 1, HB_LANE_DOWNLOAD = 2 };
+int hb_event_new(hb_ctx* ctx, hb_event** out);
+int hb_event_free(hb_ctx* ctx, hb_event* ev);
+int hb_lane_record(hb_ctx* ctx, int lane, hb_event* ev);
+int hb_lane_wait(hb_ctx* ctx, int lane, const hb_event* ev);
+int hb_event_sync(hb_ctx* ctx, const hb_event* ev);
+int hb_upload_async(hb_ctx* ctx, void* dst_device, const void* src_host, size_t bytes);   /* upload lane */
+int hb_download_async(hb_ctx* ctx, void* dst_host, const void* src_device, size_t bytes); /* download lane */
+int hb_host_alloc(hb_ctx* ctx, size_t bytes, void** host_ptr);
+int hb_host_free(hb_ctx* ctx, void* host_ptr);
+
 /* ---- kernels ------------------------------------------------------------ */
 
 /* Prefill GEMM Y[m][n] = out(X[m][k] . W[n][k]^T), bf16 inputs, f32 accumulation on the tensor cores.

@@ -1,0 +1,73 @@
+"""Copy lanes: uploads and downloads that overlap the kernels, ordered by events (include/hb200.h).
+
+The streamed form must give, block by block, the bits of the plain upload -> kernels -> download sequence,
+whatever the interleaving, and the host must be able to read block i as soon as wait(i) returns.
+"""
+import numpy as np
+import pytest
+
+from gpu_util import gemm_inputs, within_contract
+from oracle_lib import OUT_BF16, OUT_RESIDUAL
+
+pytestmark = pytest.mark.gpu
+
+
+def test_streamed_blocks_match_serial(ctx, hb200, oracle):
+    m, k, n, blocks_n = 256, 512, 768, 7
+    x0, w, y0 = gemm_inputs(oracle, m, k, n)
+    rng = np.random.default_rng(5)
+    xs = [np.ascontiguousarray(np.roll(x0, int(rng.integers(1, m)), axis=0)) for _ in range(blocks_n)]
+    d_w = ctx.to_device(w)
+    kern = ctx.gemm(k, n, OUT_BF16, rows_max=m)
+    # serial
+    want = []
+    d_x, d_y = ctx.alloc(m * k * 2), ctx.alloc(m * n * 2)
+    for x in xs:
+        d_x.upload(x)
+        kern(m, d_w, d_x, d_y)
+        want.append(d_y.download(np.uint16, (m, n)))
+    # streamed over three buffer sets
+    sets = []
+    for _ in range(3):
+        dx, dy = ctx.alloc(m * k * 2), ctx.alloc(m * n * 2)
+        sets.append(([(kern, m, d_w, dx, dy)], dx, dy))
+    sb = hb200.StreamedBlocks(ctx, sets)
+    h_in = ctx.host_array((blocks_n, m, k))
+    h_out = ctx.host_array((blocks_n, m, n))
+    for i, x in enumerate(xs):
+        h_in[i] = x
+    for i in range(blocks_n):
+        sb.step(i, h_in[i], h_out[i])
+        if i >= 1:
+            sb.wait(i - 1)
+            assert np.array_equal(h_out[i - 1], want[i - 1]), f"block {i - 1}"
+    sb.wait(blocks_n - 1)
+    assert np.array_equal(h_out[blocks_n - 1], want[blocks_n - 1])
+    within_contract(oracle, oracle.gemm_f64(xs[-1], w), h_out[blocks_n - 1], "streamed block")
+    sb.close()
+    ctx.sync()
+
+
+def test_events_order_lanes(ctx, hb200, oracle):
+    # a download enqueued before the kernels' lane has run must still see the kernels' output
+    m, k, n = 128, 256, 256
+    x, w, y0 = gemm_inputs(oracle, m, k, n)
+    d_w, d_x, d_y = ctx.to_device(w), ctx.alloc(m * k * 2), ctx.to_device(y0)
+    h_x, h_y = ctx.host_array((m, k)), ctx.host_array((m, n))
+    h_x[:] = x
+    up, done = ctx.event(), ctx.event()
+    never = ctx.event()
+    never.wait(hb200.LANE_KERNELS)  # an event nobody recorded does not block
+    ctx.upload_async(d_x, h_x)
+    up.record(hb200.LANE_UPLOAD).wait(hb200.LANE_KERNELS)
+    ctx.gemm(k, n, OUT_RESIDUAL, rows_max=m)(m, d_w, d_x, d_y)
+    done.record(hb200.LANE_KERNELS).wait(hb200.LANE_DOWNLOAD)
+    ctx.download_async(h_y, d_y)
+    fin = ctx.event().record(hb200.LANE_DOWNLOAD)
+    fin.sync()
+    within_contract(oracle, oracle.gemm_f64(x, w, OUT_RESIDUAL, y0), np.array(h_y), "residual through lanes")
+    for e in (up, done, never, fin):
+        e.free()
+    with pytest.raises(hb200.HbError):
+        ctx.event().record(7)
+    ctx.sync()

@@ -28,7 +28,7 @@ def test_gemm_selection_logs_and_caches(ctx, hb200, oracle):
     log = sel.log()
     line = [l for l in log.splitlines() if l.startswith("[autotune] gemm 1024x2048 Bf16, 512 rows: ") and " -> " in l]
     assert len(line) == 1
-    assert re.search(r"t128x256 \d+\.\d{3} ms, t128x128 \d+\.\d{3} ms, t128x64 \d+\.\d{3} ms.* -> (t|sk)128x\d+n?$", line[0]) and "sk128x256 " in line[0]
+    assert re.search(r"t128x256 \d+\.\d{3} ms, t128x128 \d+\.\d{3} ms, t128x64 \d+\.\d{3} ms.* -> ((t|sk)128x\d+n?|pair256x256)$", line[0]) and "sk128x256 " in line[0] and "pair256x256 " in line[0]
     assert "wrong" not in log
     # (Y is scratch during selection: the check restores it, the timing rounds that follow write it again,
     # as in the reference where the loop runs at load before any prompt)
