@@ -584,10 +584,21 @@ def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks)
                 sc = torch.randn(m, E, device=dev, generator=g).bfloat16()[rank * rl : (rank + 1) * rl].contiguous()
                 wgu_l = (torch.randn(epr * 2 * mi, h, device=dev, generator=gl) * h**-0.5).bfloat16()
                 wd_l = (torch.randn(epr * h, mi, device=dev, generator=gl) * mi**-0.5).bfloat16()
-                sec = timed(lambda: D.ep_moe(be, xs, sc, wgu_l, wd_l, E, top_k, mi, bm), 3, 10)
                 wbytes = 2.0 * E * 3 * mi * h
+                # the exchange through peer memory by the library's own kernels (the production form) ...
+                st = D.EpPeer(hb, ctx, rank, world, rl, h, mi, E, top_k, bm)
+                D.ep_peer_connect(st)
+                got = D.ep_moe_peer(st, xs, sc, wgu_l, wd_l).clone()
+                sec = timed(lambda: D.ep_moe_peer(st, xs, sc, wgu_l, wd_l), 3, 20)
+                # ... and the same block with the rows exchanged by NCCL all-to-all, host-known counts (the baseline form)
+                ref = D.ep_moe(be, xs, sc, wgu_l, wd_l, E, top_k, mi, bm)
+                same = bool(torch.equal(ref, got))
+                sec_nccl = timed(lambda: D.ep_moe(be, xs, sc, wgu_l, wd_l, E, top_k, mi, bm), 2, 5)
+                barrier()
+                st.close()
                 out["moe_ep_2048tok"] = {"n_gpus": world, "us": sec * 1e6, "weight_gbs_total": wbytes / sec / 1e9, "tokens_per_s": m / sec, "scaling": "strong",
-                                         "tile_rows": bm}
+                                         "tile_rows": bm, "exchange": "peer-memory stores and loads in ep_dispatch / ep_return, 1 all-gather of 1 KB + 2 barriers",
+                                         "nccl_all_to_all_form_us": sec_nccl * 1e6, "equals_nccl_form_bitwise": same}
     finally:
         stream.synchronize()
         ctx.set_stream(None)

@@ -93,6 +93,12 @@ def lib() -> C.CDLL:
         "hb_memset": (ci, [vp, vp, ci, sz]),
         "hb_sync": (ci, [vp]),
         "hb_launch_count": (C.c_uint64, [vp]),
+        "hb_ipc_export": (ci, [vp, vp, vp]),
+        "hb_ipc_open": (ci, [vp, vp, pvp]),
+        "hb_ipc_close": (ci, [vp, vp]),
+        "hb_ep_dispatch_get": (ci, [vp, u32, u32, u32, u32, u32, u32, pvp]),
+        "hb_ep_return_get": (ci, [vp, u32, u32, u32, u32, u32, u32, pvp]),
+        "hb_ep_plan_get": (ci, [vp, u32, u32, u32, u32, u32, pvp]),
         "hb_event_new": (ci, [vp, pvp]),
         "hb_event_free": (ci, [vp, vp]),
         "hb_lane_record": (ci, [vp, ci, vp]),
@@ -145,7 +151,8 @@ def lib() -> C.CDLL:
 EXPORTS = [
     "hb_open", "hb_close", "hb_last_error", "hb_describe", "hb_set_stream", "hb_alloc", "hb_set_alloc_limit", "hb_upload",
     "hb_download", "hb_memset", "hb_sync", "hb_launch_count", "hb_event_new", "hb_event_free", "hb_lane_record", "hb_lane_wait", "hb_event_sync",
-    "hb_upload_async", "hb_download_async", "hb_host_alloc", "hb_host_free", "hb_gemm_get", "hb_matvec_get", "hb_swiglu_get", "hb_route_get",
+    "hb_upload_async", "hb_download_async", "hb_host_alloc", "hb_host_free", "hb_ipc_export", "hb_ipc_open", "hb_ipc_close",
+    "hb_ep_dispatch_get", "hb_ep_plan_get", "hb_ep_return_get", "hb_gemm_get", "hb_matvec_get", "hb_swiglu_get", "hb_route_get",
     "hb_moe_sort_get", "hb_moe_tiles", "hb_moe_gather_get", "hb_moe_combine_get", "hb_epilogue_get", "hb_gemm_static_scratch", "hb_kernel_name", "hb_launch", "hb_run", "hb_time",
     "hb_tune_new", "hb_tune_free", "hb_tune_apply", "hb_tune_get", "hb_tune_summary", "hb_tune_gemm_timed", "hb_selector_new",
     "hb_selector_free", "hb_selector_log", "hb_selector_buckets", "hb_fill_random16", "hb_select_gemm", "hb_select_gate_up",
@@ -318,6 +325,29 @@ class Context:
 
     def launch_count(self) -> int:
         return int(lib().hb_launch_count(self.h))
+
+    # ---- peer memory
+    def ipc_export(self, buf: "Buffer") -> bytes:
+        h = C.create_string_buffer(64)
+        self._check(lib().hb_ipc_export(self.h, buf.ptr, h))
+        return h.raw
+
+    def ipc_open(self, handle: bytes, nbytes: int) -> "Buffer":
+        p = C.c_void_p()
+        self._check(lib().hb_ipc_open(self.h, handle, C.byref(p)))
+        return Buffer(self, p.value, nbytes)
+
+    def ipc_close(self, buf: "Buffer") -> None:
+        self._check(lib().hb_ipc_close(self.h, buf.ptr))
+
+    def ep_dispatch(self, h, top_k, experts, world, rank, cap) -> "Kernel":
+        return self._get(lib().hb_ep_dispatch_get, h, top_k, experts, world, rank, cap)
+
+    def ep_return(self, h, top_k, experts, world, rank, cap) -> "Kernel":
+        return self._get(lib().hb_ep_return_get, h, top_k, experts, world, rank, cap)
+
+    def ep_plan(self, experts, world, rank, bm, cap) -> "Kernel":
+        return self._get(lib().hb_ep_plan_get, experts, world, rank, bm, cap)
 
     # ---- copy lanes (kernels 0, upload 1, download 2): in-order queues tied together by events
     def event(self) -> "Event":

@@ -1,0 +1,265 @@
+// Expert-parallel exchange over peer memory: the token rows of an MoE block travel to the GPUs that hold their
+// experts, and the expert outputs travel back, as plain stores and loads through NVLink inside three small kernels -
+// no host-side counts, no variable-size collective.
+//
+// Every rank sorts its (row, slot) pairs by GLOBAL expert (the sort kernel, which also writes the first sorted
+// position of every expert: `offs[experts + 1]`). Experts are partitioned contiguously, `epr` per rank, so the sorted
+// list is at the same time grouped by destination rank. After an all-gather of the offset vectors every rank knows,
+// for every source s and expert e, how many rows s sends for e: cnt(s, e) = offs[s][e + 1] - offs[s][e].
+//
+//   receive buffer of rank d:  [rows of source 0 | rows of source 1 | ...], each source's rows in its sorted order
+//                              (expert ascending, pair ascending within an expert)
+//   ep_dispatch (source side): sorted position p -> d = rank of its expert, row base(d, s) + (p - first(s, d)) of d's
+//                              receive buffer, where first(s, d) = offs[s][d * epr] and base(d, s) is the number of
+//                              rows the sources below s send to d. The row X[list[p] / top_k] is written there.
+//   ep_plan (owner side):      the list and the tile table the expert GEMMs need, built from the counts alone:
+//                              local expert e owns, from source 0, 1, ..., a contiguous range of the receive buffer
+//                              each. Expert-major, then source, then the source's pair order: the concatenation over
+//                              the ranks is the order a single GPU's sort would give the same pairs.
+//   ep_return (source side):   EY[list[p]] = row (base(d, s) + p - first(s, d)) of d's output buffer, read from d.
+//
+// A kernel of this file never waits for another GPU: the steps are separated by the host's collectives on the stream
+// (the all-gather of the offsets before the dispatch, a barrier after it and another after the expert GEMMs).
+// No reference counterpart: the reference runs on one GPU.
+#include <algorithm>
+
+#include "hb_internal.hpp"
+#include "tc05.cuh"
+
+namespace hb {
+
+constexpr int EP_MAX_WORLD = 16;
+
+struct EpParams {
+    const uint4* x;            // dispatch: X [rows][h]; return: unused
+    uint4* ey;                 // return: EY [pairs][h]
+    const uint32_t* list;      // this rank's sorted list
+    const uint32_t* offs_all;  // [world][experts + 1]
+    const uint64_t* peers;     // [world] base of every rank's receive (dispatch) or output (return) buffer
+    uint32_t h8, top_k, experts, world, rank, epr, cap;
+    uint32_t* status;
+};
+
+// first[d], base[d] for this rank as a source, in shared memory.
+__device__ __forceinline__ void ep_source_tables(const EpParams& p, uint32_t* first, uint32_t* base) {
+    const uint32_t stride = p.experts + 1;
+    if (threadIdx.x < p.world) {
+        const uint32_t d = threadIdx.x;
+        first[d] = p.offs_all[p.rank * stride + d * p.epr];
+        uint32_t b = 0;
+        for (uint32_t s = 0; s < p.rank; ++s) b += p.offs_all[s * stride + (d + 1) * p.epr] - p.offs_all[s * stride + d * p.epr];
+        base[d] = b;
+    }
+    if (threadIdx.x == 0) first[p.world] = p.offs_all[p.rank * stride + p.experts];
+    __syncthreads();
+}
+
+template <bool RETURN>
+__global__ void __launch_bounds__(256) ep_move_kernel(const EpParams p) {
+    __shared__ uint32_t first[EP_MAX_WORLD + 1], base[EP_MAX_WORLD];
+    ep_source_tables(p, first, base);
+    const uint32_t pairs = first[p.world];
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    // a warp per sorted position: the destination is found once per row, the row moves as 16-byte pieces
+    for (uint32_t pos = blockIdx.x * warps + warp; pos < pairs; pos += gridDim.x * warps) {
+        uint32_t d = 0;
+        while (d + 1 < p.world && pos >= first[d + 1]) ++d;
+        const uint32_t r = base[d] + pos - first[d];
+        if (r >= p.cap) {  // the counts do not fit the buffers the host sized: report, move nothing
+            if (lane == 0) report(p.status, ST_BAD_TABLE, pos, r);
+            continue;
+        }
+        const uint32_t pair = p.list[pos];
+        uint4* remote = reinterpret_cast<uint4*>(p.peers[d]) + (size_t)r * p.h8;
+        if constexpr (RETURN) {
+            uint4* dst = p.ey + (size_t)pair * p.h8;
+            for (uint32_t c = lane; c < p.h8; c += 32) dst[c] = remote[c];
+        } else {
+            const uint4* src = p.x + (size_t)(pair / p.top_k) * p.h8;
+            for (uint32_t c = lane; c < p.h8; c += 32) remote[c] = src[c];
+        }
+    }
+}
+
+struct PlanParams {
+    const uint32_t* offs_all;
+    uint32_t* list;
+    uint32_t* tiles;
+    uint32_t experts, world, rank, epr, bm, cap;
+    uint32_t* status;
+};
+
+constexpr int PLAN_THREADS = 1024;
+
+__global__ void __launch_bounds__(PLAN_THREADS) ep_plan_kernel(const PlanParams p) {
+    extern __shared__ uint32_t sm[];
+    uint32_t* start = sm;                  // [epr] first sorted row of local expert e
+    uint32_t* sa = start + p.epr;          // [epr] scan scratch (rows)
+    uint32_t* st = sa + p.epr;             // [epr] scan scratch (tiles)
+    uint32_t* recvbase = st + p.epr;       // [world] first receive row of source s
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t stride = p.experts + 1, e0 = p.rank * p.epr;
+    if (tid == 0) {
+        uint32_t b = 0;
+        for (uint32_t s = 0; s < p.world; ++s) {
+            recvbase[s] = b;
+            b += p.offs_all[s * stride + e0 + p.epr] - p.offs_all[s * stride + e0];
+        }
+    }
+    uint32_t total_e = 0;
+    if (tid < p.epr)
+        for (uint32_t s = 0; s < p.world; ++s) total_e += p.offs_all[s * stride + e0 + tid + 1] - p.offs_all[s * stride + e0 + tid];
+    const uint32_t ntile_e = (total_e + p.bm - 1) / p.bm;
+    uint32_t a = total_e, t = ntile_e;
+    if (tid < p.epr) { sa[tid] = a; st[tid] = t; }
+    __syncthreads();
+    for (uint32_t d = 1; d < p.epr; d <<= 1) {
+        uint32_t va = 0, vt = 0;
+        if (tid < p.epr && tid >= d) { va = sa[tid - d]; vt = st[tid - d]; }
+        __syncthreads();
+        if (tid < p.epr) { a += va; t += vt; sa[tid] = a; st[tid] = t; }
+        __syncthreads();
+    }
+    if (tid < p.epr) {
+        const uint32_t s0 = a - total_e, tfirst = t - ntile_e;
+        start[tid] = s0;
+        if (a <= p.cap) {
+            for (uint32_t j = 0, ti = tfirst; j < total_e; j += p.bm, ++ti) {
+                p.tiles[1 + 3 * ti] = tid;
+                p.tiles[2 + 3 * ti] = s0 + j;
+                p.tiles[3 + 3 * ti] = min(p.bm, total_e - j);
+            }
+        }
+        if (tid == p.epr - 1) {
+            if (a <= p.cap) {
+                p.tiles[0] = t;
+            } else {  // more rows than the buffers hold: an empty table, and the host learns why
+                p.tiles[0] = 0;
+                report(p.status, ST_BAD_TABLE, a, p.cap);
+            }
+        }
+    }
+    __syncthreads();
+    if (sa[p.epr - 1] > p.cap) return;
+    // the list: a warp per local expert, the sources in rank order, each a contiguous range of the receive buffer
+    for (uint32_t e = warp; e < p.epr; e += PLAN_THREADS / 32) {
+        uint32_t pos = start[e];
+        for (uint32_t s = 0; s < p.world; ++s) {
+            const uint32_t lo = p.offs_all[s * stride + e0 + e], hi = p.offs_all[s * stride + e0 + e + 1];
+            const uint32_t src0 = recvbase[s] + lo - p.offs_all[s * stride + e0];
+            for (uint32_t j = lane; j < hi - lo; j += 32) p.list[pos + j] = src0 + j;
+            pos += hi - lo;
+        }
+    }
+}
+
+namespace {
+
+uint32_t ep_grid(hb_ctx* ctx, uint32_t rows) { return std::max(1u, std::min<uint32_t>((rows + 7) / 8, (uint32_t)ctx->sm_count * 8)); }
+
+struct EpMove : hb_kernel {
+    uint32_t h = 0, top_k = 0, experts = 0, world = 0, rank = 0, cap = 0;
+    bool ret = false;
+    int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
+        if (na != 4) return fail(ctx, HB_INVALID, name + (ret ? ": bindings are peers, EY, list, offsets" : ": bindings are X, peers, list, offsets"));
+        if (m == 0) return fail(ctx, HB_INVALID, name + ": m = 0");
+        const uint32_t pairs = m * top_k;
+        const hb_range& rows = ret ? a[1] : a[0];
+        const hb_range& peers = ret ? a[0] : a[1];
+        if (!range_ok(rows, (size_t)(ret ? pairs : m) * h * 2) || !range_ok(peers, (size_t)world * 8) || !range_ok(a[2], (size_t)pairs * 4) ||
+            !range_ok(a[3], (size_t)world * (experts + 1) * 4))
+            return fail(ctx, HB_INVALID, name + ": a bound range is too small");
+        if (reinterpret_cast<uintptr_t>(rows.ptr) & 15u) return fail(ctx, HB_INVALID, name + ": rows must be 16-byte aligned");
+        EpParams p{};
+        p.x = ret ? nullptr : static_cast<const uint4*>(rows.ptr);
+        p.ey = ret ? static_cast<uint4*>(rows.ptr) : nullptr;
+        p.peers = static_cast<const uint64_t*>(peers.ptr);
+        p.list = static_cast<const uint32_t*>(a[2].ptr);
+        p.offs_all = static_cast<const uint32_t*>(a[3].ptr);
+        p.h8 = h / 8;
+        p.top_k = top_k;
+        p.experts = experts;
+        p.world = world;
+        p.rank = rank;
+        p.epr = experts / world;
+        p.cap = cap;
+        p.status = ctx->status_dev;
+        if (ret) ep_move_kernel<true><<<ep_grid(ctx, pairs), 256, 0, ctx->stream>>>(p);
+        else ep_move_kernel<false><<<ep_grid(ctx, pairs), 256, 0, ctx->stream>>>(p);
+        HB_CUDA(ctx, cudaGetLastError());
+        ctx->launches++;
+        return HB_OK;
+    }
+};
+
+struct EpPlan : hb_kernel {
+    uint32_t experts = 0, world = 0, rank = 0, bm = 0, cap = 0;
+    int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
+        if (na != 3) return fail(ctx, HB_INVALID, name + ": bindings are offsets, list, tiles");
+        (void)m;
+        const uint32_t epr = experts / world;
+        if (!range_ok(a[0], (size_t)world * (experts + 1) * 4) || !range_ok(a[1], (size_t)cap * 4) ||
+            !range_ok(a[2], (1 + 3 * (size_t)hb_moe_tiles(cap, 1, epr, bm)) * 4))
+            return fail(ctx, HB_INVALID, name + ": a bound range is too small");
+        PlanParams p{};
+        p.offs_all = static_cast<const uint32_t*>(a[0].ptr);
+        p.list = static_cast<uint32_t*>(a[1].ptr);
+        p.tiles = static_cast<uint32_t*>(a[2].ptr);
+        p.experts = experts;
+        p.world = world;
+        p.rank = rank;
+        p.epr = epr;
+        p.bm = bm;
+        p.cap = cap;
+        p.status = ctx->status_dev;
+        ep_plan_kernel<<<1, PLAN_THREADS, (3 * epr + world) * 4, ctx->stream>>>(p);
+        HB_CUDA(ctx, cudaGetLastError());
+        ctx->launches++;
+        return HB_OK;
+    }
+};
+
+bool ep_shape_ok(uint32_t experts, uint32_t world, uint32_t rank) {
+    return world >= 1 && world <= EP_MAX_WORLD && rank < world && experts >= world && experts % world == 0 && experts <= 1024;
+}
+
+}  // namespace
+
+int make_ep_move(hb_ctx* ctx, bool ret, uint32_t h, uint32_t top_k, uint32_t experts, uint32_t world, uint32_t rank, uint32_t cap, hb_kernel** out) {
+    *out = nullptr;
+    if (!ep_shape_ok(experts, world, rank) || h == 0 || h % 8 != 0 || top_k == 0 || cap == 0)
+        return fail(ctx, HB_UNSUPPORTED, "ep exchange: 1..16 ranks dividing at most 1024 experts, h a positive multiple of 8");
+    auto k = std::make_unique<EpMove>();
+    k->h = h;
+    k->top_k = top_k;
+    k->experts = experts;
+    k->world = world;
+    k->rank = rank;
+    k->cap = cap;
+    k->ret = ret;
+    k->kind = ret ? 12 : 11;
+    k->nargs = 4;
+    k->name = std::string(ret ? "ep_return_" : "ep_dispatch_") + std::to_string(h) + "_k" + std::to_string(top_k) + "_e" + std::to_string(experts) + "_r" +
+              std::to_string(rank) + "of" + std::to_string(world) + "_c" + std::to_string(cap);
+    *out = intern(ctx, std::move(k));
+    return HB_OK;
+}
+
+int make_ep_plan(hb_ctx* ctx, uint32_t experts, uint32_t world, uint32_t rank, uint32_t bm, uint32_t cap, hb_kernel** out) {
+    *out = nullptr;
+    if (!ep_shape_ok(experts, world, rank) || cap == 0) return fail(ctx, HB_UNSUPPORTED, "ep plan: 1..16 ranks dividing at most 1024 experts");
+    if (bm != 16 && bm != 32 && bm != 64) return fail(ctx, HB_UNSUPPORTED, "ep plan: tile rows 16, 32 or 64");
+    auto k = std::make_unique<EpPlan>();
+    k->experts = experts;
+    k->world = world;
+    k->rank = rank;
+    k->bm = bm;
+    k->cap = cap;
+    k->kind = 13;
+    k->nargs = 3;
+    k->name = "ep_plan_e" + std::to_string(experts) + "_r" + std::to_string(rank) + "of" + std::to_string(world) + "_m" + std::to_string(bm) + "_c" + std::to_string(cap);
+    *out = intern(ctx, std::move(k));
+    return HB_OK;
+}
+
+}  // namespace hb

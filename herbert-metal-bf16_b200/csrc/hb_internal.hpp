@@ -37,6 +37,7 @@ struct hb_ctx {
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     cudaStream_t copy_lane[2] = {nullptr, nullptr};  // upload, download: made on first use
     std::vector<void*> host_allocs;
+    std::vector<void*> ipc_opened;  // peers' allocations mapped into this process
     uint32_t* status_dev = nullptr;  // 8 words, see tc05.cuh
     std::string err;
     std::vector<void*> allocs;
@@ -79,6 +80,8 @@ int make_route(hb_ctx* ctx, uint32_t experts, uint32_t top_k, hb_kernel** out);
 int make_moe_sort(hb_ctx* ctx, uint32_t experts, uint32_t top_k, uint32_t rows_max, uint32_t bm, hb_kernel** out);
 int make_moe_gather(hb_ctx* ctx, uint32_t h, uint32_t top_k, hb_kernel** out);
 int make_moe_combine(hb_ctx* ctx, uint32_t d, uint32_t top_k, uint32_t f32_sum, hb_kernel** out);
+int make_ep_move(hb_ctx* ctx, bool ret, uint32_t h, uint32_t top_k, uint32_t experts, uint32_t world, uint32_t rank, uint32_t cap, hb_kernel** out);
+int make_ep_plan(hb_ctx* ctx, uint32_t experts, uint32_t world, uint32_t rank, uint32_t bm, uint32_t cap, hb_kernel** out);
 
 // Registers `k` under its name (or returns the existing object of that name).
 hb_kernel* intern(hb_ctx* ctx, std::unique_ptr<hb_kernel> k);

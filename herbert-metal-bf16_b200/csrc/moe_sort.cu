@@ -24,6 +24,7 @@ struct SortParams {
     const uint32_t* route;
     uint32_t* list;
     uint32_t* tiles;
+    uint32_t* offsets;  // optional [experts + 1]: first sorted row of every expert, then the number of pairs
     uint32_t rows, experts, top_k, bm;
     uint32_t staged;    // the experts of all pairs fit in shared memory as 16-bit values
     uint32_t use_masks; // the per-expert row masks fit in shared memory
@@ -130,6 +131,10 @@ __global__ void __launch_bounds__(SORT_THREADS) moe_sort_kernel(const SortParams
     if (tid < experts) {
         const uint32_t start = a - total_e, tfirst = t - ntile_e;
         off[tid] = start;
+        if (p.offsets) {
+            p.offsets[tid] = start;
+            if (tid == experts - 1) p.offsets[experts] = a;
+        }
         for (uint32_t j = 0, ti = tfirst; j < total_e; j += bm, ++ti) {
             p.tiles[1 + 3 * ti] = tid;
             p.tiles[2 + 3 * ti] = start + j;
@@ -172,7 +177,8 @@ struct MoeSort : hb_kernel {
     uint32_t experts = 0, top_k = 0, rows_max = 0, bm = 0, staged = 0, use_masks = 0, words = 0;
     size_t smem = 0;
     int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
-        if (na != 3) return fail(ctx, HB_INVALID, name + ": bindings are route, list, tiles");
+        if (na != 3 && na != 4) return fail(ctx, HB_INVALID, name + ": bindings are route, list, tiles[, offsets]");
+        if (na == 4 && !range_ok(a[3], ((size_t)experts + 1) * 4)) return fail(ctx, HB_INVALID, name + ": the offsets range is too small");
         if (m == 0 || m > rows_max) return fail(ctx, HB_INVALID, name + ": m outside 1.." + std::to_string(rows_max));
         const size_t tiles_words = 1 + 3 * (size_t)hb_moe_tiles(m, top_k, experts, bm);
         if (!range_ok(a[0], (size_t)m * 2 * top_k * 4) || !range_ok(a[1], (size_t)m * top_k * 4) || !range_ok(a[2], tiles_words * 4))
@@ -181,6 +187,7 @@ struct MoeSort : hb_kernel {
         p.route = static_cast<const uint32_t*>(a[0].ptr);
         p.list = static_cast<uint32_t*>(a[1].ptr);
         p.tiles = static_cast<uint32_t*>(a[2].ptr);
+        p.offsets = na == 4 ? static_cast<uint32_t*>(a[3].ptr) : nullptr;
         p.rows = m;
         p.experts = experts;
         p.top_k = top_k;

@@ -1,5 +1,6 @@
 // Device layer of the C ABI: context, buffers, copies, launches, timing.
 // Takes the place of the reference's src/metal/gpu.rs for the matrix-multiply path.
+#include <algorithm>
 #include <cstring>
 #include <mutex>
 
@@ -54,7 +55,8 @@ int check_status(hb_ctx* ctx) {
     HB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     if (st[0] != 0) {
         char msg[160];
-        snprintf(msg, sizeof msg, "kernel status %u: block %u gave up waiting at point %u (detail %u)", st[0], st[1], st[2], st[3]);
+        if (st[0] == 2) snprintf(msg, sizeof msg, "kernel status 2: block %u read a table that does not fit its buffers (%u against %u)", st[1], st[2], st[3]);
+        else snprintf(msg, sizeof msg, "kernel status %u: block %u gave up waiting at point %u (detail %u)", st[0], st[1], st[2], st[3]);
         cudaMemsetAsync(ctx->status_dev, 0, sizeof st, ctx->stream);
         cudaStreamSynchronize(ctx->stream);
         return fail(ctx, HB_KERNEL, msg);
@@ -138,6 +140,7 @@ int hb_close(hb_ctx* ctx) {
             cudaStreamDestroy(c);
         }
     for (void* p : ctx->host_allocs) cudaFreeHost(p);
+    for (void* p : ctx->ipc_opened) cudaIpcCloseMemHandle(p);
     if (ctx->own_stream) cudaStreamDestroy(ctx->stream);
     delete ctx;
     return HB_OK;
@@ -205,6 +208,41 @@ int hb_download(hb_ctx* ctx, void* dst, const void* src, size_t bytes) {
     HB_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
     HB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return hb::check_status(ctx);
+}
+
+// ---- peer memory ------------------------------------------------------------------------------
+int hb_ipc_export(hb_ctx* ctx, void* dptr, void* handle64) {
+    if (!ctx || !dptr || !handle64) return fail(ctx, HB_INVALID, "hb_ipc_export: bad argument");
+    static_assert(sizeof(cudaIpcMemHandle_t) == HB_IPC_HANDLE_BYTES, "handle size");
+    if (std::find(ctx->allocs.begin(), ctx->allocs.end(), dptr) == ctx->allocs.end())
+        return fail(ctx, HB_INVALID, "hb_ipc_export: not the start of an hb_alloc allocation");
+    cudaIpcMemHandle_t h;
+    HB_CUDA(ctx, cudaIpcGetMemHandle(&h, dptr));
+    memcpy(handle64, &h, sizeof h);
+    return HB_OK;
+}
+
+int hb_ipc_open(hb_ctx* ctx, const void* handle64, void** dptr) {
+    if (!ctx || !handle64 || !dptr) return fail(ctx, HB_INVALID, "hb_ipc_open: bad argument");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle64, sizeof h);
+    void* p = nullptr;
+    HB_CUDA(ctx, cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    ctx->ipc_opened.push_back(p);
+    *dptr = p;
+    return HB_OK;
+}
+
+int hb_ipc_close(hb_ctx* ctx, void* dptr) {
+    if (!ctx || !dptr) return HB_OK;
+    for (size_t i = 0; i < ctx->ipc_opened.size(); ++i)
+        if (ctx->ipc_opened[i] == dptr) {
+            ctx->ipc_opened.erase(ctx->ipc_opened.begin() + i);
+            HB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+            HB_CUDA(ctx, cudaIpcCloseMemHandle(dptr));
+            return HB_OK;
+        }
+    return fail(ctx, HB_INVALID, "hb_ipc_close: not a pointer of hb_ipc_open");
 }
 
 // ---- copy lanes -------------------------------------------------------------------------------
@@ -398,6 +436,24 @@ int hb_moe_gather_get(hb_ctx* ctx, uint32_t h, uint32_t top_k, hb_kernel** out) 
     if (!ctx || !out) return fail(ctx, HB_INVALID, "hb_moe_gather_get: bad argument");
     HB_GUARD_BEGIN
     return hb::make_moe_gather(ctx, h, top_k, out);
+    HB_GUARD_END(ctx)
+}
+int hb_ep_dispatch_get(hb_ctx* ctx, uint32_t h, uint32_t top_k, uint32_t experts, uint32_t world, uint32_t rank, uint32_t cap, hb_kernel** out) {
+    if (!ctx || !out) return fail(ctx, HB_INVALID, "hb_ep_dispatch_get: bad argument");
+    HB_GUARD_BEGIN
+    return hb::make_ep_move(ctx, false, h, top_k, experts, world, rank, cap, out);
+    HB_GUARD_END(ctx)
+}
+int hb_ep_return_get(hb_ctx* ctx, uint32_t h, uint32_t top_k, uint32_t experts, uint32_t world, uint32_t rank, uint32_t cap, hb_kernel** out) {
+    if (!ctx || !out) return fail(ctx, HB_INVALID, "hb_ep_return_get: bad argument");
+    HB_GUARD_BEGIN
+    return hb::make_ep_move(ctx, true, h, top_k, experts, world, rank, cap, out);
+    HB_GUARD_END(ctx)
+}
+int hb_ep_plan_get(hb_ctx* ctx, uint32_t experts, uint32_t world, uint32_t rank, uint32_t bm, uint32_t cap, hb_kernel** out) {
+    if (!ctx || !out) return fail(ctx, HB_INVALID, "hb_ep_plan_get: bad argument");
+    HB_GUARD_BEGIN
+    return hb::make_ep_plan(ctx, experts, world, rank, bm, cap, out);
     HB_GUARD_END(ctx)
 }
 int hb_moe_combine_get(hb_ctx* ctx, uint32_t d, uint32_t top_k, uint32_t f32_sum, hb_kernel** out) {

@@ -208,3 +208,175 @@ class GpuBackend:
         out = torch.empty((m, h), device=ey.device, dtype=torch.bfloat16)
         self.ctx.moe_combine(h, top_k)(m, self._w(ey), self._w(route), self._w(out))
         return out
+
+
+# --------------------------------------------------------------------------- expert-parallel MoE over peer memory
+#
+# The same block as ep_moe with the exchange done by the library's own kernels through NVLink (include/hb200.h,
+# "expert-parallel exchange over peer memory"): nothing is read back to the host, no variable-size collective.
+# Per rank and call: route, sort by global expert (+ offsets), all-gather of the offsets (1 KB per rank),
+# dispatch (stores into the owners' receive buffers), barrier, plan + gate/up + down on the received rows,
+# barrier, return (loads from the owners' output buffers), combine.
+
+def ep_positions_np(offs_all, rank: int, epr: int):
+    """Host mirror of the dispatch / return index arithmetic: for every sorted position p of `rank`, the
+    destination rank and the row in that rank's receive buffer. offs_all: int array [world][experts + 1]."""
+    import numpy as np
+
+    offs_all = np.asarray(offs_all, dtype=np.int64)
+    world = offs_all.shape[0]
+    pairs = int(offs_all[rank, -1])
+    first = np.array([offs_all[rank, d * epr] for d in range(world)] + [pairs])
+    base = np.array([sum(int(offs_all[s, (d + 1) * epr] - offs_all[s, d * epr]) for s in range(rank)) for d in range(world)])
+    p = np.arange(pairs)
+    d = np.searchsorted(first[1:], p, side="right")
+    return d, base[d] + p - first[d]
+
+
+def ep_plan_np(offs_all, rank: int, epr: int, bm: int):
+    """Host mirror of the plan kernel: (list, tiles) of `rank`'s experts over its receive buffer."""
+    import numpy as np
+
+    offs_all = np.asarray(offs_all, dtype=np.int64)
+    world = offs_all.shape[0]
+    e0 = rank * epr
+    n_from = [int(offs_all[s, e0 + epr] - offs_all[s, e0]) for s in range(world)]
+    recvbase = np.concatenate([[0], np.cumsum(n_from)])
+    lst, tiles = [], []
+    for e in range(epr):
+        start = len(lst)
+        for s in range(world):
+            lo, hi = int(offs_all[s, e0 + e]), int(offs_all[s, e0 + e + 1])
+            src0 = int(recvbase[s]) + lo - int(offs_all[s, e0])
+            lst.extend(range(src0, src0 + hi - lo))
+        total = len(lst) - start
+        for j in range(0, total, bm):
+            tiles.append((e, start + j, min(bm, total - j)))
+    flat = [len(tiles)] + [v for t in tiles for v in t]
+    return np.array(lst, dtype=np.uint32), np.array(flat, dtype=np.uint32)
+
+
+class EpPeer:
+    """One rank of the peer-memory MoE block: its buffers, kernels and the four phases between the collectives.
+
+    `ctx` must launch on torch's current stream (Context.set_stream) so that the phases and the collectives are
+    ordered. `cap` is the number of rows the receive and output buffers hold; the default, every pair of every
+    rank, can never overflow.
+    """
+
+    def __init__(self, hb, ctx, rank: int, world: int, rows: int, h: int, mi: int, experts: int, top_k: int, bm: int = 64, cap: int | None = None,
+                 device=None):
+        assert experts % world == 0
+        self.hb, self.ctx, self.rank, self.world = hb, ctx, rank, world
+        self.rows, self.h, self.mi, self.experts, self.top_k, self.bm = rows, h, mi, experts, top_k, bm
+        self.epr = experts // world
+        self.pairs = rows * top_k
+        self.cap = cap if cap is not None else self.pairs * world
+        dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        i32 = dict(device=dev, dtype=torch.int32)
+        # exported: the rows this rank receives and the outputs of its experts, both [cap][h] bf16
+        self.recv = ctx.alloc(self.cap * h * 2)
+        self.ey_recv = ctx.alloc(self.cap * h * 2)
+        self.route = torch.zeros(rows, 2 * top_k, **i32)
+        self.list = torch.zeros(self.pairs, **i32)
+        self.tiles = torch.zeros(1 + 3 * hb.lib().hb_moe_tiles(rows, top_k, experts, bm), **i32)
+        self.offs = torch.zeros(experts + 1, **i32)
+        self.offs_all = torch.zeros(world, experts + 1, **i32)
+        self.rlist = torch.zeros(self.cap, **i32)
+        self.rtiles = torch.zeros(1 + 3 * hb.lib().hb_moe_tiles(self.cap, 1, self.epr, bm), **i32)
+        self.ehb = torch.zeros(self.cap, mi, device=dev, dtype=torch.bfloat16)
+        self.ey = torch.zeros(self.pairs, h, device=dev, dtype=torch.bfloat16)
+        self.out = torch.zeros(rows, h, device=dev, dtype=torch.bfloat16)
+        self.peers_recv = torch.zeros(world, device=dev, dtype=torch.int64)
+        self.peers_ey = torch.zeros(world, device=dev, dtype=torch.int64)
+        self.token = torch.zeros(1, device=dev, dtype=torch.float32)  # the barrier's operand
+        self.opened = []
+        rows_cap = 1 << max(rows - 1, 0).bit_length()
+        kw = dict(rows_max=self.cap, top_k=1, experts=self.epr, bm=bm, merge_runs=1)
+        self.k_route = ctx.route(experts, top_k)
+        self.k_sort = ctx.moe_sort(experts, top_k, rows_cap, bm)
+        self.k_dispatch = ctx.ep_dispatch(h, top_k, experts, world, rank, self.cap)
+        self.k_plan = ctx.ep_plan(experts, world, rank, bm, self.cap)
+        self.k_gate_up = ctx.gemm(h, 2 * mi, OUT_SWIGLU, rows_mode=hb.ROWS_GATHER, **kw)
+        self.k_down = ctx.gemm(mi, h, OUT_BF16, rows_mode=hb.ROWS_SCATTER, **kw)
+        self.k_return = ctx.ep_return(h, top_k, experts, world, rank, self.cap)
+        self.k_combine = ctx.moe_combine(h, top_k)
+
+    def _w(self, t):
+        return self.ctx.wrap(t.data_ptr(), max(t.numel() * t.element_size(), 1))
+
+    # ---- wiring
+    def handles(self):
+        return self.ctx.ipc_export(self.recv), self.ctx.ipc_export(self.ey_recv)
+
+    def connect(self, all_handles=None, local_peers=None) -> None:
+        """all_handles: per rank the pair of handles() (other processes); local_peers: the EpPeer objects of all
+        ranks when they live in this process on this GPU (tests)."""
+        recv_ptrs, ey_ptrs = [], []
+        for r in range(self.world):
+            if r == self.rank:
+                recv_ptrs.append(self.recv.ptr)
+                ey_ptrs.append(self.ey_recv.ptr)
+            elif local_peers is not None:
+                recv_ptrs.append(local_peers[r].recv.ptr)
+                ey_ptrs.append(local_peers[r].ey_recv.ptr)
+            else:
+                a = self.ctx.ipc_open(all_handles[r][0], self.cap * self.h * 2)
+                b = self.ctx.ipc_open(all_handles[r][1], self.cap * self.h * 2)
+                self.opened += [a, b]
+                recv_ptrs.append(a.ptr)
+                ey_ptrs.append(b.ptr)
+        self.peers_recv.copy_(torch.tensor(recv_ptrs, dtype=torch.int64))
+        self.peers_ey.copy_(torch.tensor(ey_ptrs, dtype=torch.int64))
+
+    def close(self) -> None:
+        for b in self.opened:
+            self.ctx.ipc_close(b)
+        self.opened = []
+
+    # ---- the phases
+    def phase_sort(self, x, scores) -> None:
+        self.x = x
+        self.k_route(self.rows, self._w(scores), self._w(self.route))
+        self.k_sort(self.rows, self._w(self.route), self._w(self.list), self._w(self.tiles), self._w(self.offs))
+
+    def phase_dispatch(self) -> None:  # offs_all holds every rank's offsets
+        self.k_dispatch(self.rows, self._w(self.x), self._w(self.peers_recv), self._w(self.list), self._w(self.offs_all))
+
+    def phase_experts(self, wgu_local, wd_local) -> None:  # every rank's dispatch has finished
+        self.k_plan(1, self._w(self.offs_all), self._w(self.rlist), self._w(self.rtiles))
+        self.k_gate_up(self.cap, self._w(wgu_local), self.recv, self._w(self.ehb), self._w(self.rlist), self._w(self.rtiles))
+        self.k_down(self.cap, self._w(wd_local), self._w(self.ehb), self.ey_recv, self._w(self.rlist), self._w(self.rtiles))
+
+    def phase_return(self):  # every rank's expert GEMMs have finished
+        self.k_return(self.rows, self._w(self.peers_ey), self._w(self.ey), self._w(self.list), self._w(self.offs_all))
+        self.k_combine(self.rows, self._w(self.ey), self._w(self.route), self._w(self.out))
+        return self.out
+
+
+def ep_peer_connect(state: EpPeer, group=None) -> None:
+    """Exchanges the buffer handles among the processes of the group and maps the peers' buffers."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world == 1:
+        state.connect(local_peers=[state])
+        return
+    gathered = [None] * world
+    dist.all_gather_object(gathered, state.handles(), group=group)
+    state.connect(all_handles=gathered)
+
+
+def ep_moe_peer(state: EpPeer, x_local, scores_local, wgu_local, wd_local, group=None):
+    """The sparse block for this rank's token rows with the exchange through peer memory; returns out [rows][h]."""
+    multi = state.world > 1
+    state.phase_sort(x_local, scores_local)
+    if multi:
+        dist.all_gather_into_tensor(state.offs_all.view(-1), state.offs, group=group)
+    else:
+        state.offs_all[0].copy_(state.offs)
+    state.phase_dispatch()
+    if multi:
+        dist.all_reduce(state.token, group=group)  # every rank's rows have landed
+    state.phase_experts(wgu_local, wd_local)
+    if multi:
+        dist.all_reduce(state.token, group=group)  # every rank's outputs are complete
+    return state.phase_return()

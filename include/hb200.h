@@ -100,6 +100,16 @@ int hb_sync(hb_ctx* ctx);
 /* Number of kernels this context has enqueued so far. */
 uint64_t hb_launch_count(const hb_ctx* ctx);
 
+/* ---- peer memory ---------------------------------------------------------
+ * One process per GPU: a buffer of hb_alloc is made visible to the other processes of the node by passing the
+ * 64-byte handle of hb_ipc_export to them (any channel) and opening it there; the pointer hb_ipc_open returns is
+ * valid in kernels of that process (loads and stores cross NVLink). Close before the owner frees. No reference
+ * counterpart. */
+#define HB_IPC_HANDLE_BYTES 64
+int hb_ipc_export(hb_ctx* ctx, void* dptr, void* handle64);
+int hb_ipc_open(hb_ctx* ctx, const void* handle64, void** dptr);
+int hb_ipc_close(hb_ctx* ctx, void* dptr);
+
 /* ---- copy lanes ---------------------------------------------------------
  * The reference's buffers are shared between CPU and GPU (src/metal/gpu.rs:92-110), so its engine
  * never copies activations. On a discrete GPU a prompt block crosses PCIe both ways; these calls let
@@ -185,6 +195,24 @@ int hb_moe_gather_get(hb_ctx* ctx, uint32_t h, uint32_t top_k, hb_kernel** out);
 /* moe_combine, src/metal/qwen_kernels.rs:2119-2161: acc = bf16(acc + bf16(y*w)) over the slots in route order.
  * f32_sum = 1 is the variant that keeps the sum in f32 and rounds once. Bindings: y ([m][top_k][d]), route, out. */
 int hb_moe_combine_get(hb_ctx* ctx, uint32_t d, uint32_t top_k, uint32_t f32_sum, hb_kernel** out);
+/* ---- expert-parallel exchange over peer memory (no reference counterpart: the reference runs on one GPU) ----
+ * Experts are partitioned contiguously over `world` ranks, the token rows are each rank's own. A rank sorts its
+ * (row, slot) pairs by global expert with hb_moe_sort_get, binding a fourth range `offsets` u32[experts + 1] (first
+ * sorted position of every expert, then the pair count); the host all-gathers these into u32[world][experts + 1].
+ * `peers` is a device array u64[world] of the base addresses of every rank's buffer ([cap][h] bf16), the rank's own
+ * included, obtained through hb_ipc_export / hb_ipc_open.
+ *   dispatch, bindings X, peers, list, offsets_all: writes row X[list[p] / top_k] of every sorted position p into
+ *     the receive buffer of the rank that owns p's expert (sources in rank order, each source's rows in its order).
+ *   plan, bindings offsets_all, list, tiles: the list (sorted row -> receive-buffer row) and the tile table for this
+ *     rank's experts, for expert GEMMs built with top_k = 1, experts / world experts and rows_max = cap, which are
+ *     then launched with m = cap (the table, not m, says how many rows there are).
+ *   return, bindings peers, EY, list, offsets_all: EY[list[p]] = the row of p in its owner's output buffer.
+ * The kernels never wait for another GPU. The host orders the steps on the stream: all-gather of the offsets, then
+ * dispatch, a barrier, plan and the expert GEMMs, a barrier, return. A count that exceeds `cap` rows is reported
+ * through the status words (HB_KERNEL at the next hb_sync) and nothing is written past the buffers. */
+int hb_ep_dispatch_get(hb_ctx* ctx, uint32_t h, uint32_t top_k, uint32_t experts, uint32_t world, uint32_t rank, uint32_t cap, hb_kernel** out);
+int hb_ep_plan_get(hb_ctx* ctx, uint32_t experts, uint32_t world, uint32_t rank, uint32_t bm, uint32_t cap, hb_kernel** out);
+int hb_ep_return_get(hb_ctx* ctx, uint32_t h, uint32_t top_k, uint32_t experts, uint32_t world, uint32_t rank, uint32_t cap, hb_kernel** out);
 /* The output mode (BF16 or RESIDUAL: store, src/metal/kernels.rs:217-234) applied to an f32 accumulator array
  * [m][n] that was completed outside a GEMM: a row-parallel projection sums f32 partial products across GPUs
  * (hb_gemm_get with HB_OUT_F32 on each, then an all-reduce) and rounds once afterwards. Bindings: acc, y. */
