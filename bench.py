@@ -570,11 +570,28 @@ def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks)
                 y = torch.randn(m, h, device=dev, generator=g).bfloat16()
                 wgu_l = (torch.randn(2 * ip, h, device=dev, generator=gl) * h**-0.5).bfloat16()
                 wd_l = (torch.randn(h, ip, device=dev, generator=gl) * inter**-0.5).bfloat16()
-                sec = timed(lambda: D.tp_ffn(be, x, wgu_l, wd_l, y), 3, 10)
                 flop = 2.0 * m * (2 * inter) * h + 2.0 * m * h * inter
+                # the sum across ranks, the rounding, the residual and the distribution of Y in the library's tp_reduce
+                # kernel over peer memory (the production form) ...
+                tp = D.TpPeer(hb, ctx, rank, world, m, h)
+                D.tp_peer_connect(tp)
+                tp.set_y(y)
+                got = D.tp_ffn_peer(tp, x, wgu_l, wd_l).clone()
+                sec = timed(lambda: D.tp_ffn_peer(tp, x, wgu_l, wd_l), 3, 10)
+                sec_ns = timed(lambda: D.tp_ffn_peer(tp, x, wgu_l, wd_l, nccl_sync=True), 3, 10) if world > 1 else sec
+                # ... and the same FFN with an NCCL all-reduce of the f32 partials and a separate epilogue (the baseline form)
+                y2 = y.clone()
+                D.tp_ffn(be, x, wgu_l, wd_l, y2)
+                same = bool(torch.equal(y2, got))
+                sec_nccl = timed(lambda: D.tp_ffn(be, x, wgu_l, wd_l, y2), 3, 10)
+                barrier()
+                tp.close()
                 out["tp_ffn_27b_m2048"] = {"n_gpus": world, "us": sec * 1e6, "tflops_total": flop / sec / 1e12, "tflops_per_gpu": flop / sec / 1e12 / world,
                                            "frac_of_measured_peak_per_gpu": flop / sec / 1e12 / world / pk["bf16_tflops"],
-                                           "allreduce_bytes": m * h * 4 if world > 1 else 0, "scaling": "strong"}
+                                           "nvlink_bytes_per_gpu": (m * h * 4 + m * h * 2) * (world - 1) // world // 1 if world > 1 else 0, "scaling": "strong",
+                                           "exchange": "tp_reduce kernel: peer loads of the f32 partials, peer stores of bf16 Y, 2 barrier kernels (no NCCL call in the step)",
+                                           "with_nccl_barriers_us": sec_ns * 1e6,
+                                           "nccl_all_reduce_form_us": sec_nccl * 1e6, "equals_nccl_form_bitwise": same}
                 del wgu_l, wd_l
             # -- config 5: 2048 tokens, hidden 2048, 256 experts, top-8, expert intermediate 512
             m, h, mi, E, top_k, bm = 2048, 2048, 512, 256, 8, 64
@@ -590,6 +607,7 @@ def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks)
                 D.ep_peer_connect(st)
                 got = D.ep_moe_peer(st, xs, sc, wgu_l, wd_l).clone()
                 sec = timed(lambda: D.ep_moe_peer(st, xs, sc, wgu_l, wd_l), 3, 20)
+                sec_ns = timed(lambda: D.ep_moe_peer(st, xs, sc, wgu_l, wd_l, nccl_sync=True), 3, 20) if world > 1 else sec
                 # ... and the same block with the rows exchanged by NCCL all-to-all, host-known counts (the baseline form)
                 ref = D.ep_moe(be, xs, sc, wgu_l, wd_l, E, top_k, mi, bm)
                 same = bool(torch.equal(ref, got))
@@ -597,7 +615,8 @@ def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks)
                 barrier()
                 st.close()
                 out["moe_ep_2048tok"] = {"n_gpus": world, "us": sec * 1e6, "weight_gbs_total": wbytes / sec / 1e9, "tokens_per_s": m / sec, "scaling": "strong",
-                                         "tile_rows": bm, "exchange": "peer-memory stores and loads in ep_dispatch / ep_return, 1 all-gather of 1 KB + 2 barriers",
+                                         "tile_rows": bm, "exchange": "peer-memory stores and loads in ep_dispatch / ep_return, offsets all-gather + 2 barriers as kernels (no NCCL call in the step)",
+                                         "with_nccl_barriers_us": sec_ns * 1e6,
                                          "nccl_all_to_all_form_us": sec_nccl * 1e6, "equals_nccl_form_bitwise": same}
     finally:
         stream.synchronize()

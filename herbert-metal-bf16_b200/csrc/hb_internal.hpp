@@ -37,6 +37,7 @@ struct hb_ctx {
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     cudaStream_t copy_lane[2] = {nullptr, nullptr};  // upload, download: made on first use
     std::vector<void*> host_allocs;
+    uint32_t peer_wait_ms = 5000;  // bound of a barrier's wait for the other GPUs
     std::vector<void*> ipc_opened;  // peers' allocations mapped into this process
     uint32_t* status_dev = nullptr;  // 8 words, see tc05.cuh
     std::string err;

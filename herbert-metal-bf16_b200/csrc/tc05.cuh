@@ -89,7 +89,7 @@ __device__ __forceinline__ uint32_t swiglu_bf16(float g, float u) {
 // bounded wait: [0] = code (0 ok), [1] = block, [2] = where, [3] = detail. ST_BAD_TABLE: a table
 // the kernel read (row counts of an exchange) does not fit the buffers it was given; [2], [3] = the numbers.
 enum : uint32_t { ST_OK = 0, ST_WAIT_TIMEOUT = 1, ST_BAD_TABLE = 2 };
-enum : uint32_t { WHERE_EMPTY = 1, WHERE_FULL = 2, WHERE_TMEM_FULL = 3, WHERE_TMEM_EMPTY = 4 };
+enum : uint32_t { WHERE_EMPTY = 1, WHERE_FULL = 2, WHERE_TMEM_FULL = 3, WHERE_TMEM_EMPTY = 4, WHERE_PEER = 5 };
 
 __device__ __forceinline__ void report(uint32_t* status, uint32_t code, uint32_t where, uint32_t detail) {
     if (atomicCAS(status, 0u, code) == 0u) {

@@ -256,10 +256,91 @@ def ep_plan_np(offs_all, rank: int, epr: int, bm: int):
     return np.array(lst, dtype=np.uint32), np.array(flat, dtype=np.uint32)
 
 
-class EpPeer:
-    """One rank of the peer-memory MoE block: its buffers, kernels and the four phases between the collectives.
+def _view(buf, shape, typestr: str, device) -> torch.Tensor:
+    """A torch tensor over a library allocation (no copy)."""
+    class _Holder:
+        pass
 
-    `ctx` must launch on torch's current stream (Context.set_stream) so that the phases and the collectives are
+    h = _Holder()
+    h.__cuda_array_interface__ = {"shape": tuple(shape), "typestr": typestr, "data": (buf.ptr, False), "version": 3}
+    return torch.as_tensor(h, device=device)
+
+
+class PeerBuffers:
+    """Named buffers of this rank that the other ranks of the node read and write, with the device tables
+    (u64[world], one address per rank) the kernels take. A flag array for the barrier kernel is always there."""
+
+    def __init__(self, ctx, rank: int, world: int, sizes: dict, device):
+        self.ctx, self.rank, self.world, self.device = ctx, rank, world, device
+        self.sizes = dict(sizes, flags=256)
+        self.local = {name: ctx.alloc(size) for name, size in self.sizes.items()}
+        self.tables = {name: torch.zeros(world, device=device, dtype=torch.int64) for name in self.sizes}
+        self.opened = []
+        self.emulated = True
+        self.epoch = 0
+
+    def handles(self) -> dict:
+        return {name: self.ctx.ipc_export(buf) for name, buf in self.local.items()}
+
+    def connect(self, all_handles=None, local_peers=None) -> None:
+        """all_handles: handles() of every rank (other processes); local_peers: the PeerBuffers of every rank when
+        all ranks live in this process on this GPU (the tests' emulation: no barrier kernel may run then)."""
+        self.emulated = all_handles is None
+        for name in self.sizes:
+            ptrs = []
+            for r in range(self.world):
+                if r == self.rank:
+                    ptrs.append(self.local[name].ptr)
+                elif local_peers is not None:
+                    ptrs.append(local_peers[r].local[name].ptr)
+                else:
+                    b = self.ctx.ipc_open(all_handles[r][name], self.sizes[name])
+                    self.opened.append(b)
+                    ptrs.append(b.ptr)
+            self.tables[name].copy_(torch.tensor(ptrs, dtype=torch.int64))
+
+    def connect_group(self, group=None) -> None:
+        if self.world == 1:
+            self.connect(local_peers=[self])
+            return
+        gathered = [None] * self.world
+        dist.all_gather_object(gathered, self.handles(), group=group)
+        self.connect(all_handles=gathered)
+        dist.barrier(group=group)  # every rank has mapped every buffer before the first kernel touches one
+
+    def table(self, name: str):
+        t = self.tables[name]
+        return self.ctx.wrap(t.data_ptr(), t.numel() * 8)
+
+    def barrier(self) -> None:
+        """The barrier kernel on the stream (nothing on one rank or in the emulation)."""
+        if self.world == 1 or self.emulated:
+            return
+        if not hasattr(self, "_k_barrier"):
+            self._k_barrier = self.ctx.peer_sync(0, self.world, self.rank)
+        self.epoch += 1
+        self._k_barrier(self.epoch, self.table("flags"))
+
+    def allgather(self, payload: torch.Tensor, name: str) -> None:
+        """payload (int32 words) -> slot `rank` of buffer `name` on every rank, then the barrier."""
+        words = payload.numel()
+        if not hasattr(self, "_k_gather"):
+            self._k_gather = {}
+        if words not in self._k_gather:
+            self._k_gather[words] = self.ctx.peer_sync(words, self.world, self.rank)
+        self.epoch += 1
+        self._k_gather[words](self.epoch, self.table("flags"), self.ctx.wrap(payload.data_ptr(), words * 4), self.table(name))
+
+    def close(self) -> None:
+        for b in self.opened:
+            self.ctx.ipc_close(b)
+        self.opened = []
+
+
+class EpPeer:
+    """One rank of the peer-memory MoE block: its buffers, kernels and the four phases between the barriers.
+
+    `ctx` must launch on torch's current stream (Context.set_stream) so that the phases and any collective are
     ordered. `cap` is the number of rows the receive and output buffers hold; the default, every pair of every
     rank, can never overflow.
     """
@@ -274,23 +355,23 @@ class EpPeer:
         self.cap = cap if cap is not None else self.pairs * world
         dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         i32 = dict(device=dev, dtype=torch.int32)
-        # exported: the rows this rank receives and the outputs of its experts, both [cap][h] bf16
-        self.recv = ctx.alloc(self.cap * h * 2)
-        self.ey_recv = ctx.alloc(self.cap * h * 2)
+        # shared with the peers: the rows this rank receives and the outputs of its experts, both [cap][h] bf16, and
+        # two copies of the offsets of all ranks (calls alternate: a peer may write the next while this one is read)
+        offs_bytes = world * (experts + 1) * 4
+        self.pb = PeerBuffers(ctx, rank, world, {"recv": self.cap * h * 2, "ey": self.cap * h * 2, "offs0": offs_bytes, "offs1": offs_bytes}, dev)
+        self.recv, self.ey_recv = self.pb.local["recv"], self.pb.local["ey"]
+        self.offs_both = [_view(self.pb.local[n], (world, experts + 1), "<i4", dev) for n in ("offs0", "offs1")]
+        self.parity = 0
         self.route = torch.zeros(rows, 2 * top_k, **i32)
         self.list = torch.zeros(self.pairs, **i32)
         self.tiles = torch.zeros(1 + 3 * hb.lib().hb_moe_tiles(rows, top_k, experts, bm), **i32)
         self.offs = torch.zeros(experts + 1, **i32)
-        self.offs_all = torch.zeros(world, experts + 1, **i32)
         self.rlist = torch.zeros(self.cap, **i32)
         self.rtiles = torch.zeros(1 + 3 * hb.lib().hb_moe_tiles(self.cap, 1, self.epr, bm), **i32)
         self.ehb = torch.zeros(self.cap, mi, device=dev, dtype=torch.bfloat16)
         self.ey = torch.zeros(self.pairs, h, device=dev, dtype=torch.bfloat16)
         self.out = torch.zeros(rows, h, device=dev, dtype=torch.bfloat16)
-        self.peers_recv = torch.zeros(world, device=dev, dtype=torch.int64)
-        self.peers_ey = torch.zeros(world, device=dev, dtype=torch.int64)
-        self.token = torch.zeros(1, device=dev, dtype=torch.float32)  # the barrier's operand
-        self.opened = []
+        self.token = torch.zeros(1, device=dev, dtype=torch.float32)  # operand of the NCCL form of the barrier
         rows_cap = 1 << max(rows - 1, 0).bit_length()
         kw = dict(rows_max=self.cap, top_k=1, experts=self.epr, bm=bm, merge_runs=1)
         self.k_route = ctx.route(experts, top_k)
@@ -305,43 +386,26 @@ class EpPeer:
     def _w(self, t):
         return self.ctx.wrap(t.data_ptr(), max(t.numel() * t.element_size(), 1))
 
-    # ---- wiring
-    def handles(self):
-        return self.ctx.ipc_export(self.recv), self.ctx.ipc_export(self.ey_recv)
+    @property
+    def offs_all(self) -> torch.Tensor:
+        """[world][experts + 1]: the offsets of every rank for the call in progress."""
+        return self.offs_both[self.parity]
 
-    def connect(self, all_handles=None, local_peers=None) -> None:
-        """all_handles: per rank the pair of handles() (other processes); local_peers: the EpPeer objects of all
-        ranks when they live in this process on this GPU (tests)."""
-        recv_ptrs, ey_ptrs = [], []
-        for r in range(self.world):
-            if r == self.rank:
-                recv_ptrs.append(self.recv.ptr)
-                ey_ptrs.append(self.ey_recv.ptr)
-            elif local_peers is not None:
-                recv_ptrs.append(local_peers[r].recv.ptr)
-                ey_ptrs.append(local_peers[r].ey_recv.ptr)
-            else:
-                a = self.ctx.ipc_open(all_handles[r][0], self.cap * self.h * 2)
-                b = self.ctx.ipc_open(all_handles[r][1], self.cap * self.h * 2)
-                self.opened += [a, b]
-                recv_ptrs.append(a.ptr)
-                ey_ptrs.append(b.ptr)
-        self.peers_recv.copy_(torch.tensor(recv_ptrs, dtype=torch.int64))
-        self.peers_ey.copy_(torch.tensor(ey_ptrs, dtype=torch.int64))
+    def connect(self, local_peers) -> None:
+        self.pb.connect(local_peers=[p.pb for p in local_peers])
 
     def close(self) -> None:
-        for b in self.opened:
-            self.ctx.ipc_close(b)
-        self.opened = []
+        self.pb.close()
 
     # ---- the phases
     def phase_sort(self, x, scores) -> None:
         self.x = x
+        self.parity ^= 1
         self.k_route(self.rows, self._w(scores), self._w(self.route))
         self.k_sort(self.rows, self._w(self.route), self._w(self.list), self._w(self.tiles), self._w(self.offs))
 
     def phase_dispatch(self) -> None:  # offs_all holds every rank's offsets
-        self.k_dispatch(self.rows, self._w(self.x), self._w(self.peers_recv), self._w(self.list), self._w(self.offs_all))
+        self.k_dispatch(self.rows, self._w(self.x), self.pb.table("recv"), self._w(self.list), self._w(self.offs_all))
 
     def phase_experts(self, wgu_local, wd_local) -> None:  # every rank's dispatch has finished
         self.k_plan(1, self._w(self.offs_all), self._w(self.rlist), self._w(self.rtiles))
@@ -349,34 +413,101 @@ class EpPeer:
         self.k_down(self.cap, self._w(wd_local), self._w(self.ehb), self.ey_recv, self._w(self.rlist), self._w(self.rtiles))
 
     def phase_return(self):  # every rank's expert GEMMs have finished
-        self.k_return(self.rows, self._w(self.peers_ey), self._w(self.ey), self._w(self.list), self._w(self.offs_all))
+        self.k_return(self.rows, self.pb.table("ey"), self._w(self.ey), self._w(self.list), self._w(self.offs_all))
         self.k_combine(self.rows, self._w(self.ey), self._w(self.route), self._w(self.out))
         return self.out
 
 
 def ep_peer_connect(state: EpPeer, group=None) -> None:
     """Exchanges the buffer handles among the processes of the group and maps the peers' buffers."""
-    world = dist.get_world_size(group) if dist.is_initialized() else 1
-    if world == 1:
-        state.connect(local_peers=[state])
-        return
-    gathered = [None] * world
-    dist.all_gather_object(gathered, state.handles(), group=group)
-    state.connect(all_handles=gathered)
+    state.pb.connect_group(group)
 
 
-def ep_moe_peer(state: EpPeer, x_local, scores_local, wgu_local, wd_local, group=None):
-    """The sparse block for this rank's token rows with the exchange through peer memory; returns out [rows][h]."""
+def ep_moe_peer(state: EpPeer, x_local, scores_local, wgu_local, wd_local, group=None, nccl_sync: bool = False):
+    """The sparse block for this rank's token rows with the exchange through peer memory; returns out [rows][h].
+    nccl_sync = True orders the steps with NCCL collectives (an all-gather and two one-word all-reduces) instead
+    of the library's barrier kernel; the data path is the same."""
     multi = state.world > 1
     state.phase_sort(x_local, scores_local)
-    if multi:
+    if not multi:
+        state.offs_all[0].copy_(state.offs)
+    elif nccl_sync:
         dist.all_gather_into_tensor(state.offs_all.view(-1), state.offs, group=group)
     else:
-        state.offs_all[0].copy_(state.offs)
+        state.pb.allgather(state.offs, "offs1" if state.parity else "offs0")
     state.phase_dispatch()
     if multi:
-        dist.all_reduce(state.token, group=group)  # every rank's rows have landed
+        dist.all_reduce(state.token, group=group) if nccl_sync else state.pb.barrier()  # every rank's rows have landed
     state.phase_experts(wgu_local, wd_local)
     if multi:
-        dist.all_reduce(state.token, group=group)  # every rank's outputs are complete
+        dist.all_reduce(state.token, group=group) if nccl_sync else state.pb.barrier()  # every rank's outputs are complete
     return state.phase_return()
+
+
+# --------------------------------------------------------------------------- tensor-parallel FFN over peer memory
+#
+# The same FFN as tp_ffn with the all-reduce replaced by the library's tp_reduce kernel: every rank's down GEMM
+# leaves its f32 partial in a buffer the peers can read; after a barrier each rank sums its slice of rows from all
+# partials (rank order), rounds, adds the residual and writes the bf16 rows into every rank's Y; a second barrier
+# closes the step. Per rank (P-1)/P of one f32 [m/P][h] slice per peer crosses NVLink instead of an all-reduce of
+# the whole f32 matrix, and the output mode needs no pass of its own.
+
+class TpPeer:
+    """One rank of the peer-memory FFN: the partial-product buffer, the output Y and their peer tables."""
+
+    def __init__(self, hb, ctx, rank: int, world: int, m: int, h: int, out: int = OUT_RESIDUAL, device=None):
+        self.hb, self.ctx, self.rank, self.world, self.m, self.h = hb, ctx, rank, world, m, h
+        dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+        self.pb = PeerBuffers(ctx, rank, world, {"acc": m * h * 4, "y": m * h * 2}, dev)
+        self.acc, self.y = self.pb.local["acc"], self.pb.local["y"]
+        self._yv = _view(self.y, (m, h), "<i2", dev).view(torch.bfloat16)
+        self.token = torch.zeros(1, device=dev, dtype=torch.float32)
+        self.k_reduce = ctx.tp_reduce(h, out, world, rank)
+        self.kernels = {}
+
+    def _w(self, t):
+        return self.ctx.wrap(t.data_ptr(), max(t.numel() * t.element_size(), 1))
+
+    def connect(self, local_peers) -> None:
+        self.pb.connect(local_peers=[p.pb for p in local_peers])
+
+    def close(self) -> None:
+        self.pb.close()
+
+    def set_y(self, y: torch.Tensor) -> None:
+        """Loads the residual stream (replicated: the same on every rank) into the shared Y."""
+        self._yv.copy_(y)
+
+    def y_view(self) -> torch.Tensor:
+        """Y as a torch tensor over the library's allocation (no copy)."""
+        return self._yv
+
+    def phase_gemms(self, x, wgu_local, wd_local) -> None:
+        m, h = x.shape
+        ip = wgu_local.shape[0] // 2
+        key = (h, ip)
+        if key not in self.kernels:
+            hmid = torch.empty((self.m, ip), device=x.device, dtype=torch.bfloat16)
+            self.kernels[key] = (self.ctx.gemm(h, 2 * ip, OUT_SWIGLU, rows_max=self.m, cta_pair=1), self.ctx.gemm(ip, h, OUT_F32, rows_max=self.m, cta_pair=1), hmid)
+        k_gu, k_down, hmid = self.kernels[key]
+        k_gu(m, self._w(wgu_local), self._w(x), self._w(hmid))
+        k_down(m, self._w(wd_local), self._w(hmid), self.acc)
+
+    def phase_reduce(self) -> None:  # every rank's partial is complete
+        self.k_reduce(self.m, self.pb.table("acc"), self.pb.table("y"))
+
+
+def tp_peer_connect(state: TpPeer, group=None) -> None:
+    state.pb.connect_group(group)
+
+
+def tp_ffn_peer(state: TpPeer, x, wgu_local, wd_local, group=None, nccl_sync: bool = False):
+    """state.y <- bf16(state.y + bf16(sum over ranks of H_r . Wd_r^T)) on every rank; returns the view of Y."""
+    multi = state.world > 1
+    state.phase_gemms(x, wgu_local, wd_local)
+    if multi:
+        dist.all_reduce(state.token, group=group) if nccl_sync else state.pb.barrier()  # every rank's partial is complete
+    state.phase_reduce()
+    if multi:
+        dist.all_reduce(state.token, group=group) if nccl_sync else state.pb.barrier()  # every rank's Y is complete
+    return state.y_view()

@@ -110,6 +110,19 @@ int hb_ipc_export(hb_ctx* ctx, void* dptr, void* handle64);
 int hb_ipc_open(hb_ctx* ctx, const void* handle64, void** dptr);
 int hb_ipc_close(hb_ctx* ctx, void* dptr);
 
+/* A barrier among the ranks of one node (one process and one GPU each) as a kernel on the stream, with an optional
+ * all-gather of a small table riding on it. Every rank owns flags u32[world] (zeroed) in a buffer the others have
+ * opened; `peers_flags` is a device array u64[world] of their addresses. hb_launch's m is the barrier's number:
+ * 1, 2, 3, ... in the same sequence on every rank. With words > 0 the kernel first copies `payload` u32[words] into
+ * slot `rank` of every rank's gather buffer u32[world][words] (`peers_gather`: their addresses); use two gather
+ * buffers in turn, a rank may start the next gather while another still reads this one. What a rank wrote before
+ * the barrier, to its own or a peer's memory, is visible to all after it. A rank that does not arrive within a few
+ * seconds turns into HB_KERNEL on the others at their next hb_sync. Never launch it for two ranks on one GPU.
+ * Bindings: peers_flags[, payload, peers_gather]. */
+int hb_peer_sync_get(hb_ctx* ctx, uint32_t words, uint32_t world, uint32_t rank, hb_kernel** res);
+/* How long a barrier waits for its peers before it gives up (default 5000 ms; 1..60000). */
+int hb_set_peer_wait_ms(hb_ctx* ctx, uint32_t ms);
+
 /* ---- copy lanes ---------------------------------------------------------
  * The reference's buffers are shared between CPU and GPU (src/metal/gpu.rs:92-110), so its engine
  * never copies activations. On a discrete GPU a prompt block crosses PCIe both ways; these calls let
@@ -217,6 +230,13 @@ int hb_ep_return_get(hb_ctx* ctx, uint32_t h, uint32_t top_k, uint32_t experts, 
  * [m][n] that was completed outside a GEMM: a row-parallel projection sums f32 partial products across GPUs
  * (hb_gemm_get with HB_OUT_F32 on each, then an all-reduce) and rounds once afterwards. Bindings: acc, y. */
 int hb_epilogue_get(hb_ctx* ctx, uint32_t n, uint32_t out, hb_kernel** res);
+/* The same, with the sum across GPUs and the distribution of the result inside the kernel (no reference
+ * counterpart): every rank holds an f32 partial [m][n] and a Y [m][n] in buffers the other ranks have opened
+ * (hb_ipc_open); `peers_acc` and `peers_y` are device arrays u64[world] of their addresses, the rank's own included.
+ * Rank r sums rows [r * ceil(m / world), ...) of all partials in rank order through NVLink loads, rounds once,
+ * applies the output mode with its own old Y and stores the result into every rank's Y. The host puts a barrier
+ * before (partials complete everywhere) and after (Y complete everywhere). Bindings: peers_acc, peers_y. */
+int hb_tp_reduce_get(hb_ctx* ctx, uint32_t n, uint32_t out, uint32_t world, uint32_t rank, hb_kernel** res);
 
 /* The GEMM for callers that must not allocate device memory. (No counterpart in the reference: its buffers all
  * come from Gpu::alloc at load.)

@@ -29,7 +29,7 @@ def inputs(oracle, m, h, mi, E, **_):
 
 def single_gpu_block(hb200, ctx, d, x, scores, wgu, wd, m, h, mi, E, top_k, bm):
     st = d.EpPeer(hb200, ctx, 0, 1, m, h, mi, E, top_k, bm)
-    st.connect(local_peers=[st])
+    st.connect([st])
     out = d.ep_moe_peer(st, x, scores, wgu, wd)
     return st, out
 
@@ -92,13 +92,13 @@ def test_emulated_ranks_equal_one_rank(env, hb200, oracle, world):
     rpr, epr = s["m"] // world, s["E"] // world
     ranks = [d.EpPeer(hb200, ctx, r, world, rpr, s["h"], s["mi"], s["E"], s["top_k"], s["bm"]) for r in range(world)]
     for st in ranks:
-        st.connect(local_peers=ranks)
+        st.connect(ranks)
     for rep in range(2):  # twice: the buffers carry the previous call's rows
         for r, st in enumerate(ranks):
             st.phase_sort(xt[r * rpr : (r + 1) * rpr].contiguous(), st_[r * rpr : (r + 1) * rpr].contiguous())
         offs_all = torch.stack([st.offs for st in ranks])
         for st in ranks:
-            st.offs_all.copy_(offs_all)
+            st.offs_all.copy_(offs_all)  # what the all-gather step of the multi-GPU job delivers
         for st in ranks:
             st.phase_dispatch()
         for r, st in enumerate(ranks):
@@ -122,7 +122,7 @@ def test_receive_buffer_too_small_is_reported_not_overrun(env, hb200, oracle):
     xt, st_, wgut, wdt = (t16(a).cuda() for a in (x, scores, wgu, wd))
     pairs = s["m"] * s["top_k"]
     st = d.EpPeer(hb200, ctx, 0, 1, s["m"], s["h"], s["mi"], s["E"], s["top_k"], s["bm"], cap=pairs - 64)
-    st.connect(local_peers=[st])
+    st.connect([st])
     guard = torch.full((4096,), 0x5A5A, device="cuda", dtype=torch.int16)  # lives right after nothing in particular: a canary of our own
     d.ep_moe_peer(st, xt, st_, wgut, wdt)
     torch.cuda.synchronize()
@@ -132,6 +132,26 @@ def test_receive_buffer_too_small_is_reported_not_overrun(env, hb200, oracle):
     assert int(st.rtiles[0]) == 0  # the plan published an empty table: the GEMMs did nothing
     assert bool((guard == 0x5A5A).all())
     ctx.sync()  # the status was cleared: the context is usable again
+
+
+def test_barrier_gives_up_on_a_rank_that_never_arrives(hb200):
+    # a two-rank barrier whose "peer" is a spare flag array on this GPU that nothing ever sets: the wait runs out
+    # (100 ms here), the kernel returns, the context reports it and stays usable
+    ctx = hb200.Context(0)
+    try:
+        ctx.set_peer_wait_ms(100)
+        mine, spare = ctx.alloc(256), ctx.alloc(256)
+        table = ctx.to_device(np.array([mine.ptr, spare.ptr], dtype=np.uint64))
+        ctx.peer_sync(0, 2, 0)(1, table)
+        with pytest.raises(hb200.HbError) as e:
+            ctx.sync()
+        assert e.value.status == hb200.KERNEL and "gave up waiting at point 5" in e.value.message
+        assert spare.download(np.uint32, (2,))[0] == 1  # its own arrival was published
+        ctx.sync()
+        with pytest.raises(hb200.HbError):
+            ctx.peer_sync(0, 1, 0)  # one rank has nobody to wait for
+    finally:
+        ctx.close()
 
 
 def _two_process_worker(rank, world, port, repo, result):
@@ -156,18 +176,37 @@ def _two_process_worker(rank, world, port, repo, result):
     with torch.cuda.stream(stream):
         xt, st_, wgut, wdt = (t16(a).cuda() for a in (x, scores, wgu, wd))
         one = d.EpPeer(hb, ctx, 0, 1, s["m"], s["h"], s["mi"], s["E"], s["top_k"], s["bm"])
-        one.connect(local_peers=[one])
+        one.connect([one])
         want = d.ep_moe_peer(one, xt, st_, wgut, wdt).clone()
         rpr, epr = s["m"] // world, s["E"] // world
         st = d.EpPeer(hb, ctx, rank, world, rpr, s["h"], s["mi"], s["E"], s["top_k"], s["bm"])
         d.ep_peer_connect(st)
-        for _ in range(3):
+        for it in range(6):  # the library's barrier kernel, then the NCCL form of the same steps
             out = d.ep_moe_peer(st, xt[rank * rpr : (rank + 1) * rpr].contiguous(), st_[rank * rpr : (rank + 1) * rpr].contiguous(),
-                                wgut[rank * epr * 2 * s["mi"] : (rank + 1) * epr * 2 * s["mi"]], wdt[rank * epr * s["h"] : (rank + 1) * epr * s["h"]])
+                                wgut[rank * epr * 2 * s["mi"] : (rank + 1) * epr * 2 * s["mi"]], wdt[rank * epr * s["h"] : (rank + 1) * epr * s["h"]],
+                                nccl_sync=it >= 4)
             stream.synchronize()
+            ctx.sync()
             ok = ok and bool(torch.equal(out, want[rank * rpr : (rank + 1) * rpr]))
         dist.barrier()
         st.close()
+        # the tensor-parallel FFN: both ranks end with the same Y, equal to the all-reduce form
+        m, h, inter = 200, 256, 512
+        x2, wgu2, wd2, y0 = o.normal((m, h), 1, 1, 1.0), o.normal((2 * inter, h), 2, 2, h**-0.5), o.normal((h, inter), 3, 3, inter**-0.5), o.normal((m, h), 4, 4, 1.0)
+        a, b = d.shard_gate_up(t16(wgu2), rank, world).cuda(), d.shard_down(t16(wd2), rank, world).cuda()
+        be = d.GpuBackend(hb, ctx, rows_max=512)
+        y_ref = d.tp_ffn(be, t16(x2).cuda(), a, b, t16(y0).cuda())
+        tp = d.TpPeer(hb, ctx, rank, world, m, h)
+        d.tp_peer_connect(tp)
+        for it in range(3):
+            tp.set_y(t16(y0).cuda())
+            dist.barrier()
+            y = d.tp_ffn_peer(tp, t16(x2).cuda(), a, b, nccl_sync=it == 2)
+            stream.synchronize()
+            ctx.sync()
+            ok = ok and bool(torch.equal(y, y_ref))
+            dist.barrier()
+        tp.close()
     flag = torch.tensor([1 if ok else 0], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
@@ -191,3 +230,43 @@ def test_two_processes_over_nvlink():
         p.join(timeout=300)
     assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
     assert result.get(timeout=10) == 1
+
+
+# ---------------------------------------------------------------- the tensor-parallel FFN through tp_reduce
+
+@pytest.mark.parametrize("world", [1, 2, 4])
+def test_tp_reduce_emulated_ranks(env, hb200, oracle, world):
+    d, ctx = env
+    m, h, inter = 200, 256, 512
+    x, wgu, wd, y0 = oracle.normal((m, h), 1, 1, 1.0), oracle.normal((2 * inter, h), 2, 2, h**-0.5), oracle.normal((h, inter), 3, 3, inter**-0.5), oracle.normal((m, h), 4, 4, 1.0)
+    xt = t16(x).cuda()
+    ranks = [d.TpPeer(hb200, ctx, r, world, m, h) for r in range(world)]
+    for st in ranks:
+        st.connect(ranks)
+        st.set_y(t16(y0).cuda())
+    shards = [(d.shard_gate_up(t16(wgu), r, world).cuda(), d.shard_down(t16(wd), r, world).cuda()) for r in range(world)]
+    for st, (a, b) in zip(ranks, shards):
+        st.phase_gemms(xt, a, b)
+    # what the all-reduce form gives from the same partials: f32 sum in rank order, then the epilogue kernel
+    acc = None
+    for st in ranks:
+        part = torch.empty(m, h, device="cuda", dtype=torch.float32)
+        part.copy_(torch.as_tensor(_cai(st.acc.ptr, (m, h), "<f4"), device="cuda"))
+        acc = part if acc is None else acc + part
+    be = d.GpuBackend(hb200, ctx, rows_max=512)
+    want = be.epilogue(acc, t16(y0).cuda(), 2)
+    for st in ranks:
+        st.phase_reduce()
+    torch.cuda.synchronize()
+    for st in ranks:
+        assert torch.equal(st.y_view(), want), f"rank {st.rank}"
+    hmid = oracle.gemm_f64(x, wgu, 3)
+    within_contract(oracle, oracle.gemm_f64(hmid, wd, 2, y0), n16(ranks[0].y_view().cpu()), f"FFN over {world} emulated ranks")
+
+
+def _cai(ptr, shape, typestr):
+    class H:
+        pass
+    h = H()
+    h.__cuda_array_interface__ = {"shape": shape, "typestr": typestr, "data": (ptr, False), "version": 3}
+    return h
