@@ -417,7 +417,8 @@ def run_case(args):
         w, x = rnd(n, k, scale=k**-0.5), rnd(8, k)
         y = torch.zeros(8, n, device=dev, dtype=torch.bfloat16)
         torch.cuda.synchronize()
-        kern = ctx.matvec(k, n, 0, rows_max=m, rows_per_warp=2 if m == 1 else 4, split=2 if m == 1 else 1, x_stationary=0 if m == 1 else 1)
+        # one row: a warp per two weight rows on the CUDA cores; eight rows: the weight stream on the tensor cores
+        kern = ctx.matvec(k, n, 0, rows_max=m, rows_per_warp=2, split=2) if m == 1 else ctx.matvec(k, n, 0, rows_max=m, tensor_core=1, split=4)
         ops = [(kern, m, wrap(w), wrap(x), wrap(y))]
         work = {"bytes": 2.0 * (n * k + m * k + m * n)}
     else:

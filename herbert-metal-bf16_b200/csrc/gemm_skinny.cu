@@ -1,0 +1,399 @@
+// Decode-time products with a few activation rows (1..64) on the tensor cores: Y[m][n] = out(X[m][k] . W[n][k]^T).
+//
+// The reference's matvec (src/metal/kernels.rs:146-214, 502-981) multiplies one activation row; its multi-row twin
+// exists only for Q4 weights (kernels.rs:990). With 4 or 8 rows a CUDA-core kernel spends 4 or 8 FMAs per weight
+// element and becomes issue-bound long before HBM is busy. Here the weights are the 128-row operand of tcgen05.mma
+// and the activation rows its narrow N side (16, 32 or 64 columns, rows past m zero-filled by TMA): the arithmetic
+// is free and the kernel is a pure weight stream - 16 KB TMA boxes of W into a ring of up to 12 stages, 2..8 KB of
+// X beside each. One persistent CTA per SM:
+//   warp 0    TMA producer;   warp 1    MMA issuer (TMEM: two accumulator sets, so an epilogue overlaps the next item);
+//   warps 2-5 epilogue: TMEM lane = output feature, TMEM column = activation row.
+// A work item is 128 features x one K range. When n / 128 gives too few items for 148 SMs the K loop is cut into
+// `ksplit` ranges; each item then leaves its f32 partial in scratch and bumps a counter, and whichever item of a
+// feature block arrives last adds the partials in range order (the same order whoever is last) and applies the
+// output mode (src/metal/kernels.rs:217-234). Nobody waits for anybody: no spin, only the bounded pipeline waits.
+#include <algorithm>
+#include <cstring>
+
+#include "hb_internal.hpp"
+#include "tc05.cuh"
+
+namespace hb {
+
+constexpr int SK_THREADS = 192;
+constexpr int SK_MAX_STAGES = 12;
+constexpr int SK_A_BYTES = 128 * 64 * 2;
+
+struct SkinnyParams {
+    void* y;
+    uint32_t m, n_out;
+    uint32_t k_blocks, ksplit, feat_blocks, items, stages;
+    float* scratch;       // [items][NACC * NP][128]
+    uint32_t* counters;   // [feat_blocks][4], zero between launches
+    uint32_t* status;
+};
+
+struct __align__(8) SkinnyBarriers {
+    uint64_t full[SK_MAX_STAGES];
+    uint64_t empty[SK_MAX_STAGES];
+    uint64_t tmem_full[2];
+    uint64_t tmem_empty[2];
+    uint32_t tmem_base;
+};
+
+template <int NP>
+__device__ __forceinline__ void skinny_ld(uint32_t taddr, uint32_t (&v)[NP]) {
+    if constexpr (NP == 16) {
+        tmem_ld_32x16(taddr, v);
+    } else if constexpr (NP == 32) {
+        tmem_ld_32x32(taddr, v);
+    } else {
+        uint32_t a[32], b[32];
+        tmem_ld_32x32(taddr, a);
+        tmem_ld_32x32(taddr + 32, b);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) { v[i] = a[i]; v[32 + i] = b[i]; }
+    }
+}
+
+// One output element of row j, feature f: the output mode applied to the finished sums.
+template <int OUT>
+__device__ __forceinline__ void skinny_store(const SkinnyParams& p, uint32_t j, uint32_t f, float g, float u) {
+    if constexpr (OUT == HB_OUT_F32) {
+        reinterpret_cast<float*>(p.y)[(size_t)j * p.n_out + f] = g;
+    } else {
+        uint16_t* y = reinterpret_cast<uint16_t*>(p.y) + (size_t)j * p.n_out + f;
+        uint32_t o;
+        if constexpr (OUT == HB_OUT_BF16) o = f32_to_bf16(g);
+        else if constexpr (OUT == HB_OUT_SWIGLU) o = swiglu_bf16(round_bf16(g), round_bf16(u));
+        else o = f32_to_bf16(__fadd_rn(bf16_to_f32(*y), round_bf16(g)));
+        *y = (uint16_t)o;
+    }
+}
+
+template <int OUT, int NP, int KPS>
+__global__ void __launch_bounds__(SK_THREADS, 1)
+gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const SkinnyParams p) {
+    constexpr int NACC = OUT == HB_OUT_SWIGLU ? 2 : 1;
+    constexpr int A_STAGE = NACC * SK_A_BYTES;
+    constexpr int B_BYTES = NP * 128;
+    constexpr int KB_BYTES = A_STAGE + B_BYTES;       // one 64-element k-block of W and X
+    constexpr int STAGE_BYTES = KPS * KB_BYTES;       // a stage holds KPS neighbouring k-blocks: longer runs per W row in DRAM
+    constexpr uint32_t SET_COLS = NACC * NP;
+    constexpr uint32_t TMEM_COLS = 2 * SET_COLS < 32 ? 32 : 2 * SET_COLS;
+    constexpr uint32_t IDESC = umma_idesc_bf16(128, NP);
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ SkinnyBarriers bars;
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t S = p.stages;
+
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < S; ++s) {
+            mbar_init(smem_u32(&bars.full[s]), 1);
+            mbar_init(smem_u32(&bars.empty[s]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&bars.tmem_full[a]), 1);
+            mbar_init(smem_u32(&bars.tmem_empty[a]), 4);
+        }
+        fence_mbar_init();
+        fence_proxy_async();
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&bars.tmem_base), TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = bars.tmem_base;
+
+    // item w: feature block w / ksplit, K range number w % ksplit = k-blocks [ks * KB / ksplit, (ks + 1) * KB / ksplit)
+    auto k_range = [&](uint32_t ks, uint32_t& kb0, uint32_t& kb1) {
+        kb0 = (uint32_t)(((uint64_t)ks * p.k_blocks) / p.ksplit);
+        kb1 = (uint32_t)(((uint64_t)(ks + 1) * p.k_blocks) / p.ksplit);
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            tma_prefetch_desc(&tm_w);
+            tma_prefetch_desc(&tm_x);
+            uint32_t s = 0, ph = 0;
+            bool ok = true;
+            for (uint32_t w = blockIdx.x; ok && w < p.items; w += gridDim.x) {
+                const uint32_t fb = w / p.ksplit;
+                uint32_t kb0, kb1;
+                k_range(w % p.ksplit, kb0, kb1);
+                const int row_w0 = (int)(fb * 128);
+                const int row_w1 = (int)(p.n_out + fb * 128);  // SWIGLU: the up rows of the same features
+                for (uint32_t kb = kb0; kb < kb1; kb += KPS) {
+                    if (!mbar_wait(smem_u32(&bars.empty[s]), ph ^ 1u)) {
+                        report(p.status, ST_WAIT_TIMEOUT, WHERE_EMPTY, s);
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t full = smem_u32(&bars.full[s]);
+                    const uint32_t nkb = min((uint32_t)KPS, kb1 - kb);
+                    mbar_arrive_expect_tx(full, nkb * KB_BYTES);
+#pragma unroll
+                    for (uint32_t i = 0; i < (uint32_t)KPS; ++i) {
+                        if (i < nkb) {
+                            const uint32_t dst = smem_base + s * STAGE_BYTES + i * KB_BYTES;
+                            tma_load_2d(dst, &tm_w, full, (int)((kb + i) * 64), row_w0);
+                            if (NACC == 2) tma_load_2d(dst + SK_A_BYTES, &tm_w, full, (int)((kb + i) * 64), row_w1);
+                            tma_load_2d(dst + A_STAGE, &tm_x, full, (int)((kb + i) * 64), 0);
+                        }
+                    }
+                    if (++s == S) { s = 0; ph ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            uint32_t s = 0, ph = 0, it = 0;
+            bool ok = true;
+            for (uint32_t w = blockIdx.x; ok && w < p.items; w += gridDim.x, ++it) {
+                uint32_t kb0, kb1;
+                k_range(w % p.ksplit, kb0, kb1);
+                const uint32_t acc = it & 1u, acc_ph = (it >> 1) & 1u;
+                if (!mbar_wait(smem_u32(&bars.tmem_empty[acc]), acc_ph ^ 1u)) {
+                    report(p.status, ST_WAIT_TIMEOUT, WHERE_TMEM_EMPTY, acc);
+                    break;
+                }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * SET_COLS;
+                for (uint32_t kb = kb0; kb < kb1; kb += KPS) {
+                    if (!mbar_wait(smem_u32(&bars.full[s]), ph)) {
+                        report(p.status, ST_WAIT_TIMEOUT, WHERE_FULL, s);
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after();
+                    const uint32_t nkb = min((uint32_t)KPS, kb1 - kb);
+#pragma unroll
+                    for (uint32_t i = 0; i < (uint32_t)KPS; ++i) {
+                        if (i < nkb) {
+                            const uint32_t a_addr = smem_base + s * STAGE_BYTES + i * KB_BYTES;
+                            const uint64_t a_desc = umma_desc_sw128(a_addr);
+                            const uint64_t b_desc = umma_desc_sw128(a_addr + A_STAGE);
+#pragma unroll
+                            for (uint32_t k4 = 0; k4 < 4; ++k4) {
+                                const uint32_t accum = (kb + i != kb0 || k4 != 0) ? 1u : 0u;
+                                umma_bf16(d_tmem, a_desc + 2 * k4, b_desc + 2 * k4, IDESC, accum);
+                                if (NACC == 2) umma_bf16(d_tmem + NP, umma_desc_sw128(a_addr + SK_A_BYTES) + 2 * k4, b_desc + 2 * k4, IDESC, accum);
+                            }
+                        }
+                    }
+                    umma_commit(smem_u32(&bars.empty[s]));
+                    if (++s == S) { s = 0; ph ^= 1u; }
+                }
+                if (ok) umma_commit(smem_u32(&bars.tmem_full[acc]));
+            }
+        }
+    } else {
+        const uint32_t q = (uint32_t)warp & 3u;
+        uint32_t it = 0;
+        for (uint32_t w = blockIdx.x; w < p.items; w += gridDim.x, ++it) {
+            const uint32_t fb = w / p.ksplit;
+            const uint32_t acc = it & 1u, acc_ph = (it >> 1) & 1u;
+            const bool got = mbar_wait(smem_u32(&bars.tmem_full[acc]), acc_ph);
+            if (!__all_sync(0xffffffffu, got)) {
+                if (lane == 0) report(p.status, ST_WAIT_TIMEOUT, WHERE_TMEM_FULL, acc);
+                break;
+            }
+            tc_fence_after();
+            const uint32_t t_addr = tmem_base + ((q * 32u) << 16) + acc * SET_COLS;
+            uint32_t g[NP], u[NP];
+            skinny_ld<NP>(t_addr, g);
+            if (NACC == 2) skinny_ld<NP>(t_addr + NP, u);
+            tmem_ld_wait();
+            // the accumulator is in registers: the MMA warp may have the set back
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bars.tmem_empty[acc]));
+            const uint32_t f = fb * 128 + q * 32 + lane;
+            if (p.ksplit == 1) {
+                if (f < p.n_out) {
+#pragma unroll
+                    for (int j = 0; j < NP; ++j)
+                        if ((uint32_t)j < p.m) skinny_store<OUT>(p, j, f, __uint_as_float(g[j]), NACC == 2 ? __uint_as_float(u[j]) : 0.f);
+                }
+                continue;
+            }
+            // this item's partial: [set row a * NP + j][128 features], this warp's 32 features of each row
+            float* mine = p.scratch + (size_t)w * (NACC * NP) * 128 + q * 32 + lane;
+#pragma unroll
+            for (int j = 0; j < NP; ++j) {
+                if ((uint32_t)j < p.m) {
+                    mine[(size_t)j * 128] = __uint_as_float(g[j]);
+                    if (NACC == 2) mine[(size_t)(NP + j) * 128] = __uint_as_float(u[j]);
+                }
+            }
+            __threadfence();
+            __syncwarp();
+            uint32_t arrived = 0;
+            if (lane == 0) arrived = atomicAdd(&p.counters[fb * 4 + q], 1u);
+            arrived = __shfl_sync(0xffffffffu, arrived, 0);
+            if (arrived + 1 != p.ksplit) continue;
+            // last of this feature quarter: every range's partial is in memory; add them in range order
+            __threadfence();
+            if (lane == 0) p.counters[fb * 4 + q] = 0;
+            const float* part = p.scratch + (size_t)fb * p.ksplit * (NACC * NP) * 128 + q * 32 + lane;
+            // range by range (the order of the sum), all rows of a range at once (independent loads in flight)
+            float sg[NP], su[NACC == 2 ? NP : 1];
+            for (uint32_t ks = 0; ks < p.ksplit; ++ks) {
+                const float* src = part + (size_t)ks * (NACC * NP) * 128;
+                float a[NP], b[NACC == 2 ? NP : 1];
+#pragma unroll
+                for (int j = 0; j < NP; ++j) {
+                    a[j] = (uint32_t)j < p.m ? __ldcg(src + (size_t)j * 128) : 0.f;
+                    if (NACC == 2) b[j] = (uint32_t)j < p.m ? __ldcg(src + (size_t)(NP + j) * 128) : 0.f;
+                }
+#pragma unroll
+                for (int j = 0; j < NP; ++j) {
+                    sg[j] = ks == 0 ? a[j] : __fadd_rn(sg[j], a[j]);
+                    if (NACC == 2) su[j] = ks == 0 ? b[j] : __fadd_rn(su[j], b[j]);
+                }
+            }
+            if (f < p.n_out) {
+#pragma unroll
+                for (int j = 0; j < NP; ++j)
+                    if ((uint32_t)j < p.m) skinny_store<OUT>(p, j, f, sg[j], NACC == 2 ? su[j] : 0.f);
+            }
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ------------------------------------------------------------------ host side
+
+namespace {
+
+typedef void (*skinny_fn)(const CUtensorMap, const CUtensorMap, const SkinnyParams);
+
+template <int NP, int KPS>
+skinny_fn skinny_pick_out(uint32_t out) {
+    switch (out) {
+        case HB_OUT_BF16: return gemm_skinny_kernel<HB_OUT_BF16, NP, KPS>;
+        case HB_OUT_F32: return gemm_skinny_kernel<HB_OUT_F32, NP, KPS>;
+        case HB_OUT_RESIDUAL: return gemm_skinny_kernel<HB_OUT_RESIDUAL, NP, KPS>;
+        case HB_OUT_SWIGLU: return gemm_skinny_kernel<HB_OUT_SWIGLU, NP, KPS>;
+    }
+    return nullptr;
+}
+
+template <int NP>
+skinny_fn skinny_pick_kps(uint32_t out, uint32_t kps) {
+    return kps == 1 ? skinny_pick_out<NP, 1>(out) : kps == 2 ? skinny_pick_out<NP, 2>(out) : skinny_pick_out<NP, 4>(out);
+}
+
+struct SkinnyGemm : hb_kernel {
+    uint32_t k = 0, n = 0, out = 0, rows_max = 0, np = 0, ksplit = 0, stages = 0;
+    skinny_fn fn = nullptr;
+    size_t smem = 0;
+    float* scratch = nullptr;
+    uint32_t* counters = nullptr;
+    const void* last_w = nullptr;
+    const void* last_x = nullptr;
+    uint32_t last_m = 0;
+    CUtensorMap tm_w{}, tm_x{};
+
+    int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
+        if (na != 3) return fail(ctx, HB_INVALID, name + ": bindings are W, x, y");
+        if (m == 0 || m > rows_max) return fail(ctx, HB_INVALID, name + ": m = " + std::to_string(m) + " outside 1.." + std::to_string(rows_max));
+        const uint32_t n_out = out == HB_OUT_SWIGLU ? n / 2 : n;
+        if (!range_ok(a[0], (size_t)n * k * 2) || !range_ok(a[1], (size_t)m * k * 2) || !range_ok(a[2], (size_t)m * n_out * (out == HB_OUT_F32 ? 4 : 2)))
+            return fail(ctx, HB_INVALID, name + ": a bound range is too small for " + std::to_string(m) + " rows");
+        if (a[0].ptr != last_w || a[1].ptr != last_x || m != last_m) {
+            int r = make_tmap_bf16(ctx, &tm_w, a[0].ptr, n, k, 128);
+            if (r != HB_OK) return r;
+            if ((r = make_tmap_bf16(ctx, &tm_x, a[1].ptr, m, k, np)) != HB_OK) return r;
+            last_w = a[0].ptr;
+            last_x = a[1].ptr;
+            last_m = m;
+        }
+        SkinnyParams p{};
+        p.y = a[2].ptr;
+        p.m = m;
+        p.n_out = n_out;
+        p.k_blocks = (k + 63) / 64;
+        p.ksplit = ksplit;
+        p.feat_blocks = (n_out + 127) / 128;
+        p.items = p.feat_blocks * ksplit;
+        p.stages = stages;
+        p.scratch = scratch;
+        p.counters = counters;
+        p.status = ctx->status_dev;
+        const uint32_t grid = std::min<uint32_t>(p.items, (uint32_t)ctx->sm_count);
+        fn<<<grid, SK_THREADS, smem, ctx->stream>>>(tm_w, tm_x, p);
+        HB_CUDA(ctx, cudaGetLastError());
+        ctx->launches++;
+        return HB_OK;
+    }
+};
+
+}  // namespace
+
+// d->tensor_core = the number of K ranges (1..16).
+int make_matvec_skinny(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out) {
+    *out = nullptr;
+    const uint32_t ksplit = d->tensor_core;
+    if (d->k == 0 || d->n == 0 || d->rows_max == 0) return fail(ctx, HB_INVALID, "matvec (tensor core): k, n and rows_max must be positive");
+    if (d->k % 8 != 0) return fail(ctx, HB_UNSUPPORTED, "matvec (tensor core): k must be a multiple of 8 (16-byte rows for TMA)");
+    if (d->rows_max > 64) return fail(ctx, HB_UNSUPPORTED, "matvec (tensor core): at most 64 activation rows (the prefill GEMM takes over)");
+    if (d->out > HB_OUT_SWIGLU) return fail(ctx, HB_INVALID, "matvec: unknown output mode");
+    if (d->out == HB_OUT_SWIGLU && d->n % 2 != 0) return fail(ctx, HB_INVALID, "matvec: the SwiGLU form needs an even n ([gate | up])");
+    const uint32_t k_blocks = (d->k + 63) / 64;
+    if (ksplit == 0 || ksplit > 16 || ksplit > k_blocks) return fail(ctx, HB_UNSUPPORTED, "matvec (tensor core): 1..16 K ranges, at most one per 64 elements of k");
+    const uint32_t np = d->rows_max <= 16 ? 16 : d->rows_max <= 32 ? 32 : 64;
+    const uint32_t kps = d->split == 2 ? 2u : d->split == 4 ? 4u : 1u;  // k-blocks per pipeline stage
+    skinny_fn fn = np == 16 ? skinny_pick_kps<16>(d->out, kps) : np == 32 ? skinny_pick_kps<32>(d->out, kps) : skinny_pick_kps<64>(d->out, kps);
+    const uint32_t nacc = d->out == HB_OUT_SWIGLU ? 2 : 1;
+    const size_t stage_bytes = ((size_t)nacc * SK_A_BYTES + np * 128) * kps;
+    const size_t budget = std::min<size_t>(ctx->smem_optin, 227 * 1024) - 2048;
+    const uint32_t stages = (uint32_t)std::min<size_t>(budget / stage_bytes, SK_MAX_STAGES);
+    if (stages < 2) return fail(ctx, HB_UNSUPPORTED, "matvec (tensor core): the pipeline does not fit in shared memory");
+    auto k = std::make_unique<SkinnyGemm>();
+    k->k = d->k;
+    k->n = d->n;
+    k->out = d->out;
+    k->rows_max = np;  // the kernel is built for a padded row count: any m up to it
+    k->np = np;
+    k->ksplit = ksplit;
+    k->stages = stages;
+    k->fn = fn;
+    k->smem = stages * stage_bytes + 1024;
+    k->kind = 2;
+    k->nargs = 3;
+    char nm[160];
+    snprintf(nm, sizeof nm, "matvec_tc_%ux%u_%s_m%u_ks%u_s%ux%u", d->k, d->n, out_tag(d->out), np, ksplit, stages, kps);
+    k->name = nm;
+    if (hb_kernel* have = find(ctx, k->name)) {
+        *out = have;
+        return HB_OK;
+    }
+    if (ksplit > 1) {
+        const uint32_t n_out = d->out == HB_OUT_SWIGLU ? d->n / 2 : d->n;
+        const size_t feat_blocks = (n_out + 127) / 128;
+        void* sc = nullptr;
+        void* cn = nullptr;
+        int r = hb_alloc(ctx, feat_blocks * ksplit * nacc * np * 128 * sizeof(float), &sc);
+        if (r != HB_OK) return r;
+        if ((r = hb_alloc(ctx, feat_blocks * 4 * sizeof(uint32_t), &cn)) != HB_OK) return r;
+        k->scratch = static_cast<float*>(sc);
+        k->counters = static_cast<uint32_t*>(cn);
+    }
+    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin - 1024);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(max dynamic shared memory)");
+    *out = intern(ctx, std::move(k));
+    return HB_OK;
+}
+
+}  // namespace hb

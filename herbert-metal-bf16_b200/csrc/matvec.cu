@@ -226,12 +226,14 @@ struct Matvec : hb_kernel {
 }  // namespace
 
 int make_matvec_xs(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out);
+int make_matvec_skinny(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out);
 
 int make_matvec(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out) {
     *out = nullptr;
     if (d->k == 0 || d->n == 0) return fail(ctx, HB_INVALID, "matvec: k and n must be positive");
     if (d->k % 8 != 0) return fail(ctx, HB_UNSUPPORTED, "matvec: K = " + std::to_string(d->k) + " is not a multiple of 8");
     if (d->out > HB_OUT_SWIGLU) return fail(ctx, HB_INVALID, "matvec: unknown output mode");
+    if (d->tensor_core) return make_matvec_skinny(ctx, d, out);
     if (d->x_stationary) return make_matvec_xs(ctx, d, out);
     if (d->rows_max < 1 || d->rows_max > 8) return fail(ctx, HB_UNSUPPORTED, "matvec: 1..8 activation rows");
     if (d->out > HB_OUT_SWIGLU) return fail(ctx, HB_INVALID, "matvec: unknown output mode");

@@ -481,9 +481,10 @@ int hb_select_matvec(hb_selector* s, uint32_t k, uint32_t n, uint32_t out, uint3
     try {
         const hb_tune& t = s->tune;
         int r;
-        auto get = [&](uint32_t rpw, uint32_t split, uint32_t persist, hb_kernel** kern, uint32_t xs = 0) {
+        auto get = [&](uint32_t rpw, uint32_t split, uint32_t persist, hb_kernel** kern, uint32_t xs = 0, uint32_t tc = 0) {
             hb_matvec_desc d{};
             d.x_stationary = xs;
+            d.tensor_core = tc;
             d.k = k;
             d.n = n;
             d.out = out;
@@ -539,6 +540,27 @@ int hb_select_matvec(hb_selector* s, uint32_t k, uint32_t n, uint32_t out, uint3
                 for (int i = 0; i < copies; ++i) add_op(c, kern, {w_copies[i], x, y});
                 cands.push_back(std::move(c));
             }
+        // the weight stream on the tensor cores: 2 or 4 K blocks per pipeline stage, the K loop whole or in 3 ranges
+        // (small n: more work items than SMs)
+        {
+            struct TcForm { const char* name; uint32_t ks, kps; };
+            const uint32_t n_out = out == HB_OUT_SWIGLU ? n / 2 : n;
+            for (const TcForm& f : {TcForm{"tc", 1, 2}, TcForm{"tcw", 1, 4}, TcForm{"tck3", 3, 2}}) {
+                if (f.ks > 1 && (n_out + 127) / 128 >= 2 * 148) continue;  // two waves of items without it
+                hb_matvec_desc d{};
+                d.k = k;
+                d.n = n;
+                d.out = out;
+                d.rows_max = rows;
+                d.tensor_core = f.ks;
+                d.split = f.kps;
+                if (hb_matvec_get(ctx, &d, &kern) != HB_OK) continue;
+                Cand c;
+                c.name = f.name;
+                for (int i = 0; i < copies; ++i) add_op(c, kern, {w_copies[i], x, y});
+                cands.push_back(std::move(c));
+            }
+        }
         if (cands.empty()) return hb::fail(ctx, HB_UNSUPPORTED, "matvec " + key + ": no form could be built");
         std::vector<char> eligible(cands.size(), 1);
         size_t best;

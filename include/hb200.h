@@ -182,13 +182,20 @@ int hb_gemm_get(hb_ctx* ctx, const hb_gemm_desc* desc, hb_kernel** out);
 typedef struct {
     uint32_t k, n;
     uint32_t out;           /* BF16, F32, RESIDUAL, SWIGLU (y of n/2, kernels.rs:934-944) */
-    uint32_t rows_max;      /* 1..8 activation rows */
+    uint32_t rows_max;      /* 1..8 activation rows (1..64 with tensor_core) */
     uint32_t rows_per_warp; /* W rows one warp reduces: 1, 2, 4 or 8 (the reference's `rows`) */
     uint32_t split;         /* K split across the warps of a block: 1, 2 or 4 (mv.split) */
     uint32_t persist;       /* 1 = a fixed grid that loops over the row groups (mv.persist) */
     uint32_t x_stationary;  /* 1 = for 2..8 activation rows: K is split across the threads of a persistent block and
                                each thread keeps its slice of the activations widened in registers; rows_per_warp
                                (2 or 4) is then the W rows reduced per step; needs K * rows <= 32768 */
+    uint32_t tensor_core;   /* > 0 = the product runs on the tensor cores as a weight stream (W rows are the 128-row
+                               operand of tcgen05.mma, the activation rows its narrow side): rows_max up to 64, the
+                               value is the number of ranges the K loop is cut into (1..16) so that small n still
+                               gives every SM work; partial sums are added in range order. Accumulation order
+                               inside a range is the tensor core's, as in the prefill GEMM. `split` (1, 2 or 4) is
+                               then the number of neighbouring 64-element K blocks one pipeline stage holds
+                               (longer runs per weight row in DRAM); the other form fields are ignored. */
 } hb_matvec_desc;
 int hb_matvec_get(hb_ctx* ctx, const hb_matvec_desc* desc, hb_kernel** out);
 

@@ -30,7 +30,11 @@ def within_contract(oracle, want, got, what):
         assert err <= 2e-6 * scale * 64 + 1e-5 * scale, f"{what}: f32 output off by {err} of {scale}"
         return
     c = oracle.compare(want, got)
-    assert c.over_1ulp <= 1e-3 * c.count, f"{what}: {c.over_1ulp}/{c.count} elements over 1 bf16 ulp (max {c.max_ulp})"
+    # The 99.9 % is a rate. On a small sample (under 100 000 elements) the count of outliers is tested against that
+    # rate with three standard deviations of a Poisson count of slack (one element at least); large samples get none.
+    lam = 1e-3 * c.count
+    bound = lam if c.count >= 100000 else max(lam + 3.0 * lam**0.5, 1.0)
+    assert c.over_1ulp <= bound, f"{what}: {c.over_1ulp}/{c.count} elements over 1 bf16 ulp (max {c.max_ulp})"
     assert c.max_abs_err <= c.max_abs_ref / 64, f"{what}: max err {c.max_abs_err} over 1/64 of {c.max_abs_ref}"
 
 

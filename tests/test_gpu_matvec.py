@@ -89,3 +89,50 @@ def test_k_multiple_of_8_only_and_unsupported(ctx, oracle, hb200):
         ctx.matvec(64, 64, rows_max=9)
     with pytest.raises(hb200.HbError):
         ctx.matvec(64, 64, OUT_SWIGLU, rows_per_warp=1)
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 16, 17, 40, 64])
+@pytest.mark.parametrize("out", [OUT_BF16, OUT_F32, OUT_RESIDUAL, OUT_SWIGLU])
+def test_tensor_core_forms(ctx, oracle, hb200, m, out):
+    # the weight stream on the tensor cores: W rows are the wide MMA operand, the 1..64 activation rows the narrow one
+    for k, n, splits in ((1024, 330, (1, 2, 5)), (4096, 512, (1, 3, 16)), (72, 40, (1, 2)), (2560, 96, (1, 4))):
+        for ks in splits:
+            for kps in (1, 2, 4):
+                if out == OUT_SWIGLU and kps == 4:  # two weight tiles per K block: four blocks per stage leave room for one stage only
+                    with pytest.raises(hb200.HbError) as e:
+                        ctx.matvec(k, n, out, rows_max=m, tensor_core=ks, split=kps)
+                    assert e.value.status == hb200.UNSUPPORTED
+                    continue
+                kern, want, got = run(ctx, oracle, m, k, n, out, tensor_core=ks, split=kps)
+                assert kern.name.startswith("matvec_tc_") and f"_ks{ks}_" in kern.name and kern.name.endswith(f"x{kps}")
+                within_contract(oracle, want, got, f"{kern.name} m={m}")
+
+
+def test_tensor_core_form_twice_and_limits(ctx, oracle, hb200):
+    # the split form leaves its counters at zero: a second launch of the same kernel object gives the same bits
+    m, k, n = 8, 4096, 640
+    x, w, y0 = gemm_inputs(oracle, m, k, n)
+    d_x, d_w = ctx.to_device(x), ctx.to_device(w)
+    kern = ctx.matvec(k, n, OUT_BF16, rows_max=m, tensor_core=4)
+    outs = []
+    for _ in range(3):
+        d_y = ctx.alloc(m * n * 2)
+        kern(m, d_w, d_x, d_y)
+        ctx.sync()
+        outs.append(d_y.download(np.uint16, (m, n)))
+    assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
+    within_contract(oracle, oracle.gemm_f64(x, w), outs[0], kern.name)
+    for bad in (dict(rows_max=65, tensor_core=1), dict(rows_max=8, tensor_core=17)):
+        with pytest.raises(hb200.HbError) as e:
+            ctx.matvec(k, n, OUT_BF16, **bad)
+        assert e.value.status == hb200.UNSUPPORTED
+    with pytest.raises(hb200.HbError):
+        ctx.matvec(64, 128, OUT_BF16, rows_max=4, tensor_core=2)  # more ranges than 64-element blocks of k
+
+
+@pytest.mark.parametrize("m", [1, 4, 8])
+def test_config2_shapes_tensor_core(ctx, oracle, m):
+    k, n = 4096, 12288
+    for ks in (1, 3):
+        kern, want, got = run(ctx, oracle, m, k, n, OUT_BF16, tensor_core=ks)
+        within_contract(oracle, want, got, f"{kern.name} m={m}")
