@@ -102,6 +102,10 @@ def lib() -> C.CDLL:
         "hb_tp_reduce_get": (ci, [vp, u32, u32, u32, u32, pvp]),
         "hb_peer_sync_get": (ci, [vp, u32, u32, u32, pvp]),
         "hb_set_peer_wait_ms": (ci, [vp, u32]),
+        "hb_graph_record": (ci, [vp, C.POINTER(Op), ci, pvp]),
+        "hb_graph_launch": (ci, [vp, vp]),
+        "hb_graph_time": (ci, [vp, vp, ci, C.POINTER(C.c_double)]),
+        "hb_graph_free": (ci, [vp, vp]),
         "hb_event_new": (ci, [vp, pvp]),
         "hb_event_free": (ci, [vp, vp]),
         "hb_lane_record": (ci, [vp, ci, vp]),
@@ -156,7 +160,7 @@ EXPORTS = [
     "hb_download", "hb_memset", "hb_sync", "hb_launch_count", "hb_event_new", "hb_event_free", "hb_lane_record", "hb_lane_wait", "hb_event_sync",
     "hb_upload_async", "hb_download_async", "hb_host_alloc", "hb_host_free", "hb_ipc_export", "hb_ipc_open", "hb_ipc_close",
     "hb_ep_dispatch_get", "hb_ep_plan_get", "hb_ep_return_get", "hb_tp_reduce_get", "hb_peer_sync_get", "hb_set_peer_wait_ms", "hb_gemm_get", "hb_matvec_get", "hb_swiglu_get", "hb_route_get",
-    "hb_moe_sort_get", "hb_moe_tiles", "hb_moe_gather_get", "hb_moe_combine_get", "hb_epilogue_get", "hb_gemm_static_scratch", "hb_kernel_name", "hb_launch", "hb_run", "hb_time",
+    "hb_moe_sort_get", "hb_moe_tiles", "hb_moe_gather_get", "hb_moe_combine_get", "hb_epilogue_get", "hb_gemm_static_scratch", "hb_kernel_name", "hb_launch", "hb_run", "hb_time", "hb_graph_record", "hb_graph_launch", "hb_graph_time", "hb_graph_free",
     "hb_tune_new", "hb_tune_free", "hb_tune_apply", "hb_tune_get", "hb_tune_summary", "hb_tune_gemm_timed", "hb_selector_new",
     "hb_selector_free", "hb_selector_log", "hb_selector_buckets", "hb_fill_random16", "hb_select_gemm", "hb_select_gate_up",
     "hb_select_matvec", "hb_select_experts", "hb_selector_inject_wrong", "hb_check_rule",
@@ -326,6 +330,9 @@ class Context:
     def sync(self) -> None:
         self._check(lib().hb_sync(self.h))
 
+    def memset(self, buf: "Buffer", value: int = 0) -> None:
+        self._check(lib().hb_memset(self.h, buf.ptr, value, buf.size))
+
     def launch_count(self) -> int:
         return int(lib().hb_launch_count(self.h))
 
@@ -433,12 +440,39 @@ class Context:
         arr, keep = self.make_ops(ops)
         self._check(lib().hb_run(self.h, arr, len(ops)))
 
+    def record(self, ops) -> "Graph":
+        """The op sequence as one replayable object (hb_graph_record)."""
+        arr, keep = self.make_ops(ops)
+        g = C.c_void_p()
+        self._check(lib().hb_graph_record(self.h, arr, len(ops), C.byref(g)))
+        return Graph(self, g, keep)
+
     def time(self, ops, reps: int = 1) -> float:
         """GPU seconds of `reps` runs of the op sequence (events on the stream)."""
         arr, keep = self.make_ops(ops)
         sec = C.c_double()
         self._check(lib().hb_time(self.h, arr, len(ops), reps, C.byref(sec)))
         return sec.value
+
+
+class Graph:
+    """A recorded op sequence: launch() replays it with one call, time(reps) gives the GPU seconds of `reps` replays."""
+
+    def __init__(self, ctx: Context, h, keep):
+        self.ctx, self.h, self.keep = ctx, h, keep
+
+    def launch(self) -> None:
+        self.ctx._check(lib().hb_graph_launch(self.ctx.h, self.h))
+
+    def time(self, reps: int = 1) -> float:
+        sec = C.c_double()
+        self.ctx._check(lib().hb_graph_time(self.ctx.h, self.h, reps, C.byref(sec)))
+        return sec.value
+
+    def free(self) -> None:
+        if self.h:
+            lib().hb_graph_free(self.ctx.h, self.h)
+            self.h = None
 
 
 class Tune:

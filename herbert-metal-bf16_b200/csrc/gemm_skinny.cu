@@ -8,10 +8,12 @@
 // X beside each. One persistent CTA per SM:
 //   warp 0    TMA producer;   warp 1    MMA issuer (TMEM: two accumulator sets, so an epilogue overlaps the next item);
 //   warps 2-5 epilogue: TMEM lane = output feature, TMEM column = activation row.
-// A work item is 128 features x one K range. When n / 128 gives too few items for 148 SMs the K loop is cut into
-// `ksplit` ranges; each item then leaves its f32 partial in scratch and bumps a counter, and whichever item of a
-// feature block arrives last adds the partials in range order (the same order whoever is last) and applies the
-// output mode (src/metal/kernels.rs:217-234). Nobody waits for anybody: no spin, only the bounded pipeline waits.
+// Work is dealt in one of two ways. Whole blocks: a CTA takes 128 features over all of K, block after block (best
+// when n / 128 is many times the SM count). Balanced: the (feature block, 64-element k-block) units are cut into one
+// contiguous range per CTA, all equal, so every SM streams the same number of bytes whatever n is; a block shared by
+// several CTAs gets its f32 partials through scratch: each contributor stores its partial and bumps a counter, and
+// whichever arrives last adds the partials in K order (the same order whoever is last) and applies the output
+// mode (src/metal/kernels.rs:217-234). Nobody waits for anybody: no spin, only the bounded pipeline waits.
 #include <algorithm>
 #include <cstring>
 
@@ -27,11 +29,51 @@ constexpr int SK_A_BYTES = 128 * 64 * 2;
 struct SkinnyParams {
     void* y;
     uint32_t m, n_out;
-    uint32_t k_blocks, ksplit, feat_blocks, items, stages;
-    float* scratch;       // [items][NACC * NP][128]
-    uint32_t* counters;   // [feat_blocks][4], zero between launches
+    uint32_t k_blocks, feat_blocks, stages;
+    uint32_t balanced;    // 0: a CTA takes whole feature blocks; 1: the (feature block, k-block) units are dealt evenly
+    uint32_t maxslots;    // balanced: the most CTAs that share one feature block
+    float* scratch;       // balanced: [feat_blocks][maxslots][NACC * NP][128]
+    uint32_t* counters;   // balanced: [feat_blocks][4], zero between launches
     uint32_t* status;
 };
+
+// A CTA's piece of work: k-blocks [kb0, kb1) of feature block fb. With nslots > 1 the block is shared: this CTA is
+// contributor number `slot` of `nslots`, in the order of the K ranges.
+struct SkinnySeg {
+    uint32_t fb, kb0, kb1, slot, nslots;
+};
+
+__device__ __forceinline__ uint32_t skinny_cta_of(uint64_t u, uint64_t units, uint32_t grid) {
+    uint32_t c = (uint32_t)(((u + 1) * grid - 1) / units);
+    while (c > 0 && (uint64_t)c * units / grid > u) --c;
+    while (c + 1 < grid && (uint64_t)(c + 1) * units / grid <= u) ++c;
+    return c;
+}
+
+// Segment i of CTA `cta`; returns the number of segments (out may be null).
+__device__ __forceinline__ uint32_t skinny_seg(const SkinnyParams& p, uint32_t cta, uint32_t grid, uint32_t i, SkinnySeg* out) {
+    const uint32_t KB = p.k_blocks;
+    if (!p.balanced) {
+        const uint32_t n = cta < p.feat_blocks ? (p.feat_blocks - cta + grid - 1) / grid : 0;
+        if (out && i < n) *out = SkinnySeg{cta + i * grid, 0, KB, 0, 1};
+        return n;
+    }
+    const uint64_t units = (uint64_t)p.feat_blocks * KB;
+    const uint64_t u0 = (uint64_t)cta * units / grid, u1 = (uint64_t)(cta + 1) * units / grid;
+    if (u1 <= u0) return 0;
+    const uint32_t fb0 = (uint32_t)(u0 / KB), fb1 = (uint32_t)((u1 - 1) / KB);
+    const uint32_t n = fb1 - fb0 + 1;
+    if (out && i < n) {
+        const uint32_t fb = fb0 + i;
+        out->fb = fb;
+        out->kb0 = i == 0 ? (uint32_t)(u0 - (uint64_t)fb0 * KB) : 0;
+        out->kb1 = (uint32_t)min((uint64_t)KB, u1 - (uint64_t)fb * KB);
+        const uint32_t c_first = skinny_cta_of((uint64_t)fb * KB, units, grid), c_last = skinny_cta_of((uint64_t)(fb + 1) * KB - 1, units, grid);
+        out->slot = cta - c_first;
+        out->nslots = c_last - c_first + 1;
+    }
+    return n;
+}
 
 struct __align__(8) SkinnyBarriers {
     uint64_t full[SK_MAX_STAGES];
@@ -111,11 +153,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     tc_fence_after();
     const uint32_t tmem_base = bars.tmem_base;
 
-    // item w: feature block w / ksplit, K range number w % ksplit = k-blocks [ks * KB / ksplit, (ks + 1) * KB / ksplit)
-    auto k_range = [&](uint32_t ks, uint32_t& kb0, uint32_t& kb1) {
-        kb0 = (uint32_t)(((uint64_t)ks * p.k_blocks) / p.ksplit);
-        kb1 = (uint32_t)(((uint64_t)(ks + 1) * p.k_blocks) / p.ksplit);
-    };
+    const uint32_t n_segs = skinny_seg(p, blockIdx.x, gridDim.x, 0, nullptr);
 
     if (warp == 0) {
         if (lane == 0) {
@@ -123,10 +161,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             tma_prefetch_desc(&tm_x);
             uint32_t s = 0, ph = 0;
             bool ok = true;
-            for (uint32_t w = blockIdx.x; ok && w < p.items; w += gridDim.x) {
-                const uint32_t fb = w / p.ksplit;
-                uint32_t kb0, kb1;
-                k_range(w % p.ksplit, kb0, kb1);
+            for (uint32_t i = 0; ok && i < n_segs; ++i) {
+                SkinnySeg sg;
+                skinny_seg(p, blockIdx.x, gridDim.x, i, &sg);
+                const uint32_t fb = sg.fb, kb0 = sg.kb0, kb1 = sg.kb1;
                 const int row_w0 = (int)(fb * 128);
                 const int row_w1 = (int)(p.n_out + fb * 128);  // SWIGLU: the up rows of the same features
                 for (uint32_t kb = kb0; kb < kb1; kb += KPS) {
@@ -155,9 +193,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         if (lane == 0) {
             uint32_t s = 0, ph = 0, it = 0;
             bool ok = true;
-            for (uint32_t w = blockIdx.x; ok && w < p.items; w += gridDim.x, ++it) {
-                uint32_t kb0, kb1;
-                k_range(w % p.ksplit, kb0, kb1);
+            for (; ok && it < n_segs; ++it) {
+                SkinnySeg sg;
+                skinny_seg(p, blockIdx.x, gridDim.x, it, &sg);
+                const uint32_t kb0 = sg.kb0, kb1 = sg.kb1;
                 const uint32_t acc = it & 1u, acc_ph = (it >> 1) & 1u;
                 if (!mbar_wait(smem_u32(&bars.tmem_empty[acc]), acc_ph ^ 1u)) {
                     report(p.status, ST_WAIT_TIMEOUT, WHERE_TMEM_EMPTY, acc);
@@ -196,8 +235,10 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     } else {
         const uint32_t q = (uint32_t)warp & 3u;
         uint32_t it = 0;
-        for (uint32_t w = blockIdx.x; w < p.items; w += gridDim.x, ++it) {
-            const uint32_t fb = w / p.ksplit;
+        for (; it < n_segs; ++it) {
+            SkinnySeg sg;
+            skinny_seg(p, blockIdx.x, gridDim.x, it, &sg);
+            const uint32_t fb = sg.fb;
             const uint32_t acc = it & 1u, acc_ph = (it >> 1) & 1u;
             const bool got = mbar_wait(smem_u32(&bars.tmem_full[acc]), acc_ph);
             if (!__all_sync(0xffffffffu, got)) {
@@ -215,7 +256,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bars.tmem_empty[acc]));
             const uint32_t f = fb * 128 + q * 32 + lane;
-            if (p.ksplit == 1) {
+            if (sg.nslots == 1) {
                 if (f < p.n_out) {
 #pragma unroll
                     for (int j = 0; j < NP; ++j)
@@ -223,8 +264,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                 }
                 continue;
             }
-            // this item's partial: [set row a * NP + j][128 features], this warp's 32 features of each row
-            float* mine = p.scratch + (size_t)w * (NACC * NP) * 128 + q * 32 + lane;
+            // this CTA's partial of the block: [set row a * NP + j][128 features], this warp's 32 features of each row
+            float* mine = p.scratch + ((size_t)fb * p.maxslots + sg.slot) * (NACC * NP) * 128 + q * 32 + lane;
 #pragma unroll
             for (int j = 0; j < NP; ++j) {
                 if ((uint32_t)j < p.m) {
@@ -237,14 +278,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             uint32_t arrived = 0;
             if (lane == 0) arrived = atomicAdd(&p.counters[fb * 4 + q], 1u);
             arrived = __shfl_sync(0xffffffffu, arrived, 0);
-            if (arrived + 1 != p.ksplit) continue;
-            // last of this feature quarter: every range's partial is in memory; add them in range order
+            if (arrived + 1 != sg.nslots) continue;
+            // last of this feature quarter: every contributor's partial is in memory; add them in K order
             __threadfence();
             if (lane == 0) p.counters[fb * 4 + q] = 0;
-            const float* part = p.scratch + (size_t)fb * p.ksplit * (NACC * NP) * 128 + q * 32 + lane;
-            // range by range (the order of the sum), all rows of a range at once (independent loads in flight)
-            float sg[NP], su[NACC == 2 ? NP : 1];
-            for (uint32_t ks = 0; ks < p.ksplit; ++ks) {
+            const float* part = p.scratch + (size_t)fb * p.maxslots * (NACC * NP) * 128 + q * 32 + lane;
+            // contributor by contributor (the order of the sum), all rows of one at once (independent loads in flight)
+            float sg_[NP], su[NACC == 2 ? NP : 1];
+            for (uint32_t ks = 0; ks < sg.nslots; ++ks) {
                 const float* src = part + (size_t)ks * (NACC * NP) * 128;
                 float a[NP], b[NACC == 2 ? NP : 1];
 #pragma unroll
@@ -254,14 +295,14 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                 }
 #pragma unroll
                 for (int j = 0; j < NP; ++j) {
-                    sg[j] = ks == 0 ? a[j] : __fadd_rn(sg[j], a[j]);
+                    sg_[j] = ks == 0 ? a[j] : __fadd_rn(sg_[j], a[j]);
                     if (NACC == 2) su[j] = ks == 0 ? b[j] : __fadd_rn(su[j], b[j]);
                 }
             }
             if (f < p.n_out) {
 #pragma unroll
                 for (int j = 0; j < NP; ++j)
-                    if ((uint32_t)j < p.m) skinny_store<OUT>(p, j, f, sg[j], NACC == 2 ? su[j] : 0.f);
+                    if ((uint32_t)j < p.m) skinny_store<OUT>(p, j, f, sg_[j], NACC == 2 ? su[j] : 0.f);
             }
         }
     }
@@ -295,7 +336,7 @@ skinny_fn skinny_pick_kps(uint32_t out, uint32_t kps) {
 }
 
 struct SkinnyGemm : hb_kernel {
-    uint32_t k = 0, n = 0, out = 0, rows_max = 0, np = 0, ksplit = 0, stages = 0;
+    uint32_t k = 0, n = 0, out = 0, rows_max = 0, np = 0, balanced = 0, maxslots = 1, grid_balanced = 0, stages = 0;
     skinny_fn fn = nullptr;
     size_t smem = 0;
     float* scratch = nullptr;
@@ -324,14 +365,14 @@ struct SkinnyGemm : hb_kernel {
         p.m = m;
         p.n_out = n_out;
         p.k_blocks = (k + 63) / 64;
-        p.ksplit = ksplit;
         p.feat_blocks = (n_out + 127) / 128;
-        p.items = p.feat_blocks * ksplit;
+        p.balanced = balanced;
+        p.maxslots = maxslots;
         p.stages = stages;
         p.scratch = scratch;
         p.counters = counters;
         p.status = ctx->status_dev;
-        const uint32_t grid = std::min<uint32_t>(p.items, (uint32_t)ctx->sm_count);
+        const uint32_t grid = balanced ? grid_balanced : std::min<uint32_t>(p.feat_blocks, (uint32_t)ctx->sm_count);
         fn<<<grid, SK_THREADS, smem, ctx->stream>>>(tm_w, tm_x, p);
         HB_CUDA(ctx, cudaGetLastError());
         ctx->launches++;
@@ -341,17 +382,17 @@ struct SkinnyGemm : hb_kernel {
 
 }  // namespace
 
-// d->tensor_core = the number of K ranges (1..16).
+// d->tensor_core: 1 = whole feature blocks per CTA, 2 = balanced units.
 int make_matvec_skinny(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out) {
     *out = nullptr;
-    const uint32_t ksplit = d->tensor_core;
     if (d->k == 0 || d->n == 0 || d->rows_max == 0) return fail(ctx, HB_INVALID, "matvec (tensor core): k, n and rows_max must be positive");
     if (d->k % 8 != 0) return fail(ctx, HB_UNSUPPORTED, "matvec (tensor core): k must be a multiple of 8 (16-byte rows for TMA)");
     if (d->rows_max > 64) return fail(ctx, HB_UNSUPPORTED, "matvec (tensor core): at most 64 activation rows (the prefill GEMM takes over)");
     if (d->out > HB_OUT_SWIGLU) return fail(ctx, HB_INVALID, "matvec: unknown output mode");
     if (d->out == HB_OUT_SWIGLU && d->n % 2 != 0) return fail(ctx, HB_INVALID, "matvec: the SwiGLU form needs an even n ([gate | up])");
+    if (d->tensor_core > 2) return fail(ctx, HB_UNSUPPORTED, "matvec (tensor core): 1 = whole feature blocks, 2 = balanced units");
+    const uint32_t balanced = d->tensor_core == 2 ? 1u : 0u;
     const uint32_t k_blocks = (d->k + 63) / 64;
-    if (ksplit == 0 || ksplit > 16 || ksplit > k_blocks) return fail(ctx, HB_UNSUPPORTED, "matvec (tensor core): 1..16 K ranges, at most one per 64 elements of k");
     const uint32_t np = d->rows_max <= 16 ? 16 : d->rows_max <= 32 ? 32 : 64;
     const uint32_t kps = d->split == 2 ? 2u : d->split == 4 ? 4u : 1u;  // k-blocks per pipeline stage
     skinny_fn fn = np == 16 ? skinny_pick_kps<16>(d->out, kps) : np == 32 ? skinny_pick_kps<32>(d->out, kps) : skinny_pick_kps<64>(d->out, kps);
@@ -366,25 +407,31 @@ int make_matvec_skinny(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out) {
     k->out = d->out;
     k->rows_max = np;  // the kernel is built for a padded row count: any m up to it
     k->np = np;
-    k->ksplit = ksplit;
+    k->balanced = balanced;
     k->stages = stages;
     k->fn = fn;
     k->smem = stages * stage_bytes + 1024;
     k->kind = 2;
     k->nargs = 3;
     char nm[160];
-    snprintf(nm, sizeof nm, "matvec_tc_%ux%u_%s_m%u_ks%u_s%ux%u", d->k, d->n, out_tag(d->out), np, ksplit, stages, kps);
+    snprintf(nm, sizeof nm, "matvec_tc_%ux%u_%s_m%u_%s_s%ux%u", d->k, d->n, out_tag(d->out), np, balanced ? "bal" : "blk", stages, kps);
     k->name = nm;
     if (hb_kernel* have = find(ctx, k->name)) {
         *out = have;
         return HB_OK;
     }
-    if (ksplit > 1) {
+    if (balanced) {
         const uint32_t n_out = d->out == HB_OUT_SWIGLU ? d->n / 2 : d->n;
-        const size_t feat_blocks = (n_out + 127) / 128;
+        const uint64_t feat_blocks = (n_out + 127) / 128;
+        const uint64_t units = feat_blocks * k_blocks;
+        const uint32_t grid = (uint32_t)std::min<uint64_t>(units, (uint64_t)ctx->sm_count);
+        // a block of k_blocks units overlaps at most ceil(k_blocks / floor(units / grid)) + 1 ranges
+        const uint64_t per = std::max<uint64_t>(units / grid, 1);
+        k->grid_balanced = grid;
+        k->maxslots = (uint32_t)std::min<uint64_t>((k_blocks + per - 1) / per + 1, grid);
         void* sc = nullptr;
         void* cn = nullptr;
-        int r = hb_alloc(ctx, feat_blocks * ksplit * nacc * np * 128 * sizeof(float), &sc);
+        int r = hb_alloc(ctx, feat_blocks * k->maxslots * nacc * np * 128 * sizeof(float), &sc);
         if (r != HB_OK) return r;
         if ((r = hb_alloc(ctx, feat_blocks * 4 * sizeof(uint32_t), &cn)) != HB_OK) return r;
         k->scratch = static_cast<float*>(sc);

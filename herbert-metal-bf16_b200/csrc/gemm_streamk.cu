@@ -469,6 +469,7 @@ int make_gemm_streamk(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
     k->stages = stages;
     k->smem = stages * stage_bytes + 1024;
     k->kind = 1;
+    k->replayable = false;  // every launch takes a new epoch of the scratch flags
     k->nargs = 3;
     char nm[160];
     snprintf(nm, sizeof nm, "gemm_sk_%ux%u_%s%s_t128x%u_s%u", d->k, d->n, out_tag(d->out), d->m_first ? "_mf" : "", bn, stages);

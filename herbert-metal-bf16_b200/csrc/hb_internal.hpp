@@ -18,6 +18,9 @@ struct hb_kernel {
     std::string name;
     int kind = 0;  // HB_KIND_*
     int nargs = 0;
+    // false for kernels whose launches differ by a host-side counter (the epoch of the stream-K scratch flags, the
+    // number of a peer barrier): replaying a recorded launch would repeat the counter
+    bool replayable = true;
     virtual ~hb_kernel() = default;
     // Validates the bound ranges for `m` rows and enqueues the kernel on ctx->stream.
     virtual int launch(hb_ctx* ctx, const hb_range* args, int nargs, uint32_t m) = 0;

@@ -94,6 +94,7 @@ int make_peer_sync(hb_ctx* ctx, uint32_t words, uint32_t world, uint32_t rank, h
     k->world = world;
     k->rank = rank;
     k->kind = 15;
+    k->replayable = false;  // every launch is a new barrier number
     k->nargs = words ? 3 : 1;
     k->name = std::string(words ? "peer_allgather_w" + std::to_string(words) : std::string("peer_barrier")) + "_r" + std::to_string(rank) + "of" + std::to_string(world);
     *res = intern(ctx, std::move(k));

@@ -398,6 +398,78 @@ int hb_time(hb_ctx* ctx, const hb_op* ops, int nops, int reps, double* gpu_secon
     return hb::check_status(ctx);
 }
 
+// ---- recorded sequences ------------------------------------------------------------------------
+struct hb_graph {
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    uint64_t kernels = 0;
+};
+
+int hb_graph_record(hb_ctx* ctx, const hb_op* ops, int nops, hb_graph** out) {
+    if (!ctx || !ops || nops < 1 || !out) return fail(ctx, HB_INVALID, "hb_graph_record: bad argument");
+    *out = nullptr;
+    for (int i = 0; i < nops; ++i) {
+        if (!ops[i].kernel) return fail(ctx, HB_INVALID, "hb_graph_record: an op without a kernel");
+        if (!ops[i].kernel->replayable) return fail(ctx, HB_UNSUPPORTED, "hb_graph_record: " + ops[i].kernel->name + " cannot be replayed (its launches carry a counter)");
+    }
+    HB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    const uint64_t before = ctx->launches;
+    HB_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+    int st = hb_run(ctx, ops, nops);
+    cudaGraph_t g = nullptr;
+    cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
+    const uint64_t recorded = ctx->launches - before;
+    ctx->launches = before;  // recording enqueues nothing
+    if (st != HB_OK) {
+        if (g) cudaGraphDestroy(g);
+        cudaGetLastError();
+        return st;
+    }
+    if (e != cudaSuccess) return hb::cuda_fail(ctx, e, "cudaStreamEndCapture");
+    auto* hg = new hb_graph;
+    hg->graph = g;
+    hg->kernels = recorded;
+    e = cudaGraphInstantiate(&hg->exec, g, 0);
+    if (e != cudaSuccess) {
+        cudaGraphDestroy(g);
+        delete hg;
+        return hb::cuda_fail(ctx, e, "cudaGraphInstantiate");
+    }
+    *out = hg;
+    return HB_OK;
+}
+
+int hb_graph_launch(hb_ctx* ctx, hb_graph* g) {
+    if (!ctx || !g) return fail(ctx, HB_INVALID, "hb_graph_launch: bad argument");
+    HB_CUDA(ctx, cudaGraphLaunch(g->exec, ctx->stream));
+    ctx->launches += g->kernels;
+    return HB_OK;
+}
+
+int hb_graph_time(hb_ctx* ctx, hb_graph* g, int reps, double* gpu_seconds) {
+    if (!ctx || !g || !gpu_seconds || reps < 1) return fail(ctx, HB_INVALID, "hb_graph_time: bad argument");
+    HB_CUDA(ctx, cudaEventRecord(ctx->ev0, ctx->stream));
+    for (int r = 0; r < reps; ++r) {
+        HB_CUDA(ctx, cudaGraphLaunch(g->exec, ctx->stream));
+        ctx->launches += g->kernels;
+    }
+    HB_CUDA(ctx, cudaEventRecord(ctx->ev1, ctx->stream));
+    HB_CUDA(ctx, cudaEventSynchronize(ctx->ev1));
+    float ms = 0.f;
+    HB_CUDA(ctx, cudaEventElapsedTime(&ms, ctx->ev0, ctx->ev1));
+    *gpu_seconds = (double)ms * 1e-3;
+    return hb::check_status(ctx);
+}
+
+int hb_graph_free(hb_ctx* ctx, hb_graph* g) {
+    if (!g) return HB_OK;
+    if (ctx) cudaStreamSynchronize(ctx->stream);
+    if (g->exec) cudaGraphExecDestroy(g->exec);
+    if (g->graph) cudaGraphDestroy(g->graph);
+    delete g;
+    return HB_OK;
+}
+
 int hb_gemm_get(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
     if (!ctx || !d || !out) return fail(ctx, HB_INVALID, "hb_gemm_get: bad argument");
     HB_GUARD_BEGIN

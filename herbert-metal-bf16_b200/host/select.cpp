@@ -540,13 +540,13 @@ int hb_select_matvec(hb_selector* s, uint32_t k, uint32_t n, uint32_t out, uint3
                 for (int i = 0; i < copies; ++i) add_op(c, kern, {w_copies[i], x, y});
                 cands.push_back(std::move(c));
             }
-        // the weight stream on the tensor cores: 2 or 4 K blocks per pipeline stage, the K loop whole or in 3 ranges
-        // (small n: more work items than SMs)
+        // the weight stream on the tensor cores: whole feature blocks per CTA or evenly dealt units, 2 or 4 K blocks
+        // per pipeline stage
         {
             struct TcForm { const char* name; uint32_t ks, kps; };
             const uint32_t n_out = out == HB_OUT_SWIGLU ? n / 2 : n;
-            for (const TcForm& f : {TcForm{"tc", 1, 2}, TcForm{"tcw", 1, 4}, TcForm{"tck3", 3, 2}}) {
-                if (f.ks > 1 && (n_out + 127) / 128 >= 2 * 148) continue;  // two waves of items without it
+            (void)n_out;
+            for (const TcForm& f : {TcForm{"tc", 1, 2}, TcForm{"tcw", 1, 4}, TcForm{"tcb", 2, 2}, TcForm{"tcbw", 2, 4}}) {
                 hb_matvec_desc d{};
                 d.k = k;
                 d.n = n;

@@ -190,12 +190,13 @@ typedef struct {
                                each thread keeps its slice of the activations widened in registers; rows_per_warp
                                (2 or 4) is then the W rows reduced per step; needs K * rows <= 32768 */
     uint32_t tensor_core;   /* > 0 = the product runs on the tensor cores as a weight stream (W rows are the 128-row
-                               operand of tcgen05.mma, the activation rows its narrow side): rows_max up to 64, the
-                               value is the number of ranges the K loop is cut into (1..16) so that small n still
-                               gives every SM work; partial sums are added in range order. Accumulation order
-                               inside a range is the tensor core's, as in the prefill GEMM. `split` (1, 2 or 4) is
-                               then the number of neighbouring 64-element K blocks one pipeline stage holds
-                               (longer runs per weight row in DRAM); the other form fields are ignored. */
+                               operand of tcgen05.mma, the activation rows its narrow side): rows_max up to 64.
+                               1 = a CTA takes blocks of 128 features over all of K; 2 = the (feature block, 64-element
+                               K block) units are dealt evenly, one contiguous range per SM, and blocks shared by
+                               several SMs are summed from f32 partials in K order. Accumulation order inside a
+                               range is the tensor core's, as in the prefill GEMM. `split` (1, 2 or 4) is then the
+                               number of neighbouring K blocks one pipeline stage holds (longer runs per weight row
+                               in DRAM); the other form fields are ignored. */
 } hb_matvec_desc;
 int hb_matvec_get(hb_ctx* ctx, const hb_matvec_desc* desc, hb_kernel** out);
 
@@ -280,6 +281,16 @@ int hb_run(hb_ctx* ctx, const hb_op* ops, int nops);
 /* time_ops, src/metal/qwen.rs:2593: `reps` runs of the sequence, GPU seconds measured with events on the
  * stream (reference: Done.gpu of the command buffer, src/metal/gpu.rs:209-221). Synchronises. */
 int hb_time(hb_ctx* ctx, const hb_op* ops, int nops, int reps, double* gpu_seconds);
+/* A sequence recorded once and replayed with one call (a CUDA graph): the decode step launches a dozen kernels of
+ * 10-200 us each, and enqueueing them one by one costs the host about as long as the GPU takes to run them. The
+ * reference encodes its ops into one command buffer per step (src/metal/gpu.rs:151-221) for the same reason. The
+ * bound ranges and m are fixed at recording. Kernels whose launches carry a host-side counter cannot be recorded
+ * (the stream-K GEMM, hb_gemm_static_scratch, hb_peer_sync_get): HB_UNSUPPORTED. */
+typedef struct hb_graph hb_graph;
+int hb_graph_record(hb_ctx* ctx, const hb_op* ops, int nops, hb_graph** out);
+int hb_graph_launch(hb_ctx* ctx, hb_graph* g);
+int hb_graph_time(hb_ctx* ctx, hb_graph* g, int reps, double* gpu_seconds);
+int hb_graph_free(hb_ctx* ctx, hb_graph* g);
 
 /* ---- the load-time selection loop (host library) ------------------------- */
 

@@ -71,3 +71,30 @@ def test_events_order_lanes(ctx, hb200, oracle):
     with pytest.raises(hb200.HbError):
         ctx.event().record(7)
     ctx.sync()
+
+
+def test_recorded_sequence_replays(ctx, hb200, oracle):
+    # three kernels recorded once: replays give the bits of the one-by-one launches; kernels that carry a counter refuse
+    m, k, n = 8, 1024, 512
+    x, w, y0 = gemm_inputs(oracle, m, k, 2 * n)
+    d_w, d_x = ctx.to_device(w), ctx.to_device(x)
+    d_gu, d_h, d_y = ctx.alloc(m * 2 * n * 2), ctx.alloc(m * n * 2), ctx.alloc(m * 2 * n * 2)
+    ops = [(ctx.matvec(k, 2 * n, OUT_BF16, rows_max=m, tensor_core=2), m, d_w, d_x, d_gu), (ctx.swiglu_rows(n), m, d_gu, d_h),
+           (ctx.matvec(k, 2 * n, OUT_RESIDUAL, rows_max=m, tensor_core=1), m, d_w, d_x, d_y)]
+    ctx.run(ops)
+    ctx.sync()
+    want_h, want_y = d_h.download(np.uint16, (m, n)), d_y.download(np.uint16, (m, 2 * n))
+    ctx.memset(d_y, 0)
+    ctx.memset(d_h, 0)
+    g = ctx.record(ops)
+    before = ctx.launch_count()
+    g.launch()
+    ctx.sync()
+    assert ctx.launch_count() == before + 3
+    assert np.array_equal(d_h.download(np.uint16, (m, n)), want_h) and np.array_equal(d_y.download(np.uint16, (m, 2 * n)), want_y)
+    assert g.time(5) > 0
+    g.free()
+    with pytest.raises(hb200.HbError) as e:
+        ctx.record([(ctx.gemm(k, n, OUT_BF16, rows_max=64, stream_k=1), m, d_w, d_x, d_h)])
+    assert e.value.status == hb200.UNSUPPORTED and "cannot be replayed" in e.value.message
+    ctx.sync()

@@ -95,8 +95,10 @@ def test_k_multiple_of_8_only_and_unsupported(ctx, oracle, hb200):
 @pytest.mark.parametrize("out", [OUT_BF16, OUT_F32, OUT_RESIDUAL, OUT_SWIGLU])
 def test_tensor_core_forms(ctx, oracle, hb200, m, out):
     # the weight stream on the tensor cores: W rows are the wide MMA operand, the 1..64 activation rows the narrow one
-    for k, n, splits in ((1024, 330, (1, 2, 5)), (4096, 512, (1, 3, 16)), (72, 40, (1, 2)), (2560, 96, (1, 4))):
-        for ks in splits:
+    for k, n in ((1024, 330), (4096, 512), (72, 40), (2560, 96), (8192, 1200)):
+        if out == OUT_SWIGLU and k > 4096:
+            continue  # three roundings after a sum of 8192 f32 terms: outside what the one-ulp rate is stated for
+        for ks in (1, 2):  # whole feature blocks per CTA; evenly dealt (block, k-block) units
             for kps in (1, 2, 4):
                 if out == OUT_SWIGLU and kps == 4:  # two weight tiles per K block: four blocks per stage leave room for one stage only
                     with pytest.raises(hb200.HbError) as e:
@@ -104,7 +106,7 @@ def test_tensor_core_forms(ctx, oracle, hb200, m, out):
                     assert e.value.status == hb200.UNSUPPORTED
                     continue
                 kern, want, got = run(ctx, oracle, m, k, n, out, tensor_core=ks, split=kps)
-                assert kern.name.startswith("matvec_tc_") and f"_ks{ks}_" in kern.name and kern.name.endswith(f"x{kps}")
+                assert kern.name.startswith("matvec_tc_") and ("_blk_", "_bal_")[ks - 1] in kern.name and kern.name.endswith(f"x{kps}")
                 within_contract(oracle, want, got, f"{kern.name} m={m}")
 
 
@@ -113,7 +115,7 @@ def test_tensor_core_form_twice_and_limits(ctx, oracle, hb200):
     m, k, n = 8, 4096, 640
     x, w, y0 = gemm_inputs(oracle, m, k, n)
     d_x, d_w = ctx.to_device(x), ctx.to_device(w)
-    kern = ctx.matvec(k, n, OUT_BF16, rows_max=m, tensor_core=4)
+    kern = ctx.matvec(k, n, OUT_BF16, rows_max=m, tensor_core=2)
     outs = []
     for _ in range(3):
         d_y = ctx.alloc(m * n * 2)
@@ -122,17 +124,15 @@ def test_tensor_core_form_twice_and_limits(ctx, oracle, hb200):
         outs.append(d_y.download(np.uint16, (m, n)))
     assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
     within_contract(oracle, oracle.gemm_f64(x, w), outs[0], kern.name)
-    for bad in (dict(rows_max=65, tensor_core=1), dict(rows_max=8, tensor_core=17)):
+    for bad in (dict(rows_max=65, tensor_core=1), dict(rows_max=8, tensor_core=3)):
         with pytest.raises(hb200.HbError) as e:
             ctx.matvec(k, n, OUT_BF16, **bad)
         assert e.value.status == hb200.UNSUPPORTED
-    with pytest.raises(hb200.HbError):
-        ctx.matvec(64, 128, OUT_BF16, rows_max=4, tensor_core=2)  # more ranges than 64-element blocks of k
 
 
 @pytest.mark.parametrize("m", [1, 4, 8])
 def test_config2_shapes_tensor_core(ctx, oracle, m):
     k, n = 4096, 12288
-    for ks in (1, 3):
-        kern, want, got = run(ctx, oracle, m, k, n, OUT_BF16, tensor_core=ks)
+    for ks in (1, 2):
+        kern, want, got = run(ctx, oracle, m, k, n, OUT_BF16, tensor_core=ks, split=2)
         within_contract(oracle, want, got, f"{kern.name} m={m}")
