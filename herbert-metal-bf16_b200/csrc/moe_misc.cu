@@ -138,9 +138,12 @@ __global__ void moe_combine_kernel(const uint16_t* __restrict__ y, const uint32_
     const size_t total = (size_t)rows * d8;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const uint32_t row = (uint32_t)(i / d8), c = (uint32_t)(i % d8);
-        float acc[8];
+        float acc[8];        // F32SUM: the running sums
+        uint32_t accp[4];    // otherwise: the running bf16 values, two per word
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) accp[j] = 0u;
         // slots in batches of eight: all of a batch's loads are issued before the first is used (the slot chain
         // itself is sequential by contract, the loads need not be)
         for (uint32_t s0 = 0; s0 < top_k; s0 += 8) {
@@ -158,13 +161,15 @@ __global__ void moe_combine_kernel(const uint16_t* __restrict__ y, const uint32_
                     const uint32_t vw[4] = {v[b].x, v[b].y, v[b].z, v[b].w};
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const float lo = bf16_to_f32(vw[j] & 0xffffu), hi = bf16_to_f32(vw[j] >> 16);
+                        const float lo = __uint_as_float(vw[j] << 16), hi = __uint_as_float(vw[j] & 0xffff0000u);
                         if (F32SUM) {
                             acc[2 * j] = __fmaf_rn(lo, w[b], acc[2 * j]);
                             acc[2 * j + 1] = __fmaf_rn(hi, w[b], acc[2 * j + 1]);
                         } else {
-                            acc[2 * j] = round_bf16(__fadd_rn(acc[2 * j], round_bf16(__fmul_rn(lo, w[b]))));
-                            acc[2 * j + 1] = round_bf16(__fadd_rn(acc[2 * j + 1], round_bf16(__fmul_rn(hi, w[b]))));
+                            // bf16(y * w), then bf16(acc + that): both roundings by the paired hardware conversion
+                            const uint32_t t = f32x2_to_bf16x2(__fmul_rn(lo, w[b]), __fmul_rn(hi, w[b]));
+                            accp[j] = f32x2_to_bf16x2(__fadd_rn(__uint_as_float(accp[j] << 16), __uint_as_float(t << 16)),
+                                                      __fadd_rn(__uint_as_float(accp[j] & 0xffff0000u), __uint_as_float(t & 0xffff0000u)));
                         }
                     }
                 }
@@ -172,7 +177,7 @@ __global__ void moe_combine_kernel(const uint16_t* __restrict__ y, const uint32_
         }
         uint32_t o[4];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) o[j] = f32_to_bf16(acc[2 * j]) | (f32_to_bf16(acc[2 * j + 1]) << 16);
+        for (int j = 0; j < 4; ++j) o[j] = F32SUM ? f32x2_to_bf16x2(acc[2 * j], acc[2 * j + 1]) : accp[j];
         *reinterpret_cast<uint4*>(out + (size_t)row * d + c * 8) = make_uint4(o[0], o[1], o[2], o[3]);
     }
 }

@@ -22,17 +22,28 @@ __host__ __device__ __forceinline__ float bf16_to_f32(uint32_t h) {
 #endif
 }
 
-// Round to nearest even on the integer bits, no NaN special case: the engine's
-// rule (reference src/core/bf16.rs:13-23, src/msl/mod.rs:1333-1345).
+// Round to nearest even: the engine's rule is the integer form (bits + 0x7fff + lsb) >> 16 with no NaN special
+// case (reference src/core/bf16.rs:13-23, src/msl/mod.rs:1333-1345). On the device the hardware conversion does the
+// same for every value that is not a NaN (zeros, subnormals, the carry into the exponent and into infinity
+// included; a test walks the bit patterns), in one instruction instead of five; NaN inputs are outside the contract.
 __host__ __device__ __forceinline__ uint32_t f32_to_bf16(float f) {
 #ifdef __CUDA_ARCH__
-    uint32_t bits = __float_as_uint(f);
+    uint16_t r;
+    asm("cvt.rn.bf16.f32 %0, %1;" : "=h"(r) : "f"(f));
+    return r;
 #else
     union { uint32_t u; float f; } v;
     v.f = f;
     uint32_t bits = v.u;
-#endif
     return ((bits + 0x7fffu + ((bits >> 16) & 1u)) >> 16) & 0xffffu;
+#endif
+}
+
+// Two values at once, `lo` into the low half of the result.
+__device__ __forceinline__ uint32_t f32x2_to_bf16x2(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
 }
 
 __device__ __forceinline__ float round_bf16(float f) { return bf16_to_f32(f32_to_bf16(f)); }
