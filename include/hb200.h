@@ -216,6 +216,19 @@ int hb_moe_gather_get(hb_ctx* ctx, uint32_t h, uint32_t top_k, hb_kernel** out);
 /* moe_combine, src/metal/qwen_kernels.rs:2119-2161: acc = bf16(acc + bf16(y*w)) over the slots in route order.
  * f32_sum = 1 is the variant that keeps the sum in f32 and rounds once. Bindings: y ([m][top_k][d]), route, out. */
 int hb_moe_combine_get(hb_ctx* ctx, uint32_t d, uint32_t top_k, uint32_t f32_sum, hb_kernel** out);
+/* ---- the rows around the products (the steps on either side of the GEMMs in the reference's op list) ----
+ * rmsnorm_rows, src/metal/prefill.rs:70-117 (decode twin: norm_into, src/metal/kernels.rs:355-442):
+ * y = bf16((x / sqrt(mean(x^2) + eps)) * (w + plus_one)), the sums in the reference's order. Bindings x, w, y
+ * (y may be x). */
+int hb_rmsnorm_get(hb_ctx* ctx, uint32_t d, float eps, uint32_t plus_one, hb_kernel** out);
+/* argmax_partial + argmax_final, src/metal/kernels.rs:1461-1565, in one launch: index[r] = the first index of the
+ * largest logit of row r (0xffffffff when no logit is greater than -inf). Bindings logits (bf16 [m][n]), index
+ * (u32 [m]; the reference writes state[STATE_ARGMAX] for its single row). */
+int hb_argmax_get(hb_ctx* ctx, uint32_t n, uint32_t rows_max, hb_kernel** out);
+/* moe_out, src/metal/qwen_kernels.rs:2163-2214: g = bf16(sigmoid(bf16(xn . gate))),
+ * x = bf16(x + bf16(experts + bf16(g * shared))), in place. Bindings xn, gate (bf16 [d]), experts, shared, x. */
+int hb_moe_out_get(hb_ctx* ctx, uint32_t d, hb_kernel** out);
+
 /* ---- expert-parallel exchange over peer memory (no reference counterpart: the reference runs on one GPU) ----
  * Experts are partitioned contiguously over `world` ranks, the token rows are each rank's own. A rank sorts its
  * (row, slot) pairs by global expert with hb_moe_sort_get, binding a fourth range `offsets` u32[experts + 1] (first

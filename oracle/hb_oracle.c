@@ -408,6 +408,76 @@ void hbo_moe_combine_f32(const uint16_t* ey, const uint32_t* route, uint16_t* ou
         }
 }
 
+/* -------------------------------------------------- rows around the products */
+
+/* The sum a 256-thread group makes of one f32 per thread (msl/mod.rs:716-756): simd_sum per simdgroup (taken as
+ * the xor butterfly 16,8,4,2,1, as everywhere in this file), thread 0 folds the 8 partials in order. */
+static float group_sum256(const float* lane_vals) {
+    float acc = butterfly_sum32(lane_vals);
+    for (int g = 1; g < 8; ++g) acc = acc + butterfly_sum32(lane_vals + 32 * g);
+    return acc;
+}
+
+void hbo_rmsnorm_rows(const uint16_t* x, const uint16_t* w, uint16_t* y, int rows, int d, float eps, int plus_one) {
+    const float inv_d = 1.0f / (float)d;
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < rows; ++r) {
+        const uint16_t* xr = x + (size_t)r * d;
+        float lanes[256];
+        for (int l = 0; l < 256; ++l) {
+            float a = 0.0f;
+            for (int i = l; i < d; i += 256) {
+                float v = hbo_bf16_to_f32(xr[i]);
+                a = fmaf(v, v, a);
+            }
+            lanes[l] = a;
+        }
+        float ss = group_sum256(lanes);
+        float mm = ss * inv_d;
+        mm = mm + eps;
+        float inv = 1.0f / sqrtf(mm);
+        for (int i = 0; i < d; ++i) {
+            float wf = hbo_bf16_to_f32(w[i]);
+            if (plus_one) wf = wf + 1.0f;
+            float n = hbo_bf16_to_f32(xr[i]) * inv;
+            y[(size_t)r * d + i] = hbo_f32_to_bf16(n * wf);
+        }
+    }
+}
+
+void hbo_argmax_rows(const uint16_t* logits, uint32_t* idx, int rows, int n) {
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < rows; ++r) {
+        float best = -INFINITY;
+        uint32_t best_i = 0xffffffffu;
+        for (int i = 0; i < n; ++i) {
+            float v = hbo_bf16_to_f32(logits[(size_t)r * n + i]);
+            if (v > best) { best = v; best_i = (uint32_t)i; }
+        }
+        idx[r] = best_i;
+    }
+}
+
+void hbo_moe_out(const uint16_t* xn, const uint16_t* gate, const uint16_t* experts, const uint16_t* shared, uint16_t* x, int rows, int d) {
+#pragma omp parallel for schedule(static)
+    for (int r = 0; r < rows; ++r) {
+        const size_t base = (size_t)r * d;
+        float lanes[256];
+        for (int l = 0; l < 256; ++l) {
+            float a = 0.0f;
+            for (int i = l; i < d; i += 256) a = fmaf(hbo_bf16_to_f32(xn[base + i]), hbo_bf16_to_f32(gate[i]), a);
+            lanes[l] = a;
+        }
+        float logit = hbo_round_bf16(group_sum256(lanes));
+        float g = hbo_round_bf16(hbo_sigmoid(logit));
+        for (int i = 0; i < d; ++i) {
+            float s = hbo_round_bf16(g * hbo_bf16_to_f32(shared[base + i]));
+            float o = hbo_round_bf16(hbo_bf16_to_f32(experts[base + i]) + s);
+            x[base + i] = hbo_f32_to_bf16(hbo_bf16_to_f32(x[base + i]) + o);
+        }
+    }
+}
+
 /* -------------------------------------------------------------------- check */
 
 int hbo_check_1_64(const void* ref, const void* got, size_t count, int f32_out, float* err_out, float* scale_out) {

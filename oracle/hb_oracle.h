@@ -90,6 +90,18 @@ void hbo_moe_combine(const uint16_t* ey, const uint32_t* route, uint16_t* out, i
 /* BASELINE config 5 words the combine as an f32 sum: out = bf16(sum_s y_s*w_s), f32 FMA chain in slot order. */
 void hbo_moe_combine_f32(const uint16_t* ey, const uint32_t* route, uint16_t* out, int rows, int d, int top_k);
 
+/* ---- the rows around the matrix products ------------------------------- */
+/* prefill.rs:70-117 (rmsnorm_rows), kernels.rs:355-442 (norm_into, the same sums): per row of d, 256 lanes each an
+ * FMA chain over i = lane, lane + 256, ...; the 32 lanes of a simdgroup summed (xor butterfly 16..1), the 8 partials
+ * folded in order; inv = 1 / sqrt(ss * (1/d) + eps); y = bf16((x * inv) * (w [+ 1])). */
+void hbo_rmsnorm_rows(const uint16_t* x, const uint16_t* w, uint16_t* y, int rows, int d, float eps, int plus_one);
+/* kernels.rs:1461-1565 (argmax_partial + argmax_final): index of the largest bf16 logit of each row, the first
+ * index on a tie; 0xffffffff when no logit is greater than -inf (NaN never wins: the compare is v > best). */
+void hbo_argmax_rows(const uint16_t* logits, uint32_t* idx, int rows, int n);
+/* qwen_kernels.rs:2163-2214 (moe_out): g = bf16(sigmoid(bf16(xn . gate))) with the dot product summed as in
+ * rmsnorm_rows; x = bf16(x + bf16(experts + bf16(g * shared))), in place. */
+void hbo_moe_out(const uint16_t* xn, const uint16_t* gate, const uint16_t* experts, const uint16_t* shared, uint16_t* x, int rows, int d);
+
 /* ---- the selection loop's correctness rule ----------------------------- */
 /* qwen.rs:2497-2543: scale = max(max|ref|,1e-6); err = max|ref-got|;
  * returns 1 (eligible) iff err <= scale/64 (NaN fails). f32_out selects the

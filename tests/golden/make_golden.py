@@ -271,6 +271,77 @@ def moe_combine(ey, route, top_k):
     return out
 
 
+def fma_f32(a, b, c):
+    """fmaf: a * b + c rounded once (exact rational arithmetic)."""
+    from fractions import Fraction
+
+    return round_fraction_f32(Fraction(float(a)) * Fraction(float(b)) + Fraction(float(c)))
+
+
+def group_sum256(lanes):
+    """256 per-thread values: simd_sum of each 32 (xor butterfly), the 8 partials folded in order."""
+    f = np.float32
+    acc = butterfly_sum(lanes[0:32])
+    for gidx in range(1, 8):
+        acc = f(acc + butterfly_sum(lanes[32 * gidx : 32 * gidx + 32]))
+    return acc
+
+
+def rmsnorm_rows(x, w, eps, plus_one):
+    f = np.float32
+    rows, d = x.shape
+    out = np.zeros((rows, d), dtype=np.uint16)
+    for r in range(rows):
+        lanes = []
+        for lane in range(256):
+            a = f(0.0)
+            for i in range(lane, d, 256):
+                v = widen(x[r, i])
+                a = fma_f32(v, v, a)
+            lanes.append(a)
+        ss = group_sum256(lanes)
+        mm = f(f(ss * f(1.0 / d)) + f(eps))
+        inv = f(f(1.0) / np.sqrt(mm, dtype=np.float32))
+        for i in range(d):
+            wf = widen(w[i])
+            if plus_one:
+                wf = f(wf + f(1.0))
+            out[r, i] = rne_bf16(f(f(widen(x[r, i]) * inv) * wf))
+    return out
+
+
+def argmax_rows(logits):
+    out = []
+    for row in logits:
+        best, best_i = np.float32(-np.inf), 0xFFFFFFFF
+        for i, h in enumerate(row):
+            v = widen(h)
+            if v > best:
+                best, best_i = v, i
+        out.append(best_i)
+    return np.array(out, dtype=np.uint32)
+
+
+def moe_out(xn, gate, experts, shared, x):
+    f = np.float32
+    rows, d = x.shape
+    out = np.zeros((rows, d), dtype=np.uint16)
+    for r in range(rows):
+        lanes = []
+        for lane in range(256):
+            a = f(0.0)
+            for i in range(lane, d, 256):
+                a = fma_f32(widen(xn[r, i]), widen(gate[i]), a)
+            lanes.append(a)
+        logit = widen(rne_bf16(group_sum256(lanes)))
+        gsig = widen(rne_bf16(sigmoid_f32(logit)))
+        for i in range(d):
+            sh = widen(rne_bf16(f(gsig * widen(shared[r, i]))))
+            o = widen(rne_bf16(f(widen(experts[r, i]) + sh)))
+            out[r, i] = rne_bf16(f(widen(x[r, i]) + o))
+    return out
+
+
 def main():
     g = {}
     # RNE known answers: (f32 bits, bf16 bits) - ties to even, carries, signed zero, subnormal, infinity.
@@ -332,6 +403,26 @@ def main():
     bad = ref.copy()
     bad[17] += scale / 64.0 * 1.02
     g["check_ref"], g["check_ok"], g["check_bad"] = ref, ok, bad
+    # the rows around the products: RMSNorm (both weight conventions), argmax (ties, -inf, NaN), the MoE block's end
+    rows, d = 3, 768
+    nx = fill_normal(rows * d, 0x9E3779B9, 21, 1.5).reshape(rows, d)
+    nw = fill_normal(d, 0x2545F491, 22, 0.2)
+    g["norm_x"], g["norm_w"] = nx, nw
+    g["norm_out"] = rmsnorm_rows(nx, nw, 1e-6, False)
+    g["norm_out_p1"] = rmsnorm_rows(nx, nw, 1e-6, True)
+    lg = fill_normal(5 * 300, 0xC2B2AE35, 23, 3.0).reshape(5, 300)
+    lg[0, 7] = lg[0, 250] = 0x4120    # 10.0 twice, above everything else in the row: the first index wins
+    lg[1, :] = 0xFF80                 # all -inf: no index
+    lg[2, 3] = 0x7FC0                 # a NaN never wins
+    lg[3, 100], lg[3, 299] = 0x0000, 0x8000  # +0 and -0 compare equal
+    lg[3, [i for i in range(300) if i not in (100, 299)]] = 0xBF80
+    lg[4, 299] = 0x7F80               # +inf in the last place
+    g["argmax_logits"], g["argmax_out"] = lg, argmax_rows(lg)
+    assert list(g["argmax_out"][:2]) == [7, 0xFFFFFFFF] and g["argmax_out"][3] == 100 and g["argmax_out"][4] == 299
+    mo = [fill_normal(rows * d, 0x85EBCA6B, 24 + i, s).reshape(rows, d) for i, s in enumerate((1.0, 0.7, 0.5, 1.0))]
+    mg = fill_normal(d, 0x2545F491, 29, d ** -0.5)
+    g["moe_out_xn"], g["moe_out_experts"], g["moe_out_shared"], g["moe_out_x"], g["moe_out_gate"] = mo[0], mo[1], mo[2], mo[3], mg
+    g["moe_out_out"] = moe_out(mo[0], mg, mo[1], mo[2], mo[3])
     np.savez_compressed(os.path.join(HERE, "golden.npz"), **g)
     print("wrote", os.path.join(HERE, "golden.npz"), "with", len(g), "arrays")
 

@@ -80,6 +80,12 @@ def load(native: bool = False) -> C.CDLL:
     for f in (lib.hbo_moe_combine, lib.hbo_moe_combine_f32):
         f.restype = None
         f.argtypes = [_u16p, _u32p, _u16p, C.c_int, C.c_int, C.c_int]
+    lib.hbo_rmsnorm_rows.restype = None
+    lib.hbo_rmsnorm_rows.argtypes = [_u16p, _u16p, _u16p, C.c_int, C.c_int, C.c_float, C.c_int]
+    lib.hbo_argmax_rows.restype = None
+    lib.hbo_argmax_rows.argtypes = [_u16p, _u32p, C.c_int, C.c_int]
+    lib.hbo_moe_out.restype = None
+    lib.hbo_moe_out.argtypes = [_u16p, _u16p, _u16p, _u16p, _u16p, C.c_int, C.c_int]
     lib.hbo_check_1_64.restype = C.c_int
     lib.hbo_check_1_64.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_float)]
     lib.hbo_fill_normal.restype = None
@@ -211,6 +217,24 @@ class Oracle:
         out = np.zeros((rows, d), dtype=np.uint16)
         fn = self.lib.hbo_moe_combine_f32 if f32 else self.lib.hbo_moe_combine
         fn(np.ascontiguousarray(ey), np.ascontiguousarray(route), out, rows, d, top_k)
+        return out
+
+    def rmsnorm_rows(self, x, w, eps=1e-6, plus_one=False):
+        rows, d = x.shape
+        y = np.zeros((rows, d), dtype=np.uint16)
+        self.lib.hbo_rmsnorm_rows(np.ascontiguousarray(x), np.ascontiguousarray(w), y, rows, d, float(eps), int(plus_one))
+        return y
+
+    def argmax_rows(self, logits):
+        rows, n = logits.shape
+        idx = np.zeros(rows, dtype=np.uint32)
+        self.lib.hbo_argmax_rows(np.ascontiguousarray(logits), idx, rows, n)
+        return idx
+
+    def moe_out(self, xn, gate, experts, shared, x):
+        rows, d = x.shape
+        out = np.ascontiguousarray(x).copy()
+        self.lib.hbo_moe_out(np.ascontiguousarray(xn), np.ascontiguousarray(gate), np.ascontiguousarray(experts), np.ascontiguousarray(shared), out, rows, d)
         return out
 
     def check_1_64(self, ref, got):

@@ -168,6 +168,26 @@ def test_combine_known_answers(oracle):
     assert c.max_abs_err <= c.max_abs_ref / 64
 
 
+def test_rmsnorm_known_answers(oracle):
+    assert np.array_equal(oracle.rmsnorm_rows(G["norm_x"], G["norm_w"], 1e-6, False), G["norm_out"])
+    assert np.array_equal(oracle.rmsnorm_rows(G["norm_x"], G["norm_w"], 1e-6, True), G["norm_out_p1"])
+    # and what it means: rows of unit root-mean-square times the weight, to bf16 accuracy
+    x = (G["norm_x"].astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    w = (G["norm_w"].astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    want = x / np.sqrt((x * x).mean(axis=1, keepdims=True) + 1e-6) * (1.0 + w)
+    got = (G["norm_out_p1"].astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    assert np.abs(got - want).max() <= np.abs(want).max() * 2.0**-7
+
+
+def test_argmax_known_answers(oracle):
+    assert np.array_equal(oracle.argmax_rows(G["argmax_logits"]), G["argmax_out"])
+
+
+def test_moe_out_known_answers(oracle):
+    got = oracle.moe_out(G["moe_out_xn"], G["moe_out_gate"], G["moe_out_experts"], G["moe_out_shared"], G["moe_out_x"])
+    assert np.array_equal(got, G["moe_out_out"])
+
+
 def test_check_rule(oracle):
     ref = G["check_ref"]
     assert oracle.check_1_64(ref, G["check_ok"])[0] is True
