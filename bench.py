@@ -492,6 +492,20 @@ def bench_extra(hb, ctx, sel, torch, dev, wrap, pk, rank, world, barrier, max_ov
         bytes_ = 2.0 * (n2 * k + m * k + m * n2)
         mv2[f"m{m}"] = {"us": sec * 1e6, "gbs": bytes_ / sec / 1e9, "frac_hbm": bytes_ / sec / 1e9 / pk["hbm_gbs"], "form": kern.name}
     out["matvec_4096x151936"] = mv2
+    # the LM head with the greedy pick: projection + argmax as two kernels, and the projection that folds the argmax in
+    idx = torch.zeros(8, device=dev, dtype=torch.int32)
+    form = dict(rows_per_warp=2, split=2)
+    apart = [(ctx.matvec(k, n2, 0, rows_max=1, **form), 1, wrap(w2), wrap(xs), wrap(y2)), (ctx.argmax(n2, rows_max=1), 1, wrap(y2), wrap(idx))]
+    fused = [(ctx.matvec(k, n2, 0, rows_max=1, argmax=1, **form), 1, wrap(w2), wrap(xs), wrap(y2), wrap(idx))]
+    lm = {}
+    for name, ops in (("apart", apart), ("fused", fused)):
+        gr = ctx.record(ops)
+        gr.time(3)
+        barrier()
+        lm[name + "_us"] = max_over_ranks(gr.time(20) / 20) * 1e6
+        gr.free()
+    lm["fused_form"] = fused[0][0].name
+    out["lm_head_argmax_m1"] = lm
     del w2, y2
     # -- MoE block (config 5): 2048 tokens, hidden 2048, 256 experts, top-8, expert intermediate 512
     m, h, mi, E, top_k = 2048, 2048, 512, 256, 8

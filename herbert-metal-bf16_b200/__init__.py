@@ -45,7 +45,7 @@ class GemmDesc(C.Structure):
 
 
 class MatvecDesc(C.Structure):
-    _fields_ = [(n, C.c_uint32) for n in ("k", "n", "out", "rows_max", "rows_per_warp", "split", "persist", "x_stationary", "tensor_core")]
+    _fields_ = [(n, C.c_uint32) for n in ("k", "n", "out", "rows_max", "rows_per_warp", "split", "persist", "x_stationary", "tensor_core", "argmax")]
 
 
 class ExpertIo(C.Structure):
@@ -412,8 +412,8 @@ class Context:
         d = GemmDesc(k, n, out, rows_mode, top_k, experts, bm, tile_n, stages, cta_pair, m_first, rows_max, stream_k, merge_runs)
         return self._get(lib().hb_gemm_get, C.byref(d))
 
-    def matvec(self, k, n, out=OUT_BF16, rows_max=1, rows_per_warp=2, split=1, persist=0, x_stationary=0, tensor_core=0) -> Kernel:
-        d = MatvecDesc(k, n, out, rows_max, rows_per_warp, split, persist, x_stationary, tensor_core)
+    def matvec(self, k, n, out=OUT_BF16, rows_max=1, rows_per_warp=2, split=1, persist=0, x_stationary=0, tensor_core=0, argmax=0) -> Kernel:
+        d = MatvecDesc(k, n, out, rows_max, rows_per_warp, split, persist, x_stationary, tensor_core, argmax)
         return self._get(lib().hb_matvec_get, C.byref(d))
 
     def swiglu_rows(self, n) -> Kernel:

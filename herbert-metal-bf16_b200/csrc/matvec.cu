@@ -23,6 +23,11 @@ struct MatvecParams {
     uint32_t m;        // activation rows in use
     uint32_t split;    // warps sharing one row group
     uint32_t groups;   // row groups in all
+    // fused argmax over the outputs (Out::Bf16 only): see argmax_fold in tc05.cuh
+    unsigned long long* keys;  // [rows][ARGMAX_SLOTS]
+    uint32_t* counter;
+    uint32_t* index;           // [rows]
+    uint32_t store_y;          // 0: the index only
 };
 
 __device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
@@ -34,9 +39,13 @@ __device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
 constexpr int MV_THREADS = 256;
 constexpr int MV_WARPS = MV_THREADS / 32;
 
-template <int M, int R, int OUT>
+template <int M, int R, int OUT, bool ARGMAX = false>
 __global__ void __launch_bounds__(MV_THREADS) matvec_kernel(const MatvecParams p) {
     __shared__ float part[MV_WARPS][R * M];
+    __shared__ unsigned long long best_s[ARGMAX ? MV_WARPS : 1][M];
+    unsigned long long best[M];
+#pragma unroll
+    for (int i = 0; i < M; ++i) best[i] = 0ull;
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t split = p.split;
     const uint32_t slots = MV_WARPS / split;  // row groups a block works on at a time
@@ -137,8 +146,14 @@ __global__ void __launch_bounds__(MV_THREADS) matvec_kernel(const MatvecParams p
                             if ((uint32_t)i < p.m) {
                                 const size_t at = (size_t)i * p.n + col;
                                 if constexpr (OUT == HB_OUT_F32) reinterpret_cast<float*>(p.y)[at] = acc[r][i];
-                                else if constexpr (OUT == HB_OUT_BF16) reinterpret_cast<uint16_t*>(p.y)[at] = (uint16_t)f32_to_bf16(acc[r][i]);
-                                else {
+                                else if constexpr (OUT == HB_OUT_BF16) {
+                                    const uint32_t h = f32_to_bf16(acc[r][i]);
+                                    if (!ARGMAX || p.store_y) reinterpret_cast<uint16_t*>(p.y)[at] = (uint16_t)h;
+                                    if constexpr (ARGMAX) {
+                                        const unsigned long long key = argmax_key(h, col);
+                                        best[i] = key > best[i] ? key : best[i];
+                                    }
+                                } else {
                                     uint16_t* y = reinterpret_cast<uint16_t*>(p.y) + at;
                                     *y = (uint16_t)f32_to_bf16(__fadd_rn(bf16_to_f32(*y), round_bf16(acc[r][i])));
                                 }
@@ -150,6 +165,21 @@ __global__ void __launch_bounds__(MV_THREADS) matvec_kernel(const MatvecParams p
         }
         if (split > 1) __syncthreads();  // `part` is reused by the next group
     }
+    if constexpr (ARGMAX) {
+        // lane 0 of every warp holds the best of the outputs it wrote; fold the block, then the grid
+        if (lane == 0) {
+#pragma unroll
+            for (int i = 0; i < M; ++i) best_s[warp][i] = best[i];
+        }
+        __syncthreads();
+        if (threadIdx.x < M) {
+            unsigned long long b = best_s[0][threadIdx.x];
+            for (int w = 1; w < MV_WARPS; ++w) b = best_s[w][threadIdx.x] > b ? best_s[w][threadIdx.x] : b;
+            best_s[0][threadIdx.x] = b;
+        }
+        __syncthreads();
+        argmax_fold(best_s[0], p.m, p.keys, p.counter, p.index, gridDim.x);
+    }
 }
 
 namespace {
@@ -157,7 +187,8 @@ namespace {
 typedef void (*mv_fn)(const MatvecParams);
 
 template <int M, int R>
-mv_fn mv_out(uint32_t out) {
+mv_fn mv_out(uint32_t out, bool argmax) {
+    if (argmax) return out == HB_OUT_BF16 ? matvec_kernel<M, R, HB_OUT_BF16, true> : nullptr;
     switch (out) {
         case HB_OUT_BF16: return matvec_kernel<M, R, HB_OUT_BF16>;
         case HB_OUT_F32: return matvec_kernel<M, R, HB_OUT_F32>;
@@ -169,21 +200,21 @@ mv_fn mv_out(uint32_t out) {
     return nullptr;
 }
 template <int M>
-mv_fn mv_rows(uint32_t r, uint32_t out) {
+mv_fn mv_rows(uint32_t r, uint32_t out, bool argmax) {
     switch (r) {
-        case 1: return mv_out<M, 1>(out);
-        case 2: return mv_out<M, 2>(out);
-        case 4: return mv_out<M, 4>(out);
-        case 8: return mv_out<M, 8>(out);
+        case 1: return mv_out<M, 1>(out, argmax);
+        case 2: return mv_out<M, 2>(out, argmax);
+        case 4: return mv_out<M, 4>(out, argmax);
+        case 8: return mv_out<M, 8>(out, argmax);
     }
     return nullptr;
 }
-mv_fn mv_pick(uint32_t mcap, uint32_t r, uint32_t out) {
+mv_fn mv_pick(uint32_t mcap, uint32_t r, uint32_t out, bool argmax) {
     switch (mcap) {
-        case 1: return mv_rows<1>(r, out);
-        case 2: return mv_rows<2>(r, out);
-        case 4: return mv_rows<4>(r, out);
-        case 8: return mv_rows<8>(r, out);
+        case 1: return mv_rows<1>(r, out, argmax);
+        case 2: return mv_rows<2>(r, out, argmax);
+        case 4: return mv_rows<4>(r, out, argmax);
+        case 8: return mv_rows<8>(r, out, argmax);
     }
     return nullptr;
 }
@@ -193,9 +224,13 @@ struct Matvec : hb_kernel {
     mv_fn fn = nullptr;
     int blocks_per_sm = 1;
 
+    unsigned long long* keys = nullptr;
+    uint32_t* counter = nullptr;
+
     int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
-        if (na != 3) return fail(ctx, HB_INVALID, name + ": bindings are W, x, y");
+        if (na != (d.argmax ? 4 : 3)) return fail(ctx, HB_INVALID, name + (d.argmax ? ": bindings are W, x, y, index" : ": bindings are W, x, y"));
         if (m == 0 || m > d.rows_max) return fail(ctx, HB_INVALID, name + ": m outside 1.." + std::to_string(d.rows_max));
+        if (d.argmax && !range_ok(a[3], (size_t)m * 4)) return fail(ctx, HB_INVALID, name + ": the index range is too small");
         const uint32_t n_out = d.out == HB_OUT_SWIGLU ? d.n / 2 : d.n;
         const size_t ybytes = (size_t)m * n_out * (d.out == HB_OUT_F32 ? 4 : 2);
         if (!range_ok(a[0], (size_t)d.n * d.k * 2) || !range_ok(a[1], (size_t)m * d.k * 2) || !range_ok(a[2], ybytes))
@@ -211,6 +246,10 @@ struct Matvec : hb_kernel {
         p.k8 = d.k / 8;
         p.m = m;
         p.split = d.split;
+        p.keys = keys;
+        p.counter = counter;
+        p.index = d.argmax ? static_cast<uint32_t*>(a[3].ptr) : nullptr;
+        p.store_y = d.argmax == 2 ? 0u : 1u;
         const uint32_t rows_per_group = d.out == HB_OUT_SWIGLU ? d.rows_per_warp / 2 : d.rows_per_warp;
         p.groups = (n_out + rows_per_group - 1) / rows_per_group;
         const uint32_t slots = MV_WARPS / d.split;
@@ -244,7 +283,9 @@ int make_matvec(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out) {
     if (d->out == HB_OUT_SWIGLU && (r < 2 || d->n % 2 != 0)) return fail(ctx, HB_UNSUPPORTED, "matvec: the SwiGLU form pairs gate and up rows (rows_per_warp >= 2, even n)");
     uint32_t mcap = 1;
     while (mcap < d->rows_max) mcap *= 2;
-    mv_fn fn = mv_pick(mcap, r, d->out);
+    if (d->argmax > 2) return fail(ctx, HB_INVALID, "matvec: argmax is 0, 1 (logits and index) or 2 (index only)");
+    if (d->argmax && d->out != HB_OUT_BF16) return fail(ctx, HB_UNSUPPORTED, "matvec: the fused argmax is over bf16 outputs (Out::Bf16)");
+    mv_fn fn = mv_pick(mcap, r, d->out, d->argmax != 0);
     if (!fn) return fail(ctx, HB_UNSUPPORTED, "matvec: form not built");
     auto k = std::make_unique<Matvec>();
     k->d = *d;
@@ -253,14 +294,22 @@ int make_matvec(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out) {
     k->d.rows_max = mcap;
     k->fn = fn;
     k->kind = 2;
-    k->nargs = 3;
+    k->nargs = d->argmax ? 4 : 3;
     char nm[160];
-    snprintf(nm, sizeof nm, "matvec_%ux%u_%s_m%u_r%u%s%s", d->k, d->n, out_tag(d->out), mcap, r,
-             split > 1 ? (std::string("_s") + std::to_string(split)).c_str() : "", d->persist ? "_p" : "");
+    snprintf(nm, sizeof nm, "matvec_%ux%u_%s_m%u_r%u%s%s%s", d->k, d->n, out_tag(d->out), mcap, r,
+             split > 1 ? (std::string("_s") + std::to_string(split)).c_str() : "", d->persist ? "_p" : "",
+             d->argmax == 1 ? "_argmax" : d->argmax == 2 ? "_argmaxonly" : "");
     k->name = nm;
     if (hb_kernel* have = find(ctx, k->name)) {
         *out = have;
         return HB_OK;
+    }
+    if (d->argmax) {
+        void* pk = nullptr;
+        int st = hb_alloc(ctx, (size_t)mcap * ARGMAX_SLOTS * 8 + 16, &pk);  // zeroed: the keys, then the counter
+        if (st != HB_OK) return st;
+        k->keys = static_cast<unsigned long long*>(pk);
+        k->counter = reinterpret_cast<uint32_t*>(k->keys + (size_t)mcap * ARGMAX_SLOTS);
     }
     int occ = 1;
     cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, reinterpret_cast<const void*>(fn), MV_THREADS, 0);

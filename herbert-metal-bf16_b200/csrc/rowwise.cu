@@ -138,15 +138,6 @@ __global__ void __launch_bounds__(ROW_THREADS) moe_out_kernel(const uint16_t* __
 // winner gives 0xffffffff. -0 and +0 compare equal, as there.
 constexpr uint32_t ARGMAX_CHUNK = 4096;
 
-__device__ __forceinline__ unsigned long long argmax_key(uint32_t h, uint32_t idx) {
-    const float v = bf16_to_f32(h);
-    if (!(v > -INFINITY)) return 0ull;  // NaN, -inf
-    uint32_t b = __float_as_uint(v);
-    if (b == 0x80000000u) b = 0u;  // -0 == +0
-    const uint32_t ord = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
-    return ((unsigned long long)ord << 32) | (unsigned long long)(0xffffffffu - idx);
-}
-
 __global__ void __launch_bounds__(ROW_THREADS) argmax_rows_kernel(const uint16_t* __restrict__ logits, uint32_t* __restrict__ idx, unsigned long long* keys,
                                                                   uint32_t* counter, uint32_t rows, uint32_t n, uint32_t chunks) {
     __shared__ unsigned long long best_s[ROW_THREADS / 32];
@@ -177,7 +168,7 @@ __global__ void __launch_bounds__(ROW_THREADS) argmax_rows_kernel(const uint16_t
         __threadfence();
         for (uint32_t r = threadIdx.x; r < rows; r += ROW_THREADS) {
             const unsigned long long k = atomicExch(&keys[r], 0ull);
-            idx[r] = k ? 0xffffffffu - (uint32_t)(k & 0xffffffffull) : 0xffffffffu;
+            idx[r] = argmax_index_of(k);
         }
         if (threadIdx.x == 0) *counter = 0u;
     }

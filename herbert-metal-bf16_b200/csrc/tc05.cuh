@@ -94,6 +94,53 @@ __device__ __forceinline__ uint32_t swiglu_bf16(float g, float u) {
     return f32_to_bf16(__fmul_rn(gs, u));
 }
 
+// ----------------------------------------------------------------- argmax
+// "The largest logit, the first index on a tie" (reference src/metal/kernels.rs:1461-1565) as the maximum of a
+// 64-bit key: order-preserving value bits above the inverted index. The result does not depend on the order in
+// which candidates meet. A logit is a candidate only if it is greater than -inf (the reference's compare is
+// v > best, starting from -inf): NaN and -inf give key 0, and a row without a candidate gives index 0xffffffff.
+// -0 and +0 compare equal, as there.
+__device__ __forceinline__ unsigned long long argmax_key(uint32_t bf16_bits, uint32_t idx) {
+    const float v = bf16_to_f32(bf16_bits);
+    if (!(v > -INFINITY)) return 0ull;
+    uint32_t b = __float_as_uint(v);
+    if (b == 0x80000000u) b = 0u;
+    const uint32_t ord = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+    return ((unsigned long long)ord << 32) | (unsigned long long)(0xffffffffu - idx);
+}
+__device__ __forceinline__ uint32_t argmax_index_of(unsigned long long key) { return key ? 0xffffffffu - (uint32_t)(key & 0xffffffffull) : 0xffffffffu; }
+
+// Folds one key per row from every block of a grid: block_best[r] (shared memory, r < rows) goes into one of
+// ARGMAX_SLOTS global keys of the row (spread so that the atomics do not queue on one address); the block that
+// arrives last reduces the slots, writes index[r] and clears keys and counter for the next launch. Call with all
+// threads of the block; `arrivals` blocks call it.
+constexpr uint32_t ARGMAX_SLOTS = 64;
+__device__ __forceinline__ void argmax_fold(const unsigned long long* block_best, uint32_t rows, unsigned long long* keys, uint32_t* counter, uint32_t* index,
+                                            uint32_t arrivals) {
+    __shared__ uint32_t last_s;
+    if (threadIdx.x < rows && block_best[threadIdx.x]) atomicMax(&keys[(size_t)threadIdx.x * ARGMAX_SLOTS + blockIdx.x % ARGMAX_SLOTS], block_best[threadIdx.x]);
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) last_s = atomicAdd(counter, 1u) == arrivals - 1 ? 1u : 0u;
+    __syncthreads();
+    if (!last_s) return;
+    __threadfence();
+    for (uint32_t r = threadIdx.x / 32; r < rows; r += blockDim.x / 32) {  // a warp per row
+        unsigned long long b = 0ull;
+        for (uint32_t sidx = threadIdx.x & 31; sidx < ARGMAX_SLOTS; sidx += 32) {
+            const unsigned long long k = atomicExch(&keys[(size_t)r * ARGMAX_SLOTS + sidx], 0ull);
+            b = k > b ? k : b;
+        }
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) {
+            const unsigned long long o = __shfl_xor_sync(0xffffffffu, b, off);
+            b = o > b ? o : b;
+        }
+        if ((threadIdx.x & 31) == 0) index[r] = argmax_index_of(b);
+    }
+    if (threadIdx.x == 0) *counter = 0u;
+}
+
 // ----------------------------------------------------------------- status
 
 // Words of the per-context device status buffer that kernels write on a failed

@@ -197,6 +197,10 @@ typedef struct {
                                range is the tensor core's, as in the prefill GEMM. `split` (1, 2 or 4) is then the
                                number of neighbouring K blocks one pipeline stage holds (longer runs per weight row
                                in DRAM); the other form fields are ignored. */
+    uint32_t argmax;        /* Out::Bf16 only: 1 = also the index of the largest output of every row, the first on a tie
+                               (argmax_partial + argmax_final, src/metal/kernels.rs:1461-1565, folded into the
+                               projection: no pass over the logits, no launch of its own); 2 = the index only, y is
+                               not written. A fourth binding, index u32[m], follows y. */
 } hb_matvec_desc;
 int hb_matvec_get(hb_ctx* ctx, const hb_matvec_desc* desc, hb_kernel** out);
 

@@ -136,3 +136,37 @@ def test_config2_shapes_tensor_core(ctx, oracle, m):
     for ks in (1, 2):
         kern, want, got = run(ctx, oracle, m, k, n, OUT_BF16, tensor_core=ks, split=2)
         within_contract(oracle, want, got, f"{kern.name} m={m}")
+
+
+@pytest.mark.parametrize("m", [1, 3, 8])
+def test_fused_argmax(ctx, oracle, hb200, m):
+    # the projection also reports, per activation row, the first index of its largest bf16 output
+    for k, n, form in ((1024, 3000, dict(rows_per_warp=2, split=2)), (4096, 12288, dict(rows_per_warp=4)), (512, 70, dict(rows_per_warp=1, persist=1)),
+                       (4096, 151936, dict(rows_per_warp=2, split=2))):
+        x = oracle.normal((m, k), 1, n, 1.0)
+        w = oracle.normal((n, k), 2, n, k**-0.5)
+        w[n // 3] = w[2 * n // 3]  # two equal rows of W: equal outputs, so ties between far-apart indices exist
+        d_x, d_w, d_y, d_i = ctx.to_device(x), ctx.to_device(w), ctx.alloc(m * n * 2), ctx.alloc(m * 4)
+        kern = ctx.matvec(k, n, OUT_BF16, rows_max=m, argmax=1, **form)
+        assert kern.name.endswith("_argmax")
+        plain = ctx.matvec(k, n, OUT_BF16, rows_max=m, **form)
+        d_y2 = ctx.alloc(m * n * 2)
+        plain(m, d_w, d_x, d_y2)
+        for _ in range(2):  # twice: the kernel clears its own scratch
+            ctx.memset(d_i, 0xEE)
+            kern(m, d_w, d_x, d_y, d_i)
+            ctx.sync()
+            logits = d_y.download(np.uint16, (m, n))
+            assert np.array_equal(logits, d_y2.download(np.uint16, (m, n)))  # the same logits as without the fusion
+            assert np.array_equal(d_i.download(np.uint32, (m,)), oracle.argmax_rows(logits))
+        # index only: y stays untouched
+        only = ctx.matvec(k, n, OUT_BF16, rows_max=m, argmax=2, **form)
+        ctx.memset(d_y, 0)
+        ctx.memset(d_i, 0xEE)
+        only(m, d_w, d_x, d_y, d_i)
+        ctx.sync()
+        assert not d_y.download(np.uint16, (m, n)).any()
+        assert np.array_equal(d_i.download(np.uint32, (m,)), oracle.argmax_rows(logits))
+    with pytest.raises(hb200.HbError) as e:
+        ctx.matvec(1024, 512, OUT_RESIDUAL, rows_max=1, argmax=1)
+    assert e.value.status == hb200.UNSUPPORTED
