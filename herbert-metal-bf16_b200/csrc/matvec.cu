@@ -292,12 +292,13 @@ int make_matvec(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out) {
     k->d.rows_per_warp = r;
     k->d.split = split;
     k->d.rows_max = mcap;
+    if (d->argmax) k->d.persist = 1;  // the fold at the end of a block costs a round trip: few long-lived blocks, not thousands
     k->fn = fn;
     k->kind = 2;
     k->nargs = d->argmax ? 4 : 3;
     char nm[160];
     snprintf(nm, sizeof nm, "matvec_%ux%u_%s_m%u_r%u%s%s%s", d->k, d->n, out_tag(d->out), mcap, r,
-             split > 1 ? (std::string("_s") + std::to_string(split)).c_str() : "", d->persist ? "_p" : "",
+             split > 1 ? (std::string("_s") + std::to_string(split)).c_str() : "", k->d.persist ? "_p" : "",
              d->argmax == 1 ? "_argmax" : d->argmax == 2 ? "_argmaxonly" : "");
     k->name = nm;
     if (hb_kernel* have = find(ctx, k->name)) {

@@ -148,7 +148,7 @@ def test_fused_argmax(ctx, oracle, hb200, m):
         w[n // 3] = w[2 * n // 3]  # two equal rows of W: equal outputs, so ties between far-apart indices exist
         d_x, d_w, d_y, d_i = ctx.to_device(x), ctx.to_device(w), ctx.alloc(m * n * 2), ctx.alloc(m * 4)
         kern = ctx.matvec(k, n, OUT_BF16, rows_max=m, argmax=1, **form)
-        assert kern.name.endswith("_argmax")
+        assert kern.name.endswith("_p_argmax")  # always the persistent grid
         plain = ctx.matvec(k, n, OUT_BF16, rows_max=m, **form)
         d_y2 = ctx.alloc(m * n * 2)
         plain(m, d_w, d_x, d_y2)
