@@ -343,6 +343,29 @@ def main():
     extra = {"selection_seconds": t_sel, "picks": picks}
     if not args.no_extra:
         try:
+            # the same layer set at the other block sizes of config 3 (64 and 512 rows), kernels picked per size
+            small = {}
+            for rows_s in (64, 512):
+                xs_ = x[:rows_s].contiguous()
+                qkv_, res_, hm_, gu_ = qkv[:rows_s], resid[:rows_s].clone(), hmid[:rows_s], gu_scratch[:rows_s]
+                ks = [sel.gemm(HIDDEN, 6144, 0, wrap(weights[0]), wrap(xs_), wrap(qkv_), rows_s), sel.gemm(HIDDEN, HIDDEN, 2, wrap(weights[1]), wrap(xs_), wrap(res_), rows_s)]
+                kg = sel.gate_up(HIDDEN, INTER, wrap(weights[2]), wrap(xs_), wrap(gu_), wrap(hm_), rows_s)
+                kd = sel.gemm(INTER, HIDDEN, 2, wrap(weights[3]), wrap(hm_), wrap(res_), rows_s)
+                ops_s = [(ks[0], rows_s, wrap(weights[0]), wrap(xs_), wrap(qkv_)), (ks[1], rows_s, wrap(weights[1]), wrap(xs_), wrap(res_))]
+                ops_s += [(kg[0], rows_s, wrap(weights[2]), wrap(xs_), wrap(gu_)), (kg[1], rows_s, wrap(gu_), wrap(hm_))] if len(kg) == 2 else [(kg[0], rows_s, wrap(weights[2]), wrap(xs_), wrap(hm_))]
+                ops_s += [(kd, rows_s, wrap(weights[3]), wrap(hm_), wrap(res_))]
+                ctx.time(ops_s, 5)
+                barrier()
+                sec_s = max_over_ranks(ctx.time(ops_s, 50) / 50)
+                flop_s = STEP_FLOP * rows_s / ROWS
+                wbytes_s = sum(2.0 * n * k for _, k, n, _ in LAYER)
+                small[f"M{rows_s}"] = {"us": sec_s * 1e6, "tflops": flop_s / sec_s / 1e12, "weight_gbs": wbytes_s / sec_s / 1e9,
+                                       "frac_hbm_weights": wbytes_s / sec_s / 1e9 / pk["hbm_gbs"], "frac_bf16_peak": flop_s / sec_s / 1e12 / pk["bf16_tflops"],
+                                       "picks": [o[0].name for o in ops_s]}
+            extra["layer_set_small_blocks"] = small
+        except Exception as e:
+            extra["small_error"] = repr(e)
+        try:
             extra.update(bench_extra(hb, ctx, sel, torch, dev, wrap, pk, rank, world, barrier, max_over_ranks))
         except Exception as e:  # the headline stands on its own
             extra["error"] = repr(e)
@@ -602,6 +625,9 @@ def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks)
                 y2 = y.clone()
                 D.tp_ffn(be, x, wgu_l, wd_l, y2)
                 same = bool(torch.equal(y2, got))
+                # (beyond two ranks NCCL sums the partials in another order than rank 0 + rank 1 + ...: not the same bits)
+                diff = float((y2.float() - got.float()).abs().max())
+                scale = float(got.float().abs().max())
                 sec_nccl = timed(lambda: D.tp_ffn(be, x, wgu_l, wd_l, y2), 3, 10)
                 barrier()
                 tp.close()
@@ -610,7 +636,8 @@ def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks)
                                            "nvlink_bytes_per_gpu": (m * h * 4 + m * h * 2) * (world - 1) // world // 1 if world > 1 else 0, "scaling": "strong",
                                            "exchange": "tp_reduce kernel: peer loads of the f32 partials, peer stores of bf16 Y, 2 barrier kernels (no NCCL call in the step)",
                                            "with_nccl_barriers_us": sec_ns * 1e6,
-                                           "nccl_all_reduce_form_us": sec_nccl * 1e6, "equals_nccl_form_bitwise": same}
+                                           "nccl_all_reduce_form_us": sec_nccl * 1e6, "equals_nccl_form_bitwise": same,
+                                           "max_abs_diff_vs_nccl_form": diff, "max_abs_value": scale}
                 del wgu_l, wd_l
             # -- config 5: 2048 tokens, hidden 2048, 256 experts, top-8, expert intermediate 512
             m, h, mi, E, top_k, bm = 2048, 2048, 512, 256, 8, 64

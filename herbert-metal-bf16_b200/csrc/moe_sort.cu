@@ -25,10 +25,11 @@ struct SortParams {
     uint32_t* list;
     uint32_t* tiles;
     uint32_t* offsets;  // optional [experts + 1]: first sorted row of every expert, then the number of pairs
-    uint32_t rows, experts, top_k, bm;
+    uint32_t rows, rows_cap, experts, top_k, bm;
     uint32_t staged;    // the experts of all pairs fit in shared memory as 16-bit values
     uint32_t use_masks; // the per-expert row masks fit in shared memory
     uint32_t words;     // stride of an expert's mask in words: ceil(rows_max / 32) made odd
+    uint32_t list_staged;  // the sorted list fits in shared memory as 16-bit pair numbers
 };
 
 __global__ void __launch_bounds__(SORT_THREADS) moe_sort_kernel(const SortParams p) {
@@ -36,8 +37,8 @@ __global__ void __launch_bounds__(SORT_THREADS) moe_sort_kernel(const SortParams
     const uint32_t experts = p.experts, top_k = p.top_k, bm = p.bm;
     uint32_t* off = sm;                   // [experts] first sorted row of expert e
     uint32_t* tot = off + experts;        // [experts] pairs of expert e
-    uint32_t* scan = tot + experts;       // [2][experts] scratch
-    uint32_t* flag = scan + 2 * experts;  // [4]
+    uint32_t* scan = tot + experts;       // [2][max(experts, 32)] scratch: the warps' totals of the two scans
+    uint32_t* flag = scan + 2 * max(experts, 32u);  // [4]
     uint32_t* big = flag + 4;             // masks + prefixes, or the per-warp counters
     uint32_t* mask = big;                                     // [experts][words]
     uint32_t* pre = big + (p.use_masks ? experts * p.words : 0);  // [experts][words]
@@ -45,14 +46,38 @@ __global__ void __launch_bounds__(SORT_THREADS) moe_sort_kernel(const SortParams
     const size_t big_words = p.use_masks ? 2 * (size_t)experts * p.words : (size_t)SORT_WARPS * experts;
     const size_t counter_words = (size_t)SORT_WARPS * experts;
     uint16_t* ex16 = reinterpret_cast<uint16_t*>(big + (big_words > counter_words ? big_words : counter_words));
+    uint16_t* list16 = ex16 + ((size_t)p.rows_cap * top_k + 7) / 8 * 8;  // after the staged experts
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t pairs = p.rows * top_k;
     const uint32_t words = (p.rows + 31) / 32;  // words in use this launch (<= p.words)
 
     auto expert_global = [&](uint32_t i) { return p.route[(size_t)(i / top_k) * 2 * top_k + (i % top_k)]; };
     if (tid == 0) flag[0] = 0;
-    if (p.staged)
-        for (uint32_t i = tid; i < pairs; i += SORT_THREADS) ex16[i] = (uint16_t)expert_global(i);
+    if (p.staged) {
+        if (top_k % 4 == 0 && (reinterpret_cast<uintptr_t>(p.route) & 15u) == 0) {
+            // a row's experts are top_k consecutive words: 16-byte loads, and all of a thread's loads issued before
+            // the first is used (one memory round trip for the whole table instead of one per pair)
+            const uint32_t q4 = top_k / 4, vecs = p.rows * q4;
+            for (uint32_t v0 = tid; v0 < vecs; v0 += 4 * SORT_THREADS) {
+                uint4 e[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const uint32_t v = v0 + u * SORT_THREADS;
+                    if (v < vecs) e[u] = reinterpret_cast<const uint4*>(p.route + (size_t)(v / q4) * 2 * top_k)[v % q4];
+                }
+#pragma unroll
+                for (int u = 0; u < 4; ++u) {
+                    const uint32_t v = v0 + u * SORT_THREADS;
+                    if (v < vecs) {
+                        const uint32_t at = (v / q4) * top_k + (v % q4) * 4;
+                        ex16[at] = (uint16_t)e[u].x; ex16[at + 1] = (uint16_t)e[u].y; ex16[at + 2] = (uint16_t)e[u].z; ex16[at + 3] = (uint16_t)e[u].w;
+                    }
+                }
+            }
+        } else {
+            for (uint32_t i = tid; i < pairs; i += SORT_THREADS) ex16[i] = (uint16_t)expert_global(i);
+        }
+    }
     auto expert_of = [&](uint32_t i) -> uint32_t { return p.staged ? (uint32_t)ex16[i] : expert_global(i); };
 
     bool fast = p.use_masks != 0;
@@ -71,22 +96,31 @@ __global__ void __launch_bounds__(SORT_THREADS) moe_sort_kernel(const SortParams
 
     uint32_t total_e = 0;
     if (fast) {
-        // per expert: exclusive prefix of the popcounts of its mask words (a warp per expert, lanes over words)
-        for (uint32_t e = warp; e < experts; e += SORT_WARPS) {
-            uint32_t carry = 0;
-            for (uint32_t w0 = 0; w0 < words; w0 += 32) {
-                const uint32_t w = w0 + lane;
-                const uint32_t c = w < words ? __popc(mask[e * p.words + w]) : 0;
-                uint32_t incl = c;
-#pragma unroll
-                for (int d = 1; d < 32; d <<= 1) {
-                    const uint32_t v = __shfl_up_sync(0xffffffffu, incl, d);
-                    if (lane >= (uint32_t)d) incl += v;
+        // per expert: exclusive prefix of the popcounts of its mask words. `tpe` neighbouring threads share an expert,
+        // each walks a contiguous run of the words, then the runs' totals are passed along the group by shuffles.
+        const uint32_t tpe = experts <= 256 ? 4u : experts <= 512 ? 2u : 1u;
+        const uint32_t seg = (words + tpe - 1) / tpe;
+        {
+            const uint32_t e = tid / tpe, part = tid % tpe;
+            const uint32_t w0 = min(words, part * seg), w1 = min(words, w0 + seg);
+            uint32_t run = 0;
+            if (e < experts)
+                for (uint32_t w = w0; w < w1; ++w) {
+                    pre[e * p.words + w] = run;
+                    run += __popc(mask[e * p.words + w]);
                 }
-                if (w < words) pre[e * p.words + w] = carry + incl - c;
-                carry += __shfl_sync(0xffffffffu, incl, 31);
+            // exclusive scan of `run` over the tpe lanes of the group (groups are aligned inside a warp)
+            uint32_t incl = run;
+            for (uint32_t d = 1; d < tpe; d <<= 1) {
+                const uint32_t v = __shfl_up_sync(0xffffffffu, incl, d);
+                if (part >= d) incl += v;
             }
-            if (lane == 0) tot[e] = carry;
+            const uint32_t base = incl - run;
+            if (e < experts) {
+                if (base)
+                    for (uint32_t w = w0; w < w1; ++w) pre[e * p.words + w] += base;
+                if (part == tpe - 1) tot[e] = incl;
+            }
         }
         __syncthreads();
         if (tid < experts) total_e = tot[tid];
@@ -116,18 +150,29 @@ __global__ void __launch_bounds__(SORT_THREADS) moe_sort_kernel(const SortParams
 
     // exclusive scans over the experts of (pairs) and (tiles per expert); the tile table
     const uint32_t ntile_e = (total_e + bm - 1) / bm;
+    // inclusive scans of both over the experts: inside each warp by shuffles, the warps' totals by warp 0
     uint32_t a = total_e, t = ntile_e;
     uint32_t* sa = scan;
-    uint32_t* st = scan + experts;
-    if (tid < experts) { sa[tid] = a; st[tid] = t; }
-    __syncthreads();
-    for (uint32_t d = 1; d < experts; d <<= 1) {
-        uint32_t va = 0, vt = 0;
-        if (tid < experts && tid >= d) { va = sa[tid - d]; vt = st[tid - d]; }
-        __syncthreads();
-        if (tid < experts) { a += va; t += vt; sa[tid] = a; st[tid] = t; }
-        __syncthreads();
+    uint32_t* st = scan + max(experts, 32u);
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t va = __shfl_up_sync(0xffffffffu, a, d), vt = __shfl_up_sync(0xffffffffu, t, d);
+        if (lane >= (uint32_t)d) { a += va; t += vt; }
     }
+    if (lane == 31) { sa[warp] = a; st[warp] = t; }
+    __syncthreads();
+    if (warp == 0) {
+        uint32_t wa = sa[lane], wt = st[lane];
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const uint32_t va = __shfl_up_sync(0xffffffffu, wa, d), vt = __shfl_up_sync(0xffffffffu, wt, d);
+            if (lane >= (uint32_t)d) { wa += va; wt += vt; }
+        }
+        sa[lane] = wa;
+        st[lane] = wt;
+    }
+    __syncthreads();
+    if (warp > 0) { a += sa[warp - 1]; t += st[warp - 1]; }
     if (tid < experts) {
         const uint32_t start = a - total_e, tfirst = t - ntile_e;
         off[tid] = start;
@@ -144,7 +189,24 @@ __global__ void __launch_bounds__(SORT_THREADS) moe_sort_kernel(const SortParams
     }
     __syncthreads();
 
-    if (fast) {
+    if (fast && p.list_staged) {
+        // the sorted list is put together in shared memory (16384 scattered 4-byte stores from one SM cost more
+        // than everything else in this kernel) and written out in order
+        for (uint32_t i = tid; i < pairs; i += SORT_THREADS) {
+            const uint32_t e = expert_of(i), r = i / top_k;
+            const uint32_t at = e * p.words + (r >> 5);
+            list16[off[e] + pre[at] + __popc(mask[at] & ((1u << (r & 31)) - 1u))] = (uint16_t)i;
+        }
+        __syncthreads();
+        if ((pairs & 1u) == 0 && (reinterpret_cast<uintptr_t>(p.list) & 7u) == 0) {
+            for (uint32_t j = tid; j < pairs / 2; j += SORT_THREADS) {
+                const uint32_t two = reinterpret_cast<const uint32_t*>(list16)[j];
+                reinterpret_cast<uint2*>(p.list)[j] = make_uint2(two & 0xffffu, two >> 16);
+            }
+        } else {
+            for (uint32_t j = tid; j < pairs; j += SORT_THREADS) p.list[j] = list16[j];
+        }
+    } else if (fast) {
         for (uint32_t i = tid; i < pairs; i += SORT_THREADS) {
             const uint32_t e = expert_of(i), r = i / top_k;
             const uint32_t at = e * p.words + (r >> 5);
@@ -174,7 +236,7 @@ __global__ void __launch_bounds__(SORT_THREADS) moe_sort_kernel(const SortParams
 namespace {
 
 struct MoeSort : hb_kernel {
-    uint32_t experts = 0, top_k = 0, rows_max = 0, bm = 0, staged = 0, use_masks = 0, words = 0;
+    uint32_t experts = 0, top_k = 0, rows_max = 0, bm = 0, staged = 0, use_masks = 0, words = 0, list_staged = 0;
     size_t smem = 0;
     int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
         if (na != 3 && na != 4) return fail(ctx, HB_INVALID, name + ": bindings are route, list, tiles[, offsets]");
@@ -189,6 +251,8 @@ struct MoeSort : hb_kernel {
         p.tiles = static_cast<uint32_t*>(a[2].ptr);
         p.offsets = na == 4 ? static_cast<uint32_t*>(a[3].ptr) : nullptr;
         p.rows = m;
+        p.rows_cap = rows_max;
+        p.list_staged = list_staged;
         p.experts = experts;
         p.top_k = top_k;
         p.bm = bm;
@@ -220,8 +284,8 @@ int make_moe_sort(hb_ctx* ctx, uint32_t experts, uint32_t top_k, uint32_t rows_m
         *out = have;
         return HB_OK;
     }
-    const size_t limit = 200 * 1024;
-    const size_t fixed = (4 * (size_t)experts + 4) * 4;
+    const size_t limit = 220 * 1024;
+    const size_t fixed = (2 * (size_t)experts + 2 * std::max<size_t>(experts, 32) + 4) * 4;
     const size_t counters = (size_t)SORT_WARPS * experts * 4;
     k->words = ((rows_max + 31) / 32) | 1u;  // odd stride: the same word of different experts falls in different banks
     const size_t masks = 2 * (size_t)experts * k->words * 4;
@@ -235,6 +299,10 @@ int make_moe_sort(hb_ctx* ctx, uint32_t experts, uint32_t top_k, uint32_t rows_m
     if (k->smem + stage <= limit) {
         k->staged = 1;
         k->smem += stage;
+        if (k->use_masks && (size_t)rows_max * top_k <= 65536 && k->smem + stage <= limit) {
+            k->list_staged = 1;
+            k->smem += stage;
+        }
     }
     cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(moe_sort_kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin - 1024);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(moe_sort)");

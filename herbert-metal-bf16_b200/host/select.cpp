@@ -373,6 +373,27 @@ int hb_select_gemm(hb_selector* s, uint32_t k, uint32_t n, uint32_t out, hb_rang
             cands.push_back(std::move(c));
             eligible.push_back(1);
         }
+        // blocks of at most 64 rows are weight streams, not GEMMs (64 FLOP per weight byte): the decode kernel that
+        // feeds the weights to the tensor cores as the wide operand takes the same bindings
+        if (m <= 64) {
+            struct SkForm { const char* name; uint32_t tc, kps; };
+            // (K blocks per stage: four while the activation tile is small, two when it is 64 rows: at least three stages must fit)
+            for (const SkForm& f : {SkForm{"stream", 1, m <= 16 ? 4u : 2u}, SkForm{"streamb", 2, m <= 16 ? 2u : 1u}}) {
+                hb_matvec_desc d{};
+                d.k = k;
+                d.n = n;
+                d.out = out;
+                d.rows_max = m;
+                d.tensor_core = f.tc;
+                d.split = f.kps;
+                if (hb_matvec_get(ctx, &d, &kern) != HB_OK) continue;
+                Cand c;
+                c.name = f.name;
+                add_op(c, kern, {w, x, y});
+                cands.push_back(std::move(c));
+                eligible.push_back(1);
+            }
+        }
         if (s->inject_wrong) {
             auto wrong = std::make_unique<WrongKernel>();
             wrong->inner = const_cast<hb_kernel*>(cands[0].kernels[0]);
@@ -457,6 +478,24 @@ int hb_select_gate_up(hb_selector* s, uint32_t k, uint32_t inter, hb_range w, hb
                     add_op(c, f, {w, x, h});
                     cands.push_back(std::move(c));
                     eligible.push_back(1);
+                }
+                if (m <= 64) {  // the weight-stream form with the SwiGLU epilogue (two weight tiles per step: two K blocks per stage)
+                    for (uint32_t tc : {1u, 2u}) {
+                        hb_matvec_desc d{};
+                        d.k = k;
+                        d.n = 2 * inter;
+                        d.out = HB_OUT_SWIGLU;
+                        d.rows_max = m;
+                        d.tensor_core = tc;
+                        d.split = 2;
+                        hb_kernel* f = nullptr;
+                        if (hb_matvec_get(ctx, &d, &f) != HB_OK) continue;
+                        Cand c;
+                        c.name = tc == 1 ? "fusedstream" : "fusedstreamb";
+                        add_op(c, f, {w, x, h});
+                        cands.push_back(std::move(c));
+                        eligible.push_back(1);
+                    }
                 }
                 const std::string what = "gate_up " + key;
                 if ((r = check_candidates(s, what, cands, eligible, h, (size_t)inter * 2, false, m)) != HB_OK) return r;

@@ -210,3 +210,31 @@ def test_alloc_limit_reports_oom(hb200):
         assert not z.download(np.uint8, (4096,)).any()  # zero-initialised (gpu.rs:92)
     finally:
         c.close()
+
+
+def test_small_blocks_get_the_weight_stream_candidates(ctx, hb200, oracle):
+    # a block of 64 rows or fewer: the tensor-core weight stream is among the candidates, checked like the others
+    m, k, n = 48, 1024, 2048
+    for out in (OUT_BF16, OUT_RESIDUAL):
+        (x, w, y0), d_w, d_x, d_y = bufs(ctx, oracle, m, k, n, out)
+        sel = hb200.Selector(ctx, hb200.Tune("prefill.block=2048"))
+        kern = sel.gemm(k, n, out, d_w, d_x, d_y, m)
+        line = [l for l in sel.log().splitlines() if l.startswith("[autotune] gemm 1024x2048") and " -> " in l][0]
+        assert re.search(r"stream \d+\.\d{3} ms, streamb \d+\.\d{3} ms", line) and "wrong" not in sel.log()
+        d_y.upload(y0 if out == OUT_RESIDUAL else np.zeros_like(y0))
+        kern(m, d_w, d_x, d_y)
+        ctx.sync()
+        within_contract(oracle, oracle.gemm_f64(x, w, out, y0), d_y.download(np.uint16, (m, n)), kern.name)
+        sel.close()
+    inter = 512
+    x, wgu = oracle.normal((m, k), 1, 1, 1.0), oracle.normal((2 * inter, k), 2, 2, k**-0.5)
+    d_w, d_x, d_gu, d_h = ctx.to_device(wgu), ctx.to_device(x), ctx.alloc(m * 2 * inter * 2), ctx.alloc(m * inter * 2)
+    sel = hb200.Selector(ctx, hb200.Tune(""))
+    ks = sel.gate_up(k, inter, d_w, d_x, d_gu, d_h, m)
+    assert "fusedstream " in sel.log() and "fusedstreamb " in sel.log()
+    for kk in ks[:-1]:
+        kk(m, d_w, d_x, d_gu)
+    (ks[-1](m, d_w, d_x, d_h) if len(ks) == 1 else ks[-1](m, d_gu, d_h))
+    ctx.sync()
+    within_contract(oracle, oracle.gemm_f64(x, wgu, OUT_SWIGLU), d_h.download(np.uint16, (m, inter)), "picked gate/up at 48 rows")
+    sel.close()
