@@ -18,6 +18,11 @@ struct GemmParams {
     uint32_t m_first;
     uint32_t vec_ok;      // Y rows allow 16-byte accesses
     uint32_t* status;
+    // Out::F32 only: Y cut into blocks of shard_rows rows, block b stored at address y_shards[b] (a device array);
+    // the blocks may be other GPUs' memory (a row-parallel projection pushes each block of its partial product
+    // to the rank that will sum it). Null: Y is one array at y.
+    const uint64_t* y_shards;
+    uint32_t shard_rows;
 };
 
 constexpr int BM = 128;
@@ -42,7 +47,8 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t row, u
     if (row >= p.m || col0 >= p.n_out) return;
     const uint32_t ncols = min(32u, p.n_out - col0);
     if constexpr (OUT == HB_OUT_F32) {
-        float* y = reinterpret_cast<float*>(p.y) + (size_t)row * p.n_out + col0;
+        float* y = p.y_shards ? reinterpret_cast<float*>(p.y_shards[row / p.shard_rows]) + (size_t)(row % p.shard_rows) * p.n_out + col0
+                              : reinterpret_cast<float*>(p.y) + (size_t)row * p.n_out + col0;
         if (ncols == 32 && p.vec_ok) {
 #pragma unroll
             for (int i = 0; i < 8; ++i)

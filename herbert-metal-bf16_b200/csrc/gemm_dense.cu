@@ -255,6 +255,7 @@ int make_gemm(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
     if (d->out > HB_OUT_SWIGLU) return fail(ctx, HB_INVALID, "gemm: unknown output mode");
     if (d->out == HB_OUT_SWIGLU && d->n % 2 != 0) return fail(ctx, HB_INVALID, "gemm: the SwiGLU form needs an even n ([gate | up])");
     if (d->cta_pair) return make_gemm_pair(ctx, d, out);
+    if (d->y_shards > 1) return fail(ctx, HB_UNSUPPORTED, "gemm: a Y in row blocks is built for the CTA-pair form only");
     if (d->stream_k) return make_gemm_streamk(ctx, d, out);
     const uint32_t bn = d->tile_n ? d->tile_n : 256;
     gemm_fn fn = nullptr;

@@ -249,7 +249,7 @@ struct PairGemm : hb_kernel {
         if (na != 3) return fail(ctx, HB_INVALID, name + ": bindings are W, X, Y");
         if (m == 0 || m > d.rows_max) return fail(ctx, HB_INVALID, name + ": m = " + std::to_string(m) + " outside 1.." + std::to_string(d.rows_max));
         const uint32_t n_out = d.out == HB_OUT_SWIGLU ? d.n / 2 : d.n;
-        const size_t ybytes = (size_t)m * n_out * (d.out == HB_OUT_F32 ? 4 : 2);
+        const size_t ybytes = d.y_shards > 1 ? (size_t)d.y_shards * 8 : (size_t)m * n_out * (d.out == HB_OUT_F32 ? 4 : 2);
         if (!range_ok(a[0], (size_t)d.n * d.k * 2) || !range_ok(a[1], (size_t)m * d.k * 2) || !range_ok(a[2], ybytes))
             return fail(ctx, HB_INVALID, name + ": a bound range is too small for " + std::to_string(m) + " rows");
         if (a[0].ptr != last_w || a[1].ptr != last_x || m != last_m) {
@@ -276,6 +276,12 @@ struct PairGemm : hb_kernel {
         const uint32_t elem = d.out == HB_OUT_F32 ? 4 : 2;
         p.vec_ok = ((reinterpret_cast<uintptr_t>(a[2].ptr) & 15u) == 0 && ((size_t)n_out * elem) % 16 == 0) ? 1u : 0u;
         p.status = ctx->status_dev;
+        if (d.y_shards > 1) {  // Y is a table of block addresses (every block 16-byte aligned by contract)
+            p.y_shards = static_cast<const uint64_t*>(a[2].ptr);
+            p.shard_rows = (m + d.y_shards - 1) / d.y_shards;
+            p.y = nullptr;
+            p.vec_ok = ((size_t)n_out * elem) % 16 == 0 ? 1u : 0u;
+        }
         const uint32_t pairs = std::min<uint32_t>(p.num_tiles, (uint32_t)ctx->sm_count / 2);
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(2 * pairs);
@@ -300,6 +306,8 @@ struct PairGemm : hb_kernel {
 int make_gemm_pair(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
     *out = nullptr;
     if (d->tile_n != 0 && d->tile_n != 256) return fail(ctx, HB_UNSUPPORTED, "gemm: the CTA-pair form has 256 x 256 tiles only");
+    if (d->y_shards > 1 && d->out != HB_OUT_F32) return fail(ctx, HB_UNSUPPORTED, "gemm: a Y in row blocks is for f32 partial products (Out::F32)");
+    if (d->y_shards > 16) return fail(ctx, HB_UNSUPPORTED, "gemm: at most 16 row blocks of Y");
     pair_fn fn = pair_pick(d->out);
     const size_t budget = std::min<size_t>(ctx->smem_optin, 227 * 1024) - 2048;
     const uint32_t max_stages = (uint32_t)std::min<size_t>(budget / PAIR_STAGE_BYTES, MAX_STAGES);
@@ -314,7 +322,8 @@ int make_gemm_pair(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
     k->kind = 1;
     k->nargs = 3;
     char nm[160];
-    snprintf(nm, sizeof nm, "gemm_pair_%ux%u_%s%s_t256x256_s%u", d->k, d->n, out_tag(d->out), d->m_first ? "_mf" : "", stages);
+    snprintf(nm, sizeof nm, "gemm_pair_%ux%u_%s%s_t256x256_s%u%s", d->k, d->n, out_tag(d->out), d->m_first ? "_mf" : "", stages,
+             d->y_shards > 1 ? (std::string("_y") + std::to_string(d->y_shards)).c_str() : "");
     k->name = nm;
     if (hb_kernel* have = find(ctx, k->name)) {
         auto* g = static_cast<PairGemm*>(have);

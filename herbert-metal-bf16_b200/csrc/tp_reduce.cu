@@ -18,16 +18,19 @@ namespace hb {
 constexpr int TP_MAX_WORLD = 8;
 
 struct TpParams {
+    const float* staging;       // STAGED: this rank's f32 [world][rows_per][n], slot s from rank s
     const uint64_t* peers_acc;  // [world] f32 [m][n] on every rank
     const uint64_t* peers_y;    // [world] bf16 [m][n] on every rank
     uint32_t m, n8, world, rank, rows_per;
 };
 
-template <int OUT>
+template <int OUT, bool STAGED>
 __global__ void __launch_bounds__(256) tp_reduce_kernel(const TpParams p) {
     __shared__ uint64_t acc_s[TP_MAX_WORLD], y_s[TP_MAX_WORLD];
     if (threadIdx.x < p.world) {
-        acc_s[threadIdx.x] = p.peers_acc[threadIdx.x];
+        // STAGED: slot s of the local staging buffer, rebased so that the row index of the whole matrix applies
+        acc_s[threadIdx.x] = STAGED ? reinterpret_cast<uint64_t>(p.staging + ((size_t)threadIdx.x * p.rows_per - (size_t)p.rank * p.rows_per) * p.n8 * 8)
+                                    : p.peers_acc[threadIdx.x];
         y_s[threadIdx.x] = p.peers_y[threadIdx.x];
     }
     __syncthreads();
@@ -79,22 +82,31 @@ __global__ void __launch_bounds__(256) tp_reduce_kernel(const TpParams p) {
 namespace {
 struct TpReduce : hb_kernel {
     uint32_t n = 0, out = 0, world = 0, rank = 0;
+    bool staged = false;
     int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
-        if (na != 2) return fail(ctx, HB_INVALID, name + ": bindings are peers_acc, peers_y (device arrays of one address per rank)");
+        if (na != 2) return fail(ctx, HB_INVALID, name + (staged ? ": bindings are staging, peers_y" : ": bindings are peers_acc, peers_y (device arrays of one address per rank)"));
         if (m == 0) return fail(ctx, HB_INVALID, name + ": m = 0");
-        if (!range_ok(a[0], (size_t)world * 8) || !range_ok(a[1], (size_t)world * 8)) return fail(ctx, HB_INVALID, name + ": a bound range is too small");
+        const uint32_t rows_per = (m + world - 1) / world;
+        if (!range_ok(a[0], staged ? (size_t)world * rows_per * n * 4 : (size_t)world * 8) || !range_ok(a[1], (size_t)world * 8))
+            return fail(ctx, HB_INVALID, name + ": a bound range is too small");
         TpParams p{};
-        p.peers_acc = static_cast<const uint64_t*>(a[0].ptr);
+        if (staged) p.staging = static_cast<const float*>(a[0].ptr);
+        else p.peers_acc = static_cast<const uint64_t*>(a[0].ptr);
         p.peers_y = static_cast<const uint64_t*>(a[1].ptr);
         p.m = m;
         p.n8 = n / 8;
         p.world = world;
         p.rank = rank;
-        p.rows_per = (m + world - 1) / world;
+        p.rows_per = rows_per;
         const size_t units = (size_t)p.rows_per * p.n8;
         const uint32_t grid = (uint32_t)std::max<size_t>(1, std::min<size_t>((units + 255) / 256, (size_t)ctx->sm_count * 8));
-        if (out == HB_OUT_RESIDUAL) tp_reduce_kernel<HB_OUT_RESIDUAL><<<grid, 256, 0, ctx->stream>>>(p);
-        else tp_reduce_kernel<HB_OUT_BF16><<<grid, 256, 0, ctx->stream>>>(p);
+        if (staged) {
+            if (out == HB_OUT_RESIDUAL) tp_reduce_kernel<HB_OUT_RESIDUAL, true><<<grid, 256, 0, ctx->stream>>>(p);
+            else tp_reduce_kernel<HB_OUT_BF16, true><<<grid, 256, 0, ctx->stream>>>(p);
+        } else {
+            if (out == HB_OUT_RESIDUAL) tp_reduce_kernel<HB_OUT_RESIDUAL, false><<<grid, 256, 0, ctx->stream>>>(p);
+            else tp_reduce_kernel<HB_OUT_BF16, false><<<grid, 256, 0, ctx->stream>>>(p);
+        }
         HB_CUDA(ctx, cudaGetLastError());
         ctx->launches++;
         return HB_OK;
@@ -102,7 +114,7 @@ struct TpReduce : hb_kernel {
 };
 }  // namespace
 
-int make_tp_reduce(hb_ctx* ctx, uint32_t n, uint32_t out, uint32_t world, uint32_t rank, hb_kernel** res) {
+int make_tp_reduce(hb_ctx* ctx, uint32_t n, uint32_t out, uint32_t world, uint32_t rank, bool staged, hb_kernel** res) {
     *res = nullptr;
     if (n == 0 || n % 8 != 0) return fail(ctx, HB_UNSUPPORTED, "tp_reduce: n a positive multiple of 8");
     if (out != HB_OUT_BF16 && out != HB_OUT_RESIDUAL) return fail(ctx, HB_UNSUPPORTED, "tp_reduce: output Bf16 or Residual");
@@ -112,9 +124,10 @@ int make_tp_reduce(hb_ctx* ctx, uint32_t n, uint32_t out, uint32_t world, uint32
     k->out = out;
     k->world = world;
     k->rank = rank;
+    k->staged = staged;
     k->kind = 14;
     k->nargs = 2;
-    k->name = std::string("tp_reduce_") + std::to_string(n) + "_" + out_tag(out) + "_r" + std::to_string(rank) + "of" + std::to_string(world);
+    k->name = std::string(staged ? "tp_sum_" : "tp_reduce_") + std::to_string(n) + "_" + out_tag(out) + "_r" + std::to_string(rank) + "of" + std::to_string(world);
     *res = intern(ctx, std::move(k));
     return HB_OK;
 }
@@ -124,7 +137,16 @@ int make_tp_reduce(hb_ctx* ctx, uint32_t n, uint32_t out, uint32_t world, uint32
 extern "C" int hb_tp_reduce_get(hb_ctx* ctx, uint32_t n, uint32_t out, uint32_t world, uint32_t rank, hb_kernel** res) {
     if (!ctx || !res) return hb::fail(ctx, HB_INVALID, "hb_tp_reduce_get: bad argument");
     try {
-        return hb::make_tp_reduce(ctx, n, out, world, rank, res);
+        return hb::make_tp_reduce(ctx, n, out, world, rank, false, res);
+    } catch (const std::exception& e) {
+        return hb::fail(ctx, HB_BACKEND, e.what());
+    }
+}
+
+extern "C" int hb_tp_sum_get(hb_ctx* ctx, uint32_t n, uint32_t out, uint32_t world, uint32_t rank, hb_kernel** res) {
+    if (!ctx || !res) return hb::fail(ctx, HB_INVALID, "hb_tp_sum_get: bad argument");
+    try {
+        return hb::make_tp_reduce(ctx, n, out, world, rank, true, res);
     } catch (const std::exception& e) {
         return hb::fail(ctx, HB_BACKEND, e.what());
     }

@@ -453,16 +453,25 @@ def ep_moe_peer(state: EpPeer, x_local, scores_local, wgu_local, wd_local, group
 # the whole f32 matrix, and the output mode needs no pass of its own.
 
 class TpPeer:
-    """One rank of the peer-memory FFN: the partial-product buffer, the output Y and their peer tables."""
+    """One rank of the peer-memory FFN: the partial-product buffer, the output Y and their peer tables.
 
-    def __init__(self, hb, ctx, rank: int, world: int, m: int, h: int, out: int = OUT_RESIDUAL, device=None):
+    push = True (the default beyond one rank): the down GEMM stores every block of rows of its partial straight
+    into the staging buffer of the rank that sums that block, tile by tile while it computes (hb_gemm_desc.y_shards),
+    and the sum reads local memory only. push = False: the partial stays local and the sum pulls the blocks it
+    needs from the peers (tp_reduce)."""
+
+    def __init__(self, hb, ctx, rank: int, world: int, m: int, h: int, out: int = OUT_RESIDUAL, device=None, push: bool | None = None):
         self.hb, self.ctx, self.rank, self.world, self.m, self.h = hb, ctx, rank, world, m, h
         dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
-        self.pb = PeerBuffers(ctx, rank, world, {"acc": m * h * 4, "y": m * h * 2}, dev)
+        self.push = (world > 1) if push is None else (push and world > 1)
+        self.rows_per = (m + world - 1) // world
+        # acc: the whole partial [m][h] (pull), or the staging [world][rows_per][h] of the blocks this rank sums (push)
+        self.pb = PeerBuffers(ctx, rank, world, {"acc": max(m, world * self.rows_per) * h * 4, "y": m * h * 2}, dev)
         self.acc, self.y = self.pb.local["acc"], self.pb.local["y"]
         self._yv = _view(self.y, (m, h), "<i2", dev).view(torch.bfloat16)
         self.token = torch.zeros(1, device=dev, dtype=torch.float32)
-        self.k_reduce = ctx.tp_reduce(h, out, world, rank)
+        self.k_reduce = ctx.tp_sum(h, out, world, rank) if self.push else ctx.tp_reduce(h, out, world, rank)
+        self.push_table = torch.zeros(world, device=dev, dtype=torch.int64)  # where this rank's block for owner d goes
         self.kernels = {}
 
     def _w(self, t):
@@ -470,6 +479,11 @@ class TpPeer:
 
     def connect(self, local_peers) -> None:
         self.pb.connect(local_peers=[p.pb for p in local_peers])
+        self._after_connect()
+
+    def _after_connect(self) -> None:
+        slot = self.rank * self.rows_per * self.h * 4  # slot `rank` of every owner's staging buffer
+        self.push_table.copy_(self.pb.tables["acc"] + slot)
 
     def close(self) -> None:
         self.pb.close()
@@ -488,17 +502,19 @@ class TpPeer:
         key = (h, ip)
         if key not in self.kernels:
             hmid = torch.empty((self.m, ip), device=x.device, dtype=torch.bfloat16)
-            self.kernels[key] = (self.ctx.gemm(h, 2 * ip, OUT_SWIGLU, rows_max=self.m, cta_pair=1), self.ctx.gemm(ip, h, OUT_F32, rows_max=self.m, cta_pair=1), hmid)
+            self.kernels[key] = (self.ctx.gemm(h, 2 * ip, OUT_SWIGLU, rows_max=self.m, cta_pair=1),
+                                 self.ctx.gemm(ip, h, OUT_F32, rows_max=self.m, cta_pair=1, y_shards=self.world if self.push else 0), hmid)
         k_gu, k_down, hmid = self.kernels[key]
         k_gu(m, self._w(wgu_local), self._w(x), self._w(hmid))
-        k_down(m, self._w(wd_local), self._w(hmid), self.acc)
+        k_down(m, self._w(wd_local), self._w(hmid), self._w(self.push_table) if self.push else self.acc)
 
-    def phase_reduce(self) -> None:  # every rank's partial is complete
-        self.k_reduce(self.m, self.pb.table("acc"), self.pb.table("y"))
+    def phase_reduce(self) -> None:  # every rank's partial is complete (push: has arrived)
+        self.k_reduce(self.m, self.acc if self.push else self.pb.table("acc"), self.pb.table("y"))
 
 
 def tp_peer_connect(state: TpPeer, group=None) -> None:
     state.pb.connect_group(group)
+    state._after_connect()
 
 
 def tp_ffn_peer(state: TpPeer, x, wgu_local, wd_local, group=None, nccl_sync: bool = False):

@@ -172,6 +172,11 @@ typedef struct {
                            count is not a multiple of the SM count, and splits K for short row buckets. */
     uint32_t merge_runs; /* expert modes: 1 = the consecutive tiles of one expert are merged into work items of up to
                             128 rows, so that an expert's weights are read once whatever the tile size */
+    uint32_t y_shards;   /* DENSE, cta_pair, Out::F32: P > 1 = Y is cut into P blocks of ceil(m / P) rows and the Y binding
+                            is a device array u64[P] of the blocks' addresses (16-byte aligned, row stride n), which may be
+                            other GPUs' memory opened with hb_ipc_open: the GEMM of a row-parallel projection stores every
+                            block of its partial product straight into the buffer of the rank that sums it, tile by tile
+                            while it computes (no reference counterpart) */
 } hb_gemm_desc;
 int hb_gemm_get(hb_ctx* ctx, const hb_gemm_desc* desc, hb_kernel** out);
 
@@ -262,6 +267,11 @@ int hb_epilogue_get(hb_ctx* ctx, uint32_t n, uint32_t out, hb_kernel** res);
  * applies the output mode with its own old Y and stores the result into every rank's Y. The host puts a barrier
  * before (partials complete everywhere) and after (Y complete everywhere). Bindings: peers_acc, peers_y. */
 int hb_tp_reduce_get(hb_ctx* ctx, uint32_t n, uint32_t out, uint32_t world, uint32_t rank, hb_kernel** res);
+/* The second half of the same step when the partials were pushed by the GEMMs (hb_gemm_desc.y_shards): this rank's
+ * staging buffer f32 [world][ceil(m / world)][n] holds, from every rank s in slot s, the partial rows this rank sums.
+ * Sums the slots in rank order, rounds once, applies the output mode with its own old Y and stores the rows into
+ * every rank's Y. Bindings: staging (local), peers_y. The host puts a barrier before and after. */
+int hb_tp_sum_get(hb_ctx* ctx, uint32_t n, uint32_t out, uint32_t world, uint32_t rank, hb_kernel** res);
 
 /* The GEMM for callers that must not allocate device memory. (No counterpart in the reference: its buffers all
  * come from Gpu::alloc at load.)

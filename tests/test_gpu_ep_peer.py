@@ -234,32 +234,42 @@ def test_two_processes_over_nvlink():
 
 # ---------------------------------------------------------------- the tensor-parallel FFN through tp_reduce
 
+@pytest.mark.parametrize("push", [False, True])
 @pytest.mark.parametrize("world", [1, 2, 4])
-def test_tp_reduce_emulated_ranks(env, hb200, oracle, world):
+def test_tp_reduce_emulated_ranks(env, hb200, oracle, world, push):
+    # push: the down GEMM stores each block of rows of its partial into its owner's staging buffer (y_shards) and the
+    # sum reads local memory; pull: the partial stays whole and the sum fetches the blocks from the peers
     d, ctx = env
     m, h, inter = 200, 256, 512
     x, wgu, wd, y0 = oracle.normal((m, h), 1, 1, 1.0), oracle.normal((2 * inter, h), 2, 2, h**-0.5), oracle.normal((h, inter), 3, 3, inter**-0.5), oracle.normal((m, h), 4, 4, 1.0)
     xt = t16(x).cuda()
-    ranks = [d.TpPeer(hb200, ctx, r, world, m, h) for r in range(world)]
+    ranks = [d.TpPeer(hb200, ctx, r, world, m, h, push=push) for r in range(world)]
+    assert all(st.push == (push and world > 1) for st in ranks)
     for st in ranks:
         st.connect(ranks)
         st.set_y(t16(y0).cuda())
     shards = [(d.shard_gate_up(t16(wgu), r, world).cuda(), d.shard_down(t16(wd), r, world).cuda()) for r in range(world)]
-    for st, (a, b) in zip(ranks, shards):
-        st.phase_gemms(xt, a, b)
-    # what the all-reduce form gives from the same partials: f32 sum in rank order, then the epilogue kernel
-    acc = None
-    for st in ranks:
-        part = torch.empty(m, h, device="cuda", dtype=torch.float32)
-        part.copy_(torch.as_tensor(_cai(st.acc.ptr, (m, h), "<f4"), device="cuda"))
-        acc = part if acc is None else acc + part
+    # what the all-reduce form gives: the same GEMM kernels, f32 sum in rank order, then the epilogue kernel
     be = d.GpuBackend(hb200, ctx, rows_max=512)
+    acc = None
+    for a, b in shards:
+        hm = torch.empty(m, a.shape[0] // 2, device="cuda", dtype=torch.bfloat16)
+        part = torch.empty(m, h, device="cuda", dtype=torch.float32)
+        ctx.gemm(h, a.shape[0], 3, rows_max=m, cta_pair=1)(m, be._w(a), be._w(xt), be._w(hm))
+        ctx.gemm(hm.shape[1], h, 1, rows_max=m, cta_pair=1)(m, be._w(b), be._w(hm), be._w(part))
+        torch.cuda.synchronize()
+        acc = part if acc is None else acc + part
     want = be.epilogue(acc, t16(y0).cuda(), 2)
-    for st in ranks:
-        st.phase_reduce()
-    torch.cuda.synchronize()
-    for st in ranks:
-        assert torch.equal(st.y_view(), want), f"rank {st.rank}"
+    for rep in range(2):
+        for st in ranks:
+            st.set_y(t16(y0).cuda())
+        for st, (a, b) in zip(ranks, shards):
+            st.phase_gemms(xt, a, b)
+        for st in ranks:
+            st.phase_reduce()
+        torch.cuda.synchronize()
+        for st in ranks:
+            assert torch.equal(st.y_view(), want), f"rank {st.rank}, pass {rep}"
     hmid = oracle.gemm_f64(x, wgu, 3)
     within_contract(oracle, oracle.gemm_f64(hmid, wd, 2, y0), n16(ranks[0].y_view().cpu()), f"FFN over {world} emulated ranks")
 
