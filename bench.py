@@ -530,6 +530,46 @@ def bench_extra(hb, ctx, sel, torch, dev, wrap, pk, rank, world, barrier, max_ov
     lm["fused_form"] = fused[0][0].name
     out["lm_head_argmax_m1"] = lm
     del w2, y2
+    # -- the matrix products of one 9B-class layer at decode time (1, 4 and 8 rows), with the norms before them, as one
+    # recorded sequence over four layers' worth of weights (1.5 GB: every byte streams from HBM)
+    try:
+        layers = 4
+        wl = [[(torch.randn(nn, kk, device=dev, generator=g) * kk**-0.5).bfloat16() for _, kk, nn, _ in LAYER] for _ in range(layers)]
+        nw = (torch.randn(HIDDEN, device=dev, generator=g) * 0.1).bfloat16()
+        dec = {}
+        for m in (1, 4, 8):
+            xd = torch.randn(m, HIDDEN, device=dev, generator=g).bfloat16()
+            xn = torch.zeros_like(xd)
+            qkvd = torch.zeros(m, 6144, device=dev, dtype=torch.bfloat16)
+            hd = torch.zeros(m, INTER, device=dev, dtype=torch.bfloat16)
+            copies = lambda i: [wrap(wl[l][i]) for l in range(layers)]
+            k_q = sel.matvec(HIDDEN, 6144, 0, m, copies(0), wrap(xn), wrap(qkvd))
+            k_o = sel.matvec(HIDDEN, HIDDEN, 2, m, copies(1), wrap(xn), wrap(xd))
+            k_g = sel.matvec(HIDDEN, 2 * INTER, 3, m, copies(2), wrap(xn), wrap(hd))
+            k_d = sel.matvec(INTER, HIDDEN, 2, m, copies(3), wrap(hd), wrap(xd))
+            k_n = ctx.rmsnorm(HIDDEN, 1e-6, True)
+            ops_d = []
+            for l in range(layers):
+                ops_d += [(k_n, m, wrap(xd), wrap(nw), wrap(xn)), (k_q, m, wrap(wl[l][0]), wrap(xn), wrap(qkvd)), (k_o, m, wrap(wl[l][1]), wrap(xn), wrap(xd)),
+                          (k_n, m, wrap(xd), wrap(nw), wrap(xn)), (k_g, m, wrap(wl[l][2]), wrap(xn), wrap(hd)), (k_d, m, wrap(wl[l][3]), wrap(hd), wrap(xd))]
+            secs = {}
+            for mode in ("plain", "overlapped"):  # overlapped: each kernel is launched ahead of its predecessor's end and waits inside
+                ctx.set_launch_overlap(mode == "overlapped")
+                gr = ctx.record(ops_d)
+                gr.time(3)
+                barrier()
+                secs[mode] = max_over_ranks(gr.time(20) / (20 * layers))
+                gr.free()
+            ctx.set_launch_overlap(False)
+            sec_d = min(secs.values())
+            wb = sum(2.0 * nn * kk for _, kk, nn, _ in LAYER)
+            dec[f"m{m}"] = {"us_per_layer": sec_d * 1e6, "weight_gbs": wb / sec_d / 1e9, "frac_hbm": wb / sec_d / 1e9 / pk["hbm_gbs"], "kernels_per_layer": 6,
+                            "us_per_layer_plain_launches": secs["plain"] * 1e6, "us_per_layer_overlapped_launches": secs["overlapped"] * 1e6,
+                            "forms": [k_q.name, k_o.name, k_g.name, k_d.name]}
+        out["decode_layer_9b"] = dec
+        del wl
+    except Exception as e:
+        out["decode_error"] = repr(e)
     # -- MoE block (config 5): 2048 tokens, hidden 2048, 256 experts, top-8, expert intermediate 512
     m, h, mi, E, top_k = 2048, 2048, 512, 256, 8
     pairs = m * top_k

@@ -106,6 +106,7 @@ def lib() -> C.CDLL:
         "hb_moe_out_get": (ci, [vp, u32, pvp]),
         "hb_peer_sync_get": (ci, [vp, u32, u32, u32, pvp]),
         "hb_set_peer_wait_ms": (ci, [vp, u32]),
+        "hb_set_launch_overlap": (ci, [vp, ci]),
         "hb_graph_record": (ci, [vp, C.POINTER(Op), ci, pvp]),
         "hb_graph_launch": (ci, [vp, vp]),
         "hb_graph_time": (ci, [vp, vp, ci, C.POINTER(C.c_double)]),
@@ -164,7 +165,7 @@ EXPORTS = [
     "hb_download", "hb_memset", "hb_sync", "hb_launch_count", "hb_event_new", "hb_event_free", "hb_lane_record", "hb_lane_wait", "hb_event_sync",
     "hb_upload_async", "hb_download_async", "hb_host_alloc", "hb_host_free", "hb_ipc_export", "hb_ipc_open", "hb_ipc_close",
     "hb_ep_dispatch_get", "hb_ep_plan_get", "hb_ep_return_get", "hb_tp_reduce_get", "hb_tp_sum_get", "hb_rmsnorm_get", "hb_argmax_get", "hb_moe_out_get", "hb_peer_sync_get", "hb_set_peer_wait_ms", "hb_gemm_get", "hb_matvec_get", "hb_swiglu_get", "hb_route_get",
-    "hb_moe_sort_get", "hb_moe_tiles", "hb_moe_gather_get", "hb_moe_combine_get", "hb_epilogue_get", "hb_gemm_static_scratch", "hb_kernel_name", "hb_launch", "hb_run", "hb_time", "hb_graph_record", "hb_graph_launch", "hb_graph_time", "hb_graph_free",
+    "hb_moe_sort_get", "hb_moe_tiles", "hb_moe_gather_get", "hb_moe_combine_get", "hb_epilogue_get", "hb_gemm_static_scratch", "hb_kernel_name", "hb_launch", "hb_run", "hb_time", "hb_set_launch_overlap", "hb_graph_record", "hb_graph_launch", "hb_graph_time", "hb_graph_free",
     "hb_tune_new", "hb_tune_free", "hb_tune_apply", "hb_tune_get", "hb_tune_summary", "hb_tune_gemm_timed", "hb_selector_new",
     "hb_selector_free", "hb_selector_log", "hb_selector_buckets", "hb_fill_random16", "hb_select_gemm", "hb_select_gate_up",
     "hb_select_matvec", "hb_select_experts", "hb_selector_inject_wrong", "hb_check_rule",
@@ -455,6 +456,9 @@ class Context:
     def run(self, ops) -> None:
         arr, keep = self.make_ops(ops)
         self._check(lib().hb_run(self.h, arr, len(ops)))
+
+    def set_launch_overlap(self, on: bool) -> None:
+        self._check(lib().hb_set_launch_overlap(self.h, 1 if on else 0))
 
     def record(self, ops) -> "Graph":
         """The op sequence as one replayable object (hb_graph_record)."""

@@ -154,40 +154,54 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     const uint32_t tmem_base = bars.tmem_base;
 
     const uint32_t n_segs = skinny_seg(p, blockIdx.x, gridDim.x, 0, nullptr);
+    griddep_launch_dependents();
 
     if (warp == 0) {
         if (lane == 0) {
             tma_prefetch_desc(&tm_w);
             tma_prefetch_desc(&tm_x);
-            uint32_t s = 0, ph = 0;
-            bool ok = true;
-            for (uint32_t i = 0; ok && i < n_segs; ++i) {
-                SkinnySeg sg;
-                skinny_seg(p, blockIdx.x, gridDim.x, i, &sg);
-                const uint32_t fb = sg.fb, kb0 = sg.kb0, kb1 = sg.kb1;
-                const int row_w0 = (int)(fb * 128);
-                const int row_w1 = (int)(p.n_out + fb * 128);  // SWIGLU: the up rows of the same features
-                for (uint32_t kb = kb0; kb < kb1; kb += KPS) {
-                    if (!mbar_wait(smem_u32(&bars.empty[s]), ph ^ 1u)) {
-                        report(p.status, ST_WAIT_TIMEOUT, WHERE_EMPTY, s);
-                        ok = false;
-                        break;
-                    }
-                    const uint32_t full = smem_u32(&bars.full[s]);
-                    const uint32_t nkb = min((uint32_t)KPS, kb1 - kb);
-                    mbar_arrive_expect_tx(full, nkb * KB_BYTES);
-#pragma unroll
-                    for (uint32_t i = 0; i < (uint32_t)KPS; ++i) {
-                        if (i < nkb) {
-                            const uint32_t dst = smem_base + s * STAGE_BYTES + i * KB_BYTES;
-                            tma_load_2d(dst, &tm_w, full, (int)((kb + i) * 64), row_w0);
-                            if (NACC == 2) tma_load_2d(dst + SK_A_BYTES, &tm_w, full, (int)((kb + i) * 64), row_w1);
-                            tma_load_2d(dst + A_STAGE, &tm_x, full, (int)((kb + i) * 64), 0);
+            // The stage fills of this CTA, in order. The first S of them find their stage free; their weight boxes do
+            // not depend on the kernel before this one on the stream, so they are issued first (pass 0), then the
+            // predecessor is waited for, then their activation boxes follow (pass 1) and the rest of the fills (pass 2).
+            auto walk = [&](int pass) -> bool {
+                uint32_t s = 0, ph = 0, fill = 0;
+                for (uint32_t i = 0; i < n_segs; ++i) {
+                    SkinnySeg sg;
+                    skinny_seg(p, blockIdx.x, gridDim.x, i, &sg);
+                    const uint32_t fb = sg.fb, kb0 = sg.kb0, kb1 = sg.kb1;
+                    const int row_w0 = (int)(fb * 128);
+                    const int row_w1 = (int)(p.n_out + fb * 128);  // SWIGLU: the up rows of the same features
+                    for (uint32_t kb = kb0; kb < kb1; kb += KPS, ++fill) {
+                        const bool early = fill < S;
+                        if (pass != 2 && !early) return true;
+                        const bool do_w = pass == 0 || (pass == 2 && !early), do_x = pass == 1 || (pass == 2 && !early);
+                        if (pass == 2 && !early && !mbar_wait(smem_u32(&bars.empty[s]), ph ^ 1u)) {
+                            report(p.status, ST_WAIT_TIMEOUT, WHERE_EMPTY, s);
+                            return false;
                         }
+                        const uint32_t full = smem_u32(&bars.full[s]);
+                        const uint32_t nkb = min((uint32_t)KPS, kb1 - kb);
+                        if (do_w) mbar_arrive_expect_tx(full, nkb * KB_BYTES);
+#pragma unroll
+                        for (uint32_t j = 0; j < (uint32_t)KPS; ++j) {
+                            if (j < nkb) {
+                                const uint32_t dst = smem_base + s * STAGE_BYTES + j * KB_BYTES;
+                                if (do_w) {
+                                    tma_load_2d(dst, &tm_w, full, (int)((kb + j) * 64), row_w0);
+                                    if (NACC == 2) tma_load_2d(dst + SK_A_BYTES, &tm_w, full, (int)((kb + j) * 64), row_w1);
+                                }
+                                if (do_x) tma_load_2d(dst + A_STAGE, &tm_x, full, (int)((kb + j) * 64), 0);
+                            }
+                        }
+                        if (++s == S) { s = 0; ph ^= 1u; }
                     }
-                    if (++s == S) { s = 0; ph ^= 1u; }
                 }
-            }
+                return true;
+            };
+            walk(0);
+            griddep_wait();
+            walk(1);
+            walk(2);
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -235,6 +249,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     } else {
         const uint32_t q = (uint32_t)warp & 3u;
         uint32_t it = 0;
+        griddep_wait();  // Y may be read (residual) or still be in use by the kernel before this one
         for (; it < n_segs; ++it) {
             SkinnySeg sg;
             skinny_seg(p, blockIdx.x, gridDim.x, it, &sg);
@@ -373,8 +388,7 @@ struct SkinnyGemm : hb_kernel {
         p.counters = counters;
         p.status = ctx->status_dev;
         const uint32_t grid = balanced ? grid_balanced : std::min<uint32_t>(p.feat_blocks, (uint32_t)ctx->sm_count);
-        fn<<<grid, SK_THREADS, smem, ctx->stream>>>(tm_w, tm_x, p);
-        HB_CUDA(ctx, cudaGetLastError());
+        HB_CUDA(ctx, launch_kernel(ctx, true, fn, dim3(grid), dim3(SK_THREADS), smem, tm_w, tm_x, p));
         ctx->launches++;
         return HB_OK;
     }
@@ -399,8 +413,12 @@ int make_matvec_skinny(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out) {
     const uint32_t nacc = d->out == HB_OUT_SWIGLU ? 2 : 1;
     const size_t stage_bytes = ((size_t)nacc * SK_A_BYTES + np * 128) * kps;
     const size_t budget = std::min<size_t>(ctx->smem_optin, 227 * 1024) - 2048;
-    const uint32_t stages = (uint32_t)std::min<size_t>(budget / stage_bytes, SK_MAX_STAGES);
+    uint32_t stages = (uint32_t)std::min<size_t>(budget / stage_bytes, SK_MAX_STAGES);
     if (stages < 2) return fail(ctx, HB_UNSUPPORTED, "matvec (tensor core): the pipeline does not fit in shared memory");
+    // `persist` caps the pipeline depth: with half the shared memory or less, the CTAs of two kernels that follow one
+    // another on the stream fit on an SM together, and with overlapped launches the second streams its first
+    // weights while the first drains
+    if (d->persist >= 2) stages = std::min(stages, d->persist);
     auto k = std::make_unique<SkinnyGemm>();
     k->k = d->k;
     k->n = d->n;
@@ -439,6 +457,10 @@ int make_matvec_skinny(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out) {
     }
     cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin - 1024);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(max dynamic shared memory)");
+    // all of the SM's L1/shared array as shared memory, whatever one CTA asks for: with a capped pipeline two CTAs
+    // (of two consecutive kernels) must fit side by side
+    e = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(shared memory carveout)");
     *out = intern(ctx, std::move(k));
     return HB_OK;
 }

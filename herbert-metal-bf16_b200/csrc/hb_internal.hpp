@@ -40,6 +40,7 @@ struct hb_ctx {
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
     cudaStream_t copy_lane[2] = {nullptr, nullptr};  // upload, download: made on first use
     std::vector<void*> host_allocs;
+    bool overlap_launches = false;  // kernels that know how to wait for their predecessor are launched ahead of its end
     uint32_t peer_wait_ms = 5000;  // bound of a barrier's wait for the other GPUs
     std::vector<void*> ipc_opened;  // peers' allocations mapped into this process
     uint32_t* status_dev = nullptr;  // 8 words, see tc05.cuh
@@ -86,6 +87,25 @@ int make_moe_gather(hb_ctx* ctx, uint32_t h, uint32_t top_k, hb_kernel** out);
 int make_moe_combine(hb_ctx* ctx, uint32_t d, uint32_t top_k, uint32_t f32_sum, hb_kernel** out);
 int make_ep_move(hb_ctx* ctx, bool ret, uint32_t h, uint32_t top_k, uint32_t experts, uint32_t world, uint32_t rank, uint32_t cap, hb_kernel** out);
 int make_ep_plan(hb_ctx* ctx, uint32_t experts, uint32_t world, uint32_t rank, uint32_t bm, uint32_t cap, hb_kernel** out);
+
+// Launches `fn`; with `waits_itself` (the kernel calls griddep_wait before it touches its predecessor's data) and the
+// context's overlap switch on, with programmatic stream serialization.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(hb_ctx* ctx, bool waits_itself, void (*fn)(KArgs...), dim3 grid, dim3 block, size_t smem, Args&&... args) {
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    if (waits_itself && ctx->overlap_launches) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    return cudaLaunchKernelEx(&cfg, fn, static_cast<KArgs>(args)...);
+}
 
 // Registers `k` under its name (or returns the existing object of that name).
 hb_kernel* intern(hb_ctx* ctx, std::unique_ptr<hb_kernel> k);

@@ -46,6 +46,8 @@ __global__ void __launch_bounds__(MV_THREADS) matvec_kernel(const MatvecParams p
     unsigned long long best[M];
 #pragma unroll
     for (int i = 0; i < M; ++i) best[i] = 0ull;
+    griddep_launch_dependents();
+    griddep_wait();  // x comes from the kernel before this one
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t split = p.split;
     const uint32_t slots = MV_WARPS / split;  // row groups a block works on at a time
@@ -255,8 +257,7 @@ struct Matvec : hb_kernel {
         const uint32_t slots = MV_WARPS / d.split;
         uint32_t grid = (p.groups + slots - 1) / slots;
         if (d.persist) grid = std::min<uint32_t>(grid, (uint32_t)(ctx->sm_count * blocks_per_sm));
-        fn<<<grid, MV_THREADS, 0, ctx->stream>>>(p);
-        HB_CUDA(ctx, cudaGetLastError());
+        HB_CUDA(ctx, launch_kernel(ctx, true, fn, dim3(grid), dim3(MV_THREADS), 0, p));
         ctx->launches++;
         return HB_OK;
     }

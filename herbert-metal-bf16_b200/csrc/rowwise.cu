@@ -48,6 +48,8 @@ __global__ void __launch_bounds__(ROW_THREADS) rmsnorm_rows_kernel(const uint16_
                                                                    uint32_t rows, uint32_t d, float inv_d, float eps, uint32_t plus_one, uint32_t vec) {
     extern __shared__ uint16_t row_s[];
     __shared__ float part[9];
+    griddep_launch_dependents();
+    griddep_wait();
     for (uint32_t row = blockIdx.x; row < rows; row += gridDim.x) {
         const uint16_t* xr = x + (size_t)row * d;
         stage_row(row_s, xr, d, vec);
@@ -188,9 +190,8 @@ struct RmsNorm : hb_kernel {
             return fail(ctx, HB_INVALID, name + ": a bound range is too small");
         const uintptr_t al = reinterpret_cast<uintptr_t>(a[0].ptr) | reinterpret_cast<uintptr_t>(a[1].ptr) | reinterpret_cast<uintptr_t>(a[2].ptr);
         const uint32_t vec = (d % 8 == 0 && (al & 15u) == 0) ? 1u : 0u;
-        rmsnorm_rows_kernel<<<row_grid(ctx, m), ROW_THREADS, (size_t)d * 2 + 16, ctx->stream>>>(static_cast<const uint16_t*>(a[0].ptr), static_cast<const uint16_t*>(a[1].ptr),
-                                                                                               static_cast<uint16_t*>(a[2].ptr), m, d, 1.0f / (float)d, eps, plus_one, vec);
-        HB_CUDA(ctx, cudaGetLastError());
+        HB_CUDA(ctx, launch_kernel(ctx, true, rmsnorm_rows_kernel, dim3(row_grid(ctx, m)), dim3(ROW_THREADS), (size_t)d * 2 + 16, static_cast<const uint16_t*>(a[0].ptr),
+                                   static_cast<const uint16_t*>(a[1].ptr), static_cast<uint16_t*>(a[2].ptr), m, d, 1.0f / (float)d, eps, plus_one, vec));
         ctx->launches++;
         return HB_OK;
     }

@@ -398,6 +398,12 @@ int hb_time(hb_ctx* ctx, const hb_op* ops, int nops, int reps, double* gpu_secon
     return hb::check_status(ctx);
 }
 
+int hb_set_launch_overlap(hb_ctx* ctx, int on) {
+    if (!ctx) return HB_INVALID;
+    ctx->overlap_launches = on != 0;
+    return HB_OK;
+}
+
 // ---- recorded sequences ------------------------------------------------------------------------
 struct hb_graph {
     cudaGraph_t graph = nullptr;

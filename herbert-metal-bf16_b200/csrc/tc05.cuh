@@ -94,6 +94,14 @@ __device__ __forceinline__ uint32_t swiglu_bf16(float g, float u) {
     return f32_to_bf16(__fmul_rn(gs, u));
 }
 
+// ------------------------------------------------- overlapped launches
+// A kernel launched with programmatic stream serialization may start while its predecessor on the stream is still
+// running; griddep_wait() is where it stops until the predecessor has completed and its memory is visible. What
+// comes before the wait must not touch anything the predecessor writes (prefetching weights is fine). A kernel
+// calls griddep_launch_dependents() early to let its successor start as SMs free up. Both are no-ops in a plain launch.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ----------------------------------------------------------------- argmax
 // "The largest logit, the first index on a tie" (reference src/metal/kernels.rs:1461-1565) as the maximum of a
 // 64-bit key: order-preserving value bits above the inverted index. The result does not depend on the order in

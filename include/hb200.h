@@ -201,7 +201,9 @@ typedef struct {
                                several SMs are summed from f32 partials in K order. Accumulation order inside a
                                range is the tensor core's, as in the prefill GEMM. `split` (1, 2 or 4) is then the
                                number of neighbouring K blocks one pipeline stage holds (longer runs per weight row
-                               in DRAM); the other form fields are ignored. */
+                               in DRAM) and `persist` >= 2 caps the number of stages (with half the shared memory
+                               or less two consecutive kernels share an SM, see hb_set_launch_overlap); the other
+                               form fields are ignored. */
     uint32_t argmax;        /* Out::Bf16 only: 1 = also the index of the largest output of every row, the first on a tie
                                (argmax_partial + argmax_final, src/metal/kernels.rs:1461-1565, folded into the
                                projection: no pass over the logits, no launch of its own); 2 = the index only, y is
@@ -313,6 +315,12 @@ int hb_time(hb_ctx* ctx, const hb_op* ops, int nops, int reps, double* gpu_secon
  * reference encodes its ops into one command buffer per step (src/metal/gpu.rs:151-221) for the same reason. The
  * bound ranges and m are fixed at recording. Kernels whose launches carry a host-side counter cannot be recorded
  * (the stream-K GEMM, hb_gemm_static_scratch, hb_peer_sync_get): HB_UNSUPPORTED. */
+/* Overlapped launches (off by default): the decode kernels (hb_matvec_get in all its forms, hb_rmsnorm_get) are then
+ * launched with programmatic stream serialization: a kernel may start while the one before it on the stream is
+ * still finishing, sets up, prefetches weights, and waits inside for its predecessor's completion before it reads
+ * an activation or writes an output. Results are unchanged; a chain of 15-20 us kernels loses its launch gaps.
+ * Applies to plain launches and to sequences recorded afterwards. */
+int hb_set_launch_overlap(hb_ctx* ctx, int on);
 typedef struct hb_graph hb_graph;
 int hb_graph_record(hb_ctx* ctx, const hb_op* ops, int nops, hb_graph** out);
 int hb_graph_launch(hb_ctx* ctx, hb_graph* g);

@@ -98,3 +98,38 @@ def test_recorded_sequence_replays(ctx, hb200, oracle):
         ctx.record([(ctx.gemm(k, n, OUT_BF16, rows_max=64, stream_k=1), m, d_w, d_x, d_h)])
     assert e.value.status == hb200.UNSUPPORTED and "cannot be replayed" in e.value.message
     ctx.sync()
+
+
+def test_overlapped_launches_change_nothing_but_time(hb200, oracle):
+    # a decode-like chain (norm -> projection -> residual projection), each kernel consuming its predecessor's output:
+    # launched ahead of their predecessors' end, the kernels wait inside; the bits are those of plain launches
+    ctx = hb200.Context(0)
+    try:
+        k, n = 2048, 4096
+        for m in (1, 8):
+            x = oracle.normal((m, k), 1, m, 1.0)
+            w1, w2 = oracle.normal((n, k), 2, 2, k**-0.5), oracle.normal((k, n), 3, 3, n**-0.5)
+            nw = oracle.normal((k,), 4, 4, 0.1)
+            outs = []
+            for overlap in (False, True):
+                ctx.set_launch_overlap(overlap)
+                d_x, d_xn, d_h = ctx.to_device(x), ctx.alloc(m * k * 2), ctx.alloc(m * n * 2)
+                d_w1, d_w2, d_nw = ctx.to_device(w1), ctx.to_device(w2), ctx.to_device(nw)
+                form = dict(tensor_core=1, split=2) if m > 1 else dict(rows_per_warp=2, split=2)
+                ops = [(ctx.rmsnorm(k, 1e-6, True), m, d_x, d_nw, d_xn), (ctx.matvec(k, n, OUT_BF16, rows_max=m, **form), m, d_w1, d_xn, d_h),
+                       (ctx.matvec(n, k, OUT_RESIDUAL, rows_max=m, **form), m, d_w2, d_h, d_x)]
+                for _ in range(5):  # the residual stream feeds the next pass: five dependent passes
+                    ctx.run(ops)
+                ctx.sync()
+                res = [d_x.download(np.uint16, (m, k))]
+                g = ctx.record(ops)
+                for _ in range(5):
+                    g.launch()
+                ctx.sync()
+                res.append(d_x.download(np.uint16, (m, k)))
+                g.free()
+                outs.append(res)
+            assert np.array_equal(outs[0][0], outs[1][0]) and np.array_equal(outs[0][1], outs[1][1])
+        ctx.set_launch_overlap(False)
+    finally:
+        ctx.close()
