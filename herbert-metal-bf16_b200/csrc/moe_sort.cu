@@ -30,10 +30,16 @@ struct SortParams {
     uint32_t use_masks; // the per-expert row masks fit in shared memory
     uint32_t words;     // stride of an expert's mask in words: ceil(rows_max / 32) made odd
     uint32_t list_staged;  // the sorted list fits in shared memory as 16-bit pair numbers
+    uint32_t* only_if;     // when set: run only if this word is not zero (the cluster form could not do it), and clear it
 };
 
 __global__ void __launch_bounds__(SORT_THREADS) moe_sort_kernel(const SortParams p) {
     extern __shared__ uint32_t sm[];
+    if (p.only_if) {
+        if (*p.only_if == 0) return;
+        __syncthreads();  // everybody has read the word
+        if (threadIdx.x == 0) *p.only_if = 0;
+    }
     const uint32_t experts = p.experts, top_k = p.top_k, bm = p.bm;
     uint32_t* off = sm;                   // [experts] first sorted row of expert e
     uint32_t* tot = off + experts;        // [experts] pairs of expert e
@@ -233,11 +239,166 @@ __global__ void __launch_bounds__(SORT_THREADS) moe_sort_kernel(const SortParams
     }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// The same sort by a cluster of eight CTAs (distributed shared memory), for the case the fast path above covers: a
+// route that names an expert at most once per row. The rows are dealt to the CTAs in contiguous blocks (a multiple of
+// 32 rows each). Every CTA builds the masks of its own rows, counts its pairs per expert and stores the counts into
+// the shared memory of all eight CTAs; after one cluster barrier each CTA knows, per expert, the total and how many
+// pairs the CTAs before it hold, scans the totals itself and places its own pairs:
+//   first row of the expert + pairs of that expert in the CTAs before + rank inside the CTA.
+// The order is the single-CTA kernel's (and the reference's): experts ascending, pairs ascending inside an expert.
+// One SM's shared-memory and store throughput bound the single-CTA form; eight SMs share the work here.
+// A route with a repeated expert in a row makes the cluster raise `fallback` and write nothing; the single-CTA
+// kernel, enqueued behind it with only_if = fallback, then does the sort (otherwise it returns at once).
+constexpr int CS_THREADS = 512;
+constexpr int CS_CTAS = 8;
+
+struct ClusterSortParams {
+    const uint32_t* route;
+    uint32_t* list;
+    uint32_t* tiles;
+    uint32_t* offsets;
+    uint32_t* fallback;
+    uint32_t rows, experts, top_k, bm;
+    uint32_t rows_per_cta;  // a multiple of 32
+    uint32_t words;         // stride of an expert's mask: rows_per_cta_max / 32, made odd
+    uint32_t ex_cap;        // u16 slots of the staged experts
+};
+
+__device__ __forceinline__ uint32_t cs_map(uint32_t smem_addr, uint32_t cta) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(cta));
+    return r;
+}
+__device__ __forceinline__ void cs_store(uint32_t cluster_addr, uint32_t v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+
+__global__ void __cluster_dims__(CS_CTAS, 1, 1) __launch_bounds__(CS_THREADS) moe_sort_cluster_kernel(const ClusterSortParams p) {
+    extern __shared__ uint32_t sm[];
+    const uint32_t experts = p.experts, top_k = p.top_k, bm = p.bm;
+    uint32_t* cnt_all = sm;                          // [CS_CTAS][experts]: pairs of expert e in CTA c (written by CTA c)
+    uint32_t* dup_all = cnt_all + CS_CTAS * experts; // [CS_CTAS]
+    uint32_t* off = dup_all + CS_CTAS;               // [experts] first sorted row of e + pairs of e in the CTAs before
+    uint32_t* sa = off + experts;                    // [32] warp totals of the scans
+    uint32_t* st = sa + 32;                          // [32]
+    uint32_t* mask = st + 32;                        // [experts][words]
+    uint32_t* pre = mask + experts * p.words;        // [experts][words]
+    uint16_t* ex16 = reinterpret_cast<uint16_t*>(pre + experts * p.words);
+    const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    uint32_t cta;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(cta));
+    const uint32_t r0 = min(p.rows, cta * p.rows_per_cta), r1 = min(p.rows, r0 + p.rows_per_cta);
+    const uint32_t my_rows = r1 - r0, my_pairs = my_rows * top_k, words = p.rows_per_cta / 32;
+    __shared__ uint32_t dup_s;
+
+    for (uint32_t i = tid; i < experts * p.words; i += CS_THREADS) mask[i] = 0;
+    if (tid == 0) dup_s = 0;
+    // the experts of this CTA's rows
+    const uint32_t* rt = p.route + (size_t)r0 * 2 * top_k;
+    if (top_k % 4 == 0 && (reinterpret_cast<uintptr_t>(p.route) & 15u) == 0) {
+        const uint32_t q4 = top_k / 4, vecs = my_rows * q4;
+        for (uint32_t v = tid; v < vecs; v += CS_THREADS) {
+            const uint4 e = reinterpret_cast<const uint4*>(rt + (size_t)(v / q4) * 2 * top_k)[v % q4];
+            const uint32_t at = (v / q4) * top_k + (v % q4) * 4;
+            ex16[at] = (uint16_t)e.x; ex16[at + 1] = (uint16_t)e.y; ex16[at + 2] = (uint16_t)e.z; ex16[at + 3] = (uint16_t)e.w;
+        }
+    } else {
+        for (uint32_t i = tid; i < my_pairs; i += CS_THREADS) ex16[i] = (uint16_t)rt[(size_t)(i / top_k) * 2 * top_k + (i % top_k)];
+    }
+    __syncthreads();
+    for (uint32_t i = tid; i < my_pairs; i += CS_THREADS) {
+        const uint32_t e = ex16[i], r = i / top_k, bit = 1u << (r & 31);
+        if (e >= experts || (atomicOr(&mask[e * p.words + (r >> 5)], bit) & bit)) dup_s = 1;  // twice in a row (or not an expert)
+    }
+    __syncthreads();
+    // per expert: prefix of the popcounts of its words; the count goes to every CTA of the cluster
+    for (uint32_t e = tid; e < experts; e += CS_THREADS) {
+        uint32_t run = 0;
+        for (uint32_t w = 0; w < words; ++w) {
+            pre[e * p.words + w] = run;
+            run += __popc(mask[e * p.words + w]);
+        }
+        const uint32_t mine = smem_u32(&cnt_all[cta * experts + e]);
+#pragma unroll
+        for (uint32_t c = 0; c < CS_CTAS; ++c) cs_store(cs_map(mine, c), run);
+    }
+    if (tid < CS_CTAS) cs_store(cs_map(smem_u32(&dup_all[cta]), tid), dup_s);
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    // (no CTA touches another's shared memory after this barrier, so none has to wait for the others to finish)
+    uint32_t any_dup = 0;
+#pragma unroll
+    for (uint32_t c = 0; c < CS_CTAS; ++c) any_dup |= dup_all[c];
+    if (any_dup) {
+        if (cta == 0 && tid == 0) *p.fallback = 1;
+        return;
+    }
+    // totals and the share of the CTAs before this one; scans of (pairs, tiles) over the experts
+    // (thread e for e < CS_THREADS; the cluster form is built for at most CS_THREADS experts)
+    uint32_t total_e = 0, before = 0;
+    if (tid < experts) {
+#pragma unroll
+        for (uint32_t c = 0; c < CS_CTAS; ++c) {
+            const uint32_t v = cnt_all[c * experts + tid];
+            total_e += v;
+            if (c < cta) before += v;
+        }
+    }
+    const uint32_t ntile_e = (total_e + bm - 1) / bm;
+    uint32_t a = total_e, t = ntile_e;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+        const uint32_t va = __shfl_up_sync(0xffffffffu, a, d), vt = __shfl_up_sync(0xffffffffu, t, d);
+        if (lane >= (uint32_t)d) { a += va; t += vt; }
+    }
+    if (lane == 31) { sa[warp] = a; st[warp] = t; }
+    __syncthreads();
+    if (warp == 0) {
+        uint32_t wa = lane < CS_THREADS / 32 ? sa[lane] : 0, wt = lane < CS_THREADS / 32 ? st[lane] : 0;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const uint32_t va = __shfl_up_sync(0xffffffffu, wa, d), vt = __shfl_up_sync(0xffffffffu, wt, d);
+            if (lane >= (uint32_t)d) { wa += va; wt += vt; }
+        }
+        if (lane < CS_THREADS / 32) { sa[lane] = wa; st[lane] = wt; }
+    }
+    __syncthreads();
+    if (warp > 0) { a += sa[warp - 1]; t += st[warp - 1]; }
+    if (tid < experts) {
+        const uint32_t start = a - total_e, tfirst = t - ntile_e;
+        off[tid] = start + before;
+        if (cta == 0) {  // the table and the offsets are the same in every CTA: one writes them
+            if (p.offsets) {
+                p.offsets[tid] = start;
+                if (tid == experts - 1) p.offsets[experts] = a;
+            }
+            for (uint32_t j = 0, ti = tfirst; j < total_e; j += bm, ++ti) {
+                p.tiles[1 + 3 * ti] = tid;
+                p.tiles[2 + 3 * ti] = start + j;
+                p.tiles[3 + 3 * ti] = min(bm, total_e - j);
+            }
+            if (tid == experts - 1) p.tiles[0] = t;
+        }
+    }
+    __syncthreads();
+    // placement: the pairs of one (expert, CTA) are neighbours in the list, so the stores fill whole sectors
+    const uint32_t pair0 = r0 * top_k;
+    for (uint32_t i = tid; i < my_pairs; i += CS_THREADS) {
+        const uint32_t e = ex16[i], r = i / top_k;
+        const uint32_t at = e * p.words + (r >> 5);
+        p.list[off[e] + pre[at] + __popc(mask[at] & ((1u << (r & 31)) - 1u))] = pair0 + i;
+    }
+}
+
 namespace {
 
 struct MoeSort : hb_kernel {
     uint32_t experts = 0, top_k = 0, rows_max = 0, bm = 0, staged = 0, use_masks = 0, words = 0, list_staged = 0;
     size_t smem = 0;
+    // the cluster form, when the shape allows it: its mask stride, shared memory and the fallback word
+    uint32_t cl_words = 0, cl_ex_cap = 0;
+    size_t cl_smem = 0;
+    uint32_t* fallback = nullptr;
     int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
         if (na != 3 && na != 4) return fail(ctx, HB_INVALID, name + ": bindings are route, list, tiles[, offsets]");
         if (na == 4 && !range_ok(a[3], ((size_t)experts + 1) * 4)) return fail(ctx, HB_INVALID, name + ": the offsets range is too small");
@@ -259,6 +420,25 @@ struct MoeSort : hb_kernel {
         p.staged = staged;
         p.use_masks = use_masks;
         p.words = words;
+        if (fallback) {
+            ClusterSortParams c{};
+            c.route = p.route;
+            c.list = p.list;
+            c.tiles = p.tiles;
+            c.offsets = p.offsets;
+            c.fallback = fallback;
+            c.rows = m;
+            c.experts = experts;
+            c.top_k = top_k;
+            c.bm = bm;
+            c.rows_per_cta = ((m + CS_CTAS - 1) / CS_CTAS + 31) / 32 * 32;
+            c.words = cl_words;
+            c.ex_cap = cl_ex_cap;
+            moe_sort_cluster_kernel<<<CS_CTAS, CS_THREADS, cl_smem, ctx->stream>>>(c);
+            HB_CUDA(ctx, cudaGetLastError());
+            ctx->launches++;
+            p.only_if = fallback;  // the single-CTA kernel behind it runs only if the cluster gave up
+        }
         moe_sort_kernel<<<1, SORT_THREADS, smem, ctx->stream>>>(p);
         HB_CUDA(ctx, cudaGetLastError());
         ctx->launches++;
@@ -306,6 +486,25 @@ int make_moe_sort(hb_ctx* ctx, uint32_t experts, uint32_t top_k, uint32_t rows_m
     }
     cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(moe_sort_kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin - 1024);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(moe_sort)");
+    // the cluster form: at most CS_THREADS experts (a thread per expert in the scans), at least a few rows per CTA,
+    // and masks of one CTA's rows that fit its shared memory
+    if (experts <= CS_THREADS && rows_max >= 256) {
+        const uint32_t rpc = ((rows_max + CS_CTAS - 1) / CS_CTAS + 31) / 32 * 32;
+        const uint32_t cw = (rpc / 32) | 1u;
+        const size_t ex_cap = ((size_t)rpc * top_k + 7) / 8 * 8;
+        const size_t need = ((size_t)CS_CTAS * experts + CS_CTAS + experts + 64 + 2 * (size_t)experts * cw) * 4 + ex_cap * 2 + 16;
+        if (need <= limit) {
+            void* fb = nullptr;
+            int r = hb_alloc(ctx, 16, &fb);
+            if (r != HB_OK) return r;
+            k->fallback = static_cast<uint32_t*>(fb);
+            k->cl_words = cw;
+            k->cl_ex_cap = (uint32_t)ex_cap;
+            k->cl_smem = need;
+            e = cudaFuncSetAttribute(reinterpret_cast<const void*>(moe_sort_cluster_kernel), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin - 1024);
+            if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(moe_sort cluster)");
+        }
+    }
     *out = intern(ctx, std::move(k));
     return HB_OK;
 }
