@@ -196,17 +196,18 @@ def _two_process_worker(rank, world, port, repo, result):
         a, b = d.shard_gate_up(t16(wgu2), rank, world).cuda(), d.shard_down(t16(wd2), rank, world).cuda()
         be = d.GpuBackend(hb, ctx, rows_max=512)
         y_ref = d.tp_ffn(be, t16(x2).cuda(), a, b, t16(y0).cuda())
-        tp = d.TpPeer(hb, ctx, rank, world, m, h)
-        d.tp_peer_connect(tp)
-        for it in range(3):
-            tp.set_y(t16(y0).cuda())
-            dist.barrier()
-            y = d.tp_ffn_peer(tp, t16(x2).cuda(), a, b, nccl_sync=it == 2)
-            stream.synchronize()
-            ctx.sync()
-            ok = ok and bool(torch.equal(y, y_ref))
-            dist.barrier()
-        tp.close()
+        for push in (False, True):  # the partial pulled by the summing kernel; pushed by the GEMM's epilogue
+            tp = d.TpPeer(hb, ctx, rank, world, m, h, push=push)
+            d.tp_peer_connect(tp)
+            for it in range(3):
+                tp.set_y(t16(y0).cuda())
+                dist.barrier()
+                y = d.tp_ffn_peer(tp, t16(x2).cuda(), a, b, nccl_sync=it == 2)
+                stream.synchronize()
+                ctx.sync()
+                ok = ok and bool(torch.equal(y, y_ref))
+                dist.barrier()
+            tp.close()
     flag = torch.tensor([1 if ok else 0], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
