@@ -16,6 +16,7 @@
 // mode (src/metal/kernels.rs:217-234). Nobody waits for anybody: no spin, only the bounded pipeline waits.
 #include <algorithm>
 #include <cstring>
+#include <vector>
 
 #include "hb_internal.hpp"
 #include "tc05.cuh"
@@ -25,6 +26,13 @@ namespace hb {
 constexpr int SK_THREADS = 192;
 constexpr int SK_MAX_STAGES = 12;
 constexpr int SK_A_BYTES = 128 * 64 * 2;
+constexpr int SK_SEG_CACHE = 32;
+
+// A CTA's piece of work: k-blocks [kb0, kb1) of feature block fb. With nslots > 1 the block is shared: this CTA is
+// contributor number `slot` of `nslots`, in the order of the K ranges.
+struct SkinnySeg {
+    uint32_t fb, kb0, kb1, slot, nslots;
+};
 
 struct SkinnyParams {
     void* y;
@@ -35,15 +43,11 @@ struct SkinnyParams {
     float* scratch;       // balanced: [feat_blocks][maxslots][NACC * NP][128]
     uint32_t* counters;   // balanced: [feat_blocks][4], zero between launches
     uint32_t* status;
+    const uint32_t* seg_start;   // [grid + 1]: where each CTA's segments begin in `segs` (worked out on the host once)
+    const SkinnySeg* segs;
 };
 
-// A CTA's piece of work: k-blocks [kb0, kb1) of feature block fb. With nslots > 1 the block is shared: this CTA is
-// contributor number `slot` of `nslots`, in the order of the K ranges.
-struct SkinnySeg {
-    uint32_t fb, kb0, kb1, slot, nslots;
-};
-
-__device__ __forceinline__ uint32_t skinny_cta_of(uint64_t u, uint64_t units, uint32_t grid) {
+__host__ __device__ __forceinline__ uint32_t skinny_cta_of(uint64_t u, uint64_t units, uint32_t grid) {
     uint32_t c = (uint32_t)(((u + 1) * grid - 1) / units);
     while (c > 0 && (uint64_t)c * units / grid > u) --c;
     while (c + 1 < grid && (uint64_t)(c + 1) * units / grid <= u) ++c;
@@ -51,7 +55,7 @@ __device__ __forceinline__ uint32_t skinny_cta_of(uint64_t u, uint64_t units, ui
 }
 
 // Segment i of CTA `cta`; returns the number of segments (out may be null).
-__device__ __forceinline__ uint32_t skinny_seg(const SkinnyParams& p, uint32_t cta, uint32_t grid, uint32_t i, SkinnySeg* out) {
+__host__ __device__ __forceinline__ uint32_t skinny_seg(const SkinnyParams& p, uint32_t cta, uint32_t grid, uint32_t i, SkinnySeg* out) {
     const uint32_t KB = p.k_blocks;
     if (!p.balanced) {
         const uint32_t n = cta < p.feat_blocks ? (p.feat_blocks - cta + grid - 1) / grid : 0;
@@ -67,7 +71,8 @@ __device__ __forceinline__ uint32_t skinny_seg(const SkinnyParams& p, uint32_t c
         const uint32_t fb = fb0 + i;
         out->fb = fb;
         out->kb0 = i == 0 ? (uint32_t)(u0 - (uint64_t)fb0 * KB) : 0;
-        out->kb1 = (uint32_t)min((uint64_t)KB, u1 - (uint64_t)fb * KB);
+        const uint64_t rest = u1 - (uint64_t)fb * KB;
+        out->kb1 = rest < KB ? (uint32_t)rest : KB;
         const uint32_t c_first = skinny_cta_of((uint64_t)fb * KB, units, grid), c_last = skinny_cta_of((uint64_t)(fb + 1) * KB - 1, units, grid);
         out->slot = cta - c_first;
         out->nslots = c_last - c_first + 1;
@@ -153,7 +158,13 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     tc_fence_after();
     const uint32_t tmem_base = bars.tmem_base;
 
-    const uint32_t n_segs = skinny_seg(p, blockIdx.x, gridDim.x, 0, nullptr);
+    // this CTA's segments: the table was worked out on the host when the kernel object was made (it depends on n, k
+    // and the grid only); the first SK_SEG_CACHE of them are copied to shared memory for the three roles
+    __shared__ SkinnySeg segs_s[SK_SEG_CACHE];
+    const uint32_t seg0 = p.seg_start[blockIdx.x], n_segs = p.seg_start[blockIdx.x + 1] - seg0;
+    if (threadIdx.x < min(n_segs, (uint32_t)SK_SEG_CACHE)) segs_s[threadIdx.x] = p.segs[seg0 + threadIdx.x];
+    __syncthreads();
+    auto seg_at = [&](uint32_t i, SkinnySeg* out) { *out = i < (uint32_t)SK_SEG_CACHE ? segs_s[i] : p.segs[seg0 + i]; };
     griddep_launch_dependents();
 
     if (warp == 0) {
@@ -167,7 +178,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                 uint32_t s = 0, ph = 0, fill = 0;
                 for (uint32_t i = 0; i < n_segs; ++i) {
                     SkinnySeg sg;
-                    skinny_seg(p, blockIdx.x, gridDim.x, i, &sg);
+                    seg_at(i, &sg);
                     const uint32_t fb = sg.fb, kb0 = sg.kb0, kb1 = sg.kb1;
                     const int row_w0 = (int)(fb * 128);
                     const int row_w1 = (int)(p.n_out + fb * 128);  // SWIGLU: the up rows of the same features
@@ -209,7 +220,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             bool ok = true;
             for (; ok && it < n_segs; ++it) {
                 SkinnySeg sg;
-                skinny_seg(p, blockIdx.x, gridDim.x, it, &sg);
+                seg_at(it, &sg);
                 const uint32_t kb0 = sg.kb0, kb1 = sg.kb1;
                 const uint32_t acc = it & 1u, acc_ph = (it >> 1) & 1u;
                 if (!mbar_wait(smem_u32(&bars.tmem_empty[acc]), acc_ph ^ 1u)) {
@@ -252,7 +263,7 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         griddep_wait();  // Y may be read (residual) or still be in use by the kernel before this one
         for (; it < n_segs; ++it) {
             SkinnySeg sg;
-            skinny_seg(p, blockIdx.x, gridDim.x, it, &sg);
+            seg_at(it, &sg);
             const uint32_t fb = sg.fb;
             const uint32_t acc = it & 1u, acc_ph = (it >> 1) & 1u;
             const bool got = mbar_wait(smem_u32(&bars.tmem_full[acc]), acc_ph);
@@ -300,18 +311,35 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             const float* part = p.scratch + (size_t)fb * p.maxslots * (NACC * NP) * 128 + q * 32 + lane;
             // contributor by contributor (the order of the sum), all rows of one at once (independent loads in flight)
             float sg_[NP], su[NACC == 2 ? NP : 1];
-            for (uint32_t ks = 0; ks < sg.nslots; ++ks) {
-                const float* src = part + (size_t)ks * (NACC * NP) * 128;
-                float a[NP], b[NACC == 2 ? NP : 1];
 #pragma unroll
-                for (int j = 0; j < NP; ++j) {
-                    a[j] = (uint32_t)j < p.m ? __ldcg(src + (size_t)j * 128) : 0.f;
-                    if (NACC == 2) b[j] = (uint32_t)j < p.m ? __ldcg(src + (size_t)(NP + j) * 128) : 0.f;
+            for (int j = 0; j < NP; ++j) {
+                sg_[j] = 0.f;
+                if (NACC == 2) su[j] = 0.f;
+            }
+            // contributors in batches: all loads of a batch are in flight together, the additions follow in K order
+            constexpr uint32_t BATCH = NP <= 16 ? 4 : NP <= 32 ? 2 : 1;
+            for (uint32_t k0 = 0; k0 < sg.nslots; k0 += BATCH) {
+                float a[BATCH][NP], b[BATCH][NACC == 2 ? NP : 1];
+#pragma unroll
+                for (uint32_t u = 0; u < BATCH; ++u) {
+                    const bool live = k0 + u < sg.nslots;
+                    const float* src = part + (size_t)(k0 + u) * (NACC * NP) * 128;
+#pragma unroll
+                    for (int j = 0; j < NP; ++j) {
+                        a[u][j] = live && (uint32_t)j < p.m ? __ldcg(src + (size_t)j * 128) : 0.f;
+                        if (NACC == 2) b[u][j] = live && (uint32_t)j < p.m ? __ldcg(src + (size_t)(NP + j) * 128) : 0.f;
+                    }
                 }
 #pragma unroll
-                for (int j = 0; j < NP; ++j) {
-                    sg_[j] = ks == 0 ? a[j] : __fadd_rn(sg_[j], a[j]);
-                    if (NACC == 2) su[j] = ks == 0 ? b[j] : __fadd_rn(su[j], b[j]);
+                for (uint32_t u = 0; u < BATCH; ++u) {
+                    if (k0 + u < sg.nslots) {
+                        const bool first = k0 + u == 0;
+#pragma unroll
+                        for (int j = 0; j < NP; ++j) {
+                            sg_[j] = first ? a[u][j] : __fadd_rn(sg_[j], a[u][j]);
+                            if (NACC == 2) su[j] = first ? b[u][j] : __fadd_rn(su[j], b[u][j]);
+                        }
+                    }
                 }
             }
             if (f < p.n_out) {
@@ -356,6 +384,8 @@ struct SkinnyGemm : hb_kernel {
     size_t smem = 0;
     float* scratch = nullptr;
     uint32_t* counters = nullptr;
+    uint32_t* seg_start = nullptr;
+    SkinnySeg* segs = nullptr;
     const void* last_w = nullptr;
     const void* last_x = nullptr;
     uint32_t last_m = 0;
@@ -386,6 +416,8 @@ struct SkinnyGemm : hb_kernel {
         p.stages = stages;
         p.scratch = scratch;
         p.counters = counters;
+        p.seg_start = seg_start;
+        p.segs = segs;
         p.status = ctx->status_dev;
         const uint32_t grid = balanced ? grid_balanced : std::min<uint32_t>(p.feat_blocks, (uint32_t)ctx->sm_count);
         HB_CUDA(ctx, launch_kernel(ctx, true, fn, dim3(grid), dim3(SK_THREADS), smem, tm_w, tm_x, p));
@@ -412,7 +444,7 @@ int make_matvec_skinny(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out) {
     skinny_fn fn = np == 16 ? skinny_pick_kps<16>(d->out, kps) : np == 32 ? skinny_pick_kps<32>(d->out, kps) : skinny_pick_kps<64>(d->out, kps);
     const uint32_t nacc = d->out == HB_OUT_SWIGLU ? 2 : 1;
     const size_t stage_bytes = ((size_t)nacc * SK_A_BYTES + np * 128) * kps;
-    const size_t budget = std::min<size_t>(ctx->smem_optin, 227 * 1024) - 2048;
+    const size_t budget = std::min<size_t>(ctx->smem_optin, 227 * 1024) - 3072;  // alignment slack, barriers, the segment table
     uint32_t stages = (uint32_t)std::min<size_t>(budget / stage_bytes, SK_MAX_STAGES);
     if (stages < 2) return fail(ctx, HB_UNSUPPORTED, "matvec (tensor core): the pipeline does not fit in shared memory");
     // `persist` caps the pipeline depth: with half the shared memory or less, the CTAs of two kernels that follow one
@@ -455,7 +487,35 @@ int make_matvec_skinny(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out) {
         k->scratch = static_cast<float*>(sc);
         k->counters = static_cast<uint32_t*>(cn);
     }
-    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin - 1024);
+    {   // the segment table: what every CTA of the (fixed) grid works on
+        const uint32_t n_out = d->out == HB_OUT_SWIGLU ? d->n / 2 : d->n;
+        SkinnyParams tp{};
+        tp.k_blocks = k_blocks;
+        tp.feat_blocks = (n_out + 127) / 128;
+        tp.balanced = balanced;
+        const uint32_t grid = balanced ? k->grid_balanced : std::min<uint32_t>(tp.feat_blocks, (uint32_t)ctx->sm_count);
+        std::vector<uint32_t> start(grid + 1, 0);
+        std::vector<SkinnySeg> all;
+        for (uint32_t c = 0; c < grid; ++c) {
+            const uint32_t ns = skinny_seg(tp, c, grid, 0, nullptr);
+            for (uint32_t i = 0; i < ns; ++i) {
+                SkinnySeg sg{};
+                skinny_seg(tp, c, grid, i, &sg);
+                all.push_back(sg);
+            }
+            start[c + 1] = (uint32_t)all.size();
+        }
+        void* ds = nullptr;
+        void* da = nullptr;
+        int r = hb_alloc(ctx, start.size() * 4, &ds);
+        if (r != HB_OK) return r;
+        if ((r = hb_alloc(ctx, std::max<size_t>(all.size(), 1) * sizeof(SkinnySeg), &da)) != HB_OK) return r;
+        if ((r = hb_upload(ctx, ds, start.data(), start.size() * 4)) != HB_OK) return r;
+        if (!all.empty() && (r = hb_upload(ctx, da, all.data(), all.size() * sizeof(SkinnySeg))) != HB_OK) return r;
+        k->seg_start = static_cast<uint32_t*>(ds);
+        k->segs = static_cast<SkinnySeg*>(da);
+    }
+    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin - 2048);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(max dynamic shared memory)");
     // all of the SM's L1/shared array as shared memory, whatever one CTA asks for: with a capped pipeline two CTAs
     // (of two consecutive kernels) must fit side by side
