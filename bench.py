@@ -187,7 +187,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the matvec / MoE / tensor-parallel sections")
     ap.add_argument("--tune", default="", help="engine tune keys, e.g. gemm.auto=0 to skip the load-time timing")
-    ap.add_argument("--form", default="", choices=["", "pair", "sk"], help="with --case gate_up/down: the GEMM form")
+    ap.add_argument("--form", default="", choices=["", "pair", "sk", "one"], help="with --case gate_up/down/layer: the GEMM form (one = one CTA per 128x256 tile)")
     ap.add_argument("--case", default="", choices=["", "layer", "gate_up", "down", "matvec", "matvec8", "moe"],
                     help="run one small case of one kernel a few times and exit (the command profiled under ncu)")
     args = ap.parse_args()
@@ -332,7 +332,7 @@ def main():
     per_gpu_tflops = value / world
     roofline = {
         "bound": "tensor", "achieved": per_gpu_tflops, "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": per_gpu_tflops / pk["bf16_tflops"],
-        "traffic": TRAFFIC_BYTES_PER_LAUNCH if all(v.startswith("gemm_pair_") for v in picks.values()) else None,
+        "traffic": traffic_of(picks),
         "kernel": "gemm_bf16_tn_pair_kernel" if all(v.startswith("gemm_pair_") for v in picks.values()) else "gemm_bf16_tn_kernel / gemm_bf16_tn_pair_kernel", "peak_source": pk["source"] + " (burst cuBLAS bf16)",
         "frac_of_sustained_peak": per_gpu_tflops / pk["bf16_tflops_sustained"], "frac_of_nominal_2250": per_gpu_tflops / 2250.0,
         "algorithmic_flop_per_launch": STEP_FLOP / 4, "launches_per_step": len(ops),
@@ -420,7 +420,7 @@ def run_case(args):
         w, x = rnd(n, k, scale=k**-0.5), rnd(ROWS, k)
         y = rnd(ROWS, n // 2 if out == 3 else n)
         torch.cuda.synchronize()
-        form = {"": {}, "pair": {"cta_pair": 1}, "sk": {"stream_k": 1}}[args.form]
+        form = {"": {}, "one": {}, "pair": {"cta_pair": 1}, "sk": {"stream_k": 1}}[args.form]
         kern = ctx.gemm(k, n, out, rows_max=ROWS, **form)
         ops = [(kern, ROWS, wrap(w), wrap(x), wrap(y))]
         work = {"flop": 2.0 * ROWS * k * n}
@@ -430,7 +430,8 @@ def run_case(args):
         x, hmid = rnd(ROWS, HIDDEN), rnd(ROWS, INTER)
         qkv, resid = rnd(ROWS, 6144), rnd(ROWS, HIDDEN)
         torch.cuda.synchronize()
-        ks = [ctx.gemm(k, n, out, rows_max=ROWS, cta_pair=1) for _, k, n, out in LAYER]
+        form = {"": {"cta_pair": 1}, "pair": {"cta_pair": 1}, "sk": {"stream_k": 1}, "one": {}}[args.form]
+        ks = [ctx.gemm(k, n, out, rows_max=ROWS, **form) for _, k, n, out in LAYER]
         ops = [(ks[0], ROWS, wrap(ws[0]), wrap(x), wrap(qkv)), (ks[1], ROWS, wrap(ws[1]), wrap(x), wrap(resid)),
                (ks[2], ROWS, wrap(ws[2]), wrap(x), wrap(hmid)), (ks[3], ROWS, wrap(ws[3]), wrap(hmid), wrap(resid))]
         work = {"flop": STEP_FLOP}
@@ -471,9 +472,21 @@ def run_case(args):
     ctx.close()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the CTA-pair GEMM kernel, averaged over the four launches
-# of a step (72.3, 70.0, 257.8 and 236.4 MB), from the ncu capture summarised in profiles/.
-TRAFFIC_BYTES_PER_LAUNCH = 159.1e6
+# dram__bytes_read.sum + dram__bytes_write.sum per launch (MB) of each projection of the step, from the ncu captures
+# summarised in profiles/: the CTA-pair kernel and the one-CTA 128x256 kernel. `roofline.traffic` is the mean over the
+# four launches of the forms the selection picked (None when a pick has no capture).
+TRAFFIC_MB = {"gemm_pair": {"qkv": 72.3, "o_proj": 70.0, "gate_up": 257.8, "down": 236.4},
+              "gemm_tc_t128x256": {"qkv": 71.8, "o_proj": 67.5, "gate_up": 252.1, "down": 232.4}}
+
+
+def traffic_of(picks):
+    total = 0.0
+    for name, kernel in picks.items():
+        form = "gemm_pair" if kernel.startswith("gemm_pair_") else "gemm_tc_t128x256" if kernel.startswith("gemm_tc_") and "_t128x256_" in kernel else None
+        if form is None or name not in TRAFFIC_MB[form]:
+            return None
+        total += TRAFFIC_MB[form][name]
+    return total / len(picks) * 1e6
 
 
 def bench_extra(hb, ctx, sel, torch, dev, wrap, pk, rank, world, barrier, max_over_ranks):
