@@ -535,6 +535,34 @@ def bench_extra(hb, ctx, sel, torch, dev, wrap, pk, rank, world, barrier, max_ov
         bytes_ = 2.0 * (n2 * k + m * k + m * n2)
         mv2[f"m{m}"] = {"us": sec * 1e6, "gbs": bytes_ / sec / 1e9, "frac_hbm": bytes_ / sec / 1e9 / pk["hbm_gbs"], "form": kern.name}
     out["matvec_4096x151936"] = mv2
+    # the same product from Q4_0 weights (4.5 bits per weight: 16 bytes of nibbles and an f16 scale per 32 weights; any
+    # bytes are valid nibbles, so the synthetic weights are random bytes and small random scales)
+    try:
+        q4 = {}
+        for nq in (12288, n2):
+            blocks = nq * k // 32
+            copies_q = 6 if nq == 12288 else 1
+            wq = [torch.randint(0, 256, (blocks * 16,), device=dev, dtype=torch.uint8, generator=g) for _ in range(copies_q)]
+            sq = (torch.rand(blocks, device=dev, generator=g) * 0.01 + 0.001).half()
+            yq = torch.zeros(nq, device=dev, dtype=torch.bfloat16)
+            best = None
+            for rows in (1, 2, 4):
+                kq = ctx.matvec_q4(k, nq, 0, rows)
+                ops_q = [(kq, 1, wrap(w_), wrap(xs), wrap(yq), wrap(sq)) for w_ in wq]
+                gr = ctx.record(ops_q)
+                gr.time(3)
+                barrier()
+                sec_q = max_over_ranks(gr.time(20) / (20 * copies_q))
+                gr.free()
+                if best is None or sec_q < best[0]:
+                    best = (sec_q, kq.name)
+            qbytes = blocks * 18.0 + 2.0 * k + 2.0 * nq
+            q4[f"n{nq}"] = {"us": best[0] * 1e6, "gbs": qbytes / best[0] / 1e9, "frac_hbm": qbytes / best[0] / 1e9 / pk["hbm_gbs"], "form": best[1],
+                            "bf16_equivalent_gbs": 2.0 * nq * k / best[0] / 1e9}
+            del wq, sq
+        out["matvec_q4_4096"] = q4
+    except Exception as e:
+        out["q4_error"] = repr(e)
     # the LM head with the greedy pick: projection + argmax as two kernels, and the projection that folds the argmax in
     idx = torch.zeros(8, device=dev, dtype=torch.int32)
     form = dict(rows_per_warp=2, split=2)

@@ -1,0 +1,232 @@
+// Q4_0 weights (reference src/metal/q4.rs:7-24): per block of 32 weights along k one 16-byte group of nibbles and one
+// f16 scale d, w = d * q with q in -8..7 (two's complement nibble; byte b of word i holds weight 8i + b low and
+// 8i + 4 + b high). 4.5 bits per weight: the decode product streams 3.6 times fewer bytes than bf16.
+//   dequant_q4  (src/metal/kernels.rs:1074-1102): W as bf16 [n][k], each value bf16(d * q) - what the reference's
+//               prefill GEMM stages from Q4 weights (prefill.rs:1058-1076), so dequant + the bf16 GEMM gives its bits.
+//   matvec_q4   (src/metal/kernels.rs:526-632): y = out(W . x), one activation row. A warp per R rows of W, the lanes
+//               stride over the blocks; per block an FMA chain of q * x in the reference's element order, then
+//               acc = fma(d, part, acc); the lanes summed by the xor butterfly: the reference's bits.
+// The nibbles become floats without an integer-to-float conversion: a byte b placed in the low byte of 0x4B000000
+// is the float 8388608 + b, so (that) - 8388616 is exactly (b ^ 8's value) - 8 once the bytes were xored with 8.
+#include <algorithm>
+
+#include <cuda_fp16.h>
+
+#include "hb_internal.hpp"
+#include "tc05.cuh"
+
+namespace hb {
+
+__device__ __forceinline__ float q4_byte_to_q(uint32_t bytes, uint32_t sel) {
+    // byte `sel` of `bytes` (a nibble xor 8, 0..15) -> that value minus 8, exactly
+    return __uint_as_float(__byte_perm(bytes, 0x4B000000u, 0x7650u + sel)) - 8388616.0f;
+}
+
+__global__ void __launch_bounds__(256) dequant_q4_kernel(const uint4* __restrict__ w, const uint16_t* __restrict__ sc, uint4* __restrict__ out, uint32_t blocks) {
+    for (uint32_t g = blockIdx.x * blockDim.x + threadIdx.x; g < blocks; g += gridDim.x * blockDim.x) {
+        const uint4 wv = w[g];
+        const float d = __half2float(__ushort_as_half(sc[g]));
+        const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const uint32_t lo = (ww[i] & 0x0F0F0F0Fu) ^ 0x08080808u, hi = ((ww[i] >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;
+            uint32_t o[4];
+            // weights 8i + 0..3 are the low nibbles of bytes 0..3, weights 8i + 4..7 the high ones
+            o[0] = f32x2_to_bf16x2(__fmul_rn(d, q4_byte_to_q(lo, 0)), __fmul_rn(d, q4_byte_to_q(lo, 1)));
+            o[1] = f32x2_to_bf16x2(__fmul_rn(d, q4_byte_to_q(lo, 2)), __fmul_rn(d, q4_byte_to_q(lo, 3)));
+            o[2] = f32x2_to_bf16x2(__fmul_rn(d, q4_byte_to_q(hi, 0)), __fmul_rn(d, q4_byte_to_q(hi, 1)));
+            o[3] = f32x2_to_bf16x2(__fmul_rn(d, q4_byte_to_q(hi, 2)), __fmul_rn(d, q4_byte_to_q(hi, 3)));
+            out[(size_t)g * 4 + i] = make_uint4(o[0], o[1], o[2], o[3]);
+        }
+    }
+}
+
+struct MatvecQ4Params {
+    const uint4* w;
+    const uint16_t* sc;
+    const uint4* x;
+    void* y;
+    uint32_t n, nblk, groups;
+};
+
+constexpr int Q4_THREADS = 256;
+constexpr int Q4_WARPS = Q4_THREADS / 32;
+
+template <int R, int OUT>
+__global__ void __launch_bounds__(Q4_THREADS) matvec_q4_kernel(const MatvecQ4Params p) {
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    griddep_launch_dependents();
+    griddep_wait();  // x comes from the kernel before this one
+    for (uint32_t group = blockIdx.x * Q4_WARPS + warp; group < p.groups; group += gridDim.x * Q4_WARPS) {
+        size_t base[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) base[r] = (size_t)min(group * R + r, p.n - 1) * p.nblk;  // rows past the end read the last row
+        float acc[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) acc[r] = 0.f;
+        for (uint32_t b = lane; b < p.nblk; b += 32) {
+            uint4 wv[R];
+            uint16_t dh[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                wv[r] = __ldcs(p.w + base[r] + b);
+                dh[r] = __ldcs(p.sc + base[r] + b);
+            }
+            // the 32 activations of the block, in order
+            float xs[32];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint4 xv = __ldg(p.x + (size_t)b * 4 + i);
+                const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    xs[8 * i + 2 * c] = __uint_as_float(xw[c] << 16);
+                    xs[8 * i + 2 * c + 1] = __uint_as_float(xw[c] & 0xffff0000u);
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const uint32_t ww[4] = {wv[r].x, wv[r].y, wv[r].z, wv[r].w};
+                float part = 0.f;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint32_t lo = (ww[i] & 0x0F0F0F0Fu) ^ 0x08080808u, hi = ((ww[i] >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;
+#pragma unroll
+                    for (int byte = 0; byte < 4; ++byte) {  // the reference's order: weight 8i + byte, then 8i + 4 + byte
+                        part = __fmaf_rn(q4_byte_to_q(lo, byte), xs[8 * i + byte], part);
+                        part = __fmaf_rn(q4_byte_to_q(hi, byte), xs[8 * i + 4 + byte], part);
+                    }
+                }
+                acc[r] = __fmaf_rn(__half2float(__ushort_as_half(dh[r])), part, acc[r]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            float a = acc[r];
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, off));
+            const uint32_t row = group * R + r;
+            if (lane == 0 && row < p.n) {
+                if constexpr (OUT == HB_OUT_F32) reinterpret_cast<float*>(p.y)[row] = a;
+                else if constexpr (OUT == HB_OUT_BF16) reinterpret_cast<uint16_t*>(p.y)[row] = (uint16_t)f32_to_bf16(a);
+                else {
+                    uint16_t* y = reinterpret_cast<uint16_t*>(p.y) + row;
+                    *y = (uint16_t)f32_to_bf16(__fadd_rn(bf16_to_f32(*y), round_bf16(a)));
+                }
+            }
+        }
+    }
+}
+
+namespace {
+
+struct DequantQ4 : hb_kernel {
+    uint32_t k = 0, n = 0;
+    int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
+        (void)m;
+        if (na != 3) return fail(ctx, HB_INVALID, name + ": bindings are W (nibbles), scales (f16), out (bf16)");
+        const size_t blocks = (size_t)n * (k / 32);
+        if (!range_ok(a[0], blocks * 16) || !range_ok(a[1], blocks * 2) || !range_ok(a[2], blocks * 64)) return fail(ctx, HB_INVALID, name + ": a bound range is too small");
+        if ((reinterpret_cast<uintptr_t>(a[0].ptr) | reinterpret_cast<uintptr_t>(a[2].ptr)) & 15u) return fail(ctx, HB_INVALID, name + ": W and out must be 16-byte aligned");
+        const uint32_t grid = (uint32_t)std::max<size_t>(1, std::min<size_t>((blocks + 255) / 256, (size_t)ctx->sm_count * 16));
+        dequant_q4_kernel<<<grid, 256, 0, ctx->stream>>>(static_cast<const uint4*>(a[0].ptr), static_cast<const uint16_t*>(a[1].ptr), static_cast<uint4*>(a[2].ptr), (uint32_t)blocks);
+        HB_CUDA(ctx, cudaGetLastError());
+        ctx->launches++;
+        return HB_OK;
+    }
+};
+
+typedef void (*q4_fn)(const MatvecQ4Params);
+
+template <int R>
+q4_fn q4_out(uint32_t out) {
+    switch (out) {
+        case HB_OUT_BF16: return matvec_q4_kernel<R, HB_OUT_BF16>;
+        case HB_OUT_F32: return matvec_q4_kernel<R, HB_OUT_F32>;
+        case HB_OUT_RESIDUAL: return matvec_q4_kernel<R, HB_OUT_RESIDUAL>;
+    }
+    return nullptr;
+}
+
+struct MatvecQ4 : hb_kernel {
+    uint32_t k = 0, n = 0, out = 0, rows = 0;
+    q4_fn fn = nullptr;
+    int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
+        if (na != 4) return fail(ctx, HB_INVALID, name + ": bindings are W (nibbles), x, y, scales (f16)");
+        if (m != 1) return fail(ctx, HB_INVALID, name + ": one activation row");
+        const size_t blocks = (size_t)n * (k / 32);
+        if (!range_ok(a[0], blocks * 16) || !range_ok(a[1], (size_t)k * 2) || !range_ok(a[2], (size_t)n * (out == HB_OUT_F32 ? 4 : 2)) || !range_ok(a[3], blocks * 2))
+            return fail(ctx, HB_INVALID, name + ": a bound range is too small");
+        if ((reinterpret_cast<uintptr_t>(a[0].ptr) | reinterpret_cast<uintptr_t>(a[1].ptr)) & 15u) return fail(ctx, HB_INVALID, name + ": W and x must be 16-byte aligned");
+        MatvecQ4Params p{};
+        p.w = static_cast<const uint4*>(a[0].ptr);
+        p.x = static_cast<const uint4*>(a[1].ptr);
+        p.y = a[2].ptr;
+        p.sc = static_cast<const uint16_t*>(a[3].ptr);
+        p.n = n;
+        p.nblk = k / 32;
+        p.groups = (n + rows - 1) / rows;
+        const uint32_t grid = std::max(1u, std::min<uint32_t>((p.groups + Q4_WARPS - 1) / Q4_WARPS, (uint32_t)ctx->sm_count * 8));
+        HB_CUDA(ctx, launch_kernel(ctx, true, fn, dim3(grid), dim3(Q4_THREADS), 0, p));
+        ctx->launches++;
+        return HB_OK;
+    }
+};
+
+}  // namespace
+
+int make_dequant_q4(hb_ctx* ctx, uint32_t k, uint32_t n, hb_kernel** out) {
+    *out = nullptr;
+    if (k == 0 || n == 0 || k % 32 != 0) return fail(ctx, HB_UNSUPPORTED, "Q4: K = " + std::to_string(k) + " is not a multiple of 32");
+    auto kn = std::make_unique<DequantQ4>();
+    kn->k = k;
+    kn->n = n;
+    kn->kind = 19;
+    kn->nargs = 3;
+    kn->name = "dequant_q4_" + std::to_string(k) + "x" + std::to_string(n);
+    *out = intern(ctx, std::move(kn));
+    return HB_OK;
+}
+
+int make_matvec_q4(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t out_mode, uint32_t rows, hb_kernel** out) {
+    *out = nullptr;
+    if (k == 0 || n == 0 || k % 32 != 0) return fail(ctx, HB_UNSUPPORTED, "Q4: K = " + std::to_string(k) + " is not a multiple of 32");
+    if (rows == 0) rows = 2;
+    q4_fn fn = rows == 1 ? q4_out<1>(out_mode) : rows == 2 ? q4_out<2>(out_mode) : rows == 4 ? q4_out<4>(out_mode) : nullptr;
+    if (!fn) return fail(ctx, HB_UNSUPPORTED, "matvec_q4: rows per warp 1, 2 or 4; output Bf16, F32 or Residual");
+    auto kn = std::make_unique<MatvecQ4>();
+    kn->k = k;
+    kn->n = n;
+    kn->out = out_mode;
+    kn->rows = rows;
+    kn->fn = fn;
+    kn->kind = 20;
+    kn->nargs = 4;
+    kn->name = "matvec_q4_" + std::to_string(k) + "x" + std::to_string(n) + "_" + out_tag(out_mode) + "_r" + std::to_string(rows);
+    *out = intern(ctx, std::move(kn));
+    return HB_OK;
+}
+
+}  // namespace hb
+
+extern "C" {
+
+int hb_dequant_q4_get(hb_ctx* ctx, uint32_t k, uint32_t n, hb_kernel** out) {
+    if (!ctx || !out) return hb::fail(ctx, HB_INVALID, "hb_dequant_q4_get: bad argument");
+    try {
+        return hb::make_dequant_q4(ctx, k, n, out);
+    } catch (const std::exception& e) {
+        return hb::fail(ctx, HB_BACKEND, e.what());
+    }
+}
+
+int hb_matvec_q4_get(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t out_mode, uint32_t rows_per_warp, hb_kernel** out) {
+    if (!ctx || !out) return hb::fail(ctx, HB_INVALID, "hb_matvec_q4_get: bad argument");
+    try {
+        return hb::make_matvec_q4(ctx, k, n, out_mode, rows_per_warp, out);
+    } catch (const std::exception& e) {
+        return hb::fail(ctx, HB_BACKEND, e.what());
+    }
+}
+
+}  // extern "C"

@@ -240,6 +240,15 @@ int hb_argmax_get(hb_ctx* ctx, uint32_t n, uint32_t rows_max, hb_kernel** out);
  * x = bf16(x + bf16(experts + bf16(g * shared))), in place. Bindings xn, gate (bf16 [d]), experts, shared, x. */
 int hb_moe_out_get(hb_ctx* ctx, uint32_t d, hb_kernel** out);
 
+/* ---- Q4_0 weights (src/metal/q4.rs:7-24: per block of 32 weights 16 bytes of nibbles + an f16 scale) ----
+ * dequant_q4, src/metal/kernels.rs:1074-1102: W as bf16 [n][k], every value bf16(d * q); what the reference's prefill
+ * GEMM stages from Q4 weights (prefill.rs:1058-1076), so this kernel followed by hb_gemm_get gives its bits.
+ * Bindings W (nibbles, n*k/2 bytes), scales (f16, n*k/32), out (bf16 [n][k]); m is ignored. */
+int hb_dequant_q4_get(hb_ctx* ctx, uint32_t k, uint32_t n, hb_kernel** out);
+/* matvec_q4, src/metal/kernels.rs:444-632: y = out(W . x) for one activation row, the sums in the reference's order
+ * (bit-exact). rows_per_warp 1, 2 or 4 (0 = 2); out BF16, F32 or RESIDUAL. Bindings W, x, y, scales as there. */
+int hb_matvec_q4_get(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t out, uint32_t rows_per_warp, hb_kernel** res);
+
 /* ---- expert-parallel exchange over peer memory (no reference counterpart: the reference runs on one GPU) ----
  * Experts are partitioned contiguously over `world` ranks, the token rows are each rank's own. A rank sorts its
  * (row, slot) pairs by global expert with hb_moe_sort_get, binding a fourth range `offsets` u32[experts + 1] (first

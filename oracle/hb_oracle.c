@@ -478,6 +478,107 @@ void hbo_moe_out(const uint16_t* xn, const uint16_t* gate, const uint16_t* exper
     }
 }
 
+/* ------------------------------------------------------------- Q4_0 weights */
+
+static inline float f16_bits_to_f32(uint16_t h) {
+    _Float16 v;
+    memcpy(&v, &h, 2);
+    return (float)v;
+}
+static inline uint16_t f32_to_f16_bits(float f) {
+    _Float16 v = (_Float16)f; /* round to nearest even */
+    uint16_t h;
+    memcpy(&h, &v, 2);
+    return h;
+}
+
+void hbo_q4_quantize(const uint16_t* w, int n, int k, uint8_t* data, uint16_t* scales) {
+    static const int cands[15] = {-8, 7, -7, 6, -6, 5, -5, 4, -4, 3, -3, 2, -2, 1, -1};
+    const int nblk = k / 32;
+#pragma omp parallel for schedule(static)
+    for (long blk = 0; blk < (long)n * nblk; ++blk) {
+        float v[32];
+        float m = 0.0f;
+        for (int i = 0; i < 32; ++i) {
+            v[i] = hbo_bf16_to_f32(w[(size_t)blk * 32 + i]);
+            if (fabsf(v[i]) > fabsf(m)) m = v[i];
+        }
+        uint8_t q[32], best_q[32];
+        double best_e = INFINITY;
+        uint16_t best_d = 0;
+        if (m != 0.0f) {
+            for (int ci = 0; ci < 15; ++ci) {
+                uint16_t dh = f32_to_f16_bits(m / (float)cands[ci]);
+                float dq = f16_bits_to_f32(dh);
+                if (dq == 0.0f || !isfinite(dq)) continue;
+                float inv = 1.0f / dq;
+                double e = 0.0;
+                for (int i = 0; i < 32; ++i) {
+                    float qi = roundf(v[i] * inv); /* half away from zero, as f32::round */
+                    qi = qi < -8.0f ? -8.0f : qi > 7.0f ? 7.0f : qi;
+                    q[i] = (uint8_t)((int)qi + 8);
+                    double r = (double)(v[i] - dq * qi);
+                    e += r * r;
+                }
+                if (e < best_e) {
+                    best_e = e;
+                    best_d = dh;
+                    memcpy(best_q, q, 32);
+                }
+            }
+        } else {
+            best_e = 0.0;
+            memset(best_q, 8, 32);
+        }
+        if (!isfinite(best_e)) memset(best_q, 8, 32); /* every candidate scale rounds to 0 in f16: zeros */
+        for (int i = 0; i < 4; ++i)
+            for (int b = 0; b < 4; ++b)
+                data[(size_t)blk * 16 + 4 * i + b] = (uint8_t)(((best_q[8 * i + b] ^ 8) & 15) | (((best_q[8 * i + 4 + b] ^ 8) & 15) << 4));
+        scales[blk] = best_d;
+    }
+}
+
+/* weight e of a block: the nibble, two's complement */
+static inline float q4_weight(const uint8_t* blk, int e) {
+    int i = e / 8, j = e % 8;
+    uint8_t byte = blk[4 * i + (j % 4)];
+    uint8_t nib = j < 4 ? (byte & 15) : (byte >> 4);
+    return (float)(nib ^ 8) - 8.0f;
+}
+
+void hbo_q4_dequant(const uint8_t* data, const uint16_t* scales, int n, int k, uint16_t* out) {
+    const long nblk = (long)n * (k / 32);
+#pragma omp parallel for schedule(static)
+    for (long blk = 0; blk < nblk; ++blk) {
+        float d = f16_bits_to_f32(scales[blk]);
+        for (int e = 0; e < 32; ++e) out[(size_t)blk * 32 + e] = hbo_f32_to_bf16(d * q4_weight(data + (size_t)blk * 16, e));
+    }
+}
+
+void hbo_matvec_q4(const uint8_t* data, const uint16_t* scales, const uint16_t* x, void* y, int n, int k, int out) {
+    const int nblk = k / 32;
+#pragma omp parallel for schedule(static)
+    for (int row = 0; row < n; ++row) {
+        float lane[32];
+        for (int l = 0; l < 32; ++l) {
+            float acc = 0.0f;
+            for (int b = l; b < nblk; b += 32) {
+                const uint8_t* blk = data + ((size_t)row * nblk + b) * 16;
+                float part = 0.0f;
+                for (int i = 0; i < 4; ++i)
+                    for (int byte = 0; byte < 4; ++byte) {
+                        int e0 = 8 * i + byte, e1 = 8 * i + 4 + byte;
+                        part = fmaf(q4_weight(blk, e0), hbo_bf16_to_f32(x[b * 32 + e0]), part);
+                        part = fmaf(q4_weight(blk, e1), hbo_bf16_to_f32(x[b * 32 + e1]), part);
+                    }
+                acc = fmaf(f16_bits_to_f32(scales[(size_t)row * nblk + b]), part, acc);
+            }
+            lane[l] = acc;
+        }
+        store_out(y, (size_t)row, butterfly_sum32(lane), out);
+    }
+}
+
 /* -------------------------------------------------------------------- check */
 
 int hbo_check_1_64(const void* ref, const void* got, size_t count, int f32_out, float* err_out, float* scale_out) {

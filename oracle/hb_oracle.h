@@ -102,6 +102,19 @@ void hbo_argmax_rows(const uint16_t* logits, uint32_t* idx, int rows, int n);
  * rmsnorm_rows; x = bf16(x + bf16(experts + bf16(g * shared))), in place. */
 void hbo_moe_out(const uint16_t* xn, const uint16_t* gate, const uint16_t* experts, const uint16_t* shared, uint16_t* x, int rows, int d);
 
+/* ---- Q4_0 weights -------------------------------------------------------- */
+/* src/metal/q4.rs:16-103 (quantize): W [n][k] bf16 -> per block of 32 along k a 16-byte word group and an f16 scale.
+ * Byte b of word i of a block holds weight 8i + b in its low nibble and 8i + 4 + b in its high one, two's complement
+ * (q in -8..7); d is the candidate m / c (m the value of largest magnitude, c in -8, 7, -7, ... -1 in that order) with
+ * the least squared error, the first on a tie. data: n*k/2 bytes, scales: n*k/32 f16 bit patterns. */
+void hbo_q4_quantize(const uint16_t* w, int n, int k, uint8_t* data, uint16_t* scales);
+/* src/metal/kernels.rs:1074-1102, 1425-1450 (dequant_q4, q4_word_bf16): out[n][k] = bf16(d * q). */
+void hbo_q4_dequant(const uint8_t* data, const uint16_t* scales, int n, int k, uint16_t* out);
+/* src/metal/kernels.rs:526-632 (matvec_q4, rows = 1): lane l of 32 takes blocks l, l + 32, ...; per block an FMA chain
+ * part = fma(q_e, x_e, part) over e in the order 8i + b, 8i + 4 + b (i, b = 0..3), then acc = fma(d, part, acc); the
+ * lanes are summed by the xor butterfly; the output mode as for the matvec (y holds the old values for RESIDUAL). */
+void hbo_matvec_q4(const uint8_t* data, const uint16_t* scales, const uint16_t* x, void* y, int n, int k, int out);
+
 /* ---- the selection loop's correctness rule ----------------------------- */
 /* qwen.rs:2497-2543: scale = max(max|ref|,1e-6); err = max|ref-got|;
  * returns 1 (eligible) iff err <= scale/64 (NaN fails). f32_out selects the

@@ -342,6 +342,85 @@ def moe_out(xn, gate, experts, shared, x):
     return out
 
 
+def q4_quantize(w):
+    """q4.rs:16-103 restated: (data bytes [n*k/2], f16 scale bits [n*k/32])."""
+    f = np.float32
+    n, k = w.shape
+    data = np.zeros(n * k // 2, dtype=np.uint8)
+    scales = np.zeros(n * k // 32, dtype=np.uint16)
+    flat = w.reshape(-1)
+    for blk in range(n * k // 32):
+        v = [widen(h) for h in flat[32 * blk : 32 * blk + 32]]
+        m = f(0.0)
+        for x in v:
+            if abs(x) > abs(m):
+                m = x
+        best_e, best_d, best_q = float("inf"), 0, [8] * 32
+        if m != 0.0:
+            for c in (-8, 7, -7, 6, -6, 5, -5, 4, -4, 3, -3, 2, -2, 1, -1):
+                dh = np.float16(f(m / f(c)))
+                dq = f(dh)
+                if dq == 0.0 or not np.isfinite(dq):
+                    continue
+                inv = f(f(1.0) / dq)
+                e, q = 0.0, []
+                for x in v:
+                    t = f(x * inv)
+                    qi = float(np.sign(t) * np.floor(abs(float(t)) + 0.5))  # half away from zero
+                    qi = max(-8.0, min(7.0, qi))
+                    q.append(int(qi) + 8)
+                    r = float(f(x - f(dq * f(qi))))
+                    e += r * r
+                if e < best_e:
+                    best_e, best_d, best_q = e, int(dh.view(np.uint16)), q
+        else:
+            best_e = 0.0
+        for i in range(4):
+            for b in range(4):
+                data[16 * blk + 4 * i + b] = ((best_q[8 * i + b] ^ 8) & 15) | (((best_q[8 * i + 4 + b] ^ 8) & 15) << 4)
+        scales[blk] = best_d
+    return data, scales
+
+
+def q4_value(data, blk, e):
+    i, j = e // 8, e % 8
+    byte = int(data[16 * blk + 4 * i + (j % 4)])
+    nib = (byte & 15) if j < 4 else (byte >> 4)
+    return np.float32((nib ^ 8) - 8)
+
+
+def q4_dequant(data, scales, n, k):
+    f = np.float32
+    out = np.zeros(n * k, dtype=np.uint16)
+    for blk in range(n * k // 32):
+        d = f(np.uint16(scales[blk]).view(np.float16))
+        for e in range(32):
+            out[32 * blk + e] = rne_bf16(f(d * q4_value(data, blk, e)))
+    return out.reshape(n, k)
+
+
+def q4_matvec(data, scales, x, n, k):
+    """kernels.rs:526-632 (rows = 1): lanes over blocks, FMA chains in the reference's element order, butterfly."""
+    f = np.float32
+    nblk = k // 32
+    out = np.zeros(n, dtype=np.uint16)
+    for row in range(n):
+        lanes = []
+        for lane in range(32):
+            acc = f(0.0)
+            for b in range(lane, nblk, 32):
+                blk = row * nblk + b
+                part = f(0.0)
+                for i in range(4):
+                    for byte in range(4):
+                        for e in (8 * i + byte, 8 * i + 4 + byte):
+                            part = fma_f32(q4_value(data, blk, e), widen(x[32 * b + e]), part)
+                acc = fma_f32(f(np.uint16(scales[blk]).view(np.float16)), part, acc)
+            lanes.append(acc)
+        out[row] = rne_bf16(butterfly_sum(lanes))
+    return out
+
+
 def main():
     g = {}
     # RNE known answers: (f32 bits, bf16 bits) - ties to even, carries, signed zero, subnormal, infinity.
@@ -423,6 +502,18 @@ def main():
     mg = fill_normal(d, 0x2545F491, 29, d ** -0.5)
     g["moe_out_xn"], g["moe_out_experts"], g["moe_out_shared"], g["moe_out_x"], g["moe_out_gate"] = mo[0], mo[1], mo[2], mo[3], mg
     g["moe_out_out"] = moe_out(mo[0], mg, mo[1], mo[2], mo[3])
+    # Q4_0: quantise a small matrix (one block on an exact grid, one all-zero block), decode it, multiply by a vector
+    qn, qk = 5, 96
+    qw = fill_normal(qn * qk, 0x2545F491, 31, 0.05).reshape(qn, qk)
+    grid = [rne_bf16(np.float32((i * 7 % 16 - 8) / 64.0)) for i in range(32)]
+    qw[1, 0:32] = np.array(grid, dtype=np.uint16)
+    qw[2, 32:64] = 0
+    qd, qs = q4_quantize(qw)
+    g["q4_w"], g["q4_data"], g["q4_scales"] = qw, qd, qs
+    g["q4_dequant"] = q4_dequant(qd, qs, qn, qk)
+    assert np.array_equal(g["q4_dequant"][1, 0:32], qw[1, 0:32]) and not g["q4_dequant"][2, 32:64].any()
+    qx = fill_normal(qk, 0x9E3779B9, 32, 1.0)
+    g["q4_x"], g["q4_matvec"] = qx, q4_matvec(qd, qs, qx, qn, qk)
     np.savez_compressed(os.path.join(HERE, "golden.npz"), **g)
     print("wrote", os.path.join(HERE, "golden.npz"), "with", len(g), "arrays")
 

@@ -86,6 +86,13 @@ def load(native: bool = False) -> C.CDLL:
     lib.hbo_argmax_rows.argtypes = [_u16p, _u32p, C.c_int, C.c_int]
     lib.hbo_moe_out.restype = None
     lib.hbo_moe_out.argtypes = [_u16p, _u16p, _u16p, _u16p, _u16p, C.c_int, C.c_int]
+    _u8p = np.ctypeslib.ndpointer(dtype=np.uint8, flags="C_CONTIGUOUS")
+    lib.hbo_q4_quantize.restype = None
+    lib.hbo_q4_quantize.argtypes = [_u16p, C.c_int, C.c_int, _u8p, _u16p]
+    lib.hbo_q4_dequant.restype = None
+    lib.hbo_q4_dequant.argtypes = [_u8p, _u16p, C.c_int, C.c_int, _u16p]
+    lib.hbo_matvec_q4.restype = None
+    lib.hbo_matvec_q4.argtypes = [_u8p, _u16p, _u16p, C.c_void_p, C.c_int, C.c_int, C.c_int]
     lib.hbo_check_1_64.restype = C.c_int
     lib.hbo_check_1_64.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_float)]
     lib.hbo_fill_normal.restype = None
@@ -236,6 +243,24 @@ class Oracle:
         out = np.ascontiguousarray(x).copy()
         self.lib.hbo_moe_out(np.ascontiguousarray(xn), np.ascontiguousarray(gate), np.ascontiguousarray(experts), np.ascontiguousarray(shared), out, rows, d)
         return out
+
+    def q4_quantize(self, w):
+        """(data uint8 [n*k/2], scales f16 bits uint16 [n*k/32]) of W [n][k] bf16 (reference src/metal/q4.rs)."""
+        n, k = w.shape
+        data = np.zeros(n * k // 2, dtype=np.uint8)
+        scales = np.zeros(n * k // 32, dtype=np.uint16)
+        self.lib.hbo_q4_quantize(np.ascontiguousarray(w), n, k, data, scales)
+        return data, scales
+
+    def q4_dequant(self, data, scales, n, k):
+        out = np.zeros((n, k), dtype=np.uint16)
+        self.lib.hbo_q4_dequant(data, scales, n, k, out)
+        return out
+
+    def matvec_q4(self, data, scales, x, n, k, out=OUT_BF16, y0=None):
+        y = np.zeros(n, dtype=np.float32 if out == OUT_F32 else np.uint16) if y0 is None else np.ascontiguousarray(y0).copy()
+        self.lib.hbo_matvec_q4(data, scales, np.ascontiguousarray(x), y.ctypes.data, n, k, out)
+        return y
 
     def check_1_64(self, ref, got):
         f32_out = ref.dtype == np.float32

@@ -1,0 +1,84 @@
+"""Q4_0 weights: the decode kernel and the Q4 matvec, bit-exact with the oracle (itself pinned to the independent
+restatement in tests/golden and to the reference's own unit test: a block on the grid comes back exactly)."""
+import numpy as np
+import pytest
+
+from gpu_util import within_contract
+from oracle_lib import OUT_BF16, OUT_F32, OUT_RESIDUAL
+
+pytestmark = pytest.mark.gpu
+G = np.load(__import__("os").path.join(__import__("os").path.dirname(__file__), "golden", "golden.npz"))
+
+
+def test_dequant_golden_and_model_shapes(ctx, oracle):
+    n, k = G["q4_w"].shape
+    d_w, d_s, d_o = ctx.to_device(G["q4_data"]), ctx.to_device(G["q4_scales"]), ctx.alloc(n * k * 2)
+    ctx.dequant_q4(k, n)(1, d_w, d_s, d_o)
+    ctx.sync()
+    assert np.array_equal(d_o.download(np.uint16, (n, k)), G["q4_dequant"])
+    for n, k in ((300, 4096), (1000, 2560), (7, 32)):
+        w = oracle.normal((n, k), 5, n, 0.03)
+        data, scales = oracle.q4_quantize(w)
+        d_w, d_s, d_o = ctx.to_device(data), ctx.to_device(scales), ctx.alloc(n * k * 2)
+        ctx.dequant_q4(k, n)(1, d_w, d_s, d_o)
+        ctx.sync()
+        assert np.array_equal(d_o.download(np.uint16, (n, k)), oracle.q4_dequant(data, scales, n, k)), (n, k)
+
+
+@pytest.mark.parametrize("out", [OUT_BF16, OUT_F32, OUT_RESIDUAL])
+@pytest.mark.parametrize("rows", [1, 2, 4])
+def test_matvec_q4_bits_and_contract(ctx, oracle, out, rows):
+    n, k = G["q4_w"].shape
+    if out == OUT_BF16:
+        d_w, d_s, d_x, d_y = ctx.to_device(G["q4_data"]), ctx.to_device(G["q4_scales"]), ctx.to_device(G["q4_x"]), ctx.alloc(max(n * 2, 16))
+        ctx.matvec_q4(k, n, out, rows)(1, d_w, d_x, d_y, d_s)
+        ctx.sync()
+        assert np.array_equal(d_y.download(np.uint16, (n,)), G["q4_matvec"])
+    for n, k in ((1001, 4096), (330, 1024), (5, 32), (64, 12288)):
+        w = oracle.normal((n, k), 6, n, k**-0.5)
+        x = oracle.normal((k,), 7, k, 1.0)
+        y0 = oracle.normal((n,), 8, n, 1.0)
+        data, scales = oracle.q4_quantize(w)
+        d_w, d_s, d_x = ctx.to_device(data), ctx.to_device(scales), ctx.to_device(x)
+        if out == OUT_F32:
+            d_y = ctx.alloc(n * 4)
+            start = None
+        else:
+            start = y0 if out == OUT_RESIDUAL else np.zeros(n, dtype=np.uint16)
+            d_y = ctx.to_device(start) if n * 2 >= 16 else ctx.alloc(16).upload(start)
+        ctx.matvec_q4(k, n, out, rows)(1, d_w, d_x, d_y, d_s)
+        ctx.sync()
+        got = d_y.download(np.float32 if out == OUT_F32 else np.uint16, (n,))
+        want = oracle.matvec_q4(data, scales, x, n, k, out, start)
+        assert np.array_equal(got.view(np.uint32 if out == OUT_F32 else np.uint16), want.view(np.uint32 if out == OUT_F32 else np.uint16)), (n, k)
+        # and the contract against the f64 product of the exact weights d * q (the matvec does not round them to bf16)
+        if out != OUT_RESIDUAL:
+            nib = np.stack([data.reshape(-1, 16)[:, 4 * (e // 8) + (e % 8) % 4] >> (4 if e % 8 >= 4 else 0) & 15 for e in range(32)], axis=1)
+            q = ((nib ^ 8).astype(np.int32) - 8).astype(np.float64)
+            wq = (q * scales.view(np.float16).astype(np.float64)[:, None]).reshape(n, k)
+            xf = (x.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+            ref64 = wq @ xf
+            if out == OUT_F32:
+                ref = ref64.astype(np.float32).reshape(1, n)
+            else:
+                ref = np.array([oracle.lib.hbo_f64_to_bf16(float(v)) for v in ref64], dtype=np.uint16).reshape(1, n)
+            within_contract(oracle, ref, got.reshape(1, n), f"matvec_q4 {n}x{k}")
+
+
+def test_q4_prefill_is_dequant_then_gemm(ctx, oracle):
+    # the reference's Q4 prefill GEMM multiplies the decoded bf16 values: decode once, then the bf16 GEMM
+    m, k, n = 96, 1024, 512
+    w = oracle.normal((n, k), 9, 1, k**-0.5)
+    x = oracle.normal((m, k), 10, 2, 1.0)
+    data, scales = oracle.q4_quantize(w)
+    d_q, d_s, d_w, d_x, d_y = ctx.to_device(data), ctx.to_device(scales), ctx.alloc(n * k * 2), ctx.to_device(x), ctx.alloc(m * n * 2)
+    ctx.run([(ctx.dequant_q4(k, n), 1, d_q, d_s, d_w), (ctx.gemm(k, n, OUT_BF16, rows_max=m), m, d_w, d_x, d_y)])
+    ctx.sync()
+    within_contract(oracle, oracle.gemm_f64(x, oracle.q4_dequant(data, scales, n, k)), d_y.download(np.uint16, (m, n)), "Q4 prefill")
+
+
+def test_q4_limits(ctx, hb200):
+    for bad in (lambda: ctx.dequant_q4(40, 8), lambda: ctx.matvec_q4(4096, 64, 3, 2), lambda: ctx.matvec_q4(4096, 64, OUT_BF16, 3)):
+        with pytest.raises(hb200.HbError) as e:
+            bad()
+        assert e.value.status == hb200.UNSUPPORTED

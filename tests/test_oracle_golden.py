@@ -188,6 +188,21 @@ def test_moe_out_known_answers(oracle):
     assert np.array_equal(got, G["moe_out_out"])
 
 
+def test_q4_known_answers(oracle):
+    w = G["q4_w"]
+    n, k = w.shape
+    data, scales = oracle.q4_quantize(w)
+    assert np.array_equal(data, G["q4_data"]) and np.array_equal(scales, G["q4_scales"])
+    deq = oracle.q4_dequant(data, scales, n, k)
+    assert np.array_equal(deq, G["q4_dequant"])
+    # the reference's own unit test (q4.rs:113-131): a block on the grid comes back exactly
+    assert np.array_equal(deq[1, :32], w[1, :32])
+    assert np.array_equal(oracle.matvec_q4(data, scales, G["q4_x"], n, k), G["q4_matvec"])
+    # quantisation error is small against the weights
+    f = lambda a: (a.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+    assert np.abs(f(deq) - f(w)).max() <= np.abs(f(w)).max() / 7.5
+
+
 def test_check_rule(oracle):
     ref = G["check_ref"]
     assert oracle.check_1_64(ref, G["check_ok"])[0] is True
