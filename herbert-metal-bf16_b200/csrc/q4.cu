@@ -41,6 +41,23 @@ __global__ void __launch_bounds__(256) dequant_q4_kernel(const uint4* __restrict
     }
 }
 
+// Two IEEE f32 operations in one instruction (two rows of W share every activation, so their chains go side by side).
+__device__ __forceinline__ uint64_t q4_pack2(uint32_t lo, uint32_t hi) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ uint64_t q4_ffma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ uint64_t q4_fadd2(uint64_t a, uint64_t b) {
+    uint64_t d;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
 struct MatvecQ4Params {
     const uint4* w;
     const uint16_t* sc;
@@ -84,9 +101,8 @@ __global__ void __launch_bounds__(Q4_THREADS) matvec_q4_kernel(const MatvecQ4Par
                     xs[8 * i + 2 * c + 1] = __uint_as_float(xw[c] & 0xffff0000u);
                 }
             }
-#pragma unroll
-            for (int r = 0; r < R; ++r) {
-                const uint32_t ww[4] = {wv[r].x, wv[r].y, wv[r].z, wv[r].w};
+            if constexpr (R == 1) {
+                const uint32_t ww[4] = {wv[0].x, wv[0].y, wv[0].z, wv[0].w};
                 float part = 0.f;
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -97,7 +113,33 @@ __global__ void __launch_bounds__(Q4_THREADS) matvec_q4_kernel(const MatvecQ4Par
                         part = __fmaf_rn(q4_byte_to_q(hi, byte), xs[8 * i + 4 + byte], part);
                     }
                 }
-                acc[r] = __fmaf_rn(__half2float(__ushort_as_half(dh[r])), part, acc[r]);
+                acc[0] = __fmaf_rn(__half2float(__ushort_as_half(dh[0])), part, acc[0]);
+            } else {
+                // rows in pairs: the two chains of a pair run as the two halves of packed f32x2 operations (each half
+                // is the same IEEE operation as the scalar one, in the same order)
+                const uint64_t minus = q4_pack2(__float_as_uint(-8388616.0f), __float_as_uint(-8388616.0f));
+#pragma unroll
+                for (int r = 0; r < R; r += 2) {
+                    const uint32_t wa[4] = {wv[r].x, wv[r].y, wv[r].z, wv[r].w}, wb[4] = {wv[r + 1].x, wv[r + 1].y, wv[r + 1].z, wv[r + 1].w};
+                    uint64_t part2 = 0ull;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const uint32_t lo_a = (wa[i] & 0x0F0F0F0Fu) ^ 0x08080808u, hi_a = ((wa[i] >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;
+                        const uint32_t lo_b = (wb[i] & 0x0F0F0F0Fu) ^ 0x08080808u, hi_b = ((wb[i] >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;
+#pragma unroll
+                        for (int byte = 0; byte < 4; ++byte) {
+                            const uint32_t xl = __float_as_uint(xs[8 * i + byte]), xh = __float_as_uint(xs[8 * i + 4 + byte]);
+                            const uint64_t ql = q4_fadd2(q4_pack2(__byte_perm(lo_a, 0x4B000000u, 0x7650u + byte), __byte_perm(lo_b, 0x4B000000u, 0x7650u + byte)), minus);
+                            part2 = q4_ffma2(ql, q4_pack2(xl, xl), part2);
+                            const uint64_t qh = q4_fadd2(q4_pack2(__byte_perm(hi_a, 0x4B000000u, 0x7650u + byte), __byte_perm(hi_b, 0x4B000000u, 0x7650u + byte)), minus);
+                            part2 = q4_ffma2(qh, q4_pack2(xh, xh), part2);
+                        }
+                    }
+                    uint32_t pa, pb;
+                    asm("mov.b64 {%0, %1}, %2;" : "=r"(pa), "=r"(pb) : "l"(part2));
+                    acc[r] = __fmaf_rn(__half2float(__ushort_as_half(dh[r])), __uint_as_float(pa), acc[r]);
+                    acc[r + 1] = __fmaf_rn(__half2float(__ushort_as_half(dh[r + 1])), __uint_as_float(pb), acc[r + 1]);
+                }
             }
         }
 #pragma unroll
