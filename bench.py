@@ -668,6 +668,32 @@ def bench_extra(hb, ctx, sel, torch, dev, wrap, pk, rank, world, barrier, max_ov
     per_kernel = {}
     for op in ops:
         per_kernel[op[0].name] = ctx.time([op], 20) / 20 * 1e6
+    # the whole sparse layer around that block (qwen.rs:2699-2733): router projection h -> E, the block, the shared
+    # expert (gate/up + SwiGLU, down), and moe_out (sigmoid gate, sum, residual)
+    try:
+        wr = (torch.randn(E, h, device=dev, generator=g) * h**-0.5).bfloat16()
+        wsg = (torch.randn(2 * mi, h, device=dev, generator=g) * h**-0.5).bfloat16()
+        wsd = (torch.randn(h, mi, device=dev, generator=g) * mi**-0.5).bfloat16()
+        gate_w = (torch.randn(h, device=dev, generator=g) * h**-0.5).bfloat16()
+        resid = torch.randn(m, h, device=dev, generator=g).bfloat16()
+        sh_h = torch.zeros(m, mi, device=dev, dtype=torch.bfloat16)
+        sh_gu = torch.zeros(m, 2 * mi, device=dev, dtype=torch.bfloat16)
+        sh_y = torch.zeros(m, h, device=dev, dtype=torch.bfloat16)
+        k_router = sel.gemm(h, E, 0, wrap(wr), wrap(x), wrap(scores), m)
+        k_sgu = sel.gate_up(h, mi, wrap(wsg), wrap(x), wrap(sh_gu), wrap(sh_h), m)
+        k_sd = sel.gemm(mi, h, 0, wrap(wsd), wrap(sh_h), wrap(sh_y), m)
+        full = [(k_router, m, wrap(wr), wrap(x), wrap(scores))] + ops
+        full += [(k_sgu[0], m, wrap(wsg), wrap(x), wrap(sh_gu)), (k_sgu[1], m, wrap(sh_gu), wrap(sh_h))] if len(k_sgu) == 2 else [(k_sgu[0], m, wrap(wsg), wrap(x), wrap(sh_h))]
+        full += [(k_sd, m, wrap(wsd), wrap(sh_h), wrap(sh_y)), (ctx.moe_out(h), m, wrap(x), wrap(gate_w), wrap(outb), wrap(sh_y), wrap(resid))]
+        gr = ctx.record(full)
+        gr.time(3)
+        barrier()
+        sec_full = max_over_ranks(gr.time(20) / 20)
+        gr.free()
+        out["moe_layer_full_2048tok"] = {"us": sec_full * 1e6, "kernels": len(full), "tokens_per_s": m / sec_full,
+                                         "router": k_router.name, "shared_gate_up": "+".join(k_.name for k_ in k_sgu), "shared_down": k_sd.name}
+    except Exception as e:
+        out["moe_layer_error"] = repr(e)
     out["moe_2048tok_256e_top8"] = {"us": sec * 1e6, "tile_rows": pick["bm"], "weight_gbs": wbytes / sec / 1e9, "frac_hbm": wbytes / sec / 1e9 / pk["hbm_gbs"],
                                     "tflops": flop / sec / 1e12, "us_per_kernel": per_kernel}
     return out
