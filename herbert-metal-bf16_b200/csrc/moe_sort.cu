@@ -30,16 +30,10 @@ struct SortParams {
     uint32_t use_masks; // the per-expert row masks fit in shared memory
     uint32_t words;     // stride of an expert's mask in words: ceil(rows_max / 32) made odd
     uint32_t list_staged;  // the sorted list fits in shared memory as 16-bit pair numbers
-    uint32_t* only_if;     // when set: run only if this word is not zero (the cluster form could not do it), and clear it
 };
 
 __global__ void __launch_bounds__(SORT_THREADS) moe_sort_kernel(const SortParams p) {
     extern __shared__ uint32_t sm[];
-    if (p.only_if) {
-        if (*p.only_if == 0) return;
-        __syncthreads();  // everybody has read the word
-        if (threadIdx.x == 0) *p.only_if = 0;
-    }
     const uint32_t experts = p.experts, top_k = p.top_k, bm = p.bm;
     uint32_t* off = sm;                   // [experts] first sorted row of expert e
     uint32_t* tot = off + experts;        // [experts] pairs of expert e
@@ -248,8 +242,7 @@ __global__ void __launch_bounds__(SORT_THREADS) moe_sort_kernel(const SortParams
 //   first row of the expert + pairs of that expert in the CTAs before + rank inside the CTA.
 // The order is the single-CTA kernel's (and the reference's): experts ascending, pairs ascending inside an expert.
 // One SM's shared-memory and store throughput bound the single-CTA form; eight SMs share the work here.
-// A route with a repeated expert in a row makes the cluster raise `fallback` and write nothing; the single-CTA
-// kernel, enqueued behind it with only_if = fallback, then does the sort (otherwise it returns at once).
+// A route with a repeated expert in a row is sorted by CTA 0 alone, serially (see below).
 constexpr int CS_THREADS = 512;
 constexpr int CS_CTAS = 8;
 
@@ -258,7 +251,6 @@ struct ClusterSortParams {
     uint32_t* list;
     uint32_t* tiles;
     uint32_t* offsets;
-    uint32_t* fallback;
     uint32_t rows, experts, top_k, bm;
     uint32_t rows_per_cta;  // a multiple of 32
     uint32_t words;         // stride of an expert's mask: rows_per_cta_max / 32, made odd
@@ -329,19 +321,25 @@ __global__ void __cluster_dims__(CS_CTAS, 1, 1) __launch_bounds__(CS_THREADS) mo
     uint32_t any_dup = 0;
 #pragma unroll
     for (uint32_t c = 0; c < CS_CTAS; ++c) any_dup |= dup_all[c];
-    if (any_dup) {
-        if (cta == 0 && tid == 0) *p.fallback = 1;
-        return;
-    }
+    // A route that repeats an expert inside a row (a top-k route never does) cannot use the masks: CTA 0 then sorts
+    // alone, a thread per expert walking all pairs in order (every thread reads the same word: a broadcast) - slow
+    // (two passes over the pairs) but exact, and taken by no route this library produces.
+    const bool serial = any_dup != 0;
+    if (serial && cta != 0) return;
+    const uint32_t pairs_all = p.rows * top_k;
     // totals and the share of the CTAs before this one; scans of (pairs, tiles) over the experts
     // (thread e for e < CS_THREADS; the cluster form is built for at most CS_THREADS experts)
     uint32_t total_e = 0, before = 0;
     if (tid < experts) {
+        if (serial) {
+            for (uint32_t i = 0; i < pairs_all; ++i) total_e += p.route[(size_t)(i / top_k) * 2 * top_k + (i % top_k)] == tid ? 1u : 0u;
+        } else {
 #pragma unroll
-        for (uint32_t c = 0; c < CS_CTAS; ++c) {
-            const uint32_t v = cnt_all[c * experts + tid];
-            total_e += v;
-            if (c < cta) before += v;
+            for (uint32_t c = 0; c < CS_CTAS; ++c) {
+                const uint32_t v = cnt_all[c * experts + tid];
+                total_e += v;
+                if (c < cta) before += v;
+            }
         }
     }
     const uint32_t ntile_e = (total_e + bm - 1) / bm;
@@ -381,6 +379,14 @@ __global__ void __cluster_dims__(CS_CTAS, 1, 1) __launch_bounds__(CS_THREADS) mo
         }
     }
     __syncthreads();
+    if (serial) {
+        if (tid < experts) {
+            uint32_t pos = off[tid];
+            for (uint32_t i = 0; i < pairs_all; ++i)
+                if (p.route[(size_t)(i / top_k) * 2 * top_k + (i % top_k)] == tid) p.list[pos++] = i;
+        }
+        return;
+    }
     // placement: the pairs of one (expert, CTA) are neighbours in the list, so the stores fill whole sectors
     const uint32_t pair0 = r0 * top_k;
     for (uint32_t i = tid; i < my_pairs; i += CS_THREADS) {
@@ -395,10 +401,9 @@ namespace {
 struct MoeSort : hb_kernel {
     uint32_t experts = 0, top_k = 0, rows_max = 0, bm = 0, staged = 0, use_masks = 0, words = 0, list_staged = 0;
     size_t smem = 0;
-    // the cluster form, when the shape allows it: its mask stride, shared memory and the fallback word
+    // the cluster form, when the shape allows it: its mask stride and shared memory
     uint32_t cl_words = 0, cl_ex_cap = 0;
     size_t cl_smem = 0;
-    uint32_t* fallback = nullptr;
     int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
         if (na != 3 && na != 4) return fail(ctx, HB_INVALID, name + ": bindings are route, list, tiles[, offsets]");
         if (na == 4 && !range_ok(a[3], ((size_t)experts + 1) * 4)) return fail(ctx, HB_INVALID, name + ": the offsets range is too small");
@@ -420,13 +425,12 @@ struct MoeSort : hb_kernel {
         p.staged = staged;
         p.use_masks = use_masks;
         p.words = words;
-        if (fallback) {
+        if (cl_smem) {
             ClusterSortParams c{};
             c.route = p.route;
             c.list = p.list;
             c.tiles = p.tiles;
             c.offsets = p.offsets;
-            c.fallback = fallback;
             c.rows = m;
             c.experts = experts;
             c.top_k = top_k;
@@ -437,7 +441,7 @@ struct MoeSort : hb_kernel {
             moe_sort_cluster_kernel<<<CS_CTAS, CS_THREADS, cl_smem, ctx->stream>>>(c);
             HB_CUDA(ctx, cudaGetLastError());
             ctx->launches++;
-            p.only_if = fallback;  // the single-CTA kernel behind it runs only if the cluster gave up
+            return HB_OK;
         }
         moe_sort_kernel<<<1, SORT_THREADS, smem, ctx->stream>>>(p);
         HB_CUDA(ctx, cudaGetLastError());
@@ -494,10 +498,6 @@ int make_moe_sort(hb_ctx* ctx, uint32_t experts, uint32_t top_k, uint32_t rows_m
         const size_t ex_cap = ((size_t)rpc * top_k + 7) / 8 * 8;
         const size_t need = ((size_t)CS_CTAS * experts + CS_CTAS + experts + 64 + 2 * (size_t)experts * cw) * 4 + ex_cap * 2 + 16;
         if (need <= limit) {
-            void* fb = nullptr;
-            int r = hb_alloc(ctx, 16, &fb);
-            if (r != HB_OK) return r;
-            k->fallback = static_cast<uint32_t*>(fb);
             k->cl_words = cw;
             k->cl_ex_cap = (uint32_t)ex_cap;
             k->cl_smem = need;
