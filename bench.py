@@ -556,8 +556,8 @@ def bench_extra(hb, ctx, sel, torch, dev, wrap, pk, rank, world, barrier, max_ov
             sq = (torch.rand(blocks, device=dev, generator=g) * 0.01 + 0.001).half()
             yq = torch.zeros(nq, device=dev, dtype=torch.bfloat16)
             best = None
-            for rows in (1, 2, 4):
-                kq = ctx.matvec_q4(k, nq, 0, rows)
+            for rows, masks in ((1, 0), (2, 0), (4, 0), (2, 1), (4, 1)):
+                kq = ctx.matvec_q4(k, nq, 0, rows, masks)
                 ops_q = [(kq, 1, wrap(w_), wrap(xs), wrap(yq), wrap(sq)) for w_ in wq]
                 gr = ctx.record(ops_q)
                 gr.time(3)

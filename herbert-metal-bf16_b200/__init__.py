@@ -102,7 +102,7 @@ def lib() -> C.CDLL:
         "hb_tp_reduce_get": (ci, [vp, u32, u32, u32, u32, pvp]),
         "hb_tp_sum_get": (ci, [vp, u32, u32, u32, u32, pvp]),
         "hb_dequant_q4_get": (ci, [vp, u32, u32, pvp]),
-        "hb_matvec_q4_get": (ci, [vp, u32, u32, u32, u32, pvp]),
+        "hb_matvec_q4_get": (ci, [vp, u32, u32, u32, u32, u32, pvp]),
         "hb_rmsnorm_get": (ci, [vp, u32, C.c_float, u32, pvp]),
         "hb_argmax_get": (ci, [vp, u32, u32, pvp]),
         "hb_moe_out_get": (ci, [vp, u32, pvp]),
@@ -372,8 +372,8 @@ class Context:
     def dequant_q4(self, k, n) -> "Kernel":
         return self._get(lib().hb_dequant_q4_get, k, n)
 
-    def matvec_q4(self, k, n, out=OUT_BF16, rows_per_warp=2) -> "Kernel":
-        return self._get(lib().hb_matvec_q4_get, k, n, out, rows_per_warp)
+    def matvec_q4(self, k, n, out=OUT_BF16, rows_per_warp=2, masks=0) -> "Kernel":
+        return self._get(lib().hb_matvec_q4_get, k, n, out, rows_per_warp, masks)
 
     def rmsnorm(self, d, eps=1e-6, plus_one=False) -> "Kernel":
         return self._get(lib().hb_rmsnorm_get, d, C.c_float(eps), 1 if plus_one else 0)

@@ -69,7 +69,11 @@ struct MatvecQ4Params {
 constexpr int Q4_THREADS = 256;
 constexpr int Q4_WARPS = Q4_THREADS / 32;
 
-template <int R, int OUT>
+// MASKS: the order of sums of the reference's matvec_q4s ("llama.cpp's masks", src/metal/kernels.rs:455-462,
+// 1387-1424): per block sx = x_0 + ... + x_31 in order, part = fma(q_e + 8, x_e, part) over e = 8i + j, j = 0..7 (the low
+// nibbles of bytes 0..3, then the high ones), part = fma(-8, sx, part). The reference multiplies the nibble taken in
+// place (q + 8)·2^s by x·2^-s: the same product exactly (powers of two), so the same bits, without the scaling.
+template <int R, int OUT, bool MASKS>
 __global__ void __launch_bounds__(Q4_THREADS) matvec_q4_kernel(const MatvecQ4Params p) {
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     griddep_launch_dependents();
@@ -101,6 +105,20 @@ __global__ void __launch_bounds__(Q4_THREADS) matvec_q4_kernel(const MatvecQ4Par
                     xs[8 * i + 2 * c + 1] = __uint_as_float(xw[c] & 0xffff0000u);
                 }
             }
+            // what is subtracted from the byte-in-0x4B000000 float: 8388608 + 8 gives q, 8388608 gives q + 8
+            constexpr float MAGIC = MASKS ? -8388608.0f : -8388616.0f;
+            float sx = 0.f;
+            if constexpr (MASKS) {
+                sx = xs[0];
+#pragma unroll
+                for (int e = 1; e < 32; ++e) sx = __fadd_rn(sx, xs[e]);
+            }
+            // step t of a word's eight: which nibble (low or high) of which byte, and which activation
+            //   plain: weight 8i + byte, then 8i + 4 + byte, byte by byte; masks: the four low nibbles, then the four high
+            auto nib_of = [](int t, bool& high, int& byte) {
+                if (MASKS) { high = t >= 4; byte = t & 3; }
+                else { high = (t & 1) != 0; byte = t >> 1; }
+            };
             if constexpr (R == 1) {
                 const uint32_t ww[4] = {wv[0].x, wv[0].y, wv[0].z, wv[0].w};
                 float part = 0.f;
@@ -108,16 +126,20 @@ __global__ void __launch_bounds__(Q4_THREADS) matvec_q4_kernel(const MatvecQ4Par
                 for (int i = 0; i < 4; ++i) {
                     const uint32_t lo = (ww[i] & 0x0F0F0F0Fu) ^ 0x08080808u, hi = ((ww[i] >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;
 #pragma unroll
-                    for (int byte = 0; byte < 4; ++byte) {  // the reference's order: weight 8i + byte, then 8i + 4 + byte
-                        part = __fmaf_rn(q4_byte_to_q(lo, byte), xs[8 * i + byte], part);
-                        part = __fmaf_rn(q4_byte_to_q(hi, byte), xs[8 * i + 4 + byte], part);
+                    for (int t = 0; t < 8; ++t) {
+                        bool high;
+                        int byte;
+                        nib_of(t, high, byte);
+                        const float q = __fadd_rn(__uint_as_float(__byte_perm(high ? hi : lo, 0x4B000000u, 0x7650u + byte)), MAGIC);
+                        part = __fmaf_rn(q, xs[8 * i + (high ? 4 : 0) + byte], part);
                     }
                 }
+                if constexpr (MASKS) part = __fmaf_rn(-8.0f, sx, part);
                 acc[0] = __fmaf_rn(__half2float(__ushort_as_half(dh[0])), part, acc[0]);
             } else {
                 // rows in pairs: the two chains of a pair run as the two halves of packed f32x2 operations (each half
                 // is the same IEEE operation as the scalar one, in the same order)
-                const uint64_t minus = q4_pack2(__float_as_uint(-8388616.0f), __float_as_uint(-8388616.0f));
+                const uint64_t minus = q4_pack2(__float_as_uint(MAGIC), __float_as_uint(MAGIC));
 #pragma unroll
                 for (int r = 0; r < R; r += 2) {
                     const uint32_t wa[4] = {wv[r].x, wv[r].y, wv[r].z, wv[r].w}, wb[4] = {wv[r + 1].x, wv[r + 1].y, wv[r + 1].z, wv[r + 1].w};
@@ -127,18 +149,25 @@ __global__ void __launch_bounds__(Q4_THREADS) matvec_q4_kernel(const MatvecQ4Par
                         const uint32_t lo_a = (wa[i] & 0x0F0F0F0Fu) ^ 0x08080808u, hi_a = ((wa[i] >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;
                         const uint32_t lo_b = (wb[i] & 0x0F0F0F0Fu) ^ 0x08080808u, hi_b = ((wb[i] >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;
 #pragma unroll
-                        for (int byte = 0; byte < 4; ++byte) {
-                            const uint32_t xl = __float_as_uint(xs[8 * i + byte]), xh = __float_as_uint(xs[8 * i + 4 + byte]);
-                            const uint64_t ql = q4_fadd2(q4_pack2(__byte_perm(lo_a, 0x4B000000u, 0x7650u + byte), __byte_perm(lo_b, 0x4B000000u, 0x7650u + byte)), minus);
-                            part2 = q4_ffma2(ql, q4_pack2(xl, xl), part2);
-                            const uint64_t qh = q4_fadd2(q4_pack2(__byte_perm(hi_a, 0x4B000000u, 0x7650u + byte), __byte_perm(hi_b, 0x4B000000u, 0x7650u + byte)), minus);
-                            part2 = q4_ffma2(qh, q4_pack2(xh, xh), part2);
+                        for (int t = 0; t < 8; ++t) {
+                            bool high;
+                            int byte;
+                            nib_of(t, high, byte);
+                            const uint32_t xe = __float_as_uint(xs[8 * i + (high ? 4 : 0) + byte]);
+                            const uint64_t q2 = q4_fadd2(q4_pack2(__byte_perm(high ? hi_a : lo_a, 0x4B000000u, 0x7650u + byte),
+                                                                  __byte_perm(high ? hi_b : lo_b, 0x4B000000u, 0x7650u + byte)), minus);
+                            part2 = q4_ffma2(q2, q4_pack2(xe, xe), part2);
                         }
                     }
                     uint32_t pa, pb;
                     asm("mov.b64 {%0, %1}, %2;" : "=r"(pa), "=r"(pb) : "l"(part2));
-                    acc[r] = __fmaf_rn(__half2float(__ushort_as_half(dh[r])), __uint_as_float(pa), acc[r]);
-                    acc[r + 1] = __fmaf_rn(__half2float(__ushort_as_half(dh[r + 1])), __uint_as_float(pb), acc[r + 1]);
+                    float fa = __uint_as_float(pa), fb = __uint_as_float(pb);
+                    if constexpr (MASKS) {
+                        fa = __fmaf_rn(-8.0f, sx, fa);
+                        fb = __fmaf_rn(-8.0f, sx, fb);
+                    }
+                    acc[r] = __fmaf_rn(__half2float(__ushort_as_half(dh[r])), fa, acc[r]);
+                    acc[r + 1] = __fmaf_rn(__half2float(__ushort_as_half(dh[r + 1])), fb, acc[r + 1]);
                 }
             }
         }
@@ -180,14 +209,18 @@ struct DequantQ4 : hb_kernel {
 
 typedef void (*q4_fn)(const MatvecQ4Params);
 
-template <int R>
+template <int R, bool MASKS>
 q4_fn q4_out(uint32_t out) {
     switch (out) {
-        case HB_OUT_BF16: return matvec_q4_kernel<R, HB_OUT_BF16>;
-        case HB_OUT_F32: return matvec_q4_kernel<R, HB_OUT_F32>;
-        case HB_OUT_RESIDUAL: return matvec_q4_kernel<R, HB_OUT_RESIDUAL>;
+        case HB_OUT_BF16: return matvec_q4_kernel<R, HB_OUT_BF16, MASKS>;
+        case HB_OUT_F32: return matvec_q4_kernel<R, HB_OUT_F32, MASKS>;
+        case HB_OUT_RESIDUAL: return matvec_q4_kernel<R, HB_OUT_RESIDUAL, MASKS>;
     }
     return nullptr;
+}
+template <bool MASKS>
+q4_fn q4_rows(uint32_t rows, uint32_t out) {
+    return rows == 1 ? q4_out<1, MASKS>(out) : rows == 2 ? q4_out<2, MASKS>(out) : rows == 4 ? q4_out<4, MASKS>(out) : nullptr;
 }
 
 struct MatvecQ4 : hb_kernel {
@@ -230,11 +263,11 @@ int make_dequant_q4(hb_ctx* ctx, uint32_t k, uint32_t n, hb_kernel** out) {
     return HB_OK;
 }
 
-int make_matvec_q4(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t out_mode, uint32_t rows, hb_kernel** out) {
+int make_matvec_q4(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t out_mode, uint32_t rows, uint32_t masks, hb_kernel** out) {
     *out = nullptr;
     if (k == 0 || n == 0 || k % 32 != 0) return fail(ctx, HB_UNSUPPORTED, "Q4: K = " + std::to_string(k) + " is not a multiple of 32");
     if (rows == 0) rows = 2;
-    q4_fn fn = rows == 1 ? q4_out<1>(out_mode) : rows == 2 ? q4_out<2>(out_mode) : rows == 4 ? q4_out<4>(out_mode) : nullptr;
+    q4_fn fn = masks ? q4_rows<true>(rows, out_mode) : q4_rows<false>(rows, out_mode);
     if (!fn) return fail(ctx, HB_UNSUPPORTED, "matvec_q4: rows per warp 1, 2 or 4; output Bf16, F32 or Residual");
     auto kn = std::make_unique<MatvecQ4>();
     kn->k = k;
@@ -244,7 +277,7 @@ int make_matvec_q4(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t out_mode, uint3
     kn->fn = fn;
     kn->kind = 20;
     kn->nargs = 4;
-    kn->name = "matvec_q4_" + std::to_string(k) + "x" + std::to_string(n) + "_" + out_tag(out_mode) + "_r" + std::to_string(rows);
+    kn->name = std::string(masks ? "matvec_q4s_" : "matvec_q4_") + std::to_string(k) + "x" + std::to_string(n) + "_" + out_tag(out_mode) + "_r" + std::to_string(rows);
     *out = intern(ctx, std::move(kn));
     return HB_OK;
 }
@@ -262,10 +295,10 @@ int hb_dequant_q4_get(hb_ctx* ctx, uint32_t k, uint32_t n, hb_kernel** out) {
     }
 }
 
-int hb_matvec_q4_get(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t out_mode, uint32_t rows_per_warp, hb_kernel** out) {
+int hb_matvec_q4_get(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t out_mode, uint32_t rows_per_warp, uint32_t masks, hb_kernel** out) {
     if (!ctx || !out) return hb::fail(ctx, HB_INVALID, "hb_matvec_q4_get: bad argument");
     try {
-        return hb::make_matvec_q4(ctx, k, n, out_mode, rows_per_warp, out);
+        return hb::make_matvec_q4(ctx, k, n, out_mode, rows_per_warp, masks, out);
     } catch (const std::exception& e) {
         return hb::fail(ctx, HB_BACKEND, e.what());
     }

@@ -245,9 +245,10 @@ int hb_moe_out_get(hb_ctx* ctx, uint32_t d, hb_kernel** out);
  * GEMM stages from Q4 weights (prefill.rs:1058-1076), so this kernel followed by hb_gemm_get gives its bits.
  * Bindings W (nibbles, n*k/2 bytes), scales (f16, n*k/32), out (bf16 [n][k]); m is ignored. */
 int hb_dequant_q4_get(hb_ctx* ctx, uint32_t k, uint32_t n, hb_kernel** out);
-/* matvec_q4, src/metal/kernels.rs:444-632: y = out(W . x) for one activation row, the sums in the reference's order
- * (bit-exact). rows_per_warp 1, 2 or 4 (0 = 2); out BF16, F32 or RESIDUAL. Bindings W, x, y, scales as there. */
-int hb_matvec_q4_get(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t out, uint32_t rows_per_warp, hb_kernel** res);
+/* matvec_q4 (masks = 0) and matvec_q4s (masks = 1: "llama.cpp's masks", the tune key mv.masks), src/metal/kernels.rs:
+ * 444-632, 1387-1424: y = out(W . x) for one activation row, the sums in the order of the form named (bit-exact with
+ * either). rows_per_warp 1, 2 or 4 (0 = 2); out BF16, F32 or RESIDUAL. Bindings W, x, y, scales as there. */
+int hb_matvec_q4_get(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t out, uint32_t rows_per_warp, uint32_t masks, hb_kernel** res);
 
 /* ---- expert-parallel exchange over peer memory (no reference counterpart: the reference runs on one GPU) ----
  * Experts are partitioned contiguously over `world` ranks, the token rows are each rank's own. A rank sorts its

@@ -579,6 +579,43 @@ void hbo_matvec_q4(const uint8_t* data, const uint16_t* scales, const uint16_t* 
     }
 }
 
+void hbo_matvec_q4s(const uint8_t* data, const uint16_t* scales, const uint16_t* x, void* y, int n, int k, int out) {
+    const int nblk = k / 32;
+#pragma omp parallel for schedule(static)
+    for (int row = 0; row < n; ++row) {
+        float lane[32];
+        for (int l = 0; l < 32; ++l) {
+            float acc = 0.0f;
+            for (int b = l; b < nblk; b += 32) {
+                float xs[32], scaled[32];
+                for (int e = 0; e < 32; ++e) xs[e] = hbo_bf16_to_f32(x[b * 32 + e]);
+                float sx = xs[0];
+                for (int e = 1; e < 32; ++e) sx = sx + xs[e];
+                for (int e = 0; e < 32; ++e) {
+                    int jj = e % 8, shift = jj < 4 ? 8 * jj : 8 * (jj - 4) + 4;
+                    scaled[e] = xs[e] * ldexpf(1.0f, -shift);
+                }
+                const uint8_t* blk = data + ((size_t)row * nblk + b) * 16;
+                float part = 0.0f;
+                for (int i = 0; i < 4; ++i) {
+                    uint32_t ww;
+                    memcpy(&ww, blk + 4 * i, 4);
+                    ww ^= 0x88888888u;
+                    for (int jj = 0; jj < 8; ++jj) {
+                        int shift = jj < 4 ? 8 * jj : 8 * (jj - 4) + 4;
+                        uint32_t v = ww & (15u << shift);
+                        part = fmaf((float)v, scaled[8 * i + jj], part);
+                    }
+                }
+                part = fmaf(-8.0f, sx, part);
+                acc = fmaf(f16_bits_to_f32(scales[(size_t)row * nblk + b]), part, acc);
+            }
+            lane[l] = acc;
+        }
+        store_out(y, (size_t)row, butterfly_sum32(lane), out);
+    }
+}
+
 /* -------------------------------------------------------------------- check */
 
 int hbo_check_1_64(const void* ref, const void* got, size_t count, int f32_out, float* err_out, float* scale_out) {

@@ -421,6 +421,35 @@ def q4_matvec(data, scales, x, n, k):
     return out
 
 
+def q4s_matvec(data, scales, x, n, k):
+    """kernels.rs:455-462, 1387-1424 (matvec_q4s): the masks' order of sums."""
+    f = np.float32
+    nblk = k // 32
+    out = np.zeros(n, dtype=np.uint16)
+    for row in range(n):
+        lanes = []
+        for lane in range(32):
+            acc = f(0.0)
+            for b in range(lane, nblk, 32):
+                blk = row * nblk + b
+                xs = [widen(x[32 * b + e]) for e in range(32)]
+                sx = xs[0]
+                for v in xs[1:]:
+                    sx = f(sx + v)
+                part = f(0.0)
+                for i in range(4):
+                    word = int.from_bytes(bytes(int(v) for v in data[16 * blk + 4 * i : 16 * blk + 4 * i + 4]), "little") ^ 0x88888888
+                    for j in range(8):
+                        shift = 8 * j if j < 4 else 8 * (j - 4) + 4
+                        val = f(word & (15 << shift))
+                        part = fma_f32(val, f(xs[8 * i + j] * f(2.0 ** -shift)), part)
+                part = fma_f32(f(-8.0), sx, part)
+                acc = fma_f32(f(np.uint16(scales[blk]).view(np.float16)), part, acc)
+            lanes.append(acc)
+        out[row] = rne_bf16(butterfly_sum(lanes))
+    return out
+
+
 def main():
     g = {}
     # RNE known answers: (f32 bits, bf16 bits) - ties to even, carries, signed zero, subnormal, infinity.
@@ -514,6 +543,7 @@ def main():
     assert np.array_equal(g["q4_dequant"][1, 0:32], qw[1, 0:32]) and not g["q4_dequant"][2, 32:64].any()
     qx = fill_normal(qk, 0x9E3779B9, 32, 1.0)
     g["q4_x"], g["q4_matvec"] = qx, q4_matvec(qd, qs, qx, qn, qk)
+    g["q4s_matvec"] = q4s_matvec(qd, qs, qx, qn, qk)
     np.savez_compressed(os.path.join(HERE, "golden.npz"), **g)
     print("wrote", os.path.join(HERE, "golden.npz"), "with", len(g), "arrays")
 

@@ -25,15 +25,18 @@ def test_dequant_golden_and_model_shapes(ctx, oracle):
         assert np.array_equal(d_o.download(np.uint16, (n, k)), oracle.q4_dequant(data, scales, n, k)), (n, k)
 
 
+@pytest.mark.parametrize("masks", [0, 1])
 @pytest.mark.parametrize("out", [OUT_BF16, OUT_F32, OUT_RESIDUAL])
 @pytest.mark.parametrize("rows", [1, 2, 4])
-def test_matvec_q4_bits_and_contract(ctx, oracle, out, rows):
+def test_matvec_q4_bits_and_contract(ctx, oracle, out, rows, masks):
     n, k = G["q4_w"].shape
     if out == OUT_BF16:
         d_w, d_s, d_x, d_y = ctx.to_device(G["q4_data"]), ctx.to_device(G["q4_scales"]), ctx.to_device(G["q4_x"]), ctx.alloc(max(n * 2, 16))
-        ctx.matvec_q4(k, n, out, rows)(1, d_w, d_x, d_y, d_s)
+        kern = ctx.matvec_q4(k, n, out, rows, masks)
+        assert kern.name.startswith("matvec_q4s_" if masks else "matvec_q4_")
+        kern(1, d_w, d_x, d_y, d_s)
         ctx.sync()
-        assert np.array_equal(d_y.download(np.uint16, (n,)), G["q4_matvec"])
+        assert np.array_equal(d_y.download(np.uint16, (n,)), G["q4s_matvec" if masks else "q4_matvec"])
     for n, k in ((1001, 4096), (330, 1024), (5, 32), (64, 12288)):
         w = oracle.normal((n, k), 6, n, k**-0.5)
         x = oracle.normal((k,), 7, k, 1.0)
@@ -46,10 +49,10 @@ def test_matvec_q4_bits_and_contract(ctx, oracle, out, rows):
         else:
             start = y0 if out == OUT_RESIDUAL else np.zeros(n, dtype=np.uint16)
             d_y = ctx.to_device(start) if n * 2 >= 16 else ctx.alloc(16).upload(start)
-        ctx.matvec_q4(k, n, out, rows)(1, d_w, d_x, d_y, d_s)
+        ctx.matvec_q4(k, n, out, rows, masks)(1, d_w, d_x, d_y, d_s)
         ctx.sync()
         got = d_y.download(np.float32 if out == OUT_F32 else np.uint16, (n,))
-        want = oracle.matvec_q4(data, scales, x, n, k, out, start)
+        want = oracle.matvec_q4(data, scales, x, n, k, out, start, masks=bool(masks))
         assert np.array_equal(got.view(np.uint32 if out == OUT_F32 else np.uint16), want.view(np.uint32 if out == OUT_F32 else np.uint16)), (n, k)
         # and the contract against the f64 product of the exact weights d * q (the matvec does not round them to bf16)
         if out != OUT_RESIDUAL:
@@ -78,7 +81,7 @@ def test_q4_prefill_is_dequant_then_gemm(ctx, oracle):
 
 
 def test_q4_limits(ctx, hb200):
-    for bad in (lambda: ctx.dequant_q4(40, 8), lambda: ctx.matvec_q4(4096, 64, 3, 2), lambda: ctx.matvec_q4(4096, 64, OUT_BF16, 3)):
+    for bad in (lambda: ctx.dequant_q4(40, 8), lambda: ctx.matvec_q4(4096, 64, 3, 2), lambda: ctx.matvec_q4(4096, 64, OUT_BF16, 3), lambda: ctx.matvec_q4(4096, 64, 3, 2, 1)):
         with pytest.raises(hb200.HbError) as e:
             bad()
         assert e.value.status == hb200.UNSUPPORTED

@@ -198,6 +198,7 @@ def test_q4_known_answers(oracle):
     # the reference's own unit test (q4.rs:113-131): a block on the grid comes back exactly
     assert np.array_equal(deq[1, :32], w[1, :32])
     assert np.array_equal(oracle.matvec_q4(data, scales, G["q4_x"], n, k), G["q4_matvec"])
+    assert np.array_equal(oracle.matvec_q4(data, scales, G["q4_x"], n, k, masks=True), G["q4s_matvec"])
     # quantisation error is small against the weights
     f = lambda a: (a.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
     assert np.abs(f(deq) - f(w)).max() <= np.abs(f(w)).max() / 7.5
