@@ -808,22 +808,27 @@ def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks)
                 sec_nccl = timed(lambda: D.ep_moe(be, xs, sc, wgu_l, wd_l, E, top_k, mi, bm), 2, 5)
                 barrier()
                 st.close()
-                if world > 1:
-                    # weak scaling: 2048 tokens on every rank (the experts still partitioned), peer-memory form
-                    xw = torch.randn(m, h, device=dev, generator=gl).bfloat16()
-                    sw = torch.randn(m, E, device=dev, generator=gl).bfloat16()
-                    stw = D.EpPeer(hb, ctx, rank, world, m, h, mi, E, top_k, bm)
-                    D.ep_peer_connect(stw)
-                    sec_w = timed(lambda: D.ep_moe_peer(stw, xw, sw, wgu_l, wd_l), 3, 10)
-                    barrier()
-                    stw.close()
-                    out["moe_ep_weak_2048tok_per_gpu"] = {"n_gpus": world, "us": sec_w * 1e6, "tokens_per_s_total": m * world / sec_w, "scaling": "weak",
-                                                          "weight_gbs_total": wbytes / sec_w / 1e9}
-                    del stw
                 out["moe_ep_2048tok"] = {"n_gpus": world, "us": sec * 1e6, "weight_gbs_total": wbytes / sec / 1e9, "tokens_per_s": m / sec, "scaling": "strong",
                                          "tile_rows": bm, "exchange": "peer-memory stores and loads in ep_dispatch / ep_return, offsets all-gather + 2 barriers as kernels (no NCCL call in the step)",
                                          "with_nccl_barriers_us": sec_ns * 1e6,
                                          "nccl_all_to_all_form_us": sec_nccl * 1e6, "equals_nccl_form_bitwise": same}
+                if world > 1:
+                    # weak scaling: 2048 tokens on every rank (the experts still partitioned), peer-memory form. The
+                    # buffers hold four times the average number of received rows (an overflow would be reported).
+                    try:
+                        xw = torch.randn(m, h, device=dev, generator=gl).bfloat16()
+                        sw = torch.randn(m, E, device=dev, generator=gl).bfloat16()
+                        stw = D.EpPeer(hb, ctx, rank, world, m, h, mi, E, top_k, bm, cap=min(m * top_k * world, 4 * m * top_k))
+                        D.ep_peer_connect(stw)
+                        sec_w = timed(lambda: D.ep_moe_peer(stw, xw, sw, wgu_l, wd_l), 3, 10)
+                        ctx.sync()
+                        barrier()
+                        stw.close()
+                        out["moe_ep_weak_2048tok_per_gpu"] = {"n_gpus": world, "us": sec_w * 1e6, "tokens_per_s_total": m * world / sec_w, "scaling": "weak",
+                                                              "weight_gbs_total": wbytes / sec_w / 1e9}
+                        del stw
+                    except Exception as e:
+                        out["moe_ep_weak_error"] = repr(e)
     finally:
         stream.synchronize()
         ctx.set_stream(None)
