@@ -504,6 +504,20 @@ def bench_extra(hb, ctx, sel, torch, dev, wrap, pk, rank, world, barrier, max_ov
     out = {}
     g = torch.Generator(device=dev)
     g.manual_seed(1234 + rank)
+    # -- BASELINE config 1: one dense GEMM, M=512, K=1024, N=4096 (4.3 GFLOP: 64 tiles of 128x256, a launch-bound case)
+    try:
+        w1 = (torch.randn(4096, 1024, device=dev, generator=g) / 32.0).bfloat16()
+        x1 = torch.randn(512, 1024, device=dev, generator=g).bfloat16()
+        y1 = torch.zeros(512, 4096, device=dev, dtype=torch.bfloat16)
+        k1 = sel.gemm(1024, 4096, 0, wrap(w1), wrap(x1), wrap(y1), 512)
+        gr = ctx.record([(k1, 512, wrap(w1), wrap(x1), wrap(y1))] * 8)
+        gr.time(3)
+        barrier()
+        sec1 = max_over_ranks(gr.time(20) / (20 * 8))
+        gr.free()
+        out["config1_gemm_512x1024x4096"] = {"us": sec1 * 1e6, "tflops": 2.0 * 512 * 1024 * 4096 / sec1 / 1e12, "form": k1.name}
+    except Exception as e:
+        out["config1_error"] = repr(e)
     # -- matvec: K=4096, N=12288, M in {1,4,8}; four weight copies walked in turn so that W streams from HBM
     k, n = 4096, 12288
     copies = [(torch.randn(n, k, device=dev, generator=g) * k**-0.5).bfloat16() for _ in range(4)]
@@ -867,8 +881,17 @@ def cpu_baseline():
         reps += 1
     dt = (time.perf_counter() - t0) / reps
     value = STEP_FLOP * rows / ROWS / dt / 1e12
+    # BASELINE config 1 in full (M=512, K=1024, N=4096): the case the CPU restatement runs whole
+    w1 = bf16(rng.standard_normal((4096, 1024), dtype=np.float32) / 32.0)
+    x1 = bf16(rng.standard_normal((512, 1024), dtype=np.float32))
+    o.gemm_f32(x1, w1, 0, None)
+    t1 = time.perf_counter()
+    for _ in range(10):
+        o.gemm_f32(x1, w1, 0, None)
+    c1 = (time.perf_counter() - t1) / 10
     return {"value": value, "unit": "TFLOP/s", "cores": o.threads(), "kind": "port",
-            "sample": f"{rows} of {ROWS} rows of every GEMM of the layer set, {reps} passes, f32 accumulate + one RNE (oracle/hb_oracle.c, OpenMP)"}
+            "sample": f"{rows} of {ROWS} rows of every GEMM of the layer set, {reps} passes, f32 accumulate + one RNE (oracle/hb_oracle.c, OpenMP)",
+            "config1_512x1024x4096_ms": c1 * 1e3, "config1_tflops": 2.0 * 512 * 1024 * 4096 / c1 / 1e12}
 
 
 if __name__ == "__main__":
