@@ -188,7 +188,7 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the matvec / MoE / tensor-parallel sections")
     ap.add_argument("--tune", default="", help="engine tune keys, e.g. gemm.auto=0 to skip the load-time timing")
     ap.add_argument("--form", default="", choices=["", "pair", "sk", "one"], help="with --case gate_up/down/layer: the GEMM form (one = one CTA per 128x256 tile)")
-    ap.add_argument("--case", default="", choices=["", "layer", "gate_up", "down", "matvec", "matvec8", "moe", "q4"],
+    ap.add_argument("--case", default="", choices=["", "layer", "gate_up", "down", "matvec", "matvec8", "moe", "q4", "q4m8"],
                     help="run one small case of one kernel a few times and exit (the command profiled under ncu)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -435,16 +435,18 @@ def run_case(args):
         ops = [(ks[0], ROWS, wrap(ws[0]), wrap(x), wrap(qkv)), (ks[1], ROWS, wrap(ws[1]), wrap(x), wrap(resid)),
                (ks[2], ROWS, wrap(ws[2]), wrap(x), wrap(hmid)), (ks[3], ROWS, wrap(ws[3]), wrap(hmid), wrap(resid))]
         work = {"flop": STEP_FLOP}
-    elif args.case == "q4":
-        # the one-row product from Q4_0 weights at the LM-head shape (350 MB of nibbles and scales)
+    elif args.case in ("q4", "q4m8"):
+        # the one-row product from Q4_0 weights at the LM-head shape (350 MB of nibbles and scales); q4m8: eight rows
         k, n = 4096, 151936
         blocks = n * k // 32
         wq = torch.randint(0, 256, (blocks * 16,), device=dev, dtype=torch.uint8, generator=g)
         sq = (torch.rand(blocks, device=dev, generator=g) * 0.01 + 0.001).half()
-        x, y = rnd(1, k), torch.zeros(n, device=dev, dtype=torch.bfloat16)
+        mq = 8 if args.case == "q4m8" else 1
+        x, y = rnd(mq, k), torch.zeros(mq, n, device=dev, dtype=torch.bfloat16)
         torch.cuda.synchronize()
-        ops = [(ctx.matvec_q4(k, n, 0, 4), 1, wrap(wq), wrap(x), wrap(y), wrap(sq))]
-        work = {"bytes": blocks * 18.0 + 2.0 * k + 2.0 * n}
+        kq = ctx.matmul_q4(k, n, mq) if mq > 1 else ctx.matvec_q4(k, n, 0, 2)
+        ops = [(kq, mq, wrap(wq), wrap(x), wrap(y), wrap(sq))]
+        work = {"bytes": blocks * 18.0 + mq * (2.0 * k + 2.0 * n)}
     elif args.case in ("matvec", "matvec8"):
         m = 1 if args.case == "matvec" else 8
         k, n = 4096, 151936
@@ -583,6 +585,17 @@ def bench_extra(hb, ctx, sel, torch, dev, wrap, pk, rank, world, barrier, max_ov
             qbytes = blocks * 18.0 + 2.0 * k + 2.0 * nq
             q4[f"n{nq}"] = {"us": best[0] * 1e6, "gbs": qbytes / best[0] / 1e9, "frac_hbm": qbytes / best[0] / 1e9 / pk["hbm_gbs"], "form": best[1],
                             "bf16_equivalent_gbs": 2.0 * nq * k / best[0] / 1e9}
+            # the rows of a short block at once (matmul_q4): each block of weights decoded once for all of them
+            for mq in (2, 4, 8):
+                xq = torch.randn(mq, k, device=dev, generator=g).bfloat16()
+                ymq = torch.zeros(mq, nq, device=dev, dtype=torch.bfloat16)
+                kq = ctx.matmul_q4(k, nq, mq)
+                gr = ctx.record([(kq, mq, wrap(w_), wrap(xq), wrap(ymq), wrap(sq)) for w_ in wq])
+                gr.time(3)
+                barrier()
+                sec_q = max_over_ranks(gr.time(20) / (20 * copies_q))
+                gr.free()
+                q4[f"n{nq}"][f"m{mq}_us"] = sec_q * 1e6
             del wq, sq
         out["matvec_q4_4096"] = q4
     except Exception as e:

@@ -6,8 +6,13 @@
 //   matvec_q4   (src/metal/kernels.rs:526-632): y = out(W . x), one activation row. A warp per R rows of W, the lanes
 //               stride over the blocks; per block an FMA chain of q * x in the reference's element order, then
 //               acc = fma(d, part, acc); the lanes summed by the xor butterfly: the reference's bits.
-// The nibbles become floats without an integer-to-float conversion: a byte b placed in the low byte of 0x4B000000
-// is the float 8388608 + b, so (that) - 8388616 is exactly (b ^ 8's value) - 8 once the bytes were xored with 8.
+//   matmul_q4   (src/metal/kernels.rs:983-1071): the same for the 1..8 rows of a short block, each block of weights
+//               decoded once and applied to every row; each row's sum in matvec_q4's order, so the decode step's bits.
+// The nibbles become numbers without an integer-to-float conversion. In dequant_q4 a byte b placed in the low byte
+// of 0x4B000000 is the float 8388608 + b. In the products two nibbles at a time become a pair of f16: a nibble v at
+// bits 0..3 of 0x6400 is the f16 1024 + v, at bits 4..7 it is 1024 + 16 v; one packed f16 operation takes the bias
+// off (exactly: these are small integers) and the widening to f32 runs on the FMA pipe, so the logic pipe spends
+// 6 operations per 8 weights instead of 13.
 #include <algorithm>
 
 #include <cuda_fp16.h>
@@ -41,6 +46,25 @@ __global__ void __launch_bounds__(256) dequant_q4_kernel(const uint4* __restrict
     }
 }
 
+// The eight weights of word `ww` of a block as four f16 pairs: h[0] = (w0, w2), h[1] = (w4, w6), h[2] = (w1, w3),
+// h[3] = (w5, w7), where w_j is weight 8i + j of the block: q_j in -8..7, or with PLUS8 q_j + 8 in 0..15.
+template <bool PLUS8>
+__device__ __forceinline__ void q4_decode_word(uint32_t ww, __half2 (&h)[4]) {
+    const uint32_t wx = ww ^ 0x88888888u, w8 = wx >> 8;
+    const __half2 lo_bias = __float2half2_rn(PLUS8 ? 1024.f : 1032.f), hi_bias = __float2half2_rn(PLUS8 ? -64.f : -72.f);
+    const __half2 sixteenth = __float2half2_rn(0.0625f);
+    auto as_h2 = [](uint32_t v) { return *reinterpret_cast<__half2*>(&v); };
+    h[0] = __hsub2(as_h2((wx & 0x000F000Fu) | 0x64006400u), lo_bias);
+    h[1] = __hfma2(as_h2((wx & 0x00F000F0u) | 0x64006400u), sixteenth, hi_bias);
+    h[2] = __hsub2(as_h2((w8 & 0x000F000Fu) | 0x64006400u), lo_bias);
+    h[3] = __hfma2(as_h2((w8 & 0x00F000F0u) | 0x64006400u), sixteenth, hi_bias);
+}
+// weight j (0..7) of a decoded word, as f32
+__device__ __forceinline__ float q4_elem(const __half2 (&h)[4], int j) {
+    const int idx = (j >= 4 ? 1 : 0) + ((j & 1) ? 2 : 0);
+    return (j & 2) ? __high2float(h[idx]) : __low2float(h[idx]);
+}
+
 // Two IEEE f32 operations in one instruction (two rows of W share every activation, so their chains go side by side).
 __device__ __forceinline__ uint64_t q4_pack2(uint32_t lo, uint32_t hi) {
     uint64_t r;
@@ -50,11 +74,6 @@ __device__ __forceinline__ uint64_t q4_pack2(uint32_t lo, uint32_t hi) {
 __device__ __forceinline__ uint64_t q4_ffma2(uint64_t a, uint64_t b, uint64_t c) {
     uint64_t d;
     asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
-    return d;
-}
-__device__ __forceinline__ uint64_t q4_fadd2(uint64_t a, uint64_t b) {
-    uint64_t d;
-    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
     return d;
 }
 
@@ -75,9 +94,14 @@ constexpr int Q4_WARPS = Q4_THREADS / 32;
 // place (q + 8)·2^s by x·2^-s: the same product exactly (powers of two), so the same bits, without the scaling.
 template <int R, int OUT, bool MASKS>
 __global__ void __launch_bounds__(Q4_THREADS) matvec_q4_kernel(const MatvecQ4Params p) {
+    // x staged in shared memory once per CTA, the four 16-byte chunks of a block xor-swizzled by the block's number:
+    // the 32 lanes read 32 different blocks (64 bytes apart), which straight from L1 costs 16 wavefronts a load
+    extern __shared__ uint4 q4_xs[];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     griddep_launch_dependents();
     griddep_wait();  // x comes from the kernel before this one
+    for (uint32_t j = threadIdx.x; j < p.nblk * 4; j += Q4_THREADS) q4_xs[(j & ~3u) + ((j & 3u) ^ ((j >> 3) & 3u))] = __ldg(p.x + j);
+    __syncthreads();
     for (uint32_t group = blockIdx.x * Q4_WARPS + warp; group < p.groups; group += gridDim.x * Q4_WARPS) {
         size_t base[R];
 #pragma unroll
@@ -97,7 +121,7 @@ __global__ void __launch_bounds__(Q4_THREADS) matvec_q4_kernel(const MatvecQ4Par
             float xs[32];
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-                const uint4 xv = __ldg(p.x + (size_t)b * 4 + i);
+                const uint4 xv = q4_xs[b * 4 + ((uint32_t)i ^ ((b >> 1) & 3u))];
                 const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
@@ -105,33 +129,26 @@ __global__ void __launch_bounds__(Q4_THREADS) matvec_q4_kernel(const MatvecQ4Par
                     xs[8 * i + 2 * c + 1] = __uint_as_float(xw[c] & 0xffff0000u);
                 }
             }
-            // what is subtracted from the byte-in-0x4B000000 float: 8388608 + 8 gives q, 8388608 gives q + 8
-            constexpr float MAGIC = MASKS ? -8388608.0f : -8388616.0f;
             float sx = 0.f;
             if constexpr (MASKS) {
                 sx = xs[0];
 #pragma unroll
                 for (int e = 1; e < 32; ++e) sx = __fadd_rn(sx, xs[e]);
             }
-            // step t of a word's eight: which nibble (low or high) of which byte, and which activation
-            //   plain: weight 8i + byte, then 8i + 4 + byte, byte by byte; masks: the four low nibbles, then the four high
-            auto nib_of = [](int t, bool& high, int& byte) {
-                if (MASKS) { high = t >= 4; byte = t & 3; }
-                else { high = (t & 1) != 0; byte = t >> 1; }
-            };
+            // step t of a word's eight is weight j of the word:
+            //   plain: weight byte, then 4 + byte, byte by byte; masks: the four low nibbles, then the four high
+            auto elem_of = [](int t) { return MASKS ? t : ((t & 1) ? 4 : 0) + (t >> 1); };
             if constexpr (R == 1) {
                 const uint32_t ww[4] = {wv[0].x, wv[0].y, wv[0].z, wv[0].w};
                 float part = 0.f;
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    const uint32_t lo = (ww[i] & 0x0F0F0F0Fu) ^ 0x08080808u, hi = ((ww[i] >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;
+                    __half2 h[4];
+                    q4_decode_word<MASKS>(ww[i], h);
 #pragma unroll
                     for (int t = 0; t < 8; ++t) {
-                        bool high;
-                        int byte;
-                        nib_of(t, high, byte);
-                        const float q = __fadd_rn(__uint_as_float(__byte_perm(high ? hi : lo, 0x4B000000u, 0x7650u + byte)), MAGIC);
-                        part = __fmaf_rn(q, xs[8 * i + (high ? 4 : 0) + byte], part);
+                        const int j = elem_of(t);
+                        part = __fmaf_rn(q4_elem(h, j), xs[8 * i + j], part);
                     }
                 }
                 if constexpr (MASKS) part = __fmaf_rn(-8.0f, sx, part);
@@ -139,24 +156,20 @@ __global__ void __launch_bounds__(Q4_THREADS) matvec_q4_kernel(const MatvecQ4Par
             } else {
                 // rows in pairs: the two chains of a pair run as the two halves of packed f32x2 operations (each half
                 // is the same IEEE operation as the scalar one, in the same order)
-                const uint64_t minus = q4_pack2(__float_as_uint(MAGIC), __float_as_uint(MAGIC));
 #pragma unroll
                 for (int r = 0; r < R; r += 2) {
                     const uint32_t wa[4] = {wv[r].x, wv[r].y, wv[r].z, wv[r].w}, wb[4] = {wv[r + 1].x, wv[r + 1].y, wv[r + 1].z, wv[r + 1].w};
                     uint64_t part2 = 0ull;
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        const uint32_t lo_a = (wa[i] & 0x0F0F0F0Fu) ^ 0x08080808u, hi_a = ((wa[i] >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;
-                        const uint32_t lo_b = (wb[i] & 0x0F0F0F0Fu) ^ 0x08080808u, hi_b = ((wb[i] >> 4) & 0x0F0F0F0Fu) ^ 0x08080808u;
+                        __half2 ha[4], hb_[4];
+                        q4_decode_word<MASKS>(wa[i], ha);
+                        q4_decode_word<MASKS>(wb[i], hb_);
 #pragma unroll
                         for (int t = 0; t < 8; ++t) {
-                            bool high;
-                            int byte;
-                            nib_of(t, high, byte);
-                            const uint32_t xe = __float_as_uint(xs[8 * i + (high ? 4 : 0) + byte]);
-                            const uint64_t q2 = q4_fadd2(q4_pack2(__byte_perm(high ? hi_a : lo_a, 0x4B000000u, 0x7650u + byte),
-                                                                  __byte_perm(high ? hi_b : lo_b, 0x4B000000u, 0x7650u + byte)), minus);
-                            part2 = q4_ffma2(q2, q4_pack2(xe, xe), part2);
+                            const int j = elem_of(t);
+                            const uint32_t xe = __float_as_uint(xs[8 * i + j]);
+                            part2 = q4_ffma2(q4_pack2(__float_as_uint(q4_elem(ha, j)), __float_as_uint(q4_elem(hb_, j))), q4_pack2(xe, xe), part2);
                         }
                     }
                     uint32_t pa, pb;
@@ -183,6 +196,119 @@ __global__ void __launch_bounds__(Q4_THREADS) matvec_q4_kernel(const MatvecQ4Par
                 else {
                     uint16_t* y = reinterpret_cast<uint16_t*>(p.y) + row;
                     *y = (uint16_t)f32_to_bf16(__fadd_rn(bf16_to_f32(*y), round_bf16(a)));
+                }
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------- matmul_q4: 1..8 activation rows
+
+struct MatmulQ4Params {
+    const uint4* w;
+    const uint16_t* sc;
+    const uint16_t* x;
+    uint16_t* y;
+    uint32_t n, nblk, groups, m, ldx, ldy;
+};
+
+// A warp per R rows of W, the lanes over the blocks as in matvec_q4; a block's weights are decoded once and meet the
+// rows of X two at a time: rows 2p and 2p + 1 are the halves of packed f32x2 chains (MP pairs; with an odd m the last
+// pair's second half repeats the last row and is not stored). X is staged in shared memory once per CTA (bf16,
+// [row][16-byte chunk], the four chunks of a block xor-swizzled by the block's number so that the 32 lanes - each on
+// its own block, 64 bytes apart - spread over all the banks).
+template <int R, int MP>
+__global__ void __launch_bounds__(Q4_THREADS, 2) matmul_q4_kernel(const MatmulQ4Params p) {
+    extern __shared__ uint4 q4_xs[];
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t chunks = p.nblk * 4;
+    griddep_launch_dependents();
+    griddep_wait();  // X comes from the kernel before this one
+    for (uint32_t c = threadIdx.x; c < 2 * MP * chunks; c += Q4_THREADS) {
+        const uint32_t r = c / chunks, j = c - r * chunks, b = j >> 2, i = j & 3;
+        const uint32_t src = min(r, p.m - 1);
+        q4_xs[r * chunks + b * 4 + (i ^ ((b >> 1) & 3u))] = __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)src * p.ldx) + j);
+    }
+    __syncthreads();
+    for (uint32_t group = blockIdx.x * Q4_WARPS + warp; group < p.groups; group += gridDim.x * Q4_WARPS) {
+        size_t base[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) base[r] = (size_t)min(group * R + r, p.n - 1) * p.nblk;  // rows past the end read the last row
+        uint64_t acc[R][MP];
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+            for (int q = 0; q < MP; ++q) acc[r][q] = 0ull;
+        for (uint32_t b = lane; b < p.nblk; b += 32) {
+            uint4 wv[R];
+            uint16_t dh[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                wv[r] = __ldcs(p.w + base[r] + b);
+                dh[r] = __ldcs(p.sc + base[r] + b);
+            }
+            uint64_t part[R][MP];
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+#pragma unroll
+                for (int q = 0; q < MP; ++q) part[r][q] = 0ull;
+            const uint32_t sw = (b >> 1) & 3u;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                // the eight activations of this word's weights, of every row: raw bf16 pairs
+                uint4 xv[2 * MP];
+#pragma unroll
+                for (int r = 0; r < 2 * MP; ++r) xv[r] = q4_xs[r * chunks + b * 4 + ((uint32_t)i ^ sw)];
+                __half2 h[R][4];
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                    const uint32_t ww = i == 0 ? wv[r].x : i == 1 ? wv[r].y : i == 2 ? wv[r].z : wv[r].w;
+                    q4_decode_word<false>(ww, h[r]);
+                }
+#pragma unroll
+                for (int t = 0; t < 8; ++t) {
+                    const int j = ((t & 1) ? 4 : 0) + (t >> 1);  // weight `byte`, then 4 + byte, byte by byte
+                    uint64_t x2[MP];
+#pragma unroll
+                    for (int q = 0; q < MP; ++q) {
+                        const uint4 &a = xv[2 * q], &c = xv[2 * q + 1];
+                        const uint32_t wa = (j >> 1) == 0 ? a.x : (j >> 1) == 1 ? a.y : (j >> 1) == 2 ? a.z : a.w;
+                        const uint32_t wc = (j >> 1) == 0 ? c.x : (j >> 1) == 1 ? c.y : (j >> 1) == 2 ? c.z : c.w;
+                        x2[q] = (j & 1) ? q4_pack2(wa & 0xffff0000u, wc & 0xffff0000u) : q4_pack2(wa << 16, wc << 16);
+                    }
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        const uint32_t qf = __float_as_uint(q4_elem(h[r], j));
+                        const uint64_t q2 = q4_pack2(qf, qf);
+#pragma unroll
+                        for (int q = 0; q < MP; ++q) part[r][q] = q4_ffma2(q2, x2[q], part[r][q]);
+                    }
+                }
+            }
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const uint32_t d = __float_as_uint(__half2float(__ushort_as_half(dh[r])));
+                const uint64_t d2 = q4_pack2(d, d);
+#pragma unroll
+                for (int q = 0; q < MP; ++q) acc[r][q] = q4_ffma2(d2, part[r][q], acc[r][q]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const uint32_t row = group * R + r;
+#pragma unroll
+            for (int q = 0; q < MP; ++q) {
+                uint32_t ua, ub;
+                asm("mov.b64 {%0, %1}, %2;" : "=r"(ua), "=r"(ub) : "l"(acc[r][q]));
+                float a = __uint_as_float(ua), c = __uint_as_float(ub);
+#pragma unroll
+                for (int off = 16; off >= 1; off >>= 1) {
+                    a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, off));
+                    c = __fadd_rn(c, __shfl_xor_sync(0xffffffffu, c, off));
+                }
+                if (lane == 0 && row < p.n) {
+                    if ((uint32_t)(2 * q) < p.m) p.y[(size_t)(2 * q) * p.ldy + row] = (uint16_t)f32_to_bf16(a);
+                    if ((uint32_t)(2 * q + 1) < p.m) p.y[(size_t)(2 * q + 1) * p.ldy + row] = (uint16_t)f32_to_bf16(c);
                 }
             }
         }
@@ -242,7 +368,38 @@ struct MatvecQ4 : hb_kernel {
         p.nblk = k / 32;
         p.groups = (n + rows - 1) / rows;
         const uint32_t grid = std::max(1u, std::min<uint32_t>((p.groups + Q4_WARPS - 1) / Q4_WARPS, (uint32_t)ctx->sm_count * 8));
-        HB_CUDA(ctx, launch_kernel(ctx, true, fn, dim3(grid), dim3(Q4_THREADS), 0, p));
+        HB_CUDA(ctx, launch_kernel(ctx, true, fn, dim3(grid), dim3(Q4_THREADS), (size_t)k * 2, p));
+        ctx->launches++;
+        return HB_OK;
+    }
+};
+
+typedef void (*q4mm_fn)(const MatmulQ4Params);
+
+struct MatmulQ4 : hb_kernel {
+    uint32_t k = 0, n = 0, m = 0, ldx = 0, ldy = 0, rows = 0, ctas_per_sm = 1;
+    size_t smem = 0;
+    q4mm_fn fn = nullptr;
+    int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m_now) override {
+        if (na != 4) return fail(ctx, HB_INVALID, name + ": bindings are W (nibbles), X, Y, scales (f16)");
+        if (m_now != m) return fail(ctx, HB_INVALID, name + ": built for " + std::to_string(m) + " rows");
+        const size_t blocks = (size_t)n * (k / 32);
+        if (!range_ok(a[0], blocks * 16) || !range_ok(a[1], ((size_t)(m - 1) * ldx + k) * 2) || !range_ok(a[2], ((size_t)(m - 1) * ldy + n) * 2) || !range_ok(a[3], blocks * 2))
+            return fail(ctx, HB_INVALID, name + ": a bound range is too small");
+        if ((reinterpret_cast<uintptr_t>(a[0].ptr) | reinterpret_cast<uintptr_t>(a[1].ptr)) & 15u) return fail(ctx, HB_INVALID, name + ": W and X must be 16-byte aligned");
+        MatmulQ4Params p{};
+        p.w = static_cast<const uint4*>(a[0].ptr);
+        p.x = static_cast<const uint16_t*>(a[1].ptr);
+        p.y = static_cast<uint16_t*>(a[2].ptr);
+        p.sc = static_cast<const uint16_t*>(a[3].ptr);
+        p.n = n;
+        p.nblk = k / 32;
+        p.groups = (n + rows - 1) / rows;
+        p.m = m;
+        p.ldx = ldx;
+        p.ldy = ldy;
+        const uint32_t grid = std::max(1u, std::min<uint32_t>((p.groups + Q4_WARPS - 1) / Q4_WARPS, (uint32_t)ctx->sm_count * ctas_per_sm));
+        HB_CUDA(ctx, launch_kernel(ctx, true, fn, dim3(grid), dim3(Q4_THREADS), smem, p));
         ctx->launches++;
         return HB_OK;
     }
@@ -269,6 +426,7 @@ int make_matvec_q4(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t out_mode, uint3
     if (rows == 0) rows = 2;
     q4_fn fn = masks ? q4_rows<true>(rows, out_mode) : q4_rows<false>(rows, out_mode);
     if (!fn) return fail(ctx, HB_UNSUPPORTED, "matvec_q4: rows per warp 1, 2 or 4; output Bf16, F32 or Residual");
+    if ((size_t)k * 2 > ctx->smem_optin) return fail(ctx, HB_UNSUPPORTED, "matvec_q4: a row of K = " + std::to_string(k) + " does not fit in shared memory");
     auto kn = std::make_unique<MatvecQ4>();
     kn->k = k;
     kn->n = n;
@@ -278,6 +436,48 @@ int make_matvec_q4(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t out_mode, uint3
     kn->kind = 20;
     kn->nargs = 4;
     kn->name = std::string(masks ? "matvec_q4s_" : "matvec_q4_") + std::to_string(k) + "x" + std::to_string(n) + "_" + out_tag(out_mode) + "_r" + std::to_string(rows);
+    if (hb_kernel* have = find(ctx, kn->name)) {
+        *out = have;
+        return HB_OK;
+    }
+    if ((size_t)k * 2 > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(max dynamic shared memory)");
+    }
+    *out = intern(ctx, std::move(kn));
+    return HB_OK;
+}
+
+int make_matmul_q4(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t m, uint32_t ldx, uint32_t ldy, hb_kernel** out) {
+    *out = nullptr;
+    if (k == 0 || n == 0 || k % 32 != 0 || ldx % 8 != 0) return fail(ctx, HB_UNSUPPORTED, "Q4 block: K = " + std::to_string(k) + ", ldx = " + std::to_string(ldx) + " (K in blocks of 32, rows of X on 16-byte boundaries)");
+    if (m == 0 || m > 8) return fail(ctx, HB_UNSUPPORTED, "matmul_q4: 1 to 8 rows (longer blocks go through dequant_q4 and the GEMM)");
+    if (ldx < k || ldy < n) return fail(ctx, HB_INVALID, "matmul_q4: ldx < k or ldy < n");
+    const uint32_t mp = (m + 1) / 2;
+    // four rows of W per warp while the accumulators fit comfortably, two with three or four pairs of rows of X
+    const uint32_t rows = mp <= 2 ? 4 : 2;
+    q4mm_fn fn = mp == 1 ? matmul_q4_kernel<4, 1> : mp == 2 ? matmul_q4_kernel<4, 2> : mp == 3 ? matmul_q4_kernel<2, 3> : matmul_q4_kernel<2, 4>;
+    const size_t smem = (size_t)2 * mp * k * 2;
+    if (smem > ctx->smem_optin) return fail(ctx, HB_UNSUPPORTED, "matmul_q4: " + std::to_string(2 * mp) + " rows of K = " + std::to_string(k) + " do not fit in shared memory");
+    auto kn = std::make_unique<MatmulQ4>();
+    kn->k = k;
+    kn->n = n;
+    kn->m = m;
+    kn->ldx = ldx;
+    kn->ldy = ldy;
+    kn->rows = rows;
+    kn->smem = smem;
+    kn->ctas_per_sm = (uint32_t)std::max<size_t>(1, std::min<size_t>(2, (size_t)(ctx->smem_optin + 1024) / (smem + 1024)));
+    kn->fn = fn;
+    kn->kind = 21;
+    kn->nargs = 4;
+    kn->name = "matmul_q4_" + std::to_string(k) + "x" + std::to_string(n) + "_m" + std::to_string(m) + "_x" + std::to_string(ldx) + "_y" + std::to_string(ldy);
+    if (hb_kernel* have = find(ctx, kn->name)) {
+        *out = have;
+        return HB_OK;
+    }
+    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin);
+    if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(max dynamic shared memory)");
     *out = intern(ctx, std::move(kn));
     return HB_OK;
 }
@@ -299,6 +499,15 @@ int hb_matvec_q4_get(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t out_mode, uin
     if (!ctx || !out) return hb::fail(ctx, HB_INVALID, "hb_matvec_q4_get: bad argument");
     try {
         return hb::make_matvec_q4(ctx, k, n, out_mode, rows_per_warp, masks, out);
+    } catch (const std::exception& e) {
+        return hb::fail(ctx, HB_BACKEND, e.what());
+    }
+}
+
+int hb_matmul_q4_get(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t m, uint32_t ldx, uint32_t ldy, hb_kernel** out) {
+    if (!ctx || !out) return hb::fail(ctx, HB_INVALID, "hb_matmul_q4_get: bad argument");
+    try {
+        return hb::make_matmul_q4(ctx, k, n, m, ldx, ldy, out);
     } catch (const std::exception& e) {
         return hb::fail(ctx, HB_BACKEND, e.what());
     }

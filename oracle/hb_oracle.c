@@ -579,6 +579,16 @@ void hbo_matvec_q4(const uint8_t* data, const uint16_t* scales, const uint16_t* 
     }
 }
 
+/* src/metal/kernels.rs:983-1071 (matmul_q4): the m rows of a prefill block, each summed as matvec_q4 sums its one. */
+void hbo_matmul_q4(const uint8_t* data, const uint16_t* scales, const uint16_t* x, uint16_t* y, int n, int k, int m, int ldx, int ldy) {
+    uint16_t* row = (uint16_t*)malloc((size_t)n * sizeof(uint16_t));
+    for (int r = 0; r < m; ++r) {
+        hbo_matvec_q4(data, scales, x + (size_t)r * ldx, row, n, k, HBO_OUT_BF16);
+        memcpy(y + (size_t)r * ldy, row, (size_t)n * sizeof(uint16_t));
+    }
+    free(row);
+}
+
 void hbo_matvec_q4s(const uint8_t* data, const uint16_t* scales, const uint16_t* x, void* y, int n, int k, int out) {
     const int nblk = k / 32;
 #pragma omp parallel for schedule(static)

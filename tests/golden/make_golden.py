@@ -544,6 +544,12 @@ def main():
     qx = fill_normal(qk, 0x9E3779B9, 32, 1.0)
     g["q4_x"], g["q4_matvec"] = qx, q4_matvec(qd, qs, qx, qn, qk)
     g["q4s_matvec"] = q4s_matvec(qd, qs, qx, qn, qk)
+    # matmul_q4 (kernels.rs:983-1071): three rows at a row stride of 104, every row summed as matvec_q4 sums its one
+    qX = np.zeros((3, 104), dtype=np.uint16)
+    qX[0, :qk] = qx
+    qX[1:, :] = fill_normal(2 * 104, 0x9E3779B9, 33, 1.0).reshape(2, 104)
+    g["q4_X"] = qX
+    g["q4_matmul"] = np.stack([q4_matvec(qd, qs, qX[r, :qk], qn, qk) for r in range(3)])
     np.savez_compressed(os.path.join(HERE, "golden.npz"), **g)
     print("wrote", os.path.join(HERE, "golden.npz"), "with", len(g), "arrays")
 

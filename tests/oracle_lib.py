@@ -91,6 +91,8 @@ def load(native: bool = False) -> C.CDLL:
     lib.hbo_q4_quantize.argtypes = [_u16p, C.c_int, C.c_int, _u8p, _u16p]
     lib.hbo_q4_dequant.restype = None
     lib.hbo_q4_dequant.argtypes = [_u8p, _u16p, C.c_int, C.c_int, _u16p]
+    lib.hbo_matmul_q4.restype = None
+    lib.hbo_matmul_q4.argtypes = [_u8p, _u16p, _u16p, _u16p, C.c_int, C.c_int, C.c_int, C.c_int, C.c_int]
     for f in (lib.hbo_matvec_q4, lib.hbo_matvec_q4s):
         f.restype = None
         f.argtypes = [_u8p, _u16p, _u16p, C.c_void_p, C.c_int, C.c_int, C.c_int]
@@ -257,6 +259,15 @@ class Oracle:
         out = np.zeros((n, k), dtype=np.uint16)
         self.lib.hbo_q4_dequant(data, scales, n, k, out)
         return out
+
+    def matmul_q4(self, data, scales, x, n, k, ldy=None):
+        """Y [m][ldy] (bf16 bits; columns past n stay 0) for X [m][ldx] (reference matmul_q4, src/metal/kernels.rs:983)."""
+        x = np.ascontiguousarray(x)
+        m, ldx = x.shape
+        ldy = ldy or n
+        y = np.zeros((m, ldy), dtype=np.uint16)
+        self.lib.hbo_matmul_q4(data, scales, x, y, n, k, m, ldx, ldy)
+        return y
 
     def matvec_q4(self, data, scales, x, n, k, out=OUT_BF16, y0=None, masks=False):
         y = np.zeros(n, dtype=np.float32 if out == OUT_F32 else np.uint16) if y0 is None else np.ascontiguousarray(y0).copy()

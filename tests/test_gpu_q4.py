@@ -80,7 +80,52 @@ def test_q4_prefill_is_dequant_then_gemm(ctx, oracle):
     within_contract(oracle, oracle.gemm_f64(x, oracle.q4_dequant(data, scales, n, k)), d_y.download(np.uint16, (m, n)), "Q4 prefill")
 
 
+@pytest.mark.parametrize("m", [1, 2, 3, 4, 5, 6, 7, 8])
+def test_matmul_q4_rows_have_the_decode_steps_bits(ctx, oracle, m):
+    """matmul_q4 (src/metal/kernels.rs:983-1071): every row of a short block comes out as matvec_q4 gives it alone."""
+    if m == 3:
+        n, k = G["q4_w"].shape
+        ldx = G["q4_X"].shape[1]
+        d_w, d_s, d_x, d_y = ctx.to_device(G["q4_data"]), ctx.to_device(G["q4_scales"]), ctx.to_device(G["q4_X"]), ctx.alloc(3 * n * 2 + 16)
+        kern = ctx.matmul_q4(k, n, 3, ldx, n)
+        assert kern.name == f"matmul_q4_{k}x{n}_m3_x{ldx}_y{n}"
+        kern(3, d_w, d_x, d_y, d_s)
+        ctx.sync()
+        assert np.array_equal(d_y.download(np.uint16, (3, n)), G["q4_matmul"])
+    for n, k, pad_x, pad_y in ((1001, 4096, 0, 0), (330, 1024, 8, 3), (5, 32, 24, 1), (64, 12288, 0, 8)):
+        if 2 * ((m + 1) // 2) * k * 2 > 227 * 1024:
+            continue  # the rows of X do not fit in shared memory: the library says so (test_q4_limits)
+        ldx, ldy = k + pad_x, n + pad_y
+        w = oracle.normal((n, k), 6, n, k**-0.5)
+        x = oracle.normal((m, ldx), 7, k + m, 1.0)
+        data, scales = oracle.q4_quantize(w)
+        start = oracle.normal((m, ldy), 8, n, 1.0)  # what lies between the rows of Y must stay
+        d_w, d_s, d_x, d_y = ctx.to_device(data), ctx.to_device(scales), ctx.to_device(x), ctx.to_device(start)
+        ctx.matmul_q4(k, n, m, ldx, ldy)(m, d_w, d_x, d_y, d_s)
+        ctx.sync()
+        got = d_y.download(np.uint16, (m, ldy))
+        want = oracle.matmul_q4(data, scales, x, n, k, ldy)
+        assert np.array_equal(got[:, :n], want[:, :n]), (m, n, k)
+        assert np.array_equal(got[:, n:], start[:, n:]), "padding of Y written"
+        # row r alone through the one-row kernel: the same bits
+        r = m - 1
+        d_y1 = ctx.alloc(max(n * 2, 16))
+        ctx.matvec_q4(k, n, OUT_BF16, 2, 0)(1, d_w, ctx.to_device(np.ascontiguousarray(x[r, :k])), d_y1, d_s)
+        ctx.sync()
+        assert np.array_equal(d_y1.download(np.uint16, (n,)), got[r, :n])
+
+
 def test_q4_limits(ctx, hb200):
+    for bad in (lambda: ctx.matmul_q4(4096, 64, 9), lambda: ctx.matmul_q4(4096, 64, 2, 4100, 64), lambda: ctx.matmul_q4(17408, 64, 8)):
+        with pytest.raises(hb200.HbError) as e:
+            bad()
+        assert e.value.status == hb200.UNSUPPORTED
+    with pytest.raises(hb200.HbError) as e:
+        ctx.matmul_q4(4096, 64, 2, 4088, 64)
+    assert e.value.status == hb200.INVALID
+    with pytest.raises(hb200.HbError) as e:
+        ctx.matmul_q4(4096, 64, 2)(3, ctx.alloc(64 * 2048), ctx.alloc(2 * 8192), ctx.alloc(256), ctx.alloc(64 * 256))
+    assert e.value.status == hb200.INVALID
     for bad in (lambda: ctx.dequant_q4(40, 8), lambda: ctx.matvec_q4(4096, 64, 3, 2), lambda: ctx.matvec_q4(4096, 64, OUT_BF16, 3), lambda: ctx.matvec_q4(4096, 64, 3, 2, 1)):
         with pytest.raises(hb200.HbError) as e:
             bad()

@@ -199,6 +199,8 @@ def test_q4_known_answers(oracle):
     assert np.array_equal(deq[1, :32], w[1, :32])
     assert np.array_equal(oracle.matvec_q4(data, scales, G["q4_x"], n, k), G["q4_matvec"])
     assert np.array_equal(oracle.matvec_q4(data, scales, G["q4_x"], n, k, masks=True), G["q4s_matvec"])
+    assert np.array_equal(oracle.matmul_q4(data, scales, G["q4_X"], n, k), G["q4_matmul"])
+    assert np.array_equal(G["q4_matmul"][0], G["q4_matvec"])
     # quantisation error is small against the weights
     f = lambda a: (a.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
     assert np.abs(f(deq) - f(w)).max() <= np.abs(f(w)).max() / 7.5
