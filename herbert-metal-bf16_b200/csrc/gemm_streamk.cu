@@ -525,6 +525,7 @@ bool s_ready[MAX_DEVICES];
 extern "C" int hb_gemm_static_scratch(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t out, uint32_t m, hb_range w, hb_range x, hb_range y) {
     using namespace hb;
     if (!ctx) return HB_INVALID;
+    bind(ctx);
     if (k == 0 || n == 0 || m == 0) return fail(ctx, HB_INVALID, "hb_gemm_static_scratch: k, n and m must be positive");
     if (k % 8 != 0) return fail(ctx, HB_UNSUPPORTED, "hb_gemm_static_scratch: k must be a multiple of 8");
     if (out > HB_OUT_SWIGLU || (out == HB_OUT_SWIGLU && n % 2 != 0)) return fail(ctx, HB_INVALID, "hb_gemm_static_scratch: bad output mode");

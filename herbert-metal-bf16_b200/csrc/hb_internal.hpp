@@ -60,6 +60,11 @@ struct hb_ctx {
 namespace hb {
 
 int fail(hb_ctx* ctx, int code, const std::string& msg);
+// Makes the context's device the calling thread's current one (a process may hold contexts on several devices).
+inline void bind(hb_ctx* ctx) {
+    int cur = -1;
+    if (cudaGetDevice(&cur) != cudaSuccess || cur != ctx->device) cudaSetDevice(ctx->device);
+}
 int cuda_fail(hb_ctx* ctx, cudaError_t e, const char* what);
 #define HB_CUDA(ctx, call)                                        \
     do {                                                          \

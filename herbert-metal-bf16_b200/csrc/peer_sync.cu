@@ -112,6 +112,7 @@ extern "C" int hb_set_peer_wait_ms(hb_ctx* ctx, uint32_t ms) {
 extern "C" int hb_peer_sync_get(hb_ctx* ctx, uint32_t words, uint32_t world, uint32_t rank, hb_kernel** res) {
     if (!ctx || !res) return hb::fail(ctx, HB_INVALID, "hb_peer_sync_get: bad argument");
     try {
+        hb::bind(ctx);
         return hb::make_peer_sync(ctx, words, world, rank, res);
     } catch (const std::exception& e) {
         return hb::fail(ctx, HB_BACKEND, e.what());

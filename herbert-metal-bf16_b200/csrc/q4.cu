@@ -489,6 +489,7 @@ extern "C" {
 int hb_dequant_q4_get(hb_ctx* ctx, uint32_t k, uint32_t n, hb_kernel** out) {
     if (!ctx || !out) return hb::fail(ctx, HB_INVALID, "hb_dequant_q4_get: bad argument");
     try {
+        hb::bind(ctx);
         return hb::make_dequant_q4(ctx, k, n, out);
     } catch (const std::exception& e) {
         return hb::fail(ctx, HB_BACKEND, e.what());
@@ -498,6 +499,7 @@ int hb_dequant_q4_get(hb_ctx* ctx, uint32_t k, uint32_t n, hb_kernel** out) {
 int hb_matvec_q4_get(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t out_mode, uint32_t rows_per_warp, uint32_t masks, hb_kernel** out) {
     if (!ctx || !out) return hb::fail(ctx, HB_INVALID, "hb_matvec_q4_get: bad argument");
     try {
+        hb::bind(ctx);
         return hb::make_matvec_q4(ctx, k, n, out_mode, rows_per_warp, masks, out);
     } catch (const std::exception& e) {
         return hb::fail(ctx, HB_BACKEND, e.what());
@@ -507,6 +509,7 @@ int hb_matvec_q4_get(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t out_mode, uin
 int hb_matmul_q4_get(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t m, uint32_t ldx, uint32_t ldy, hb_kernel** out) {
     if (!ctx || !out) return hb::fail(ctx, HB_INVALID, "hb_matmul_q4_get: bad argument");
     try {
+        hb::bind(ctx);
         return hb::make_matmul_q4(ctx, k, n, m, ldx, ldy, out);
     } catch (const std::exception& e) {
         return hb::fail(ctx, HB_BACKEND, e.what());

@@ -311,6 +311,7 @@ extern "C" {
 int hb_rmsnorm_get(hb_ctx* ctx, uint32_t d, float eps, uint32_t plus_one, hb_kernel** out) {
     if (!ctx || !out) return hb::fail(ctx, HB_INVALID, "hb_rmsnorm_get: bad argument");
     try {
+        hb::bind(ctx);
         return hb::make_rmsnorm(ctx, d, eps, plus_one, out);
     } catch (const std::exception& e) {
         return hb::fail(ctx, HB_BACKEND, e.what());
@@ -320,6 +321,7 @@ int hb_rmsnorm_get(hb_ctx* ctx, uint32_t d, float eps, uint32_t plus_one, hb_ker
 int hb_moe_out_get(hb_ctx* ctx, uint32_t d, hb_kernel** out) {
     if (!ctx || !out) return hb::fail(ctx, HB_INVALID, "hb_moe_out_get: bad argument");
     try {
+        hb::bind(ctx);
         return hb::make_moe_out(ctx, d, out);
     } catch (const std::exception& e) {
         return hb::fail(ctx, HB_BACKEND, e.what());
@@ -329,6 +331,7 @@ int hb_moe_out_get(hb_ctx* ctx, uint32_t d, hb_kernel** out) {
 int hb_argmax_get(hb_ctx* ctx, uint32_t n, uint32_t rows_max, hb_kernel** out) {
     if (!ctx || !out) return hb::fail(ctx, HB_INVALID, "hb_argmax_get: bad argument");
     try {
+        hb::bind(ctx);
         return hb::make_argmax(ctx, n, rows_max, out);
     } catch (const std::exception& e) {
         return hb::fail(ctx, HB_BACKEND, e.what());

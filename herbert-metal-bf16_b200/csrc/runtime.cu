@@ -3,6 +3,7 @@
 #include <algorithm>
 #include <cstring>
 #include <mutex>
+#include <new>
 
 #include "hb_internal.hpp"
 
@@ -82,6 +83,7 @@ hb_kernel* find(hb_ctx* ctx, const std::string& name) {
 using hb::fail;
 
 #define HB_GUARD_BEGIN try {
+#define HB_GUARD_BIND(ctx) try { hb::bind(ctx);
 #define HB_GUARD_END(ctx)                                                        \
     }                                                                            \
     catch (const std::exception& e) { return hb::fail(ctx, HB_BACKEND, e.what()); } \
@@ -110,12 +112,18 @@ int hb_open(int device, hb_ctx** out) {
     ctx->sm_count = prop.multiProcessorCount;
     ctx->smem_optin = prop.sharedMemPerBlockOptin;
     ctx->device_name = prop.name;
-    if ((e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking)) != cudaSuccess) return hb::cuda_fail(nullptr, e, "cudaStreamCreate");
+    auto undo = [&](cudaError_t err, const char* what) {  // a half-made context: give back what exists
+        if (ctx->status_dev) cudaFree(ctx->status_dev);
+        if (ctx->ev0) cudaEventDestroy(ctx->ev0);
+        if (ctx->ev1) cudaEventDestroy(ctx->ev1);
+        if (ctx->stream) cudaStreamDestroy(ctx->stream);
+        return hb::cuda_fail(nullptr, err, what);
+    };
+    if ((e = cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking)) != cudaSuccess) return undo(e, "cudaStreamCreate");
     ctx->own_stream = true;
-    cudaEventCreate(&ctx->ev0);
-    cudaEventCreate(&ctx->ev1);
-    if ((e = cudaMalloc(&ctx->status_dev, 8 * sizeof(uint32_t))) != cudaSuccess) return hb::cuda_fail(nullptr, e, "cudaMalloc(status)");
-    cudaMemset(ctx->status_dev, 0, 8 * sizeof(uint32_t));
+    if ((e = cudaEventCreate(&ctx->ev0)) != cudaSuccess || (e = cudaEventCreate(&ctx->ev1)) != cudaSuccess) return undo(e, "cudaEventCreate");
+    if ((e = cudaMalloc(&ctx->status_dev, 8 * sizeof(uint32_t))) != cudaSuccess) return undo(e, "cudaMalloc(status)");
+    if ((e = cudaMemset(ctx->status_dev, 0, 8 * sizeof(uint32_t))) != cudaSuccess) return undo(e, "cudaMemset(status)");
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult q;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess && q == cudaDriverEntryPointSuccess)
@@ -179,6 +187,7 @@ int hb_set_alloc_limit(hb_ctx* ctx, size_t bytes) {
 
 int hb_alloc(hb_ctx* ctx, size_t bytes, void** dptr) {
     if (!ctx || !dptr) return fail(ctx, HB_INVALID, "hb_alloc: bad argument");
+    hb::bind(ctx);
     *dptr = nullptr;
     if (bytes == 0) return fail(ctx, HB_INVALID, "hb_alloc: zero bytes");
     if (ctx->alloc_limit && ctx->allocated + bytes > ctx->alloc_limit)
@@ -198,6 +207,7 @@ int hb_alloc(hb_ctx* ctx, size_t bytes, void** dptr) {
 
 int hb_upload(hb_ctx* ctx, void* dst, const void* src, size_t bytes) {
     if (!ctx || !dst || !src) return fail(ctx, HB_INVALID, "hb_upload: bad argument");
+    hb::bind(ctx);
     HB_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, ctx->stream));
     HB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return HB_OK;
@@ -205,6 +215,7 @@ int hb_upload(hb_ctx* ctx, void* dst, const void* src, size_t bytes) {
 
 int hb_download(hb_ctx* ctx, void* dst, const void* src, size_t bytes) {
     if (!ctx || !dst || !src) return fail(ctx, HB_INVALID, "hb_download: bad argument");
+    hb::bind(ctx);
     HB_CUDA(ctx, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, ctx->stream));
     HB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return hb::check_status(ctx);
@@ -213,6 +224,7 @@ int hb_download(hb_ctx* ctx, void* dst, const void* src, size_t bytes) {
 // ---- peer memory ------------------------------------------------------------------------------
 int hb_ipc_export(hb_ctx* ctx, void* dptr, void* handle64) {
     if (!ctx || !dptr || !handle64) return fail(ctx, HB_INVALID, "hb_ipc_export: bad argument");
+    hb::bind(ctx);
     static_assert(sizeof(cudaIpcMemHandle_t) == HB_IPC_HANDLE_BYTES, "handle size");
     if (std::find(ctx->allocs.begin(), ctx->allocs.end(), dptr) == ctx->allocs.end())
         return fail(ctx, HB_INVALID, "hb_ipc_export: not the start of an hb_alloc allocation");
@@ -224,6 +236,7 @@ int hb_ipc_export(hb_ctx* ctx, void* dptr, void* handle64) {
 
 int hb_ipc_open(hb_ctx* ctx, const void* handle64, void** dptr) {
     if (!ctx || !handle64 || !dptr) return fail(ctx, HB_INVALID, "hb_ipc_open: bad argument");
+    hb::bind(ctx);
     cudaIpcMemHandle_t h;
     memcpy(&h, handle64, sizeof h);
     void* p = nullptr;
@@ -266,7 +279,8 @@ int lane_stream(hb_ctx* ctx, int lane, cudaStream_t* out) {
 
 int hb_event_new(hb_ctx* ctx, hb_event** out) {
     if (!ctx || !out) return fail(ctx, HB_INVALID, "hb_event_new: bad argument");
-    auto* e = new hb_event;
+    auto* e = new (std::nothrow) hb_event;
+    if (!e) return fail(ctx, HB_OOM, "hb_event_new: out of memory");
     cudaError_t st = cudaEventCreateWithFlags(&e->ev, cudaEventDisableTiming);
     if (st != cudaSuccess) {
         delete e;
@@ -310,6 +324,7 @@ int hb_event_sync(hb_ctx* ctx, const hb_event* ev) {
 
 int hb_upload_async(hb_ctx* ctx, void* dst, const void* src, size_t bytes) {
     if (!ctx || !dst || !src) return fail(ctx, HB_INVALID, "hb_upload_async: bad argument");
+    hb::bind(ctx);
     cudaStream_t s;
     int r = lane_stream(ctx, HB_LANE_UPLOAD, &s);
     if (r != HB_OK) return r;
@@ -319,6 +334,7 @@ int hb_upload_async(hb_ctx* ctx, void* dst, const void* src, size_t bytes) {
 
 int hb_download_async(hb_ctx* ctx, void* dst, const void* src, size_t bytes) {
     if (!ctx || !dst || !src) return fail(ctx, HB_INVALID, "hb_download_async: bad argument");
+    hb::bind(ctx);
     cudaStream_t s;
     int r = lane_stream(ctx, HB_LANE_DOWNLOAD, &s);
     if (r != HB_OK) return r;
@@ -358,6 +374,7 @@ int hb_memset(hb_ctx* ctx, void* dst, int value, size_t bytes) {
 
 int hb_sync(hb_ctx* ctx) {
     if (!ctx) return HB_INVALID;
+    hb::bind(ctx);
     HB_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     return hb::check_status(ctx);
 }
@@ -368,7 +385,7 @@ const char* hb_kernel_name(const hb_kernel* k) { return k ? k->name.c_str() : ""
 
 int hb_launch(hb_ctx* ctx, const hb_kernel* k, const hb_range* args, int nargs, uint32_t m) {
     if (!ctx || !k || !args) return fail(ctx, HB_INVALID, "hb_launch: bad argument");
-    HB_GUARD_BEGIN
+    HB_GUARD_BIND(ctx)
     int r = const_cast<hb_kernel*>(k)->launch(ctx, args, nargs, m);
     return r;
     HB_GUARD_END(ctx)
@@ -385,6 +402,7 @@ int hb_run(hb_ctx* ctx, const hb_op* ops, int nops) {
 
 int hb_time(hb_ctx* ctx, const hb_op* ops, int nops, int reps, double* gpu_seconds) {
     if (!ctx || !gpu_seconds || reps < 1) return fail(ctx, HB_INVALID, "hb_time: bad argument");
+    hb::bind(ctx);
     HB_CUDA(ctx, cudaEventRecord(ctx->ev0, ctx->stream));
     for (int r = 0; r < reps; ++r) {
         int s = hb_run(ctx, ops, nops);
@@ -413,6 +431,7 @@ struct hb_graph {
 
 int hb_graph_record(hb_ctx* ctx, const hb_op* ops, int nops, hb_graph** out) {
     if (!ctx || !ops || nops < 1 || !out) return fail(ctx, HB_INVALID, "hb_graph_record: bad argument");
+    hb::bind(ctx);
     *out = nullptr;
     for (int i = 0; i < nops; ++i) {
         if (!ops[i].kernel) return fail(ctx, HB_INVALID, "hb_graph_record: an op without a kernel");
@@ -432,7 +451,11 @@ int hb_graph_record(hb_ctx* ctx, const hb_op* ops, int nops, hb_graph** out) {
         return st;
     }
     if (e != cudaSuccess) return hb::cuda_fail(ctx, e, "cudaStreamEndCapture");
-    auto* hg = new hb_graph;
+    auto* hg = new (std::nothrow) hb_graph;
+    if (!hg) {
+        cudaGraphDestroy(g);
+        return fail(ctx, HB_OOM, "hb_graph_record: out of memory");
+    }
     hg->graph = g;
     hg->kernels = recorded;
     e = cudaGraphInstantiate(&hg->exec, g, 0);
@@ -447,6 +470,7 @@ int hb_graph_record(hb_ctx* ctx, const hb_op* ops, int nops, hb_graph** out) {
 
 int hb_graph_launch(hb_ctx* ctx, hb_graph* g) {
     if (!ctx || !g) return fail(ctx, HB_INVALID, "hb_graph_launch: bad argument");
+    hb::bind(ctx);
     HB_CUDA(ctx, cudaGraphLaunch(g->exec, ctx->stream));
     ctx->launches += g->kernels;
     return HB_OK;
@@ -454,6 +478,7 @@ int hb_graph_launch(hb_ctx* ctx, hb_graph* g) {
 
 int hb_graph_time(hb_ctx* ctx, hb_graph* g, int reps, double* gpu_seconds) {
     if (!ctx || !g || !gpu_seconds || reps < 1) return fail(ctx, HB_INVALID, "hb_graph_time: bad argument");
+    hb::bind(ctx);
     HB_CUDA(ctx, cudaEventRecord(ctx->ev0, ctx->stream));
     for (int r = 0; r < reps; ++r) {
         HB_CUDA(ctx, cudaGraphLaunch(g->exec, ctx->stream));
@@ -478,31 +503,31 @@ int hb_graph_free(hb_ctx* ctx, hb_graph* g) {
 
 int hb_gemm_get(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
     if (!ctx || !d || !out) return fail(ctx, HB_INVALID, "hb_gemm_get: bad argument");
-    HB_GUARD_BEGIN
+    HB_GUARD_BIND(ctx)
     return hb::make_gemm(ctx, d, out);
     HB_GUARD_END(ctx)
 }
 int hb_matvec_get(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out) {
     if (!ctx || !d || !out) return fail(ctx, HB_INVALID, "hb_matvec_get: bad argument");
-    HB_GUARD_BEGIN
+    HB_GUARD_BIND(ctx)
     return hb::make_matvec(ctx, d, out);
     HB_GUARD_END(ctx)
 }
 int hb_swiglu_get(hb_ctx* ctx, uint32_t n, hb_kernel** out) {
     if (!ctx || !out) return fail(ctx, HB_INVALID, "hb_swiglu_get: bad argument");
-    HB_GUARD_BEGIN
+    HB_GUARD_BIND(ctx)
     return hb::make_swiglu_rows(ctx, n, out);
     HB_GUARD_END(ctx)
 }
 int hb_route_get(hb_ctx* ctx, uint32_t experts, uint32_t top_k, hb_kernel** out) {
     if (!ctx || !out) return fail(ctx, HB_INVALID, "hb_route_get: bad argument");
-    HB_GUARD_BEGIN
+    HB_GUARD_BIND(ctx)
     return hb::make_route(ctx, experts, top_k, out);
     HB_GUARD_END(ctx)
 }
 int hb_moe_sort_get(hb_ctx* ctx, uint32_t experts, uint32_t top_k, uint32_t rows_max, uint32_t bm, hb_kernel** out) {
     if (!ctx || !out) return fail(ctx, HB_INVALID, "hb_moe_sort_get: bad argument");
-    HB_GUARD_BEGIN
+    HB_GUARD_BIND(ctx)
     return hb::make_moe_sort(ctx, experts, top_k, rows_max, bm, out);
     HB_GUARD_END(ctx)
 }
@@ -512,31 +537,31 @@ uint32_t hb_moe_tiles(uint32_t rows_max, uint32_t top_k, uint32_t experts, uint3
 }
 int hb_moe_gather_get(hb_ctx* ctx, uint32_t h, uint32_t top_k, hb_kernel** out) {
     if (!ctx || !out) return fail(ctx, HB_INVALID, "hb_moe_gather_get: bad argument");
-    HB_GUARD_BEGIN
+    HB_GUARD_BIND(ctx)
     return hb::make_moe_gather(ctx, h, top_k, out);
     HB_GUARD_END(ctx)
 }
 int hb_ep_dispatch_get(hb_ctx* ctx, uint32_t h, uint32_t top_k, uint32_t experts, uint32_t world, uint32_t rank, uint32_t cap, hb_kernel** out) {
     if (!ctx || !out) return fail(ctx, HB_INVALID, "hb_ep_dispatch_get: bad argument");
-    HB_GUARD_BEGIN
+    HB_GUARD_BIND(ctx)
     return hb::make_ep_move(ctx, false, h, top_k, experts, world, rank, cap, out);
     HB_GUARD_END(ctx)
 }
 int hb_ep_return_get(hb_ctx* ctx, uint32_t h, uint32_t top_k, uint32_t experts, uint32_t world, uint32_t rank, uint32_t cap, hb_kernel** out) {
     if (!ctx || !out) return fail(ctx, HB_INVALID, "hb_ep_return_get: bad argument");
-    HB_GUARD_BEGIN
+    HB_GUARD_BIND(ctx)
     return hb::make_ep_move(ctx, true, h, top_k, experts, world, rank, cap, out);
     HB_GUARD_END(ctx)
 }
 int hb_ep_plan_get(hb_ctx* ctx, uint32_t experts, uint32_t world, uint32_t rank, uint32_t bm, uint32_t cap, hb_kernel** out) {
     if (!ctx || !out) return fail(ctx, HB_INVALID, "hb_ep_plan_get: bad argument");
-    HB_GUARD_BEGIN
+    HB_GUARD_BIND(ctx)
     return hb::make_ep_plan(ctx, experts, world, rank, bm, cap, out);
     HB_GUARD_END(ctx)
 }
 int hb_moe_combine_get(hb_ctx* ctx, uint32_t d, uint32_t top_k, uint32_t f32_sum, hb_kernel** out) {
     if (!ctx || !out) return fail(ctx, HB_INVALID, "hb_moe_combine_get: bad argument");
-    HB_GUARD_BEGIN
+    HB_GUARD_BIND(ctx)
     return hb::make_moe_combine(ctx, d, top_k, f32_sum, out);
     HB_GUARD_END(ctx)
 }

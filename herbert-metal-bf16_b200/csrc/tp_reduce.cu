@@ -137,6 +137,7 @@ int make_tp_reduce(hb_ctx* ctx, uint32_t n, uint32_t out, uint32_t world, uint32
 extern "C" int hb_tp_reduce_get(hb_ctx* ctx, uint32_t n, uint32_t out, uint32_t world, uint32_t rank, hb_kernel** res) {
     if (!ctx || !res) return hb::fail(ctx, HB_INVALID, "hb_tp_reduce_get: bad argument");
     try {
+        hb::bind(ctx);
         return hb::make_tp_reduce(ctx, n, out, world, rank, false, res);
     } catch (const std::exception& e) {
         return hb::fail(ctx, HB_BACKEND, e.what());
@@ -146,6 +147,7 @@ extern "C" int hb_tp_reduce_get(hb_ctx* ctx, uint32_t n, uint32_t out, uint32_t 
 extern "C" int hb_tp_sum_get(hb_ctx* ctx, uint32_t n, uint32_t out, uint32_t world, uint32_t rank, hb_kernel** res) {
     if (!ctx || !res) return hb::fail(ctx, HB_INVALID, "hb_tp_sum_get: bad argument");
     try {
+        hb::bind(ctx);
         return hb::make_tp_reduce(ctx, n, out, world, rank, true, res);
     } catch (const std::exception& e) {
         return hb::fail(ctx, HB_BACKEND, e.what());

@@ -13,7 +13,9 @@
  * src/core/error.rs:9-27). hb_last_error() gives the message of the last
  * failure on a context. A context is not thread-safe: one context, one host
  * thread, one CUDA stream (reference: one engine, one queue,
- * src/metal/gpu.rs:59-74). Buffers are device memory; the reference's
+ * src/metal/gpu.rs:59-74). A process may hold contexts on several devices:
+ * every call that allocates, copies, builds or launches makes its context's
+ * device the calling thread's current one. Buffers are device memory; the reference's
  * host-visible shared buffers become explicit hb_upload/hb_download copies.
  * All matrices are row-major; bf16 values are passed as uint16_t bits.
  */
