@@ -779,20 +779,24 @@ def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks)
                 wgu_l = (torch.randn(2 * ip, h, device=dev, generator=gl) * h**-0.5).bfloat16()
                 wd_l = (torch.randn(h, ip, device=dev, generator=gl) * inter**-0.5).bfloat16()
                 flop = 2.0 * m * (2 * inter) * h + 2.0 * m * h * inter
-                # the sum across ranks, the rounding, the residual and the distribution of Y in the library's tp_reduce
-                # kernel over peer memory (the production form) ...
+                # the production form: the down GEMM's epilogue stores every block of rows of its f32 partial into the
+                # staging buffer of the rank that sums it (reduce-scatter under the GEMM), tp_sum adds the staged blocks
+                # in rank order, rounds, adds the residual and stores the bf16 rows into every rank's Y ...
                 tp = D.TpPeer(hb, ctx, rank, world, m, h)
                 D.tp_peer_connect(tp)
                 tp.set_y(y)
                 got = D.tp_ffn_peer(tp, x, wgu_l, wd_l).clone()
                 sec = timed(lambda: D.tp_ffn_peer(tp, x, wgu_l, wd_l), 3, 10)
                 sec_ns = timed(lambda: D.tp_ffn_peer(tp, x, wgu_l, wd_l, nccl_sync=True), 3, 10) if world > 1 else sec
-                sec_push = sec
-                if world > 1:  # the push form: the down GEMM stores the blocks of its partial into their owners' buffers
-                    tpl = D.TpPeer(hb, ctx, rank, world, m, h, push=True)
+                sec_pull = sec
+                if world > 1:  # the pull form: the partial stays local, tp_reduce loads the blocks it sums from the peers
+                    tpl = D.TpPeer(hb, ctx, rank, world, m, h, push=False)
                     D.tp_peer_connect(tpl)
                     tpl.set_y(y)
-                    sec_push = timed(lambda: D.tp_ffn_peer(tpl, x, wgu_l, wd_l), 3, 10)
+                    got_pull = D.tp_ffn_peer(tpl, x, wgu_l, wd_l).clone()
+                    sec_pull = timed(lambda: D.tp_ffn_peer(tpl, x, wgu_l, wd_l), 3, 10)
+                    if not torch.equal(got_pull, got):
+                        raise RuntimeError("tp_ffn: the push and the pull form differ")
                     barrier()
                     tpl.close()
                 # ... and the same FFN with an NCCL all-reduce of the f32 partials and a separate epilogue (the baseline form)
@@ -808,9 +812,9 @@ def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks)
                 out["tp_ffn_27b_m2048"] = {"n_gpus": world, "us": sec * 1e6, "tflops_total": flop / sec / 1e12, "tflops_per_gpu": flop / sec / 1e12 / world,
                                            "frac_of_measured_peak_per_gpu": flop / sec / 1e12 / world / pk["bf16_tflops"],
                                            "nvlink_bytes_per_gpu": (m * h * 4 + m * h * 2) * (world - 1) // world // 1 if world > 1 else 0, "scaling": "strong",
-                                           "exchange": "tp_reduce kernel: peer loads of the f32 partials in rank order, one rounding, residual, peer stores of bf16 Y; "
-                                                       "2 barrier kernels (no NCCL call in the step)",
-                                           "with_nccl_barriers_us": sec_ns * 1e6, "gemm_push_form_us": sec_push * 1e6,
+                                           "exchange": "down GEMM epilogue stores its f32 partial block by block into the summing ranks' memory (NVLink, under the GEMM); "
+                                                       "tp_sum: rank-order sum, one rounding, residual, peer stores of bf16 Y; 2 barrier kernels (no NCCL call in the step)",
+                                           "with_nccl_barriers_us": sec_ns * 1e6, "pull_form_us": sec_pull * 1e6,
                                            "nccl_all_reduce_form_us": sec_nccl * 1e6, "equals_nccl_form_bitwise": same,
                                            "max_abs_diff_vs_nccl_form": diff, "max_abs_value": scale}
                 del wgu_l, wd_l

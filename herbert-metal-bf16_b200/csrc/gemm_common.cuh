@@ -100,4 +100,36 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t row, u
     }
 }
 
+// Out::F32 into row blocks that may be other GPUs' memory: the 32 rows x 32 columns a warp holds (one row per lane)
+// go through 4 KB of the warp's shared memory and leave as whole 128-byte row segments, four rows per store
+// instruction. Stored lane by lane they would be 32 separate 16-byte writes per instruction, which NVLink carries
+// one small packet each. `scratch` is the shared-memory address of the warp's 4 KB (16-byte chunks, xor-swizzled).
+__device__ __forceinline__ void store_chunk_f32_blocks(const GemmParams& p, uint32_t row0, uint32_t col0, const uint32_t (&v)[32], uint32_t scratch) {
+    const uint32_t lane = threadIdx.x & 31u;
+#pragma unroll
+    for (uint32_t j = 0; j < 8; ++j)
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(scratch + ((lane * 8u + (j ^ (lane & 7u))) << 4)), "r"(v[4 * j]), "r"(v[4 * j + 1]),
+                     "r"(v[4 * j + 2]), "r"(v[4 * j + 3])
+                     : "memory");
+    __syncwarp();
+    const uint32_t c = lane & 7u;
+#pragma unroll
+    for (uint32_t i = 0; i < 8; ++i) {
+        const uint32_t r = 4u * i + (lane >> 3);
+        uint4 q;
+        asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "r"(scratch + ((r * 8u + (c ^ (r & 7u))) << 4)));
+        const uint32_t row = row0 + r, col = col0 + 4u * c;
+        if (row < p.m && col < p.n_out) {
+            float* y = reinterpret_cast<float*>(p.y_shards[row / p.shard_rows]) + (size_t)(row % p.shard_rows) * p.n_out + col;
+            if (p.vec_ok && col + 4u <= p.n_out) {
+                *reinterpret_cast<uint4*>(y) = q;
+            } else {
+                const uint32_t w[4] = {q.x, q.y, q.z, q.w};
+                for (uint32_t e = 0; e < 4u && col + e < p.n_out; ++e) y[e] = __uint_as_float(w[e]);
+            }
+        }
+    }
+    __syncwarp();
+}
+
 }  // namespace hb

@@ -204,7 +204,10 @@ gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                     uint32_t v[32];
                     tmem_ld_32x32(t_addr + c * 32, v);
                     tmem_ld_wait();
-                    store_chunk<OUT>(p, row, tn * PAIR_BN + c * 32, v, v);
+                    if (OUT == HB_OUT_F32 && p.y_shards)  // row blocks, possibly on other GPUs: whole row segments per store
+                        store_chunk_f32_blocks(p, row - lane, tn * PAIR_BN + c * 32, v, smem_base + S * PAIR_STAGE_BYTES + q * 4096u);
+                    else
+                        store_chunk<OUT>(p, row, tn * PAIR_BN + c * 32, v, v);
                 }
             }
             tc_fence_before();
@@ -310,7 +313,9 @@ int make_gemm_pair(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
     if (d->y_shards > 16) return fail(ctx, HB_UNSUPPORTED, "gemm: at most 16 row blocks of Y");
     pair_fn fn = pair_pick(d->out);
     const size_t budget = std::min<size_t>(ctx->smem_optin, 227 * 1024) - 2048;
-    const uint32_t max_stages = (uint32_t)std::min<size_t>(budget / PAIR_STAGE_BYTES, MAX_STAGES);
+    // a Y in row blocks: 16 KB behind the ring (4 KB per epilogue warp) for the transposing store
+    const size_t extra = d->y_shards > 1 ? 4 * 4096 : 0;
+    const uint32_t max_stages = (uint32_t)std::min<size_t>((budget - extra) / PAIR_STAGE_BYTES, MAX_STAGES);
     const uint32_t stages = d->stages ? d->stages : max_stages;
     if (stages < 2 || stages > max_stages) return fail(ctx, HB_UNSUPPORTED, "gemm: stage count does not fit");
     auto k = std::make_unique<PairGemm>();
@@ -318,7 +323,7 @@ int make_gemm_pair(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
     k->d.tile_n = 256;
     k->fn = fn;
     k->stages = stages;
-    k->smem = (size_t)stages * PAIR_STAGE_BYTES + 1024;
+    k->smem = (size_t)stages * PAIR_STAGE_BYTES + extra + 1024;
     k->kind = 1;
     k->nargs = 3;
     char nm[160];

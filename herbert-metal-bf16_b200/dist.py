@@ -455,16 +455,17 @@ def ep_moe_peer(state: EpPeer, x_local, scores_local, wgu_local, wd_local, group
 class TpPeer:
     """One rank of the peer-memory FFN: the partial-product buffer, the output Y and their peer tables.
 
-    push = False (the default): the partial stays local and the sum pulls the blocks it needs from the peers
-    (tp_reduce). push = True: the down GEMM stores every block of rows of its partial straight into the staging buffer
-    of the rank that sums that block, tile by tile while it computes (hb_gemm_desc.y_shards), and the sum reads local
-    memory only. Measured on two B200s the pull form is the faster one (480 against 537 us for the 27B-class FFN): the
-    GEMM's epilogue warps stall on the NVLink stores and hold the tensor pipe back by more than the pull costs."""
+    push = True (the default with more than one rank): the down GEMM stores every block of rows of its partial straight
+    into the staging buffer of the rank that sums that block, tile by tile while it computes (hb_gemm_desc.y_shards),
+    and the sum (tp_sum) reads local memory only: the reduce-scatter's traffic crosses NVLink under the GEMM.
+    push = False: the partial stays local and the sum pulls the blocks it needs from the peers (tp_reduce).
+    Measured for the 27B-class FFN: 449 against 483 us on two B200s, 220 against 259 us on eight. (The push form needs
+    its stores to leave as whole 128-byte row segments: written one 16-byte piece per lane they were 537 and 437 us.)"""
 
     def __init__(self, hb, ctx, rank: int, world: int, m: int, h: int, out: int = OUT_RESIDUAL, device=None, push: bool | None = None):
         self.hb, self.ctx, self.rank, self.world, self.m, self.h = hb, ctx, rank, world, m, h
         dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
-        self.push = bool(push) and world > 1
+        self.push = (True if push is None else bool(push)) and world > 1
         self.rows_per = (m + world - 1) // world
         # acc: the whole partial [m][h] (pull), or the staging [world][rows_per][h] of the blocks this rank sums (push)
         self.pb = PeerBuffers(ctx, rank, world, {"acc": max(m, world * self.rows_per) * h * 4, "y": m * h * 2}, dev)

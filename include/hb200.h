@@ -178,7 +178,8 @@ typedef struct {
                             is a device array u64[P] of the blocks' addresses (16-byte aligned, row stride n), which may be
                             other GPUs' memory opened with hb_ipc_open: the GEMM of a row-parallel projection stores every
                             block of its partial product straight into the buffer of the rank that sums it, tile by tile
-                            while it computes (no reference counterpart) */
+                            while it computes; the CTA-pair form stores whole 128-byte row segments (the form to use when
+                            the blocks are peers' memory). No reference counterpart */
 } hb_gemm_desc;
 int hb_gemm_get(hb_ctx* ctx, const hb_gemm_desc* desc, hb_kernel** out);
 
