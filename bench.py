@@ -786,7 +786,9 @@ def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks)
                 D.tp_peer_connect(tp)
                 tp.set_y(y)
                 got = D.tp_ffn_peer(tp, x, wgu_l, wd_l).clone()
-                sec = timed(lambda: D.tp_ffn_peer(tp, x, wgu_l, wd_l), 3, 10)
+                # (the step's kernels recorded once and replayed with one call; also launched one by one from the host)
+                sec = timed(lambda: D.tp_ffn_peer(tp, x, wgu_l, wd_l, recorded=True), 3, 10)
+                sec_loop = timed(lambda: D.tp_ffn_peer(tp, x, wgu_l, wd_l), 3, 10) if world > 1 else sec
                 sec_ns = timed(lambda: D.tp_ffn_peer(tp, x, wgu_l, wd_l, nccl_sync=True), 3, 10) if world > 1 else sec
                 sec_pull = sec
                 if world > 1:  # the pull form: the partial stays local, tp_reduce loads the blocks it sums from the peers
@@ -794,7 +796,7 @@ def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks)
                     D.tp_peer_connect(tpl)
                     tpl.set_y(y)
                     got_pull = D.tp_ffn_peer(tpl, x, wgu_l, wd_l).clone()
-                    sec_pull = timed(lambda: D.tp_ffn_peer(tpl, x, wgu_l, wd_l), 3, 10)
+                    sec_pull = timed(lambda: D.tp_ffn_peer(tpl, x, wgu_l, wd_l, recorded=True), 3, 10)
                     if not torch.equal(got_pull, got):
                         raise RuntimeError("tp_ffn: the push and the pull form differ")
                     barrier()
@@ -814,7 +816,7 @@ def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks)
                                            "nvlink_bytes_per_gpu": (m * h * 4 + m * h * 2) * (world - 1) // world // 1 if world > 1 else 0, "scaling": "strong",
                                            "exchange": "down GEMM epilogue stores its f32 partial block by block into the summing ranks' memory (NVLink, under the GEMM); "
                                                        "tp_sum: rank-order sum, one rounding, residual, peer stores of bf16 Y; 2 barrier kernels (no NCCL call in the step)",
-                                           "with_nccl_barriers_us": sec_ns * 1e6, "pull_form_us": sec_pull * 1e6,
+                                           "launched_one_by_one_us": sec_loop * 1e6, "with_nccl_barriers_us": sec_ns * 1e6, "pull_form_us": sec_pull * 1e6,
                                            "nccl_all_reduce_form_us": sec_nccl * 1e6, "equals_nccl_form_bitwise": same,
                                            "max_abs_diff_vs_nccl_form": diff, "max_abs_value": scale}
                 del wgu_l, wd_l
@@ -831,7 +833,11 @@ def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks)
                 st = D.EpPeer(hb, ctx, rank, world, rl, h, mi, E, top_k, bm)
                 D.ep_peer_connect(st)
                 got = D.ep_moe_peer(st, xs, sc, wgu_l, wd_l).clone()
-                sec = timed(lambda: D.ep_moe_peer(st, xs, sc, wgu_l, wd_l), 3, 20)
+                sec = timed(lambda: D.ep_moe_peer(st, xs, sc, wgu_l, wd_l, recorded=True), 4, 20)
+                got_rec = D.ep_moe_peer(st, xs, sc, wgu_l, wd_l, recorded=True).clone()
+                if not torch.equal(got_rec, got):
+                    raise RuntimeError("ep_moe: the replayed step differs from the step launched kernel by kernel")
+                sec_loop = timed(lambda: D.ep_moe_peer(st, xs, sc, wgu_l, wd_l), 3, 20) if world > 1 else sec
                 sec_ns = timed(lambda: D.ep_moe_peer(st, xs, sc, wgu_l, wd_l, nccl_sync=True), 3, 20) if world > 1 else sec
                 # ... and the same block with the rows exchanged by NCCL all-to-all, host-known counts (the baseline form)
                 ref = D.ep_moe(be, xs, sc, wgu_l, wd_l, E, top_k, mi, bm)
@@ -840,8 +846,8 @@ def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks)
                 barrier()
                 st.close()
                 out["moe_ep_2048tok"] = {"n_gpus": world, "us": sec * 1e6, "weight_gbs_total": wbytes / sec / 1e9, "tokens_per_s": m / sec, "scaling": "strong",
-                                         "tile_rows": bm, "exchange": "peer-memory stores and loads in ep_dispatch / ep_return, offsets all-gather + 2 barriers as kernels (no NCCL call in the step)",
-                                         "with_nccl_barriers_us": sec_ns * 1e6,
+                                         "tile_rows": bm, "exchange": "peer-memory stores and loads in ep_dispatch / ep_return, offsets all-gather + 2 barriers as kernels (no NCCL call in the step); the 13 kernels replayed as one recorded sequence",
+                                         "launched_one_by_one_us": sec_loop * 1e6, "with_nccl_barriers_us": sec_ns * 1e6,
                                          "nccl_all_to_all_form_us": sec_nccl * 1e6, "equals_nccl_form_bitwise": same}
                 if world > 1:
                     # weak scaling: 2048 tokens on every rank (the experts still partitioned), peer-memory form. The
@@ -851,7 +857,7 @@ def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks)
                         sw = torch.randn(m, E, device=dev, generator=gl).bfloat16()
                         stw = D.EpPeer(hb, ctx, rank, world, m, h, mi, E, top_k, bm, cap=min(m * top_k * world, 4 * m * top_k))
                         D.ep_peer_connect(stw)
-                        sec_w = timed(lambda: D.ep_moe_peer(stw, xw, sw, wgu_l, wd_l), 3, 10)
+                        sec_w = timed(lambda: D.ep_moe_peer(stw, xw, sw, wgu_l, wd_l, recorded=True), 4, 10)
                         ctx.sync()
                         barrier()
                         stw.close()

@@ -266,6 +266,41 @@ def _view(buf, shape, typestr: str, device) -> torch.Tensor:
     return torch.as_tensor(h, device=device)
 
 
+def _launch_now(kernel, m, *ranges):
+    kernel(m, *ranges)
+
+
+class _Recorded:
+    """The kernel calls of one step of a peer-memory block, taken down instead of launched, then replayed as one
+    recorded sequence (hb_graph_record): a step is 6 to 13 short kernels, and enqueueing them one by one from the
+    host takes longer than the GPU needs to run them."""
+
+    def __init__(self, ctx, *emitters):
+        self.ctx, self.emitters, self.graphs = ctx, emitters, {}
+
+    def run(self, key, step):
+        """step() makes the kernel calls of the step through the emitters; the first time a key is seen they are
+        recorded, afterwards (and then too) the recording is launched."""
+        if key not in self.graphs:
+            ops = []
+            for e in self.emitters:
+                e.emit = lambda kernel, m, *ranges: ops.append((kernel, m, *ranges))
+            try:
+                step()
+            finally:
+                for e in self.emitters:
+                    e.emit = _launch_now
+            self.graphs[key] = self.ctx.record(ops)
+        else:
+            step(replay=True)
+        self.graphs[key].launch()
+
+    def close(self):
+        for g in self.graphs.values():
+            g.free()
+        self.graphs = {}
+
+
 class PeerBuffers:
     """Named buffers of this rank that the other ranks of the node read and write, with the device tables
     (u64[world], one address per rank) the kernels take. A flag array for the barrier kernel is always there."""
@@ -277,7 +312,7 @@ class PeerBuffers:
         self.tables = {name: torch.zeros(world, device=device, dtype=torch.int64) for name in self.sizes}
         self.opened = []
         self.emulated = True
-        self.epoch = 0
+        self.emit = _launch_now  # what a kernel call does: launch it, or (while a step is recorded) note it
 
     def handles(self) -> dict:
         return {name: self.ctx.ipc_export(buf) for name, buf in self.local.items()}
@@ -318,8 +353,7 @@ class PeerBuffers:
             return
         if not hasattr(self, "_k_barrier"):
             self._k_barrier = self.ctx.peer_sync(0, self.world, self.rank)
-        self.epoch += 1
-        self._k_barrier(self.epoch, self.table("flags"))
+        self.emit(self._k_barrier, 1, self.table("flags"))  # (the barrier numbers itself)
 
     def allgather(self, payload: torch.Tensor, name: str) -> None:
         """payload (int32 words) -> slot `rank` of buffer `name` on every rank, then the barrier."""
@@ -328,8 +362,7 @@ class PeerBuffers:
             self._k_gather = {}
         if words not in self._k_gather:
             self._k_gather[words] = self.ctx.peer_sync(words, self.world, self.rank)
-        self.epoch += 1
-        self._k_gather[words](self.epoch, self.table("flags"), self.ctx.wrap(payload.data_ptr(), words * 4), self.table(name))
+        self.emit(self._k_gather[words], 1, self.table("flags"), self.ctx.wrap(payload.data_ptr(), words * 4), self.table(name))
 
     def close(self) -> None:
         for b in self.opened:
@@ -382,6 +415,8 @@ class EpPeer:
         self.k_down = ctx.gemm(mi, h, OUT_BF16, rows_mode=hb.ROWS_SCATTER, **kw)
         self.k_return = ctx.ep_return(h, top_k, experts, world, rank, self.cap)
         self.k_combine = ctx.moe_combine(h, top_k)
+        self.emit = _launch_now
+        self.recorded = _Recorded(ctx, self, self.pb)
 
     def _w(self, t):
         return self.ctx.wrap(t.data_ptr(), max(t.numel() * t.element_size(), 1))
@@ -395,26 +430,27 @@ class EpPeer:
         self.pb.connect(local_peers=[p.pb for p in local_peers])
 
     def close(self) -> None:
+        self.recorded.close()
         self.pb.close()
 
     # ---- the phases
     def phase_sort(self, x, scores) -> None:
         self.x = x
         self.parity ^= 1
-        self.k_route(self.rows, self._w(scores), self._w(self.route))
-        self.k_sort(self.rows, self._w(self.route), self._w(self.list), self._w(self.tiles), self._w(self.offs))
+        self.emit(self.k_route, self.rows, self._w(scores), self._w(self.route))
+        self.emit(self.k_sort, self.rows, self._w(self.route), self._w(self.list), self._w(self.tiles), self._w(self.offs))
 
     def phase_dispatch(self) -> None:  # offs_all holds every rank's offsets
-        self.k_dispatch(self.rows, self._w(self.x), self.pb.table("recv"), self._w(self.list), self._w(self.offs_all))
+        self.emit(self.k_dispatch, self.rows, self._w(self.x), self.pb.table("recv"), self._w(self.list), self._w(self.offs_all))
 
     def phase_experts(self, wgu_local, wd_local) -> None:  # every rank's dispatch has finished
-        self.k_plan(1, self._w(self.offs_all), self._w(self.rlist), self._w(self.rtiles))
-        self.k_gate_up(self.cap, self._w(wgu_local), self.recv, self._w(self.ehb), self._w(self.rlist), self._w(self.rtiles))
-        self.k_down(self.cap, self._w(wd_local), self._w(self.ehb), self.ey_recv, self._w(self.rlist), self._w(self.rtiles))
+        self.emit(self.k_plan, 1, self._w(self.offs_all), self._w(self.rlist), self._w(self.rtiles))
+        self.emit(self.k_gate_up, self.cap, self._w(wgu_local), self.recv, self._w(self.ehb), self._w(self.rlist), self._w(self.rtiles))
+        self.emit(self.k_down, self.cap, self._w(wd_local), self._w(self.ehb), self.ey_recv, self._w(self.rlist), self._w(self.rtiles))
 
     def phase_return(self):  # every rank's expert GEMMs have finished
-        self.k_return(self.rows, self.pb.table("ey"), self._w(self.ey), self._w(self.list), self._w(self.offs_all))
-        self.k_combine(self.rows, self._w(self.ey), self._w(self.route), self._w(self.out))
+        self.emit(self.k_return, self.rows, self.pb.table("ey"), self._w(self.ey), self._w(self.list), self._w(self.offs_all))
+        self.emit(self.k_combine, self.rows, self._w(self.ey), self._w(self.route), self._w(self.out))
         return self.out
 
 
@@ -423,10 +459,25 @@ def ep_peer_connect(state: EpPeer, group=None) -> None:
     state.pb.connect_group(group)
 
 
-def ep_moe_peer(state: EpPeer, x_local, scores_local, wgu_local, wd_local, group=None, nccl_sync: bool = False):
+def ep_moe_peer(state: EpPeer, x_local, scores_local, wgu_local, wd_local, group=None, nccl_sync: bool = False, recorded: bool = False):
     """The sparse block for this rank's token rows with the exchange through peer memory; returns out [rows][h].
     nccl_sync = True orders the steps with NCCL collectives (an all-gather and two one-word all-reduces) instead
-    of the library's barrier kernel; the data path is the same."""
+    of the library's barrier kernel; the data path is the same. recorded = True (several ranks, the library's
+    barriers): the step's 13 kernels are recorded once per (buffers, parity) and replayed with one call."""
+    multi = state.world > 1
+    if recorded and multi and not nccl_sync and not state.pb.emulated:
+        def step(replay=False):
+            if replay:
+                state.parity ^= 1  # what phase_sort does: the two offset buffers take turns
+                return
+            _ep_step(state, x_local, scores_local, wgu_local, wd_local, group, False)
+        key = (state.parity ^ 1, x_local.data_ptr(), scores_local.data_ptr(), wgu_local.data_ptr(), wd_local.data_ptr())
+        state.recorded.run(key, step)
+        return state.out
+    return _ep_step(state, x_local, scores_local, wgu_local, wd_local, group, nccl_sync)
+
+
+def _ep_step(state: EpPeer, x_local, scores_local, wgu_local, wd_local, group, nccl_sync):
     multi = state.world > 1
     state.phase_sort(x_local, scores_local)
     if not multi:
@@ -475,6 +526,8 @@ class TpPeer:
         self.k_reduce = ctx.tp_sum(h, out, world, rank) if self.push else ctx.tp_reduce(h, out, world, rank)
         self.push_table = torch.zeros(world, device=dev, dtype=torch.int64)  # where this rank's block for owner d goes
         self.kernels = {}
+        self.emit = _launch_now
+        self.recorded = _Recorded(ctx, self, self.pb)
 
     def _w(self, t):
         return self.ctx.wrap(t.data_ptr(), max(t.numel() * t.element_size(), 1))
@@ -488,6 +541,7 @@ class TpPeer:
         self.push_table.copy_(self.pb.tables["acc"] + slot)
 
     def close(self) -> None:
+        self.recorded.close()
         self.pb.close()
 
     def set_y(self, y: torch.Tensor) -> None:
@@ -507,11 +561,11 @@ class TpPeer:
             self.kernels[key] = (self.ctx.gemm(h, 2 * ip, OUT_SWIGLU, rows_max=self.m, cta_pair=1),
                                  self.ctx.gemm(ip, h, OUT_F32, rows_max=self.m, cta_pair=1, y_shards=self.world if self.push else 0), hmid)
         k_gu, k_down, hmid = self.kernels[key]
-        k_gu(m, self._w(wgu_local), self._w(x), self._w(hmid))
-        k_down(m, self._w(wd_local), self._w(hmid), self._w(self.push_table) if self.push else self.acc)
+        self.emit(k_gu, m, self._w(wgu_local), self._w(x), self._w(hmid))
+        self.emit(k_down, m, self._w(wd_local), self._w(hmid), self._w(self.push_table) if self.push else self.acc)
 
     def phase_reduce(self) -> None:  # every rank's partial is complete (push: has arrived)
-        self.k_reduce(self.m, self.acc if self.push else self.pb.table("acc"), self.pb.table("y"))
+        self.emit(self.k_reduce, self.m, self.acc if self.push else self.pb.table("acc"), self.pb.table("y"))
 
 
 def tp_peer_connect(state: TpPeer, group=None) -> None:
@@ -519,8 +573,20 @@ def tp_peer_connect(state: TpPeer, group=None) -> None:
     state._after_connect()
 
 
-def tp_ffn_peer(state: TpPeer, x, wgu_local, wd_local, group=None, nccl_sync: bool = False):
-    """state.y <- bf16(state.y + bf16(sum over ranks of H_r . Wd_r^T)) on every rank; returns the view of Y."""
+def tp_ffn_peer(state: TpPeer, x, wgu_local, wd_local, group=None, nccl_sync: bool = False, recorded: bool = False):
+    """state.y <- bf16(state.y + bf16(sum over ranks of H_r . Wd_r^T)) on every rank; returns the view of Y.
+    recorded = True (several ranks, the library's barriers): the step is recorded once per set of buffers and replayed."""
+    multi = state.world > 1
+    if recorded and multi and not nccl_sync and not state.pb.emulated:
+        def step(replay=False):
+            if not replay:
+                _tp_step(state, x, wgu_local, wd_local, group, False)
+        state.recorded.run((x.data_ptr(), wgu_local.data_ptr(), wd_local.data_ptr()), step)
+        return state.y_view()
+    return _tp_step(state, x, wgu_local, wd_local, group, nccl_sync)
+
+
+def _tp_step(state: TpPeer, x, wgu_local, wd_local, group, nccl_sync):
     multi = state.world > 1
     state.phase_gemms(x, wgu_local, wd_local)
     if multi:

@@ -113,9 +113,10 @@ int hb_ipc_open(hb_ctx* ctx, const void* handle64, void** dptr);
 int hb_ipc_close(hb_ctx* ctx, void* dptr);
 
 /* A barrier among the ranks of one node (one process and one GPU each) as a kernel on the stream, with an optional
- * all-gather of a small table riding on it. Every rank owns flags u32[world] (zeroed) in a buffer the others have
- * opened; `peers_flags` is a device array u64[world] of their addresses. hb_launch's m is the barrier's number:
- * 1, 2, 3, ... in the same sequence on every rank. With words > 0 the kernel first copies `payload` u32[words] into
+ * all-gather of a small table riding on it. Every rank owns flags u32[64] (256 bytes, zeroed) in a buffer the others
+ * have opened; `peers_flags` is a device array u64[world] of their addresses. The barrier numbers itself (word 32 of
+ * a rank's own flags counts the barriers it has passed: 1, 2, 3, ... in the same sequence on every rank), so
+ * hb_launch's m is ignored and a recorded launch can be replayed. With words > 0 the kernel first copies `payload` u32[words] into
  * slot `rank` of every rank's gather buffer u32[world][words] (`peers_gather`: their addresses); use two gather
  * buffers in turn, a rank may start the next gather while another still reads this one. What a rank wrote before
  * the barrier, to its own or a peer's memory, is visible to all after it. A rank that does not arrive within a few
@@ -332,7 +333,7 @@ int hb_time(hb_ctx* ctx, const hb_op* ops, int nops, int reps, double* gpu_secon
  * 10-200 us each, and enqueueing them one by one costs the host about as long as the GPU takes to run them. The
  * reference encodes its ops into one command buffer per step (src/metal/gpu.rs:151-221) for the same reason. The
  * bound ranges and m are fixed at recording. Kernels whose launches carry a host-side counter cannot be recorded
- * (the stream-K GEMM, hb_gemm_static_scratch, hb_peer_sync_get): HB_UNSUPPORTED. */
+ * (the stream-K GEMM, hb_gemm_static_scratch): HB_UNSUPPORTED. */
 /* Overlapped launches (off by default): the decode kernels (hb_matvec_get in all its forms, hb_rmsnorm_get) are then
  * launched with programmatic stream serialization: a kernel may start while the one before it on the stream is
  * still finishing, sets up, prefetches weights, and waits inside for its predecessor's completion before it reads

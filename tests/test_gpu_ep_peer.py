@@ -181,13 +181,16 @@ def _two_process_worker(rank, world, port, repo, result):
         rpr, epr = s["m"] // world, s["E"] // world
         st = d.EpPeer(hb, ctx, rank, world, rpr, s["h"], s["mi"], s["E"], s["top_k"], s["bm"])
         d.ep_peer_connect(st)
-        for it in range(6):  # the library's barrier kernel, then the NCCL form of the same steps
-            out = d.ep_moe_peer(st, xt[rank * rpr : (rank + 1) * rpr].contiguous(), st_[rank * rpr : (rank + 1) * rpr].contiguous(),
-                                wgut[rank * epr * 2 * s["mi"] : (rank + 1) * epr * 2 * s["mi"]], wdt[rank * epr * s["h"] : (rank + 1) * epr * s["h"]],
-                                nccl_sync=it >= 4)
+        xs, ss = xt[rank * rpr : (rank + 1) * rpr].contiguous(), st_[rank * rpr : (rank + 1) * rpr].contiguous()
+        wl, dl = wgut[rank * epr * 2 * s["mi"] : (rank + 1) * epr * 2 * s["mi"]], wdt[rank * epr * s["h"] : (rank + 1) * epr * s["h"]]
+        # the library's barrier kernel launched step by step (0, 1), the step recorded and replayed (2..6: both
+        # parities recorded, then replayed), then the NCCL form of the same steps
+        for it in range(9):
+            out = d.ep_moe_peer(st, xs, ss, wl, dl, nccl_sync=it >= 7, recorded=2 <= it < 7)
             stream.synchronize()
             ctx.sync()
             ok = ok and bool(torch.equal(out, want[rank * rpr : (rank + 1) * rpr]))
+        ok = ok and len(st.recorded.graphs) == 2
         dist.barrier()
         st.close()
         # the tensor-parallel FFN: both ranks end with the same Y, equal to the all-reduce form
@@ -199,14 +202,16 @@ def _two_process_worker(rank, world, port, repo, result):
         for push in (False, True):  # the partial pulled by the summing kernel; pushed by the GEMM's epilogue
             tp = d.TpPeer(hb, ctx, rank, world, m, h, push=push)
             d.tp_peer_connect(tp)
-            for it in range(3):
+            x2d = t16(x2).cuda()
+            for it in range(6):  # step by step, recorded then replayed (1..4), with NCCL barriers
                 tp.set_y(t16(y0).cuda())
                 dist.barrier()
-                y = d.tp_ffn_peer(tp, t16(x2).cuda(), a, b, nccl_sync=it == 2)
+                y = d.tp_ffn_peer(tp, x2d, a, b, nccl_sync=it == 5, recorded=1 <= it < 5)
                 stream.synchronize()
                 ctx.sync()
                 ok = ok and bool(torch.equal(y, y_ref))
                 dist.barrier()
+            ok = ok and len(tp.recorded.graphs) == 1
             tp.close()
     flag = torch.tensor([1 if ok else 0], device="cuda")
     dist.all_reduce(flag, op=dist.ReduceOp.MIN)
