@@ -17,8 +17,10 @@
 // A CTA therefore only ever waits for lower-numbered CTAs, which published their partials as their first act:
 // no cycle, whatever the order blocks are scheduled in. The sum of a split tile is (own k-range) + partials in a
 // fixed order: deterministic, but a different association than the unsplit kernel's (within the contract).
-// The scratch buffer and flags belong to the context (19.4 MB for 148 SMs and 128x256 tiles); launches are
-// told apart by an epoch number, so flags are never reset.
+// The scratch buffer and flags belong to the context (19.4 MB for 148 SMs and 128x256 tiles). A flag is set once
+// per launch by the warp that publishes a partial and read by exactly one warp (the same-numbered warp of the tile's
+// owner), which puts it back to 0: every launch finds the flags clear, nothing on the host counts launches, and a
+// recorded launch can be replayed. (After a wait that ran out the host clears them: see check_status.)
 #include <algorithm>
 #include <cstring>
 
@@ -236,6 +238,8 @@ gemm_bf16_tn_streamk_kernel(const __grid_constant__ CUtensorMap tm_x, const __gr
                             asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(sp.flags + j * 4 + q) : "memory");
                             if (v != sp.epoch && clock64() - t0 > HB_WAIT_LIMIT_CYCLES) got = false;
                         } while (v != sp.epoch && got);
+                        // this warp is the flag's only reader: taken, it goes back to 0 for the next launch
+                        if (got) asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(sp.flags + j * 4 + q), "r"(0u) : "memory");
                     }
                     asm volatile("fence.proxy.async;" ::: "memory");  // the bulk copies below read what those CTAs wrote
                 }
@@ -435,7 +439,7 @@ struct StreamKGemm : hb_kernel {
         sp.total_units = (uint32_t)units;
         sp.scratch = ctx->sk_scratch;
         sp.flags = ctx->sk_flags;
-        sp.epoch = ++ctx->sk_epoch;
+        sp.epoch = 1;
         const uint32_t grid = (uint32_t)std::min<uint64_t>(units, (uint64_t)ctx->sm_count);  // a whole wave or more: every SM
         fn<<<grid, GEMM_THREADS, smem, ctx->stream>>>(tm_x, tm_w, sp);
         HB_CUDA(ctx, cudaGetLastError());
@@ -469,7 +473,6 @@ int make_gemm_streamk(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
     k->stages = stages;
     k->smem = stages * stage_bytes + 1024;
     k->kind = 1;
-    k->replayable = false;  // every launch takes a new epoch of the scratch flags
     k->nargs = 3;
     char nm[160];
     snprintf(nm, sizeof nm, "gemm_sk_%ux%u_%s%s_t128x%u_s%u", d->k, d->n, out_tag(d->out), d->m_first ? "_mf" : "", bn, stages);

@@ -59,6 +59,8 @@ int check_status(hb_ctx* ctx) {
         if (st[0] == 2) snprintf(msg, sizeof msg, "kernel status 2: block %u read a table that does not fit its buffers (%u against %u)", st[1], st[2], st[3]);
         else snprintf(msg, sizeof msg, "kernel status %u: block %u gave up waiting at point %u (detail %u)", st[0], st[1], st[2], st[3]);
         cudaMemsetAsync(ctx->status_dev, 0, sizeof st, ctx->stream);
+        // a stream-K launch that gave up may have left flags of partial tiles set: clear them for the next launch
+        if (ctx->sk_flags) cudaMemsetAsync(ctx->sk_flags, 0, (size_t)ctx->sm_count * 4 * sizeof(uint32_t), ctx->stream);
         cudaStreamSynchronize(ctx->stream);
         return fail(ctx, HB_KERNEL, msg);
     }

@@ -332,8 +332,9 @@ int hb_time(hb_ctx* ctx, const hb_op* ops, int nops, int reps, double* gpu_secon
 /* A sequence recorded once and replayed with one call (a CUDA graph): the decode step launches a dozen kernels of
  * 10-200 us each, and enqueueing them one by one costs the host about as long as the GPU takes to run them. The
  * reference encodes its ops into one command buffer per step (src/metal/gpu.rs:151-221) for the same reason. The
- * bound ranges and m are fixed at recording. Kernels whose launches carry a host-side counter cannot be recorded
- * (the stream-K GEMM, hb_gemm_static_scratch): HB_UNSUPPORTED. */
+ * bound ranges and m are fixed at recording. Every kernel of this library can be recorded (none of them carries a
+ * host-side counter: the stream-K GEMM's flags are cleared by their reader, the peer barrier counts itself);
+ * hb_gemm_static_scratch is a direct call, not an hb_kernel, and is not recordable. */
 /* Overlapped launches (off by default): the decode kernels (hb_matvec_get in all its forms, hb_rmsnorm_get) are then
  * launched with programmatic stream serialization: a kernel may start while the one before it on the stream is
  * still finishing, sets up, prefetches weights, and waits inside for its predecessor's completion before it reads

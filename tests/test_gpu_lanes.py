@@ -74,7 +74,7 @@ def test_events_order_lanes(ctx, hb200, oracle):
 
 
 def test_recorded_sequence_replays(ctx, hb200, oracle):
-    # three kernels recorded once: replays give the bits of the one-by-one launches; kernels that carry a counter refuse
+    # three kernels recorded once: replays give the bits of the one-by-one launches
     m, k, n = 8, 1024, 512
     x, w, y0 = gemm_inputs(oracle, m, k, 2 * n)
     d_w, d_x = ctx.to_device(w), ctx.to_device(x)
@@ -94,10 +94,21 @@ def test_recorded_sequence_replays(ctx, hb200, oracle):
     assert np.array_equal(d_h.download(np.uint16, (m, n)), want_h) and np.array_equal(d_y.download(np.uint16, (m, 2 * n)), want_y)
     assert g.time(5) > 0
     g.free()
-    with pytest.raises(hb200.HbError) as e:
-        ctx.record([(ctx.gemm(k, n, OUT_BF16, rows_max=64, stream_k=1), m, d_w, d_x, d_h)])
-    assert e.value.status == hb200.UNSUPPORTED and "cannot be replayed" in e.value.message
+    # the stream-K GEMM (partial tiles through scratch and flags that their one reader clears) replays too
+    m2, k2, n2 = 64, 4096, 768
+    x2, w2, _ = gemm_inputs(oracle, m2, k2, n2)
+    d_w2, d_x2, d_y2 = ctx.to_device(w2), ctx.to_device(x2), ctx.alloc(m2 * n2 * 2)
+    sk = ctx.gemm(k2, n2, OUT_BF16, rows_max=64, tile_n=256, stream_k=1)
+    sk(m2, d_w2, d_x2, d_y2)
     ctx.sync()
+    want2 = d_y2.download(np.uint16, (m2, n2))
+    g2 = ctx.record([(sk, m2, d_w2, d_x2, d_y2)])
+    for _ in range(3):
+        ctx.memset(d_y2, 0)
+        g2.launch()
+        ctx.sync()
+        assert np.array_equal(d_y2.download(np.uint16, (m2, n2)), want2)
+    g2.free()
 
 
 def test_overlapped_launches_change_nothing_but_time(hb200, oracle):
