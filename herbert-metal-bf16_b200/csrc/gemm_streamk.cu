@@ -484,7 +484,7 @@ int make_gemm_streamk(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
         return HB_OK;
     }
     if (!ctx->sk_scratch) {
-        // one slot per SM, sized for the widest tile; flags start at 0 and epochs at 1
+        // one slot per SM, sized for the widest tile; flags start at 0 and every launch leaves them at 0
         void* s = nullptr;
         void* f = nullptr;
         int r = hb_alloc(ctx, (size_t)ctx->sm_count * BM * 256 * sizeof(float), &s);

@@ -54,7 +54,6 @@ struct hb_ctx {
     // scratch of the stream-K GEMM: f32 partial tiles [sm_count][128][256] and their flags, made on first use
     float* sk_scratch = nullptr;
     uint32_t* sk_flags = nullptr;
-    uint32_t sk_epoch = 0;
 };
 
 namespace hb {
