@@ -18,8 +18,8 @@ struct hb_kernel {
     std::string name;
     int kind = 0;  // HB_KIND_*
     int nargs = 0;
-    // false for kernels whose launches differ by a host-side counter (the epoch of the stream-K scratch flags, the
-    // number of a peer barrier): replaying a recorded launch would repeat the counter
+    // false for a kernel whose launches would differ by a host-side counter (replaying a recorded launch would repeat
+    // it); none of the kernels built today needs one
     bool replayable = true;
     virtual ~hb_kernel() = default;
     // Validates the bound ranges for `m` rows and enqueues the kernel on ctx->stream.
