@@ -56,3 +56,58 @@ def test_exchange_reproduces_the_single_sort(world, rows, experts, top_k, bm):
     # and so are the tile tables, once the local expert ids and row offsets are made global
     want = [tuple(int(v) for v in want_tiles[1 + 3 * t : 4 + 3 * t]) for t in range(int(want_tiles[0]))]
     assert tiles_rows == want
+
+
+def test_recorded_step_is_taken_down_once_and_replayed():
+    """dist._Recorded: the first run of a key collects the step's kernel calls from every emitter and records them;
+    later runs only tell the step to advance its own state (replay=True) and launch the recording."""
+    d = load_dist()
+
+    class FakeGraph:
+        def __init__(self, ops):
+            self.ops, self.launched, self.freed = list(ops), 0, False
+
+        def launch(self):
+            self.launched += 1
+
+        def free(self):
+            self.freed = True
+
+    class FakeCtx:
+        def __init__(self):
+            self.recorded = []
+
+        def record(self, ops):
+            g = FakeGraph(ops)
+            self.recorded.append(g)
+            return g
+
+    class Emitter:
+        emit = staticmethod(d._launch_now)
+
+    launched_directly = []
+    kernel = lambda m, *ranges: launched_directly.append((m, ranges))
+    a, b, ctx = Emitter(), Emitter(), FakeCtx()
+    rec = d._Recorded(ctx, a, b)
+    state = {"parity": 0, "replays": 0}
+
+    def step(replay=False):
+        state["parity"] ^= 1
+        if replay:
+            state["replays"] += 1
+            return
+        a.emit(kernel, 7, "x")
+        b.emit(kernel, 1, "flags")
+        a.emit(kernel, 7, "y")
+
+    for call in range(4):
+        rec.run(("key", state["parity"] ^ 1), step)
+    assert launched_directly == []                       # nothing was launched kernel by kernel
+    assert len(ctx.recorded) == 2                        # one recording per parity
+    assert [op[1:] for op in ctx.recorded[0].ops] == [(7, "x"), (1, "flags"), (7, "y")]
+    assert [g.launched for g in ctx.recorded] == [2, 2] and state["replays"] == 2
+    assert a.emit is d._launch_now and b.emit is d._launch_now  # the emitters launch again once the step is recorded
+    a.emit(kernel, 3, "z")
+    assert launched_directly == [(3, ("z",))]
+    rec.close()
+    assert all(g.freed for g in ctx.recorded) and rec.graphs == {}
