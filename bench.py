@@ -32,6 +32,23 @@ HIDDEN, INTER, ROWS = 4096, 12288, 2048
 # (name, K, N, out) of the layer's four projections; out: 0 Bf16, 2 Residual, 3 Swiglu
 LAYER = [("qkv", HIDDEN, 6144, 0), ("o_proj", HIDDEN, HIDDEN, 2), ("gate_up", HIDDEN, 2 * INTER, 3), ("down", INTER, HIDDEN, 2)]
 STEP_FLOP = sum(2.0 * ROWS * k * n for _, k, n, _ in LAYER)
+METRIC = "bf16 prefill GEMM TFLOP/s/GPU"
+
+
+def workload_config(n_gpus: int) -> dict:
+    """The `config` object of the JSON line: the same for this library's arm and for the CPU arm."""
+    return {"workload": "9B-class layer GEMM set, M=2048: qkv 4096->6144, o 4096->4096 +residual, gate/up 4096->2x12288 SiLU*mul, down 12288->4096 +residual",
+            "rows": ROWS, "hidden": HIDDEN, "intermediate": INTER, "parallelism": f"replicas x{n_gpus}" if n_gpus > 1 else "1 GPU",
+            "l2": "386 MB of weights per step: inputs larger than L2"}
+
+
+def host_threads() -> int:
+    """The host cores this process may use. A launcher that starts one process per GPU exports OMP_NUM_THREADS=1
+    for all of them; the CPU arm runs on one rank alone and takes every core it is allowed."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
 
 
 def peaks():
@@ -107,17 +124,25 @@ def dist_env():
 
 
 def run_reference(args):
-    """The CPU arm: the contract restated in C (oracle/), all host threads, a row sample of the workload."""
+    """The CPU arm: the contract restated in C (oracle/), all host threads, every row of the workload when the
+    host gets through it in time (a row sample otherwise)."""
     rank, world, _ = dist_env()
     if rank != 0:
         return
+    threads = host_threads()
+    os.environ["OMP_NUM_THREADS"] = str(threads)  # before the OpenMP runtime starts: the launcher may have set it to 1
+    import ctypes
+
     import numpy as np
 
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     from oracle_lib import Oracle
 
     o = Oracle(native=True)
-    rows = 64
+    try:  # and for a runtime that had read the old value already
+        ctypes.CDLL("libgomp.so.1").omp_set_num_threads(threads)
+    except OSError:
+        pass
     rng = np.random.default_rng(0)
 
     def bf16(a):
@@ -125,38 +150,38 @@ def run_reference(args):
         return ((b + 0x7FFF + ((b >> 16) & 1)) >> 16).astype(np.uint16)
 
     ws = [bf16(rng.standard_normal((n, k), dtype=np.float32) * k**-0.5) for _, k, n, _ in LAYER]
-    xs = [bf16(rng.standard_normal((rows, k), dtype=np.float32)) for _, k, _, _ in LAYER]
-    y0 = bf16(rng.standard_normal((rows, HIDDEN), dtype=np.float32))
 
-    def step():
+    def inputs(rows):
+        return [bf16(rng.standard_normal((rows, k), dtype=np.float32)) for _, k, _, _ in LAYER], bf16(rng.standard_normal((rows, HIDDEN), dtype=np.float32))
+
+    def step(xs, y0):
         for (name, k, n, out), w, x in zip(LAYER, ws, xs):
             o.gemm_f32(x, w, out, y0 if out == 2 else None)
 
-    # size the sample so that steps + warmup stay within about two minutes
+    # all 2048 rows unless the run (steps + warm-up) would then take more than about four minutes on this host
+    probe = inputs(64)
+    step(*probe)
     t0 = time.perf_counter()
-    step()
-    one = time.perf_counter() - t0
-    budget = 120.0 / max(1, args.steps + args.warmup)
-    while rows < ROWS and one * 2 < budget and one * 2 < 8.0:
-        rows *= 2
-        one *= 2
-    xs = [bf16(rng.standard_normal((rows, k), dtype=np.float32)) for _, k, _, _ in LAYER]
-    y0 = bf16(rng.standard_normal((rows, HIDDEN), dtype=np.float32))
+    step(*probe)
+    per_row = (time.perf_counter() - t0) / 64
+    rows = ROWS
+    while rows > 64 and per_row * rows * (args.steps + args.warmup) > 240.0:
+        rows //= 2
+    xs, y0 = inputs(rows)
     for _ in range(args.warmup):
-        step()
+        step(xs, y0)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        step()
+        step(xs, y0)
     dt = (time.perf_counter() - t0) / args.steps
     flop = STEP_FLOP * rows / ROWS
     value = flop / dt / 1e12
     sample = f"{rows} of {ROWS} rows of every GEMM of the layer set (same K and N), f32 accumulate, one RNE"
     line = {
-        "impl": "reference", "metric": "bf16 prefill GEMM TFLOP/s/GPU", "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic",
-        "config": {"workload": "9B-class layer GEMM set, M=2048 (CPU arm: row sample)", "rows": ROWS, "hidden": HIDDEN, "intermediate": INTER,
-                   "note": "the reference's kernels are Metal shaders and cannot run here; this is the CPU restatement of its contract"},
+        "data": "synthetic", "config": workload_config(args.gpus),
+        "note": "the reference's kernels are Metal shaders and cannot run here; this is the CPU restatement of its contract (oracle/hb_oracle.c, OpenMP)",
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": o.threads(), "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -271,6 +296,11 @@ def main():
     sec = max_over_ranks(sec)
     ms_per_step = sec / args.steps * 1e3
     value = STEP_FLOP * world / (sec / args.steps) / 1e12
+    # the same loop for 200 steps: long enough for the power cap to set the clock (the figure the sustained peak bounds)
+    long_steps = max(200, args.steps)
+    barrier()
+    sec_long = max_over_ranks(ctx.time(ops, long_steps))
+    barrier()
 
     # ---- end to end: activations in from page-locked host memory, result back out, every step.
     # Serial: upload, kernels, download, one after the other. Streamed: the same three per step through the
@@ -333,6 +363,10 @@ def main():
     roofline = {
         "bound": "tensor", "achieved": per_gpu_tflops, "peak": pk["bf16_tflops"], "unit": "TFLOP/s", "frac": per_gpu_tflops / pk["bf16_tflops"],
         "traffic": traffic_of(picks),
+        "traffic_source": "ncu captures of these kernel forms summarised under profiles/ (dram__bytes_read.sum + dram__bytes_write.sum per launch), not measured in this run",
+        "sustained": {"steps": long_steps, "ms_per_step": sec_long / long_steps * 1e3, "tflops_per_gpu": STEP_FLOP / (sec_long / long_steps) / 1e12,
+                      "frac_of_sustained_peak": STEP_FLOP / (sec_long / long_steps) / 1e12 / pk["bf16_tflops_sustained"],
+                      "frac_of_burst_peak": STEP_FLOP / (sec_long / long_steps) / 1e12 / pk["bf16_tflops"]},
         "kernel": "gemm_bf16_tn_pair_kernel" if all(v.startswith("gemm_pair_") for v in picks.values()) else "gemm_bf16_tn_kernel / gemm_bf16_tn_pair_kernel", "peak_source": pk["source"] + " (burst cuBLAS bf16)",
         "frac_of_sustained_peak": per_gpu_tflops / pk["bf16_tflops_sustained"], "frac_of_nominal_2250": per_gpu_tflops / 2250.0,
         "algorithmic_flop_per_launch": STEP_FLOP / 4, "launches_per_step": len(ops),
@@ -374,6 +408,10 @@ def main():
         except Exception as e:
             extra["sharded_error"] = repr(e)
 
+    # the other half of the metric (the decode matvec against the HBM roofline) and the sharded configurations, in the
+    # object of the line that records them
+    roofline.update(summaries(extra, pk))
+
     cpu = None
     if rank == 0 and world == 1:
         cpu = cpu_baseline()
@@ -381,11 +419,9 @@ def main():
     sampler.stop.set()
     if rank == 0:
         line = {
-            "metric": "bf16 prefill GEMM TFLOP/s/GPU", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "9B-class layer GEMM set, M=2048: qkv 4096->6144, o 4096->4096 +residual, gate/up 4096->2x12288 SiLU*mul, down 12288->4096 +residual",
-                       "rows": ROWS, "hidden": HIDDEN, "intermediate": INTER, "parallelism": f"replicas x{world}" if world > 1 else "1 GPU",
-                       "l2": "386 MB of weights per step: inputs larger than L2"},
+            "config": workload_config(world),
             "e2e": e2e, "gpu_launches": launches, "clocks": sampler.summary(), "roofline": roofline, "cpu_baseline": cpu, "extra": extra,
         }
         emit(line)
@@ -393,6 +429,45 @@ def main():
     ctx.close()
     if world > 1:
         dist.destroy_process_group()
+
+
+def summaries(extra: dict, pk: dict) -> dict:
+    """What the sections beside the headline measured, in short: the decode matvec (HBM-bound: us, GB/s of algorithmic
+    bytes, fraction of the measured copy bandwidth, picked form), the short prefill blocks, the decode layer chain, the
+    MoE block, and the two sharded configurations with their parity against the f64 product."""
+    out = {}
+    mv = {}
+    for key, n in (("matvec_4096x12288", 12288), ("matvec_4096x151936", 151936)):
+        for mk, v in (extra.get(key) or {}).items():
+            mv[f"n{n}_{mk}"] = {"us": v["us"], "gbs": v["gbs"], "frac": v["frac_hbm"], "form": v["form"]}
+    if mv:
+        out["matvec"] = dict(mv, bound="hbm", peak=pk["hbm_gbs"], unit="GB/s", k=4096, bytes="2(NK + MK + MN) per launch")
+    small = extra.get("layer_set_small_blocks")
+    if small:
+        out["short_blocks"] = {k_: {"us": v["us"], "tflops": v["tflops"], "frac_bf16_peak": v["frac_bf16_peak"], "frac_hbm_weights": v["frac_hbm_weights"]} for k_, v in small.items()}
+    dec = extra.get("decode_layer_9b")
+    if dec:
+        out["decode_layer_9b"] = {k_: {"us_per_layer": v["us_per_layer"], "frac_hbm": v["frac_hbm"], "kernels_per_layer": v["kernels_per_layer"]} for k_, v in dec.items()}
+    moe = extra.get("moe_2048tok_256e_top8")
+    if moe:
+        out["moe_block"] = {"us": moe["us"], "weight_gbs": moe["weight_gbs"], "frac_hbm": moe["frac_hbm"], "kernels": len(moe["us_per_kernel"])}
+    q4 = extra.get("matvec_q4_4096")
+    if q4:
+        out["matvec_q4"] = {k_: {"us": v["us"], "frac_hbm": v["frac_hbm"]} for k_, v in q4.items()}
+    sh = {}
+    for key, name in (("tp_ffn_27b_m2048", "tp_ffn_27b"), ("moe_ep_2048tok", "moe_ep")):
+        v = extra.get(key)
+        if v:
+            sh[name] = {k_: v.get(k_) for k_ in ("n_gpus", "us", "t1_us", "efficiency", "kernels_per_step", "nccl_form_us", "parity") if k_ in v}
+    weak = extra.get("moe_ep_weak_2048tok_per_gpu")
+    if weak:
+        sh["moe_ep_weak"] = {"n_gpus": weak["n_gpus"], "us": weak["us"], "tokens_per_s_total": weak["tokens_per_s_total"]}
+    if sh:
+        out["sharded"] = dict(sh, scaling="strong: global M = 2048 rows; efficiency = t1 / (n_gpus * us), t1 the same code on one GPU in the same job")
+    for k_ in ("error", "sharded_error", "small_error"):
+        if k_ in extra:
+            out[k_] = extra[k_]
+    return out
 
 
 def run_case(args):
@@ -736,10 +811,35 @@ def bench_extra(hb, ctx, sel, torch, dev, wrap, pk, rank, world, barrier, max_ov
     return out
 
 
+def contract_report(torch, ref, got, share, rows, reference):
+    """The engine's contract on two bf16 tensors (at most 1 ulp apart on all but `share` of the elements, max|err| <=
+    max|ref| / 64) as the object the JSON line carries."""
+    def ordered(t):  # bf16 bits as integers that grow with the value
+        i = t.contiguous().view(torch.int16).int()
+        return torch.where(i < 0, -(i & 0x7FFF), i)
+
+    ulp = (ordered(ref) - ordered(got)).abs()
+    err = float((ref.float() - got.float()).abs().max())
+    scale = max(float(ref.float().abs().max()), 1e-6)
+    over = int((ulp > 1).sum())
+    return {"rows": rows, "elements": ref.numel(), "bit_equal": int((ulp == 0).sum()), "over_1ulp": over, "max_ulp": int(ulp.max()),
+            "max_err_over_scale": err / scale, "within_contract": bool(over <= share * ref.numel() and err <= scale / 64), "allowed_share_over_1ulp": share,
+            "reference": reference}
+
+
+def swiglu_ref(torch, acc16):
+    """bf16(g * sigmoid(g) * u) over [gate | up] columns that are bf16 already, in f32 as the epilogue does."""
+    n = acc16.shape[1] // 2
+    g, u = acc16[:, :n].float(), acc16[:, n:].float()
+    return ((g * (1.0 / (1.0 + torch.exp(-g)))) * u).bfloat16()
+
+
 def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks):
     """The two configurations that shard (strong scaling, total work fixed): the 27B-class FFN tensor-parallel
-    over `world` ranks (config 4) and the MoE block expert-parallel (config 5). At world = 1 the same code runs
-    without an exchange."""
+    over `world` ranks and the MoE block expert-parallel. At world = 1 the same code runs without an exchange.
+    Every rank builds the whole weights from one seed and keeps its shard, so that rank 0 can check sampled rows of
+    the sharded result against the f64 product of the unsharded operands; with several ranks the one-GPU time of the
+    same code is measured in the same job (t1) for the strong-scaling efficiency t1 / (world * t)."""
     import importlib.util
 
     spec = importlib.util.spec_from_file_location("hb200_dist", os.path.join(ROOT, "herbert-metal-bf16_b200", "dist.py"))
@@ -749,13 +849,17 @@ def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks)
     stream = torch.cuda.Stream(dev)
     ctx.sync()
     ctx.set_stream(stream.cuda_stream)
+
+    def dist_all_gather(parts, t):
+        import torch.distributed as dist
+
+        dist.all_gather(parts, t)
+
     try:
         with torch.cuda.stream(stream):
             be = D.GpuBackend(hb, ctx, rows_max=2048)
             g = torch.Generator(device=dev)
-            g.manual_seed(99)  # x, y and the router scores are the same on every rank
-            gl = torch.Generator(device=dev)
-            gl.manual_seed(1000 + rank)
+            g.manual_seed(99)  # the same tensors on every rank
 
             def timed(fn, warm, reps):
                 for _ in range(warm):
@@ -770,14 +874,16 @@ def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks)
                 barrier()
                 return max_over_ranks(e0.elapsed_time(e1) * 1e-3 / reps)
 
-            # -- config 4: hidden 5120, intermediate 17408, M = 2048
+            sample = torch.randperm(2048, generator=torch.Generator().manual_seed(5))[:16].sort().values.to(dev)
+
+            # -- the 27B-class FFN: hidden 5120, intermediate 17408, M = 2048
             m, h, inter = 2048, 5120, 17408
             if inter % world == 0:
-                ip = inter // world
                 x = torch.randn(m, h, device=dev, generator=g).bfloat16()
                 y = torch.randn(m, h, device=dev, generator=g).bfloat16()
-                wgu_l = (torch.randn(2 * ip, h, device=dev, generator=gl) * h**-0.5).bfloat16()
-                wd_l = (torch.randn(h, ip, device=dev, generator=gl) * inter**-0.5).bfloat16()
+                wgu = (torch.randn(2 * inter, h, device=dev, generator=g) * h**-0.5).bfloat16()
+                wd = (torch.randn(h, inter, device=dev, generator=g) * inter**-0.5).bfloat16()
+                wgu_l, wd_l = D.shard_gate_up(wgu, rank, world), D.shard_down(wd, rank, world)
                 flop = 2.0 * m * (2 * inter) * h + 2.0 * m * h * inter
                 # the production form: the down GEMM's epilogue stores every block of rows of its f32 partial into the
                 # staging buffer of the rank that sums it (reduce-scatter under the GEMM), tp_sum adds the staged blocks
@@ -786,10 +892,26 @@ def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks)
                 D.tp_peer_connect(tp)
                 tp.set_y(y)
                 got = D.tp_ffn_peer(tp, x, wgu_l, wd_l).clone()
+                # Sampled rows against the f64 product of the unsharded operands, stage by stage as the tests do: the SwiGLU
+                # rows every rank made (three roundings: a looser rate, see tests/test_gpu_full_size.py), then the sharded
+                # sum over exactly those rows under the engine's contract.
+                hm_l = tp.kernels[(h, inter // world)][2][sample].contiguous()
+                if world > 1:
+                    parts = [torch.empty_like(hm_l) for _ in range(world)]
+                    dist_all_gather(parts, hm_l)
+                    hm_gpu = torch.cat(parts, dim=1)
+                else:
+                    hm_gpu = hm_l
+                xs_ = x[sample].double()
+                hm = swiglu_ref(torch, torch.cat([(xs_ @ wgu[c : c + 8704].double().t()).float().bfloat16() for c in range(0, 2 * inter, 8704)], dim=1))
+                parity_swiglu = contract_report(torch, hm, hm_gpu, 3e-3, int(sample.numel()), "f64 gate and up sums of the unsharded weights on the GPU, then the three roundings of the SwiGLU epilogue")
+                acc = torch.cat([(hm_gpu.double() @ wd[c : c + 1280].double().t()).float().bfloat16() for c in range(0, h, 1280)], dim=1)
+                want = (y[sample].float() + acc.float()).bfloat16()
+                parity = contract_report(torch, want, got[sample], 1e-3, int(sample.numel()), "f64 product of all ranks' SwiGLU rows with the unsharded down weights on the GPU, one rounding, residual add")
+                parity["gate_up_swiglu_stage"] = parity_swiglu
                 # (the step's kernels recorded once and replayed with one call; also launched one by one from the host)
                 sec = timed(lambda: D.tp_ffn_peer(tp, x, wgu_l, wd_l, recorded=True), 3, 10)
                 sec_loop = timed(lambda: D.tp_ffn_peer(tp, x, wgu_l, wd_l), 3, 10) if world > 1 else sec
-                sec_ns = timed(lambda: D.tp_ffn_peer(tp, x, wgu_l, wd_l, nccl_sync=True), 3, 10) if world > 1 else sec
                 sec_pull = sec
                 if world > 1:  # the pull form: the partial stays local, tp_reduce loads the blocks it sums from the peers
                     tpl = D.TpPeer(hb, ctx, rank, world, m, h, push=False)
@@ -811,48 +933,84 @@ def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks)
                 sec_nccl = timed(lambda: D.tp_ffn(be, x, wgu_l, wd_l, y2), 3, 10)
                 barrier()
                 tp.close()
-                out["tp_ffn_27b_m2048"] = {"n_gpus": world, "us": sec * 1e6, "tflops_total": flop / sec / 1e12, "tflops_per_gpu": flop / sec / 1e12 / world,
-                                           "frac_of_measured_peak_per_gpu": flop / sec / 1e12 / world / pk["bf16_tflops"],
-                                           "nvlink_bytes_per_gpu": (m * h * 4 + m * h * 2) * (world - 1) // world // 1 if world > 1 else 0, "scaling": "strong",
-                                           "exchange": "down GEMM epilogue stores its f32 partial block by block into the summing ranks' memory (NVLink, under the GEMM); "
-                                                       "tp_sum: rank-order sum, one rounding, residual, peer stores of bf16 Y; 2 barrier kernels (no NCCL call in the step)",
-                                           "launched_one_by_one_us": sec_loop * 1e6, "with_nccl_barriers_us": sec_ns * 1e6, "pull_form_us": sec_pull * 1e6,
-                                           "nccl_all_reduce_form_us": sec_nccl * 1e6, "equals_nccl_form_bitwise": same,
+                t1 = sec
+                if world > 1:  # the same code on this GPU alone, the whole weights
+                    one = D.TpPeer(hb, ctx, 0, 1, m, h)
+                    one.connect([one])
+                    one.set_y(y)
+                    t1 = timed(lambda: D.tp_ffn_peer(one, x, wgu, wd), 3, 10)
+                    one.close()
+                out["tp_ffn_27b_m2048"] = {"n_gpus": world, "us": sec * 1e6, "t1_us": t1 * 1e6, "efficiency": t1 / (world * sec), "tflops_total": flop / sec / 1e12,
+                                           "tflops_per_gpu": flop / sec / 1e12 / world, "frac_of_measured_peak_per_gpu": flop / sec / 1e12 / world / pk["bf16_tflops"],
+                                           "nvlink_bytes_per_gpu": (m * h * 4 + m * h * 2) * (world - 1) // world if world > 1 else 0, "scaling": "strong",
+                                           "kernels_per_step": tp.kernels_per_step, "parity": parity,
+                                           "exchange": tp.describe(),
+                                           "launched_one_by_one_us": sec_loop * 1e6, "pull_form_us": sec_pull * 1e6,
+                                           "nccl_form_us": sec_nccl * 1e6, "equals_nccl_form_bitwise": same,
                                            "max_abs_diff_vs_nccl_form": diff, "max_abs_value": scale}
-                del wgu_l, wd_l
-            # -- config 5: 2048 tokens, hidden 2048, 256 experts, top-8, expert intermediate 512
+                del wgu, wd, wgu_l, wd_l
+            # -- the MoE block: 2048 tokens, hidden 2048, 256 experts, top-8, expert intermediate 512
             m, h, mi, E, top_k, bm = 2048, 2048, 512, 256, 8, 64
             if m % world == 0 and E % world == 0:
                 rl, epr = m // world, E // world
-                xs = torch.randn(m, h, device=dev, generator=g).bfloat16()[rank * rl : (rank + 1) * rl].contiguous()
-                sc = torch.randn(m, E, device=dev, generator=g).bfloat16()[rank * rl : (rank + 1) * rl].contiguous()
-                wgu_l = (torch.randn(epr * 2 * mi, h, device=dev, generator=gl) * h**-0.5).bfloat16()
-                wd_l = (torch.randn(epr * h, mi, device=dev, generator=gl) * mi**-0.5).bfloat16()
+                x_all = torch.randn(m, h, device=dev, generator=g).bfloat16()
+                sc_all = torch.randn(m, E, device=dev, generator=g).bfloat16()
+                wgu = (torch.randn(E * 2 * mi, h, device=dev, generator=g) * h**-0.5).bfloat16()
+                wd = (torch.randn(E * h, mi, device=dev, generator=g) * mi**-0.5).bfloat16()
+                xs, sc = x_all[rank * rl : (rank + 1) * rl].contiguous(), sc_all[rank * rl : (rank + 1) * rl].contiguous()
+                wgu_l, wd_l = wgu[rank * epr * 2 * mi : (rank + 1) * epr * 2 * mi], wd[rank * epr * h : (rank + 1) * epr * h]
                 wbytes = 2.0 * E * 3 * mi * h
                 # the exchange through peer memory by the library's own kernels (the production form) ...
                 st = D.EpPeer(hb, ctx, rank, world, rl, h, mi, E, top_k, bm)
                 D.ep_peer_connect(st)
                 got = D.ep_moe_peer(st, xs, sc, wgu_l, wd_l).clone()
+                stream.synchronize()
+                # sampled token rows of this rank against the f64 chain over the whole weights, the route as the GPU made it
+                rows_s = sample[sample < rl][:8] if world > 1 else sample[:8]
+                if rows_s.numel() == 0:
+                    rows_s = torch.arange(min(8, rl), device=dev)
+                route = st.route[rows_s].cpu()
+                want = torch.zeros(rows_s.numel(), h, device=dev, dtype=torch.bfloat16)
+                for i in range(rows_s.numel()):
+                    xr = xs[rows_s[i]].double()[None]
+                    accr = torch.zeros(1, h, device=dev, dtype=torch.bfloat16)
+                    for s_ in range(top_k):
+                        e = int(route[i, s_])
+                        wgt = torch.tensor([int(route[i, top_k + s_])], dtype=torch.int32).view(torch.float32).to(dev)
+                        hm = swiglu_ref(torch, (xr @ wgu[e * 2 * mi : (e + 1) * 2 * mi].double().t()).float().bfloat16())
+                        yr = (hm.double() @ wd[e * h : (e + 1) * h].double().t()).float().bfloat16()
+                        accr = (accr.float() + (yr.float() * wgt).bfloat16().float()).bfloat16()
+                    want[i] = accr[0]
+                parity = contract_report(torch, want, got[rows_s], 0.05, int(rows_s.numel()), "f64 chain over the unsharded expert weights on the GPU (gate/up, SwiGLU, down, bf16 combine chain: the roundings of three stages compound, so 5 % of the outputs may be over 1 ulp)")
                 sec = timed(lambda: D.ep_moe_peer(st, xs, sc, wgu_l, wd_l, recorded=True), 4, 20)
                 got_rec = D.ep_moe_peer(st, xs, sc, wgu_l, wd_l, recorded=True).clone()
                 if not torch.equal(got_rec, got):
                     raise RuntimeError("ep_moe: the replayed step differs from the step launched kernel by kernel")
                 sec_loop = timed(lambda: D.ep_moe_peer(st, xs, sc, wgu_l, wd_l), 3, 20) if world > 1 else sec
-                sec_ns = timed(lambda: D.ep_moe_peer(st, xs, sc, wgu_l, wd_l, nccl_sync=True), 3, 20) if world > 1 else sec
                 # ... and the same block with the rows exchanged by NCCL all-to-all, host-known counts (the baseline form)
                 ref = D.ep_moe(be, xs, sc, wgu_l, wd_l, E, top_k, mi, bm)
                 same = bool(torch.equal(ref, got))
                 sec_nccl = timed(lambda: D.ep_moe(be, xs, sc, wgu_l, wd_l, E, top_k, mi, bm), 2, 5)
                 barrier()
+                kernels_per_step = st.kernels_per_step
                 st.close()
-                out["moe_ep_2048tok"] = {"n_gpus": world, "us": sec * 1e6, "weight_gbs_total": wbytes / sec / 1e9, "tokens_per_s": m / sec, "scaling": "strong",
-                                         "tile_rows": bm, "exchange": "peer-memory stores and loads in ep_dispatch / ep_return, offsets all-gather + 2 barriers as kernels (no NCCL call in the step); the 13 kernels replayed as one recorded sequence",
-                                         "launched_one_by_one_us": sec_loop * 1e6, "with_nccl_barriers_us": sec_ns * 1e6,
-                                         "nccl_all_to_all_form_us": sec_nccl * 1e6, "equals_nccl_form_bitwise": same}
+                t1 = sec
+                if world > 1:  # the same code on this GPU alone: all tokens, all experts
+                    one = D.EpPeer(hb, ctx, 0, 1, m, h, mi, E, top_k, bm)
+                    one.connect([one])
+                    t1 = timed(lambda: D.ep_moe_peer(one, x_all, sc_all, wgu, wd), 3, 10)
+                    one.close()
+                out["moe_ep_2048tok"] = {"n_gpus": world, "us": sec * 1e6, "t1_us": t1 * 1e6, "efficiency": t1 / (world * sec), "weight_gbs_total": wbytes / sec / 1e9,
+                                         "tokens_per_s": m / sec, "scaling": "strong", "tile_rows": bm, "kernels_per_step": kernels_per_step, "parity": parity,
+                                         "exchange": "peer-memory stores and loads by the library's kernels, offsets all-gather and barriers as kernels (no NCCL call in the step); the step replayed as one recorded sequence",
+                                         "launched_one_by_one_us": sec_loop * 1e6,
+                                         "nccl_form_us": sec_nccl * 1e6, "equals_nccl_form_bitwise": same}
                 if world > 1:
                     # weak scaling: 2048 tokens on every rank (the experts still partitioned), peer-memory form. The
                     # buffers hold four times the average number of received rows (an overflow would be reported).
                     try:
+                        gl = torch.Generator(device=dev)
+                        gl.manual_seed(1000 + rank)
                         xw = torch.randn(m, h, device=dev, generator=gl).bfloat16()
                         sw = torch.randn(m, E, device=dev, generator=gl).bfloat16()
                         stw = D.EpPeer(hb, ctx, rank, world, m, h, mi, E, top_k, bm, cap=min(m * top_k * world, 4 * m * top_k))

@@ -41,7 +41,7 @@ class Op(C.Structure):
 
 
 class GemmDesc(C.Structure):
-    _fields_ = [(n, C.c_uint32) for n in ("k", "n", "out", "rows_mode", "top_k", "experts", "bm", "tile_n", "stages", "cta_pair", "m_first", "rows_max", "stream_k", "merge_runs", "y_shards")]
+    _fields_ = [(n, C.c_uint32) for n in ("k", "n", "out", "rows_mode", "top_k", "experts", "bm", "tile_n", "stages", "cta_pair", "m_first", "rows_max", "stream_k", "merge_runs", "y_shards", "y_group_rows", "y_signal")]
 
 
 class MatvecDesc(C.Structure):
@@ -101,6 +101,7 @@ def lib() -> C.CDLL:
         "hb_ep_plan_get": (ci, [vp, u32, u32, u32, u32, u32, pvp]),
         "hb_tp_reduce_get": (ci, [vp, u32, u32, u32, u32, pvp]),
         "hb_tp_sum_get": (ci, [vp, u32, u32, u32, u32, pvp]),
+        "hb_tp_sum_stream_get": (ci, [vp, u32, u32, u32, u32, u32, u32, pvp]),
         "hb_dequant_q4_get": (ci, [vp, u32, u32, pvp]),
         "hb_matvec_q4_get": (ci, [vp, u32, u32, u32, u32, u32, pvp]),
         "hb_matmul_q4_get": (ci, [vp, u32, u32, u32, u32, u32, pvp]),
@@ -167,7 +168,7 @@ EXPORTS = [
     "hb_open", "hb_close", "hb_last_error", "hb_describe", "hb_set_stream", "hb_alloc", "hb_set_alloc_limit", "hb_upload",
     "hb_download", "hb_memset", "hb_sync", "hb_launch_count", "hb_event_new", "hb_event_free", "hb_lane_record", "hb_lane_wait", "hb_event_sync",
     "hb_upload_async", "hb_download_async", "hb_host_alloc", "hb_host_free", "hb_ipc_export", "hb_ipc_open", "hb_ipc_close",
-    "hb_ep_dispatch_get", "hb_ep_plan_get", "hb_ep_return_get", "hb_tp_reduce_get", "hb_tp_sum_get", "hb_dequant_q4_get", "hb_matvec_q4_get", "hb_matmul_q4_get", "hb_rmsnorm_get", "hb_argmax_get", "hb_moe_out_get", "hb_peer_sync_get", "hb_set_peer_wait_ms", "hb_gemm_get", "hb_matvec_get", "hb_swiglu_get", "hb_route_get",
+    "hb_ep_dispatch_get", "hb_ep_plan_get", "hb_ep_return_get", "hb_tp_reduce_get", "hb_tp_sum_get", "hb_tp_sum_stream_get", "hb_dequant_q4_get", "hb_matvec_q4_get", "hb_matmul_q4_get", "hb_rmsnorm_get", "hb_argmax_get", "hb_moe_out_get", "hb_peer_sync_get", "hb_set_peer_wait_ms", "hb_gemm_get", "hb_matvec_get", "hb_swiglu_get", "hb_route_get",
     "hb_moe_sort_get", "hb_moe_tiles", "hb_moe_gather_get", "hb_moe_combine_get", "hb_epilogue_get", "hb_gemm_static_scratch", "hb_kernel_name", "hb_launch", "hb_run", "hb_time", "hb_set_launch_overlap", "hb_graph_record", "hb_graph_launch", "hb_graph_time", "hb_graph_free",
     "hb_tune_new", "hb_tune_free", "hb_tune_apply", "hb_tune_get", "hb_tune_summary", "hb_tune_gemm_timed", "hb_selector_new",
     "hb_selector_free", "hb_selector_log", "hb_selector_buckets", "hb_fill_random16", "hb_select_gemm", "hb_select_gate_up",
@@ -391,6 +392,9 @@ class Context:
     def tp_sum(self, n, out, world, rank) -> "Kernel":
         return self._get(lib().hb_tp_sum_get, n, out, world, rank)
 
+    def tp_sum_stream(self, n, out, world, rank, group_rows=256, sync=1) -> "Kernel":
+        return self._get(lib().hb_tp_sum_stream_get, n, out, world, rank, group_rows, sync)
+
     def tp_reduce(self, n, out, world, rank) -> "Kernel":
         return self._get(lib().hb_tp_reduce_get, n, out, world, rank)
 
@@ -425,8 +429,8 @@ class Context:
         self._check(fn(self.h, *args, C.byref(k)))
         return Kernel(self, k.value)
 
-    def gemm(self, k, n, out=OUT_BF16, rows_max=2048, tile_n=0, stages=0, cta_pair=0, m_first=1, rows_mode=ROWS_DENSE, top_k=0, experts=0, bm=0, merge_runs=0, stream_k=0, y_shards=0) -> Kernel:
-        d = GemmDesc(k, n, out, rows_mode, top_k, experts, bm, tile_n, stages, cta_pair, m_first, rows_max, stream_k, merge_runs, y_shards)
+    def gemm(self, k, n, out=OUT_BF16, rows_max=2048, tile_n=0, stages=0, cta_pair=0, m_first=1, rows_mode=ROWS_DENSE, top_k=0, experts=0, bm=0, merge_runs=0, stream_k=0, y_shards=0, y_group_rows=0, y_signal=0) -> Kernel:
+        d = GemmDesc(k, n, out, rows_mode, top_k, experts, bm, tile_n, stages, cta_pair, m_first, rows_max, stream_k, merge_runs, y_shards, y_group_rows, y_signal)
         return self._get(lib().hb_gemm_get, C.byref(d))
 
     def matvec(self, k, n, out=OUT_BF16, rows_max=1, rows_per_warp=2, split=1, persist=0, x_stationary=0, tensor_core=0, argmax=0) -> Kernel:

@@ -23,7 +23,32 @@ struct GemmParams {
     // to the rank that will sum it). Null: Y is one array at y.
     const uint64_t* y_shards;
     uint32_t shard_rows;
+    // y_shards with the rows dealt in groups (hb_gemm_desc.y_group_rows): group_rows = G, group_part = G / P rows of
+    // every group per block; 0 = contiguous blocks of shard_rows rows
+    uint32_t group_rows, group_part;
+    // y_signal: where to tell the summing ranks that a group of rows is complete
+    const uint64_t* flag_table;  // [world] -> u32[world][TP_MAX_GROUPS] on every rank
+    uint32_t* ctl;               // this rank's control words: [0] steps completed, [TP_CTL_GROUP0 + g] arrivals of group g
+    uint32_t world, rank;
 };
+
+constexpr uint32_t TP_MAX_GROUPS = 64;   // HB_TP_MAX_GROUPS
+constexpr uint32_t TP_CTL_DONE = 1;      // of ctl: blocks of the summing kernel that have finished
+constexpr uint32_t TP_CTL_GROUP0 = 8;    // of ctl: first of the per-group arrival counters
+
+// Where row `row` of a Y in row blocks lives: the block's base address and the row inside the block.
+__device__ __forceinline__ float* shard_row(const GemmParams& p, uint32_t row) {
+    uint32_t block, local;
+    if (p.group_rows) {
+        const uint32_t g = row / p.group_rows, in = row % p.group_rows;
+        block = in / p.group_part;
+        local = g * p.group_part + in % p.group_part;
+    } else {
+        block = row / p.shard_rows;
+        local = row % p.shard_rows;
+    }
+    return reinterpret_cast<float*>(p.y_shards[block]) + (size_t)local * p.n_out;
+}
 
 constexpr int BM = 128;
 constexpr int BK = 64;
@@ -47,8 +72,7 @@ __device__ __forceinline__ void store_chunk(const GemmParams& p, uint32_t row, u
     if (row >= p.m || col0 >= p.n_out) return;
     const uint32_t ncols = min(32u, p.n_out - col0);
     if constexpr (OUT == HB_OUT_F32) {
-        float* y = p.y_shards ? reinterpret_cast<float*>(p.y_shards[row / p.shard_rows]) + (size_t)(row % p.shard_rows) * p.n_out + col0
-                              : reinterpret_cast<float*>(p.y) + (size_t)row * p.n_out + col0;
+        float* y = p.y_shards ? shard_row(p, row) + col0 : reinterpret_cast<float*>(p.y) + (size_t)row * p.n_out + col0;
         if (ncols == 32 && p.vec_ok) {
 #pragma unroll
             for (int i = 0; i < 8; ++i)
@@ -120,7 +144,7 @@ __device__ __forceinline__ void store_chunk_f32_blocks(const GemmParams& p, uint
         asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(q.x), "=r"(q.y), "=r"(q.z), "=r"(q.w) : "r"(scratch + ((r * 8u + (c ^ (r & 7u))) << 4)));
         const uint32_t row = row0 + r, col = col0 + 4u * c;
         if (row < p.m && col < p.n_out) {
-            float* y = reinterpret_cast<float*>(p.y_shards[row / p.shard_rows]) + (size_t)(row % p.shard_rows) * p.n_out + col;
+            float* y = shard_row(p, row) + col;
             if (p.vec_ok && col + 4u <= p.n_out) {
                 *reinterpret_cast<uint4*>(y) = q;
             } else {

@@ -86,6 +86,9 @@ gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
     const uint32_t S = p.stages;
     const uint32_t rank = cluster_rank();
     const uint32_t pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+    // y_signal: the kernel that sums the partials is next on the stream and may start now (it shares the SMs with
+    // this one and waits for the flags sent below, not for this kernel's end)
+    if (OUT == HB_OUT_F32 && p.flag_table) griddep_launch_dependents();
 
     if (threadIdx.x == 0) {
         for (uint32_t s = 0; s < S; ++s) {
@@ -213,6 +216,22 @@ gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&bars.tmem_empty[acc]), 0));
+            if (OUT == HB_OUT_F32 && p.flag_table && lane == 0) {
+                // This warp's rows of the tile are stored (the __syncwarp above orders the other lanes' stores before
+                // this fence). The tile's row group is complete when the eight epilogue warps of the pair have arrived
+                // for each of its column tiles; whoever arrives last tells every summing rank, with the step's number.
+                __threadfence_system();
+                uint32_t* cnt = p.ctl + TP_CTL_GROUP0 + tm;
+                if (atomicAdd(cnt, 1u) == 8u * tiles_n - 1u) {
+                    *cnt = 0u;  // for the next launch
+                    __threadfence_system();
+                    const uint32_t step = *reinterpret_cast<volatile uint32_t*>(p.ctl) + 1u;
+                    for (uint32_t d = 0; d < p.world; ++d) {
+                        uint32_t* flag = reinterpret_cast<uint32_t*>(p.flag_table[d]) + p.rank * TP_MAX_GROUPS + tm;
+                        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(step) : "memory");
+                    }
+                }
+            }
         }
     }
 
@@ -246,10 +265,11 @@ struct PairGemm : hb_kernel {
     const void* last_w = nullptr;
     const void* last_x = nullptr;
     uint32_t last_m = 0;
+    uint32_t rank_of_signal = 0;  // y_signal: which row of the flags this rank writes (hb_gemm_desc.y_signal - 1)
     CUtensorMap tm_x{}, tm_w{};
 
     int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
-        if (na != 3) return fail(ctx, HB_INVALID, name + ": bindings are W, X, Y");
+        if (na != (d.y_signal ? 5 : 3)) return fail(ctx, HB_INVALID, name + (d.y_signal ? ": bindings are W, X, Y, flag_table, ctl" : ": bindings are W, X, Y"));
         if (m == 0 || m > d.rows_max) return fail(ctx, HB_INVALID, name + ": m = " + std::to_string(m) + " outside 1.." + std::to_string(d.rows_max));
         const uint32_t n_out = d.out == HB_OUT_SWIGLU ? d.n / 2 : d.n;
         const size_t ybytes = d.y_shards > 1 ? (size_t)d.y_shards * 8 : (size_t)m * n_out * (d.out == HB_OUT_F32 ? 4 : 2);
@@ -284,6 +304,18 @@ struct PairGemm : hb_kernel {
             p.shard_rows = (m + d.y_shards - 1) / d.y_shards;
             p.y = nullptr;
             p.vec_ok = ((size_t)n_out * elem) % 16 == 0 ? 1u : 0u;
+            p.group_rows = d.y_group_rows;
+            p.group_part = d.y_group_rows / d.y_shards;
+            p.world = d.y_shards;
+            if (d.y_signal) {
+                if (!range_ok(a[3], (size_t)d.y_shards * 8) || !range_ok(a[4], (size_t)HB_TP_CTL_WORDS * 4))
+                    return fail(ctx, HB_INVALID, name + ": flag_table or ctl is too small");
+                if (p.tiles_m > TP_MAX_GROUPS) return fail(ctx, HB_INVALID, name + ": more row groups than flags");
+                p.flag_table = static_cast<const uint64_t*>(a[3].ptr);
+                p.ctl = static_cast<uint32_t*>(a[4].ptr);
+                p.rank = rank_of_signal;
+                p.m_first = 0;  // group by group: all column tiles of a row tile before the next row tile
+            }
         }
         const uint32_t pairs = std::min<uint32_t>(p.num_tiles, (uint32_t)ctx->sm_count / 2);
         cudaLaunchConfig_t cfg{};
@@ -311,6 +343,14 @@ int make_gemm_pair(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
     if (d->tile_n != 0 && d->tile_n != 256) return fail(ctx, HB_UNSUPPORTED, "gemm: the CTA-pair form has 256 x 256 tiles only");
     if (d->y_shards > 1 && d->out != HB_OUT_F32) return fail(ctx, HB_UNSUPPORTED, "gemm: a Y in row blocks is for f32 partial products (Out::F32)");
     if (d->y_shards > 16) return fail(ctx, HB_UNSUPPORTED, "gemm: at most 16 row blocks of Y");
+    if (d->y_group_rows) {
+        if (d->y_shards < 2 || d->y_group_rows > 256 || d->y_group_rows % (32 * d->y_shards) != 0)
+            return fail(ctx, HB_UNSUPPORTED, "gemm: rows dealt in groups need y_shards >= 2 and a group of a multiple of 32 * y_shards rows, at most 256");
+    }
+    if (d->y_signal) {
+        if (d->y_group_rows != 256) return fail(ctx, HB_UNSUPPORTED, "gemm: y_signal needs y_group_rows = 256 (a group is a row tile of the CTA pair)");
+        if (d->y_signal > d->y_shards) return fail(ctx, HB_UNSUPPORTED, "gemm: y_signal is this rank's number + 1, at most y_shards");
+    }
     pair_fn fn = pair_pick(d->out);
     const size_t budget = std::min<size_t>(ctx->smem_optin, 227 * 1024) - 2048;
     // a Y in row blocks: 16 KB behind the ring (4 KB per epilogue warp) for the transposing store
@@ -325,10 +365,14 @@ int make_gemm_pair(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
     k->stages = stages;
     k->smem = (size_t)stages * PAIR_STAGE_BYTES + extra + 1024;
     k->kind = 1;
-    k->nargs = 3;
-    char nm[160];
-    snprintf(nm, sizeof nm, "gemm_pair_%ux%u_%s%s_t256x256_s%u%s", d->k, d->n, out_tag(d->out), d->m_first ? "_mf" : "", stages,
-             d->y_shards > 1 ? (std::string("_y") + std::to_string(d->y_shards)).c_str() : "");
+    k->nargs = d->y_signal ? 5 : 3;
+    k->rank_of_signal = d->y_signal ? d->y_signal - 1 : 0;
+    char nm[200];
+    std::string ytag;
+    if (d->y_shards > 1) ytag = "_y" + std::to_string(d->y_shards);
+    if (d->y_group_rows) ytag += "g" + std::to_string(d->y_group_rows);
+    if (d->y_signal) ytag += "_sig" + std::to_string(d->y_signal - 1);
+    snprintf(nm, sizeof nm, "gemm_pair_%ux%u_%s%s_t256x256_s%u%s", d->k, d->n, out_tag(d->out), d->m_first && !d->y_signal ? "_mf" : "", stages, ytag.c_str());
     k->name = nm;
     if (hb_kernel* have = find(ctx, k->name)) {
         auto* g = static_cast<PairGemm*>(have);

@@ -291,6 +291,8 @@ class _Recorded:
                 for e in self.emitters:
                     e.emit = _launch_now
             self.graphs[key] = self.ctx.record(ops)
+            for e in self.emitters:
+                e.kernels_per_step = len(ops)
         else:
             step(replay=True)
         self.graphs[key].launch()
@@ -478,6 +480,15 @@ def ep_moe_peer(state: EpPeer, x_local, scores_local, wgu_local, wd_local, group
 
 
 def _ep_step(state: EpPeer, x_local, scores_local, wgu_local, wd_local, group, nccl_sync):
+    launched = state.ctx.launch_count()
+    try:
+        return _ep_step_body(state, x_local, scores_local, wgu_local, wd_local, group, nccl_sync)
+    finally:
+        if state.emit is _launch_now:
+            state.kernels_per_step = state.ctx.launch_count() - launched
+
+
+def _ep_step_body(state: EpPeer, x_local, scores_local, wgu_local, wd_local, group, nccl_sync):
     multi = state.world > 1
     state.phase_sort(x_local, scores_local)
     if not multi:
@@ -503,31 +514,68 @@ def _ep_step(state: EpPeer, x_local, scores_local, wgu_local, wd_local, group, n
 # closes the step. Per rank (P-1)/P of one f32 [m/P][h] slice per peer crosses NVLink instead of an all-reduce of
 # the whole f32 matrix, and the output mode needs no pass of its own.
 
+TP_GROUP_ROWS, TP_MAX_GROUPS, TP_CTL_WORDS = 256, 64, 128  # the CTA pair's row tile; HB_TP_MAX_GROUPS; HB_TP_CTL_WORDS
+
+
 class TpPeer:
     """One rank of the peer-memory FFN: the partial-product buffer, the output Y and their peer tables.
 
-    push = True (the default with more than one rank): the down GEMM stores every block of rows of its partial straight
-    into the staging buffer of the rank that sums that block, tile by tile while it computes (hb_gemm_desc.y_shards),
-    and the sum (tp_sum) reads local memory only: the reduce-scatter's traffic crosses NVLink under the GEMM.
-    push = False: the partial stays local and the sum pulls the blocks it needs from the peers (tp_reduce).
-    Measured for the 27B-class FFN: 449 against 483 us on two B200s, 220 against 259 us on eight. (The push form needs
-    its stores to leave as whole 128-byte row segments: written one 16-byte piece per lane they were 537 and 437 us.)"""
+    Three forms of the exchange, the same bits from each (the f32 partials are summed in rank order by one rank per row):
 
-    def __init__(self, hb, ctx, rank: int, world: int, m: int, h: int, out: int = OUT_RESIDUAL, device=None, push: bool | None = None):
-        self.hb, self.ctx, self.rank, self.world, self.m, self.h = hb, ctx, rank, world, m, h
+    "stream" (the default with 2, 4 or 8 ranks): the rows are dealt in groups of 256 (the down GEMM's row tile) and
+      every rank sums 256 / world rows of every group. The down GEMM stores each tile of its partial straight into the
+      staging buffers of the ranks that sum its rows and flags a group when its last tile is out; the summing kernel
+      (hb_tp_sum_stream_get) starts beside the GEMM, takes the groups as they complete, stores the bf16 rows into every
+      rank's Y and closes the step with a handshake of its own. Three kernels per step, none of them a barrier.
+    "push": contiguous blocks of rows, one per rank; the down GEMM pushes, a barrier kernel, tp_sum, a barrier kernel.
+    "pull": the partial stays local; a barrier kernel, tp_reduce pulls the blocks it sums from the peers, a barrier.
+    Measured for the 27B-class FFN (2048 rows), push against pull: 449 against 483 us on two B200s, 220 against 259 us
+    on eight. (The pushed stores leave as whole 128-byte row segments: one 16-byte piece per lane took 537 and 437 us.)"""
+
+    def __init__(self, hb, ctx, rank: int, world: int, m: int, h: int, out: int = OUT_RESIDUAL, device=None, push: bool | None = None, mode: str | None = None):
+        self.hb, self.ctx, self.rank, self.world, self.m, self.h, self.out = hb, ctx, rank, world, m, h, out
         dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
-        self.push = (True if push is None else bool(push)) and world > 1
+        if mode is None:
+            mode = ("push" if push else "pull") if push is not None else ("stream" if world in (2, 4, 8) else "push")
+        if world == 1:
+            mode = "pull"
+        assert mode in ("stream", "push", "pull")
+        self.mode = mode
+        self.push = mode == "push"
         self.rows_per = (m + world - 1) // world
-        # acc: the whole partial [m][h] (pull), or the staging [world][rows_per][h] of the blocks this rank sums (push)
-        self.pb = PeerBuffers(ctx, rank, world, {"acc": max(m, world * self.rows_per) * h * 4, "y": m * h * 2}, dev)
+        self.groups = (m + TP_GROUP_ROWS - 1) // TP_GROUP_ROWS
+        self.group_part = TP_GROUP_ROWS // world
+        # acc: the whole partial [m][h] (pull), the staging [world][rows_per][h] of the blocks this rank sums (push), or the
+        # staging [world][groups][256 / world][h] of its slices of every group (stream)
+        acc_rows = {"pull": m, "push": max(m, world * self.rows_per), "stream": world * self.groups * self.group_part}[mode]
+        sizes = {"acc": acc_rows * h * 4, "y": m * h * 2}
+        if mode == "stream":
+            assert self.groups <= TP_MAX_GROUPS
+            sizes.update(gflags=world * TP_MAX_GROUPS * 4, done=256)
+            self.ctl = ctx.alloc(TP_CTL_WORDS * 4)  # zeroed: step 0
+        self.pb = PeerBuffers(ctx, rank, world, sizes, dev)
         self.acc, self.y = self.pb.local["acc"], self.pb.local["y"]
         self._yv = _view(self.y, (m, h), "<i2", dev).view(torch.bfloat16)
         self.token = torch.zeros(1, device=dev, dtype=torch.float32)
-        self.k_reduce = ctx.tp_sum(h, out, world, rank) if self.push else ctx.tp_reduce(h, out, world, rank)
+        self.k_reduce = None if mode == "stream" else ctx.tp_sum(h, out, world, rank) if self.push else ctx.tp_reduce(h, out, world, rank)
+        self._k_stream = {}
         self.push_table = torch.zeros(world, device=dev, dtype=torch.int64)  # where this rank's block for owner d goes
         self.kernels = {}
+        self.kernels_per_step = 0
         self.emit = _launch_now
         self.recorded = _Recorded(ctx, self, self.pb)
+
+    def describe(self) -> str:
+        return {
+            "stream": "rows dealt in groups of 256, each rank sums 256/P rows of every group: the down GEMM's epilogue stores its f32 partial tile by tile into the "
+                      "summing ranks' staging (NVLink, under the GEMM) and flags each finished group; tp_sum_stream runs beside the GEMM (programmatic launch), sums "
+                      "the groups as they complete in rank order, rounds once, adds the residual, stores bf16 Y to every rank and ends with its own handshake "
+                      "(3 kernels per step, no barrier kernel, no NCCL call)",
+            "push": "down GEMM epilogue stores its f32 partial block by block into the summing ranks' memory (NVLink, under the GEMM); tp_sum: rank-order sum, one "
+                    "rounding, residual, peer stores of bf16 Y; 2 barrier kernels (no NCCL call in the step)",
+            "pull": "f32 partial stays local; tp_reduce pulls the blocks it sums through NVLink loads, rank-order sum, one rounding, residual, peer stores of bf16 Y; "
+                    "2 barrier kernels (no NCCL call in the step)",
+        }[self.mode]
 
     def _w(self, t):
         return self.ctx.wrap(t.data_ptr(), max(t.numel() * t.element_size(), 1))
@@ -537,7 +585,8 @@ class TpPeer:
         self._after_connect()
 
     def _after_connect(self) -> None:
-        slot = self.rank * self.rows_per * self.h * 4  # slot `rank` of every owner's staging buffer
+        # slot `rank` of every owner's staging buffer
+        slot = self.rank * (self.groups * self.group_part if self.mode == "stream" else self.rows_per) * self.h * 4
         self.push_table.copy_(self.pb.tables["acc"] + slot)
 
     def close(self) -> None:
@@ -558,14 +607,26 @@ class TpPeer:
         key = (h, ip)
         if key not in self.kernels:
             hmid = torch.empty((self.m, ip), device=x.device, dtype=torch.bfloat16)
+            form = {"pull": {}, "push": dict(y_shards=self.world), "stream": dict(y_shards=self.world, y_group_rows=TP_GROUP_ROWS, y_signal=self.rank + 1)}[self.mode]
             self.kernels[key] = (self.ctx.gemm(h, 2 * ip, OUT_SWIGLU, rows_max=self.m, cta_pair=1),
-                                 self.ctx.gemm(ip, h, OUT_F32, rows_max=self.m, cta_pair=1, y_shards=self.world if self.push else 0), hmid)
+                                 self.ctx.gemm(ip, h, OUT_F32, rows_max=self.m, cta_pair=1, **form), hmid)
         k_gu, k_down, hmid = self.kernels[key]
         self.emit(k_gu, m, self._w(wgu_local), self._w(x), self._w(hmid))
-        self.emit(k_down, m, self._w(wd_local), self._w(hmid), self._w(self.push_table) if self.push else self.acc)
+        if self.mode == "stream":
+            self.emit(k_down, m, self._w(wd_local), self._w(hmid), self._w(self.push_table), self.pb.table("gflags"), self.ctl)
+        else:
+            self.emit(k_down, m, self._w(wd_local), self._w(hmid), self._w(self.push_table) if self.push else self.acc)
 
-    def phase_reduce(self) -> None:  # every rank's partial is complete (push: has arrived)
-        self.emit(self.k_reduce, self.m, self.acc if self.push else self.pb.table("acc"), self.pb.table("y"))
+    def phase_reduce(self, sync: bool = False) -> None:
+        """pull / push: every rank's partial is complete (push: has arrived). stream with sync: right behind this
+        rank's GEMMs, the kernel waits for the flags itself; without: as for push."""
+        if self.mode == "stream":
+            sync = bool(sync)
+            if sync not in self._k_stream:
+                self._k_stream[sync] = self.ctx.tp_sum_stream(self.h, self.out, self.world, self.rank, TP_GROUP_ROWS, 1 if sync else 0)
+            self.emit(self._k_stream[sync], self.m, self.acc, self.pb.table("y"), self.pb.local["gflags"], self.pb.table("done"), self.ctl)
+        else:
+            self.emit(self.k_reduce, self.m, self.acc if self.push else self.pb.table("acc"), self.pb.table("y"))
 
 
 def tp_peer_connect(state: TpPeer, group=None) -> None:
@@ -587,8 +648,20 @@ def tp_ffn_peer(state: TpPeer, x, wgu_local, wd_local, group=None, nccl_sync: bo
 
 
 def _tp_step(state: TpPeer, x, wgu_local, wd_local, group, nccl_sync):
+    launched = state.ctx.launch_count()
+    try:
+        return _tp_step_body(state, x, wgu_local, wd_local, group, nccl_sync)
+    finally:
+        if state.emit is _launch_now:
+            state.kernels_per_step = state.ctx.launch_count() - launched
+
+
+def _tp_step_body(state: TpPeer, x, wgu_local, wd_local, group, nccl_sync):
     multi = state.world > 1
     state.phase_gemms(x, wgu_local, wd_local)
+    if state.mode == "stream" and multi and not nccl_sync and not state.pb.emulated:
+        state.phase_reduce(sync=True)  # the kernel orders itself against the other ranks: no barrier before or after
+        return state.y_view()
     if multi:
         dist.all_reduce(state.token, group=group) if nccl_sync else state.pb.barrier()  # every rank's partial is complete
     state.phase_reduce()

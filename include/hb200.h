@@ -181,6 +181,16 @@ typedef struct {
                             block of its partial product straight into the buffer of the rank that sums it, tile by tile
                             while it computes; the CTA-pair form stores whole 128-byte row segments (the form to use when
                             the blocks are peers' memory). No reference counterpart */
+    uint32_t y_group_rows; /* with y_shards = P: 0 = block b holds the contiguous rows [b * ceil(m / P), ...); G > 0 (a
+                            multiple of 32 * P, at most 256) = the rows are dealt in groups of G: block b holds, for every
+                            group g, the G / P rows [g * G + b * G / P, ...) at its rows [g * G / P, ...). Every rank then
+                            sums a slice of every group, and the sum of a group can start while the GEMM works on the next */
+    uint32_t y_signal;   /* with y_group_rows = 256: r + 1 = this GEMM runs on rank r of the y_shards ranks and tells the
+                            summing ranks when a group of rows is complete (0 = it tells nobody). Two more bindings follow Y: flag_table, a device array u64[P] of the addresses of every rank's
+                            flags u32[P][HB_TP_MAX_GROUPS], and ctl, this rank's own control words u32[HB_TP_CTL_WORDS]
+                            (zeroed once). When the last tile of group g is stored, flag [rank][g] of every rank is set to
+                            ctl[0] + 1, the step's number, which hb_tp_sum_stream_get's kernel waits for and then writes
+                            to ctl[0]. The tiles are walked group by group (m_first is ignored). */
 } hb_gemm_desc;
 int hb_gemm_get(hb_ctx* ctx, const hb_gemm_desc* desc, hb_kernel** out);
 
@@ -293,6 +303,22 @@ int hb_tp_reduce_get(hb_ctx* ctx, uint32_t n, uint32_t out, uint32_t world, uint
  * Sums the slots in rank order, rounds once, applies the output mode with its own old Y and stores the rows into
  * every rank's Y. Bindings: staging (local), peers_y. The host puts a barrier before and after. */
 int hb_tp_sum_get(hb_ctx* ctx, uint32_t n, uint32_t out, uint32_t world, uint32_t rank, hb_kernel** res);
+/* The sum as a kernel that runs beside the GEMM whose partial it sums (hb_gemm_desc.y_group_rows = group_rows,
+ * y_signal = 1 on every rank): for each group of rows in turn it waits until every rank's GEMM has flagged the group,
+ * sums this rank's slice of it from the staging slots in rank order, rounds once, applies the output mode and stores
+ * the bf16 rows into every rank's Y, while the GEMMs work on the later groups. It is launched right behind the GEMM
+ * and may start while the GEMM runs (programmatic stream serialization; the GEMM lets it go at its start); its blocks
+ * share the SMs with the GEMM's. When the last group is stored it tells every rank, waits until every rank has said
+ * the same (so that Y is complete everywhere and the staging may be overwritten when it returns: no barrier kernel
+ * before or after), and writes the step's number to ctl[0]. All waits are bounded (hb_set_peer_wait_ms).
+ * staging: this rank's f32 [world][groups][group_rows / world][n], groups = ceil(m / group_rows).
+ * sync = 0: no flag is waited for and none is sent (the host orders the kernels: one process that holds every rank on
+ * one GPU, or ranks ordered by a collective of the caller's).
+ * Bindings: staging, peers_y, flags (this rank's u32[world][HB_TP_MAX_GROUPS]), peers_done (u64[world]: every rank's
+ * u32[world], zeroed once), ctl (this rank's, the array the GEMM is bound to). No reference counterpart. */
+#define HB_TP_MAX_GROUPS 64u
+#define HB_TP_CTL_WORDS 128u
+int hb_tp_sum_stream_get(hb_ctx* ctx, uint32_t n, uint32_t out, uint32_t world, uint32_t rank, uint32_t group_rows, uint32_t sync, hb_kernel** res);
 
 /* The GEMM for callers that must not allocate device memory. (No counterpart in the reference: its buffers all
  * come from Gpu::alloc at load.)

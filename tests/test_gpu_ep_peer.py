@@ -189,7 +189,10 @@ def _two_process_worker(rank, world, port, repo, result):
             out = d.ep_moe_peer(st, xs, ss, wl, dl, nccl_sync=it >= 7, recorded=2 <= it < 7)
             stream.synchronize()
             ctx.sync()
-            ok = ok and bool(torch.equal(out, want[rank * rpr : (rank + 1) * rpr]))
+            same = bool(torch.equal(out, want[rank * rpr : (rank + 1) * rpr]))
+            if not same:
+                print(f"rank {rank}: MoE block, step {it}: differs from the one-rank block", file=sys.stderr, flush=True)
+            ok = ok and same
         ok = ok and len(st.recorded.graphs) == 2
         dist.barrier()
         st.close()
@@ -199,8 +202,8 @@ def _two_process_worker(rank, world, port, repo, result):
         a, b = d.shard_gate_up(t16(wgu2), rank, world).cuda(), d.shard_down(t16(wd2), rank, world).cuda()
         be = d.GpuBackend(hb, ctx, rows_max=512)
         y_ref = d.tp_ffn(be, t16(x2).cuda(), a, b, t16(y0).cuda())
-        for push in (False, True):  # the partial pulled by the summing kernel; pushed by the GEMM's epilogue
-            tp = d.TpPeer(hb, ctx, rank, world, m, h, push=push)
+        for mode in ("pull", "push", "stream"):  # pulled by the summing kernel; pushed by the GEMM; pushed and summed beside the GEMM
+            tp = d.TpPeer(hb, ctx, rank, world, m, h, mode=mode)
             d.tp_peer_connect(tp)
             x2d = t16(x2).cuda()
             for it in range(6):  # step by step, recorded then replayed (1..4), with NCCL barriers
@@ -209,7 +212,10 @@ def _two_process_worker(rank, world, port, repo, result):
                 y = d.tp_ffn_peer(tp, x2d, a, b, nccl_sync=it == 5, recorded=1 <= it < 5)
                 stream.synchronize()
                 ctx.sync()
-                ok = ok and bool(torch.equal(y, y_ref))
+                same = bool(torch.equal(y, y_ref))
+                if not same:
+                    print(f"rank {rank}: FFN form {mode}, step {it}: differs from the all-reduce form", file=sys.stderr, flush=True)
+                ok = ok and same
                 dist.barrier()
             ok = ok and len(tp.recorded.graphs) == 1
             tp.close()
@@ -240,17 +246,19 @@ def test_two_processes_over_nvlink():
 
 # ---------------------------------------------------------------- the tensor-parallel FFN through tp_reduce
 
-@pytest.mark.parametrize("push", [False, True])
-@pytest.mark.parametrize("world", [1, 2, 4])
-def test_tp_reduce_emulated_ranks(env, hb200, oracle, world, push):
+@pytest.mark.parametrize("mode", ["pull", "push", "stream"])
+@pytest.mark.parametrize("world,m", [(1, 200), (2, 200), (4, 200), (8, 200), (4, 700), (8, 1024)])
+def test_tp_reduce_emulated_ranks(env, hb200, oracle, world, m, mode):
     # push: the down GEMM stores each block of rows of its partial into its owner's staging buffer (y_shards) and the
-    # sum reads local memory; pull: the partial stays whole and the sum fetches the blocks from the peers
+    # sum reads local memory; pull: the partial stays whole and the sum fetches the blocks from the peers; stream: the
+    # rows dealt in groups of 256, every rank sums a slice of every group (here host-ordered: the ranks share a GPU).
+    # Row counts that end inside a group, inside a rank's slice of it, and on a group's edge.
     d, ctx = env
-    m, h, inter = 200, 256, 512
+    h, inter = 256, 512
     x, wgu, wd, y0 = oracle.normal((m, h), 1, 1, 1.0), oracle.normal((2 * inter, h), 2, 2, h**-0.5), oracle.normal((h, inter), 3, 3, inter**-0.5), oracle.normal((m, h), 4, 4, 1.0)
     xt = t16(x).cuda()
-    ranks = [d.TpPeer(hb200, ctx, r, world, m, h, push=push) for r in range(world)]
-    assert all(st.push == (push and world > 1) for st in ranks)
+    ranks = [d.TpPeer(hb200, ctx, r, world, m, h, mode=mode) for r in range(world)]
+    assert all(st.mode == (mode if world > 1 else "pull") for st in ranks)
     for st in ranks:
         st.connect(ranks)
         st.set_y(t16(y0).cuda())
