@@ -18,8 +18,17 @@
 //                              the ranks is the order a single GPU's sort would give the same pairs.
 //   ep_return (source side):   EY[list[p]] = row (base(d, s) + p - first(s, d)) of d's output buffer, read from d.
 //
-// A kernel of this file never waits for another GPU: the steps are separated by the host's collectives on the stream
-// (the all-gather of the offsets before the dispatch, a barrier after it and another after the expert GEMMs).
+//   ep_combine (source side):  the return and moe_combine in one: out[row] = the bf16 chain over the row's slots in
+//                              route order (src/metal/qwen_kernels.rs:2119-2161), every slot's expert output read
+//                              straight from its owner's output buffer at the place the dispatch noted in `where`.
+//                              EY is never written or re-read.
+//
+// Order between the ranks: the all-gather of the offsets before the dispatch, "every rank's rows have landed" before
+// the expert GEMMs, "every rank's outputs are complete" before the return. The first and the last are barrier kernels
+// on the stream. The middle one is either a barrier kernel too, or (dispatch and plan bound to their optional ranges)
+// carried by the kernels themselves: the block of the dispatch that finishes last stores the step's number into a
+// flag on every rank, and the plan, which runs before the expert GEMMs, waits (bounded) until every rank's number
+// has arrived. No other kernel of this file waits for another GPU.
 // No reference counterpart: the reference runs on one GPU.
 #include <algorithm>
 
@@ -38,7 +47,14 @@ struct EpParams {
     const uint64_t* peers;     // [world] base of every rank's receive (dispatch) or output (return) buffer
     uint32_t h8, top_k, experts, world, rank, epr, cap;
     uint32_t* status;
+    // dispatch, optional: where[pair] = owner << 28 | row in the owner's buffers (0xffffffff: did not fit), and the
+    // "my rows have landed" flag for every rank
+    uint32_t* where;
+    const uint64_t* peers_landed;  // [world] -> u32[world] on every rank
+    uint32_t* ctl;                 // [0] dispatches completed (the step's number), [1] blocks finished
 };
+
+constexpr uint32_t EP_WHERE_NONE = 0xffffffffu;
 
 // first[d], base[d] for this rank as a source, in shared memory.
 __device__ __forceinline__ void ep_source_tables(const EpParams& p, uint32_t* first, uint32_t* base) {
@@ -66,10 +82,14 @@ __global__ void __launch_bounds__(256) ep_move_kernel(const EpParams p) {
         while (d + 1 < p.world && pos >= first[d + 1]) ++d;
         const uint32_t r = base[d] + pos - first[d];
         if (r >= p.cap) {  // the counts do not fit the buffers the host sized: report, move nothing
-            if (lane == 0) report(p.status, ST_BAD_TABLE, pos, r);
+            if (lane == 0) {
+                report(p.status, ST_BAD_TABLE, pos, r);
+                if (!RETURN && p.where) p.where[p.list[pos]] = EP_WHERE_NONE;
+            }
             continue;
         }
         const uint32_t pair = p.list[pos];
+        if (!RETURN && p.where && lane == 0) p.where[pair] = (d << 28) | r;
         uint4* remote = reinterpret_cast<uint4*>(p.peers[d]) + (size_t)r * p.h8;
         if constexpr (RETURN) {
             uint4* dst = p.ey + (size_t)pair * p.h8;
@@ -79,6 +99,73 @@ __global__ void __launch_bounds__(256) ep_move_kernel(const EpParams p) {
             for (uint32_t c = lane; c < p.h8; c += 32) remote[c] = src[c];
         }
     }
+    if (!RETURN && p.peers_landed) {
+        // this block's rows are out; the block that gets here last numbers the step and tells every rank
+        __shared__ uint32_t last_s;
+        __threadfence_system();
+        __syncthreads();
+        if (threadIdx.x == 0) last_s = atomicAdd(p.ctl + 1, 1u) == gridDim.x - 1u ? 1u : 0u;
+        __syncthreads();
+        if (last_s && threadIdx.x < p.world) {
+            __threadfence_system();
+            const uint32_t step = *reinterpret_cast<volatile uint32_t*>(p.ctl) + 1u;
+            uint32_t* flag = reinterpret_cast<uint32_t*>(p.peers_landed[threadIdx.x]) + p.rank;
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(step) : "memory");
+        }
+        __syncthreads();
+        if (last_s && threadIdx.x == 0) {
+            p.ctl[1] = 0u;
+            *reinterpret_cast<volatile uint32_t*>(p.ctl) += 1u;
+        }
+    }
+}
+
+// The return and the combine in one kernel: out[row][i] over the slots in route order, acc = bf16(acc + bf16(y * w))
+// (reference src/metal/qwen_kernels.rs:2119-2161), y read from the output buffer of the rank that ran the slot's expert.
+struct EpCombineParams {
+    const uint64_t* peers_ey;  // [world] bf16 [cap][h] on every rank
+    const uint32_t* where;     // [rows * top_k]
+    const uint32_t* route;     // [rows][2 * top_k]
+    uint16_t* out;             // [rows][h]
+    uint32_t rows, h8, top_k, world;
+};
+
+__global__ void __launch_bounds__(256) ep_combine_kernel(const EpCombineParams p) {
+    __shared__ uint64_t ey_s[EP_MAX_WORLD];
+    if (threadIdx.x < p.world) ey_s[threadIdx.x] = p.peers_ey[threadIdx.x];
+    __syncthreads();
+    const size_t total = (size_t)p.rows * p.h8;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const uint32_t row = (uint32_t)(i / p.h8), c = (uint32_t)(i % p.h8);
+        uint32_t accp[4] = {0u, 0u, 0u, 0u};  // the running bf16 values, two per word
+        for (uint32_t s0 = 0; s0 < p.top_k; s0 += 8) {
+            uint4 v[8];
+            float w[8];
+            // all of a batch's loads (remote ones take a microsecond or two) before the first is used
+#pragma unroll
+            for (int b = 0; b < 8; ++b) {
+                const uint32_t s = min(s0 + b, p.top_k - 1);
+                const uint32_t loc = p.where[(size_t)row * p.top_k + s];
+                v[b] = loc == EP_WHERE_NONE ? make_uint4(0u, 0u, 0u, 0u)
+                                            : __ldcs(reinterpret_cast<const uint4*>(ey_s[loc >> 28]) + (size_t)(loc & 0x0fffffffu) * p.h8 + c);
+                w[b] = __uint_as_float(p.route[(size_t)row * 2 * p.top_k + p.top_k + s]);
+            }
+#pragma unroll
+            for (int b = 0; b < 8; ++b) {
+                if (s0 + b < p.top_k) {
+                    const uint32_t vw[4] = {v[b].x, v[b].y, v[b].z, v[b].w};
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const float lo = __uint_as_float(vw[j] << 16), hi = __uint_as_float(vw[j] & 0xffff0000u);
+                        const uint32_t t = f32x2_to_bf16x2(__fmul_rn(lo, w[b]), __fmul_rn(hi, w[b]));
+                        accp[j] = f32x2_to_bf16x2(__fadd_rn(__uint_as_float(accp[j] << 16), __uint_as_float(t << 16)),
+                                                  __fadd_rn(__uint_as_float(accp[j] & 0xffff0000u), __uint_as_float(t & 0xffff0000u)));
+                    }
+                }
+            }
+        }
+        *reinterpret_cast<uint4*>(p.out + ((size_t)row * p.h8 + c) * 8) = make_uint4(accp[0], accp[1], accp[2], accp[3]);
+    }
 }
 
 struct PlanParams {
@@ -87,6 +174,10 @@ struct PlanParams {
     uint32_t* tiles;
     uint32_t experts, world, rank, epr, bm, cap;
     uint32_t* status;
+    // optional: wait until every rank's dispatch has flagged this step before the kernels behind the plan may run
+    const uint32_t* landed;  // this rank's u32[world]
+    const uint32_t* ctl;     // the dispatch's control words: [0] = the step's number
+    long long wait_cycles;
 };
 
 constexpr int PLAN_THREADS = 1024;
@@ -99,6 +190,10 @@ __global__ void __launch_bounds__(PLAN_THREADS) ep_plan_kernel(const PlanParams 
     uint32_t* recvbase = st + p.epr;       // [world] first receive row of source s
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t stride = p.experts + 1, e0 = p.rank * p.epr;
+    if (p.landed && tid < p.world) {
+        const uint32_t step = *reinterpret_cast<const volatile uint32_t*>(p.ctl);  // this rank's dispatch has numbered the step
+        if (!wait_for_step(p.landed + tid, step, p.wait_cycles)) report(p.status, ST_WAIT_TIMEOUT, WHERE_PEER, 32u + tid);
+    }
     if (tid == 0) {
         uint32_t b = 0;
         for (uint32_t s = 0; s < p.world; ++s) {
@@ -161,7 +256,8 @@ struct EpMove : hb_kernel {
     uint32_t h = 0, top_k = 0, experts = 0, world = 0, rank = 0, cap = 0;
     bool ret = false;
     int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
-        if (na != 4) return fail(ctx, HB_INVALID, name + (ret ? ": bindings are peers, EY, list, offsets" : ": bindings are X, peers, list, offsets"));
+        if (na != 4 && !(na == 7 && !ret))
+            return fail(ctx, HB_INVALID, name + (ret ? ": bindings are peers, EY, list, offsets" : ": bindings are X, peers, list, offsets[, where, peers_landed, ctl]"));
         if (m == 0) return fail(ctx, HB_INVALID, name + ": m = 0");
         const uint32_t pairs = m * top_k;
         const hb_range& rows = ret ? a[1] : a[0];
@@ -184,6 +280,13 @@ struct EpMove : hb_kernel {
         p.epr = experts / world;
         p.cap = cap;
         p.status = ctx->status_dev;
+        if (na == 7) {
+            if (cap > 0x0fffffffu || world > 16) return fail(ctx, HB_UNSUPPORTED, name + ": `where` packs the owner in 4 bits and the row in 28");
+            if (!range_ok(a[4], (size_t)pairs * 4) || !range_ok(a[5], (size_t)world * 8) || !range_ok(a[6], 8)) return fail(ctx, HB_INVALID, name + ": a bound range is too small");
+            p.where = static_cast<uint32_t*>(a[4].ptr);
+            p.peers_landed = static_cast<const uint64_t*>(a[5].ptr);
+            p.ctl = static_cast<uint32_t*>(a[6].ptr);
+        }
         if (ret) ep_move_kernel<true><<<ep_grid(ctx, pairs), 256, 0, ctx->stream>>>(p);
         else ep_move_kernel<false><<<ep_grid(ctx, pairs), 256, 0, ctx->stream>>>(p);
         HB_CUDA(ctx, cudaGetLastError());
@@ -195,7 +298,7 @@ struct EpMove : hb_kernel {
 struct EpPlan : hb_kernel {
     uint32_t experts = 0, world = 0, rank = 0, bm = 0, cap = 0;
     int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
-        if (na != 3) return fail(ctx, HB_INVALID, name + ": bindings are offsets, list, tiles");
+        if (na != 3 && na != 5) return fail(ctx, HB_INVALID, name + ": bindings are offsets, list, tiles[, landed, ctl]");
         (void)m;
         const uint32_t epr = experts / world;
         if (!range_ok(a[0], (size_t)world * (experts + 1) * 4) || !range_ok(a[1], (size_t)cap * 4) ||
@@ -212,7 +315,39 @@ struct EpPlan : hb_kernel {
         p.bm = bm;
         p.cap = cap;
         p.status = ctx->status_dev;
+        if (na == 5) {
+            if (!range_ok(a[3], (size_t)world * 4) || !range_ok(a[4], 8)) return fail(ctx, HB_INVALID, name + ": a bound range is too small");
+            p.landed = static_cast<const uint32_t*>(a[3].ptr);
+            p.ctl = static_cast<const uint32_t*>(a[4].ptr);
+            p.wait_cycles = (long long)ctx->peer_wait_ms * 2000000ll;
+        }
         ep_plan_kernel<<<1, PLAN_THREADS, (3 * epr + world) * 4, ctx->stream>>>(p);
+        HB_CUDA(ctx, cudaGetLastError());
+        ctx->launches++;
+        return HB_OK;
+    }
+};
+
+struct EpCombine : hb_kernel {
+    uint32_t h = 0, top_k = 0, world = 0;
+    int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
+        if (na != 4) return fail(ctx, HB_INVALID, name + ": bindings are peers_ey, where, route, out");
+        if (m == 0) return fail(ctx, HB_INVALID, name + ": m = 0");
+        if (!range_ok(a[0], (size_t)world * 8) || !range_ok(a[1], (size_t)m * top_k * 4) || !range_ok(a[2], (size_t)m * 2 * top_k * 4) || !range_ok(a[3], (size_t)m * h * 2))
+            return fail(ctx, HB_INVALID, name + ": a bound range is too small");
+        if (reinterpret_cast<uintptr_t>(a[3].ptr) & 15u) return fail(ctx, HB_INVALID, name + ": out must be 16-byte aligned");
+        EpCombineParams p{};
+        p.peers_ey = static_cast<const uint64_t*>(a[0].ptr);
+        p.where = static_cast<const uint32_t*>(a[1].ptr);
+        p.route = static_cast<const uint32_t*>(a[2].ptr);
+        p.out = static_cast<uint16_t*>(a[3].ptr);
+        p.rows = m;
+        p.h8 = h / 8;
+        p.top_k = top_k;
+        p.world = world;
+        const size_t items = (size_t)m * p.h8;
+        const uint32_t grid = (uint32_t)std::max<size_t>(1, std::min<size_t>((items + 255) / 256, (size_t)ctx->sm_count * 8));
+        ep_combine_kernel<<<grid, 256, 0, ctx->stream>>>(p);
         HB_CUDA(ctx, cudaGetLastError());
         ctx->launches++;
         return HB_OK;
@@ -241,6 +376,20 @@ int make_ep_move(hb_ctx* ctx, bool ret, uint32_t h, uint32_t top_k, uint32_t exp
     k->nargs = 4;
     k->name = std::string(ret ? "ep_return_" : "ep_dispatch_") + std::to_string(h) + "_k" + std::to_string(top_k) + "_e" + std::to_string(experts) + "_r" +
               std::to_string(rank) + "of" + std::to_string(world) + "_c" + std::to_string(cap);
+    *out = intern(ctx, std::move(k));
+    return HB_OK;
+}
+
+int make_ep_combine(hb_ctx* ctx, uint32_t h, uint32_t top_k, uint32_t world, hb_kernel** out) {
+    *out = nullptr;
+    if (world < 1 || world > EP_MAX_WORLD || h == 0 || h % 8 != 0 || top_k == 0) return fail(ctx, HB_UNSUPPORTED, "ep combine: 1..16 ranks, h a positive multiple of 8");
+    auto k = std::make_unique<EpCombine>();
+    k->h = h;
+    k->top_k = top_k;
+    k->world = world;
+    k->kind = 17;
+    k->nargs = 4;
+    k->name = "ep_combine_" + std::to_string(h) + "_k" + std::to_string(top_k) + "_w" + std::to_string(world);
     *out = intern(ctx, std::move(k));
     return HB_OK;
 }

@@ -165,6 +165,19 @@ __device__ __forceinline__ void report(uint32_t* status, uint32_t code, uint32_t
     }
 }
 
+// Waits until a step number another GPU (or another kernel) stores with release semantics at system scope has reached
+// `step`; gives up after `limit` SM cycles. What the writer stored before the number is visible after the wait.
+__device__ __forceinline__ bool wait_for_step(const uint32_t* word, uint32_t step, long long limit) {
+    const long long t0 = clock64();
+    uint32_t v;
+    while (true) {
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(word) : "memory");
+        if ((int32_t)(v - step) >= 0) return true;
+        if (clock64() - t0 > limit) return false;
+        __nanosleep(64);
+    }
+}
+
 // ---------------------------------------------------------------- mbarrier
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }

@@ -99,17 +99,6 @@ struct TpStreamParams {
     uint32_t* status;
 };
 
-__device__ __forceinline__ bool wait_for_step(const uint32_t* word, uint32_t step, long long limit) {
-    const long long t0 = clock64();
-    uint32_t v;
-    while (true) {
-        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(word) : "memory");
-        if ((int32_t)(v - step) >= 0) return true;
-        if (clock64() - t0 > limit) return false;
-        __nanosleep(64);
-    }
-}
-
 template <int OUT>
 __global__ void __launch_bounds__(128) tp_sum_stream_kernel(const TpStreamParams p) {
     __shared__ uint64_t y_s[TP_MAX_WORLD];

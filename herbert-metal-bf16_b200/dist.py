@@ -378,45 +378,73 @@ class EpPeer:
     `ctx` must launch on torch's current stream (Context.set_stream) so that the phases and any collective are
     ordered. `cap` is the number of rows the receive and output buffers hold; the default, every pair of every
     rank, can never overflow.
+
+    fused (the default): the dispatch notes where every pair's output row will be and tells the other ranks when its
+    rows have landed; the plan waits for that itself (no barrier kernel between dispatch and expert GEMMs); the return
+    and the combine are one kernel that reads every slot's output row from its owner (no EY written and re-read).
+    fused = False: dispatch, barrier, plan, GEMMs, barrier, return into EY, combine.
+    With one rank there is nothing to exchange and the step is the plain block (route, sort, the expert GEMMs gathering
+    from X and scattering into EY, combine) unless plain_when_alone is False (the exchange kernels with one rank, as the
+    tests run them).
     """
 
     def __init__(self, hb, ctx, rank: int, world: int, rows: int, h: int, mi: int, experts: int, top_k: int, bm: int = 64, cap: int | None = None,
-                 device=None):
+                 device=None, fused: bool = True, plain_when_alone: bool = True):
         assert experts % world == 0
         self.hb, self.ctx, self.rank, self.world = hb, ctx, rank, world
         self.rows, self.h, self.mi, self.experts, self.top_k, self.bm = rows, h, mi, experts, top_k, bm
         self.epr = experts // world
         self.pairs = rows * top_k
+        self.plain = world == 1 and plain_when_alone
+        self.fused = fused and not self.plain
         self.cap = cap if cap is not None else self.pairs * world
         dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         i32 = dict(device=dev, dtype=torch.int32)
         # shared with the peers: the rows this rank receives and the outputs of its experts, both [cap][h] bf16, and
         # two copies of the offsets of all ranks (calls alternate: a peer may write the next while this one is read)
         offs_bytes = world * (experts + 1) * 4
-        self.pb = PeerBuffers(ctx, rank, world, {"recv": self.cap * h * 2, "ey": self.cap * h * 2, "offs0": offs_bytes, "offs1": offs_bytes}, dev)
-        self.recv, self.ey_recv = self.pb.local["recv"], self.pb.local["ey"]
+        sizes = {"offs0": offs_bytes, "offs1": offs_bytes}
+        if not self.plain:
+            sizes.update(recv=self.cap * h * 2, ey=self.cap * h * 2)
+        if self.fused:
+            sizes["landed"] = 256
+        self.pb = PeerBuffers(ctx, rank, world, sizes, dev)
         self.offs_both = [_view(self.pb.local[n], (world, experts + 1), "<i4", dev) for n in ("offs0", "offs1")]
         self.parity = 0
         self.route = torch.zeros(rows, 2 * top_k, **i32)
         self.list = torch.zeros(self.pairs, **i32)
         self.tiles = torch.zeros(1 + 3 * hb.lib().hb_moe_tiles(rows, top_k, experts, bm), **i32)
         self.offs = torch.zeros(experts + 1, **i32)
-        self.rlist = torch.zeros(self.cap, **i32)
-        self.rtiles = torch.zeros(1 + 3 * hb.lib().hb_moe_tiles(self.cap, 1, self.epr, bm), **i32)
-        self.ehb = torch.zeros(self.cap, mi, device=dev, dtype=torch.bfloat16)
-        self.ey = torch.zeros(self.pairs, h, device=dev, dtype=torch.bfloat16)
         self.out = torch.zeros(rows, h, device=dev, dtype=torch.bfloat16)
         self.token = torch.zeros(1, device=dev, dtype=torch.float32)  # operand of the NCCL form of the barrier
         rows_cap = 1 << max(rows - 1, 0).bit_length()
-        kw = dict(rows_max=self.cap, top_k=1, experts=self.epr, bm=bm, merge_runs=1)
         self.k_route = ctx.route(experts, top_k)
         self.k_sort = ctx.moe_sort(experts, top_k, rows_cap, bm)
-        self.k_dispatch = ctx.ep_dispatch(h, top_k, experts, world, rank, self.cap)
-        self.k_plan = ctx.ep_plan(experts, world, rank, bm, self.cap)
-        self.k_gate_up = ctx.gemm(h, 2 * mi, OUT_SWIGLU, rows_mode=hb.ROWS_GATHER, **kw)
-        self.k_down = ctx.gemm(mi, h, OUT_BF16, rows_mode=hb.ROWS_SCATTER, **kw)
-        self.k_return = ctx.ep_return(h, top_k, experts, world, rank, self.cap)
         self.k_combine = ctx.moe_combine(h, top_k)
+        if self.plain:
+            kw = dict(rows_max=rows_cap, top_k=top_k, experts=experts, bm=bm, merge_runs=1)
+            self.ehb = torch.zeros(self.pairs, mi, device=dev, dtype=torch.bfloat16)
+            self.ey = torch.zeros(self.pairs, h, device=dev, dtype=torch.bfloat16)
+            self.k_gate_up = ctx.gemm(h, 2 * mi, OUT_SWIGLU, rows_mode=hb.ROWS_GATHER, **kw)
+            self.k_down = ctx.gemm(mi, h, OUT_BF16, rows_mode=hb.ROWS_SCATTER, **kw)
+        else:
+            self.recv, self.ey_recv = self.pb.local["recv"], self.pb.local["ey"]
+            self.rlist = torch.zeros(self.cap, **i32)
+            self.rtiles = torch.zeros(1 + 3 * hb.lib().hb_moe_tiles(self.cap, 1, self.epr, bm), **i32)
+            self.ehb = torch.zeros(self.cap, mi, device=dev, dtype=torch.bfloat16)
+            kw = dict(rows_max=self.cap, top_k=1, experts=self.epr, bm=bm, merge_runs=1)
+            self.k_dispatch = ctx.ep_dispatch(h, top_k, experts, world, rank, self.cap)
+            self.k_plan = ctx.ep_plan(experts, world, rank, bm, self.cap)
+            self.k_gate_up = ctx.gemm(h, 2 * mi, OUT_SWIGLU, rows_mode=hb.ROWS_GATHER, **kw)
+            self.k_down = ctx.gemm(mi, h, OUT_BF16, rows_mode=hb.ROWS_SCATTER, **kw)
+            if self.fused:
+                self.where = torch.zeros(self.pairs, **i32)
+                self.ctl = ctx.alloc(256)  # zeroed: step 0
+                self.k_ep_combine = ctx.ep_combine(h, top_k, world)
+            else:
+                self.ey = torch.zeros(self.pairs, h, device=dev, dtype=torch.bfloat16)
+                self.k_return = ctx.ep_return(h, top_k, experts, world, rank, self.cap)
+        self.kernels_per_step = 0
         self.emit = _launch_now
         self.recorded = _Recorded(ctx, self, self.pb)
 
@@ -440,18 +468,37 @@ class EpPeer:
         self.x = x
         self.parity ^= 1
         self.emit(self.k_route, self.rows, self._w(scores), self._w(self.route))
-        self.emit(self.k_sort, self.rows, self._w(self.route), self._w(self.list), self._w(self.tiles), self._w(self.offs))
+        if self.plain:
+            self.emit(self.k_sort, self.rows, self._w(self.route), self._w(self.list), self._w(self.tiles))
+        else:
+            self.emit(self.k_sort, self.rows, self._w(self.route), self._w(self.list), self._w(self.tiles), self._w(self.offs))
 
     def phase_dispatch(self) -> None:  # offs_all holds every rank's offsets
-        self.emit(self.k_dispatch, self.rows, self._w(self.x), self.pb.table("recv"), self._w(self.list), self._w(self.offs_all))
+        if self.plain:
+            return
+        args = [self._w(self.x), self.pb.table("recv"), self._w(self.list), self._w(self.offs_all)]
+        if self.fused:
+            args += [self._w(self.where), self.pb.table("landed"), self.ctl]
+        self.emit(self.k_dispatch, self.rows, *args)
 
-    def phase_experts(self, wgu_local, wd_local) -> None:  # every rank's dispatch has finished
-        self.emit(self.k_plan, 1, self._w(self.offs_all), self._w(self.rlist), self._w(self.rtiles))
+    def phase_experts(self, wgu_local, wd_local) -> None:  # every rank's dispatch has finished (fused: the plan sees to that)
+        if self.plain:
+            self.emit(self.k_gate_up, self.rows, self._w(wgu_local), self._w(self.x), self._w(self.ehb), self._w(self.list), self._w(self.tiles))
+            self.emit(self.k_down, self.rows, self._w(wd_local), self._w(self.ehb), self._w(self.ey), self._w(self.list), self._w(self.tiles))
+            return
+        args = [self._w(self.offs_all), self._w(self.rlist), self._w(self.rtiles)]
+        if self.fused:
+            args += [self.pb.local["landed"], self.ctl]
+        self.emit(self.k_plan, 1, *args)
         self.emit(self.k_gate_up, self.cap, self._w(wgu_local), self.recv, self._w(self.ehb), self._w(self.rlist), self._w(self.rtiles))
         self.emit(self.k_down, self.cap, self._w(wd_local), self._w(self.ehb), self.ey_recv, self._w(self.rlist), self._w(self.rtiles))
 
     def phase_return(self):  # every rank's expert GEMMs have finished
-        self.emit(self.k_return, self.rows, self.pb.table("ey"), self._w(self.ey), self._w(self.list), self._w(self.offs_all))
+        if self.fused:
+            self.emit(self.k_ep_combine, self.rows, self.pb.table("ey"), self._w(self.where), self._w(self.route), self._w(self.out))
+            return self.out
+        if not self.plain:
+            self.emit(self.k_return, self.rows, self.pb.table("ey"), self._w(self.ey), self._w(self.list), self._w(self.offs_all))
         self.emit(self.k_combine, self.rows, self._w(self.ey), self._w(self.route), self._w(self.out))
         return self.out
 
@@ -491,6 +538,9 @@ def _ep_step(state: EpPeer, x_local, scores_local, wgu_local, wd_local, group, n
 def _ep_step_body(state: EpPeer, x_local, scores_local, wgu_local, wd_local, group, nccl_sync):
     multi = state.world > 1
     state.phase_sort(x_local, scores_local)
+    if state.plain:
+        state.phase_experts(wgu_local, wd_local)
+        return state.phase_return()
     if not multi:
         state.offs_all[0].copy_(state.offs)
     elif nccl_sync:
@@ -498,8 +548,10 @@ def _ep_step_body(state: EpPeer, x_local, scores_local, wgu_local, wd_local, gro
     else:
         state.pb.allgather(state.offs, "offs1" if state.parity else "offs0")
     state.phase_dispatch()
-    if multi:
-        dist.all_reduce(state.token, group=group) if nccl_sync else state.pb.barrier()  # every rank's rows have landed
+    if multi and nccl_sync:
+        dist.all_reduce(state.token, group=group)
+    elif multi and not state.fused:
+        state.pb.barrier()  # every rank's rows have landed (fused: the dispatch flags it and the plan waits)
     state.phase_experts(wgu_local, wd_local)
     if multi:
         dist.all_reduce(state.token, group=group) if nccl_sync else state.pb.barrier()  # every rank's outputs are complete

@@ -281,12 +281,22 @@ int hb_matmul_q4_get(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t m, uint32_t l
  *     rank's experts, for expert GEMMs built with top_k = 1, experts / world experts and rows_max = cap, which are
  *     then launched with m = cap (the table, not m, says how many rows there are).
  *   return, bindings peers, EY, list, offsets_all: EY[list[p]] = the row of p in its owner's output buffer.
- * The kernels never wait for another GPU. The host orders the steps on the stream: all-gather of the offsets, then
- * dispatch, a barrier, plan and the expert GEMMs, a barrier, return. A count that exceeds `cap` rows is reported
+ *   combine (hb_ep_combine_get), bindings peers_ey, where, route, out: the return and moe_combine in one kernel:
+ *     out[row] = the bf16 chain acc = bf16(acc + bf16(y * w)) over the row's slots in route order
+ *     (src/metal/qwen_kernels.rs:2119-2161), every y read straight from its owner's output buffer; EY is never made.
+ *     `where` u32[m * top_k] is written by the dispatch when it is bound to three more ranges (below).
+ * The host orders the steps on the stream: all-gather of the offsets, then dispatch, a barrier, plan and the expert
+ * GEMMs, a barrier, return (or combine). The barrier between dispatch and plan may be carried by the two kernels
+ * themselves: dispatch bound to X, peers, list, offsets_all, where, peers_landed, ctl (peers_landed: u64[world], the
+ * addresses of every rank's u32[world] flags, zeroed once; ctl: this rank's u32[2], zeroed once) numbers the step in
+ * ctl[0] and stores the number into flag `rank` of every rank when its last row is out; plan bound to offsets_all,
+ * list, tiles, landed (this rank's flags), ctl waits (bounded, hb_set_peer_wait_ms) until every rank's number has
+ * arrived. No other kernel of the exchange waits for another GPU. A count that exceeds `cap` rows is reported
  * through the status words (HB_KERNEL at the next hb_sync) and nothing is written past the buffers. */
 int hb_ep_dispatch_get(hb_ctx* ctx, uint32_t h, uint32_t top_k, uint32_t experts, uint32_t world, uint32_t rank, uint32_t cap, hb_kernel** out);
 int hb_ep_plan_get(hb_ctx* ctx, uint32_t experts, uint32_t world, uint32_t rank, uint32_t bm, uint32_t cap, hb_kernel** out);
 int hb_ep_return_get(hb_ctx* ctx, uint32_t h, uint32_t top_k, uint32_t experts, uint32_t world, uint32_t rank, uint32_t cap, hb_kernel** out);
+int hb_ep_combine_get(hb_ctx* ctx, uint32_t h, uint32_t top_k, uint32_t world, hb_kernel** out);
 /* The output mode (BF16 or RESIDUAL: store, src/metal/kernels.rs:217-234) applied to an f32 accumulator array
  * [m][n] that was completed outside a GEMM: a row-parallel projection sums f32 partial products across GPUs
  * (hb_gemm_get with HB_OUT_F32 on each, then an all-reduce) and rounds once afterwards. Bindings: acc, y. */

@@ -46,13 +46,20 @@ def env(hb200):
     ctx.close()
 
 
-def test_one_rank_matches_the_plain_block(env, hb200, oracle):
+@pytest.mark.parametrize("fused", [True, False])
+def test_one_rank_matches_the_plain_block(env, hb200, oracle, fused):
+    # the exchange kernels with a single rank (dispatch into its own receive buffer, plan, return or the fused combine)
     d, ctx = env
     s = SHAPE
     x, scores, wgu, wd = inputs(oracle, **s)
     xt, st_, wgut, wdt = (t16(a).cuda() for a in (x, scores, wgu, wd))
-    st, out = single_gpu_block(hb200, ctx, d, xt, st_, wgut, wdt, **s)
+    st = d.EpPeer(hb200, ctx, 0, 1, s["m"], s["h"], s["mi"], s["E"], s["top_k"], s["bm"], fused=fused, plain_when_alone=False)
+    st.connect([st])
+    out = d.ep_moe_peer(st, xt, st_, wgut, wdt)
     torch.cuda.synchronize()
+    plain, out_plain = single_gpu_block(hb200, ctx, d, xt, st_, wgut, wdt, **s)  # one rank as the library runs it: no exchange
+    torch.cuda.synchronize()
+    assert plain.plain and torch.equal(out_plain, out)
     route = oracle.route_topk(scores, s["top_k"])
     lst, tiles = oracle.moe_sort(route, s["E"], s["top_k"], s["bm"])
     assert np.array_equal(st.route.cpu().numpy().view(np.uint32), route)
@@ -81,8 +88,9 @@ def test_one_rank_matches_the_plain_block(env, hb200, oracle):
     assert c.max_abs_err <= c.max_abs_ref / 64 and c.over_1ulp <= 0.05 * c.count
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_emulated_ranks_equal_one_rank(env, hb200, oracle, world):
+@pytest.mark.parametrize("fused", [True, False])
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_emulated_ranks_equal_one_rank(env, hb200, oracle, world, fused):
     d, ctx = env
     s = SHAPE
     x, scores, wgu, wd = inputs(oracle, **s)
@@ -90,10 +98,10 @@ def test_emulated_ranks_equal_one_rank(env, hb200, oracle, world):
     _, want = single_gpu_block(hb200, ctx, d, xt, st_, wgut, wdt, **s)
     want = want.clone()
     rpr, epr = s["m"] // world, s["E"] // world
-    ranks = [d.EpPeer(hb200, ctx, r, world, rpr, s["h"], s["mi"], s["E"], s["top_k"], s["bm"]) for r in range(world)]
+    ranks = [d.EpPeer(hb200, ctx, r, world, rpr, s["h"], s["mi"], s["E"], s["top_k"], s["bm"], fused=fused) for r in range(world)]
     for st in ranks:
         st.connect(ranks)
-    for rep in range(2):  # twice: the buffers carry the previous call's rows
+    for rep in range(3):  # twice: the buffers carry the previous call's rows
         for r, st in enumerate(ranks):
             st.phase_sort(xt[r * rpr : (r + 1) * rpr].contiguous(), st_[r * rpr : (r + 1) * rpr].contiguous())
         offs_all = torch.stack([st.offs for st in ranks])
@@ -121,7 +129,7 @@ def test_receive_buffer_too_small_is_reported_not_overrun(env, hb200, oracle):
     x, scores, wgu, wd = inputs(oracle, **s)
     xt, st_, wgut, wdt = (t16(a).cuda() for a in (x, scores, wgu, wd))
     pairs = s["m"] * s["top_k"]
-    st = d.EpPeer(hb200, ctx, 0, 1, s["m"], s["h"], s["mi"], s["E"], s["top_k"], s["bm"], cap=pairs - 64)
+    st = d.EpPeer(hb200, ctx, 0, 1, s["m"], s["h"], s["mi"], s["E"], s["top_k"], s["bm"], cap=pairs - 64, plain_when_alone=False)
     st.connect([st])
     guard = torch.full((4096,), 0x5A5A, device="cuda", dtype=torch.int16)  # lives right after nothing in particular: a canary of our own
     d.ep_moe_peer(st, xt, st_, wgut, wdt)
@@ -179,23 +187,24 @@ def _two_process_worker(rank, world, port, repo, result):
         one.connect([one])
         want = d.ep_moe_peer(one, xt, st_, wgut, wdt).clone()
         rpr, epr = s["m"] // world, s["E"] // world
-        st = d.EpPeer(hb, ctx, rank, world, rpr, s["h"], s["mi"], s["E"], s["top_k"], s["bm"])
-        d.ep_peer_connect(st)
         xs, ss = xt[rank * rpr : (rank + 1) * rpr].contiguous(), st_[rank * rpr : (rank + 1) * rpr].contiguous()
         wl, dl = wgut[rank * epr * 2 * s["mi"] : (rank + 1) * epr * 2 * s["mi"]], wdt[rank * epr * s["h"] : (rank + 1) * epr * s["h"]]
-        # the library's barrier kernel launched step by step (0, 1), the step recorded and replayed (2..6: both
-        # parities recorded, then replayed), then the NCCL form of the same steps
-        for it in range(9):
-            out = d.ep_moe_peer(st, xs, ss, wl, dl, nccl_sync=it >= 7, recorded=2 <= it < 7)
-            stream.synchronize()
-            ctx.sync()
-            same = bool(torch.equal(out, want[rank * rpr : (rank + 1) * rpr]))
-            if not same:
-                print(f"rank {rank}: MoE block, step {it}: differs from the one-rank block", file=sys.stderr, flush=True)
-            ok = ok and same
-        ok = ok and len(st.recorded.graphs) == 2
-        dist.barrier()
-        st.close()
+        for fused in (True, False):  # the dispatch's flag and the combine that reads the owners' rows; barrier kernels and a return into EY
+            st = d.EpPeer(hb, ctx, rank, world, rpr, s["h"], s["mi"], s["E"], s["top_k"], s["bm"], fused=fused)
+            d.ep_peer_connect(st)
+            # the library's barrier kernel launched step by step (0, 1), the step recorded and replayed (2..6: both
+            # parities recorded, then replayed), then the NCCL form of the same steps
+            for it in range(9):
+                out = d.ep_moe_peer(st, xs, ss, wl, dl, nccl_sync=it >= 7, recorded=2 <= it < 7)
+                stream.synchronize()
+                ctx.sync()
+                same = bool(torch.equal(out, want[rank * rpr : (rank + 1) * rpr]))
+                if not same:
+                    print(f"rank {rank}: MoE block (fused={fused}), step {it}: differs from the one-rank block", file=sys.stderr, flush=True)
+                ok = ok and same
+            ok = ok and len(st.recorded.graphs) == 2
+            dist.barrier()
+            st.close()
         # the tensor-parallel FFN: both ranks end with the same Y, equal to the all-reduce form
         m, h, inter = 200, 256, 512
         x2, wgu2, wd2, y0 = o.normal((m, h), 1, 1, 1.0), o.normal((2 * inter, h), 2, 2, h**-0.5), o.normal((h, inter), 3, 3, inter**-0.5), o.normal((m, h), 4, 4, 1.0)
