@@ -447,7 +447,8 @@ def summaries(extra: dict, pk: dict) -> dict:
         out["short_blocks"] = {k_: {"us": v["us"], "tflops": v["tflops"], "frac_bf16_peak": v["frac_bf16_peak"], "frac_hbm_weights": v["frac_hbm_weights"]} for k_, v in small.items()}
     dec = extra.get("decode_layer_9b")
     if dec:
-        out["decode_layer_9b"] = {k_: {"us_per_layer": v["us_per_layer"], "frac_hbm": v["frac_hbm"], "kernels_per_layer": v["kernels_per_layer"]} for k_, v in dec.items()}
+        out["decode_layer_9b"] = {k_: {"us_per_layer": v["us_per_layer"], "frac_hbm": v["frac_hbm"], "kernels_per_layer": v["kernels_per_layer"], "dec.fnorm": v.get("dec.fnorm"), "dec.fswi": v.get("dec.fswi"),
+                                        "variants_us": {n_: min(t_.values()) for n_, t_ in (v.get("variants_us") or {}).items()}} for k_, v in dec.items()}
     moe = extra.get("moe_2048tok_256e_top8")
     if moe:
         out["moe_block"] = {"us": moe["us"], "weight_gbs": moe["weight_gbs"], "frac_hbm": moe["frac_hbm"], "kernels": len(moe["us_per_kernel"])}
@@ -691,28 +692,51 @@ def bench_extra(hb, ctx, sel, torch, dev, wrap, pk, rank, world, barrier, max_ov
     out["lm_head_argmax_m1"] = lm
     del w2, y2
     # -- the matrix products of one 9B-class layer at decode time (1, 4 and 8 rows), with the norms before them, as one
-    # recorded sequence over four layers' worth of weights (1.5 GB: every byte streams from HBM)
+    # recorded sequence over four layers' worth of weights (1.5 GB: every byte streams from HBM). The forms are chosen
+    # as the engine chooses them at load: every projection's form by hb_select_matvec(_x), then the step's axes
+    # (the norms apart or inside the projections: dec.fnorm; the SwiGLU in gate/up's epilogue or in down's input:
+    # dec.fswi) on the whole chain by hb_select_axis.
     try:
+        import struct
+
         layers = 4
+        eps_bits = struct.unpack("<I", struct.pack("<f", 1e-6))[0]
         wl = [[(torch.randn(nn, kk, device=dev, generator=g) * kk**-0.5).bfloat16() for _, kk, nn, _ in LAYER] for _ in range(layers)]
         nw = (torch.randn(HIDDEN, device=dev, generator=g) * 0.1).bfloat16()
         dec = {}
         for m in (1, 4, 8):
             xd = torch.randn(m, HIDDEN, device=dev, generator=g).bfloat16()
+            attn = torch.randn(m, HIDDEN, device=dev, generator=g).bfloat16()  # stands for the attention's output, the o projection's input
             xn = torch.zeros_like(xd)
             qkvd = torch.zeros(m, 6144, device=dev, dtype=torch.bfloat16)
             hd = torch.zeros(m, INTER, device=dev, dtype=torch.bfloat16)
+            gud = torch.zeros(m, 2 * INTER, device=dev, dtype=torch.bfloat16)
             copies = lambda i: [wrap(wl[l][i]) for l in range(layers)]
             k_q = sel.matvec(HIDDEN, 6144, 0, m, copies(0), wrap(xn), wrap(qkvd))
-            k_o = sel.matvec(HIDDEN, HIDDEN, 2, m, copies(1), wrap(xn), wrap(xd))
+            k_o = sel.matvec(HIDDEN, HIDDEN, 2, m, copies(1), wrap(attn), wrap(xd))
             k_g = sel.matvec(HIDDEN, 2 * INTER, 3, m, copies(2), wrap(xn), wrap(hd))
             k_d = sel.matvec(INTER, HIDDEN, 2, m, copies(3), wrap(hd), wrap(xd))
             k_n = ctx.rmsnorm(HIDDEN, 1e-6, True)
-            def chain(kq, ko, kg, kd):
+            k_qf = sel.matvec_x(HIDDEN, 6144, 0, m, hb.X_NORM, eps_bits, 1, copies(0), wrap(xd), wrap(qkvd), wrap(nw))
+            k_gf = sel.matvec_x(HIDDEN, 2 * INTER, 3, m, hb.X_NORM, eps_bits, 1, copies(2), wrap(xd), wrap(hd), wrap(nw))
+
+            def chain_ops(fnorm, fswi=0, kq=None, ko=None, kg=None, kd=None):
                 ops_c = []
                 for l in range(layers):
-                    ops_c += [(k_n, m, wrap(xd), wrap(nw), wrap(xn)), (kq, m, wrap(wl[l][0]), wrap(xn), wrap(qkvd)), (ko, m, wrap(wl[l][1]), wrap(xn), wrap(xd)),
-                              (k_n, m, wrap(xd), wrap(nw), wrap(xn)), (kg, m, wrap(wl[l][2]), wrap(xn), wrap(hd)), (kd, m, wrap(wl[l][3]), wrap(hd), wrap(xd))]
+                    if fnorm:
+                        ops_c += [(kq or k_qf, m, wrap(wl[l][0]), wrap(xd), wrap(qkvd), wrap(nw)), (ko or k_o, m, wrap(wl[l][1]), wrap(attn), wrap(xd))]
+                    else:
+                        ops_c += [(k_n, m, wrap(xd), wrap(nw), wrap(xn)), (kq or k_q, m, wrap(wl[l][0]), wrap(xn), wrap(qkvd)), (ko or k_o, m, wrap(wl[l][1]), wrap(attn), wrap(xd))]
+                    if fswi:  # gate/up writes [gate | up], down makes the SwiGLU where it loads its input
+                        gsrc = [(k_gpf, m, wrap(wl[l][2]), wrap(xd), wrap(gud), wrap(nw))] if fnorm else [(k_n, m, wrap(xd), wrap(nw), wrap(xn)), (k_gp, m, wrap(wl[l][2]), wrap(xn), wrap(gud))]
+                        ops_c += gsrc + [(k_ds, m, wrap(wl[l][3]), wrap(gud), wrap(xd))]
+                    elif fnorm:
+                        ops_c += [(kg or k_gf, m, wrap(wl[l][2]), wrap(xd), wrap(hd), wrap(nw)), (kd or k_d, m, wrap(wl[l][3]), wrap(hd), wrap(xd))]
+                    else:
+                        ops_c += [(k_n, m, wrap(xd), wrap(nw), wrap(xn)), (kg or k_g, m, wrap(wl[l][2]), wrap(xn), wrap(hd)), (kd or k_d, m, wrap(wl[l][3]), wrap(hd), wrap(xd))]
+                return ops_c
+
+            def replay(ops_c):
                 res = {}
                 for mode in ("plain", "overlapped"):  # overlapped: each kernel is launched ahead of its predecessor's end and waits inside
                     ctx.set_launch_overlap(mode == "overlapped")
@@ -724,20 +748,39 @@ def bench_extra(hb, ctx, sel, torch, dev, wrap, pk, rank, world, barrier, max_ov
                 ctx.set_launch_overlap(False)
                 return res
 
-            # the forms the selection picked shape by shape (each timed alone), and for several rows the chain of
-            # evenly dealt tensor-core streams, whose start-up hides under the kernel before them once launches overlap
-            secs = chain(k_q, k_o, k_g, k_d)
-            forms = [k_q.name, k_o.name, k_g.name, k_d.name]
+            ctx.set_launch_overlap(True)  # the axes are timed as the step will run
+            fnorm = sel.axis("fnorm", "dec.fnorm", [chain_ops(0), chain_ops(1)], [0, 1], position=0)
+            fswi, k_gp = 0, None
+            try:  # the SwiGLU made by the down projection: a CUDA-core form, its rows must fit in shared memory
+                k_ds = sel.matvec_x(INTER, HIDDEN, 2, m, hb.X_SWIGLU, 0, 0, copies(3), wrap(gud), wrap(xd))
+                k_gp = sel.matvec(HIDDEN, 2 * INTER, 0, m, copies(2), wrap(xn), wrap(gud))
+                k_gpf = sel.matvec_x(HIDDEN, 2 * INTER, 0, m, hb.X_NORM, eps_bits, 1, copies(2), wrap(xd), wrap(gud), wrap(nw))
+                fswi = sel.axis("fswi", "dec.fswi", [chain_ops(fnorm, 0), chain_ops(fnorm, 1)], [0, 1], position=0)
+            except hb.HbError:
+                pass
+            ctx.set_launch_overlap(False)
+            variants = {"norms apart": replay(chain_ops(0)), "norms inside the projections": replay(chain_ops(1))}
+            if k_gp is not None:
+                variants["SwiGLU inside down"] = replay(chain_ops(fnorm, 1))
+            picked_ops = chain_ops(fnorm, fswi)
+            secs = replay(picked_ops)
+            forms = sorted({o[0].name for o in picked_ops})
+            # for several rows also the chain of evenly dealt tensor-core streams, whose start-up hides under the kernel
+            # before them once launches overlap (each projection's pick above was timed alone)
             alt = None
             if m > 1:
                 ka = [ctx.matvec(kk, nn, oo, rows_max=m, tensor_core=2, split=2) for _, kk, nn, oo in LAYER]
-                alt = chain(*ka)
+                kaf = [ctx.matvec(kk, nn, oo, rows_max=m, tensor_core=2, split=2, x_src=hb.X_NORM, norm_eps_bits=eps_bits, norm_plus_one=1) for _, kk, nn, oo in (LAYER[0], LAYER[2])]
+                alt_ops = chain_ops(fnorm, 0, kaf[0] if fnorm else ka[0], ka[1], kaf[1] if fnorm else ka[2], ka[3])
+                alt = replay(alt_ops)
                 if min(alt.values()) < min(secs.values()):
-                    forms = [k.name for k in ka]
+                    forms = sorted({o[0].name for o in alt_ops})
+                    picked_ops = alt_ops
             sec_d = min(list(secs.values()) + (list(alt.values()) if alt else []))
             wb = sum(2.0 * nn * kk for _, kk, nn, _ in LAYER)
-            dec[f"m{m}"] = {"us_per_layer": sec_d * 1e6, "weight_gbs": wb / sec_d / 1e9, "frac_hbm": wb / sec_d / 1e9 / pk["hbm_gbs"], "kernels_per_layer": 6,
-                            "selected_forms_us": {k_: v * 1e6 for k_, v in secs.items()},
+            dec[f"m{m}"] = {"us_per_layer": sec_d * 1e6, "weight_gbs": wb / sec_d / 1e9, "frac_hbm": wb / sec_d / 1e9 / pk["hbm_gbs"], "kernels_per_layer": len(picked_ops) // layers,
+                            "dec.fnorm": fnorm, "dec.fswi": fswi, "selected_forms_us": {k_: v * 1e6 for k_, v in secs.items()},
+                            "variants_us": {k_: {kk_: vv * 1e6 for kk_, vv in v.items()} for k_, v in variants.items()},
                             "balanced_stream_forms_us": {k_: v * 1e6 for k_, v in alt.items()} if alt else None, "forms": forms}
         out["decode_layer_9b"] = dec
         del wl

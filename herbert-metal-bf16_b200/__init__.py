@@ -22,6 +22,7 @@ LIB_PATH = os.path.join(_HERE, "lib", "libhb200.so")
 OK, INVALID, UNSUPPORTED, BACKEND, OOM, KERNEL = range(6)
 OUT_BF16, OUT_F32, OUT_RESIDUAL, OUT_SWIGLU = range(4)
 ROWS_DENSE, ROWS_GATHER, ROWS_SCATTER, ROWS_SORTED = range(4)
+X_PLAIN, X_NORM, X_SWIGLU = range(3)
 OUT_NAMES = {OUT_BF16: "Bf16", OUT_F32: "F32", OUT_RESIDUAL: "Residual", OUT_SWIGLU: "Swiglu"}
 
 
@@ -45,7 +46,7 @@ class GemmDesc(C.Structure):
 
 
 class MatvecDesc(C.Structure):
-    _fields_ = [(n, C.c_uint32) for n in ("k", "n", "out", "rows_max", "rows_per_warp", "split", "persist", "x_stationary", "tensor_core", "argmax")]
+    _fields_ = [(n, C.c_uint32) for n in ("k", "n", "out", "rows_max", "rows_per_warp", "split", "persist", "x_stationary", "tensor_core", "argmax", "x_src", "norm_eps_bits", "norm_plus_one")]
 
 
 class ExpertIo(C.Structure):
@@ -153,6 +154,8 @@ def lib() -> C.CDLL:
         "hb_select_gemm": (ci, [vp, u32, u32, u32, Range, Range, Range, u32, pvp]),
         "hb_select_gate_up": (ci, [vp, u32, u32, Range, Range, Range, Range, u32, pvp, C.POINTER(ci)]),
         "hb_select_matvec": (ci, [vp, u32, u32, u32, u32, C.POINTER(Range), ci, Range, Range, pvp]),
+        "hb_select_matvec_x": (ci, [vp, u32, u32, u32, u32, u32, u32, u32, C.POINTER(Range), ci, Range, Range, Range, pvp]),
+        "hb_select_axis": (ci, [vp, C.c_char_p, C.c_char_p, C.POINTER(C.POINTER(Op)), C.POINTER(ci), C.POINTER(u32), ci, u32, C.POINTER(u32)]),
         "hb_select_experts": (ci, [vp, C.POINTER(ExpertIo), C.POINTER(ExpertPick)]),
         "hb_selector_inject_wrong": (ci, [vp, ci]),
         "hb_check_rule": (ci, [vp, vp, sz, ci, C.POINTER(ci), C.POINTER(C.c_float), C.POINTER(C.c_float)]),
@@ -173,7 +176,7 @@ EXPORTS = [
     "hb_moe_sort_get", "hb_moe_tiles", "hb_moe_gather_get", "hb_moe_combine_get", "hb_epilogue_get", "hb_gemm_static_scratch", "hb_kernel_name", "hb_launch", "hb_run", "hb_time", "hb_set_launch_overlap", "hb_graph_record", "hb_graph_launch", "hb_graph_time", "hb_graph_free",
     "hb_tune_new", "hb_tune_free", "hb_tune_apply", "hb_tune_get", "hb_tune_summary", "hb_tune_gemm_timed", "hb_selector_new",
     "hb_selector_free", "hb_selector_log", "hb_selector_buckets", "hb_fill_random16", "hb_select_gemm", "hb_select_gate_up",
-    "hb_select_matvec", "hb_select_experts", "hb_selector_inject_wrong", "hb_check_rule",
+    "hb_select_matvec", "hb_select_matvec_x", "hb_select_axis", "hb_select_experts", "hb_selector_inject_wrong", "hb_check_rule",
 ]
 
 
@@ -437,8 +440,9 @@ class Context:
         d = GemmDesc(k, n, out, rows_mode, top_k, experts, bm, tile_n, stages, cta_pair, m_first, rows_max, stream_k, merge_runs, y_shards, y_group_rows, y_signal)
         return self._get(lib().hb_gemm_get, C.byref(d))
 
-    def matvec(self, k, n, out=OUT_BF16, rows_max=1, rows_per_warp=2, split=1, persist=0, x_stationary=0, tensor_core=0, argmax=0) -> Kernel:
-        d = MatvecDesc(k, n, out, rows_max, rows_per_warp, split, persist, x_stationary, tensor_core, argmax)
+    def matvec(self, k, n, out=OUT_BF16, rows_max=1, rows_per_warp=2, split=1, persist=0, x_stationary=0, tensor_core=0, argmax=0, x_src=X_PLAIN, norm_eps_bits=0,
+               norm_plus_one=0) -> Kernel:
+        d = MatvecDesc(k, n, out, rows_max, rows_per_warp, split, persist, x_stationary, tensor_core, argmax, x_src, norm_eps_bits, norm_plus_one)
         return self._get(lib().hb_matvec_get, C.byref(d))
 
     def swiglu_rows(self, n) -> Kernel:
@@ -597,6 +601,26 @@ class Selector:
         p = C.c_void_p()
         self.ctx._check(lib().hb_select_matvec(self.h, k, n, out, rows, arr, len(w_copies), _as_range(x), _as_range(y), C.byref(p)))
         return Kernel(self.ctx, p.value)
+
+    def matvec_x(self, k, n, out, rows, x_src, norm_eps_bits, norm_plus_one, w_copies, x, y, norm_w=None) -> Kernel:
+        """The form of a projection whose input is made inside the kernel (x_src X_NORM: x is the residual stream and
+        norm_w the norm's weights; X_SWIGLU: x holds rows of [gate | up])."""
+        arr = (Range * len(w_copies))(*[_as_range(w) for w in w_copies])
+        p = C.c_void_p()
+        nw = _as_range(norm_w) if norm_w is not None else Range(None, 0)
+        self.ctx._check(lib().hb_select_matvec_x(self.h, k, n, out, rows, x_src, norm_eps_bits, norm_plus_one, arr, len(w_copies), _as_range(x), _as_range(y), nw, C.byref(p)))
+        return Kernel(self.ctx, p.value)
+
+    def axis(self, axis: str, key: str, variants, values, position: int = 0) -> int:
+        """One axis of the decode step's load-time timing: `variants` are op lists [(kernel, m, bufs...), ...], one per
+        value (None: that form is unavailable); returns the value to use."""
+        made = [self.ctx.make_ops(v) if v else None for v in variants]
+        arrs = (C.POINTER(Op) * len(variants))(*[C.cast(m_[0], C.POINTER(Op)) if m_ else None for m_ in made])
+        nops = (C.c_int * len(variants))(*[len(v) if v else 0 for v in variants])
+        vals = (C.c_uint32 * len(values))(*values)
+        best = C.c_uint32()
+        self.ctx._check(lib().hb_select_axis(self.h, axis.encode(), key.encode(), arrs, nops, vals, len(variants), position, C.byref(best)))
+        return best.value
 
     def experts(self, experts, top_k, h, mi, m, route, lst, tiles, x, wgu, wdown, ehb, ey, egu=None, xs=None):
         """Returns dict(bm, sort, gather, gate_up, swiglu, down); gather and swiglu may be None."""

@@ -19,6 +19,7 @@
 #include <vector>
 
 #include "hb_internal.hpp"
+#include "rowwise.cuh"
 #include "tc05.cuh"
 
 namespace hb {
@@ -45,6 +46,12 @@ struct SkinnyParams {
     uint32_t* status;
     const uint32_t* seg_start;   // [grid + 1]: where each CTA's segments begin in `segs` (worked out on the host once)
     const SkinnySeg* segs;
+    // NORM: the input rows are the RMSNorm of x_raw [m][k], made by every CTA into xn (which the X descriptor covers)
+    const uint16_t* x_raw;
+    const uint16_t* norm_w;
+    uint16_t* xn;
+    uint32_t k, plus_one;
+    float eps;
 };
 
 __host__ __device__ __forceinline__ uint32_t skinny_cta_of(uint64_t u, uint64_t units, uint32_t grid) {
@@ -118,7 +125,11 @@ __device__ __forceinline__ void skinny_store(const SkinnyParams& p, uint32_t j, 
     }
 }
 
-template <int OUT, int NP, int KPS>
+// NORM (the reference's XSrc::Norm, src/metal/kernels.rs:236-252, 355-442): x is the residual stream. Every CTA makes
+// the normalised rows itself (rmsnorm_rows' sums in their order, so the same bits as the separate kernel) and writes
+// them to one scratch array the X descriptor covers; all CTAs write the same values, and a CTA's TMA reads follow its
+// own writes. The first weight boxes are in flight before that starts.
+template <int OUT, int NP, int KPS, bool NORM = false>
 __global__ void __launch_bounds__(SK_THREADS, 1)
 gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x, const SkinnyParams p) {
     constexpr int NACC = OUT == HB_OUT_SWIGLU ? 2 : 1;
@@ -167,50 +178,66 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     auto seg_at = [&](uint32_t i, SkinnySeg* out) { *out = i < (uint32_t)SK_SEG_CACHE ? segs_s[i] : p.segs[seg0 + i]; };
     griddep_launch_dependents();
 
-    if (warp == 0) {
-        if (lane == 0) {
-            tma_prefetch_desc(&tm_w);
-            tma_prefetch_desc(&tm_x);
-            // The stage fills of this CTA, in order. The first S of them find their stage free; their weight boxes do
-            // not depend on the kernel before this one on the stream, so they are issued first (pass 0), then the
-            // predecessor is waited for, then their activation boxes follow (pass 1) and the rest of the fills (pass 2).
-            auto walk = [&](int pass) -> bool {
-                uint32_t s = 0, ph = 0, fill = 0;
-                for (uint32_t i = 0; i < n_segs; ++i) {
-                    SkinnySeg sg;
-                    seg_at(i, &sg);
-                    const uint32_t fb = sg.fb, kb0 = sg.kb0, kb1 = sg.kb1;
-                    const int row_w0 = (int)(fb * 128);
-                    const int row_w1 = (int)(p.n_out + fb * 128);  // SWIGLU: the up rows of the same features
-                    for (uint32_t kb = kb0; kb < kb1; kb += KPS, ++fill) {
-                        const bool early = fill < S;
-                        if (pass != 2 && !early) return true;
-                        const bool do_w = pass == 0 || (pass == 2 && !early), do_x = pass == 1 || (pass == 2 && !early);
-                        if (pass == 2 && !early && !mbar_wait(smem_u32(&bars.empty[s]), ph ^ 1u)) {
-                            report(p.status, ST_WAIT_TIMEOUT, WHERE_EMPTY, s);
-                            return false;
-                        }
-                        const uint32_t full = smem_u32(&bars.full[s]);
-                        const uint32_t nkb = min((uint32_t)KPS, kb1 - kb);
-                        if (do_w) mbar_arrive_expect_tx(full, nkb * KB_BYTES);
+    // The stage fills of this CTA, in order. The first S of them find their stage free; their weight boxes do
+    // not depend on the kernel before this one on the stream, so they are issued first (pass 0), then the
+    // predecessor is waited for, then their activation boxes follow (pass 1) and the rest of the fills (pass 2).
+    auto walk = [&](int pass) -> bool {
+        uint32_t s = 0, ph = 0, fill = 0;
+        for (uint32_t i = 0; i < n_segs; ++i) {
+            SkinnySeg sg;
+            seg_at(i, &sg);
+            const uint32_t fb = sg.fb, kb0 = sg.kb0, kb1 = sg.kb1;
+            const int row_w0 = (int)(fb * 128);
+            const int row_w1 = (int)(p.n_out + fb * 128);  // SWIGLU: the up rows of the same features
+            for (uint32_t kb = kb0; kb < kb1; kb += KPS, ++fill) {
+                const bool early = fill < S;
+                if (pass != 2 && !early) return true;
+                const bool do_w = pass == 0 || (pass == 2 && !early), do_x = pass == 1 || (pass == 2 && !early);
+                if (pass == 2 && !early && !mbar_wait(smem_u32(&bars.empty[s]), ph ^ 1u)) {
+                    report(p.status, ST_WAIT_TIMEOUT, WHERE_EMPTY, s);
+                    return false;
+                }
+                const uint32_t full = smem_u32(&bars.full[s]);
+                const uint32_t nkb = min((uint32_t)KPS, kb1 - kb);
+                if (do_w) mbar_arrive_expect_tx(full, nkb * KB_BYTES);
 #pragma unroll
-                        for (uint32_t j = 0; j < (uint32_t)KPS; ++j) {
-                            if (j < nkb) {
-                                const uint32_t dst = smem_base + s * STAGE_BYTES + j * KB_BYTES;
-                                if (do_w) {
-                                    tma_load_2d(dst, &tm_w, full, (int)((kb + j) * 64), row_w0);
-                                    if (NACC == 2) tma_load_2d(dst + SK_A_BYTES, &tm_w, full, (int)((kb + j) * 64), row_w1);
-                                }
-                                if (do_x) tma_load_2d(dst + A_STAGE, &tm_x, full, (int)((kb + j) * 64), 0);
-                            }
+                for (uint32_t j = 0; j < (uint32_t)KPS; ++j) {
+                    if (j < nkb) {
+                        const uint32_t dst = smem_base + s * STAGE_BYTES + j * KB_BYTES;
+                        if (do_w) {
+                            tma_load_2d(dst, &tm_w, full, (int)((kb + j) * 64), row_w0);
+                            if (NACC == 2) tma_load_2d(dst + SK_A_BYTES, &tm_w, full, (int)((kb + j) * 64), row_w1);
                         }
-                        if (++s == S) { s = 0; ph ^= 1u; }
+                        if (do_x) tma_load_2d(dst + A_STAGE, &tm_x, full, (int)((kb + j) * 64), 0);
                     }
                 }
-                return true;
-            };
+                if (++s == S) { s = 0; ph ^= 1u; }
+            }
+        }
+        return true;
+    };
+    if constexpr (NORM) {
+        if (warp == 0 && lane == 0) {
+            tma_prefetch_desc(&tm_w);
+            tma_prefetch_desc(&tm_x);
             walk(0);
-            griddep_wait();
+        }
+        griddep_wait();
+        __shared__ float npart[NP * 9];
+        norm_rows_into<NP>(p.x_raw, p.k, p.norm_w, p.m, p.k, p.eps, p.plus_one != 0, p.xn, npart);
+        // written through the generic proxy, read by TMA
+        __threadfence();
+        asm volatile("fence.proxy.async;" ::: "memory");
+        __syncthreads();
+    }
+    if (warp == 0) {
+        if (lane == 0) {
+            if constexpr (!NORM) {
+                tma_prefetch_desc(&tm_w);
+                tma_prefetch_desc(&tm_x);
+                walk(0);
+                griddep_wait();
+            }
             walk(1);
             walk(2);
         }
@@ -362,13 +389,13 @@ namespace {
 
 typedef void (*skinny_fn)(const CUtensorMap, const CUtensorMap, const SkinnyParams);
 
-template <int NP, int KPS>
+template <int NP, int KPS, bool NORM = false>
 skinny_fn skinny_pick_out(uint32_t out) {
     switch (out) {
-        case HB_OUT_BF16: return gemm_skinny_kernel<HB_OUT_BF16, NP, KPS>;
-        case HB_OUT_F32: return gemm_skinny_kernel<HB_OUT_F32, NP, KPS>;
-        case HB_OUT_RESIDUAL: return gemm_skinny_kernel<HB_OUT_RESIDUAL, NP, KPS>;
-        case HB_OUT_SWIGLU: return gemm_skinny_kernel<HB_OUT_SWIGLU, NP, KPS>;
+        case HB_OUT_BF16: return gemm_skinny_kernel<HB_OUT_BF16, NP, KPS, NORM>;
+        case HB_OUT_F32: return gemm_skinny_kernel<HB_OUT_F32, NP, KPS, NORM>;
+        case HB_OUT_RESIDUAL: return gemm_skinny_kernel<HB_OUT_RESIDUAL, NP, KPS, NORM>;
+        case HB_OUT_SWIGLU: return gemm_skinny_kernel<HB_OUT_SWIGLU, NP, KPS, NORM>;
     }
     return nullptr;
 }
@@ -376,6 +403,10 @@ skinny_fn skinny_pick_out(uint32_t out) {
 template <int NP>
 skinny_fn skinny_pick_kps(uint32_t out, uint32_t kps) {
     return kps == 1 ? skinny_pick_out<NP, 1>(out) : kps == 2 ? skinny_pick_out<NP, 2>(out) : skinny_pick_out<NP, 4>(out);
+}
+// the fused norm: at most 16 activation rows
+skinny_fn skinny_pick_norm(uint32_t out, uint32_t kps) {
+    return kps == 1 ? skinny_pick_out<16, 1, true>(out) : kps == 2 ? skinny_pick_out<16, 2, true>(out) : skinny_pick_out<16, 4, true>(out);
 }
 
 struct SkinnyGemm : hb_kernel {
@@ -386,13 +417,19 @@ struct SkinnyGemm : hb_kernel {
     uint32_t* counters = nullptr;
     uint32_t* seg_start = nullptr;
     SkinnySeg* segs = nullptr;
+    bool norm = false;         // x is the residual stream: the rows are normalised inside the kernel
+    uint16_t* xn = nullptr;    // norm: [np][k], what the X descriptor covers
+    float eps = 0.f;
+    uint32_t plus_one = 0;
     const void* last_w = nullptr;
     const void* last_x = nullptr;
     uint32_t last_m = 0;
     CUtensorMap tm_w{}, tm_x{};
 
     int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
-        if (na != 3) return fail(ctx, HB_INVALID, name + ": bindings are W, x, y");
+        if (na != (norm ? 4 : 3)) return fail(ctx, HB_INVALID, name + (norm ? ": bindings are W, x, y, norm_w" : ": bindings are W, x, y"));
+        if (norm && (!range_ok(a[3], (size_t)k * 2) || ((reinterpret_cast<uintptr_t>(a[3].ptr) | reinterpret_cast<uintptr_t>(a[1].ptr)) & 15u)))
+            return fail(ctx, HB_INVALID, name + ": norm_w is too small, or x or norm_w is not 16-byte aligned");
         if (m == 0 || m > rows_max) return fail(ctx, HB_INVALID, name + ": m = " + std::to_string(m) + " outside 1.." + std::to_string(rows_max));
         const uint32_t n_out = out == HB_OUT_SWIGLU ? n / 2 : n;
         if (!range_ok(a[0], (size_t)n * k * 2) || !range_ok(a[1], (size_t)m * k * 2) || !range_ok(a[2], (size_t)m * n_out * (out == HB_OUT_F32 ? 4 : 2)))
@@ -400,7 +437,7 @@ struct SkinnyGemm : hb_kernel {
         if (a[0].ptr != last_w || a[1].ptr != last_x || m != last_m) {
             int r = make_tmap_bf16(ctx, &tm_w, a[0].ptr, n, k, 128);
             if (r != HB_OK) return r;
-            if ((r = make_tmap_bf16(ctx, &tm_x, a[1].ptr, m, k, np)) != HB_OK) return r;
+            if ((r = make_tmap_bf16(ctx, &tm_x, norm ? static_cast<const void*>(xn) : a[1].ptr, m, k, np)) != HB_OK) return r;
             last_w = a[0].ptr;
             last_x = a[1].ptr;
             last_m = m;
@@ -419,6 +456,14 @@ struct SkinnyGemm : hb_kernel {
         p.seg_start = seg_start;
         p.segs = segs;
         p.status = ctx->status_dev;
+        if (norm) {
+            p.x_raw = static_cast<const uint16_t*>(a[1].ptr);
+            p.norm_w = static_cast<const uint16_t*>(a[3].ptr);
+            p.xn = xn;
+            p.k = k;
+            p.eps = eps;
+            p.plus_one = plus_one;
+        }
         const uint32_t grid = balanced ? grid_balanced : std::min<uint32_t>(p.feat_blocks, (uint32_t)ctx->sm_count);
         HB_CUDA(ctx, launch_kernel(ctx, true, fn, dim3(grid), dim3(SK_THREADS), smem, tm_w, tm_x, p));
         ctx->launches++;
@@ -441,7 +486,11 @@ int make_matvec_skinny(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out) {
     const uint32_t k_blocks = (d->k + 63) / 64;
     const uint32_t np = d->rows_max <= 16 ? 16 : d->rows_max <= 32 ? 32 : 64;
     const uint32_t kps = d->split == 2 ? 2u : d->split == 4 ? 4u : 1u;  // k-blocks per pipeline stage
-    skinny_fn fn = np == 16 ? skinny_pick_kps<16>(d->out, kps) : np == 32 ? skinny_pick_kps<32>(d->out, kps) : skinny_pick_kps<64>(d->out, kps);
+    if (d->x_src == HB_X_SWIGLU) return fail(ctx, HB_UNSUPPORTED, "matvec (tensor core): the SwiGLU of [gate | up] as input is built for the CUDA-core form");
+    const bool norm = d->x_src == HB_X_NORM;
+    if (norm && np != 16) return fail(ctx, HB_UNSUPPORTED, "matvec (tensor core): the fused norm is built for at most 16 activation rows");
+    skinny_fn fn = norm ? skinny_pick_norm(d->out, kps)
+                        : np == 16 ? skinny_pick_kps<16>(d->out, kps) : np == 32 ? skinny_pick_kps<32>(d->out, kps) : skinny_pick_kps<64>(d->out, kps);
     const uint32_t nacc = d->out == HB_OUT_SWIGLU ? 2 : 1;
     const size_t stage_bytes = ((size_t)nacc * SK_A_BYTES + np * 128) * kps;
     const size_t budget = std::min<size_t>(ctx->smem_optin, 227 * 1024) - 3072;  // alignment slack, barriers, the segment table
@@ -462,13 +511,25 @@ int make_matvec_skinny(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out) {
     k->fn = fn;
     k->smem = stages * stage_bytes + 1024;
     k->kind = 2;
-    k->nargs = 3;
-    char nm[160];
-    snprintf(nm, sizeof nm, "matvec_tc_%ux%u_%s_m%u_%s_s%ux%u", d->k, d->n, out_tag(d->out), np, balanced ? "bal" : "blk", stages, kps);
+    k->nargs = norm ? 4 : 3;
+    k->norm = norm;
+    char nm[200], xtag[48] = "";
+    if (norm) {
+        memcpy(&k->eps, &d->norm_eps_bits, 4);
+        k->plus_one = d->norm_plus_one;
+        snprintf(xtag, sizeof xtag, "_nrm%08x%s", d->norm_eps_bits, d->norm_plus_one ? "p1" : "");
+    }
+    snprintf(nm, sizeof nm, "matvec_tc_%ux%u_%s_m%u_%s_s%ux%u%s", d->k, d->n, out_tag(d->out), np, balanced ? "bal" : "blk", stages, kps, xtag);
     k->name = nm;
     if (hb_kernel* have = find(ctx, k->name)) {
         *out = have;
         return HB_OK;
+    }
+    if (norm) {
+        void* xs = nullptr;
+        int r = hb_alloc(ctx, (size_t)np * d->k * 2, &xs);
+        if (r != HB_OK) return r;
+        k->xn = static_cast<uint16_t*>(xs);
     }
     if (balanced) {
         const uint32_t n_out = d->out == HB_OUT_SWIGLU ? d->n / 2 : d->n;
@@ -484,6 +545,7 @@ int make_matvec_skinny(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out) {
         int r = hb_alloc(ctx, feat_blocks * k->maxslots * nacc * np * 128 * sizeof(float), &sc);
         if (r != HB_OK) return r;
         if ((r = hb_alloc(ctx, feat_blocks * 4 * sizeof(uint32_t), &cn)) != HB_OK) return r;
+        zero_on_failure(ctx, cn, feat_blocks * 4 * sizeof(uint32_t));  // arrival counters: the last arriver resets them
         k->scratch = static_cast<float*>(sc);
         k->counters = static_cast<uint32_t*>(cn);
     }

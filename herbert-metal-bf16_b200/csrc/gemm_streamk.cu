@@ -22,6 +22,7 @@
 // owner), which puts it back to 0: every launch finds the flags clear, nothing on the host counts launches, and a
 // recorded launch can be replayed. (After a wait that ran out the host clears them: see check_status.)
 #include <algorithm>
+#include <mutex>
 #include <cstring>
 
 #include "gemm_common.cuh"
@@ -465,6 +466,10 @@ int make_gemm_streamk(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
     const uint32_t max_stages = (uint32_t)std::min<size_t>(budget / stage_bytes, MAX_STAGES);
     const uint32_t stages = d->stages ? d->stages : max_stages;
     if (stages < 2 || stages > max_stages) return fail(ctx, HB_UNSUPPORTED, "gemm: stage count does not fit");
+    // the epilogue of an owned piece lands a contributor's whole f32 partial tile (BM x bn) in the pipeline's shared memory
+    if ((size_t)stages * stage_bytes < (size_t)BM * bn * sizeof(float))
+        return fail(ctx, HB_UNSUPPORTED, "gemm: the stream-K form needs a pipeline at least as large as one f32 partial tile (" + std::to_string(BM) + " x " +
+                                             std::to_string(bn) + "): more stages or a narrower tile");
     auto k = std::make_unique<StreamKGemm>();
     k->d = *d;
     k->d.tile_n = bn;
@@ -490,6 +495,7 @@ int make_gemm_streamk(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
         int r = hb_alloc(ctx, (size_t)ctx->sm_count * BM * 256 * sizeof(float), &s);
         if (r != HB_OK) return r;
         if ((r = hb_alloc(ctx, (size_t)ctx->sm_count * 4 * sizeof(uint32_t), &f)) != HB_OK) return r;
+        zero_on_failure(ctx, f, (size_t)ctx->sm_count * 4 * sizeof(uint32_t));  // flags of partial tiles: their reader clears them
         ctx->sk_scratch = static_cast<float*>(s);
         ctx->sk_flags = static_cast<uint32_t*>(f);
     }
@@ -516,6 +522,8 @@ static __device__ __align__(256) float g_static_partials[hb::STATIC_SLOTS * hb::
 static __device__ __align__(256) uint32_t g_static_flags[hb::STATIC_SLOTS * 4];
 
 namespace {
+static_assert((size_t)2 * (hb::A_BYTES + (size_t)hb::STATIC_BN * hb::BK * 2) >= (size_t)hb::BM * hb::STATIC_BN * sizeof(float),
+              "the static form's pipeline holds one f32 partial tile at any stage count");
 constexpr int MAX_DEVICES = 64;
 // Per device: the device addresses of the arrays (their names are host-side stand-ins, not addresses a kernel
 // could use) and the epoch that tells this device's launches apart.
@@ -523,6 +531,9 @@ float* s_partials[MAX_DEVICES];
 uint32_t* s_flags[MAX_DEVICES];
 uint32_t s_epoch[MAX_DEVICES];
 bool s_ready[MAX_DEVICES];
+// Host threads with contexts of their own may call the entry point at the same time: the set-up and the drawing of an
+// epoch are serialised here. (The array itself stays shared: kernels that overlap on the GPU race, as the header says.)
+std::mutex s_lock;
 }  // namespace
 
 extern "C" int hb_gemm_static_scratch(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t out, uint32_t m, hb_range w, hb_range x, hb_range y) {
@@ -541,6 +552,7 @@ extern "C" int hb_gemm_static_scratch(hb_ctx* ctx, uint32_t k, uint32_t n, uint3
     sk_fn fn = sk_pick_out<STATIC_BN>(out);
     const int dev = ctx->device;
     HB_CUDA(ctx, cudaSetDevice(dev));
+    std::lock_guard<std::mutex> guard(s_lock);
     if (!s_ready[dev]) {
         // Set-up, once per device, with that device current: ask the runtime where the arrays live on it.
         float* pp = nullptr;
@@ -551,7 +563,9 @@ extern "C" int hb_gemm_static_scratch(hb_ctx* ctx, uint32_t k, uint32_t n, uint3
             HB_CUDA(ctx, cudaFuncSetAttribute(reinterpret_cast<const void*>(sk_pick_out<STATIC_BN>(o)), cudaFuncAttributeMaxDynamicSharedMemorySize,
                                               (int)ctx->smem_optin - 1024));
         // The flags keep whatever the last call left; launches are told apart by the epoch, and the arrays start
-        // zeroed when the module loads, so epochs begin at 1 and nothing needs clearing.
+        // zeroed when the module loads, so epochs begin at 1 and nothing needs clearing. That also covers a launch
+        // whose bounded wait ran out: the context's own stream-K flags are cleared when the failure is reported, these
+        // are not, and need not be, because no later launch uses that launch's epoch again.
         s_partials[dev] = pp;
         s_flags[dev] = fp;
         s_epoch[dev] = 0;
@@ -585,7 +599,8 @@ extern "C" int hb_gemm_static_scratch(hb_ctx* ctx, uint32_t k, uint32_t n, uint3
     sp.total_units = (uint32_t)units;
     sp.scratch = s_partials[dev];
     sp.flags = s_flags[dev];
-    sp.epoch = ++s_epoch[dev];
+    if (++s_epoch[dev] == 0) s_epoch[dev] = 1;  // after 2^32 calls: 0 is what a never-written flag holds
+    sp.epoch = s_epoch[dev];
     const uint32_t grid = (uint32_t)std::min<uint64_t>(units, std::min<uint64_t>((uint64_t)ctx->sm_count, STATIC_SLOTS));
     fn<<<grid, GEMM_THREADS, stages * stage_bytes + 1024, ctx->stream>>>(tm_x, tm_w, sp);
     HB_CUDA(ctx, cudaGetLastError());

@@ -54,6 +54,10 @@ struct hb_ctx {
     // scratch of the stream-K GEMM: f32 partial tiles [sm_count][128][256] and their flags, made on first use
     float* sk_scratch = nullptr;
     uint32_t* sk_flags = nullptr;
+    // Counters and flags that kernels leave at zero when they end normally (arrival counters of the split forms, the
+    // argmax fold's keys, the stream-K flags): a launch that gave up on a bounded wait may leave them set, so they are
+    // all cleared when the failure is reported (check_status). Registered by whoever allocates them.
+    std::vector<std::pair<void*, size_t>> zero_on_failure;
 };
 
 namespace hb {
@@ -80,6 +84,7 @@ int make_tmap_bf16(hb_ctx* ctx, CUtensorMap* out, const void* base, uint64_t row
 int check_status(hb_ctx* ctx);
 
 inline bool range_ok(const hb_range& r, size_t need) { return r.ptr != nullptr && r.size >= need; }
+inline void zero_on_failure(hb_ctx* ctx, void* p, size_t bytes) { ctx->zero_on_failure.emplace_back(p, bytes); }
 
 // Factories (one translation unit per kernel family).
 int make_gemm(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out);

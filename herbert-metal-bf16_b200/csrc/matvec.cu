@@ -6,187 +6,15 @@
 // sharing the x loads (the reference's `rows` axis), sums cross the warp by an xor
 // butterfly and, with `split`, the K range is cut across the warps of a block and the
 // partial sums folded in a fixed order (kernels.rs:916-928). CUDA cores only.
-#include <algorithm>
+#include <cstring>
 
-#include "hb_internal.hpp"
-#include "tc05.cuh"
+#include "matvec_kernel.cuh"
 
 namespace hb {
 
-struct MatvecParams {
-    const uint4* w;
-    const uint4* x;
-    void* y;
-    uint32_t n;        // rows of W
-    uint32_t n_out;    // outputs per activation row (n, or n/2 for SWIGLU)
-    uint32_t k8;       // 16-byte chunks per row
-    uint32_t m;        // activation rows in use
-    uint32_t split;    // warps sharing one row group
-    uint32_t groups;   // row groups in all
-    // fused argmax over the outputs (Out::Bf16 only): see argmax_fold in tc05.cuh
-    unsigned long long* keys;  // [rows][ARGMAX_SLOTS]
-    uint32_t* counter;
-    uint32_t* index;           // [rows]
-    uint32_t store_y;          // 0: the index only
-};
-
-__device__ __forceinline__ uint4 ldg_stream(const uint4* p) {
-    uint4 v;
-    asm volatile("ld.global.nc.L1::no_allocate.L2::128B.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
-    return v;
-}
-
-constexpr int MV_THREADS = 256;
-constexpr int MV_WARPS = MV_THREADS / 32;
-
-template <int M, int R, int OUT, bool ARGMAX = false>
-__global__ void __launch_bounds__(MV_THREADS) matvec_kernel(const MatvecParams p) {
-    __shared__ float part[MV_WARPS][R * M];
-    __shared__ unsigned long long best_s[ARGMAX ? MV_WARPS : 1][M];
-    unsigned long long best[M];
-#pragma unroll
-    for (int i = 0; i < M; ++i) best[i] = 0ull;
-    griddep_launch_dependents();
-    griddep_wait();  // x comes from the kernel before this one
-    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t split = p.split;
-    const uint32_t slots = MV_WARPS / split;  // row groups a block works on at a time
-    const uint32_t slot = warp / split, piece = warp % split;
-    const uint32_t per = (p.k8 + split - 1) / split;
-    const uint32_t c_begin = piece * per, c_end = min(p.k8, c_begin + per);
-
-    for (uint32_t g0 = blockIdx.x * slots; g0 < p.groups; g0 += gridDim.x * slots) {
-        const uint32_t group = g0 + slot;
-        const bool live = group < p.groups;
-        float acc[R][M];
-#pragma unroll
-        for (int r = 0; r < R; ++r)
-#pragma unroll
-            for (int i = 0; i < M; ++i) acc[r][i] = 0.f;
-        uint32_t rows[R];
-        if (live) {
-            // The W rows of this group. SWIGLU: R/2 gate rows and their up rows (kernels.rs:934-944).
-#pragma unroll
-            for (int r = 0; r < R; ++r) {
-                uint32_t row;
-                if constexpr (OUT == HB_OUT_SWIGLU) row = (r < R / 2) ? group * (R / 2) + r : p.n_out + group * (R / 2) + (r - R / 2);
-                else row = group * R + r;
-                rows[r] = min(row, p.n - 1);  // rows past the end read the last row and are not written
-            }
-            for (uint32_t c = c_begin + lane; c < c_end; c += 32) {
-                uint4 wv[R];
-#pragma unroll
-                for (int r = 0; r < R; ++r) wv[r] = ldg_stream(p.w + (size_t)rows[r] * p.k8 + c);
-#pragma unroll
-                for (int i = 0; i < M; ++i) {
-                    if ((uint32_t)i < p.m) {
-                        const uint4 xv = __ldg(p.x + (size_t)i * p.k8 + c);
-                        const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
-#pragma unroll
-                        for (int r = 0; r < R; ++r) {
-                            const uint32_t ww[4] = {wv[r].x, wv[r].y, wv[r].z, wv[r].w};
-                            float a = acc[r][i];
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                a = __fmaf_rn(__uint_as_float(ww[j] << 16), __uint_as_float(xw[j] << 16), a);
-                                a = __fmaf_rn(__uint_as_float(ww[j] & 0xffff0000u), __uint_as_float(xw[j] & 0xffff0000u), a);
-                            }
-                            acc[r][i] = a;
-                        }
-                    }
-                }
-            }
-#pragma unroll
-            for (int r = 0; r < R; ++r)
-#pragma unroll
-                for (int i = 0; i < M; ++i) {
-                    float a = acc[r][i];
-#pragma unroll
-                    for (int off = 16; off >= 1; off >>= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
-                    acc[r][i] = a;
-                }
-        }
-        if (split > 1) {
-            if (live && lane == 0) {
-#pragma unroll
-                for (int r = 0; r < R; ++r)
-#pragma unroll
-                    for (int i = 0; i < M; ++i) part[warp][r * M + i] = acc[r][i];
-            }
-            __syncthreads();
-            if (live && piece == 0 && lane == 0) {
-#pragma unroll
-                for (int r = 0; r < R; ++r)
-#pragma unroll
-                    for (int i = 0; i < M; ++i) {
-                        float a = acc[r][i];
-                        for (uint32_t s = 1; s < split; ++s) a += part[warp + s][r * M + i];
-                        acc[r][i] = a;
-                    }
-            }
-        }
-        if (live && piece == 0 && lane == 0) {
-            if constexpr (OUT == HB_OUT_SWIGLU) {
-#pragma unroll
-                for (int r = 0; r < R / 2; ++r) {
-                    const uint32_t col = group * (R / 2) + r;
-                    if (col < p.n_out) {
-#pragma unroll
-                        for (int i = 0; i < M; ++i)
-                            if ((uint32_t)i < p.m)
-                                reinterpret_cast<uint16_t*>(p.y)[(size_t)i * p.n_out + col] =
-                                    (uint16_t)swiglu_bf16(round_bf16(acc[r][i]), round_bf16(acc[r + R / 2][i]));
-                    }
-                }
-            } else {
-#pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    const uint32_t col = group * R + r;
-                    if (col < p.n) {
-#pragma unroll
-                        for (int i = 0; i < M; ++i) {
-                            if ((uint32_t)i < p.m) {
-                                const size_t at = (size_t)i * p.n + col;
-                                if constexpr (OUT == HB_OUT_F32) reinterpret_cast<float*>(p.y)[at] = acc[r][i];
-                                else if constexpr (OUT == HB_OUT_BF16) {
-                                    const uint32_t h = f32_to_bf16(acc[r][i]);
-                                    if (!ARGMAX || p.store_y) reinterpret_cast<uint16_t*>(p.y)[at] = (uint16_t)h;
-                                    if constexpr (ARGMAX) {
-                                        const unsigned long long key = argmax_key(h, col);
-                                        best[i] = key > best[i] ? key : best[i];
-                                    }
-                                } else {
-                                    uint16_t* y = reinterpret_cast<uint16_t*>(p.y) + at;
-                                    *y = (uint16_t)f32_to_bf16(__fadd_rn(bf16_to_f32(*y), round_bf16(acc[r][i])));
-                                }
-                            }
-                        }
-                    }
-                }
-            }
-        }
-        if (split > 1) __syncthreads();  // `part` is reused by the next group
-    }
-    if constexpr (ARGMAX) {
-        // lane 0 of every warp holds the best of the outputs it wrote; fold the block, then the grid
-        if (lane == 0) {
-#pragma unroll
-            for (int i = 0; i < M; ++i) best_s[warp][i] = best[i];
-        }
-        __syncthreads();
-        if (threadIdx.x < M) {
-            unsigned long long b = best_s[0][threadIdx.x];
-            for (int w = 1; w < MV_WARPS; ++w) b = best_s[w][threadIdx.x] > b ? best_s[w][threadIdx.x] : b;
-            best_s[0][threadIdx.x] = b;
-        }
-        __syncthreads();
-        argmax_fold(best_s[0], p.m, p.keys, p.counter, p.index, gridDim.x);
-    }
-}
+typedef void (*mv_fn)(const MatvecParams);
 
 namespace {
-
-typedef void (*mv_fn)(const MatvecParams);
 
 template <int M, int R>
 mv_fn mv_out(uint32_t out, bool argmax) {
@@ -225,17 +53,23 @@ struct Matvec : hb_kernel {
     hb_matvec_desc d{};
     mv_fn fn = nullptr;
     int blocks_per_sm = 1;
+    size_t smem = 0;  // x_src != 0: the input rows made in the kernel
 
     unsigned long long* keys = nullptr;
     uint32_t* counter = nullptr;
 
     int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
-        if (na != (d.argmax ? 4 : 3)) return fail(ctx, HB_INVALID, name + (d.argmax ? ": bindings are W, x, y, index" : ": bindings are W, x, y"));
+        const bool norm = d.x_src == HB_X_NORM;
+        if (na != 3 + (norm ? 1 : 0) + (d.argmax ? 1 : 0))
+            return fail(ctx, HB_INVALID, name + (norm ? ": bindings are W, x, y, norm_w" : d.argmax ? ": bindings are W, x, y, index" : ": bindings are W, x, y"));
         if (m == 0 || m > d.rows_max) return fail(ctx, HB_INVALID, name + ": m outside 1.." + std::to_string(d.rows_max));
         if (d.argmax && !range_ok(a[3], (size_t)m * 4)) return fail(ctx, HB_INVALID, name + ": the index range is too small");
+        if (norm && (!range_ok(a[3], (size_t)d.k * 2) || (reinterpret_cast<uintptr_t>(a[3].ptr) & 15u)))
+            return fail(ctx, HB_INVALID, name + ": norm_w is too small or not 16-byte aligned");
         const uint32_t n_out = d.out == HB_OUT_SWIGLU ? d.n / 2 : d.n;
         const size_t ybytes = (size_t)m * n_out * (d.out == HB_OUT_F32 ? 4 : 2);
-        if (!range_ok(a[0], (size_t)d.n * d.k * 2) || !range_ok(a[1], (size_t)m * d.k * 2) || !range_ok(a[2], ybytes))
+        const size_t xbytes = (size_t)m * d.k * 2 * (d.x_src == HB_X_SWIGLU ? 2 : 1);  // XSrc::Swiglu: rows of [gate | up]
+        if (!range_ok(a[0], (size_t)d.n * d.k * 2) || !range_ok(a[1], xbytes) || !range_ok(a[2], ybytes))
             return fail(ctx, HB_INVALID, name + ": a bound range is too small");
         if ((reinterpret_cast<uintptr_t>(a[0].ptr) | reinterpret_cast<uintptr_t>(a[1].ptr)) & 15u)
             return fail(ctx, HB_INVALID, name + ": W and x must be 16-byte aligned");
@@ -252,12 +86,17 @@ struct Matvec : hb_kernel {
         p.counter = counter;
         p.index = d.argmax ? static_cast<uint32_t*>(a[3].ptr) : nullptr;
         p.store_y = d.argmax == 2 ? 0u : 1u;
+        if (norm) {
+            p.norm_w = static_cast<const uint16_t*>(a[3].ptr);
+            memcpy(&p.eps, &d.norm_eps_bits, 4);
+            p.plus_one = d.norm_plus_one;
+        }
         const uint32_t rows_per_group = d.out == HB_OUT_SWIGLU ? d.rows_per_warp / 2 : d.rows_per_warp;
         p.groups = (n_out + rows_per_group - 1) / rows_per_group;
         const uint32_t slots = MV_WARPS / d.split;
         uint32_t grid = (p.groups + slots - 1) / slots;
         if (d.persist) grid = std::min<uint32_t>(grid, (uint32_t)(ctx->sm_count * blocks_per_sm));
-        HB_CUDA(ctx, launch_kernel(ctx, true, fn, dim3(grid), dim3(MV_THREADS), 0, p));
+        HB_CUDA(ctx, launch_kernel(ctx, true, fn, dim3(grid), dim3(MV_THREADS), smem, p));
         ctx->launches++;
         return HB_OK;
     }
@@ -265,6 +104,7 @@ struct Matvec : hb_kernel {
 
 }  // namespace
 
+mv_fn mv_pick_fused_x(uint32_t mcap, uint32_t r, uint32_t out, uint32_t x_src);  // matvec_fused_x.cu
 int make_matvec_xs(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out);
 int make_matvec_skinny(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out);
 
@@ -273,7 +113,11 @@ int make_matvec(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out) {
     if (d->k == 0 || d->n == 0) return fail(ctx, HB_INVALID, "matvec: k and n must be positive");
     if (d->k % 8 != 0) return fail(ctx, HB_UNSUPPORTED, "matvec: K = " + std::to_string(d->k) + " is not a multiple of 8");
     if (d->out > HB_OUT_SWIGLU) return fail(ctx, HB_INVALID, "matvec: unknown output mode");
+    if (d->x_src > HB_X_SWIGLU) return fail(ctx, HB_INVALID, "matvec: x_src is 0 (x), 1 (RMSNorm of x) or 2 (SwiGLU of [gate | up])");
+    if (d->x_src == HB_X_NORM && (d->k % 256 != 0 || d->k / 256 > 32))
+        return fail(ctx, HB_UNSUPPORTED, "matvec: the fused norm is built for k a multiple of 256, at most 8192 (the reference's condition, src/metal/qwen.rs:1604)");
     if (d->tensor_core) return make_matvec_skinny(ctx, d, out);
+    if (d->x_src && d->x_stationary) return fail(ctx, HB_UNSUPPORTED, "matvec: the activation-stationary form takes x as it is");
     if (d->x_stationary) return make_matvec_xs(ctx, d, out);
     if (d->rows_max < 1 || d->rows_max > 8) return fail(ctx, HB_UNSUPPORTED, "matvec: 1..8 activation rows");
     if (d->out > HB_OUT_SWIGLU) return fail(ctx, HB_INVALID, "matvec: unknown output mode");
@@ -286,7 +130,10 @@ int make_matvec(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out) {
     while (mcap < d->rows_max) mcap *= 2;
     if (d->argmax > 2) return fail(ctx, HB_INVALID, "matvec: argmax is 0, 1 (logits and index) or 2 (index only)");
     if (d->argmax && d->out != HB_OUT_BF16) return fail(ctx, HB_UNSUPPORTED, "matvec: the fused argmax is over bf16 outputs (Out::Bf16)");
-    mv_fn fn = mv_pick(mcap, r, d->out, d->argmax != 0);
+    if (d->x_src && d->argmax) return fail(ctx, HB_UNSUPPORTED, "matvec: the fused argmax takes x as it is");
+    const size_t smem = d->x_src ? (size_t)mcap * d->k * 2 : 0;
+    if (smem > 96 * 1024) return fail(ctx, HB_UNSUPPORTED, "matvec: the rows made in the kernel do not fit in shared memory (rows * k * 2 <= 96 KiB)");
+    mv_fn fn = d->x_src ? mv_pick_fused_x(mcap, r, d->out, d->x_src) : mv_pick(mcap, r, d->out, d->argmax != 0);
     if (!fn) return fail(ctx, HB_UNSUPPORTED, "matvec: form not built");
     auto k = std::make_unique<Matvec>();
     k->d = *d;
@@ -295,12 +142,21 @@ int make_matvec(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out) {
     k->d.rows_max = mcap;
     if (d->argmax) k->d.persist = 1;  // the fold at the end of a block costs a round trip: few long-lived blocks, not thousands
     k->fn = fn;
+    k->smem = smem;
     k->kind = 2;
-    k->nargs = d->argmax ? 4 : 3;
-    char nm[160];
-    snprintf(nm, sizeof nm, "matvec_%ux%u_%s_m%u_r%u%s%s%s", d->k, d->n, out_tag(d->out), mcap, r,
+    k->nargs = 3 + (d->argmax ? 1 : 0) + (d->x_src == HB_X_NORM ? 1 : 0);
+    char nm[200];
+    std::string xtag;  // the reference's x_tag (src/metal/kernels.rs:286-293); the norm's constants are part of the kernel
+    if (d->x_src == HB_X_NORM) {
+        char t[48];
+        snprintf(t, sizeof t, "_nrm%08x%s", d->norm_eps_bits, d->norm_plus_one ? "p1" : "");
+        xtag = t;
+    } else if (d->x_src == HB_X_SWIGLU) {
+        xtag = "_swi";
+    }
+    snprintf(nm, sizeof nm, "matvec_%ux%u_%s_m%u_r%u%s%s%s%s", d->k, d->n, out_tag(d->out), mcap, r,
              split > 1 ? (std::string("_s") + std::to_string(split)).c_str() : "", k->d.persist ? "_p" : "",
-             d->argmax == 1 ? "_argmax" : d->argmax == 2 ? "_argmaxonly" : "");
+             d->argmax == 1 ? "_argmax" : d->argmax == 2 ? "_argmaxonly" : "", xtag.c_str());
     k->name = nm;
     if (hb_kernel* have = find(ctx, k->name)) {
         *out = have;
@@ -310,11 +166,16 @@ int make_matvec(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out) {
         void* pk = nullptr;
         int st = hb_alloc(ctx, (size_t)mcap * ARGMAX_SLOTS * 8 + 16, &pk);  // zeroed: the keys, then the counter
         if (st != HB_OK) return st;
+        zero_on_failure(ctx, pk, (size_t)mcap * ARGMAX_SLOTS * 8 + 16);
         k->keys = static_cast<unsigned long long*>(pk);
         k->counter = reinterpret_cast<uint32_t*>(k->keys + (size_t)mcap * ARGMAX_SLOTS);
     }
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
+        if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(max dynamic shared memory)");
+    }
     int occ = 1;
-    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, reinterpret_cast<const void*>(fn), MV_THREADS, 0);
+    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, reinterpret_cast<const void*>(fn), MV_THREADS, smem);
     k->blocks_per_sm = std::max(occ, 1);
     *out = intern(ctx, std::move(k));
     return HB_OK;

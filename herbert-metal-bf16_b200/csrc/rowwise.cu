@@ -6,40 +6,9 @@
 // loads so that the lane-strided chains read it from there.
 #include <algorithm>
 
-#include "hb_internal.hpp"
-#include "tc05.cuh"
+#include "rowwise.cuh"
 
 namespace hb {
-
-constexpr int ROW_THREADS = 256;
-
-// The group's sum of one f32 per thread, in the reference's order. `part` is shared scratch of 9 floats.
-__device__ __forceinline__ float group_sum256(float v, float* part) {
-    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) v = __fadd_rn(v, __shfl_xor_sync(0xffffffffu, v, off));
-    if (lane == 0) part[warp] = v;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        float acc = part[0];
-#pragma unroll
-        for (int g = 1; g < 8; ++g) acc = __fadd_rn(acc, part[g]);
-        part[8] = acc;
-    }
-    __syncthreads();
-    const float r = part[8];
-    __syncthreads();  // the scratch can be reused right after
-    return r;
-}
-
-// Copies a row of d bf16 into shared memory (16-byte pieces when the row allows).
-__device__ __forceinline__ void stage_row(uint16_t* dst, const uint16_t* src, uint32_t d, bool vec) {
-    if (vec) {
-        for (uint32_t i = threadIdx.x; i < d / 8; i += ROW_THREADS) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
-    } else {
-        for (uint32_t i = threadIdx.x; i < d; i += ROW_THREADS) dst[i] = src[i];
-    }
-}
 
 // ----------------------------------------------------------------- rmsnorm_rows
 // y = bf16((x * inv) * (w [+ 1])), inv = 1 / sqrt(sum(x^2) * (1/d) + eps) (reference src/metal/prefill.rs:70-117;
@@ -298,6 +267,7 @@ int make_argmax(hb_ctx* ctx, uint32_t n, uint32_t rows_max, hb_kernel** out) {
     void* p = nullptr;
     int r = hb_alloc(ctx, (size_t)rows_max * 8 + 16, &p);  // zeroed: the keys, then the counter
     if (r != HB_OK) return r;
+    zero_on_failure(ctx, p, (size_t)rows_max * 8 + 16);
     k->keys = static_cast<unsigned long long*>(p);
     k->counter = reinterpret_cast<uint32_t*>(k->keys + rows_max);
     *out = intern(ctx, std::move(k));

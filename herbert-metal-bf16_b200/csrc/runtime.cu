@@ -59,8 +59,8 @@ int check_status(hb_ctx* ctx) {
         if (st[0] == 2) snprintf(msg, sizeof msg, "kernel status 2: block %u read a table that does not fit its buffers (%u against %u)", st[1], st[2], st[3]);
         else snprintf(msg, sizeof msg, "kernel status %u: block %u gave up waiting at point %u (detail %u)", st[0], st[1], st[2], st[3]);
         cudaMemsetAsync(ctx->status_dev, 0, sizeof st, ctx->stream);
-        // a stream-K launch that gave up may have left flags of partial tiles set: clear them for the next launch
-        if (ctx->sk_flags) cudaMemsetAsync(ctx->sk_flags, 0, (size_t)ctx->sm_count * 4 * sizeof(uint32_t), ctx->stream);
+        // a launch that gave up may have left flags of partial tiles or arrival counters set: clear them for the next launch
+        for (const auto& z : ctx->zero_on_failure) cudaMemsetAsync(z.first, 0, z.second, ctx->stream);
         cudaStreamSynchronize(ctx->stream);
         return fail(ctx, HB_KERNEL, msg);
     }
@@ -250,6 +250,7 @@ int hb_ipc_open(hb_ctx* ctx, const void* handle64, void** dptr) {
 
 int hb_ipc_close(hb_ctx* ctx, void* dptr) {
     if (!ctx || !dptr) return HB_OK;
+    hb::bind(ctx);
     for (size_t i = 0; i < ctx->ipc_opened.size(); ++i)
         if (ctx->ipc_opened[i] == dptr) {
             ctx->ipc_opened.erase(ctx->ipc_opened.begin() + i);
@@ -281,6 +282,7 @@ int lane_stream(hb_ctx* ctx, int lane, cudaStream_t* out) {
 
 int hb_event_new(hb_ctx* ctx, hb_event** out) {
     if (!ctx || !out) return fail(ctx, HB_INVALID, "hb_event_new: bad argument");
+    hb::bind(ctx);  // an event belongs to the device that is current when it is made
     auto* e = new (std::nothrow) hb_event;
     if (!e) return fail(ctx, HB_OOM, "hb_event_new: out of memory");
     cudaError_t st = cudaEventCreateWithFlags(&e->ev, cudaEventDisableTiming);
@@ -294,14 +296,15 @@ int hb_event_new(hb_ctx* ctx, hb_event** out) {
 
 int hb_event_free(hb_ctx* ctx, hb_event* ev) {
     if (!ev) return HB_OK;
+    if (ctx) hb::bind(ctx);
     cudaEventDestroy(ev->ev);
     delete ev;
-    (void)ctx;
     return HB_OK;
 }
 
 int hb_lane_record(hb_ctx* ctx, int lane, hb_event* ev) {
     if (!ctx || !ev) return fail(ctx, HB_INVALID, "hb_lane_record: bad argument");
+    hb::bind(ctx);
     cudaStream_t s;
     int r = lane_stream(ctx, lane, &s);
     if (r != HB_OK) return r;
@@ -311,6 +314,7 @@ int hb_lane_record(hb_ctx* ctx, int lane, hb_event* ev) {
 
 int hb_lane_wait(hb_ctx* ctx, int lane, const hb_event* ev) {
     if (!ctx || !ev) return fail(ctx, HB_INVALID, "hb_lane_wait: bad argument");
+    hb::bind(ctx);
     cudaStream_t s;
     int r = lane_stream(ctx, lane, &s);
     if (r != HB_OK) return r;
@@ -320,6 +324,7 @@ int hb_lane_wait(hb_ctx* ctx, int lane, const hb_event* ev) {
 
 int hb_event_sync(hb_ctx* ctx, const hb_event* ev) {
     if (!ctx || !ev) return fail(ctx, HB_INVALID, "hb_event_sync: bad argument");
+    hb::bind(ctx);
     HB_CUDA(ctx, cudaEventSynchronize(ev->ev));
     return HB_OK;
 }
@@ -370,6 +375,7 @@ int hb_host_free(hb_ctx* ctx, void* host_ptr) {
 
 int hb_memset(hb_ctx* ctx, void* dst, int value, size_t bytes) {
     if (!ctx || !dst) return fail(ctx, HB_INVALID, "hb_memset: bad argument");
+    hb::bind(ctx);
     HB_CUDA(ctx, cudaMemsetAsync(dst, value, bytes, ctx->stream));
     return HB_OK;
 }
@@ -443,16 +449,17 @@ int hb_graph_record(hb_ctx* ctx, const hb_op* ops, int nops, hb_graph** out) {
     const uint64_t before = ctx->launches;
     HB_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
     int st = hb_run(ctx, ops, nops);
+    const std::string why = st != HB_OK ? ctx->err : std::string();  // the failing launch's message, before anything overwrites it
     cudaGraph_t g = nullptr;
     cudaError_t e = cudaStreamEndCapture(ctx->stream, &g);
     const uint64_t recorded = ctx->launches - before;
     ctx->launches = before;  // recording enqueues nothing
-    if (st != HB_OK) {
+    if (st != HB_OK || e != cudaSuccess) {
         if (g) cudaGraphDestroy(g);
-        cudaGetLastError();
-        return st;
+        cudaGetLastError();  // a capture that was invalidated leaves a sticky error behind
+        if (st != HB_OK) return fail(ctx, st, why);
+        return hb::cuda_fail(ctx, e, "cudaStreamEndCapture");
     }
-    if (e != cudaSuccess) return hb::cuda_fail(ctx, e, "cudaStreamEndCapture");
     auto* hg = new (std::nothrow) hb_graph;
     if (!hg) {
         cudaGraphDestroy(g);
@@ -496,7 +503,10 @@ int hb_graph_time(hb_ctx* ctx, hb_graph* g, int reps, double* gpu_seconds) {
 
 int hb_graph_free(hb_ctx* ctx, hb_graph* g) {
     if (!g) return HB_OK;
-    if (ctx) cudaStreamSynchronize(ctx->stream);
+    if (ctx) {
+        hb::bind(ctx);
+        cudaStreamSynchronize(ctx->stream);
+    }
     if (g->exec) cudaGraphExecDestroy(g->exec);
     if (g->graph) cudaGraphDestroy(g->graph);
     delete g;

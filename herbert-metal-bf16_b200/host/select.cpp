@@ -6,6 +6,7 @@
 // The "[autotune] ..." lines keep the reference's formats: they are the observable
 // behaviour of the loop.
 #include <algorithm>
+#include <chrono>
 #include <cmath>
 #include <cstring>
 #include <deque>
@@ -92,6 +93,8 @@ struct hb_selector {
     std::map<std::string, const hb_kernel*> mv_pick;
     bool inject_wrong = false;
     double autotune_seconds = 0.0;
+    bool timed_before = false;
+    std::chrono::steady_clock::time_point last_timed;  // when a timed comparison last ended (heat, qwen.rs:2577)
 };
 
 namespace {
@@ -192,12 +195,34 @@ int check_candidates(hb_selector* s, const std::string& what, const std::vector<
     return HB_OK;
 }
 
+// heat, qwen.rs:2577-2590 (auto.heat, in ms): the GPU brought to its sustained regime before a timed comparison when it
+// has been idle for more than 200 ms: the first candidate run back to back, about 50 ms a call, until auto.heat ms of
+// GPU time. On a power-capped part the first candidate of a cold chip is otherwise timed at a higher clock than the rest.
+int heat(hb_selector* s, const Cand& c, uint32_t m) {
+    const double want = s->tune.get("auto.heat") * 1e-3;
+    const auto now = std::chrono::steady_clock::now();
+    if (want <= 0.0 || (s->timed_before && std::chrono::duration<double>(now - s->last_timed).count() < 0.2)) return HB_OK;
+    double one = 0.0;
+    int r = time_ops(s, c, m, 1, &one);
+    if (r != HB_OK) return r;
+    const int reps = (int)std::min(256.0, std::max(1.0, std::ceil(0.05 / std::max(one, 1e-6))));
+    for (double t = 0.0; t < want;) {
+        double dt;
+        if ((r = time_ops(s, c, m, reps, &dt)) != HB_OK) return r;
+        t += dt;
+    }
+    s->timed_before = true;
+    s->last_timed = std::chrono::steady_clock::now();
+    return HB_OK;
+}
+
 // pick_flagged, qwen.rs:2547-2573: warm the first candidate, reps sized to about 2 ms, five rounds with the
 // candidates in turn, medians, the fastest eligible one; the others are timed and starred.
 int pick_flagged(hb_selector* s, const std::string& what, const std::vector<Cand>& cands, const std::vector<char>& eligible, uint32_t m, size_t* best_out,
                  double* median_out) {
     int r;
     double one = 0.0;
+    if ((r = heat(s, cands[0], m)) != HB_OK) return r;
     if ((r = time_ops(s, cands[0], m, 1, &one)) != HB_OK) return r;
     if ((r = time_ops(s, cands[0], m, 1, &one)) != HB_OK) return r;
     const int reps = (int)std::min(64.0, std::max(1.0, std::ceil(2e-3 / std::max(one, 1e-6))));
@@ -229,6 +254,8 @@ int pick_flagged(hb_selector* s, const std::string& what, const std::vector<Cand
         for (double t : v) s->autotune_seconds += t * reps;
     *best_out = best;
     if (median_out) *median_out = med[best];
+    s->timed_before = true;
+    s->last_timed = std::chrono::steady_clock::now();
     return HB_OK;
 }
 
@@ -515,13 +542,28 @@ int hb_select_gate_up(hb_selector* s, uint32_t k, uint32_t inter, hb_range w, hb
 
 int hb_select_matvec(hb_selector* s, uint32_t k, uint32_t n, uint32_t out, uint32_t rows, const hb_range* w_copies, int ncopies, hb_range x, hb_range y,
                      const hb_kernel** picked) {
-    if (!s || !picked || !w_copies || ncopies < 1) return HB_INVALID;
+    return hb_select_matvec_x(s, k, n, out, rows, HB_X_PLAIN, 0, 0, w_copies, ncopies, x, y, hb_range{nullptr, 0}, picked);
+}
+
+int hb_select_matvec_x(hb_selector* s, uint32_t k, uint32_t n, uint32_t out, uint32_t rows, uint32_t x_src, uint32_t norm_eps_bits, uint32_t norm_plus_one,
+                       const hb_range* w_copies, int ncopies, hb_range x, hb_range y, hb_range norm_w, const hb_kernel** picked) {
+    if (!s || !picked || !w_copies || ncopies < 1 || x_src > HB_X_SWIGLU) return HB_INVALID;
     hb_ctx* ctx = s->ctx;
+    if (x_src == HB_X_NORM && !norm_w.ptr) return hb::fail(ctx, HB_INVALID, "hb_select_matvec_x: XSrc::Norm and its weights go together");  // qwen.rs:1332
     try {
         const hb_tune& t = s->tune;
         int r;
+        // the bindings of a candidate: W, x, y and, with the norm made inside the kernel, its weights
+        auto bind = [&](int copy) {
+            std::vector<hb_range> b = {w_copies[copy], x, y};
+            if (x_src == HB_X_NORM) b.push_back(norm_w);
+            return b;
+        };
         auto get = [&](uint32_t rpw, uint32_t split, uint32_t persist, hb_kernel** kern, uint32_t xs = 0, uint32_t tc = 0) {
             hb_matvec_desc d{};
+            d.x_src = x_src;
+            d.norm_eps_bits = norm_eps_bits;
+            d.norm_plus_one = norm_plus_one;
             d.x_stationary = xs;
             d.tensor_core = tc;
             d.k = k;
@@ -541,6 +583,8 @@ int hb_select_matvec(hb_selector* s, uint32_t k, uint32_t n, uint32_t out, uint3
             return HB_OK;
         }
         std::string key = std::to_string(k) + "x" + std::to_string(n) + " " + out_debug(out);
+        if (x_src == HB_X_NORM) key += " norm";  // qwen.rs:1410
+        if (x_src == HB_X_SWIGLU) key += " swiglu";
         if (rows > 1) key += ", " + std::to_string(rows) + " rows";
         if (!t.mv_persists.empty()) {
             key += " p[";
@@ -558,6 +602,8 @@ int hb_select_matvec(hb_selector* s, uint32_t k, uint32_t n, uint32_t out, uint3
         std::vector<uint32_t> splits = t.get("mv.splitauto") != 0 ? std::vector<uint32_t>{1, 2, 4} : std::vector<uint32_t>{1};
         std::vector<uint32_t> persists = {0};
         for (uint32_t p : t.mv_persists) persists.push_back(p);
+        // an input made inside the kernel is made once per block: a grid of long-lived blocks is always a candidate
+        if (x_src != HB_X_PLAIN && t.mv_persists.empty()) persists.push_back(1);
         std::vector<Cand> cands;
         for (uint32_t split : splits)
             for (uint32_t persist : persists)
@@ -567,16 +613,16 @@ int hb_select_matvec(hb_selector* s, uint32_t k, uint32_t n, uint32_t out, uint3
                     if (get(rpw, split, persist ? 1u : 0u, &kern) != HB_OK) continue;
                     Cand c;
                     c.name = "r" + std::to_string(rpw) + (split > 1 ? "k" + std::to_string(split) : "") + (persist ? "p" + std::to_string(persist) : "");
-                    for (int i = 0; i < copies; ++i) add_op(c, kern, {w_copies[i], x, y});
+                    for (int i = 0; i < copies; ++i) add_op(c, kern, bind(i));
                     cands.push_back(std::move(c));
                 }
         // with several activation rows: the forms that keep the activations widened in registers
-        if (rows > 1)
+        if (rows > 1 && x_src == HB_X_PLAIN)
             for (uint32_t rpw : {2u, 4u}) {
                 if (get(rpw, 1, 1, &kern, 1) != HB_OK) continue;
                 Cand c;
                 c.name = "x" + std::to_string(rpw);
-                for (int i = 0; i < copies; ++i) add_op(c, kern, {w_copies[i], x, y});
+                for (int i = 0; i < copies; ++i) add_op(c, kern, bind(i));
                 cands.push_back(std::move(c));
             }
         // the weight stream on the tensor cores: whole feature blocks per CTA or evenly dealt units, 2 or 4 K blocks
@@ -593,10 +639,13 @@ int hb_select_matvec(hb_selector* s, uint32_t k, uint32_t n, uint32_t out, uint3
                 d.rows_max = rows;
                 d.tensor_core = f.ks;
                 d.split = f.kps;
+                d.x_src = x_src;
+                d.norm_eps_bits = norm_eps_bits;
+                d.norm_plus_one = norm_plus_one;
                 if (hb_matvec_get(ctx, &d, &kern) != HB_OK) continue;
                 Cand c;
                 c.name = f.name;
-                for (int i = 0; i < copies; ++i) add_op(c, kern, {w_copies[i], x, y});
+                for (int i = 0; i < copies; ++i) add_op(c, kern, bind(i));
                 cands.push_back(std::move(c));
             }
         }
@@ -606,6 +655,53 @@ int hb_select_matvec(hb_selector* s, uint32_t k, uint32_t n, uint32_t out, uint3
         if ((r = pick_flagged(s, "matvec " + key, cands, eligible, rows, &best, nullptr)) != HB_OK) return r;
         s->mv_pick[key] = cands[best].kernels[0];
         *picked = cands[best].kernels[0];
+        return HB_OK;
+    } catch (const std::exception& e) {
+        return hb::fail(ctx, HB_BACKEND, e.what());
+    }
+}
+
+// One axis of tune_step (src/metal/qwen.rs:3043-3170): the forms of the decode step that --tune does not fix are
+// timed at load on the whole step, one axis after another. The caller records the step once per value of the axis;
+// each is run twice to warm, then seven times, the median (ts[3]) kept; the first strictly fastest value wins.
+int hb_select_axis(hb_selector* s, const char* axis, const char* key, const hb_op* const* variants, const int* nops, const uint32_t* values, int nvariants,
+                   uint32_t position, uint32_t* best_value) {
+    if (!s || !axis || !key || !variants || !nops || !values || nvariants < 1 || !best_value) return HB_INVALID;
+    hb_ctx* ctx = s->ctx;
+    try {
+        const hb_tune& t = s->tune;
+        // an axis whose key --tune gives keeps it (qwen.rs:3121-3123); dec.auto=0 times nothing
+        if (t.was_given(key) || t.get("dec.auto") == 0) {
+            *best_value = t.get(key);
+            return HB_OK;
+        }
+        std::string line;
+        double best = 1e300;
+        uint32_t best_v = values[0];
+        for (int v = 0; v < nvariants; ++v) {
+            if (!variants[v] || nops[v] <= 0) {
+                line += (line.empty() ? "" : ", ") + std::to_string(values[v]) + " unavailable";
+                continue;
+            }
+            double sec;
+            int r = hb_time(ctx, variants[v], nops[v], 2, &sec);
+            if (r != HB_OK) return r;
+            std::vector<double> ts(7);
+            for (double& x : ts) {
+                if ((r = hb_time(ctx, variants[v], nops[v], 1, &x)) != HB_OK) return r;
+                s->autotune_seconds += x;
+            }
+            std::sort(ts.begin(), ts.end());
+            char buf[64];
+            snprintf(buf, sizeof buf, " %.3f ms", ts[3] * 1e3);
+            line += (line.empty() ? "" : ", ") + std::to_string(values[v]) + buf;
+            if (ts[3] < best) {
+                best = ts[3];
+                best_v = values[v];
+            }
+        }
+        say(s, "[autotune] decode step at position " + std::to_string(position) + ", " + axis + ": " + line + " -> " + std::to_string(best_v));
+        *best_value = best_v;
         return HB_OK;
     } catch (const std::exception& e) {
         return hb::fail(ctx, HB_BACKEND, e.what());

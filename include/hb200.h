@@ -194,6 +194,8 @@ typedef struct {
 } hb_gemm_desc;
 int hb_gemm_get(hb_ctx* ctx, const hb_gemm_desc* desc, hb_kernel** out);
 
+typedef enum { HB_X_PLAIN = 0, HB_X_NORM = 1, HB_X_SWIGLU = 2 } hb_x_src;
+
 /* Decode matvec y[r][n] = out(W[n][k] . x[r][k]) for m = 1..8 activation rows, an HBM-streaming kernel on the
  * CUDA cores: 128-bit loads, f32 FMA chains, warp-shuffle sums. Stands for matvec / matvec_split
  * (src/metal/kernels.rs:146-214,502-981). Bindings: W, x, y (kernels.rs:145). The reference is m = 1 only;
@@ -222,6 +224,16 @@ typedef struct {
                                (argmax_partial + argmax_final, src/metal/kernels.rs:1461-1565, folded into the
                                projection: no pass over the logits, no launch of its own); 2 = the index only, y is
                                not written. A fourth binding, index u32[m], follows y. */
+    uint32_t x_src;         /* hb_x_src: what the x binding holds (enum XSrc, src/metal/kernels.rs:236-252). HB_X_NORM: x is
+                               the residual stream and the input of the product is its RMSNorm, made by every block in
+                               shared memory first with rmsnorm_rows' sums in their order (norm_into, kernels.rs:355-442;
+                               the engine's dec.fnorm, src/metal/qwen.rs:224-228,1603): one launch less a norm, the same
+                               bits; k a multiple of 256, at most 8192; a binding norm_w (bf16 [k]) follows y.
+                               HB_X_SWIGLU: x rows are [gate (k) | up (k)] and the input is bf16(g * sigmoid(g) * u)
+                               (dec.fswi). Built for the CUDA-core form with 2 or 4 weight rows per warp, and HB_X_NORM
+                               also for the tensor-core stream with at most 16 activation rows. */
+    uint32_t norm_eps_bits; /* HB_X_NORM: the f32 bits of eps (the reference passes them so, XSrc::Norm{eps}) */
+    uint32_t norm_plus_one; /* HB_X_NORM: 1 = the weights are w + 1 */
 } hb_matvec_desc;
 int hb_matvec_get(hb_ctx* ctx, const hb_matvec_desc* desc, hb_kernel** out);
 
@@ -385,9 +397,12 @@ int hb_graph_free(hb_ctx* ctx, hb_graph* g);
 
 /* ---- the load-time selection loop (host library) ------------------------- */
 
-/* Tune, src/metal/qwen.rs:62-397. Keys on this path are acted on (gemm.auto gemm.mma gemm.tn gemm.mform
- * gemm.mfirst gemm.half gemm.simt prefill.block moe.grouped moe.tile pf.fswi mv.auto mv.split mv.persist
- * mv.cold dec.fswi); every other key of the reference is parsed, validated as a u32 and stored. */
+/* Tune, src/metal/qwen.rs:62-397. Acted on by the selection loop: gemm.auto gemm.mma gemm.tn gemm.mform gemm.mfirst
+ * prefill.block moe.tile pf.fswi mv.auto mv.split mv.splitauto mv.persist mv.persists mv.cold auto.heat, and through
+ * hb_select_axis dec.auto dec.fnorm dec.fswi. Every other key of the reference is parsed, range-checked where the
+ * reference checks it, stored and ignored: among the keys of this path that is gemm.simt (the layouts of a CUDA-core
+ * GEMM that does not exist here), gemm.half (half-staged Q4 tiles) and moe.grouped (0 = experts_matvec per (row, slot),
+ * src/metal/qwen_kernels.rs:1886, not built: the grouped GEMMs are the only expert form). */
 typedef struct hb_tune hb_tune;
 int hb_tune_new(hb_tune** out);
 void hb_tune_free(hb_tune* t);
@@ -425,6 +440,19 @@ int hb_select_gate_up(hb_selector* s, uint32_t k, uint32_t inter, hb_range w, hb
  * matrices are walked in turn so that weights come from memory, not cache (mv.cold, qwen.rs:248-251,1177). */
 int hb_select_matvec(hb_selector* s, uint32_t k, uint32_t n, uint32_t out, uint32_t rows, const hb_range* w_copies, int ncopies,
                      hb_range x, hb_range y, const hb_kernel** picked);
+/* The same for a projection whose input is made inside the kernel (mv_full with XSrc::Norm / XSrc::Swiglu,
+ * qwen.rs:1308-1335; the pick is cached under the key with " norm" appended, qwen.rs:1410): x is the residual stream
+ * and norm_w the norm's weights (HB_X_NORM), or x holds rows of [gate | up] (HB_X_SWIGLU, norm_w empty). */
+int hb_select_matvec_x(hb_selector* s, uint32_t k, uint32_t n, uint32_t out, uint32_t rows, uint32_t x_src, uint32_t norm_eps_bits, uint32_t norm_plus_one,
+                       const hb_range* w_copies, int ncopies, hb_range x, hb_range y, hb_range norm_w, const hb_kernel** picked);
+/* One axis of tune_step, qwen.rs:3043-3170 (dec.auto): the decode step recorded once per value of a switch (axis
+ * "fnorm" with key "dec.fnorm": the norms as kernels of their own, or made by the projections that follow them;
+ * "fswi" with "dec.fswi": the SwiGLU as the gate/up projection's epilogue, or made by the down projection) is run
+ * twice to warm and seven times for the median; the first strictly fastest value is returned and the line
+ * "[autotune] decode step at position {p}, {axis}: {v} {ms} ms, ... -> {v}" logged. A key that --tune gives is
+ * returned untimed, and so is the key's value when dec.auto = 0. variants[i] may be NULL (that form is unavailable). */
+int hb_select_axis(hb_selector* s, const char* axis, const char* key, const hb_op* const* variants, const int* nops, const uint32_t* values, int nvariants,
+                   uint32_t position, uint32_t* best_value);
 /* expert_pipes, qwen.rs:2326-2386: for bm in {16, 32, 64} (moe.tile only, if given) the sort and the two expert
  * GEMMs are timed on a real route (the caller has run the router on its block); per tile size the fastest
  * checked gate/up form is kept, then the tile whose sort + gate/up + down time is least.
