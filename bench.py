@@ -3,7 +3,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
 
 One JSON line on stdout. A step is one pass of the 9B-class layer GEMM set at M = 2048 rows
-(BASELINE config 3: qkv 4096->6144, o_proj 4096->4096 + residual, fused gate/up 4096->2x12288 with
+(the layer set: qkv 4096->6144, o_proj 4096->4096 + residual, fused gate/up 4096->2x12288 with
 SiLU*mul, down 12288->4096 + residual) through the C ABI of libhb200.so, kernels chosen by the
 load-time selection loop. `value` is TFLOP/s over all ranks with inputs resident in HBM, timed with
 CUDA events on the launching stream; `e2e` is the same step with the block's activations copied in
@@ -582,7 +582,7 @@ def bench_extra(hb, ctx, sel, torch, dev, wrap, pk, rank, world, barrier, max_ov
     out = {}
     g = torch.Generator(device=dev)
     g.manual_seed(1234 + rank)
-    # -- BASELINE config 1: one dense GEMM, M=512, K=1024, N=4096 (4.3 GFLOP: 64 tiles of 128x256, a launch-bound case)
+    # -- the small dense GEMM the CPU restatement runs whole: M=512, K=1024, N=4096 (4.3 GFLOP: 64 tiles of 128x256, a launch-bound case)
     try:
         w1 = (torch.randn(4096, 1024, device=dev, generator=g) / 32.0).bfloat16()
         x1 = torch.randn(512, 1024, device=dev, generator=g).bfloat16()
@@ -1074,7 +1074,7 @@ def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks)
 
 
 def cpu_baseline():
-    """The oracle's f32-accumulate contract kernel on the host cores, on a bounded sample: BASELINE config 1
+    """The oracle's f32-accumulate contract kernel on the host cores, on a bounded sample: the small dense GEMM
     (M=512, K=1024, N=4096) repeated, and one matvec pass; about 10-20 s in all."""
     import numpy as np
 
@@ -1105,7 +1105,7 @@ def cpu_baseline():
         reps += 1
     dt = (time.perf_counter() - t0) / reps
     value = STEP_FLOP * rows / ROWS / dt / 1e12
-    # BASELINE config 1 in full (M=512, K=1024, N=4096): the case the CPU restatement runs whole
+    # the small dense GEMM in full (M=512, K=1024, N=4096): the case the CPU restatement runs whole
     w1 = bf16(rng.standard_normal((4096, 1024), dtype=np.float32) / 32.0)
     x1 = bf16(rng.standard_normal((512, 1024), dtype=np.float32))
     o.gemm_f32(x1, w1, 0, None)

@@ -42,7 +42,7 @@ class Op(C.Structure):
 
 
 class GemmDesc(C.Structure):
-    _fields_ = [(n, C.c_uint32) for n in ("k", "n", "out", "rows_mode", "top_k", "experts", "bm", "tile_n", "stages", "cta_pair", "m_first", "rows_max", "stream_k", "merge_runs", "y_shards", "y_group_rows", "y_signal")]
+    _fields_ = [(n, C.c_uint32) for n in ("k", "n", "out", "rows_mode", "top_k", "experts", "bm", "tile_n", "stages", "cta_pair", "m_first", "rows_max", "stream_k", "merge_runs", "y_shards", "y_group_rows", "y_signal", "split_k")]
 
 
 class MatvecDesc(C.Structure):
@@ -107,6 +107,8 @@ def lib() -> C.CDLL:
         "hb_dequant_q4_get": (ci, [vp, u32, u32, pvp]),
         "hb_matvec_q4_get": (ci, [vp, u32, u32, u32, u32, u32, pvp]),
         "hb_matmul_q4_get": (ci, [vp, u32, u32, u32, u32, u32, pvp]),
+        "hb_gemm_q4_get": (ci, [vp, u32, u32, u32, u32, u32, u32, pvp]),
+        "hb_select_gemm_q4": (ci, [vp, u32, u32, u32, Range, Range, Range, Range, Range, u32, pvp, C.POINTER(ci)]),
         "hb_rmsnorm_get": (ci, [vp, u32, C.c_float, u32, pvp]),
         "hb_argmax_get": (ci, [vp, u32, u32, pvp]),
         "hb_moe_out_get": (ci, [vp, u32, pvp]),
@@ -172,7 +174,7 @@ EXPORTS = [
     "hb_open", "hb_close", "hb_last_error", "hb_describe", "hb_set_stream", "hb_alloc", "hb_set_alloc_limit", "hb_upload",
     "hb_download", "hb_memset", "hb_sync", "hb_launch_count", "hb_event_new", "hb_event_free", "hb_lane_record", "hb_lane_wait", "hb_event_sync",
     "hb_upload_async", "hb_download_async", "hb_host_alloc", "hb_host_free", "hb_ipc_export", "hb_ipc_open", "hb_ipc_close",
-    "hb_ep_dispatch_get", "hb_ep_plan_get", "hb_ep_return_get", "hb_ep_combine_get", "hb_tp_reduce_get", "hb_tp_sum_get", "hb_tp_sum_stream_get", "hb_dequant_q4_get", "hb_matvec_q4_get", "hb_matmul_q4_get", "hb_rmsnorm_get", "hb_argmax_get", "hb_moe_out_get", "hb_peer_sync_get", "hb_set_peer_wait_ms", "hb_gemm_get", "hb_matvec_get", "hb_swiglu_get", "hb_route_get",
+    "hb_ep_dispatch_get", "hb_ep_plan_get", "hb_ep_return_get", "hb_ep_combine_get", "hb_tp_reduce_get", "hb_tp_sum_get", "hb_tp_sum_stream_get", "hb_dequant_q4_get", "hb_matvec_q4_get", "hb_matmul_q4_get", "hb_gemm_q4_get", "hb_select_gemm_q4", "hb_rmsnorm_get", "hb_argmax_get", "hb_moe_out_get", "hb_peer_sync_get", "hb_set_peer_wait_ms", "hb_gemm_get", "hb_matvec_get", "hb_swiglu_get", "hb_route_get",
     "hb_moe_sort_get", "hb_moe_tiles", "hb_moe_gather_get", "hb_moe_combine_get", "hb_epilogue_get", "hb_gemm_static_scratch", "hb_kernel_name", "hb_launch", "hb_run", "hb_time", "hb_set_launch_overlap", "hb_graph_record", "hb_graph_launch", "hb_graph_time", "hb_graph_free",
     "hb_tune_new", "hb_tune_free", "hb_tune_apply", "hb_tune_get", "hb_tune_summary", "hb_tune_gemm_timed", "hb_selector_new",
     "hb_selector_free", "hb_selector_log", "hb_selector_buckets", "hb_fill_random16", "hb_select_gemm", "hb_select_gate_up",
@@ -387,6 +389,9 @@ class Context:
     def matmul_q4(self, k, n, m, ldx=0, ldy=0) -> "Kernel":
         return self._get(lib().hb_matmul_q4_get, k, n, m, ldx or k, ldy or n)
 
+    def gemm_q4(self, k, n, out=OUT_BF16, tile_n=0, m_first=1, rows_max=2048) -> "Kernel":
+        return self._get(lib().hb_gemm_q4_get, k, n, out, tile_n, m_first, rows_max)
+
     def rmsnorm(self, d, eps=1e-6, plus_one=False) -> "Kernel":
         return self._get(lib().hb_rmsnorm_get, d, C.c_float(eps), 1 if plus_one else 0)
 
@@ -436,8 +441,8 @@ class Context:
         self._check(fn(self.h, *args, C.byref(k)))
         return Kernel(self, k.value)
 
-    def gemm(self, k, n, out=OUT_BF16, rows_max=2048, tile_n=0, stages=0, cta_pair=0, m_first=1, rows_mode=ROWS_DENSE, top_k=0, experts=0, bm=0, merge_runs=0, stream_k=0, y_shards=0, y_group_rows=0, y_signal=0) -> Kernel:
-        d = GemmDesc(k, n, out, rows_mode, top_k, experts, bm, tile_n, stages, cta_pair, m_first, rows_max, stream_k, merge_runs, y_shards, y_group_rows, y_signal)
+    def gemm(self, k, n, out=OUT_BF16, rows_max=2048, tile_n=0, stages=0, cta_pair=0, m_first=1, rows_mode=ROWS_DENSE, top_k=0, experts=0, bm=0, merge_runs=0, stream_k=0, y_shards=0, y_group_rows=0, y_signal=0, split_k=0) -> Kernel:
+        d = GemmDesc(k, n, out, rows_mode, top_k, experts, bm, tile_n, stages, cta_pair, m_first, rows_max, stream_k, merge_runs, y_shards, y_group_rows, y_signal, split_k)
         return self._get(lib().hb_gemm_get, C.byref(d))
 
     def matvec(self, k, n, out=OUT_BF16, rows_max=1, rows_per_warp=2, split=1, persist=0, x_stationary=0, tensor_core=0, argmax=0, x_src=X_PLAIN, norm_eps_bits=0,
@@ -601,6 +606,14 @@ class Selector:
         p = C.c_void_p()
         self.ctx._check(lib().hb_select_matvec(self.h, k, n, out, rows, arr, len(w_copies), _as_range(x), _as_range(y), C.byref(p)))
         return Kernel(self.ctx, p.value)
+
+    def gemm_q4(self, k, n, out, wq, scales, w_bf16, x, y, m) -> list[Kernel]:
+        """[fused] (bindings W, X, Y, scales) or [dequant, gemm] (bindings W, scales, w_bf16 and w_bf16, X, Y)."""
+        ks = (C.c_void_p * 2)()
+        nk = C.c_int()
+        wb = _as_range(w_bf16) if w_bf16 is not None else Range(None, 0)
+        self.ctx._check(lib().hb_select_gemm_q4(self.h, k, n, out, _as_range(wq), _as_range(scales), wb, _as_range(x), _as_range(y), m, ks, C.byref(nk)))
+        return [Kernel(self.ctx, ks[i]) for i in range(nk.value)]
 
     def matvec_x(self, k, n, out, rows, x_src, norm_eps_bits, norm_plus_one, w_copies, x, y, norm_w=None) -> Kernel:
         """The form of a projection whose input is made inside the kernel (x_src X_NORM: x is the residual stream and

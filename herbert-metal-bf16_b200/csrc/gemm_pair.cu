@@ -114,6 +114,8 @@ gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
     const uint32_t tiles_m = (p.m + 255u) / 256u;
     const uint32_t tiles_n = p.tiles_n;
     const uint32_t num_tiles = tiles_m * tiles_n;
+    const uint32_t nsplit = p.split_k > 1 ? p.split_k : 1u;  // K slices per tile (hb_gemm_desc.split_k)
+    const uint32_t num_items = num_tiles * nsplit;           // slice-major: the items that run together share a K slice
 
     if (warp == 0) {
         // ---------------------------------------------------------- producer (one per CTA)
@@ -122,14 +124,16 @@ gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
             tma_prefetch_desc(&tm_w);
             uint32_t s = 0, ph = 0;
             bool ok = true;
-            for (uint32_t tile = pair; ok && tile < num_tiles; tile += npairs) {
+            for (uint32_t item = pair; ok && item < num_items; item += npairs) {
+                const uint32_t tile = item % num_tiles, slice = item / num_tiles;
                 const uint32_t tm = p.m_first ? tile % tiles_m : tile / tiles_n;
                 const uint32_t tn = p.m_first ? tile / tiles_m : tile % tiles_n;
                 const int row_x = (int)(tm * 256 + rank * 128);
                 int row_w;
                 if constexpr (OUT == HB_OUT_SWIGLU) row_w = (int)(rank * p.n_out + tn * HALF);  // rank 0: gate rows, rank 1: up rows
                 else row_w = (int)(tn * PAIR_BN + rank * HALF);
-                for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+                const uint32_t kb0 = slice * p.k_blocks / nsplit, kb1 = (slice + 1) * p.k_blocks / nsplit;
+                for (uint32_t kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(smem_u32(&bars.empty[s]), ph ^ 1u)) {
                         report(p.status, ST_WAIT_TIMEOUT, WHERE_EMPTY, s);
                         ok = false;
@@ -149,7 +153,9 @@ gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
         if (lane == 0 && rank == 0) {
             uint32_t s = 0, ph = 0, it = 0;
             bool ok = true;
-            for (uint32_t tile = pair; ok && tile < num_tiles; tile += npairs, ++it) {
+            for (uint32_t item = pair; ok && item < num_items; item += npairs, ++it) {
+                const uint32_t slice = item / num_tiles;
+                const uint32_t kb0 = slice * p.k_blocks / nsplit, kb1 = (slice + 1) * p.k_blocks / nsplit;
                 const uint32_t acc = it & 1u, acc_ph = (it >> 1) & 1u;
                 if (!mbar_wait(smem_u32(&bars.tmem_empty[acc]), acc_ph ^ 1u)) {
                     report(p.status, ST_WAIT_TIMEOUT, WHERE_TMEM_EMPTY, acc);
@@ -157,7 +163,7 @@ gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                 }
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + acc * PAIR_BN;
-                for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
+                for (uint32_t kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(smem_u32(&bars.full[s]), ph)) {
                         report(p.status, ST_WAIT_TIMEOUT, WHERE_FULL, s);
                         ok = false;
@@ -169,7 +175,7 @@ gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                     const uint64_t b_desc = umma_desc_sw128(a_addr + A_BYTES);
 #pragma unroll
                     for (uint32_t k4 = 0; k4 < BK / 16; ++k4)
-                        umma_bf16_pair(d_tmem, a_desc + 2 * k4, b_desc + 2 * k4, IDESC, (kb | k4) != 0 ? 1u : 0u);
+                        umma_bf16_pair(d_tmem, a_desc + 2 * k4, b_desc + 2 * k4, IDESC, (kb != kb0 || k4 != 0) ? 1u : 0u);
                     umma_commit_pair(smem_u32(&bars.empty[s]));
                     if (++s == S) { s = 0; ph ^= 1u; }
                 }
@@ -180,7 +186,8 @@ gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
         // ------------------------------------------------------------ epilogue (both CTAs: their own 128 rows)
         const uint32_t q = (uint32_t)warp & 3u;
         uint32_t it = 0;
-        for (uint32_t tile = pair; tile < num_tiles; tile += npairs, ++it) {
+        for (uint32_t item = pair; item < num_items; item += npairs, ++it) {
+            const uint32_t tile = item % num_tiles, slice = item / num_tiles;
             const uint32_t tm = p.m_first ? tile % tiles_m : tile / tiles_n;
             const uint32_t tn = p.m_first ? tile / tiles_m : tile % tiles_n;
             const uint32_t acc = it & 1u, acc_ph = (it >> 1) & 1u;
@@ -192,6 +199,71 @@ gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
             tc_fence_after();
             const uint32_t row = tm * 256 + rank * 128 + q * 32 + lane;
             const uint32_t t_addr = tmem_base + ((q * 32u) << 16) + acc * PAIR_BN;
+            if (nsplit > 1) {
+                // This item's partial of the warp's 32 rows x 256 columns: 16-byte piece j of 32-column chunk c of the
+                // lane's row at slot (c * 8 + j) * 32 + lane of the block, so a warp's store is 512 contiguous bytes.
+                constexpr uint32_t BLOCK16 = 32 * PAIR_BN / 4;  // 16-byte slots of a 32 x 256 f32 block
+                const uint32_t which = (tile * 2 + rank) * 4 + q;
+                uint4* mine = reinterpret_cast<uint4*>(p.partial) + ((size_t)slice * num_tiles * 8 + which) * BLOCK16 + lane;
+#pragma unroll 1
+                for (int c = 0; c < PAIR_BN / 32; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_32x32(t_addr + c * 32, v);
+                    tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) __stcg(mine + (c * 8 + j) * 32, make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
+                }
+                tc_fence_before();
+                __threadfence();
+                __syncwarp();
+                uint32_t arrived = 0;
+                if (lane == 0) {
+                    mbar_arrive_cluster(map_to_cta(smem_u32(&bars.tmem_empty[acc]), 0));  // the accumulator is in memory
+                    arrived = atomicAdd(&p.split_counters[which], 1u);
+                }
+                arrived = __shfl_sync(0xffffffffu, arrived, 0);
+                if (arrived + 1 != nsplit) continue;
+                // last of this quarter of the tile: every slice's partial is in memory; add them in slice order
+                __threadfence();
+                if (lane == 0) p.split_counters[which] = 0u;  // for the next launch
+                const uint4* all = reinterpret_cast<const uint4*>(p.partial) + (size_t)which * BLOCK16 + lane;
+                const size_t slice_stride = (size_t)num_tiles * 8 * BLOCK16;
+                auto sum_chunk = [&](int c, uint32_t (&v)[32]) {
+                    float a[32];
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) a[i] = 0.f;
+                    for (uint32_t s2 = 0; s2 < nsplit; ++s2) {
+                        uint4 t[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) t[j] = __ldcg(all + s2 * slice_stride + (c * 8 + j) * 32);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const uint32_t w4[4] = {t[j].x, t[j].y, t[j].z, t[j].w};
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) a[4 * j + e] = s2 == 0 ? __uint_as_float(w4[e]) : __fadd_rn(a[4 * j + e], __uint_as_float(w4[e]));
+                        }
+                    }
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(a[i]);
+                };
+                if constexpr (OUT == HB_OUT_SWIGLU) {
+#pragma unroll 1
+                    for (int c = 0; c < HALF / 32; ++c) {
+                        uint32_t g[32], u[32];
+                        sum_chunk(c, g);
+                        sum_chunk(HALF / 32 + c, u);
+                        store_chunk<OUT>(p, row, tn * HALF + c * 32, g, u);
+                    }
+                } else {
+#pragma unroll 1
+                    for (int c = 0; c < PAIR_BN / 32; ++c) {
+                        uint32_t v[32];
+                        sum_chunk(c, v);
+                        store_chunk<OUT>(p, row, tn * PAIR_BN + c * 32, v, v);
+                    }
+                }
+                continue;
+            }
             if constexpr (OUT == HB_OUT_SWIGLU) {
 #pragma unroll 1
                 for (int c = 0; c < HALF / 32; ++c) {
@@ -266,6 +338,7 @@ struct PairGemm : hb_kernel {
     const void* last_x = nullptr;
     uint32_t last_m = 0;
     uint32_t rank_of_signal = 0;  // y_signal: which row of the flags this rank writes (hb_gemm_desc.y_signal - 1)
+    uint32_t split_rows_cap = 0;  // split_k: the rows the context's partial-tile scratch was sized for
     CUtensorMap tm_x{}, tm_w{};
 
     int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
@@ -317,7 +390,14 @@ struct PairGemm : hb_kernel {
                 p.m_first = 0;  // group by group: all column tiles of a row tile before the next row tile
             }
         }
-        const uint32_t pairs = std::min<uint32_t>(p.num_tiles, (uint32_t)ctx->sm_count / 2);
+        if (d.split_k > 1) {
+            if (m > split_rows_cap) return fail(ctx, HB_INVALID, name + ": the split-K form is built for blocks of at most " + std::to_string(split_rows_cap) + " rows");
+            if (d.split_k > p.k_blocks) return fail(ctx, HB_INVALID, name + ": more K slices than 64-element K blocks");
+            p.split_k = d.split_k;
+            p.partial = ctx->splitk_partial;
+            p.split_counters = ctx->splitk_counters;
+        }
+        const uint32_t pairs = std::min<uint32_t>(p.num_tiles * std::max(1u, d.split_k), (uint32_t)ctx->sm_count / 2);
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(2 * pairs);
         cfg.blockDim = dim3(GEMM_THREADS);
@@ -338,6 +418,34 @@ struct PairGemm : hb_kernel {
 
 }  // namespace
 
+// The f32 partial tiles of all split-K kernels of a context live in one scratch range (kernels on one stream run one
+// after the other), grown when a shape needs more: S x tiles blocks of 256 x 256 f32, for blocks of at most 1024 rows
+// (the form is for short blocks: few tiles for many SMs), and a counter per quarter of a CTA's half tile.
+static int ensure_split_scratch(hb_ctx* ctx, const hb_gemm_desc* d, uint32_t* rows_cap_out) {
+    const uint32_t rows_cap = std::min<uint32_t>(std::max<uint32_t>(d->rows_max, 256u), 1024u);
+    const uint32_t n_out = d->out == HB_OUT_SWIGLU ? d->n / 2 : d->n;
+    const uint32_t cols_per_tile = d->out == HB_OUT_SWIGLU ? PAIR_BN / 2 : PAIR_BN;
+    const size_t tiles = (size_t)((rows_cap + 255) / 256) * ((n_out + cols_per_tile - 1) / cols_per_tile);
+    const size_t need = tiles * d->split_k * 256 * 256 * sizeof(float), need_counters = tiles * 8 * sizeof(uint32_t);
+    if (need > ctx->splitk_partial_bytes) {
+        void* sc = nullptr;
+        int r = hb_alloc(ctx, need, &sc);
+        if (r != HB_OK) return r;
+        ctx->splitk_partial = static_cast<float*>(sc);
+        ctx->splitk_partial_bytes = need;
+    }
+    if (need_counters > ctx->splitk_counter_bytes) {
+        void* cn = nullptr;
+        int r = hb_alloc(ctx, need_counters, &cn);
+        if (r != HB_OK) return r;
+        zero_on_failure(ctx, cn, need_counters);
+        ctx->splitk_counters = static_cast<uint32_t*>(cn);
+        ctx->splitk_counter_bytes = need_counters;
+    }
+    *rows_cap_out = rows_cap;
+    return HB_OK;
+}
+
 int make_gemm_pair(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
     *out = nullptr;
     if (d->tile_n != 0 && d->tile_n != 256) return fail(ctx, HB_UNSUPPORTED, "gemm: the CTA-pair form has 256 x 256 tiles only");
@@ -351,6 +459,7 @@ int make_gemm_pair(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
         if (d->y_group_rows != 256) return fail(ctx, HB_UNSUPPORTED, "gemm: y_signal needs y_group_rows = 256 (a group is a row tile of the CTA pair)");
         if (d->y_signal > d->y_shards) return fail(ctx, HB_UNSUPPORTED, "gemm: y_signal is this rank's number + 1, at most y_shards");
     }
+    if (d->split_k > 1 && (d->y_shards > 1 || d->split_k > 64)) return fail(ctx, HB_UNSUPPORTED, "gemm: split_k is 2..64 slices of K, not together with a Y in row blocks");
     pair_fn fn = pair_pick(d->out);
     const size_t budget = std::min<size_t>(ctx->smem_optin, 227 * 1024) - 2048;
     // a Y in row blocks: 16 KB behind the ring (4 KB per epilogue warp) for the transposing store
@@ -372,13 +481,22 @@ int make_gemm_pair(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
     if (d->y_shards > 1) ytag = "_y" + std::to_string(d->y_shards);
     if (d->y_group_rows) ytag += "g" + std::to_string(d->y_group_rows);
     if (d->y_signal) ytag += "_sig" + std::to_string(d->y_signal - 1);
+    if (d->split_k > 1) ytag += "_k" + std::to_string(d->split_k);
     snprintf(nm, sizeof nm, "gemm_pair_%ux%u_%s%s_t256x256_s%u%s", d->k, d->n, out_tag(d->out), d->m_first && !d->y_signal ? "_mf" : "", stages, ytag.c_str());
     k->name = nm;
     if (hb_kernel* have = find(ctx, k->name)) {
         auto* g = static_cast<PairGemm*>(have);
         g->d.rows_max = std::max(g->d.rows_max, d->rows_max);
+        if (d->split_k > 1) {
+            int r = ensure_split_scratch(ctx, &g->d, &g->split_rows_cap);
+            if (r != HB_OK) return r;
+        }
         *out = have;
         return HB_OK;
+    }
+    if (d->split_k > 1) {
+        int r = ensure_split_scratch(ctx, d, &k->split_rows_cap);
+        if (r != HB_OK) return r;
     }
     cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ctx->smem_optin - 1024);
     if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(max dynamic shared memory)");

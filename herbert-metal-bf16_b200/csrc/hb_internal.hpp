@@ -58,6 +58,11 @@ struct hb_ctx {
     // argmax fold's keys, the stream-K flags): a launch that gave up on a bounded wait may leave them set, so they are
     // all cleared when the failure is reported (check_status). Registered by whoever allocates them.
     std::vector<std::pair<void*, size_t>> zero_on_failure;
+    // scratch of the split-K CTA-pair GEMM: f32 partial tiles and their arrival counters, grown on demand
+    float* splitk_partial = nullptr;
+    size_t splitk_partial_bytes = 0;
+    uint32_t* splitk_counters = nullptr;
+    size_t splitk_counter_bytes = 0;
 };
 
 namespace hb {

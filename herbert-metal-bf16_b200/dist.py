@@ -1,6 +1,6 @@
 """Sharding of the two configurations of the path that partition across the GPUs of one box.
 
-The reference engine is single-GPU; these are the partitionings BASELINE.json asks for:
+The reference engine is single-GPU; these are the partitionings of its two workloads that shard across GPUs:
 
 * 27B-class FFN, tensor parallel: gate/up column-parallel (a rank owns a slice of gate rows AND the matching up
   rows, so the SwiGLU epilogue stays local), down row-parallel with f32 partial products, one all-reduce (sum)

@@ -259,13 +259,27 @@ int pick_flagged(hb_selector* s, const std::string& what, const std::vector<Cand
     return HB_OK;
 }
 
+// The K splits worth timing for the CTA-pair form at m rows: those that bring the work items (tiles x slices) close to
+// one, two, three or four whole waves of the SM pairs. None when the tiles alone fill a wave, or the block is long.
+std::vector<uint32_t> pair_splits(hb_ctx* ctx, uint32_t m, uint32_t k, uint32_t n_out, uint32_t cols_per_tile) {
+    std::vector<uint32_t> v;
+    if (m > 1024) return v;
+    const uint32_t tiles = ((m + 255) / 256) * ((n_out + cols_per_tile - 1) / cols_per_tile), pairs = (uint32_t)ctx->sm_count / 2, k_blocks = (k + 63) / 64;
+    for (uint32_t waves = 1; waves <= 4; ++waves) {
+        const uint32_t sp = pairs * waves / std::max(tiles, 1u);
+        if (sp >= 2 && sp <= 16 && sp <= k_blocks && std::find(v.begin(), v.end(), sp) == v.end()) v.push_back(sp);
+    }
+    return v;
+}
+
 // gemm.tn names the columns of the reference's tile (16/32/64); the B200 tile has four times as many.
 uint32_t tile_n_of_tn(uint32_t tn) { return tn >= 64 ? 256 : tn == 32 ? 128 : 64; }
 
 int get_dense(hb_selector* s, uint32_t k, uint32_t n, uint32_t out, uint32_t tile_n, uint32_t stages, uint32_t m_first, uint32_t pair, uint32_t rows_max,
-              hb_kernel** kern, uint32_t stream_k = 0) {
+              hb_kernel** kern, uint32_t stream_k = 0, uint32_t split_k = 0) {
     hb_gemm_desc d{};
     d.stream_k = stream_k;
+    d.split_k = split_k;
     d.k = k;
     d.n = n;
     d.out = out;
@@ -400,6 +414,15 @@ int hb_select_gemm(hb_selector* s, uint32_t k, uint32_t n, uint32_t out, hb_rang
             cands.push_back(std::move(c));
             eligible.push_back(1);
         }
+        // short blocks have too few 256 x 256 tiles for the SM pairs: the pair form with K cut into slices
+        for (uint32_t sp : pair_splits(ctx, m, k, out == HB_OUT_SWIGLU ? n / 2 : n, out == HB_OUT_SWIGLU ? 128 : 256)) {
+            if (get_dense(s, k, n, out, 256, 0, mf, 1, std::min(rows_max, 1024u), &kern, 0, sp) != HB_OK) continue;
+            Cand c;
+            c.name = "pair256x256k" + std::to_string(sp);
+            add_op(c, kern, {w, x, y});
+            cands.push_back(std::move(c));
+            eligible.push_back(1);
+        }
         // blocks of at most 64 rows are weight streams, not GEMMs (64 FLOP per weight byte): the decode kernel that
         // feeds the weights to the tensor cores as the wide operand takes the same bindings
         if (m <= 64) {
@@ -441,6 +464,82 @@ int hb_select_gemm(hb_selector* s, uint32_t k, uint32_t n, uint32_t out, hb_rang
         if ((r = pick_flagged(s, what, cands, eligible, m, &best, nullptr)) != HB_OK) return r;
         s->gemm_pick[key] = cands[best].kernels[0];
         *picked = cands[best].kernels[0];
+        return HB_OK;
+    } catch (const std::exception& e) {
+        return hb::fail(ctx, HB_BACKEND, e.what());
+    }
+}
+
+int hb_select_gemm_q4(hb_selector* s, uint32_t k, uint32_t n, uint32_t out, hb_range wq, hb_range scales, hb_range w_bf16, hb_range x, hb_range y, uint32_t m,
+                      const hb_kernel** kernels_out, int* nkernels) {
+    if (!s || !kernels_out || !nkernels) return HB_INVALID;
+    hb_ctx* ctx = s->ctx;
+    try {
+        const hb_tune& t = s->tune;
+        const uint32_t mf = t.get("gemm.mfirst") != 0 ? 1u : 0u;
+        const uint32_t rows_max = std::max(m, t.get("prefill.block"));
+        const bool have_copy = w_bf16.ptr != nullptr;
+        int r;
+        auto fused = [&](uint32_t tile_n, hb_kernel** kern) { return hb_gemm_q4_get(ctx, k, n, out, tile_n, mf, rows_max, kern); };
+        auto apart = [&](std::vector<const hb_kernel*>* ks) -> int {
+            hb_kernel* dq = nullptr;
+            int rr = hb_dequant_q4_get(ctx, k, n, &dq);
+            if (rr != HB_OK) return rr;
+            const hb_kernel* g = nullptr;
+            // the decoded matrix must be there before bf16 candidates are checked and timed on it
+            hb_range a[3] = {wq, scales, w_bf16};
+            if ((rr = hb_launch(ctx, dq, a, 3, 1)) != HB_OK) return rr;
+            if ((rr = hb_select_gemm(s, k, n, out, w_bf16, x, y, m, &g)) != HB_OK) return rr;
+            *ks = {dq, g};
+            return HB_OK;
+        };
+        std::vector<const hb_kernel*> ks;
+        if (!t.gemm_timed() || !have_copy) {  // q4.fuse names the form (qwen.rs:2234); without a scratch copy only the fused form exists
+            if (t.get("q4.fuse") == 1 || !have_copy) {
+                hb_kernel* f = nullptr;
+                if ((r = fused(256, &f)) != HB_OK) return r;
+                ks = {f};
+            } else if ((r = apart(&ks)) != HB_OK) {
+                return r;
+            }
+        } else {
+            const std::string key = std::to_string(k) + "x" + std::to_string(n) + " " + out_debug(out) + " q4, " + std::to_string(m) + " rows";
+            auto it = s->gate_up_pick.find(key);
+            if (it != s->gate_up_pick.end()) {
+                ks = it->second;
+            } else {
+                std::vector<const hb_kernel*> ap;
+                if ((r = apart(&ap)) != HB_OK) return r;
+                std::vector<Cand> cands;
+                Cand c0;
+                c0.name = "dequant+gemm";
+                add_op(c0, ap[0], {wq, scales, w_bf16}, 0, 1);
+                add_op(c0, ap[1], {w_bf16, x, y});
+                cands.push_back(std::move(c0));
+                for (uint32_t tn : {256u, 128u}) {
+                    hb_kernel* f = nullptr;
+                    if (fused(tn, &f) != HB_OK) {
+                        say(s, "[autotune] gemm " + key + ": fused128x" + std::to_string(tn) + " not built (" + hb_last_error(ctx) + ")");
+                        continue;
+                    }
+                    Cand c;
+                    c.name = "fused128x" + std::to_string(tn);
+                    add_op(c, f, {wq, x, y, scales});
+                    cands.push_back(std::move(c));
+                }
+                std::vector<char> eligible(cands.size(), 1);
+                const uint32_t n_out = out == HB_OUT_SWIGLU ? n / 2 : n;
+                const bool f32_out = out == HB_OUT_F32;
+                const std::string what = "gemm " + key;
+                if ((r = check_candidates(s, what, cands, eligible, y, (size_t)n_out * (f32_out ? 4 : 2), f32_out, m)) != HB_OK) return r;
+                size_t best;
+                if ((r = pick_flagged(s, what, cands, eligible, m, &best, nullptr)) != HB_OK) return r;
+                ks = cands[best].kernels;
+                s->gate_up_pick[key] = ks;
+            }
+        }
+        for (size_t i = 0; i < ks.size(); ++i) kernels_out[i] = ks[i];
+        *nkernels = (int)ks.size();
         return HB_OK;
     } catch (const std::exception& e) {
         return hb::fail(ctx, HB_BACKEND, e.what());
@@ -502,6 +601,15 @@ int hb_select_gate_up(hb_selector* s, uint32_t k, uint32_t inter, hb_range w, hb
                     }
                     Cand c;
                     c.name = name;
+                    add_op(c, f, {w, x, h});
+                    cands.push_back(std::move(c));
+                    eligible.push_back(1);
+                }
+                for (uint32_t sp : pair_splits(ctx, m, k, inter, 128)) {
+                    hb_kernel* f = nullptr;
+                    if (get_dense(s, k, 2 * inter, HB_OUT_SWIGLU, 256, 0, mf, 1, std::min(rows_max, 1024u), &f, 0, sp) != HB_OK) continue;
+                    Cand c;
+                    c.name = "fusedpair256x256k" + std::to_string(sp);
                     add_op(c, f, {w, x, h});
                     cands.push_back(std::move(c));
                     eligible.push_back(1);

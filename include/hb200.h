@@ -191,6 +191,11 @@ typedef struct {
                             (zeroed once). When the last tile of group g is stored, flag [rank][g] of every rank is set to
                             ctl[0] + 1, the step's number, which hb_tp_sum_stream_get's kernel waits for and then writes
                             to ctl[0]. The tiles are walked group by group (m_first is ignored). */
+    uint32_t split_k;    /* DENSE, cta_pair: S = 2..64 = every 256 x 256 tile is computed as S work items, one per equal slice
+                            of K, so that a short block (few tiles) still gives every SM work at the tile size that reads
+                            the operands least often; an item leaves its f32 partial in scratch memory of the context and
+                            whoever completes a quarter of a CTA's half tile last adds the S partials in slice order
+                            (the same bits whoever is last) and applies the output mode. For blocks of at most 1024 rows. */
 } hb_gemm_desc;
 int hb_gemm_get(hb_ctx* ctx, const hb_gemm_desc* desc, hb_kernel** out);
 
@@ -280,6 +285,13 @@ int hb_matvec_q4_get(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t out, uint32_t
  * rows and every row is summed in matvec_q4's order (the decode step's bits). The kernel is built for m: launch it
  * with that m. Bindings W, X, Y, scales. */
 int hb_matmul_q4_get(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t m, uint32_t ldx, uint32_t ldy, hb_kernel** res);
+
+/* gemm_mma_q4, src/metal/prefill.rs:427-434, 1058-1076 (the engine's q4.fuse = 1, src/metal/qwen.rs:169-173): the
+ * prefill GEMM on Q4_0 weights, every staged cell of W decoded to bf16(d * q) as dequant_q4 decodes it while the tile
+ * is staged, so that the sums are those of hb_dequant_q4_get followed by hb_gemm_get, bit for bit, without the bf16
+ * copy of W ever being written or read. k a multiple of 32; tile_n 128 or 256 (0 = 256); any 1 <= m <= rows_max.
+ * Bindings W (Q4 data), X, Y, scales (the reference's order: state, W, X, Y, scales). */
+int hb_gemm_q4_get(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t out, uint32_t tile_n, uint32_t m_first, uint32_t rows_max, hb_kernel** res);
 
 /* ---- expert-parallel exchange over peer memory (no reference counterpart: the reference runs on one GPU) ----
  * Experts are partitioned contiguously over `world` ranks, the token rows are each rank's own. A rank sorts its
@@ -398,7 +410,7 @@ int hb_graph_free(hb_ctx* ctx, hb_graph* g);
 /* ---- the load-time selection loop (host library) ------------------------- */
 
 /* Tune, src/metal/qwen.rs:62-397. Acted on by the selection loop: gemm.auto gemm.mma gemm.tn gemm.mform gemm.mfirst
- * prefill.block moe.tile pf.fswi mv.auto mv.split mv.splitauto mv.persist mv.persists mv.cold auto.heat, and through
+ * prefill.block moe.tile pf.fswi q4.fuse mv.auto mv.split mv.splitauto mv.persist mv.persists mv.cold auto.heat, and through
  * hb_select_axis dec.auto dec.fnorm dec.fswi. Every other key of the reference is parsed, range-checked where the
  * reference checks it, stored and ignored: among the keys of this path that is gemm.simt (the layouts of a CUDA-core
  * GEMM that does not exist here), gemm.half (half-staged Q4 tiles) and moe.grouped (0 = experts_matvec per (row, slot),
@@ -440,6 +452,14 @@ int hb_select_gate_up(hb_selector* s, uint32_t k, uint32_t inter, hb_range w, hb
  * matrices are walked in turn so that weights come from memory, not cache (mv.cold, qwen.rs:248-251,1177). */
 int hb_select_matvec(hb_selector* s, uint32_t k, uint32_t n, uint32_t out, uint32_t rows, const hb_range* w_copies, int ncopies,
                      hb_range x, hb_range y, const hb_kernel** picked);
+/* QwenEngine::gemm for a Q4_0 matrix (qwen.rs:2200-2315 with q4; the key gets " q4", qwen.rs:2239): with q4.fuse given,
+ * 0 = dequant_q4 into `w_bf16` and then the GEMM the keys name (2 kernels), 1 = the GEMM that decodes while it stages
+ * (1 kernel); with timing on both are built ("dequant+" the picked bf16 form, and the fused tiles), checked against the
+ * first (check_candidates) and timed. kernels_out receives 1 or 2 kernels: [fused] with bindings W (Q4 data), X, Y,
+ * scales, or [dequant, gemm] with bindings W (Q4 data), scales, w_bf16 and w_bf16, X, Y. w_bf16 is the scratch for the
+ * decoded matrix (bf16 [n][k]); it may be empty, and then only the fused form is built. */
+int hb_select_gemm_q4(hb_selector* s, uint32_t k, uint32_t n, uint32_t out, hb_range wq, hb_range scales, hb_range w_bf16, hb_range x, hb_range y, uint32_t m,
+                      const hb_kernel** kernels_out, int* nkernels);
 /* The same for a projection whose input is made inside the kernel (mv_full with XSrc::Norm / XSrc::Swiglu,
  * qwen.rs:1308-1335; the pick is cached under the key with " norm" appended, qwen.rs:1410): x is the residual stream
  * and norm_w the norm's weights (HB_X_NORM), or x holds rows of [gate | up] (HB_X_SWIGLU, norm_w empty). */

@@ -87,7 +87,7 @@ void hbo_swiglu_slots(const uint16_t* egu, uint16_t* ehb, int pairs, int mi);
 void hbo_moe_down(const uint16_t* ehb, const uint16_t* wd, const uint32_t* list, const uint32_t* tiles, uint16_t* ey, int h, int mi);
 /* qwen_kernels.rs:2119-2161: acc = bf16(acc + bf16(y*w)) over the slots. */
 void hbo_moe_combine(const uint16_t* ey, const uint32_t* route, uint16_t* out, int rows, int d, int top_k);
-/* BASELINE config 5 words the combine as an f32 sum: out = bf16(sum_s y_s*w_s), f32 FMA chain in slot order. */
+/* The combine as an f32 sum (a variant some callers ask for; the reference rounds to bf16 at every step): out = bf16(sum_s y_s*w_s), f32 FMA chain in slot order. */
 void hbo_moe_combine_f32(const uint16_t* ey, const uint32_t* route, uint16_t* out, int rows, int d, int top_k);
 
 /* ---- the rows around the matrix products ------------------------------- */

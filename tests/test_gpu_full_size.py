@@ -110,6 +110,11 @@ def test_layer_9b_every_gemm_form(ctx, oracle, m, name, k, n, out):
     for tile_n in (128, 64):
         assert np.array_equal(s.check(ctx, oracle, ctx.gemm(k, n, out, rows_max=m, tile_n=tile_n)), base)
     assert np.array_equal(s.check(ctx, oracle, ctx.gemm(k, n, out, rows_max=m, m_first=0)), base)
+    if m <= 1024:  # the split-K candidates of a short block ("pair256x256k{S}")
+        for sp in (2, 4, 9):
+            kern = ctx.gemm(k, n, out, rows_max=m, cta_pair=1, split_k=sp)
+            assert kern.name.endswith(f"_k{sp}")
+            s.check(ctx, oracle, kern)
 
 
 @pytest.mark.parametrize("name,k,n,out", LAYER_9B, ids=[f"{s[0]}_{s[1]}x{s[2]}" for s in LAYER_9B])

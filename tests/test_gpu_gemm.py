@@ -80,6 +80,49 @@ def test_cta_pair_form(ctx, oracle, out, m, k, n):
     within_contract(oracle, oracle.gemm_f64(x, w, out, y0), got, kern.name)
 
 
+@pytest.mark.parametrize("out", MODES)
+@pytest.mark.parametrize("m,k,n,splits", [(300, 320, 520, (2, 5)), (256, 128, 256, (2,)), (1, 1024, 72, (3, 16)), (683, 1024, 1000, (2, 7)), (512, 4096, 1024, (4, 9)), (1024, 200, 264, (3,))])
+def test_cta_pair_split_k_form(ctx, oracle, hb200, out, m, k, n, splits):
+    # every 256 x 256 tile as S work items over equal slices of K, the f32 partials summed in slice order by whoever
+    # finishes a quarter of the tile last: the contract holds, and the bits do not depend on who that was
+    if out == OUT_SWIGLU and n % 2:
+        pytest.skip("odd n")
+    x, w, y0 = gemm_inputs(oracle, m, k, n)
+    d_x, d_w = ctx.to_device(x), ctx.to_device(w)
+    want = oracle.gemm_f64(x, w, out, y0)
+    for sp in splits:
+        kern = ctx.gemm(k, n, out, rows_max=m, cta_pair=1, split_k=sp)
+        assert kern.name.startswith("gemm_pair_") and kern.name.endswith(f"_k{sp}")
+        outs = []
+        for _ in range(3):  # the counters are back at zero after every launch
+            d_y, dtype, shape = out_buffer(ctx, out, m, n, y0)
+            kern(m, d_w, d_x, d_y)
+            ctx.sync()
+            outs.append(d_y.download(dtype, shape))
+        within_contract(oracle, want, outs[0], kern.name)
+        assert all(np.array_equal(outs[0].view(np.uint8), o.view(np.uint8)) for o in outs[1:]), f"{kern.name}: the bits change from launch to launch"
+
+
+def test_cta_pair_split_k_limits(ctx, hb200):
+    for bad in (dict(split_k=65), dict(split_k=2, y_shards=2, out=OUT_F32)):
+        with pytest.raises(hb200.HbError) as e:
+            ctx.gemm(1024, 512, **dict(dict(out=OUT_BF16, cta_pair=1, rows_max=256), **bad))
+        assert e.value.status == hb200.UNSUPPORTED
+    kern = ctx.gemm(128, 512, OUT_BF16, rows_max=2048, cta_pair=1, split_k=2)
+    buf = ctx.alloc(2048 * 512 * 2)
+    with pytest.raises(hb200.HbError) as e:
+        kern(2048, buf, buf, buf)  # the partial-tile scratch is sized for short blocks
+    assert e.value.status == hb200.INVALID and "1024 rows" in e.value.message
+    with pytest.raises(hb200.HbError) as e:
+        ctx.gemm(128, 512, OUT_BF16, rows_max=256, cta_pair=1, split_k=3)(256, buf, buf, buf)  # K = 128 is two blocks of 64
+    assert e.value.status == hb200.INVALID
+    # the stream-K form refuses a pipeline smaller than one f32 partial tile (it would land a partial beyond its shared memory)
+    with pytest.raises(hb200.HbError) as e:
+        ctx.gemm(1024, 512, OUT_BF16, rows_max=256, stream_k=1, tile_n=256, stages=2)
+    assert e.value.status == hb200.UNSUPPORTED and "partial tile" in e.value.message
+    ctx.gemm(1024, 512, OUT_BF16, rows_max=256, stream_k=1, tile_n=128, stages=2)  # 64 KiB of pipeline for a 64 KiB tile: fits
+
+
 def test_cta_pair_matches_single_cta_bits(ctx, oracle):
     # the pair changes who stages what, not the order of the K loop: same bits as the 128 x 256 kernel
     m, k, n = 512, 2048, 768
@@ -89,7 +132,7 @@ def test_cta_pair_matches_single_cta_bits(ctx, oracle):
 
 
 def test_config1_dense_gemm(ctx, oracle):
-    # BASELINE config 1: M=512, K=1024, N=4096
+    # the small dense GEMM: M=512, K=1024, N=4096
     for m_first in (1, 0):
         kern, (x, w, y0), got = run_gemm(ctx, oracle, 512, 1024, 4096, OUT_BF16, m_first=m_first)
         within_contract(oracle, oracle.gemm_f64(x, w), got, kern.name)

@@ -59,7 +59,7 @@ def test_m1_equals_reference_lane_order_closely(ctx, oracle):
 
 @pytest.mark.parametrize("m", [1, 4, 8])
 def test_config2_shapes(ctx, oracle, m):
-    # BASELINE config 2: K=4096, N=12288 (and the LM-head-like N=151936 on a row sample of W)
+    # the decode projections of the 9B-class layer: K=4096, N=12288 (and the LM-head-like N=151936 on a row sample of W)
     k, n = 4096, 12288
     kern, want, got = run(ctx, oracle, m, k, n, OUT_BF16, rows_per_warp=4)
     within_contract(oracle, want, got, f"{kern.name} m={m}")
