@@ -30,9 +30,9 @@ struct GemmParams {
     const uint64_t* flag_table;  // [world] -> u32[world][TP_MAX_GROUPS] on every rank
     uint32_t* ctl;               // this rank's control words: [0] steps completed, [TP_CTL_GROUP0 + g] arrivals of group g
     uint32_t world, rank;
-    // split_k = S > 1 (the CTA-pair form): a work item is (tile, one of S equal slices of K); every item leaves its f32
-    // partial in `partial`, and whoever completes a tile's quarter last adds the S partials in slice order and applies
-    // the output mode. partial: [S][tiles][2][4] blocks of 32 x 256 f32; split_counters: [tiles][2][4], zero between launches.
+    // split_k = S > 1 (the CTA-pair form): a work item is (tile, one of S equal slices of K); the slices of a tile hand a
+    // running f32 sum from one to the next through `partial` and the last applies the output mode.
+    // partial: [tiles][2][4] blocks of 32 x 256 f32; split_counters: [tiles][2][4], slices done, zero between launches.
     uint32_t split_k;
     float* partial;
     uint32_t* split_counters;

@@ -200,67 +200,82 @@ gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
             const uint32_t row = tm * 256 + rank * 128 + q * 32 + lane;
             const uint32_t t_addr = tmem_base + ((q * 32u) << 16) + acc * PAIR_BN;
             if (nsplit > 1) {
-                // This item's partial of the warp's 32 rows x 256 columns: 16-byte piece j of 32-column chunk c of the
-                // lane's row at slot (c * 8 + j) * 32 + lane of the block, so a warp's store is 512 contiguous bytes.
+                // The slices of a tile hand a running f32 sum from one to the next through one block of scratch per
+                // quarter of a CTA's half tile: slice 0 stores its accumulator, slice s adds its own to what the slices
+                // before it left (waiting, bounded, until they are done: they come earlier in every pair's item order,
+                // so they are running or finished), the last slice applies the output mode. The order of the sum is
+                // the order of the slices, whoever runs when. 16-byte piece j of 32-column chunk c of the lane's row is
+                // slot (c * 8 + j) * 32 + lane of the block: a warp's access is 512 contiguous bytes.
                 constexpr uint32_t BLOCK16 = 32 * PAIR_BN / 4;  // 16-byte slots of a 32 x 256 f32 block
                 const uint32_t which = (tile * 2 + rank) * 4 + q;
-                uint4* mine = reinterpret_cast<uint4*>(p.partial) + ((size_t)slice * num_tiles * 8 + which) * BLOCK16 + lane;
-#pragma unroll 1
-                for (int c = 0; c < PAIR_BN / 32; ++c) {
-                    uint32_t v[32];
+                uint4* buf = reinterpret_cast<uint4*>(p.partial) + (size_t)which * BLOCK16 + lane;
+                uint32_t* flag = p.split_counters + which;  // slices of this quarter done so far
+                const bool first = slice == 0, last = slice + 1 == nsplit;
+                bool ready = true;
+                if (!first) {
+                    if (lane == 0) {
+                        const long long t0 = clock64();
+                        uint32_t v;
+                        do {
+                            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+                            if (v != slice && clock64() - t0 > HB_WAIT_LIMIT_CYCLES) ready = false;
+                        } while (v != slice && ready);
+                    }
+                    ready = __shfl_sync(0xffffffffu, ready ? 1 : 0, 0) != 0;
+                    if (!ready) {
+                        if (lane == 0) report(p.status, ST_WAIT_TIMEOUT, WHERE_TMEM_FULL, 64u + slice);
+                        break;
+                    }
+                }
+                // own accumulator chunk c plus the running sum (if any): v[] as f32 bits
+                auto chunk = [&](int c, uint32_t (&v)[32]) {
+                    uint4 t[8];
+                    if (!first) {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) t[j] = __ldcg(buf + (c * 8 + j) * 32);
+                    }
                     tmem_ld_32x32(t_addr + c * 32, v);
                     tmem_ld_wait();
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) __stcg(mine + (c * 8 + j) * 32, make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
-                }
-                tc_fence_before();
-                __threadfence();
-                __syncwarp();
-                uint32_t arrived = 0;
-                if (lane == 0) {
-                    mbar_arrive_cluster(map_to_cta(smem_u32(&bars.tmem_empty[acc]), 0));  // the accumulator is in memory
-                    arrived = atomicAdd(&p.split_counters[which], 1u);
-                }
-                arrived = __shfl_sync(0xffffffffu, arrived, 0);
-                if (arrived + 1 != nsplit) continue;
-                // last of this quarter of the tile: every slice's partial is in memory; add them in slice order
-                __threadfence();
-                if (lane == 0) p.split_counters[which] = 0u;  // for the next launch
-                const uint4* all = reinterpret_cast<const uint4*>(p.partial) + (size_t)which * BLOCK16 + lane;
-                const size_t slice_stride = (size_t)num_tiles * 8 * BLOCK16;
-                auto sum_chunk = [&](int c, uint32_t (&v)[32]) {
-                    float a[32];
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) a[i] = 0.f;
-                    for (uint32_t s2 = 0; s2 < nsplit; ++s2) {
-                        uint4 t[8];
-#pragma unroll
-                        for (int j = 0; j < 8; ++j) t[j] = __ldcg(all + s2 * slice_stride + (c * 8 + j) * 32);
+                    if (!first) {
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
                             const uint32_t w4[4] = {t[j].x, t[j].y, t[j].z, t[j].w};
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) a[4 * j + e] = s2 == 0 ? __uint_as_float(w4[e]) : __fadd_rn(a[4 * j + e], __uint_as_float(w4[e]));
+                            for (int e = 0; e < 4; ++e) v[4 * j + e] = __float_as_uint(__fadd_rn(__uint_as_float(w4[e]), __uint_as_float(v[4 * j + e])));
                         }
                     }
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(a[i]);
                 };
-                if constexpr (OUT == HB_OUT_SWIGLU) {
+                if (!last) {
+#pragma unroll 1
+                    for (int c = 0; c < PAIR_BN / 32; ++c) {
+                        uint32_t v[32];
+                        chunk(c, v);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) __stcg(buf + (c * 8 + j) * 32, make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
+                    }
+                } else if constexpr (OUT == HB_OUT_SWIGLU) {
 #pragma unroll 1
                     for (int c = 0; c < HALF / 32; ++c) {
                         uint32_t g[32], u[32];
-                        sum_chunk(c, g);
-                        sum_chunk(HALF / 32 + c, u);
+                        chunk(c, g);
+                        chunk(HALF / 32 + c, u);
                         store_chunk<OUT>(p, row, tn * HALF + c * 32, g, u);
                     }
                 } else {
 #pragma unroll 1
                     for (int c = 0; c < PAIR_BN / 32; ++c) {
                         uint32_t v[32];
-                        sum_chunk(c, v);
+                        chunk(c, v);
                         store_chunk<OUT>(p, row, tn * PAIR_BN + c * 32, v, v);
                     }
+                }
+                tc_fence_before();
+                if (!last) __threadfence();  // this lane's part of the running sum is out before the flag says so
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive_cluster(map_to_cta(smem_u32(&bars.tmem_empty[acc]), 0));
+                    const uint32_t next = last ? 0u : slice + 1u;  // the last slice leaves the flag at zero for the next launch
+                    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(next) : "memory");
                 }
                 continue;
             }
@@ -418,15 +433,15 @@ struct PairGemm : hb_kernel {
 
 }  // namespace
 
-// The f32 partial tiles of all split-K kernels of a context live in one scratch range (kernels on one stream run one
-// after the other), grown when a shape needs more: S x tiles blocks of 256 x 256 f32, for blocks of at most 1024 rows
-// (the form is for short blocks: few tiles for many SMs), and a counter per quarter of a CTA's half tile.
+// The running f32 sums of all split-K kernels of a context live in one scratch range (kernels on one stream run one
+// after the other), grown when a shape needs more: one block of 256 x 256 f32 per tile, for blocks of at most 1024 rows
+// (the form is for short blocks: few tiles for many SMs), and a flag per quarter of a CTA's half tile.
 static int ensure_split_scratch(hb_ctx* ctx, const hb_gemm_desc* d, uint32_t* rows_cap_out) {
     const uint32_t rows_cap = std::min<uint32_t>(std::max<uint32_t>(d->rows_max, 256u), 1024u);
     const uint32_t n_out = d->out == HB_OUT_SWIGLU ? d->n / 2 : d->n;
     const uint32_t cols_per_tile = d->out == HB_OUT_SWIGLU ? PAIR_BN / 2 : PAIR_BN;
     const size_t tiles = (size_t)((rows_cap + 255) / 256) * ((n_out + cols_per_tile - 1) / cols_per_tile);
-    const size_t need = tiles * d->split_k * 256 * 256 * sizeof(float), need_counters = tiles * 8 * sizeof(uint32_t);
+    const size_t need = tiles * 256 * 256 * sizeof(float), need_counters = tiles * 8 * sizeof(uint32_t);
     if (need > ctx->splitk_partial_bytes) {
         void* sc = nullptr;
         int r = hb_alloc(ctx, need, &sc);

@@ -170,7 +170,7 @@ int make_matvec(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out) {
         k->keys = static_cast<unsigned long long*>(pk);
         k->counter = reinterpret_cast<uint32_t*>(k->keys + (size_t)mcap * ARGMAX_SLOTS);
     }
-    if (smem > 48 * 1024) {
+    if (smem > 32 * 1024) {  // with the kernel's static shared memory the default limit of 48 KiB is near
         cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(fn), cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);
         if (e != cudaSuccess) return cuda_fail(ctx, e, "cudaFuncSetAttribute(max dynamic shared memory)");
     }

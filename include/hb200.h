@@ -193,9 +193,9 @@ typedef struct {
                             to ctl[0]. The tiles are walked group by group (m_first is ignored). */
     uint32_t split_k;    /* DENSE, cta_pair: S = 2..64 = every 256 x 256 tile is computed as S work items, one per equal slice
                             of K, so that a short block (few tiles) still gives every SM work at the tile size that reads
-                            the operands least often; an item leaves its f32 partial in scratch memory of the context and
-                            whoever completes a quarter of a CTA's half tile last adds the S partials in slice order
-                            (the same bits whoever is last) and applies the output mode. For blocks of at most 1024 rows. */
+                            the operands least often; the slices of a tile hand a running f32 sum from one to the next
+                            through scratch memory of the context (slice order, so the same bits whoever runs when) and the
+                            last one applies the output mode. For blocks of at most 1024 rows. */
 } hb_gemm_desc;
 int hb_gemm_get(hb_ctx* ctx, const hb_gemm_desc* desc, hb_kernel** out);
 

@@ -117,3 +117,29 @@ def test_moe_tiles_bound(hb200):
     L = hb200.lib()
     assert L.hb_moe_tiles(2048, 8, 256, 16) == 1280 and L.hb_moe_tiles(2048, 8, 256, 32) == 768 and L.hb_moe_tiles(2048, 8, 256, 64) == 512
     assert L.hb_moe_tiles(1, 1, 1, 16) == 2
+
+
+def test_integration_stub_declares_every_export(hb200):
+    """The Rust extern block of INTEGRATION.md is meant to be pasted as the -sys file: it must name every function
+    the header declares (and nothing the library does not export)."""
+    import os
+    import re
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    text = open(os.path.join(root, "INTEGRATION.md")).read()
+    block = text[text.index('extern "C" {') : text.index("/// Status ->")]
+    in_stub = set(re.findall(r"pub fn (hb_[a-z0-9_]+)\(", block))
+    header = open(os.path.join(root, "include", "hb200.h")).read()
+    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+    declared = set(re.findall(r"\b(hb_[a-z0-9_]+)\s*\(", header))
+    assert declared == set(hb200.EXPORTS), sorted(declared ^ set(hb200.EXPORTS))
+    assert in_stub == declared, sorted(in_stub ^ declared)
+    # the descriptors field for field
+    for struct, cls in (("hb_gemm_desc", hb200.GemmDesc), ("hb_matvec_desc", hb200.MatvecDesc)):
+        body = header[: header.index("} " + struct + ";")]
+        body = body[body.rindex("typedef struct {") :]
+        fields = re.findall(r"uint32_t\s+([a-z_0-9, ]+);", body)
+        names = [n.strip() for f in fields for n in f.split(",")]
+        assert names == [n for n, _ in cls._fields_], (struct, names)
+        rust = re.search(r"pub struct " + struct + r" \{(.*?)\}", text, flags=re.S).group(1)
+        assert re.findall(r"pub ([a-z_0-9]+): u32", rust) == names, struct
