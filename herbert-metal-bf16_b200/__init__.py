@@ -136,6 +136,7 @@ def lib() -> C.CDLL:
         "hb_moe_tiles": (u32, [u32, u32, u32, u32]),
         "hb_moe_gather_get": (ci, [vp, u32, u32, pvp]),
         "hb_moe_combine_get": (ci, [vp, u32, u32, u32, pvp]),
+        "hb_experts_matvec_get": (ci, [vp, u32, u32, u32, u32, u32, u32, u32, pvp]),
         "hb_epilogue_get": (ci, [vp, u32, u32, pvp]),
         "hb_gemm_static_scratch": (ci, [vp, u32, u32, u32, u32, Range, Range, Range]),
         "hb_kernel_name": (C.c_char_p, [vp]),
@@ -175,7 +176,7 @@ EXPORTS = [
     "hb_download", "hb_memset", "hb_sync", "hb_launch_count", "hb_event_new", "hb_event_free", "hb_lane_record", "hb_lane_wait", "hb_event_sync",
     "hb_upload_async", "hb_download_async", "hb_host_alloc", "hb_host_free", "hb_ipc_export", "hb_ipc_open", "hb_ipc_close",
     "hb_ep_dispatch_get", "hb_ep_plan_get", "hb_ep_return_get", "hb_ep_combine_get", "hb_tp_reduce_get", "hb_tp_sum_get", "hb_tp_sum_stream_get", "hb_dequant_q4_get", "hb_matvec_q4_get", "hb_matmul_q4_get", "hb_gemm_q4_get", "hb_select_gemm_q4", "hb_rmsnorm_get", "hb_argmax_get", "hb_moe_out_get", "hb_peer_sync_get", "hb_set_peer_wait_ms", "hb_gemm_get", "hb_matvec_get", "hb_swiglu_get", "hb_route_get",
-    "hb_moe_sort_get", "hb_moe_tiles", "hb_moe_gather_get", "hb_moe_combine_get", "hb_epilogue_get", "hb_gemm_static_scratch", "hb_kernel_name", "hb_launch", "hb_run", "hb_time", "hb_set_launch_overlap", "hb_graph_record", "hb_graph_launch", "hb_graph_time", "hb_graph_free",
+    "hb_moe_sort_get", "hb_moe_tiles", "hb_moe_gather_get", "hb_moe_combine_get", "hb_experts_matvec_get", "hb_epilogue_get", "hb_gemm_static_scratch", "hb_kernel_name", "hb_launch", "hb_run", "hb_time", "hb_set_launch_overlap", "hb_graph_record", "hb_graph_launch", "hb_graph_time", "hb_graph_free",
     "hb_tune_new", "hb_tune_free", "hb_tune_apply", "hb_tune_get", "hb_tune_summary", "hb_tune_gemm_timed", "hb_selector_new",
     "hb_selector_free", "hb_selector_log", "hb_selector_buckets", "hb_fill_random16", "hb_select_gemm", "hb_select_gate_up",
     "hb_select_matvec", "hb_select_matvec_x", "hb_select_axis", "hb_select_experts", "hb_selector_inject_wrong", "hb_check_rule",
@@ -461,6 +462,9 @@ class Context:
 
     def moe_gather(self, h, top_k) -> Kernel:
         return self._get(lib().hb_moe_gather_get, h, top_k)
+
+    def experts_matvec(self, k, n, top_k, experts, x_row, x_stride=0, rows_per_warp=2) -> Kernel:
+        return self._get(lib().hb_experts_matvec_get, k, n, top_k, experts, x_row, x_stride, rows_per_warp)
 
     def moe_combine(self, d, top_k, f32_sum=0) -> Kernel:
         return self._get(lib().hb_moe_combine_get, d, top_k, f32_sum)

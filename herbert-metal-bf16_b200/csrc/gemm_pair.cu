@@ -227,14 +227,25 @@ gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                         break;
                     }
                 }
-                // own accumulator chunk c plus the running sum (if any): v[] as f32 bits
-                auto chunk = [&](int c, uint32_t (&v)[32]) {
+                // own accumulator chunk c plus the running sum (if any): v[] as f32 bits. The running sum of the next
+                // chunk is asked for before this one is worked on (a chunk's loads take about a microsecond).
+                constexpr int NCHUNK = PAIR_BN / 32;
+                uint4 ahead[8];
+                auto ask = [&](int c) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) ahead[j] = __ldcg(buf + (c * 8 + j) * 32);
+                };
+                // the order the chunks are visited in: 0, 1, .. or, for the SwiGLU's last slice, gate and up chunks in turn
+                auto nth = [&](int i) { return (last && OUT == HB_OUT_SWIGLU) ? ((i & 1) ? HALF / 32 + (i >> 1) : (i >> 1)) : i; };
+                if (!first) ask(nth(0));
+                auto chunk = [&](int i, uint32_t (&v)[32]) {
                     uint4 t[8];
                     if (!first) {
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) t[j] = __ldcg(buf + (c * 8 + j) * 32);
+                        for (int j = 0; j < 8; ++j) t[j] = ahead[j];
+                        if (i + 1 < NCHUNK) ask(nth(i + 1));
                     }
-                    tmem_ld_32x32(t_addr + c * 32, v);
+                    tmem_ld_32x32(t_addr + nth(i) * 32, v);
                     tmem_ld_wait();
                     if (!first) {
 #pragma unroll
@@ -247,7 +258,7 @@ gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                 };
                 if (!last) {
 #pragma unroll 1
-                    for (int c = 0; c < PAIR_BN / 32; ++c) {
+                    for (int c = 0; c < NCHUNK; ++c) {
                         uint32_t v[32];
                         chunk(c, v);
 #pragma unroll
@@ -257,13 +268,13 @@ gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
 #pragma unroll 1
                     for (int c = 0; c < HALF / 32; ++c) {
                         uint32_t g[32], u[32];
-                        chunk(c, g);
-                        chunk(HALF / 32 + c, u);
+                        chunk(2 * c, g);
+                        chunk(2 * c + 1, u);
                         store_chunk<OUT>(p, row, tn * HALF + c * 32, g, u);
                     }
                 } else {
 #pragma unroll 1
-                    for (int c = 0; c < PAIR_BN / 32; ++c) {
+                    for (int c = 0; c < NCHUNK; ++c) {
                         uint32_t v[32];
                         chunk(c, v);
                         store_chunk<OUT>(p, row, tn * PAIR_BN + c * 32, v, v);

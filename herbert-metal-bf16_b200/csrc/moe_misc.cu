@@ -128,6 +128,56 @@ __global__ void moe_gather_kernel(const uint4* __restrict__ x, const uint32_t* _
     }
 }
 
+// ---------------------------------------------------------- experts_matvec
+// The projections of the top_k routed experts of every row, one matvec per (row, slot) (reference
+// src/metal/qwen_kernels.rs:1880-1990; the engine's moe.grouped = 0 and its decode step): slot s of row r (g = r * top_k
+// + s) multiplies the rows of expert route[r][s] in W ([experts * n][k]) with the input at r * x_row + s * x_stride
+// (x_stride 0: every slot of a row the same input) and writes y[g * n ..] in bf16. The arithmetic is the matvec's: 32
+// lanes stride K by chunks of 8, an f32 FMA chain per lane, the xor-butterfly sum, one rounding. A warp per R rows of W.
+template <int R>
+__global__ void __launch_bounds__(256) experts_matvec_kernel(const uint4* __restrict__ w, const uint4* __restrict__ x, uint16_t* __restrict__ y,
+                                                             const uint32_t* __restrict__ route, uint32_t pairs, uint32_t n, uint32_t k8, uint32_t top_k,
+                                                             uint32_t x_row8, uint32_t x_stride8) {
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t groups = (n + R - 1) / R;                 // row groups of one slot
+    const size_t total = (size_t)pairs * groups;
+    for (size_t item = (size_t)blockIdx.x * 8 + warp; item < total; item += (size_t)gridDim.x * 8) {
+        const uint32_t g = (uint32_t)(item / groups), row0 = (uint32_t)(item % groups) * R;
+        const uint32_t token = g / top_k, s_in = g % top_k;
+        const uint32_t expert = route[(size_t)token * 2 * top_k + s_in];
+        const uint4* xs = x + (size_t)token * x_row8 + (size_t)s_in * x_stride8;
+        const uint4* base[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) base[r] = w + ((size_t)expert * n + min(row0 + r, n - 1)) * k8;  // rows past the end read the last row
+        float acc[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) acc[r] = 0.f;
+        for (uint32_t c = lane; c < k8; c += 32) {
+            const uint4 xv = __ldg(xs + c);
+            const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const uint4 wv = __ldg(base[r] + c);
+                const uint32_t ww[4] = {wv.x, wv.y, wv.z, wv.w};
+                float a = acc[r];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    a = __fmaf_rn(__uint_as_float(ww[j] << 16), __uint_as_float(xw[j] << 16), a);
+                    a = __fmaf_rn(__uint_as_float(ww[j] & 0xffff0000u), __uint_as_float(xw[j] & 0xffff0000u), a);
+                }
+                acc[r] = a;
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            float a = acc[r];
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
+            if (lane == 0 && row0 + r < n) y[(size_t)g * n + row0 + r] = (uint16_t)f32_to_bf16(a);
+        }
+    }
+}
+
 // ------------------------------------------------------------- moe_combine
 // out[r][i] over the slots in route order: acc = bf16(acc + bf16(y*w)) (reference
 // src/metal/qwen_kernels.rs:2119-2161), or with F32SUM an f32 FMA chain rounded once.
@@ -244,6 +294,34 @@ struct MoeGather : hb_kernel {
     }
 };
 
+struct ExpertsMatvec : hb_kernel {
+    uint32_t k = 0, n = 0, top_k = 0, experts = 0, x_row = 0, x_stride = 0, rows = 0;
+    int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
+        if (na != 4) return fail(ctx, HB_INVALID, name + ": bindings are W, x, y, route");
+        if (m == 0) return fail(ctx, HB_INVALID, name + ": m = 0");
+        const uint32_t pairs = m * top_k;
+        const size_t xbytes = ((size_t)(m - 1) * x_row + (size_t)(top_k - 1) * x_stride + k) * 2;
+        if (!range_ok(a[0], (size_t)experts * n * k * 2) || !range_ok(a[1], xbytes) || !range_ok(a[2], (size_t)pairs * n * 2) || !range_ok(a[3], (size_t)m * 2 * top_k * 4))
+            return fail(ctx, HB_INVALID, name + ": a bound range is too small");
+        if ((reinterpret_cast<uintptr_t>(a[0].ptr) | reinterpret_cast<uintptr_t>(a[1].ptr)) & 15u) return fail(ctx, HB_INVALID, name + ": W and x must be 16-byte aligned");
+        const size_t items = (size_t)pairs * ((n + rows - 1) / rows);
+        const uint32_t grid = (uint32_t)std::max<size_t>(1, std::min<size_t>((items + 7) / 8, (size_t)ctx->sm_count * 16));
+        auto go = [&](auto fn) {
+            fn<<<grid, 256, 0, ctx->stream>>>(static_cast<const uint4*>(a[0].ptr), static_cast<const uint4*>(a[1].ptr), static_cast<uint16_t*>(a[2].ptr),
+                                              static_cast<const uint32_t*>(a[3].ptr), pairs, n, k / 8, top_k, x_row / 8, x_stride / 8);
+        };
+        switch (rows) {
+            case 1: go(experts_matvec_kernel<1>); break;
+            case 2: go(experts_matvec_kernel<2>); break;
+            case 4: go(experts_matvec_kernel<4>); break;
+            default: go(experts_matvec_kernel<8>); break;
+        }
+        HB_CUDA(ctx, cudaGetLastError());
+        ctx->launches++;
+        return HB_OK;
+    }
+};
+
 struct MoeCombine : hb_kernel {
     uint32_t d = 0, top_k = 0, f32_sum = 0;
     int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
@@ -302,6 +380,29 @@ int make_moe_gather(hb_ctx* ctx, uint32_t h, uint32_t top_k, hb_kernel** out) {
     k->nargs = 3;
     k->name = "moe_gather_" + std::to_string(h) + "_k" + std::to_string(top_k);
     *out = intern(ctx, std::move(k));
+    return HB_OK;
+}
+
+int make_experts_matvec(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t top_k, uint32_t experts, uint32_t x_row, uint32_t x_stride, uint32_t rows, hb_kernel** out) {
+    *out = nullptr;
+    if (k == 0 || n == 0 || top_k == 0 || experts == 0) return fail(ctx, HB_INVALID, "experts_matvec: k, n, top_k and experts must be positive");
+    if (k % 8 != 0 || x_row % 8 != 0 || x_stride % 8 != 0)  // the reference's own assertion (qwen_kernels.rs:1887)
+        return fail(ctx, HB_UNSUPPORTED, "experts_matvec: K = " + std::to_string(k) + ", x row " + std::to_string(x_row) + ", x stride " + std::to_string(x_stride) + ": not multiples of 8");
+    if (rows == 0) rows = 2;
+    if (rows != 1 && rows != 2 && rows != 4 && rows != 8) return fail(ctx, HB_UNSUPPORTED, "experts_matvec: rows per warp must be 1, 2, 4 or 8");
+    auto km = std::make_unique<ExpertsMatvec>();
+    km->k = k;
+    km->n = n;
+    km->top_k = top_k;
+    km->experts = experts;
+    km->x_row = x_row;
+    km->x_stride = x_stride;
+    km->rows = rows;
+    km->kind = 19;
+    km->nargs = 4;
+    km->name = "experts_matvec_" + std::to_string(k) + "x" + std::to_string(n) + "_k" + std::to_string(top_k) + "_e" + std::to_string(experts) + "_x" + std::to_string(x_row) + "_" +
+               std::to_string(x_stride) + "_r" + std::to_string(rows);
+    *out = intern(ctx, std::move(km));
     return HB_OK;
 }
 

@@ -571,6 +571,12 @@ int hb_ep_plan_get(hb_ctx* ctx, uint32_t experts, uint32_t world, uint32_t rank,
     return hb::make_ep_plan(ctx, experts, world, rank, bm, cap, out);
     HB_GUARD_END(ctx)
 }
+int hb_experts_matvec_get(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t top_k, uint32_t experts, uint32_t x_row, uint32_t x_stride, uint32_t rows_per_warp, hb_kernel** out) {
+    if (!ctx || !out) return fail(ctx, HB_INVALID, "hb_experts_matvec_get: bad argument");
+    HB_GUARD_BIND(ctx)
+    return hb::make_experts_matvec(ctx, k, n, top_k, experts, x_row, x_stride, rows_per_warp, out);
+    HB_GUARD_END(ctx)
+}
 int hb_ep_combine_get(hb_ctx* ctx, uint32_t h, uint32_t top_k, uint32_t world, hb_kernel** out) {
     if (!ctx || !out) return fail(ctx, HB_INVALID, "hb_ep_combine_get: bad argument");
     HB_GUARD_BIND(ctx)

@@ -823,6 +823,22 @@ int hb_select_experts(hb_selector* s, const hb_expert_io* io, hb_expert_pick* pi
         const hb_tune& t = s->tune;
         const uint32_t m = io->m, pairs = io->m * io->top_k;
         const uint32_t rows_max = std::max(m, t.get("prefill.block"));
+        if (t.get("moe.grouped") == 0) {
+            // moe.grouped = 0 (qwen.rs:2085-2088, 2725-2729): no sort, a matvec per (row, slot) against its expert's rows
+            if (!io->egu.ptr) return hb::fail(ctx, HB_INVALID, "hb_select_experts: moe.grouped = 0 needs the [gate | up] rows (io.egu)");
+            hb_kernel *gu = nullptr, *sw = nullptr, *dn = nullptr;
+            int r0;
+            if ((r0 = hb_experts_matvec_get(ctx, io->h, 2 * io->mi, io->top_k, io->experts, io->h, 0, 0, &gu)) != HB_OK) return r0;
+            if ((r0 = hb_swiglu_get(ctx, io->mi, &sw)) != HB_OK) return r0;
+            if ((r0 = hb_experts_matvec_get(ctx, io->mi, io->h, io->top_k, io->experts, io->top_k * io->mi, io->mi, 0, &dn)) != HB_OK) return r0;
+            pick->bm = 0;
+            pick->sort = nullptr;
+            pick->gather = nullptr;
+            pick->gate_up = gu;
+            pick->swiglu = sw;
+            pick->down = dn;
+            return HB_OK;
+        }
         std::vector<uint32_t> bms;
         if (t.moe_tile_set || !t.gemm_timed()) bms = {t.get("moe.tile")};  // qwen.rs:2352
         else bms = {16, 32, 64};

@@ -255,6 +255,13 @@ int hb_moe_sort_get(hb_ctx* ctx, uint32_t experts, uint32_t top_k, uint32_t rows
 uint32_t hb_moe_tiles(uint32_t rows_max, uint32_t top_k, uint32_t experts, uint32_t bm);
 /* moe_gather, src/metal/prefill.rs:579: XS[p] = X[list[p] / top_k]. Bindings: X, list, XS. m = token rows. */
 int hb_moe_gather_get(hb_ctx* ctx, uint32_t h, uint32_t top_k, hb_kernel** out);
+/* experts_matvec, src/metal/qwen_kernels.rs:1880-1990 (the engine's moe.grouped = 0, src/metal/qwen.rs:2085-2088,
+ * 2725-2729, and its decode step): one matvec per (row, slot) against the rows of the slot's expert in W
+ * ([experts * n][k]); slot s of row r reads its input at r * x_row + s * x_stride elements of x (x_stride 0: every slot
+ * the row's input) and writes y[(r * top_k + s) * n ..] in bf16, the matvec's arithmetic and bits.
+ * Bindings W, x, y, route. rows_per_warp 1, 2, 4 or 8 (0 = 2). */
+int hb_experts_matvec_get(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t top_k, uint32_t experts, uint32_t x_row, uint32_t x_stride, uint32_t rows_per_warp,
+                          hb_kernel** out);
 /* moe_combine, src/metal/qwen_kernels.rs:2119-2161: acc = bf16(acc + bf16(y*w)) over the slots in route order.
  * f32_sum = 1 is the variant that keeps the sum in f32 and rounds once. Bindings: y ([m][top_k][d]), route, out. */
 int hb_moe_combine_get(hb_ctx* ctx, uint32_t d, uint32_t top_k, uint32_t f32_sum, hb_kernel** out);
@@ -410,11 +417,11 @@ int hb_graph_free(hb_ctx* ctx, hb_graph* g);
 /* ---- the load-time selection loop (host library) ------------------------- */
 
 /* Tune, src/metal/qwen.rs:62-397. Acted on by the selection loop: gemm.auto gemm.mma gemm.tn gemm.mform gemm.mfirst
- * prefill.block moe.tile pf.fswi q4.fuse mv.auto mv.split mv.splitauto mv.persist mv.persists mv.cold auto.heat, and through
+ * prefill.block moe.grouped moe.tile pf.fswi q4.fuse mv.auto mv.split mv.splitauto mv.persist mv.persists mv.cold auto.heat, and through
  * hb_select_axis dec.auto dec.fnorm dec.fswi. Every other key of the reference is parsed, range-checked where the
  * reference checks it, stored and ignored: among the keys of this path that is gemm.simt (the layouts of a CUDA-core
- * GEMM that does not exist here), gemm.half (half-staged Q4 tiles) and moe.grouped (0 = experts_matvec per (row, slot),
- * src/metal/qwen_kernels.rs:1886, not built: the grouped GEMMs are the only expert form). */
+ * GEMM that does not exist here) and gemm.half (half-staged Q4 tiles: the tensor cores take bf16 here).
+ * moe.grouped = 0 makes hb_select_experts return the per-slot form (experts_matvec). */
 typedef struct hb_tune hb_tune;
 int hb_tune_new(hb_tune** out);
 void hb_tune_free(hb_tune* t);
@@ -486,7 +493,9 @@ typedef struct {
     hb_range xs;  /* optional: bf16 [m*top_k][h] */
 } hb_expert_io;
 typedef struct {
-    uint32_t bm;
+    uint32_t bm;              /* 0: moe.grouped = 0, the per-slot form: sort and gather are NULL, gate_up is experts_matvec over X
+                                 (bindings W, X, EGU, route; rows of [gate | up]), swiglu turns EGU into EHB, down is
+                                 experts_matvec over EHB (bindings W, EHB, EY, route); io.egu is then required */
     const hb_kernel* sort;    /* bindings route, list, tiles */
     const hb_kernel* gather;  /* NULL, or moe_gather: X, list, XS */
     const hb_kernel* gate_up; /* W, X (or XS), EHB (or EGU), list, tiles */

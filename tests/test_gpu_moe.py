@@ -178,3 +178,71 @@ def test_moe_layer_forms_agree_bitwise(ctx, hb200, oracle):
 def test_config5_full_size(ctx, hb200, oracle, merge_runs):
     # hidden 2048, 256 experts, top-8, expert intermediate 512, 2048 tokens
     moe_layer(ctx, hb200, oracle, 2048, 2048, 512, 256, 8, 16, merge_runs=merge_runs)
+
+
+@pytest.mark.parametrize("rows_per_warp", [1, 2, 4, 8])
+def test_experts_matvec_is_the_matvec_per_slot(ctx, hb200, oracle, rows_per_warp):
+    """experts_matvec (src/metal/qwen_kernels.rs:1880-1990; moe.grouped = 0 and the decode step): slot s of row r is the
+    one-row matvec, in the reference's lane order, of its input against its expert's rows: bit-exact with that matvec."""
+    m, h, mi, E, top_k = 5, 256, 136, 16, 4
+    x = oracle.normal((m, h), SEED_X, 1, 1.0)
+    wgu = oracle.normal((E * 2 * mi, h), SEED_W, 2, h**-0.5)
+    wd = oracle.normal((E * h, mi), SEED_W, 3, mi**-0.5)
+    route = oracle.route_topk(oracle.normal((m, E), SEED_ROUTER, 3, 1.0), top_k)
+    pairs = m * top_k
+    d_x, d_wgu, d_wd, d_r = ctx.to_device(x), ctx.to_device(wgu), ctx.to_device(wd), ctx.to_device(route)
+    d_egu, d_ehb, d_ey = ctx.alloc(pairs * 2 * mi * 2), ctx.alloc(pairs * mi * 2), ctx.alloc(pairs * h * 2)
+    k_gu = ctx.experts_matvec(h, 2 * mi, top_k, E, h, 0, rows_per_warp)          # every slot reads the row's x
+    k_dn = ctx.experts_matvec(mi, h, top_k, E, top_k * mi, mi, rows_per_warp)    # slot s reads its own SwiGLU row
+    assert k_gu.name.startswith("experts_matvec_")
+    k_gu(m, d_wgu, d_x, d_egu, d_r)
+    ctx.swiglu_rows(mi)(pairs, d_egu, d_ehb)
+    k_dn(m, d_wd, d_ehb, d_ey, d_r)
+    ctx.sync()
+    egu, ehb, ey = d_egu.download(np.uint16, (pairs, 2 * mi)), d_ehb.download(np.uint16, (pairs, mi)), d_ey.download(np.uint16, (pairs, h))
+    for g in range(pairs):
+        r, s = divmod(g, top_k)
+        e = int(route[r, s])
+        assert np.array_equal(egu[g], oracle.matvec_ref_order(x[r], np.ascontiguousarray(wgu[e * 2 * mi : (e + 1) * 2 * mi]))), g
+        assert np.array_equal(ey[g], oracle.matvec_ref_order(ehb[g], np.ascontiguousarray(wd[e * h : (e + 1) * h]))), g
+    assert np.array_equal(ehb, oracle.swiglu_slots(egu))
+    # against the grouped form of the same block, under the GEMM contract (the grouped GEMMs sum in another order)
+    lst, tiles = oracle.moe_sort(route, E, top_k, 16)
+    want = oracle.moe_down(oracle.swiglu_slots(oracle.moe_gate_up(x, wgu, lst, tiles, mi, top_k)), wd, lst, tiles, h)
+    c = oracle.compare(want, ey)
+    assert c.max_abs_err <= c.max_abs_ref / 64 and c.over_1ulp <= 0.02 * c.count
+    with pytest.raises(hb200.HbError):
+        ctx.experts_matvec(100, 64, 4, 8, 100)  # K not a multiple of 8 (the reference's assertion)
+
+
+def test_selection_moe_grouped_0_returns_the_per_slot_form(ctx, hb200, oracle):
+    m, h, mi, E, top_k = 32, 256, 128, 16, 4
+    pairs = m * top_k
+    x = oracle.normal((m, h), SEED_X, 1, 1.0)
+    wgu, wd = oracle.normal((E * 2 * mi, h), SEED_W, 2, h**-0.5), oracle.normal((E * h, mi), SEED_W, 3, mi**-0.5)
+    route = oracle.route_topk(oracle.normal((m, E), SEED_ROUTER, 3, 1.0), top_k)
+    d = {n_: ctx.to_device(a) for n_, a in dict(x=x, wgu=wgu, wd=wd, route=route).items()}
+    nt = hb200.lib().hb_moe_tiles(m, top_k, E, 16)
+    d_l, d_t, d_ehb, d_ey, d_egu, d_out = ctx.alloc(pairs * 4), ctx.alloc((1 + 3 * nt) * 4), ctx.alloc(pairs * mi * 2), ctx.alloc(pairs * h * 2), ctx.alloc(pairs * 2 * mi * 2), ctx.alloc(m * h * 2)
+    outs = []
+    for tune in ("moe.grouped=0,gemm.auto=0", "gemm.auto=0"):
+        sel = hb200.Selector(ctx, hb200.Tune(tune))
+        try:
+            pick = sel.experts(E, top_k, h, mi, m, d["route"], d_l, d_t, d["x"], d["wgu"], d["wd"], d_ehb, d_ey, egu=d_egu)
+            if "grouped=0" in tune:
+                assert pick["bm"] == 0 and pick["sort"] is None and pick["gate_up"].name.startswith("experts_matvec_") and pick["swiglu"] is not None
+                pick["gate_up"](m, d["wgu"], d["x"], d_egu, d["route"])
+                pick["swiglu"](pairs, d_egu, d_ehb)
+                pick["down"](m, d["wd"], d_ehb, d_ey, d["route"])
+            else:
+                assert pick["bm"] == 16 and pick["sort"] is not None
+                pick["sort"](m, d["route"], d_l, d_t)
+                pick["gate_up"](m, d["wgu"], d["x"], d_ehb, d_l, d_t)
+                pick["down"](m, d["wd"], d_ehb, d_ey, d_l, d_t)
+            ctx.moe_combine(h, top_k)(m, d_ey, d["route"], d_out)
+            ctx.sync()
+            outs.append(d_out.download(np.uint16, (m, h)))
+        finally:
+            sel.close()
+    c = oracle.compare(outs[1], outs[0])  # the two forms of the same block: the same values up to the order of the sums
+    assert c.max_abs_err <= c.max_abs_ref / 64 and c.over_1ulp <= 0.05 * c.count
