@@ -106,6 +106,7 @@ def lib() -> C.CDLL:
         "hb_tp_sum_stream_get": (ci, [vp, u32, u32, u32, u32, u32, u32, pvp]),
         "hb_dequant_q4_get": (ci, [vp, u32, u32, pvp]),
         "hb_matvec_q4_get": (ci, [vp, u32, u32, u32, u32, u32, pvp]),
+        "hb_matvec_q4_split_get": (ci, [vp, u32, u32, u32, u32, u32, u32, u32, pvp]),
         "hb_matmul_q4_get": (ci, [vp, u32, u32, u32, u32, u32, pvp]),
         "hb_gemm_q4_get": (ci, [vp, u32, u32, u32, u32, u32, u32, pvp]),
         "hb_select_gemm_q4": (ci, [vp, u32, u32, u32, Range, Range, Range, Range, Range, u32, pvp, C.POINTER(ci)]),
@@ -175,7 +176,7 @@ EXPORTS = [
     "hb_open", "hb_close", "hb_last_error", "hb_describe", "hb_set_stream", "hb_alloc", "hb_set_alloc_limit", "hb_upload",
     "hb_download", "hb_memset", "hb_sync", "hb_launch_count", "hb_event_new", "hb_event_free", "hb_lane_record", "hb_lane_wait", "hb_event_sync",
     "hb_upload_async", "hb_download_async", "hb_host_alloc", "hb_host_free", "hb_ipc_export", "hb_ipc_open", "hb_ipc_close",
-    "hb_ep_dispatch_get", "hb_ep_plan_get", "hb_ep_return_get", "hb_ep_combine_get", "hb_tp_reduce_get", "hb_tp_sum_get", "hb_tp_sum_stream_get", "hb_dequant_q4_get", "hb_matvec_q4_get", "hb_matmul_q4_get", "hb_gemm_q4_get", "hb_select_gemm_q4", "hb_rmsnorm_get", "hb_argmax_get", "hb_moe_out_get", "hb_peer_sync_get", "hb_set_peer_wait_ms", "hb_gemm_get", "hb_matvec_get", "hb_swiglu_get", "hb_route_get",
+    "hb_ep_dispatch_get", "hb_ep_plan_get", "hb_ep_return_get", "hb_ep_combine_get", "hb_tp_reduce_get", "hb_tp_sum_get", "hb_tp_sum_stream_get", "hb_dequant_q4_get", "hb_matvec_q4_get", "hb_matvec_q4_split_get", "hb_matmul_q4_get", "hb_gemm_q4_get", "hb_select_gemm_q4", "hb_rmsnorm_get", "hb_argmax_get", "hb_moe_out_get", "hb_peer_sync_get", "hb_set_peer_wait_ms", "hb_gemm_get", "hb_matvec_get", "hb_swiglu_get", "hb_route_get",
     "hb_moe_sort_get", "hb_moe_tiles", "hb_moe_gather_get", "hb_moe_combine_get", "hb_experts_matvec_get", "hb_epilogue_get", "hb_gemm_static_scratch", "hb_kernel_name", "hb_launch", "hb_run", "hb_time", "hb_set_launch_overlap", "hb_graph_record", "hb_graph_launch", "hb_graph_time", "hb_graph_free",
     "hb_tune_new", "hb_tune_free", "hb_tune_apply", "hb_tune_get", "hb_tune_summary", "hb_tune_gemm_timed", "hb_selector_new",
     "hb_selector_free", "hb_selector_log", "hb_selector_buckets", "hb_fill_random16", "hb_select_gemm", "hb_select_gate_up",
@@ -384,7 +385,9 @@ class Context:
     def dequant_q4(self, k, n) -> "Kernel":
         return self._get(lib().hb_dequant_q4_get, k, n)
 
-    def matvec_q4(self, k, n, out=OUT_BF16, rows_per_warp=2, masks=0) -> "Kernel":
+    def matvec_q4(self, k, n, out=OUT_BF16, rows_per_warp=2, masks=0, split=1, persist=0) -> "Kernel":
+        if split > 1 or persist:
+            return self._get(lib().hb_matvec_q4_split_get, k, n, out, rows_per_warp, masks, split, persist)
         return self._get(lib().hb_matvec_q4_get, k, n, out, rows_per_warp, masks)
 
     def matmul_q4(self, k, n, m, ldx=0, ldy=0) -> "Kernel":

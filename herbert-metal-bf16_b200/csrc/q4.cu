@@ -83,6 +83,7 @@ struct MatvecQ4Params {
     const uint4* x;
     void* y;
     uint32_t n, nblk, groups;
+    uint32_t split;  // warps sharing the blocks of one row group: block b to warp (b / 32) % split (matvec_q4_split, kernels.rs:472-500)
 };
 
 constexpr int Q4_THREADS = 256;
@@ -102,14 +103,18 @@ __global__ void __launch_bounds__(Q4_THREADS) matvec_q4_kernel(const MatvecQ4Par
     griddep_wait();  // x comes from the kernel before this one
     for (uint32_t j = threadIdx.x; j < p.nblk * 4; j += Q4_THREADS) q4_xs[(j & ~3u) + ((j & 3u) ^ ((j >> 3) & 3u))] = __ldg(p.x + j);
     __syncthreads();
-    for (uint32_t group = blockIdx.x * Q4_WARPS + warp; group < p.groups; group += gridDim.x * Q4_WARPS) {
+    __shared__ float red[Q4_WARPS][R];
+    const uint32_t split = p.split, slots = Q4_WARPS / split, slot = warp / split, piece = warp % split;
+    for (uint32_t g0 = blockIdx.x * slots; g0 < p.groups; g0 += gridDim.x * slots) {
+        const uint32_t group = min(g0 + slot, p.groups - 1);  // a slot past the end repeats the last group and writes nothing
+        const bool live = g0 + slot < p.groups;
         size_t base[R];
 #pragma unroll
         for (int r = 0; r < R; ++r) base[r] = (size_t)min(group * R + r, p.n - 1) * p.nblk;  // rows past the end read the last row
         float acc[R];
 #pragma unroll
         for (int r = 0; r < R; ++r) acc[r] = 0.f;
-        for (uint32_t b = lane; b < p.nblk; b += 32) {
+        for (uint32_t b = lane + 32u * piece; b < p.nblk; b += 32u * split) {
             uint4 wv[R];
             uint16_t dh[R];
 #pragma unroll
@@ -189,8 +194,25 @@ __global__ void __launch_bounds__(Q4_THREADS) matvec_q4_kernel(const MatvecQ4Par
             float a = acc[r];
 #pragma unroll
             for (int off = 16; off >= 1; off >>= 1) a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, off));
+            acc[r] = a;
+        }
+        if (split > 1) {  // the row's sum: its `split` partials in warp order (kernels.rs:916-928)
+            if (lane == 0) {
+#pragma unroll
+                for (int r = 0; r < R; ++r) red[warp][r] = acc[r];
+            }
+            __syncthreads();
+            if (piece == 0 && lane == 0) {
+#pragma unroll
+                for (int r = 0; r < R; ++r)
+                    for (uint32_t s2 = 1; s2 < split; ++s2) acc[r] = __fadd_rn(acc[r], red[warp + s2][r]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const float a = acc[r];
             const uint32_t row = group * R + r;
-            if (lane == 0 && row < p.n) {
+            if (live && piece == 0 && lane == 0 && row < p.n) {
                 if constexpr (OUT == HB_OUT_F32) reinterpret_cast<float*>(p.y)[row] = a;
                 else if constexpr (OUT == HB_OUT_BF16) reinterpret_cast<uint16_t*>(p.y)[row] = (uint16_t)f32_to_bf16(a);
                 else {
@@ -199,6 +221,7 @@ __global__ void __launch_bounds__(Q4_THREADS) matvec_q4_kernel(const MatvecQ4Par
                 }
             }
         }
+        if (split > 1) __syncthreads();  // `red` is read by the head before the next group writes it
     }
 }
 
@@ -350,7 +373,7 @@ q4_fn q4_rows(uint32_t rows, uint32_t out) {
 }
 
 struct MatvecQ4 : hb_kernel {
-    uint32_t k = 0, n = 0, out = 0, rows = 0;
+    uint32_t k = 0, n = 0, out = 0, rows = 0, split = 1, persist = 0;
     q4_fn fn = nullptr;
     int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
         if (na != 4) return fail(ctx, HB_INVALID, name + ": bindings are W (nibbles), x, y, scales (f16)");
@@ -367,7 +390,12 @@ struct MatvecQ4 : hb_kernel {
         p.n = n;
         p.nblk = k / 32;
         p.groups = (n + rows - 1) / rows;
-        const uint32_t grid = std::max(1u, std::min<uint32_t>((p.groups + Q4_WARPS - 1) / Q4_WARPS, (uint32_t)ctx->sm_count * 8));
+        p.split = split;
+        const uint32_t slots = Q4_WARPS / split;
+        // persist > 0: only that many blocks, each taking one row group after another (mv.persist); else as many as there are
+        // row groups, up to eight a multiprocessor
+        const uint32_t want = (p.groups + slots - 1) / slots;
+        const uint32_t grid = std::max(1u, std::min<uint32_t>(want, persist ? persist : (uint32_t)ctx->sm_count * 8));
         HB_CUDA(ctx, launch_kernel(ctx, true, fn, dim3(grid), dim3(Q4_THREADS), (size_t)k * 2, p));
         ctx->launches++;
         return HB_OK;
@@ -420,10 +448,12 @@ int make_dequant_q4(hb_ctx* ctx, uint32_t k, uint32_t n, hb_kernel** out) {
     return HB_OK;
 }
 
-int make_matvec_q4(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t out_mode, uint32_t rows, uint32_t masks, hb_kernel** out) {
+int make_matvec_q4(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t out_mode, uint32_t rows, uint32_t masks, uint32_t split, uint32_t persist, hb_kernel** out) {
     *out = nullptr;
     if (k == 0 || n == 0 || k % 32 != 0) return fail(ctx, HB_UNSUPPORTED, "Q4: K = " + std::to_string(k) + " is not a multiple of 32");
     if (rows == 0) rows = 2;
+    if (split == 0) split = 1;
+    if (split != 1 && split != 2 && split != 4 && split != 8) return fail(ctx, HB_UNSUPPORTED, "matvec_q4: split must be 1, 2, 4 or 8 (it divides the eight warps of a block)");
     q4_fn fn = masks ? q4_rows<true>(rows, out_mode) : q4_rows<false>(rows, out_mode);
     if (!fn) return fail(ctx, HB_UNSUPPORTED, "matvec_q4: rows per warp 1, 2 or 4; output Bf16, F32 or Residual");
     if ((size_t)k * 2 > ctx->smem_optin) return fail(ctx, HB_UNSUPPORTED, "matvec_q4: a row of K = " + std::to_string(k) + " does not fit in shared memory");
@@ -432,10 +462,13 @@ int make_matvec_q4(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t out_mode, uint3
     kn->n = n;
     kn->out = out_mode;
     kn->rows = rows;
+    kn->split = split;
+    kn->persist = persist;
     kn->fn = fn;
     kn->kind = 20;
     kn->nargs = 4;
-    kn->name = std::string(masks ? "matvec_q4s_" : "matvec_q4_") + std::to_string(k) + "x" + std::to_string(n) + "_" + out_tag(out_mode) + "_r" + std::to_string(rows);
+    kn->name = std::string(masks ? "matvec_q4s_" : "matvec_q4_") + std::to_string(k) + "x" + std::to_string(n) + "_" + out_tag(out_mode) + "_r" + std::to_string(rows) +
+               (split > 1 ? "_s" + std::to_string(split) : "") + (persist ? "_p" + std::to_string(persist) : "");
     if (hb_kernel* have = find(ctx, kn->name)) {
         *out = have;
         return HB_OK;
@@ -500,7 +533,18 @@ int hb_matvec_q4_get(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t out_mode, uin
     if (!ctx || !out) return hb::fail(ctx, HB_INVALID, "hb_matvec_q4_get: bad argument");
     try {
         hb::bind(ctx);
-        return hb::make_matvec_q4(ctx, k, n, out_mode, rows_per_warp, masks, out);
+        return hb::make_matvec_q4(ctx, k, n, out_mode, rows_per_warp, masks, 1, 0, out);
+    } catch (const std::exception& e) {
+        return hb::fail(ctx, HB_BACKEND, e.what());
+    }
+}
+
+int hb_matvec_q4_split_get(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t out_mode, uint32_t rows_per_warp, uint32_t masks, uint32_t split, uint32_t persist,
+                           hb_kernel** out) {
+    if (!ctx || !out) return hb::fail(ctx, HB_INVALID, "hb_matvec_q4_split_get: bad argument");
+    try {
+        hb::bind(ctx);
+        return hb::make_matvec_q4(ctx, k, n, out_mode, rows_per_warp, masks, split, persist, out);
     } catch (const std::exception& e) {
         return hb::fail(ctx, HB_BACKEND, e.what());
     }

@@ -287,6 +287,12 @@ int hb_dequant_q4_get(hb_ctx* ctx, uint32_t k, uint32_t n, hb_kernel** out);
  * 444-632, 1387-1424: y = out(W . x) for one activation row, the sums in the order of the form named (bit-exact with
  * either). rows_per_warp 1, 2 or 4 (0 = 2); out BF16, F32 or RESIDUAL. Bindings W, x, y, scales as there. */
 int hb_matvec_q4_get(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t out, uint32_t rows_per_warp, uint32_t masks, hb_kernel** res);
+/* matvec_q4_split, src/metal/kernels.rs:472-500, 896-928: the same product with the blocks of each row shared by `split`
+ * (1, 2, 4 or 8) warps of a block (block b to warp (b / 32) % split), their sums added in warp order: `split` times the
+ * warps on a matrix of few rows, the sums in another order (bit-exact with that order). persist > 0: only that many
+ * blocks, each taking one row group after another (mv.persist). Bindings as hb_matvec_q4_get. */
+int hb_matvec_q4_split_get(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t out, uint32_t rows_per_warp, uint32_t masks, uint32_t split, uint32_t persist,
+                           hb_kernel** res);
 /* matmul_q4, src/metal/kernels.rs:983-1071: Y[r] = bf16(W . X[r]) for the m (1..8) rows of a short block, row r of X at
  * r * ldx and of Y at r * ldy (bf16 elements; ldx a multiple of 8); each block of weights is decoded once for all
  * rows and every row is summed in matvec_q4's order (the decode step's bits). The kernel is built for m: launch it

@@ -579,6 +579,38 @@ void hbo_matvec_q4(const uint8_t* data, const uint16_t* scales, const uint16_t* 
     }
 }
 
+/* src/metal/kernels.rs:472-500, 896-928 (matvec_q4_split): the blocks of a row shared by `split` simdgroups (block b to
+ * simdgroup (b / 32) % split, lane b % 32), every simdgroup's lanes summed by the butterfly, the partials added in
+ * simdgroup order. split = 1 is hbo_matvec_q4. */
+void hbo_matvec_q4_split(const uint8_t* data, const uint16_t* scales, const uint16_t* x, void* y, int n, int k, int out, int split) {
+    const int nblk = k / 32;
+#pragma omp parallel for schedule(static)
+    for (int row = 0; row < n; ++row) {
+        float total = 0.0f;
+        for (int sub = 0; sub < split; ++sub) {
+            float lane[32];
+            for (int l = 0; l < 32; ++l) {
+                float acc = 0.0f;
+                for (int b = l + 32 * sub; b < nblk; b += 32 * split) {
+                    const uint8_t* blk = data + ((size_t)row * nblk + b) * 16;
+                    float part = 0.0f;
+                    for (int i = 0; i < 4; ++i)
+                        for (int byte = 0; byte < 4; ++byte) {
+                            int e0 = 8 * i + byte, e1 = 8 * i + 4 + byte;
+                            part = fmaf(q4_weight(blk, e0), hbo_bf16_to_f32(x[b * 32 + e0]), part);
+                            part = fmaf(q4_weight(blk, e1), hbo_bf16_to_f32(x[b * 32 + e1]), part);
+                        }
+                    acc = fmaf(f16_bits_to_f32(scales[(size_t)row * nblk + b]), part, acc);
+                }
+                lane[l] = acc;
+            }
+            const float s = butterfly_sum32(lane);
+            total = sub == 0 ? s : total + s;
+        }
+        store_out(y, (size_t)row, total, out);
+    }
+}
+
 /* src/metal/kernels.rs:983-1071 (matmul_q4): the m rows of a prefill block, each summed as matvec_q4 sums its one. */
 void hbo_matmul_q4(const uint8_t* data, const uint16_t* scales, const uint16_t* x, uint16_t* y, int n, int k, int m, int ldx, int ldy) {
     uint16_t* row = (uint16_t*)malloc((size_t)n * sizeof(uint16_t));

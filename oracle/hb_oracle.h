@@ -114,6 +114,9 @@ void hbo_q4_dequant(const uint8_t* data, const uint16_t* scales, int n, int k, u
  * part = fma(q_e, x_e, part) over e in the order 8i + b, 8i + 4 + b (i, b = 0..3), then acc = fma(d, part, acc); the
  * lanes are summed by the xor butterfly; the output mode as for the matvec (y holds the old values for RESIDUAL). */
 void hbo_matvec_q4(const uint8_t* data, const uint16_t* scales, const uint16_t* x, void* y, int n, int k, int out);
+/* src/metal/kernels.rs:472-500, 896-928 (matvec_q4_split): the same with the blocks of a row shared by `split`
+ * simdgroups (block b to simdgroup (b / 32) % split), each simdgroup's butterfly sum, the partials added in order. */
+void hbo_matvec_q4_split(const uint8_t* data, const uint16_t* scales, const uint16_t* x, void* y, int n, int k, int out, int split);
 /* src/metal/kernels.rs:983-1071 (matmul_q4): Y[r][.] = bf16(W . X[r]) for the m rows of a block, row r of X at r * ldx
  * and of Y at r * ldy (bf16 elements); each row's sum runs in matvec_q4's order, so a block gives the decode step's bits. */
 void hbo_matmul_q4(const uint8_t* data, const uint16_t* scales, const uint16_t* x, uint16_t* y, int n, int k, int m, int ldx, int ldy);

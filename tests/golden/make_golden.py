@@ -399,16 +399,20 @@ def q4_dequant(data, scales, n, k):
     return out.reshape(n, k)
 
 
-def q4_matvec(data, scales, x, n, k):
-    """kernels.rs:526-632 (rows = 1): lanes over blocks, FMA chains in the reference's element order, butterfly."""
+def q4_matvec(data, scales, x, n, k, split=1):
+    """kernels.rs:526-632 (rows = 1): lanes over blocks, FMA chains in the reference's element order, butterfly.
+    split > 1 (matvec_q4_split, kernels.rs:472-500, 896-928): block b to simdgroup (b / 32) % split, each simdgroup's
+    butterfly sum, the partials added in simdgroup order."""
     f = np.float32
     nblk = k // 32
     out = np.zeros(n, dtype=np.uint16)
     for row in range(n):
+      total = None
+      for sub in range(split):
         lanes = []
         for lane in range(32):
             acc = f(0.0)
-            for b in range(lane, nblk, 32):
+            for b in range(lane + 32 * sub, nblk, 32 * split):
                 blk = row * nblk + b
                 part = f(0.0)
                 for i in range(4):
@@ -417,7 +421,9 @@ def q4_matvec(data, scales, x, n, k):
                             part = fma_f32(q4_value(data, blk, e), widen(x[32 * b + e]), part)
                 acc = fma_f32(f(np.uint16(scales[blk]).view(np.float16)), part, acc)
             lanes.append(acc)
-        out[row] = rne_bf16(butterfly_sum(lanes))
+        s_ = butterfly_sum(lanes)
+        total = s_ if total is None else f(total + s_)
+      out[row] = rne_bf16(total)
     return out
 
 
@@ -550,6 +556,13 @@ def main():
     qX[1:, :] = fill_normal(2 * 104, 0x9E3779B9, 33, 1.0).reshape(2, 104)
     g["q4_X"] = qX
     g["q4_matmul"] = np.stack([q4_matvec(qd, qs, qX[r, :qk], qn, qk) for r in range(3)])
+    # matvec_q4_split: 80 blocks a row, so that with two and with four simdgroups a row every one of them has blocks
+    sn, sk = 3, 2560
+    sw = fill_normal(sn * sk, 0x2545F491, 34, 0.05).reshape(sn, sk)
+    sd, ss = q4_quantize(sw)
+    sx = fill_normal(sk, 0x9E3779B9, 35, 1.0)
+    g["q4split_w"], g["q4split_x"] = sw, sx
+    g["q4split_1"], g["q4split_2"], g["q4split_4"] = (q4_matvec(sd, ss, sx, sn, sk, sp) for sp in (1, 2, 4))
     np.savez_compressed(os.path.join(HERE, "golden.npz"), **g)
     print("wrote", os.path.join(HERE, "golden.npz"), "with", len(g), "arrays")
 

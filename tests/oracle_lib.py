@@ -96,6 +96,8 @@ def load(native: bool = False) -> C.CDLL:
     for f in (lib.hbo_matvec_q4, lib.hbo_matvec_q4s):
         f.restype = None
         f.argtypes = [_u8p, _u16p, _u16p, C.c_void_p, C.c_int, C.c_int, C.c_int]
+    lib.hbo_matvec_q4_split.restype = None
+    lib.hbo_matvec_q4_split.argtypes = [_u8p, _u16p, _u16p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_int]
     lib.hbo_check_1_64.restype = C.c_int
     lib.hbo_check_1_64.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_float)]
     lib.hbo_fill_normal.restype = None
@@ -269,9 +271,13 @@ class Oracle:
         self.lib.hbo_matmul_q4(data, scales, x, y, n, k, m, ldx, ldy)
         return y
 
-    def matvec_q4(self, data, scales, x, n, k, out=OUT_BF16, y0=None, masks=False):
+    def matvec_q4(self, data, scales, x, n, k, out=OUT_BF16, y0=None, masks=False, split=1):
         y = np.zeros(n, dtype=np.float32 if out == OUT_F32 else np.uint16) if y0 is None else np.ascontiguousarray(y0).copy()
-        (self.lib.hbo_matvec_q4s if masks else self.lib.hbo_matvec_q4)(data, scales, np.ascontiguousarray(x), y.ctypes.data, n, k, out)
+        if split > 1:
+            assert not masks
+            self.lib.hbo_matvec_q4_split(data, scales, np.ascontiguousarray(x), y.ctypes.data, n, k, out, split)
+        else:
+            (self.lib.hbo_matvec_q4s if masks else self.lib.hbo_matvec_q4)(data, scales, np.ascontiguousarray(x), y.ctypes.data, n, k, out)
         return y
 
     def check_1_64(self, ref, got):

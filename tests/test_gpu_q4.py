@@ -130,3 +130,38 @@ def test_q4_limits(ctx, hb200):
         with pytest.raises(hb200.HbError) as e:
             bad()
         assert e.value.status == hb200.UNSUPPORTED
+
+
+@pytest.mark.parametrize("split", [2, 4, 8])
+@pytest.mark.parametrize("rows", [1, 2, 4])
+def test_matvec_q4_split_and_persistent_forms(ctx, oracle, hb200, rows, split):
+    """matvec_q4_split (src/metal/kernels.rs:472-500): the blocks of a row shared by `split` warps, the partial sums added
+    in warp order - bit-exact with the oracle's statement of that order; a fixed grid (persist) changes no bit."""
+    for n, k in ((1001, 4096), (330, 1024), (5, 32), (64, 12288)):
+        w = oracle.normal((n, k), 6, n, k**-0.5)
+        x = oracle.normal((k,), 7, k, 1.0)
+        y0 = oracle.normal((n,), 8, n, 1.0)
+        data, scales = oracle.q4_quantize(w)
+        d_w, d_s, d_x = ctx.to_device(data), ctx.to_device(scales), ctx.to_device(x)
+        for out in (OUT_BF16, OUT_RESIDUAL):
+            start = y0 if out == OUT_RESIDUAL else np.zeros(n, dtype=np.uint16)
+            want = oracle.matvec_q4(data, scales, x, n, k, out, start, split=split)
+            for persist in (0, 3):
+                d_y = ctx.to_device(start) if n * 2 >= 16 else ctx.alloc(16).upload(start)
+                kern = ctx.matvec_q4(k, n, out, rows, 0, split=split, persist=persist)
+                assert f"_s{split}" in kern.name and (("_p3" in kern.name) == bool(persist))
+                kern(1, d_w, d_x, d_y, d_s)
+                ctx.sync()
+                assert np.array_equal(d_y.download(np.uint16, (n,)), want), (n, k, out, persist)
+    # the masks order with a split: the same form, held to the plain form under the contract
+    n, k = 1001, 4096
+    w = oracle.normal((n, k), 6, n, k**-0.5)
+    x = oracle.normal((k,), 7, k, 1.0)
+    data, scales = oracle.q4_quantize(w)
+    d_w, d_s, d_x, d_y = ctx.to_device(data), ctx.to_device(scales), ctx.to_device(x), ctx.alloc(n * 2)
+    ctx.matvec_q4(k, n, OUT_BF16, rows, 1, split=split)(1, d_w, d_x, d_y, d_s)
+    ctx.sync()
+    c = oracle.compare(oracle.matvec_q4(data, scales, x, n, k, OUT_BF16, masks=True), d_y.download(np.uint16, (n,)))
+    assert c.over_1ulp <= 2 and c.max_abs_err <= c.max_abs_ref / 64
+    with pytest.raises(hb200.HbError):
+        ctx.matvec_q4(k, n, OUT_BF16, 2, 0, split=3)

@@ -201,6 +201,11 @@ def test_q4_known_answers(oracle):
     assert np.array_equal(oracle.matvec_q4(data, scales, G["q4_x"], n, k, masks=True), G["q4s_matvec"])
     assert np.array_equal(oracle.matmul_q4(data, scales, G["q4_X"], n, k), G["q4_matmul"])
     assert np.array_equal(G["q4_matmul"][0], G["q4_matvec"])
+    # the split order (matvec_q4_split): the blocks of a row shared by 2 and by 4 simdgroups
+    sw, sx = G["q4split_w"], G["q4split_x"]
+    sd, ss = oracle.q4_quantize(sw)
+    for sp in (1, 2, 4):
+        assert np.array_equal(oracle.matvec_q4(sd, ss, sx, sw.shape[0], sw.shape[1], split=sp) if sp > 1 else oracle.matvec_q4(sd, ss, sx, sw.shape[0], sw.shape[1]), G[f"q4split_{sp}"]), sp
     # quantisation error is small against the weights
     f = lambda a: (a.astype(np.uint32) << 16).view(np.float32).astype(np.float64)
     assert np.abs(f(deq) - f(w)).max() <= np.abs(f(w)).max() / 7.5
