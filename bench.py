@@ -455,6 +455,8 @@ def summaries(extra: dict, pk: dict) -> dict:
     q4 = extra.get("matvec_q4_4096")
     if q4:
         out["matvec_q4"] = {k_: {"us": v["us"], "frac_hbm": v["frac_hbm"]} for k_, v in q4.items()}
+    if extra.get("gemm_q4_gate_up_4096x24576"):
+        out["gemm_q4"] = extra["gemm_q4_gate_up_4096x24576"]
     sh = {}
     for key, name in (("tp_ffn_27b_m2048", "tp_ffn_27b"), ("moe_ep_2048tok", "moe_ep")):
         v = extra.get(key)
@@ -676,6 +678,36 @@ def bench_extra(hb, ctx, sel, torch, dev, wrap, pk, rank, world, barrier, max_ov
         out["matvec_q4_4096"] = q4
     except Exception as e:
         out["q4_error"] = repr(e)
+    # the prefill GEMM from Q4_0 weights: dequant_q4 into a bf16 copy + the bf16 GEMM, against the GEMM that decodes
+    # while it stages (q4.fuse), at the gate/up shape of the layer, 2048 and 512 rows
+    try:
+        kq_, nq_ = HIDDEN, 2 * INTER
+        blocks = nq_ * kq_ // 32
+        wq_ = torch.randint(0, 256, (blocks * 16,), device=dev, dtype=torch.uint8, generator=g)
+        sq_ = (torch.rand(blocks, device=dev, generator=g) * 0.01 + 0.001).half()
+        wb_ = torch.zeros(nq_, kq_, device=dev, dtype=torch.bfloat16)
+        gus_ = torch.zeros(2048, nq_, device=dev, dtype=torch.bfloat16)
+        q4g = {}
+        for rows_q in (2048, 512, 128):
+            xq_ = torch.randn(rows_q, kq_, device=dev, generator=g).bfloat16()
+            hq_ = torch.zeros(rows_q, INTER, device=dev, dtype=torch.bfloat16)
+            k_dq = ctx.dequant_q4(kq_, nq_)
+            k_dq(1, wrap(wq_), wrap(sq_), wrap(wb_))
+            k_bf = sel.gate_up(kq_, INTER, wrap(wb_), wrap(xq_), wrap(gus_[:rows_q]), wrap(hq_), rows_q)
+            apart = [(k_dq, 1, wrap(wq_), wrap(sq_), wrap(wb_))]
+            apart += [(k_bf[0], rows_q, wrap(wb_), wrap(xq_), wrap(gus_[:rows_q])), (k_bf[1], rows_q, wrap(gus_[:rows_q]), wrap(hq_))] if len(k_bf) == 2 else [(k_bf[0], rows_q, wrap(wb_), wrap(xq_), wrap(hq_))]
+            res_q = {}
+            for name, ops_q in [("dequant+gemm", apart)] + [(f"fused128x{tn}", [(ctx.gemm_q4(kq_, nq_, 3, tile_n=tn, rows_max=rows_q), rows_q, wrap(wq_), wrap(xq_), wrap(hq_), wrap(sq_))]) for tn in (256, 128)]:
+                ctx.time(ops_q, 3)
+                barrier()
+                res_q[name] = max_over_ranks(ctx.time(ops_q, 10) / 10) * 1e6
+            best = min(res_q, key=res_q.get)
+            q4g[f"M{rows_q}"] = {"us": res_q, "picked": best, "tflops": 2.0 * rows_q * kq_ * nq_ / (res_q[best] * 1e-6) / 1e12,
+                                 "dequant_alone_us": ctx.time(apart[:1], 10) / 10 * 1e6}
+        out["gemm_q4_gate_up_4096x24576"] = q4g
+        del wq_, sq_, wb_, gus_
+    except Exception as e:
+        out["q4_gemm_error"] = repr(e)
     # the LM head with the greedy pick: projection + argmax as two kernels, and the projection that folds the argmax in
     idx = torch.zeros(8, device=dev, dtype=torch.int32)
     form = dict(rows_per_warp=2, split=2)
