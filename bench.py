@@ -116,6 +116,28 @@ class ClockSampler(threading.Thread):
         return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(s)}
 
 
+def bind_near_gpu(index: int):
+    """With several ranks on one host, every rank's page-locked buffers should live in the memory of the socket its GPU
+    hangs on: eight ranks copying through one socket's memory share its bandwidth and the link between the sockets.
+    Restricts this process to the CPUs NVML names as the GPU's own (a property of the process, not of the GPU), so
+    that the buffers it allocates afterwards are placed there. Returns the number of CPUs, or None when NVML cannot say."""
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        words = (os.cpu_count() + 63) // 64
+        mask = pynvml.nvmlDeviceGetCpuAffinity(h, words)
+        cpus = {64 * i + b for i, w in enumerate(mask) for b in range(64) if (w >> b) & 1}
+        cpus &= set(os.sched_getaffinity(0))
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return len(cpus)
+    except Exception:
+        pass
+    return None
+
+
 def dist_env():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -238,6 +260,7 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     dev = torch.device("cuda", local)
     torch.cuda.set_device(dev)
+    numa = bind_near_gpu(local) if world > 1 else None  # before any page-locked buffer is made: first touch places it
     ctx = hb.Context(local)
     pk = peaks()
     sampler = ClockSampler(local)
@@ -357,6 +380,7 @@ def main():
     barrier()
     e2e = {"value": STEP_FLOP * world / str_sec / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": io_bytes, "d2h_bytes_per_step": io_bytes,
            "ms_per_step": str_sec * 1e3, "steps": n_str, "mode": "streamed: copy lanes, 2 buffer sets, host reads every result",
+           "cpus_near_gpu": numa,
            "serial": {"value": STEP_FLOP * world / serial_sec / 1e12, "ms_per_step": serial_sec * 1e3, "steps": n_e2e}}
 
     per_gpu_tflops = value / world

@@ -52,6 +52,11 @@ struct EpParams {
     uint32_t* where;
     const uint64_t* peers_landed;  // [world] -> u32[world] on every rank
     uint32_t* ctl;                 // [0] dispatches completed (the step's number), [1] blocks finished
+    // direct form: every source owns a fixed region of `region` rows in every receive buffer (source s at s * region),
+    // so a source needs nobody else's counts to place its rows: no all-gather before the dispatch. The dispatch then
+    // also delivers its own offsets (`offs_all` is this rank's u32[experts + 1]) into row `rank` of every rank's table.
+    uint32_t region;
+    const uint64_t* peers_offs;    // [world] -> u32[world][experts + 1] on every rank
 };
 
 constexpr uint32_t EP_WHERE_NONE = 0xffffffffu;
@@ -59,14 +64,16 @@ constexpr uint32_t EP_WHERE_NONE = 0xffffffffu;
 // first[d], base[d] for this rank as a source, in shared memory.
 __device__ __forceinline__ void ep_source_tables(const EpParams& p, uint32_t* first, uint32_t* base) {
     const uint32_t stride = p.experts + 1;
+    const uint32_t* mine = p.region ? p.offs_all : p.offs_all + p.rank * stride;  // direct form: the binding is this rank's own row
     if (threadIdx.x < p.world) {
         const uint32_t d = threadIdx.x;
-        first[d] = p.offs_all[p.rank * stride + d * p.epr];
-        uint32_t b = 0;
-        for (uint32_t s = 0; s < p.rank; ++s) b += p.offs_all[s * stride + (d + 1) * p.epr] - p.offs_all[s * stride + d * p.epr];
+        first[d] = mine[d * p.epr];
+        uint32_t b = p.rank * p.region;
+        if (!p.region)
+            for (uint32_t s = 0; s < p.rank; ++s) b += p.offs_all[s * stride + (d + 1) * p.epr] - p.offs_all[s * stride + d * p.epr];
         base[d] = b;
     }
-    if (threadIdx.x == 0) first[p.world] = p.offs_all[p.rank * stride + p.experts];
+    if (threadIdx.x == 0) first[p.world] = mine[p.experts];
     __syncthreads();
 }
 
@@ -81,7 +88,7 @@ __global__ void __launch_bounds__(256) ep_move_kernel(const EpParams p) {
         uint32_t d = 0;
         while (d + 1 < p.world && pos >= first[d + 1]) ++d;
         const uint32_t r = base[d] + pos - first[d];
-        if (r >= p.cap) {  // the counts do not fit the buffers the host sized: report, move nothing
+        if (r >= p.cap || (p.region && pos - first[d] >= p.region)) {  // the counts do not fit the buffers the host sized: report, move nothing
             if (lane == 0) {
                 report(p.status, ST_BAD_TABLE, pos, r);
                 if (!RETURN && p.where) p.where[p.list[pos]] = EP_WHERE_NONE;
@@ -100,6 +107,14 @@ __global__ void __launch_bounds__(256) ep_move_kernel(const EpParams p) {
         }
     }
     if (!RETURN && p.peers_landed) {
+        // direct form: this rank's offsets into its row of every rank's table (the first blocks share the work)
+        if (p.region) {
+            const uint32_t words = p.experts + 1;
+            for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < p.world * words; i += gridDim.x * blockDim.x) {
+                const uint32_t d = i / words, e = i - d * words;
+                reinterpret_cast<uint32_t*>(p.peers_offs[d])[(size_t)p.rank * words + e] = p.offs_all[e];
+            }
+        }
         // this block's rows are out; the block that gets here last numbers the step and tells every rank
         __shared__ uint32_t last_s;
         __threadfence_system();
@@ -178,6 +193,7 @@ struct PlanParams {
     const uint32_t* landed;  // this rank's u32[world]
     const uint32_t* ctl;     // the dispatch's control words: [0] = the step's number
     long long wait_cycles;
+    uint32_t region;         // direct form: source s's rows start at s * region of the receive buffer
 };
 
 constexpr int PLAN_THREADS = 1024;
@@ -190,20 +206,24 @@ __global__ void __launch_bounds__(PLAN_THREADS) ep_plan_kernel(const PlanParams 
     uint32_t* recvbase = st + p.epr;       // [world] first receive row of source s
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t stride = p.experts + 1, e0 = p.rank * p.epr;
+    // (in the direct form the table was written by the other GPUs' dispatch kernels: read it from L2, not through a
+    // read-only path)
+    auto offs = [&](uint32_t i) { return __ldcg(p.offs_all + i); };
     if (p.landed && tid < p.world) {
         const uint32_t step = *reinterpret_cast<const volatile uint32_t*>(p.ctl);  // this rank's dispatch has numbered the step
         if (!wait_for_step(p.landed + tid, step, p.wait_cycles)) report(p.status, ST_WAIT_TIMEOUT, WHERE_PEER, 32u + tid);
     }
+    __syncthreads();  // (the waits above: the offsets the peers delivered are read below)
     if (tid == 0) {
         uint32_t b = 0;
         for (uint32_t s = 0; s < p.world; ++s) {
-            recvbase[s] = b;
-            b += p.offs_all[s * stride + e0 + p.epr] - p.offs_all[s * stride + e0];
+            recvbase[s] = p.region ? s * p.region : b;
+            b += offs(s * stride + e0 + p.epr) - offs(s * stride + e0);
         }
     }
     uint32_t total_e = 0;
     if (tid < p.epr)
-        for (uint32_t s = 0; s < p.world; ++s) total_e += p.offs_all[s * stride + e0 + tid + 1] - p.offs_all[s * stride + e0 + tid];
+        for (uint32_t s = 0; s < p.world; ++s) total_e += offs(s * stride + e0 + tid + 1) - offs(s * stride + e0 + tid);
     const uint32_t ntile_e = (total_e + p.bm - 1) / p.bm;
     uint32_t a = total_e, t = ntile_e;
     if (tid < p.epr) { sa[tid] = a; st[tid] = t; }
@@ -240,8 +260,8 @@ __global__ void __launch_bounds__(PLAN_THREADS) ep_plan_kernel(const PlanParams 
     for (uint32_t e = warp; e < p.epr; e += PLAN_THREADS / 32) {
         uint32_t pos = start[e];
         for (uint32_t s = 0; s < p.world; ++s) {
-            const uint32_t lo = p.offs_all[s * stride + e0 + e], hi = p.offs_all[s * stride + e0 + e + 1];
-            const uint32_t src0 = recvbase[s] + lo - p.offs_all[s * stride + e0];
+            const uint32_t lo = offs(s * stride + e0 + e), hi = offs(s * stride + e0 + e + 1);
+            const uint32_t src0 = recvbase[s] + lo - offs(s * stride + e0);
             for (uint32_t j = lane; j < hi - lo; j += 32) p.list[pos + j] = src0 + j;
             pos += hi - lo;
         }
@@ -255,15 +275,17 @@ uint32_t ep_grid(hb_ctx* ctx, uint32_t rows) { return std::max(1u, std::min<uint
 struct EpMove : hb_kernel {
     uint32_t h = 0, top_k = 0, experts = 0, world = 0, rank = 0, cap = 0;
     bool ret = false;
+    bool direct = false;  // every source a fixed region of every receive buffer: no all-gather before the dispatch
     int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
-        if (na != 4 && !(na == 7 && !ret))
-            return fail(ctx, HB_INVALID, name + (ret ? ": bindings are peers, EY, list, offsets" : ": bindings are X, peers, list, offsets[, where, peers_landed, ctl]"));
+        if (direct ? na != 8 : (na != 4 && !(na == 7 && !ret)))
+            return fail(ctx, HB_INVALID, name + (direct ? ": bindings are X, peers, list, offsets (this rank's), where, peers_landed, ctl, peers_offsets"
+                                                    : ret ? ": bindings are peers, EY, list, offsets" : ": bindings are X, peers, list, offsets[, where, peers_landed, ctl]"));
         if (m == 0) return fail(ctx, HB_INVALID, name + ": m = 0");
         const uint32_t pairs = m * top_k;
         const hb_range& rows = ret ? a[1] : a[0];
         const hb_range& peers = ret ? a[0] : a[1];
         if (!range_ok(rows, (size_t)(ret ? pairs : m) * h * 2) || !range_ok(peers, (size_t)world * 8) || !range_ok(a[2], (size_t)pairs * 4) ||
-            !range_ok(a[3], (size_t)world * (experts + 1) * 4))
+            !range_ok(a[3], (size_t)(direct ? 1 : world) * (experts + 1) * 4))
             return fail(ctx, HB_INVALID, name + ": a bound range is too small");
         if (reinterpret_cast<uintptr_t>(rows.ptr) & 15u) return fail(ctx, HB_INVALID, name + ": rows must be 16-byte aligned");
         EpParams p{};
@@ -280,12 +302,17 @@ struct EpMove : hb_kernel {
         p.epr = experts / world;
         p.cap = cap;
         p.status = ctx->status_dev;
-        if (na == 7) {
+        if (na >= 7) {
             if (cap > 0x0fffffffu || world > 16) return fail(ctx, HB_UNSUPPORTED, name + ": `where` packs the owner in 4 bits and the row in 28");
             if (!range_ok(a[4], (size_t)pairs * 4) || !range_ok(a[5], (size_t)world * 8) || !range_ok(a[6], 8)) return fail(ctx, HB_INVALID, name + ": a bound range is too small");
             p.where = static_cast<uint32_t*>(a[4].ptr);
             p.peers_landed = static_cast<const uint64_t*>(a[5].ptr);
             p.ctl = static_cast<uint32_t*>(a[6].ptr);
+        }
+        if (direct) {
+            if (!range_ok(a[7], (size_t)world * 8)) return fail(ctx, HB_INVALID, name + ": a bound range is too small");
+            p.region = cap / world;
+            p.peers_offs = static_cast<const uint64_t*>(a[7].ptr);
         }
         if (ret) ep_move_kernel<true><<<ep_grid(ctx, pairs), 256, 0, ctx->stream>>>(p);
         else ep_move_kernel<false><<<ep_grid(ctx, pairs), 256, 0, ctx->stream>>>(p);
@@ -297,8 +324,9 @@ struct EpMove : hb_kernel {
 
 struct EpPlan : hb_kernel {
     uint32_t experts = 0, world = 0, rank = 0, bm = 0, cap = 0;
+    bool direct = false;
     int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
-        if (na != 3 && na != 5) return fail(ctx, HB_INVALID, name + ": bindings are offsets, list, tiles[, landed, ctl]");
+        if (direct ? na != 5 : (na != 3 && na != 5)) return fail(ctx, HB_INVALID, name + (direct ? ": bindings are offsets, list, tiles, landed, ctl" : ": bindings are offsets, list, tiles[, landed, ctl]"));
         (void)m;
         const uint32_t epr = experts / world;
         if (!range_ok(a[0], (size_t)world * (experts + 1) * 4) || !range_ok(a[1], (size_t)cap * 4) ||
@@ -321,6 +349,7 @@ struct EpPlan : hb_kernel {
             p.ctl = static_cast<const uint32_t*>(a[4].ptr);
             p.wait_cycles = (long long)ctx->peer_wait_ms * 2000000ll;
         }
+        p.region = direct ? cap / world : 0;
         ep_plan_kernel<<<1, PLAN_THREADS, (3 * epr + world) * 4, ctx->stream>>>(p);
         HB_CUDA(ctx, cudaGetLastError());
         ctx->launches++;
@@ -360,8 +389,9 @@ bool ep_shape_ok(uint32_t experts, uint32_t world, uint32_t rank) {
 
 }  // namespace
 
-int make_ep_move(hb_ctx* ctx, bool ret, uint32_t h, uint32_t top_k, uint32_t experts, uint32_t world, uint32_t rank, uint32_t cap, hb_kernel** out) {
+int make_ep_move(hb_ctx* ctx, bool ret, uint32_t h, uint32_t top_k, uint32_t experts, uint32_t world, uint32_t rank, uint32_t cap, hb_kernel** out, bool direct) {
     *out = nullptr;
+    if (direct && (ret || cap % world != 0)) return fail(ctx, HB_UNSUPPORTED, "ep dispatch (direct): the buffers' rows must divide by the number of ranks");
     if (!ep_shape_ok(experts, world, rank) || h == 0 || h % 8 != 0 || top_k == 0 || cap == 0)
         return fail(ctx, HB_UNSUPPORTED, "ep exchange: 1..16 ranks dividing at most 1024 experts, h a positive multiple of 8");
     auto k = std::make_unique<EpMove>();
@@ -372,9 +402,10 @@ int make_ep_move(hb_ctx* ctx, bool ret, uint32_t h, uint32_t top_k, uint32_t exp
     k->rank = rank;
     k->cap = cap;
     k->ret = ret;
+    k->direct = direct;
     k->kind = ret ? 12 : 11;
-    k->nargs = 4;
-    k->name = std::string(ret ? "ep_return_" : "ep_dispatch_") + std::to_string(h) + "_k" + std::to_string(top_k) + "_e" + std::to_string(experts) + "_r" +
+    k->nargs = direct ? 8 : 4;
+    k->name = std::string(ret ? "ep_return_" : direct ? "ep_dispatch_direct_" : "ep_dispatch_") + std::to_string(h) + "_k" + std::to_string(top_k) + "_e" + std::to_string(experts) + "_r" +
               std::to_string(rank) + "of" + std::to_string(world) + "_c" + std::to_string(cap);
     *out = intern(ctx, std::move(k));
     return HB_OK;
@@ -394,8 +425,9 @@ int make_ep_combine(hb_ctx* ctx, uint32_t h, uint32_t top_k, uint32_t world, hb_
     return HB_OK;
 }
 
-int make_ep_plan(hb_ctx* ctx, uint32_t experts, uint32_t world, uint32_t rank, uint32_t bm, uint32_t cap, hb_kernel** out) {
+int make_ep_plan(hb_ctx* ctx, uint32_t experts, uint32_t world, uint32_t rank, uint32_t bm, uint32_t cap, hb_kernel** out, bool direct) {
     *out = nullptr;
+    if (direct && cap % world != 0) return fail(ctx, HB_UNSUPPORTED, "ep plan (direct): the buffers' rows must divide by the number of ranks");
     if (!ep_shape_ok(experts, world, rank) || cap == 0) return fail(ctx, HB_UNSUPPORTED, "ep plan: 1..16 ranks dividing at most 1024 experts");
     if (bm != 16 && bm != 32 && bm != 64) return fail(ctx, HB_UNSUPPORTED, "ep plan: tile rows 16, 32 or 64");
     auto k = std::make_unique<EpPlan>();
@@ -404,9 +436,10 @@ int make_ep_plan(hb_ctx* ctx, uint32_t experts, uint32_t world, uint32_t rank, u
     k->rank = rank;
     k->bm = bm;
     k->cap = cap;
+    k->direct = direct;
     k->kind = 13;
-    k->nargs = 3;
-    k->name = "ep_plan_e" + std::to_string(experts) + "_r" + std::to_string(rank) + "of" + std::to_string(world) + "_m" + std::to_string(bm) + "_c" + std::to_string(cap);
+    k->nargs = direct ? 5 : 3;
+    k->name = std::string(direct ? "ep_plan_direct_e" : "ep_plan_e") + std::to_string(experts) + "_r" + std::to_string(rank) + "of" + std::to_string(world) + "_m" + std::to_string(bm) + "_c" + std::to_string(cap);
     *out = intern(ctx, std::move(k));
     return HB_OK;
 }

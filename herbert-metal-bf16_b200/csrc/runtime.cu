@@ -571,6 +571,18 @@ int hb_ep_plan_get(hb_ctx* ctx, uint32_t experts, uint32_t world, uint32_t rank,
     return hb::make_ep_plan(ctx, experts, world, rank, bm, cap, out);
     HB_GUARD_END(ctx)
 }
+int hb_ep_dispatch_direct_get(hb_ctx* ctx, uint32_t h, uint32_t top_k, uint32_t experts, uint32_t world, uint32_t rank, uint32_t cap, hb_kernel** out) {
+    if (!ctx || !out) return fail(ctx, HB_INVALID, "hb_ep_dispatch_direct_get: bad argument");
+    HB_GUARD_BIND(ctx)
+    return hb::make_ep_move(ctx, false, h, top_k, experts, world, rank, cap, out, true);
+    HB_GUARD_END(ctx)
+}
+int hb_ep_plan_direct_get(hb_ctx* ctx, uint32_t experts, uint32_t world, uint32_t rank, uint32_t bm, uint32_t cap, hb_kernel** out) {
+    if (!ctx || !out) return fail(ctx, HB_INVALID, "hb_ep_plan_direct_get: bad argument");
+    HB_GUARD_BIND(ctx)
+    return hb::make_ep_plan(ctx, experts, world, rank, bm, cap, out, true);
+    HB_GUARD_END(ctx)
+}
 int hb_experts_matvec_get(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t top_k, uint32_t experts, uint32_t x_row, uint32_t x_stride, uint32_t rows_per_warp, hb_kernel** out) {
     if (!ctx || !out) return fail(ctx, HB_INVALID, "hb_experts_matvec_get: bad argument");
     HB_GUARD_BIND(ctx)

@@ -218,30 +218,32 @@ class GpuBackend:
 # dispatch (stores into the owners' receive buffers), barrier, plan + gate/up + down on the received rows,
 # barrier, return (loads from the owners' output buffers), combine.
 
-def ep_positions_np(offs_all, rank: int, epr: int):
+def ep_positions_np(offs_all, rank: int, epr: int, region: int = 0):
     """Host mirror of the dispatch / return index arithmetic: for every sorted position p of `rank`, the
-    destination rank and the row in that rank's receive buffer. offs_all: int array [world][experts + 1]."""
+    destination rank and the row in that rank's receive buffer. offs_all: int array [world][experts + 1].
+    region > 0: the direct form, every source's rows from row source * region of every buffer."""
     import numpy as np
 
     offs_all = np.asarray(offs_all, dtype=np.int64)
     world = offs_all.shape[0]
     pairs = int(offs_all[rank, -1])
     first = np.array([offs_all[rank, d * epr] for d in range(world)] + [pairs])
-    base = np.array([sum(int(offs_all[s, (d + 1) * epr] - offs_all[s, d * epr]) for s in range(rank)) for d in range(world)])
+    base = np.array([rank * region if region else sum(int(offs_all[s, (d + 1) * epr] - offs_all[s, d * epr]) for s in range(rank)) for d in range(world)])
     p = np.arange(pairs)
     d = np.searchsorted(first[1:], p, side="right")
     return d, base[d] + p - first[d]
 
 
-def ep_plan_np(offs_all, rank: int, epr: int, bm: int):
-    """Host mirror of the plan kernel: (list, tiles) of `rank`'s experts over its receive buffer."""
+def ep_plan_np(offs_all, rank: int, epr: int, bm: int, region: int = 0):
+    """Host mirror of the plan kernel: (list, tiles) of `rank`'s experts over its receive buffer (region > 0: the
+    direct form, source s's rows from row s * region)."""
     import numpy as np
 
     offs_all = np.asarray(offs_all, dtype=np.int64)
     world = offs_all.shape[0]
     e0 = rank * epr
     n_from = [int(offs_all[s, e0 + epr] - offs_all[s, e0]) for s in range(world)]
-    recvbase = np.concatenate([[0], np.cumsum(n_from)])
+    recvbase = np.arange(world + 1) * region if region else np.concatenate([[0], np.cumsum(n_from)])
     lst, tiles = [], []
     for e in range(epr):
         start = len(lst)
@@ -382,14 +384,17 @@ class EpPeer:
     fused (the default): the dispatch notes where every pair's output row will be and tells the other ranks when its
     rows have landed; the plan waits for that itself (no barrier kernel between dispatch and expert GEMMs); the return
     and the combine are one kernel that reads every slot's output row from its owner (no EY written and re-read).
-    fused = False: dispatch, barrier, plan, GEMMs, barrier, return into EY, combine.
+    direct (the default with fused, when cap divides by the number of ranks): every source owns a fixed region of every
+    receive buffer, so nobody needs anybody's counts to place rows and the all-gather of the offsets before the dispatch
+    falls away (the dispatch delivers the offsets itself): route, sort, dispatch, plan, two GEMMs, barrier, combine.
+    fused = False: all-gather, dispatch, barrier, plan, GEMMs, barrier, return into EY, combine.
     With one rank there is nothing to exchange and the step is the plain block (route, sort, the expert GEMMs gathering
     from X and scattering into EY, combine) unless plain_when_alone is False (the exchange kernels with one rank, as the
     tests run them).
     """
 
     def __init__(self, hb, ctx, rank: int, world: int, rows: int, h: int, mi: int, experts: int, top_k: int, bm: int = 64, cap: int | None = None,
-                 device=None, fused: bool = True, plain_when_alone: bool = True):
+                 device=None, fused: bool = True, plain_when_alone: bool = True, direct: bool | None = None):
         assert experts % world == 0
         self.hb, self.ctx, self.rank, self.world = hb, ctx, rank, world
         self.rows, self.h, self.mi, self.experts, self.top_k, self.bm = rows, h, mi, experts, top_k, bm
@@ -398,6 +403,7 @@ class EpPeer:
         self.plain = world == 1 and plain_when_alone
         self.fused = fused and not self.plain
         self.cap = cap if cap is not None else self.pairs * world
+        self.direct = self.fused and self.cap % world == 0 if direct is None else bool(direct) and self.fused
         dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         i32 = dict(device=dev, dtype=torch.int32)
         # shared with the peers: the rows this rank receives and the outputs of its experts, both [cap][h] bf16, and
@@ -433,8 +439,8 @@ class EpPeer:
             self.rtiles = torch.zeros(1 + 3 * hb.lib().hb_moe_tiles(self.cap, 1, self.epr, bm), **i32)
             self.ehb = torch.zeros(self.cap, mi, device=dev, dtype=torch.bfloat16)
             kw = dict(rows_max=self.cap, top_k=1, experts=self.epr, bm=bm, merge_runs=1)
-            self.k_dispatch = ctx.ep_dispatch(h, top_k, experts, world, rank, self.cap)
-            self.k_plan = ctx.ep_plan(experts, world, rank, bm, self.cap)
+            self.k_dispatch = ctx.ep_dispatch(h, top_k, experts, world, rank, self.cap, direct=self.direct)
+            self.k_plan = ctx.ep_plan(experts, world, rank, bm, self.cap, direct=self.direct)
             self.k_gate_up = ctx.gemm(h, 2 * mi, OUT_SWIGLU, rows_mode=hb.ROWS_GATHER, **kw)
             self.k_down = ctx.gemm(mi, h, OUT_BF16, rows_mode=hb.ROWS_SCATTER, **kw)
             if self.fused:
@@ -476,9 +482,11 @@ class EpPeer:
     def phase_dispatch(self) -> None:  # offs_all holds every rank's offsets
         if self.plain:
             return
-        args = [self._w(self.x), self.pb.table("recv"), self._w(self.list), self._w(self.offs_all)]
+        args = [self._w(self.x), self.pb.table("recv"), self._w(self.list), self._w(self.offs if self.direct else self.offs_all)]
         if self.fused:
             args += [self._w(self.where), self.pb.table("landed"), self.ctl]
+        if self.direct:  # the dispatch delivers this rank's offsets into every rank's table itself
+            args += [self.pb.table("offs1" if self.parity else "offs0")]
         self.emit(self.k_dispatch, self.rows, *args)
 
     def phase_experts(self, wgu_local, wd_local) -> None:  # every rank's dispatch has finished (fused: the plan sees to that)
@@ -541,7 +549,9 @@ def _ep_step_body(state: EpPeer, x_local, scores_local, wgu_local, wd_local, gro
     if state.plain:
         state.phase_experts(wgu_local, wd_local)
         return state.phase_return()
-    if not multi:
+    if state.direct:
+        pass  # no all-gather: every source has its own region of the buffers, and the dispatch delivers the offsets
+    elif not multi:
         state.offs_all[0].copy_(state.offs)
     elif nccl_sync:
         dist.all_gather_into_tensor(state.offs_all.view(-1), state.offs, group=group)

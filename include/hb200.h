@@ -334,6 +334,17 @@ int hb_ep_dispatch_get(hb_ctx* ctx, uint32_t h, uint32_t top_k, uint32_t experts
 int hb_ep_plan_get(hb_ctx* ctx, uint32_t experts, uint32_t world, uint32_t rank, uint32_t bm, uint32_t cap, hb_kernel** out);
 int hb_ep_return_get(hb_ctx* ctx, uint32_t h, uint32_t top_k, uint32_t experts, uint32_t world, uint32_t rank, uint32_t cap, hb_kernel** out);
 int hb_ep_combine_get(hb_ctx* ctx, uint32_t h, uint32_t top_k, uint32_t world, hb_kernel** out);
+/* The direct form of dispatch and plan: every source owns a fixed region of cap / world rows in every rank's receive
+ * and output buffers (source s at row s * cap / world), so a source needs nobody else's counts to place its rows and
+ * the all-gather of the offsets before the dispatch falls away. The dispatch delivers this rank's offsets itself, into
+ * row `rank` of every rank's table, before it flags its landing; the plan waits for the flags and lays the expert tiles
+ * over the regions. A step is then route, sort, dispatch, plan, the two expert GEMMs, one barrier, combine.
+ * dispatch bindings: X, peers, list, offsets (this rank's u32[experts + 1], as the sort wrote them), where,
+ *   peers_landed, ctl, peers_offsets (u64[world]: the addresses of every rank's table u32[world][experts + 1]).
+ * plan bindings: offsets_all (this rank's table), list, tiles, landed, ctl. cap must divide by world; a source that has
+ * more than cap / world rows for one rank is reported through the status words. */
+int hb_ep_dispatch_direct_get(hb_ctx* ctx, uint32_t h, uint32_t top_k, uint32_t experts, uint32_t world, uint32_t rank, uint32_t cap, hb_kernel** out);
+int hb_ep_plan_direct_get(hb_ctx* ctx, uint32_t experts, uint32_t world, uint32_t rank, uint32_t bm, uint32_t cap, hb_kernel** out);
 /* The output mode (BF16 or RESIDUAL: store, src/metal/kernels.rs:217-234) applied to an f32 accumulator array
  * [m][n] that was completed outside a GEMM: a row-parallel projection sums f32 partial products across GPUs
  * (hb_gemm_get with HB_OUT_F32 on each, then an all-reduce) and rounds once afterwards. Bindings: acc, y. */

@@ -14,9 +14,12 @@ def offsets_of(route, experts, top_k):
     return np.concatenate([[0], np.cumsum(counts)]).astype(np.uint32)
 
 
+@pytest.mark.parametrize("direct", [False, True], ids=["packed", "direct"])
 @pytest.mark.parametrize("world", [1, 2, 4, 8])
 @pytest.mark.parametrize("rows,experts,top_k,bm", [(64, 32, 4, 16), (96, 64, 8, 32), (40, 8, 2, 64)])
-def test_exchange_reproduces_the_single_sort(world, rows, experts, top_k, bm):
+def test_exchange_reproduces_the_single_sort(world, rows, experts, top_k, bm, direct):
+    # packed: a source's rows follow those of the sources before it (needs everybody's counts: the all-gather);
+    # direct: every source has its own region of every receive buffer
     if experts % world or rows % world:
         pytest.skip("does not divide")
     d, o = load_dist(), Oracle()
@@ -34,9 +37,11 @@ def test_exchange_reproduces_the_single_sort(world, rows, experts, top_k, bm):
     offs_all = np.stack(offs)
     # dispatch: the global pair id of what lands in every receive-buffer row
     cap = rows * top_k
+    region = cap // world if direct else 0
     recv = [np.full(cap, -1, dtype=np.int64) for _ in range(world)]
     for r in range(world):
-        dest, row = d.ep_positions_np(offs_all, r, epr)
+        dest, row = d.ep_positions_np(offs_all, r, epr, region)
+        assert not direct or ((row >= r * region) & (row < (r + 1) * region)).all()
         assert len(dest) == rpr * top_k
         for p in range(len(dest)):
             assert recv[dest[p]][row[p]] == -1, "two pairs in one receive row"
@@ -45,9 +50,9 @@ def test_exchange_reproduces_the_single_sort(world, rows, experts, top_k, bm):
     # plan: the owners' lists, mapped back to global pair ids and concatenated, are the single sort
     got, tiles_rows = [], []
     for r in range(world):
-        lst, tiles = d.ep_plan_np(offs_all, r, epr, bm)
+        lst, tiles = d.ep_plan_np(offs_all, r, epr, bm, region)
         n_recv = int((recv[r] >= 0).sum())
-        assert len(lst) == n_recv and sorted(lst.tolist()) == list(range(n_recv))
+        assert len(lst) == n_recv and sorted(lst.tolist()) == np.flatnonzero(recv[r] >= 0).tolist()
         got.extend(recv[r][lst].tolist())
         for t in range(int(tiles[0])):
             e, first, n = (int(v) for v in tiles[1 + 3 * t : 4 + 3 * t])

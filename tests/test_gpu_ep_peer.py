@@ -68,6 +68,7 @@ def test_one_rank_matches_the_plain_block(env, hb200, oracle, fused):
     assert np.array_equal(st.offs.cpu().numpy(), np.concatenate([[0], np.cumsum(counts)]))
     # one rank: the receive buffer holds the pairs in sorted order, so the plan's list is the identity
     n = int(tiles[0])
+    assert st.direct == fused
     assert np.array_equal(st.rlist.cpu().numpy()[: len(lst)], np.arange(len(lst)))
     assert np.array_equal(st.rtiles.cpu().numpy().view(np.uint32)[: 1 + 3 * n], tiles[: 1 + 3 * n])
     # against the plain block of kernels (route, sort, gather GEMM, scatter GEMM, combine) on the same inputs
@@ -118,7 +119,7 @@ def test_emulated_ranks_equal_one_rank(env, hb200, oracle, world, fused):
     # the device plan equals its host mirror
     oa = offs_all.cpu().numpy()
     for r, st in enumerate(ranks):
-        lst, tiles = d.ep_plan_np(oa, r, epr, s["bm"])
+        lst, tiles = d.ep_plan_np(oa, r, epr, s["bm"], region=st.cap // world if st.direct else 0)
         assert np.array_equal(st.rlist.cpu().numpy()[: len(lst)].astype(np.uint32), lst)
         assert np.array_equal(st.rtiles.cpu().numpy().view(np.uint32)[: len(tiles)], tiles)
 
