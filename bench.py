@@ -1011,17 +1011,20 @@ def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks)
                 # (the step's kernels recorded once and replayed with one call; also launched one by one from the host)
                 sec = timed(lambda: D.tp_ffn_peer(tp, x, wgu_l, wd_l, recorded=True), 3, 10)
                 sec_loop = timed(lambda: D.tp_ffn_peer(tp, x, wgu_l, wd_l), 3, 10) if world > 1 else sec
-                sec_pull = sec
-                if world > 1:  # the pull form: the partial stays local, tp_reduce loads the blocks it sums from the peers
-                    tpl = D.TpPeer(hb, ctx, rank, world, m, h, push=False)
+                # the other two forms of the exchange over the same kernels: the partial stays local and tp_reduce pulls the
+                # blocks it sums from the peers; the GEMM flags finished row groups and the sum runs beside it
+                other_forms = {}
+                for mode_ in (("pull", "stream") if world > 1 else ()):
+                    tpl = D.TpPeer(hb, ctx, rank, world, m, h, mode=mode_)
                     D.tp_peer_connect(tpl)
                     tpl.set_y(y)
-                    got_pull = D.tp_ffn_peer(tpl, x, wgu_l, wd_l).clone()
-                    sec_pull = timed(lambda: D.tp_ffn_peer(tpl, x, wgu_l, wd_l, recorded=True), 3, 10)
-                    if not torch.equal(got_pull, got):
-                        raise RuntimeError("tp_ffn: the push and the pull form differ")
+                    got_other = D.tp_ffn_peer(tpl, x, wgu_l, wd_l).clone()
+                    other_forms[mode_] = timed(lambda: D.tp_ffn_peer(tpl, x, wgu_l, wd_l, recorded=True), 3, 10)
+                    if not torch.equal(got_other, got):
+                        raise RuntimeError(f"tp_ffn: the {tp.mode} and the {mode_} form differ")
                     barrier()
                     tpl.close()
+                sec_pull = other_forms.get("pull", sec)
                 # ... and the same FFN with an NCCL all-reduce of the f32 partials and a separate epilogue (the baseline form)
                 y2 = y.clone()
                 D.tp_ffn(be, x, wgu_l, wd_l, y2)
@@ -1045,6 +1048,7 @@ def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks)
                                            "kernels_per_step": tp.kernels_per_step, "parity": parity,
                                            "exchange": tp.describe(),
                                            "launched_one_by_one_us": sec_loop * 1e6, "pull_form_us": sec_pull * 1e6,
+                                           "forms_us": {tp.mode: sec * 1e6, **{k_: v * 1e6 for k_, v in other_forms.items()}},
                                            "nccl_form_us": sec_nccl * 1e6, "equals_nccl_form_bitwise": same,
                                            "max_abs_diff_vs_nccl_form": diff, "max_abs_value": scale}
                 del wgu, wd, wgu_l, wd_l

@@ -227,37 +227,38 @@ gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                         break;
                     }
                 }
-                // own accumulator chunk c plus the running sum (if any): v[] as f32 bits. The running sum of the next
-                // chunk is asked for before this one is worked on (a chunk's loads take about a microsecond).
+                // own accumulator chunk c plus the running sum (if any): v[] as f32 bits. A chunk's loads of the running
+                // sum take about a microsecond to come back, so AHEAD chunks are in flight at any time (the loops are
+                // unrolled: the ring of registers is indexed at compile time).
                 constexpr int NCHUNK = PAIR_BN / 32;
-                uint4 ahead[8];
-                auto ask = [&](int c) {
+                constexpr int AHEAD = OUT == HB_OUT_SWIGLU ? 3 : 4;
+                uint4 ahead[AHEAD][8];
+                auto ask = [&](int slot, int c) {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) ahead[j] = __ldcg(buf + (c * 8 + j) * 32);
+                    for (int j = 0; j < 8; ++j) ahead[slot][j] = __ldcg(buf + (c * 8 + j) * 32);
                 };
                 // the order the chunks are visited in: 0, 1, .. or, for the SwiGLU's last slice, gate and up chunks in turn
                 auto nth = [&](int i) { return (last && OUT == HB_OUT_SWIGLU) ? ((i & 1) ? HALF / 32 + (i >> 1) : (i >> 1)) : i; };
-                if (!first) ask(nth(0));
-                auto chunk = [&](int i, uint32_t (&v)[32]) {
-                    uint4 t[8];
-                    if (!first) {
+                if (!first) {
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) t[j] = ahead[j];
-                        if (i + 1 < NCHUNK) ask(nth(i + 1));
-                    }
+                    for (int i = 0; i < AHEAD; ++i) ask(i, nth(i));
+                }
+                auto chunk = [&](int i, uint32_t (&v)[32]) {
                     tmem_ld_32x32(t_addr + nth(i) * 32, v);
                     tmem_ld_wait();
                     if (!first) {
 #pragma unroll
                         for (int j = 0; j < 8; ++j) {
-                            const uint32_t w4[4] = {t[j].x, t[j].y, t[j].z, t[j].w};
+                            const uint4 t = ahead[i % AHEAD][j];
+                            const uint32_t w4[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
                             for (int e = 0; e < 4; ++e) v[4 * j + e] = __float_as_uint(__fadd_rn(__uint_as_float(w4[e]), __uint_as_float(v[4 * j + e])));
                         }
+                        if (i + AHEAD < NCHUNK) ask(i % AHEAD, nth(i + AHEAD));
                     }
                 };
                 if (!last) {
-#pragma unroll 1
+#pragma unroll
                     for (int c = 0; c < NCHUNK; ++c) {
                         uint32_t v[32];
                         chunk(c, v);
@@ -265,7 +266,7 @@ gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                         for (int j = 0; j < 8; ++j) __stcg(buf + (c * 8 + j) * 32, make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
                     }
                 } else if constexpr (OUT == HB_OUT_SWIGLU) {
-#pragma unroll 1
+#pragma unroll
                     for (int c = 0; c < HALF / 32; ++c) {
                         uint32_t g[32], u[32];
                         chunk(2 * c, g);
@@ -273,7 +274,7 @@ gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                         store_chunk<OUT>(p, row, tn * HALF + c * 32, g, u);
                     }
                 } else {
-#pragma unroll 1
+#pragma unroll
                     for (int c = 0; c < NCHUNK; ++c) {
                         uint32_t v[32];
                         chunk(c, v);

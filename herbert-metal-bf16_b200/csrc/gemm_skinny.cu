@@ -39,6 +39,7 @@ struct SkinnyParams {
     void* y;
     uint32_t m, n_out;
     uint32_t k_blocks, feat_blocks, stages;
+    uint32_t block_rows;  // W rows (output features) per feature block: 128, or fewer so that the blocks fill whole waves of CTAs
     uint32_t balanced;    // 0: a CTA takes whole feature blocks; 1: the (feature block, k-block) units are dealt evenly
     uint32_t maxslots;    // balanced: the most CTAs that share one feature block
     float* scratch;       // balanced: [feat_blocks][maxslots][NACC * NP][128]
@@ -187,8 +188,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             SkinnySeg sg;
             seg_at(i, &sg);
             const uint32_t fb = sg.fb, kb0 = sg.kb0, kb1 = sg.kb1;
-            const int row_w0 = (int)(fb * 128);
-            const int row_w1 = (int)(p.n_out + fb * 128);  // SWIGLU: the up rows of the same features
+            const int row_w0 = (int)(fb * p.block_rows);
+            const int row_w1 = (int)(p.n_out + fb * p.block_rows);  // SWIGLU: the up rows of the same features
             for (uint32_t kb = kb0; kb < kb1; kb += KPS, ++fill) {
                 const bool early = fill < S;
                 if (pass != 2 && !early) return true;
@@ -199,7 +200,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                 }
                 const uint32_t full = smem_u32(&bars.full[s]);
                 const uint32_t nkb = min((uint32_t)KPS, kb1 - kb);
-                if (do_w) mbar_arrive_expect_tx(full, nkb * KB_BYTES);
+                // (a W box is block_rows rows; the rest of its 128-row slot is never written, and the rows of the
+                // accumulator that come from it are never read)
+                if (do_w) mbar_arrive_expect_tx(full, nkb * (NACC * p.block_rows * 128u + B_BYTES));
 #pragma unroll
                 for (uint32_t j = 0; j < (uint32_t)KPS; ++j) {
                     if (j < nkb) {
@@ -308,9 +311,9 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&bars.tmem_empty[acc]));
-            const uint32_t f = fb * 128 + q * 32 + lane;
+            const uint32_t f = fb * p.block_rows + q * 32 + lane;
             if (sg.nslots == 1) {
-                if (f < p.n_out) {
+                if (q * 32 + lane < p.block_rows && f < p.n_out) {
 #pragma unroll
                     for (int j = 0; j < NP; ++j)
                         if ((uint32_t)j < p.m) skinny_store<OUT>(p, j, f, __uint_as_float(g[j]), NACC == 2 ? __uint_as_float(u[j]) : 0.f);
@@ -410,7 +413,7 @@ skinny_fn skinny_pick_norm(uint32_t out, uint32_t kps) {
 }
 
 struct SkinnyGemm : hb_kernel {
-    uint32_t k = 0, n = 0, out = 0, rows_max = 0, np = 0, balanced = 0, maxslots = 1, grid_balanced = 0, stages = 0;
+    uint32_t k = 0, n = 0, out = 0, rows_max = 0, np = 0, balanced = 0, maxslots = 1, grid_balanced = 0, stages = 0, block_rows = 128;
     skinny_fn fn = nullptr;
     size_t smem = 0;
     float* scratch = nullptr;
@@ -435,7 +438,7 @@ struct SkinnyGemm : hb_kernel {
         if (!range_ok(a[0], (size_t)n * k * 2) || !range_ok(a[1], (size_t)m * k * 2) || !range_ok(a[2], (size_t)m * n_out * (out == HB_OUT_F32 ? 4 : 2)))
             return fail(ctx, HB_INVALID, name + ": a bound range is too small for " + std::to_string(m) + " rows");
         if (a[0].ptr != last_w || a[1].ptr != last_x || m != last_m) {
-            int r = make_tmap_bf16(ctx, &tm_w, a[0].ptr, n, k, 128);
+            int r = make_tmap_bf16(ctx, &tm_w, a[0].ptr, n, k, block_rows);
             if (r != HB_OK) return r;
             if ((r = make_tmap_bf16(ctx, &tm_x, norm ? static_cast<const void*>(xn) : a[1].ptr, m, k, np)) != HB_OK) return r;
             last_w = a[0].ptr;
@@ -447,7 +450,8 @@ struct SkinnyGemm : hb_kernel {
         p.m = m;
         p.n_out = n_out;
         p.k_blocks = (k + 63) / 64;
-        p.feat_blocks = (n_out + 127) / 128;
+        p.feat_blocks = (n_out + block_rows - 1) / block_rows;
+        p.block_rows = block_rows;
         p.balanced = balanced;
         p.maxslots = maxslots;
         p.stages = stages;
@@ -473,7 +477,9 @@ struct SkinnyGemm : hb_kernel {
 
 }  // namespace
 
-// d->tensor_core: 1 = whole feature blocks per CTA, 2 = balanced units.
+// d->tensor_core: 1 = whole feature blocks of 128 rows per CTA, 2 = balanced units, 3 = whole feature blocks of as many
+// rows (at most 128) as make the blocks fill whole waves of CTAs: a block's box of W rows is what one SM pulls, and one
+// SM takes in 60-76 GB/s, so 96 blocks of 128 rows on 148 SMs cannot stream at the HBM rate where 147 blocks of 84 can.
 int make_matvec_skinny(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out) {
     *out = nullptr;
     if (d->k == 0 || d->n == 0 || d->rows_max == 0) return fail(ctx, HB_INVALID, "matvec (tensor core): k, n and rows_max must be positive");
@@ -481,7 +487,7 @@ int make_matvec_skinny(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out) {
     if (d->rows_max > 64) return fail(ctx, HB_UNSUPPORTED, "matvec (tensor core): at most 64 activation rows (the prefill GEMM takes over)");
     if (d->out > HB_OUT_SWIGLU) return fail(ctx, HB_INVALID, "matvec: unknown output mode");
     if (d->out == HB_OUT_SWIGLU && d->n % 2 != 0) return fail(ctx, HB_INVALID, "matvec: the SwiGLU form needs an even n ([gate | up])");
-    if (d->tensor_core > 2) return fail(ctx, HB_UNSUPPORTED, "matvec (tensor core): 1 = whole feature blocks, 2 = balanced units");
+    if (d->tensor_core > 3) return fail(ctx, HB_UNSUPPORTED, "matvec (tensor core): 1 = whole feature blocks, 2 = balanced units, 3 = feature blocks sized to the grid");
     const uint32_t balanced = d->tensor_core == 2 ? 1u : 0u;
     const uint32_t k_blocks = (d->k + 63) / 64;
     const uint32_t np = d->rows_max <= 16 ? 16 : d->rows_max <= 32 ? 32 : 64;
@@ -492,6 +498,12 @@ int make_matvec_skinny(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out) {
     skinny_fn fn = norm ? skinny_pick_norm(d->out, kps)
                         : np == 16 ? skinny_pick_kps<16>(d->out, kps) : np == 32 ? skinny_pick_kps<32>(d->out, kps) : skinny_pick_kps<64>(d->out, kps);
     const uint32_t nacc = d->out == HB_OUT_SWIGLU ? 2 : 1;
+    uint32_t block_rows = 128;
+    if (d->tensor_core == 3) {
+        const uint32_t n_out = d->out == HB_OUT_SWIGLU ? d->n / 2 : d->n, sms = (uint32_t)ctx->sm_count;
+        const uint32_t waves = (n_out + sms * 128 - 1) / (sms * 128);
+        block_rows = std::min(128u, std::max(8u, (n_out + sms * waves - 1) / (sms * waves)));
+    }
     const size_t stage_bytes = ((size_t)nacc * SK_A_BYTES + np * 128) * kps;
     const size_t budget = std::min<size_t>(ctx->smem_optin, 227 * 1024) - 3072;  // alignment slack, barriers, the segment table
     uint32_t stages = (uint32_t)std::min<size_t>(budget / stage_bytes, SK_MAX_STAGES);
@@ -507,6 +519,7 @@ int make_matvec_skinny(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out) {
     k->rows_max = np;  // the kernel is built for a padded row count: any m up to it
     k->np = np;
     k->balanced = balanced;
+    k->block_rows = block_rows;
     k->stages = stages;
     k->fn = fn;
     k->smem = stages * stage_bytes + 1024;
@@ -519,7 +532,9 @@ int make_matvec_skinny(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out) {
         k->plus_one = d->norm_plus_one;
         snprintf(xtag, sizeof xtag, "_nrm%08x%s", d->norm_eps_bits, d->norm_plus_one ? "p1" : "");
     }
-    snprintf(nm, sizeof nm, "matvec_tc_%ux%u_%s_m%u_%s_s%ux%u%s", d->k, d->n, out_tag(d->out), np, balanced ? "bal" : "blk", stages, kps, xtag);
+    char btag[16] = "blk";
+    if (d->tensor_core == 3) snprintf(btag, sizeof btag, "fit%u", block_rows);
+    snprintf(nm, sizeof nm, "matvec_tc_%ux%u_%s_m%u_%s_s%ux%u%s", d->k, d->n, out_tag(d->out), np, balanced ? "bal" : btag, stages, kps, xtag);
     k->name = nm;
     if (hb_kernel* have = find(ctx, k->name)) {
         *out = have;
@@ -553,7 +568,7 @@ int make_matvec_skinny(hb_ctx* ctx, const hb_matvec_desc* d, hb_kernel** out) {
         const uint32_t n_out = d->out == HB_OUT_SWIGLU ? d->n / 2 : d->n;
         SkinnyParams tp{};
         tp.k_blocks = k_blocks;
-        tp.feat_blocks = (n_out + 127) / 128;
+        tp.feat_blocks = (n_out + block_rows - 1) / block_rows;
         tp.balanced = balanced;
         const uint32_t grid = balanced ? k->grid_balanced : std::min<uint32_t>(tp.feat_blocks, (uint32_t)ctx->sm_count);
         std::vector<uint32_t> start(grid + 1, 0);

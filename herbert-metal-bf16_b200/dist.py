@@ -584,12 +584,15 @@ class TpPeer:
 
     Three forms of the exchange, the same bits from each (the f32 partials are summed in rank order by one rank per row):
 
-    "stream" (the default with 2, 4 or 8 ranks): the rows are dealt in groups of 256 (the down GEMM's row tile) and
+    "stream": the rows are dealt in groups of 256 (the down GEMM's row tile) and
       every rank sums 256 / world rows of every group. The down GEMM stores each tile of its partial straight into the
       staging buffers of the ranks that sum its rows and flags a group when its last tile is out; the summing kernel
       (hb_tp_sum_stream_get) starts beside the GEMM, takes the groups as they complete, stores the bf16 rows into every
       rank's Y and closes the step with a handshake of its own. Three kernels per step, none of them a barrier.
-    "push": contiguous blocks of rows, one per rank; the down GEMM pushes, a barrier kernel, tp_sum, a barrier kernel.
+      Slower than "push" as measured: a system-scope fence behind a tile's remote stores waits until they have all
+      been acknowledged, and with NVLink as the bound that wait is long (the down GEMM of the 27B-class FFN on eight
+      B200s: 188 us with the flags, 89 us without; the step 319 against 213 us; on two B200s 448 against 437 us).
+    "push" (the default): contiguous blocks of rows, one per rank; the down GEMM pushes, a barrier kernel, tp_sum, a barrier kernel.
     "pull": the partial stays local; a barrier kernel, tp_reduce pulls the blocks it sums from the peers, a barrier.
     Measured for the 27B-class FFN (2048 rows), push against pull: 449 against 483 us on two B200s, 220 against 259 us
     on eight. (The pushed stores leave as whole 128-byte row segments: one 16-byte piece per lane took 537 and 437 us.)"""
@@ -598,7 +601,7 @@ class TpPeer:
         self.hb, self.ctx, self.rank, self.world, self.m, self.h, self.out = hb, ctx, rank, world, m, h, out
         dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         if mode is None:
-            mode = ("push" if push else "pull") if push is not None else ("stream" if world in (2, 4, 8) else "push")
+            mode = ("push" if push else "pull") if push is not None else "push"
         if world == 1:
             mode = "pull"
         assert mode in ("stream", "push", "pull")

@@ -428,7 +428,7 @@ int hb_select_gemm(hb_selector* s, uint32_t k, uint32_t n, uint32_t out, hb_rang
         if (m <= 64) {
             struct SkForm { const char* name; uint32_t tc, kps; };
             // (K blocks per stage: four while the activation tile is small, two when it is 64 rows: at least three stages must fit)
-            for (const SkForm& f : {SkForm{"stream", 1, m <= 16 ? 4u : 2u}, SkForm{"streamb", 2, m <= 16 ? 2u : 1u}}) {
+            for (const SkForm& f : {SkForm{"stream", 1, m <= 16 ? 4u : 2u}, SkForm{"streamb", 2, m <= 16 ? 2u : 1u}, SkForm{"streamf", 3, m <= 16 ? 4u : 2u}}) {
                 hb_matvec_desc d{};
                 d.k = k;
                 d.n = n;
@@ -615,7 +615,7 @@ int hb_select_gate_up(hb_selector* s, uint32_t k, uint32_t inter, hb_range w, hb
                     eligible.push_back(1);
                 }
                 if (m <= 64) {  // the weight-stream form with the SwiGLU epilogue (two weight tiles per step: two K blocks per stage)
-                    for (uint32_t tc : {1u, 2u}) {
+                    for (uint32_t tc : {1u, 2u, 3u}) {
                         hb_matvec_desc d{};
                         d.k = k;
                         d.n = 2 * inter;
@@ -626,7 +626,7 @@ int hb_select_gate_up(hb_selector* s, uint32_t k, uint32_t inter, hb_range w, hb
                         hb_kernel* f = nullptr;
                         if (hb_matvec_get(ctx, &d, &f) != HB_OK) continue;
                         Cand c;
-                        c.name = tc == 1 ? "fusedstream" : "fusedstreamb";
+                        c.name = tc == 1 ? "fusedstream" : tc == 2 ? "fusedstreamb" : "fusedstreamf";
                         add_op(c, f, {w, x, h});
                         cands.push_back(std::move(c));
                         eligible.push_back(1);
@@ -739,7 +739,7 @@ int hb_select_matvec_x(hb_selector* s, uint32_t k, uint32_t n, uint32_t out, uin
             struct TcForm { const char* name; uint32_t ks, kps; };
             const uint32_t n_out = out == HB_OUT_SWIGLU ? n / 2 : n;
             (void)n_out;
-            for (const TcForm& f : {TcForm{"tc", 1, 2}, TcForm{"tcw", 1, 4}, TcForm{"tcb", 2, 2}, TcForm{"tcbw", 2, 4}}) {
+            for (const TcForm& f : {TcForm{"tc", 1, 2}, TcForm{"tcw", 1, 4}, TcForm{"tcb", 2, 2}, TcForm{"tcbw", 2, 4}, TcForm{"tcf", 3, 2}, TcForm{"tcfw", 3, 4}}) {
                 hb_matvec_desc d{};
                 d.k = k;
                 d.n = n;

@@ -219,7 +219,10 @@ typedef struct {
                                operand of tcgen05.mma, the activation rows its narrow side): rows_max up to 64.
                                1 = a CTA takes blocks of 128 features over all of K; 2 = the (feature block, 64-element
                                K block) units are dealt evenly, one contiguous range per SM, and blocks shared by
-                               several SMs are summed from f32 partials in K order. Accumulation order inside a
+                               several SMs are summed from f32 partials in K order; 3 = as 1 with blocks of fewer
+                               features (n / (SMs x waves), at most 128), so that the blocks fill whole waves of
+                               SMs (one SM takes in 60-76 GB/s: 96 blocks of 128 features cannot stream 12288
+                               features at the HBM rate, 147 blocks of 84 can). Accumulation order inside a
                                range is the tensor core's, as in the prefill GEMM. `split` (1, 2 or 4) is then the
                                number of neighbouring K blocks one pipeline stage holds (longer runs per weight row
                                in DRAM) and `persist` >= 2 caps the number of stages (with half the shared memory

@@ -127,7 +127,7 @@ def test_layer_9b_64_rows_gemm_and_stream_forms(ctx, oracle, hb200, name, k, n, 
     s.check(ctx, oracle, ctx.gemm(k, n, out, rows_max=m, cta_pair=1))
     for tile_n in (256, 128, 64):
         s.check(ctx, oracle, ctx.gemm(k, n, out, rows_max=m, tile_n=tile_n, stream_k=1))
-    forms = [(1, 2), (2, 2)] if out == OUT_SWIGLU else [(1, 2), (2, 1), (1, 1)]
+    forms = [(1, 2), (2, 2), (3, 2)] if out == OUT_SWIGLU else [(1, 2), (2, 1), (1, 1), (3, 2)]
     for tc, kps in forms:
         kern = ctx.matvec(k, n, out, rows_max=m, tensor_core=tc, split=kps)
         assert kern.name.startswith("matvec_tc_")
@@ -139,7 +139,7 @@ def test_lm_head_151936_tensor_core_streams(ctx, oracle, m):
     """The forms hb_select_matvec picks for 4 and 8 rows at the LM-head shape, all 151936 outputs of every row."""
     k, n = 4096, 151936
     s = Shape(ctx, oracle, m, k, n, OUT_BF16)
-    for tc, kps in ((1, 2), (1, 4), (2, 2), (2, 4)):
+    for tc, kps in ((1, 2), (1, 4), (2, 2), (2, 4), (3, 2), (3, 4)):
         kern = ctx.matvec(k, n, OUT_BF16, rows_max=m, tensor_core=tc, split=kps)
         s.check(ctx, oracle, kern)
 

@@ -98,7 +98,7 @@ def test_tensor_core_forms(ctx, oracle, hb200, m, out):
     for k, n in ((1024, 330), (4096, 512), (72, 40), (2560, 96), (8192, 1200)):
         if out == OUT_SWIGLU and k > 4096:
             continue  # three roundings after a sum of 8192 f32 terms: outside what the one-ulp rate is stated for
-        for ks in (1, 2):  # whole feature blocks per CTA; evenly dealt (block, k-block) units
+        for ks in (1, 2, 3):  # whole feature blocks per CTA; evenly dealt (block, k-block) units; blocks sized to the grid
             for kps in (1, 2, 4):
                 if out == OUT_SWIGLU and kps == 4:  # two weight tiles per K block: four blocks per stage leave room for one stage only
                     with pytest.raises(hb200.HbError) as e:
@@ -106,7 +106,7 @@ def test_tensor_core_forms(ctx, oracle, hb200, m, out):
                     assert e.value.status == hb200.UNSUPPORTED
                     continue
                 kern, want, got = run(ctx, oracle, m, k, n, out, tensor_core=ks, split=kps)
-                assert kern.name.startswith("matvec_tc_") and ("_blk_", "_bal_")[ks - 1] in kern.name and kern.name.endswith(f"x{kps}")
+                assert kern.name.startswith("matvec_tc_") and ("_blk_", "_bal_", "_fit")[ks - 1] in kern.name and kern.name.endswith(f"x{kps}")
                 within_contract(oracle, want, got, f"{kern.name} m={m}")
 
 
@@ -124,7 +124,7 @@ def test_tensor_core_form_twice_and_limits(ctx, oracle, hb200):
         outs.append(d_y.download(np.uint16, (m, n)))
     assert np.array_equal(outs[0], outs[1]) and np.array_equal(outs[0], outs[2])
     within_contract(oracle, oracle.gemm_f64(x, w), outs[0], kern.name)
-    for bad in (dict(rows_max=65, tensor_core=1), dict(rows_max=8, tensor_core=3)):
+    for bad in (dict(rows_max=65, tensor_core=1), dict(rows_max=8, tensor_core=4)):
         with pytest.raises(hb200.HbError) as e:
             ctx.matvec(k, n, OUT_BF16, **bad)
         assert e.value.status == hb200.UNSUPPORTED
@@ -133,7 +133,7 @@ def test_tensor_core_form_twice_and_limits(ctx, oracle, hb200):
 @pytest.mark.parametrize("m", [1, 4, 8])
 def test_config2_shapes_tensor_core(ctx, oracle, m):
     k, n = 4096, 12288
-    for ks in (1, 2):
+    for ks in (1, 2, 3):
         kern, want, got = run(ctx, oracle, m, k, n, OUT_BF16, tensor_core=ks, split=2)
         within_contract(oracle, want, got, f"{kern.name} m={m}")
 
