@@ -143,11 +143,33 @@ struct EpCombineParams {
     const uint32_t* route;     // [rows][2 * top_k]
     uint16_t* out;             // [rows][h]
     uint32_t rows, h8, top_k, world;
+    // optional (hb_ep_combine_sync_get): the barrier "every rank's expert outputs are complete" inside this kernel.
+    // Block 0 tells every rank that this rank's expert GEMMs are done (they precede this kernel on the stream); every
+    // block waits, bounded, until all owners have said so for this step. The step's number is kept in ctl[0] by the
+    // kernel itself (the block that finishes last advances it), so a recorded launch replays.
+    const uint64_t* peers_done;  // [world] -> u32[world] on every rank
+    const uint32_t* done;        // this rank's u32[world]
+    uint32_t* ctl;               // [0] combines completed, [1] blocks finished
+    uint32_t rank;
+    long long wait_cycles;
+    uint32_t* status;
 };
 
 __global__ void __launch_bounds__(256) ep_combine_kernel(const EpCombineParams p) {
     __shared__ uint64_t ey_s[EP_MAX_WORLD];
     if (threadIdx.x < p.world) ey_s[threadIdx.x] = p.peers_ey[threadIdx.x];
+    uint32_t step = 0;
+    if (p.peers_done) {
+        step = *reinterpret_cast<volatile uint32_t*>(p.ctl) + 1u;
+        if (threadIdx.x < p.world) {
+            if (blockIdx.x == 0) {
+                __threadfence_system();
+                uint32_t* flag = reinterpret_cast<uint32_t*>(p.peers_done[threadIdx.x]) + p.rank;
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(flag), "r"(step) : "memory");
+            }
+            if (!wait_for_step(p.done + threadIdx.x, step, p.wait_cycles) && blockIdx.x == 0) report(p.status, ST_WAIT_TIMEOUT, WHERE_PEER, 64u + threadIdx.x);
+        }
+    }
     __syncthreads();
     const size_t total = (size_t)p.rows * p.h8;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
@@ -181,6 +203,15 @@ __global__ void __launch_bounds__(256) ep_combine_kernel(const EpCombineParams p
         }
         *reinterpret_cast<uint4*>(p.out + ((size_t)row * p.h8 + c) * 8) = make_uint4(accp[0], accp[1], accp[2], accp[3]);
     }
+    if (p.peers_done) {
+        // every block has read ctl[0] before it gets here, so the last one may advance it
+        __syncthreads();
+        if (threadIdx.x == 0 && atomicAdd(p.ctl + 1, 1u) == gridDim.x - 1u) {
+            p.ctl[1] = 0u;
+            __threadfence();
+            *reinterpret_cast<volatile uint32_t*>(p.ctl) = step;
+        }
+    }
 }
 
 struct PlanParams {
@@ -206,24 +237,33 @@ __global__ void __launch_bounds__(PLAN_THREADS) ep_plan_kernel(const PlanParams 
     uint32_t* recvbase = st + p.epr;       // [world] first receive row of source s
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t stride = p.experts + 1, e0 = p.rank * p.epr;
-    // (in the direct form the table was written by the other GPUs' dispatch kernels: read it from L2, not through a
+    // (in the direct form the table was written by the other GPUs' dispatch kernels: it is read from L2, not through a
     // read-only path)
-    auto offs = [&](uint32_t i) { return __ldcg(p.offs_all + i); };
     if (p.landed && tid < p.world) {
         const uint32_t step = *reinterpret_cast<const volatile uint32_t*>(p.ctl);  // this rank's dispatch has numbered the step
         if (!wait_for_step(p.landed + tid, step, p.wait_cycles)) report(p.status, ST_WAIT_TIMEOUT, WHERE_PEER, 32u + tid);
     }
     __syncthreads();  // (the waits above: the offsets the peers delivered are read below)
+    // The part of the table this rank needs, every source's offsets of the local experts, goes to shared memory in one
+    // round trip; everything below reads it there (read one by one from L2, a microsecond each, the serial loops over
+    // the sources were most of this kernel's time).
+    uint32_t* offs_s = recvbase + p.world;  // [world][epr + 1]
+    for (uint32_t i = tid; i < p.world * (p.epr + 1); i += PLAN_THREADS) {
+        const uint32_t s = i / (p.epr + 1), e = i - s * (p.epr + 1);
+        offs_s[i] = __ldcg(p.offs_all + s * stride + e0 + e);
+    }
+    __syncthreads();
+    auto offs = [&](uint32_t s, uint32_t e) { return offs_s[s * (p.epr + 1) + e]; };  // source s, local expert e (or epr: the end)
     if (tid == 0) {
         uint32_t b = 0;
         for (uint32_t s = 0; s < p.world; ++s) {
             recvbase[s] = p.region ? s * p.region : b;
-            b += offs(s * stride + e0 + p.epr) - offs(s * stride + e0);
+            b += offs(s, p.epr) - offs(s, 0);
         }
     }
     uint32_t total_e = 0;
     if (tid < p.epr)
-        for (uint32_t s = 0; s < p.world; ++s) total_e += offs(s * stride + e0 + tid + 1) - offs(s * stride + e0 + tid);
+        for (uint32_t s = 0; s < p.world; ++s) total_e += offs(s, tid + 1) - offs(s, tid);
     const uint32_t ntile_e = (total_e + p.bm - 1) / p.bm;
     uint32_t a = total_e, t = ntile_e;
     if (tid < p.epr) { sa[tid] = a; st[tid] = t; }
@@ -260,8 +300,8 @@ __global__ void __launch_bounds__(PLAN_THREADS) ep_plan_kernel(const PlanParams 
     for (uint32_t e = warp; e < p.epr; e += PLAN_THREADS / 32) {
         uint32_t pos = start[e];
         for (uint32_t s = 0; s < p.world; ++s) {
-            const uint32_t lo = offs(s * stride + e0 + e), hi = offs(s * stride + e0 + e + 1);
-            const uint32_t src0 = recvbase[s] + lo - offs(s * stride + e0);
+            const uint32_t lo = offs(s, e), hi = offs(s, e + 1);
+            const uint32_t src0 = recvbase[s] + lo - offs(s, 0);
             for (uint32_t j = lane; j < hi - lo; j += 32) p.list[pos + j] = src0 + j;
             pos += hi - lo;
         }
@@ -350,7 +390,7 @@ struct EpPlan : hb_kernel {
             p.wait_cycles = (long long)ctx->peer_wait_ms * 2000000ll;
         }
         p.region = direct ? cap / world : 0;
-        ep_plan_kernel<<<1, PLAN_THREADS, (3 * epr + world) * 4, ctx->stream>>>(p);
+        ep_plan_kernel<<<1, PLAN_THREADS, (3 * epr + world + world * (epr + 1)) * 4, ctx->stream>>>(p);  // start, sa, st, recvbase, offs_s
         HB_CUDA(ctx, cudaGetLastError());
         ctx->launches++;
         return HB_OK;
@@ -358,9 +398,10 @@ struct EpPlan : hb_kernel {
 };
 
 struct EpCombine : hb_kernel {
-    uint32_t h = 0, top_k = 0, world = 0;
+    uint32_t h = 0, top_k = 0, world = 0, rank = 0;
+    bool sync = false;
     int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
-        if (na != 4) return fail(ctx, HB_INVALID, name + ": bindings are peers_ey, where, route, out");
+        if (na != (sync ? 7 : 4)) return fail(ctx, HB_INVALID, name + (sync ? ": bindings are peers_ey, where, route, out, peers_done, done, ctl" : ": bindings are peers_ey, where, route, out"));
         if (m == 0) return fail(ctx, HB_INVALID, name + ": m = 0");
         if (!range_ok(a[0], (size_t)world * 8) || !range_ok(a[1], (size_t)m * top_k * 4) || !range_ok(a[2], (size_t)m * 2 * top_k * 4) || !range_ok(a[3], (size_t)m * h * 2))
             return fail(ctx, HB_INVALID, name + ": a bound range is too small");
@@ -374,6 +415,15 @@ struct EpCombine : hb_kernel {
         p.h8 = h / 8;
         p.top_k = top_k;
         p.world = world;
+        if (sync) {
+            if (!range_ok(a[4], (size_t)world * 8) || !range_ok(a[5], (size_t)world * 4) || !range_ok(a[6], 8)) return fail(ctx, HB_INVALID, name + ": a bound range is too small");
+            p.peers_done = static_cast<const uint64_t*>(a[4].ptr);
+            p.done = static_cast<const uint32_t*>(a[5].ptr);
+            p.ctl = static_cast<uint32_t*>(a[6].ptr);
+            p.rank = rank;
+            p.wait_cycles = (long long)ctx->peer_wait_ms * 2000000ll;
+            p.status = ctx->status_dev;
+        }
         const size_t items = (size_t)m * p.h8;
         const uint32_t grid = (uint32_t)std::max<size_t>(1, std::min<size_t>((items + 255) / 256, (size_t)ctx->sm_count * 8));
         ep_combine_kernel<<<grid, 256, 0, ctx->stream>>>(p);
@@ -411,16 +461,19 @@ int make_ep_move(hb_ctx* ctx, bool ret, uint32_t h, uint32_t top_k, uint32_t exp
     return HB_OK;
 }
 
-int make_ep_combine(hb_ctx* ctx, uint32_t h, uint32_t top_k, uint32_t world, hb_kernel** out) {
+int make_ep_combine(hb_ctx* ctx, uint32_t h, uint32_t top_k, uint32_t world, hb_kernel** out, bool sync, uint32_t rank) {
     *out = nullptr;
     if (world < 1 || world > EP_MAX_WORLD || h == 0 || h % 8 != 0 || top_k == 0) return fail(ctx, HB_UNSUPPORTED, "ep combine: 1..16 ranks, h a positive multiple of 8");
+    if (sync && (world < 2 || rank >= world)) return fail(ctx, HB_UNSUPPORTED, "ep combine (with its barrier): 2..16 ranks, one GPU each");
     auto k = std::make_unique<EpCombine>();
     k->h = h;
     k->top_k = top_k;
     k->world = world;
+    k->rank = rank;
+    k->sync = sync;
     k->kind = 17;
-    k->nargs = 4;
-    k->name = "ep_combine_" + std::to_string(h) + "_k" + std::to_string(top_k) + "_w" + std::to_string(world);
+    k->nargs = sync ? 7 : 4;
+    k->name = "ep_combine_" + std::to_string(h) + "_k" + std::to_string(top_k) + "_w" + std::to_string(world) + (sync ? "_sync_r" + std::to_string(rank) : std::string());
     *out = intern(ctx, std::move(k));
     return HB_OK;
 }

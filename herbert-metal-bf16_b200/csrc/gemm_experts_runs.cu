@@ -75,14 +75,19 @@ __device__ __forceinline__ void cp_async_mbar_arrive(uint32_t bar) {
 
 // Builds the run list in shared memory from the table's tiles: run = (expert, first sorted row, rows <= 128).
 // A tile starts a run when it is the first of its expert or a multiple of 128 rows into the expert's rows.
-__device__ __forceinline__ void build_runs(const RunParams& p, uint32_t ntiles, uint32_t* run_first, uint32_t* run_end, uint32_t* runs, uint32_t* scratch,
+// The table is copied to shared memory once (`tl`, room for 3 words per tile: the pipeline's stage buffers, not yet in
+// use) and everything else works from there: one round trip to global memory, and the scan of the per-thread counts is
+// a shuffle scan (a serial scan over 320 counts by one thread took longer than streaming an expert's weights).
+__device__ __forceinline__ void build_runs(const RunParams& p, uint32_t ntiles, uint32_t* tl, uint32_t* run_first, uint32_t* run_end, uint32_t* runs, uint32_t* scratch,
                                            uint32_t* nruns_out) {
-    const uint32_t tid = threadIdx.x, nthr = blockDim.x;
+    const uint32_t tid = threadIdx.x, nthr = blockDim.x, lane = tid & 31u, warp = tid >> 5;
+    for (uint32_t i = tid; i < 3 * ntiles; i += nthr) tl[i] = p.tiles[1 + i];
+    __syncthreads();
     for (uint32_t t = tid; t < ntiles; t += nthr) {
-        const uint32_t e = p.tiles[1 + 3 * t], start = p.tiles[2 + 3 * t], rows = p.tiles[3 + 3 * t];
+        const uint32_t e = tl[3 * t], start = tl[3 * t + 1], rows = tl[3 * t + 2];
         if (e < RN_MAX_EXPERTS) {
-            if (t == 0 || p.tiles[1 + 3 * (t - 1)] != e) run_first[e] = start;
-            if (t + 1 == ntiles || p.tiles[1 + 3 * (t + 1)] != e) run_end[e] = start + rows;
+            if (t == 0 || tl[3 * (t - 1)] != e) run_first[e] = start;
+            if (t + 1 == ntiles || tl[3 * (t + 1)] != e) run_end[e] = start + rows;
         }
     }
     __syncthreads();
@@ -91,24 +96,27 @@ __device__ __forceinline__ void build_runs(const RunParams& p, uint32_t ntiles, 
     const uint32_t t0 = min(ntiles, tid * per), t1 = min(ntiles, t0 + per);
     uint32_t mine = 0;
     for (uint32_t t = t0; t < t1; ++t) {
-        const uint32_t e = p.tiles[1 + 3 * t], start = p.tiles[2 + 3 * t];
+        const uint32_t e = tl[3 * t], start = tl[3 * t + 1];
         if (e < RN_MAX_EXPERTS && (start - run_first[e]) % RN_NMAX == 0) mine++;
     }
-    scratch[tid] = mine;
-    __syncthreads();
-    if (tid == 0) {
-        uint32_t acc = 0;
-        for (uint32_t i = 0; i < nthr; ++i) {
-            const uint32_t c = scratch[i];
-            scratch[i] = acc;
-            acc += c;
-        }
-        *nruns_out = min(acc, (uint32_t)RN_MAX_RUNS);
+    uint32_t incl = mine;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const uint32_t o = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= (uint32_t)off) incl += o;
     }
+    if (lane == 31) scratch[warp] = incl;
     __syncthreads();
-    uint32_t at = scratch[tid];
+    uint32_t before = 0, total = 0;
+    for (uint32_t w = 0; w < nthr / 32; ++w) {
+        const uint32_t c = scratch[w];
+        if (w < warp) before += c;
+        total += c;
+    }
+    if (tid == 0) *nruns_out = min(total, (uint32_t)RN_MAX_RUNS);
+    uint32_t at = before + incl - mine;
     for (uint32_t t = t0; t < t1; ++t) {
-        const uint32_t e = p.tiles[1 + 3 * t], start = p.tiles[2 + 3 * t];
+        const uint32_t e = tl[3 * t], start = tl[3 * t + 1];
         if (e < RN_MAX_EXPERTS && (start - run_first[e]) % RN_NMAX == 0) {
             if (at < RN_MAX_RUNS) {
                 runs[3 * at] = e;
@@ -118,6 +126,8 @@ __device__ __forceinline__ void build_runs(const RunParams& p, uint32_t ntiles, 
             at++;
         }
     }
+    // `tl` becomes a pipeline stage next: written by TMA (async proxy) after these reads
+    fence_proxy_async();
     __syncthreads();
 }
 
@@ -163,7 +173,7 @@ gemm_expert_runs_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_c
         tmem_relinquish();
     }
     const uint32_t ntiles = min(p.tiles[0], p.max_tiles);
-    build_runs(p, ntiles, run_first, run_end, runs, scratch, &bars.nruns);  // ends with __syncthreads
+    build_runs(p, ntiles, reinterpret_cast<uint32_t*>(smem_raw), run_first, run_end, runs, scratch, &bars.nruns);  // ends with __syncthreads
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -371,6 +381,7 @@ struct ExpertRunsGemm : hb_kernel {
         const uint32_t max_tiles = hb_moe_tiles(m, d.top_k, d.experts, d.bm);
         if ((size_t)d.experts + (pairs + RN_NMAX - 1) / RN_NMAX > RN_MAX_RUNS)
             return fail(ctx, HB_UNSUPPORTED, name + ": more expert runs than the kernel's table holds");
+        if ((size_t)max_tiles * 12 + 1024 > smem) return fail(ctx, HB_UNSUPPORTED, name + ": the tile table does not fit in the shared memory the kernel stages it in");
         const size_t xrows = d.rows_mode == HB_ROWS_GATHER ? m : pairs;
         if (!range_ok(a[0], (size_t)d.experts * d.n * d.k * 2) || !range_ok(a[1], xrows * d.k * 2) || !range_ok(a[2], (size_t)pairs * n_feat * 2) ||
             !range_ok(a[3], (size_t)pairs * 4) || !range_ok(a[4], (1 + 3 * (size_t)max_tiles) * 4))

@@ -102,7 +102,7 @@ int make_moe_combine(hb_ctx* ctx, uint32_t d, uint32_t top_k, uint32_t f32_sum, 
 int make_ep_move(hb_ctx* ctx, bool ret, uint32_t h, uint32_t top_k, uint32_t experts, uint32_t world, uint32_t rank, uint32_t cap, hb_kernel** out, bool direct = false);
 int make_ep_plan(hb_ctx* ctx, uint32_t experts, uint32_t world, uint32_t rank, uint32_t bm, uint32_t cap, hb_kernel** out, bool direct = false);
 int make_experts_matvec(hb_ctx* ctx, uint32_t k, uint32_t n, uint32_t top_k, uint32_t experts, uint32_t x_row, uint32_t x_stride, uint32_t rows, hb_kernel** out);
-int make_ep_combine(hb_ctx* ctx, uint32_t h, uint32_t top_k, uint32_t world, hb_kernel** out);
+int make_ep_combine(hb_ctx* ctx, uint32_t h, uint32_t top_k, uint32_t world, hb_kernel** out, bool sync = false, uint32_t rank = 0);
 
 // Launches `fn`; with `waits_itself` (the kernel calls griddep_wait before it touches its predecessor's data) and the
 // context's overlap switch on, with programmatic stream serialization.

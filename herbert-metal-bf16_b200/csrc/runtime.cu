@@ -595,6 +595,12 @@ int hb_ep_combine_get(hb_ctx* ctx, uint32_t h, uint32_t top_k, uint32_t world, h
     return hb::make_ep_combine(ctx, h, top_k, world, out);
     HB_GUARD_END(ctx)
 }
+int hb_ep_combine_sync_get(hb_ctx* ctx, uint32_t h, uint32_t top_k, uint32_t world, uint32_t rank, hb_kernel** out) {
+    if (!ctx || !out) return fail(ctx, HB_INVALID, "hb_ep_combine_sync_get: bad argument");
+    HB_GUARD_BIND(ctx)
+    return hb::make_ep_combine(ctx, h, top_k, world, out, true, rank);
+    HB_GUARD_END(ctx)
+}
 int hb_moe_combine_get(hb_ctx* ctx, uint32_t d, uint32_t top_k, uint32_t f32_sum, hb_kernel** out) {
     if (!ctx || !out) return fail(ctx, HB_INVALID, "hb_moe_combine_get: bad argument");
     HB_GUARD_BIND(ctx)

@@ -414,6 +414,7 @@ class EpPeer:
             sizes.update(recv=self.cap * h * 2, ey=self.cap * h * 2)
         if self.fused:
             sizes["landed"] = 256
+            sizes["done"] = 256
         self.pb = PeerBuffers(ctx, rank, world, sizes, dev)
         self.offs_both = [_view(self.pb.local[n], (world, experts + 1), "<i4", dev) for n in ("offs0", "offs1")]
         self.parity = 0
@@ -446,7 +447,10 @@ class EpPeer:
             if self.fused:
                 self.where = torch.zeros(self.pairs, **i32)
                 self.ctl = ctx.alloc(256)  # zeroed: step 0
+                self.ctl_done = ctx.alloc(256)
                 self.k_ep_combine = ctx.ep_combine(h, top_k, world)
+                # the same with the barrier "every rank's outputs are complete" inside (one process per GPU only)
+                self.k_ep_combine_sync = ctx.ep_combine(h, top_k, world, sync_rank=rank) if world > 1 else None
             else:
                 self.ey = torch.zeros(self.pairs, h, device=dev, dtype=torch.bfloat16)
                 self.k_return = ctx.ep_return(h, top_k, experts, world, rank, self.cap)
@@ -501,9 +505,14 @@ class EpPeer:
         self.emit(self.k_gate_up, self.cap, self._w(wgu_local), self.recv, self._w(self.ehb), self._w(self.rlist), self._w(self.rtiles))
         self.emit(self.k_down, self.cap, self._w(wd_local), self._w(self.ehb), self.ey_recv, self._w(self.rlist), self._w(self.rtiles))
 
-    def phase_return(self):  # every rank's expert GEMMs have finished
+    def phase_return(self, sync: bool = False):
+        """Every rank's expert GEMMs have finished; or, fused with sync = True, the combine finds that out itself."""
         if self.fused:
-            self.emit(self.k_ep_combine, self.rows, self.pb.table("ey"), self._w(self.where), self._w(self.route), self._w(self.out))
+            args = [self.pb.table("ey"), self._w(self.where), self._w(self.route), self._w(self.out)]
+            if sync:
+                self.emit(self.k_ep_combine_sync, self.rows, *args, self.pb.table("done"), self.pb.local["done"], self.ctl_done)
+            else:
+                self.emit(self.k_ep_combine, self.rows, *args)
             return self.out
         if not self.plain:
             self.emit(self.k_return, self.rows, self.pb.table("ey"), self._w(self.ey), self._w(self.list), self._w(self.offs_all))
@@ -563,6 +572,8 @@ def _ep_step_body(state: EpPeer, x_local, scores_local, wgu_local, wd_local, gro
     elif multi and not state.fused:
         state.pb.barrier()  # every rank's rows have landed (fused: the dispatch flags it and the plan waits)
     state.phase_experts(wgu_local, wd_local)
+    if multi and state.fused and not nccl_sync and not state.pb.emulated:
+        return state.phase_return(sync=True)  # the combine carries the barrier "every rank's outputs are complete"
     if multi:
         dist.all_reduce(state.token, group=group) if nccl_sync else state.pb.barrier()  # every rank's outputs are complete
     return state.phase_return()

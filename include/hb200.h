@@ -337,6 +337,13 @@ int hb_ep_dispatch_get(hb_ctx* ctx, uint32_t h, uint32_t top_k, uint32_t experts
 int hb_ep_plan_get(hb_ctx* ctx, uint32_t experts, uint32_t world, uint32_t rank, uint32_t bm, uint32_t cap, hb_kernel** out);
 int hb_ep_return_get(hb_ctx* ctx, uint32_t h, uint32_t top_k, uint32_t experts, uint32_t world, uint32_t rank, uint32_t cap, hb_kernel** out);
 int hb_ep_combine_get(hb_ctx* ctx, uint32_t h, uint32_t top_k, uint32_t world, hb_kernel** out);
+/* The combine with the barrier before it ("every rank's expert outputs are complete") inside: bindings peers_ey,
+ * where, route, out, peers_done, done, ctl (peers_done: u64[world], the addresses of every rank's u32[world] flags,
+ * zeroed once; done: this rank's flags; ctl: this rank's u32[2], zeroed once). Its first block stores the step's
+ * number (kept in ctl[0] by the kernel) into flag `rank` of every rank, every block waits (bounded,
+ * hb_set_peer_wait_ms) until all owners' numbers have arrived, then combines. One process per GPU: never launched for
+ * several ranks on one GPU. No counterpart in the reference (one GPU). */
+int hb_ep_combine_sync_get(hb_ctx* ctx, uint32_t h, uint32_t top_k, uint32_t world, uint32_t rank, hb_kernel** out);
 /* The direct form of dispatch and plan: every source owns a fixed region of cap / world rows in every rank's receive
  * and output buffers (source s at row s * cap / world), so a source needs nobody else's counts to place its rows and
  * the all-gather of the offsets before the dispatch falls away. The dispatch delivers this rank's offsets itself, into
