@@ -872,8 +872,23 @@ def bench_extra(hb, ctx, sel, torch, dev, wrap, pk, rank, world, barrier, max_ov
     gr = ctx.record(ops)  # the block as one recorded sequence, as a layer of the prefill step would be
     gr.time(3)
     barrier()
-    sec = max_over_ranks(gr.time(20) / 20)
+    sec_plain = max_over_ranks(gr.time(20) / 20)
     gr.free()
+    out_plain = outb.clone()
+    # the same sequence with overlapped launches: every kernel sets itself up under the tail of the one before and
+    # waits for it inside
+    ctx.set_launch_overlap(True)
+    try:
+        gr = ctx.record(ops)
+    finally:
+        ctx.set_launch_overlap(False)
+    gr.time(3)
+    barrier()
+    sec_over = max_over_ranks(gr.time(20) / 20)
+    gr.free()
+    if not torch.equal(out_plain, outb):
+        raise RuntimeError("moe block: overlapped launches changed the result")
+    sec = min(sec_plain, sec_over)
     wbytes = 2.0 * E * (2 * mi * h + h * mi)
     flop = 2.0 * pairs * (2 * mi) * h + 2.0 * pairs * h * mi
     per_kernel = {}
@@ -906,7 +921,8 @@ def bench_extra(hb, ctx, sel, torch, dev, wrap, pk, rank, world, barrier, max_ov
     except Exception as e:
         out["moe_layer_error"] = repr(e)
     out["moe_2048tok_256e_top8"] = {"us": sec * 1e6, "tile_rows": pick["bm"], "weight_gbs": wbytes / sec / 1e9, "frac_hbm": wbytes / sec / 1e9 / pk["hbm_gbs"],
-                                    "tflops": flop / sec / 1e12, "us_per_kernel": per_kernel}
+                                    "tflops": flop / sec / 1e12, "us_per_kernel": per_kernel,
+                                    "launches_us": {"plain": sec_plain * 1e6, "overlapped": sec_over * 1e6}}
     return out
 
 

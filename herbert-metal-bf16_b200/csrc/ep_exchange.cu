@@ -80,6 +80,8 @@ __device__ __forceinline__ void ep_source_tables(const EpParams& p, uint32_t* fi
 template <bool RETURN>
 __global__ void __launch_bounds__(256) ep_move_kernel(const EpParams p) {
     __shared__ uint32_t first[EP_MAX_WORLD + 1], base[EP_MAX_WORLD];
+    griddep_wait();
+    griddep_launch_dependents();
     ep_source_tables(p, first, base);
     const uint32_t pairs = first[p.world];
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
@@ -157,6 +159,8 @@ struct EpCombineParams {
 
 __global__ void __launch_bounds__(256) ep_combine_kernel(const EpCombineParams p) {
     __shared__ uint64_t ey_s[EP_MAX_WORLD];
+    griddep_wait();  // (before the flag below says that this rank's expert outputs are complete)
+    griddep_launch_dependents();
     if (threadIdx.x < p.world) ey_s[threadIdx.x] = p.peers_ey[threadIdx.x];
     uint32_t step = 0;
     if (p.peers_done) {
@@ -237,6 +241,8 @@ __global__ void __launch_bounds__(PLAN_THREADS) ep_plan_kernel(const PlanParams 
     uint32_t* recvbase = st + p.epr;       // [world] first receive row of source s
     const uint32_t tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const uint32_t stride = p.experts + 1, e0 = p.rank * p.epr;
+    griddep_wait();
+    griddep_launch_dependents();
     // (in the direct form the table was written by the other GPUs' dispatch kernels: it is read from L2, not through a
     // read-only path)
     if (p.landed && tid < p.world) {
@@ -354,9 +360,7 @@ struct EpMove : hb_kernel {
             p.region = cap / world;
             p.peers_offs = static_cast<const uint64_t*>(a[7].ptr);
         }
-        if (ret) ep_move_kernel<true><<<ep_grid(ctx, pairs), 256, 0, ctx->stream>>>(p);
-        else ep_move_kernel<false><<<ep_grid(ctx, pairs), 256, 0, ctx->stream>>>(p);
-        HB_CUDA(ctx, cudaGetLastError());
+        HB_CUDA(ctx, launch_kernel(ctx, true, ret ? ep_move_kernel<true> : ep_move_kernel<false>, dim3(ep_grid(ctx, pairs)), dim3(256), 0, p));
         ctx->launches++;
         return HB_OK;
     }
@@ -390,8 +394,7 @@ struct EpPlan : hb_kernel {
             p.wait_cycles = (long long)ctx->peer_wait_ms * 2000000ll;
         }
         p.region = direct ? cap / world : 0;
-        ep_plan_kernel<<<1, PLAN_THREADS, (3 * epr + world + world * (epr + 1)) * 4, ctx->stream>>>(p);  // start, sa, st, recvbase, offs_s
-        HB_CUDA(ctx, cudaGetLastError());
+        HB_CUDA(ctx, launch_kernel(ctx, true, ep_plan_kernel, dim3(1), dim3(PLAN_THREADS), (3 * epr + world + world * (epr + 1)) * 4, p));  // start, sa, st, recvbase, offs_s
         ctx->launches++;
         return HB_OK;
     }
@@ -426,8 +429,7 @@ struct EpCombine : hb_kernel {
         }
         const size_t items = (size_t)m * p.h8;
         const uint32_t grid = (uint32_t)std::max<size_t>(1, std::min<size_t>((items + 255) / 256, (size_t)ctx->sm_count * 8));
-        ep_combine_kernel<<<grid, 256, 0, ctx->stream>>>(p);
-        HB_CUDA(ctx, cudaGetLastError());
+        HB_CUDA(ctx, launch_kernel(ctx, true, ep_combine_kernel, dim3(grid), dim3(256), 0, p));
         ctx->launches++;
         return HB_OK;
     }

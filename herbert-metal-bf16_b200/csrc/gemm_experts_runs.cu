@@ -172,6 +172,10 @@ gemm_expert_runs_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_c
         tmem_alloc(smem_u32(&bars.tmem_base), TMEM_COLS);
         tmem_relinquish();
     }
+    // (an overlapped launch: barriers and tensor memory are set up under the tail of the kernel before this one; the
+    // table, the list and the token rows are its outputs)
+    griddep_wait();
+    griddep_launch_dependents();
     const uint32_t ntiles = min(p.tiles[0], p.max_tiles);
     build_runs(p, ntiles, reinterpret_cast<uint32_t*>(smem_raw), run_first, run_end, runs, scratch, &bars.nruns);  // ends with __syncthreads
     tc_fence_before();
@@ -411,8 +415,7 @@ struct ExpertRunsGemm : hb_kernel {
         p.max_tiles = max_tiles;
         p.experts = d.experts;
         p.status = ctx->status_dev;
-        fn<<<ctx->sm_count, RN_THREADS, smem, ctx->stream>>>(tm_w, tm_x64, tm_x128, p);
-        HB_CUDA(ctx, cudaGetLastError());
+        HB_CUDA(ctx, launch_kernel(ctx, true, fn, dim3(ctx->sm_count), dim3(RN_THREADS), smem, tm_w, tm_x64, tm_x128, p));
         ctx->launches++;
         return HB_OK;
     }

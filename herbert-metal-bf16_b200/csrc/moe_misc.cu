@@ -53,6 +53,8 @@ __global__ void __launch_bounds__(ROUTE_WARPS * 32) route_topk_kernel(const uint
                                                                       uint32_t experts, uint32_t top_k) {
     __shared__ float vals_s[ROUTE_WARPS][MAXK];
     __shared__ uint32_t chosen_s[ROUTE_WARPS][MAXK];
+    griddep_wait();  // (an overlapped launch: the scores may come from the kernel before this one)
+    griddep_launch_dependents();
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t row = blockIdx.x * ROUTE_WARPS + warp;
     if (row >= rows) return;
@@ -184,6 +186,8 @@ __global__ void __launch_bounds__(256) experts_matvec_kernel(const uint4* __rest
 template <bool F32SUM>
 __global__ void moe_combine_kernel(const uint16_t* __restrict__ y, const uint32_t* __restrict__ route, uint16_t* __restrict__ out, uint32_t rows, uint32_t d,
                                    uint32_t top_k) {
+    griddep_wait();
+    griddep_launch_dependents();
     const uint32_t d8 = d / 8;
     const size_t total = (size_t)rows * d8;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
@@ -265,12 +269,12 @@ struct Route : hb_kernel {
         const uint32_t grid = (m + ROUTE_WARPS - 1) / ROUTE_WARPS, npl = experts / 32;
         const uint16_t* sc = static_cast<const uint16_t*>(a[0].ptr);
         uint32_t* rt = static_cast<uint32_t*>(a[1].ptr);
-        if (npl <= 1) route_topk_kernel<64, 1><<<grid, ROUTE_WARPS * 32, 0, ctx->stream>>>(sc, rt, m, experts, top_k);
-        else if (npl <= 2) route_topk_kernel<64, 2><<<grid, ROUTE_WARPS * 32, 0, ctx->stream>>>(sc, rt, m, experts, top_k);
-        else if (npl <= 4) route_topk_kernel<64, 4><<<grid, ROUTE_WARPS * 32, 0, ctx->stream>>>(sc, rt, m, experts, top_k);
-        else if (npl <= 8) route_topk_kernel<64, 8><<<grid, ROUTE_WARPS * 32, 0, ctx->stream>>>(sc, rt, m, experts, top_k);
-        else if (npl <= 16) route_topk_kernel<64, 16><<<grid, ROUTE_WARPS * 32, 0, ctx->stream>>>(sc, rt, m, experts, top_k);
-        else route_topk_kernel<64, 32><<<grid, ROUTE_WARPS * 32, 0, ctx->stream>>>(sc, rt, m, experts, top_k);
+        if (npl <= 1) HB_CUDA(ctx, launch_kernel(ctx, true, route_topk_kernel<64, 1>, dim3(grid), dim3(ROUTE_WARPS * 32), 0, sc, rt, m, experts, top_k));
+        else if (npl <= 2) HB_CUDA(ctx, launch_kernel(ctx, true, route_topk_kernel<64, 2>, dim3(grid), dim3(ROUTE_WARPS * 32), 0, sc, rt, m, experts, top_k));
+        else if (npl <= 4) HB_CUDA(ctx, launch_kernel(ctx, true, route_topk_kernel<64, 4>, dim3(grid), dim3(ROUTE_WARPS * 32), 0, sc, rt, m, experts, top_k));
+        else if (npl <= 8) HB_CUDA(ctx, launch_kernel(ctx, true, route_topk_kernel<64, 8>, dim3(grid), dim3(ROUTE_WARPS * 32), 0, sc, rt, m, experts, top_k));
+        else if (npl <= 16) HB_CUDA(ctx, launch_kernel(ctx, true, route_topk_kernel<64, 16>, dim3(grid), dim3(ROUTE_WARPS * 32), 0, sc, rt, m, experts, top_k));
+        else HB_CUDA(ctx, launch_kernel(ctx, true, route_topk_kernel<64, 32>, dim3(grid), dim3(ROUTE_WARPS * 32), 0, sc, rt, m, experts, top_k));
         HB_CUDA(ctx, cudaGetLastError());
         ctx->launches++;
         return HB_OK;
@@ -331,11 +335,8 @@ struct MoeCombine : hb_kernel {
             return fail(ctx, HB_INVALID, name + ": a bound range is too small");
         if ((reinterpret_cast<uintptr_t>(a[0].ptr) | reinterpret_cast<uintptr_t>(a[2].ptr)) & 15u) return fail(ctx, HB_INVALID, name + ": y and out must be 16-byte aligned");
         const uint32_t grid = grid_for(ctx, (size_t)m * (d / 8), 256);
-        if (f32_sum)
-            moe_combine_kernel<true><<<grid, 256, 0, ctx->stream>>>(static_cast<const uint16_t*>(a[0].ptr), static_cast<const uint32_t*>(a[1].ptr), static_cast<uint16_t*>(a[2].ptr), m, d, top_k);
-        else
-            moe_combine_kernel<false><<<grid, 256, 0, ctx->stream>>>(static_cast<const uint16_t*>(a[0].ptr), static_cast<const uint32_t*>(a[1].ptr), static_cast<uint16_t*>(a[2].ptr), m, d, top_k);
-        HB_CUDA(ctx, cudaGetLastError());
+        HB_CUDA(ctx, launch_kernel(ctx, true, f32_sum ? moe_combine_kernel<true> : moe_combine_kernel<false>, dim3(grid), dim3(256), 0, static_cast<const uint16_t*>(a[0].ptr),
+                                   static_cast<const uint32_t*>(a[1].ptr), static_cast<uint16_t*>(a[2].ptr), m, d, top_k));
         ctx->launches++;
         return HB_OK;
     }

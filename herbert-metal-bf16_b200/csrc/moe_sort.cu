@@ -286,6 +286,8 @@ __global__ void __cluster_dims__(CS_CTAS, 1, 1) __launch_bounds__(CS_THREADS) mo
 
     for (uint32_t i = tid; i < experts * p.words; i += CS_THREADS) mask[i] = 0;
     if (tid == 0) dup_s = 0;
+    griddep_wait();  // (an overlapped launch: the route is the output of the kernel before this one)
+    griddep_launch_dependents();
     // the experts of this CTA's rows
     const uint32_t* rt = p.route + (size_t)r0 * 2 * top_k;
     if (top_k % 4 == 0 && (reinterpret_cast<uintptr_t>(p.route) & 15u) == 0) {
@@ -438,8 +440,7 @@ struct MoeSort : hb_kernel {
             c.rows_per_cta = ((m + CS_CTAS - 1) / CS_CTAS + 31) / 32 * 32;
             c.words = cl_words;
             c.ex_cap = cl_ex_cap;
-            moe_sort_cluster_kernel<<<CS_CTAS, CS_THREADS, cl_smem, ctx->stream>>>(c);
-            HB_CUDA(ctx, cudaGetLastError());
+            HB_CUDA(ctx, launch_kernel(ctx, true, moe_sort_cluster_kernel, dim3(CS_CTAS), dim3(CS_THREADS), cl_smem, c));
             ctx->launches++;
             return HB_OK;
         }

@@ -174,6 +174,20 @@ def test_moe_layer_forms_agree_bitwise(ctx, hb200, oracle):
         assert np.array_equal(outs[0], o)
 
 
+@pytest.mark.parametrize("shape", [(100, 256, 192, 32, 8, 16), (600, 128, 160, 32, 16, 64), (2048, 2048, 512, 256, 8, 64)])
+def test_moe_layer_with_overlapped_launches(ctx, hb200, oracle, shape):
+    """hb_set_launch_overlap: every kernel of the block is launched before the one before it has finished and waits for
+    it inside; the same checks, and the same bits as with plain launches."""
+    plain = moe_layer(ctx, hb200, oracle, *shape, merge_runs=1)
+    ctx.set_launch_overlap(True)
+    try:
+        for _ in range(2):
+            over = moe_layer(ctx, hb200, oracle, *shape, merge_runs=1)
+            assert np.array_equal(plain, over)
+    finally:
+        ctx.set_launch_overlap(False)
+
+
 @pytest.mark.parametrize("merge_runs", [0, 1])
 def test_config5_full_size(ctx, hb200, oracle, merge_runs):
     # hidden 2048, 256 experts, top-8, expert intermediate 512, 2048 tokens
