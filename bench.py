@@ -235,7 +235,7 @@ def main():
     ap.add_argument("--no-extra", action="store_true", help="skip the matvec / MoE / tensor-parallel sections")
     ap.add_argument("--tune", default="", help="engine tune keys, e.g. gemm.auto=0 to skip the load-time timing")
     ap.add_argument("--form", default="", choices=["", "pair", "sk", "one"], help="with --case gate_up/down/layer: the GEMM form (one = one CTA per 128x256 tile)")
-    ap.add_argument("--case", default="", choices=["", "layer", "gate_up", "down", "matvec", "matvec8", "moe", "q4", "q4m8"],
+    ap.add_argument("--case", default="", choices=["", "layer", "gate_up", "down", "down512k2", "matvec", "matvec8", "matvec8fit", "moe", "q4", "q4m8", "q4gemm512"],
                     help="run one small case of one kernel a few times and exit (the command profiled under ncu)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
@@ -549,14 +549,32 @@ def run_case(args):
         kq = ctx.matmul_q4(k, n, mq) if mq > 1 else ctx.matvec_q4(k, n, 0, 2)
         ops = [(kq, mq, wrap(wq), wrap(x), wrap(y), wrap(sq))]
         work = {"bytes": blocks * 18.0 + mq * (2.0 * k + 2.0 * n)}
-    elif args.case in ("matvec", "matvec8"):
+    elif args.case == "down512k2":
+        # a short prefill block on the CTA-pair kernel with K cut in two: 512 rows of the down projection
+        k, n, rows = INTER, HIDDEN, 512
+        w, x, y = rnd(n, k, scale=k**-0.5), rnd(rows, k), rnd(rows, n)
+        torch.cuda.synchronize()
+        ops = [(ctx.gemm(k, n, 2, rows_max=rows, cta_pair=1, split_k=2), rows, wrap(w), wrap(x), wrap(y))]
+        work = {"flop": 2.0 * rows * k * n}
+    elif args.case == "q4gemm512":
+        # the prefill GEMM from Q4_0 weights that decodes while it stages: 512 rows of gate/up (56.6 MB of nibbles and scales)
+        k, n, rows = HIDDEN, 2 * INTER, 512
+        blocks = n * k // 32
+        wq = torch.randint(0, 256, (blocks * 16,), device=dev, dtype=torch.uint8, generator=g)
+        sq = (torch.rand(blocks, device=dev, generator=g) * 0.01 + 0.001).half()
+        x, y = rnd(rows, k), torch.zeros(rows, n, device=dev, dtype=torch.bfloat16)
+        torch.cuda.synchronize()
+        ops = [(ctx.gemm_q4(k, n, 0, tile_n=256, rows_max=rows), rows, wrap(wq), wrap(x), wrap(y), wrap(sq))]
+        work = {"flop": 2.0 * rows * k * n}
+    elif args.case in ("matvec", "matvec8", "matvec8fit"):
         m = 1 if args.case == "matvec" else 8
         k, n = 4096, 151936
         w, x = rnd(n, k, scale=k**-0.5), rnd(8, k)
         y = torch.zeros(8, n, device=dev, dtype=torch.bfloat16)
         torch.cuda.synchronize()
         # one row: a warp per two weight rows on the CUDA cores; eight rows: the weight stream on the tensor cores
-        kern = ctx.matvec(k, n, 0, rows_max=m, rows_per_warp=2, split=2) if m == 1 else ctx.matvec(k, n, 0, rows_max=m, tensor_core=1, split=4)
+        kern = (ctx.matvec(k, n, 0, rows_max=m, rows_per_warp=2, split=2) if m == 1 else
+                ctx.matvec(k, n, 0, rows_max=m, tensor_core=3 if args.case == "matvec8fit" else 1, split=4))
         ops = [(kern, m, wrap(w), wrap(x), wrap(y))]
         work = {"bytes": 2.0 * (n * k + m * k + m * n)}
     else:
