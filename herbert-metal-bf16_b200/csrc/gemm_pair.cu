@@ -71,12 +71,17 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar), "h"(mask) : "memory");
 }
 
-template <int OUT>
+template <int OUT, int BN>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant__ CUtensorMap tm_w, const GemmParams p) {
-    constexpr uint32_t TMEM_COLS = 2 * PAIR_BN;  // two accumulators of 256 columns (this CTA's 128 rows of each)
-    constexpr uint32_t IDESC = umma_idesc_bf16(256, PAIR_BN);
-    constexpr int HALF = PAIR_BN / 2;
+    // BN: the tile's columns, 256 or 192 (a narrower tile where 256 columns leave the last wave of pairs nearly empty:
+    // 2048 x 5120 is 160 tiles of 256 x 256 for 74 pairs, 2.2 waves run as 3, and 216 tiles of 256 x 192, 2.9 waves
+    // of three quarters the length). A stage keeps its 32 KB slots; the W box is BN / 2 rows.
+    static_assert(BN == 256 || BN == 192, "tile columns");
+    constexpr uint32_t TMEM_COLS = 512;  // two accumulators of BN columns (this CTA's 128 rows of each), a power of two
+    constexpr uint32_t IDESC = umma_idesc_bf16(256, BN);
+    constexpr int HALF = BN / 2;
+    constexpr uint32_t STAGE_TX = 2u * (A_BYTES + HALF * BK * 2);  // both CTAs' bytes of one stage
 
     extern __shared__ uint8_t smem_raw[];
     __shared__ GemmBarriers bars;
@@ -131,7 +136,7 @@ gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                 const int row_x = (int)(tm * 256 + rank * 128);
                 int row_w;
                 if constexpr (OUT == HB_OUT_SWIGLU) row_w = (int)(rank * p.n_out + tn * HALF);  // rank 0: gate rows, rank 1: up rows
-                else row_w = (int)(tn * PAIR_BN + rank * HALF);
+                else row_w = (int)(tn * BN + rank * HALF);
                 const uint32_t kb0 = slice * p.k_blocks / nsplit, kb1 = (slice + 1) * p.k_blocks / nsplit;
                 for (uint32_t kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(smem_u32(&bars.empty[s]), ph ^ 1u)) {
@@ -141,7 +146,7 @@ gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                     }
                     const uint32_t full_leader = map_to_cta(smem_u32(&bars.full[s]), 0);
                     const uint32_t a_dst = smem_base + s * PAIR_STAGE_BYTES;
-                    if (rank == 0) mbar_arrive_expect_tx(smem_u32(&bars.full[s]), 2 * PAIR_STAGE_BYTES);  // both CTAs' bytes
+                    if (rank == 0) mbar_arrive_expect_tx(smem_u32(&bars.full[s]), STAGE_TX);
                     tma_load_2d_pair(a_dst, &tm_x, full_leader, (int)(kb * BK), row_x);
                     tma_load_2d_pair(a_dst + A_BYTES, &tm_w, full_leader, (int)(kb * BK), row_w);
                     if (++s == S) { s = 0; ph ^= 1u; }
@@ -162,7 +167,7 @@ gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                     break;
                 }
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + acc * PAIR_BN;
+                const uint32_t d_tmem = tmem_base + acc * BN;
                 for (uint32_t kb = kb0; kb < kb1; ++kb) {
                     if (!mbar_wait(smem_u32(&bars.full[s]), ph)) {
                         report(p.status, ST_WAIT_TIMEOUT, WHERE_FULL, s);
@@ -198,7 +203,7 @@ gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
             }
             tc_fence_after();
             const uint32_t row = tm * 256 + rank * 128 + q * 32 + lane;
-            const uint32_t t_addr = tmem_base + ((q * 32u) << 16) + acc * PAIR_BN;
+            const uint32_t t_addr = tmem_base + ((q * 32u) << 16) + acc * BN;
             if (nsplit > 1) {
                 // The slices of a tile hand a running f32 sum from one to the next through one block of scratch per
                 // quarter of a CTA's half tile: slice 0 stores its accumulator, slice s adds its own to what the slices
@@ -206,7 +211,7 @@ gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                 // so they are running or finished), the last slice applies the output mode. The order of the sum is
                 // the order of the slices, whoever runs when. 16-byte piece j of 32-column chunk c of the lane's row is
                 // slot (c * 8 + j) * 32 + lane of the block: a warp's access is 512 contiguous bytes.
-                constexpr uint32_t BLOCK16 = 32 * PAIR_BN / 4;  // 16-byte slots of a 32 x 256 f32 block
+                constexpr uint32_t BLOCK16 = 32 * BN / 4;  // 16-byte slots of a 32 x 256 f32 block
                 const uint32_t which = (tile * 2 + rank) * 4 + q;
                 uint4* buf = reinterpret_cast<uint4*>(p.partial) + (size_t)which * BLOCK16 + lane;
                 uint32_t* flag = p.split_counters + which;  // slices of this quarter done so far
@@ -230,7 +235,7 @@ gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                 // own accumulator chunk c plus the running sum (if any): v[] as f32 bits. A chunk's loads of the running
                 // sum take about a microsecond to come back, so AHEAD chunks are in flight at any time (the loops are
                 // unrolled: the ring of registers is indexed at compile time).
-                constexpr int NCHUNK = PAIR_BN / 32;
+                constexpr int NCHUNK = BN / 32;
                 constexpr int AHEAD = OUT == HB_OUT_SWIGLU ? 3 : 4;
                 uint4 ahead[AHEAD][8];
                 auto ask = [&](int slot, int c) {
@@ -278,7 +283,7 @@ gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                     for (int c = 0; c < NCHUNK; ++c) {
                         uint32_t v[32];
                         chunk(c, v);
-                        store_chunk<OUT>(p, row, tn * PAIR_BN + c * 32, v, v);
+                        store_chunk<OUT>(p, row, tn * BN + c * 32, v, v);
                     }
                 }
                 tc_fence_before();
@@ -302,14 +307,14 @@ gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                 }
             } else {
 #pragma unroll 1
-                for (int c = 0; c < PAIR_BN / 32; ++c) {
+                for (int c = 0; c < BN / 32; ++c) {
                     uint32_t v[32];
                     tmem_ld_32x32(t_addr + c * 32, v);
                     tmem_ld_wait();
                     if (OUT == HB_OUT_F32 && p.y_shards)  // row blocks, possibly on other GPUs: whole row segments per store
-                        store_chunk_f32_blocks(p, row - lane, tn * PAIR_BN + c * 32, v, smem_base + S * PAIR_STAGE_BYTES + q * 4096u);
+                        store_chunk_f32_blocks(p, row - lane, tn * BN + c * 32, v, smem_base + S * PAIR_STAGE_BYTES + q * 4096u);
                     else
-                        store_chunk<OUT>(p, row, tn * PAIR_BN + c * 32, v, v);
+                        store_chunk<OUT>(p, row, tn * BN + c * 32, v, v);
                 }
             }
             tc_fence_before();
@@ -346,15 +351,17 @@ namespace {
 
 typedef void (*pair_fn)(const CUtensorMap, const CUtensorMap, const GemmParams);
 
-pair_fn pair_pick(uint32_t out) {
+template <int BN>
+pair_fn pair_pick_bn(uint32_t out) {
     switch (out) {
-        case HB_OUT_BF16: return gemm_bf16_tn_pair_kernel<HB_OUT_BF16>;
-        case HB_OUT_F32: return gemm_bf16_tn_pair_kernel<HB_OUT_F32>;
-        case HB_OUT_RESIDUAL: return gemm_bf16_tn_pair_kernel<HB_OUT_RESIDUAL>;
-        case HB_OUT_SWIGLU: return gemm_bf16_tn_pair_kernel<HB_OUT_SWIGLU>;
+        case HB_OUT_BF16: return gemm_bf16_tn_pair_kernel<HB_OUT_BF16, BN>;
+        case HB_OUT_F32: return gemm_bf16_tn_pair_kernel<HB_OUT_F32, BN>;
+        case HB_OUT_RESIDUAL: return gemm_bf16_tn_pair_kernel<HB_OUT_RESIDUAL, BN>;
+        case HB_OUT_SWIGLU: return gemm_bf16_tn_pair_kernel<HB_OUT_SWIGLU, BN>;
     }
     return nullptr;
 }
+pair_fn pair_pick(uint32_t out, uint32_t bn) { return bn == 192 ? pair_pick_bn<192>(out) : pair_pick_bn<256>(out); }
 
 struct PairGemm : hb_kernel {
     hb_gemm_desc d{};
@@ -376,7 +383,7 @@ struct PairGemm : hb_kernel {
         if (!range_ok(a[0], (size_t)d.n * d.k * 2) || !range_ok(a[1], (size_t)m * d.k * 2) || !range_ok(a[2], ybytes))
             return fail(ctx, HB_INVALID, name + ": a bound range is too small for " + std::to_string(m) + " rows");
         if (a[0].ptr != last_w || a[1].ptr != last_x || m != last_m) {
-            int r = make_tmap_bf16(ctx, &tm_w, a[0].ptr, d.n, d.k, 128);
+            int r = make_tmap_bf16(ctx, &tm_w, a[0].ptr, d.n, d.k, d.tile_n / 2);  // a CTA's half of the tile's columns
             if (r != HB_OK) return r;
             r = make_tmap_bf16(ctx, &tm_x, a[1].ptr, m, d.k, 128);
             if (r != HB_OK) return r;
@@ -391,7 +398,7 @@ struct PairGemm : hb_kernel {
         p.n_out = n_out;
         p.k_blocks = (d.k + BK - 1) / BK;
         p.tiles_m = (m + 255) / 256;
-        const uint32_t cols_per_tile = d.out == HB_OUT_SWIGLU ? PAIR_BN / 2 : PAIR_BN;
+        const uint32_t cols_per_tile = d.out == HB_OUT_SWIGLU ? d.tile_n / 2 : d.tile_n;
         p.tiles_n = (n_out + cols_per_tile - 1) / cols_per_tile;
         p.num_tiles = p.tiles_m * p.tiles_n;
         p.stages = stages;
@@ -475,7 +482,9 @@ static int ensure_split_scratch(hb_ctx* ctx, const hb_gemm_desc* d, uint32_t* ro
 
 int make_gemm_pair(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
     *out = nullptr;
-    if (d->tile_n != 0 && d->tile_n != 256) return fail(ctx, HB_UNSUPPORTED, "gemm: the CTA-pair form has 256 x 256 tiles only");
+    if (d->tile_n != 0 && d->tile_n != 256 && d->tile_n != 192) return fail(ctx, HB_UNSUPPORTED, "gemm: the CTA-pair form has tiles of 256 x 256 or 256 x 192");
+    const uint32_t bn = d->tile_n == 192 ? 192u : 256u;
+    if (bn != 256 && d->split_k > 1) return fail(ctx, HB_UNSUPPORTED, "gemm: split_k is built for the 256 x 256 tile");
     if (d->y_shards > 1 && d->out != HB_OUT_F32) return fail(ctx, HB_UNSUPPORTED, "gemm: a Y in row blocks is for f32 partial products (Out::F32)");
     if (d->y_shards > 16) return fail(ctx, HB_UNSUPPORTED, "gemm: at most 16 row blocks of Y");
     if (d->y_group_rows) {
@@ -487,7 +496,7 @@ int make_gemm_pair(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
         if (d->y_signal > d->y_shards) return fail(ctx, HB_UNSUPPORTED, "gemm: y_signal is this rank's number + 1, at most y_shards");
     }
     if (d->split_k > 1 && (d->y_shards > 1 || d->split_k > 64)) return fail(ctx, HB_UNSUPPORTED, "gemm: split_k is 2..64 slices of K, not together with a Y in row blocks");
-    pair_fn fn = pair_pick(d->out);
+    pair_fn fn = pair_pick(d->out, bn);
     const size_t budget = std::min<size_t>(ctx->smem_optin, 227 * 1024) - 2048;
     // a Y in row blocks: 16 KB behind the ring (4 KB per epilogue warp) for the transposing store
     const size_t extra = d->y_shards > 1 ? 4 * 4096 : 0;
@@ -496,7 +505,7 @@ int make_gemm_pair(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
     if (stages < 2 || stages > max_stages) return fail(ctx, HB_UNSUPPORTED, "gemm: stage count does not fit");
     auto k = std::make_unique<PairGemm>();
     k->d = *d;
-    k->d.tile_n = 256;
+    k->d.tile_n = bn;
     k->fn = fn;
     k->stages = stages;
     k->smem = (size_t)stages * PAIR_STAGE_BYTES + extra + 1024;
@@ -509,7 +518,7 @@ int make_gemm_pair(hb_ctx* ctx, const hb_gemm_desc* d, hb_kernel** out) {
     if (d->y_group_rows) ytag += "g" + std::to_string(d->y_group_rows);
     if (d->y_signal) ytag += "_sig" + std::to_string(d->y_signal - 1);
     if (d->split_k > 1) ytag += "_k" + std::to_string(d->split_k);
-    snprintf(nm, sizeof nm, "gemm_pair_%ux%u_%s%s_t256x256_s%u%s", d->k, d->n, out_tag(d->out), d->m_first && !d->y_signal ? "_mf" : "", stages, ytag.c_str());
+    snprintf(nm, sizeof nm, "gemm_pair_%ux%u_%s%s_t256x%u_s%u%s", d->k, d->n, out_tag(d->out), d->m_first && !d->y_signal ? "_mf" : "", bn, stages, ytag.c_str());
     k->name = nm;
     if (hb_kernel* have = find(ctx, k->name)) {
         auto* g = static_cast<PairGemm*>(have);

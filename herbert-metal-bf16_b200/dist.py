@@ -601,6 +601,24 @@ def _ep_step_body(state: EpPeer, x_local, scores_local, wgu_local, wd_local, gro
 TP_GROUP_ROWS, TP_MAX_GROUPS, TP_CTL_WORDS = 256, 64, 128  # the CTA pair's row tile; HB_TP_MAX_GROUPS; HB_TP_CTL_WORDS
 
 
+def pair_tile_n(ctx, m: int, k: int, n: int, out: int, w, x, y) -> int:
+    """The CTA-pair tile's columns, 256 or 192, whichever is faster on these very operands (plain output into y, which
+    is scratch here): 2048 x 5120 is 160 tiles of 256 x 256 for 74 pairs, 2.2 waves run as 3, and 216 tiles of
+    256 x 192, 2.9 waves of three quarters the length; but the narrower tile moves more bytes into the SMs per FLOP,
+    so where the waves do not decide, it loses (K = 2176: 50 against 60 us; K = 8704: no difference; the gate/up GEMM
+    at 2048 x 5120 x 17408: 285 against 253 us). Timed, not modelled: three rounds of five launches, the median."""
+    wrap = lambda t: ctx.wrap(t.data_ptr(), t.numel() * t.element_size())
+    best, best_t = 256, None
+    for bn in (256, 192):
+        kern = ctx.gemm(k, n, out, rows_max=m, cta_pair=1, tile_n=bn)
+        op = (kern, m, wrap(w), wrap(x), wrap(y))
+        ctx.time([op], 2)
+        t = sorted(ctx.time([op], 5) for _ in range(3))[1]
+        if best_t is None or t < 0.97 * best_t:  # the narrower tile has to win by a margin
+            best, best_t = bn, t
+    return best
+
+
 class TpPeer:
     """One rank of the peer-memory FFN: the partial-product buffer, the output Y and their peer tables.
 
@@ -619,8 +637,10 @@ class TpPeer:
     Measured for the 27B-class FFN (2048 rows), push against pull: 449 against 483 us on two B200s, 220 against 259 us
     on eight. (The pushed stores leave as whole 128-byte row segments: one 16-byte piece per lane took 537 and 437 us.)"""
 
-    def __init__(self, hb, ctx, rank: int, world: int, m: int, h: int, out: int = OUT_RESIDUAL, device=None, push: bool | None = None, mode: str | None = None):
+    def __init__(self, hb, ctx, rank: int, world: int, m: int, h: int, out: int = OUT_RESIDUAL, device=None, push: bool | None = None, mode: str | None = None,
+                 tune_tiles: bool = True):
         self.hb, self.ctx, self.rank, self.world, self.m, self.h, self.out = hb, ctx, rank, world, m, h, out
+        self.tune_tiles, self.tile_n = tune_tiles, (256, 256)
         dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
         if mode is None:
             mode = ("push" if push else "pull") if push is not None else "push"
@@ -695,8 +715,15 @@ class TpPeer:
         if key not in self.kernels:
             hmid = torch.empty((self.m, ip), device=x.device, dtype=torch.bfloat16)
             form = {"pull": {}, "push": dict(y_shards=self.world), "stream": dict(y_shards=self.world, y_group_rows=TP_GROUP_ROWS, y_signal=self.rank + 1)}[self.mode]
-            self.kernels[key] = (self.ctx.gemm(h, 2 * ip, OUT_SWIGLU, rows_max=self.m, cta_pair=1),
-                                 self.ctx.gemm(ip, h, OUT_F32, rows_max=self.m, cta_pair=1, **form), hmid)
+            # the tile width of each GEMM is chosen by timing both on these operands (plain local outputs: nothing of a
+            # peer's is touched)
+            tn_gu = pair_tile_n(self.ctx, self.m, h, 2 * ip, OUT_SWIGLU, wgu_local, x[: self.m], hmid) if self.tune_tiles else 256
+            tmp = torch.empty((self.m, h), device=x.device, dtype=torch.float32) if self.tune_tiles else None
+            tn_dn = pair_tile_n(self.ctx, self.m, ip, h, OUT_F32, wd_local, hmid, tmp) if self.tune_tiles else 256
+            del tmp
+            self.tile_n = (tn_gu, tn_dn)
+            self.kernels[key] = (self.ctx.gemm(h, 2 * ip, OUT_SWIGLU, rows_max=self.m, cta_pair=1, tile_n=tn_gu),
+                                 self.ctx.gemm(ip, h, OUT_F32, rows_max=self.m, cta_pair=1, tile_n=tn_dn, **form), hmid)
         k_gu, k_down, hmid = self.kernels[key]
         self.emit(k_gu, m, self._w(wgu_local), self._w(x), self._w(hmid))
         if self.mode == "stream":

@@ -301,6 +301,7 @@ struct DenseForm {
 const DenseForm kDenseForms[] = {
     {"t128x256", 256, 0, 0, 0}, {"t128x128", 128, 0, 0, 0}, {"t128x64", 64, 0, 0, 0},   {"t128x256n", 256, 0, 1, 0}, {"t128x128n", 128, 0, 1, 0},
     {"sk128x256", 256, 0, 0, 1}, {"sk128x128", 128, 0, 0, 1}, {"sk128x64", 64, 0, 0, 1}, {"pair256x256", 256, 1, 0, 0},
+    {"pair256x192", 192, 1, 0, 0},
 };
 
 }  // namespace
@@ -590,11 +591,11 @@ int hb_select_gate_up(hb_selector* s, uint32_t k, uint32_t inter, hb_range w, hb
                 add_op(c0, ap[1], {gu, h});
                 cands.push_back(std::move(c0));
                 eligible.push_back(1);
-                for (uint32_t form = 0; form < 7; ++form) {
-                    const uint32_t pair = form == 6 ? 1u : 0u;
-                    const uint32_t tn = pair ? 256u : 256u >> (form % 3), sk = pair ? 0u : form / 3;
+                for (uint32_t form = 0; form < 8; ++form) {
+                    const uint32_t pair = form >= 6 ? 1u : 0u;
+                    const uint32_t tn = pair ? (form == 6 ? 256u : 192u) : 256u >> (form % 3), sk = pair ? 0u : form / 3;
                     hb_kernel* f = nullptr;
-                    const std::string name = pair ? std::string("fusedpair256x256") : std::string(sk ? "fusedsk128x" : "fused128x") + std::to_string(tn);
+                    const std::string name = pair ? "fusedpair256x" + std::to_string(tn) : std::string(sk ? "fusedsk128x" : "fused128x") + std::to_string(tn);
                     if (get_dense(s, k, 2 * inter, HB_OUT_SWIGLU, tn, 0, mf, pair, rows_max, &f, sk) != HB_OK) {
                         say(s, "[autotune] gate_up " + key + ": " + name + " not built (" + hb_last_error(ctx) + ")");
                         continue;

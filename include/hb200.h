@@ -164,7 +164,8 @@ typedef struct {
     uint32_t top_k;     /* GATHER: slots per token row */
     uint32_t experts;   /* GATHER/SCATTER */
     uint32_t bm;        /* GATHER/SCATTER: rows of an expert tile, 16/32/64 (moe.tile) */
-    uint32_t tile_n;    /* DENSE: accumulator columns per tile, 64/128/256 (0 = default 256) */
+    uint32_t tile_n;    /* DENSE: accumulator columns per tile, 64/128/256 (0 = default 256); with cta_pair also 192
+                           (256 x 192 tiles: for shapes whose 256 x 256 tiles leave the last wave of SM pairs nearly empty) */
     uint32_t stages;    /* shared-memory pipeline depth, 0 = as many as fit */
     uint32_t cta_pair;  /* DENSE: 1 = two CTAs share a 256-row tile (tcgen05 cta_group::2) */
     uint32_t m_first;   /* tile order: 1 = walk the row tiles of a column tile first (gemm.mfirst, prefill.rs:26-42) */

@@ -68,15 +68,16 @@ def test_stream_k_repeated_launches_and_config1(ctx, oracle):
         assert np.array_equal(first, d_y.download(np.uint16, (m, n)))  # a fixed summation order: the same bits every run
 
 
+@pytest.mark.parametrize("tile_n", [256, 192])
 @pytest.mark.parametrize("out", MODES)
 @pytest.mark.parametrize("m,k,n", [(300, 320, 520), (256, 64, 256), (1, 64, 72), (683, 1024, 1000), (2048, 4096, 1024), (257, 72, 40)])
-def test_cta_pair_form(ctx, oracle, out, m, k, n):
-    # two CTAs of a cluster share a 256 x 256 tile (tcgen05 cta_group::2): rows and columns that fill only one CTA's
-    # half, ragged extents, every output mode
+def test_cta_pair_form(ctx, oracle, out, m, k, n, tile_n):
+    # two CTAs of a cluster share a 256 x 256 (or 256 x 192) tile (tcgen05 cta_group::2): rows and columns that fill only
+    # one CTA's half, ragged extents, every output mode
     if out == OUT_SWIGLU and n % 2:
         pytest.skip("odd n")
-    kern, (x, w, y0), got = run_gemm(ctx, oracle, m, k, n, out, cta_pair=1)
-    assert kern.name.startswith("gemm_pair_")
+    kern, (x, w, y0), got = run_gemm(ctx, oracle, m, k, n, out, cta_pair=1, tile_n=tile_n)
+    assert kern.name.startswith("gemm_pair_") and f"_t256x{tile_n}_" in kern.name
     within_contract(oracle, oracle.gemm_f64(x, w, out, y0), got, kern.name)
 
 
@@ -128,7 +129,8 @@ def test_cta_pair_matches_single_cta_bits(ctx, oracle):
     m, k, n = 512, 2048, 768
     a = run_gemm(ctx, oracle, m, k, n, OUT_BF16, cta_pair=1)[2]
     b = run_gemm(ctx, oracle, m, k, n, OUT_BF16, tile_n=256)[2]
-    assert np.array_equal(a, b)
+    c = run_gemm(ctx, oracle, m, k, n, OUT_BF16, cta_pair=1, tile_n=192)[2]
+    assert np.array_equal(a, b) and np.array_equal(a, c)
 
 
 def test_config1_dense_gemm(ctx, oracle):
