@@ -16,6 +16,7 @@ namespace hb {
 
 constexpr int TP_MAX_WORLD = 8;
 constexpr long long TP_CYCLES_PER_MS = 2000000ll;  // clock64 counts SM cycles: at most 2 GHz
+constexpr uint32_t TP_START_WORD = 16;  // of a rank's `done` words: [0, world) the closing handshake, [16, 16 + world) the opening barrier
 
 struct TpParams {
     const float* staging;       // STAGED: this rank's f32 [world][rows_per][n], slot s from rank s
@@ -111,57 +112,84 @@ __global__ void __launch_bounds__(128) tp_sum_stream_kernel(const TpStreamParams
     __syncthreads();
     const uint32_t step = step_s;
     const size_t slot_units = (size_t)p.groups * p.group_part * p.n8;  // units of 8 elements in one source's slot
-    for (uint32_t g = 0; g < p.groups; ++g) {
-        if (p.sync) {
+    // one unit: 8 elements of row j of this rank's part of group g
+    auto unit = [&](uint32_t g, uint32_t row0, uint32_t i) {
+        const uint32_t j = i / p.n8, c = i - j * p.n8;
+        const size_t src = ((size_t)g * p.group_part + j) * p.n8 + c;
+        const size_t at = (size_t)(row0 + j) * p.n8 + c;
+        float4 part[TP_MAX_WORLD][2];
+#pragma unroll
+        for (uint32_t s = 0; s < TP_MAX_WORLD; ++s) {
+            if (s < p.world) {
+                const float4* q = reinterpret_cast<const float4*>(p.staging) + (s * slot_units + src) * 2;
+                part[s][0] = __ldcs(q);
+                part[s][1] = __ldcs(q + 1);
+            }
+        }
+        float v[8] = {part[0][0].x, part[0][0].y, part[0][0].z, part[0][0].w, part[0][1].x, part[0][1].y, part[0][1].z, part[0][1].w};
+#pragma unroll
+        for (uint32_t s = 1; s < TP_MAX_WORLD; ++s) {
+            if (s < p.world) {
+                v[0] = __fadd_rn(v[0], part[s][0].x); v[1] = __fadd_rn(v[1], part[s][0].y);
+                v[2] = __fadd_rn(v[2], part[s][0].z); v[3] = __fadd_rn(v[3], part[s][0].w);
+                v[4] = __fadd_rn(v[4], part[s][1].x); v[5] = __fadd_rn(v[5], part[s][1].y);
+                v[6] = __fadd_rn(v[6], part[s][1].z); v[7] = __fadd_rn(v[7], part[s][1].w);
+            }
+        }
+        uint32_t o[8];
+        if (OUT == HB_OUT_RESIDUAL) {
+            const uint4 old = reinterpret_cast<const uint4*>(y_s[p.rank])[at];
+            const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                o[2 * e] = f32_to_bf16(__fadd_rn(bf16_to_f32(ow[e] & 0xffffu), round_bf16(v[2 * e])));
+                o[2 * e + 1] = f32_to_bf16(__fadd_rn(bf16_to_f32(ow[e] >> 16), round_bf16(v[2 * e + 1])));
+            }
+        } else {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) o[e] = f32_to_bf16(v[e]);
+        }
+        const uint4 res = make_uint4(o[0] | (o[1] << 16), o[2] | (o[3] << 16), o[4] | (o[5] << 16), o[6] | (o[7] << 16));
+        for (uint32_t d = 0; d < p.world; ++d) reinterpret_cast<uint4*>(y_s[d])[at] = res;
+    };
+    if (p.sync == 1) {
+        // group by group, each as soon as every rank's GEMM has flagged it
+        for (uint32_t g = 0; g < p.groups; ++g) {
             if (threadIdx.x < p.world && !wait_for_step(p.flags + threadIdx.x * TP_MAX_GROUPS + g, step, p.wait_cycles)) {
                 report(p.status, ST_WAIT_TIMEOUT, WHERE_PEER, threadIdx.x);
                 ok_s = 0u;
             }
             __syncthreads();
             if (!ok_s) break;
+            const uint32_t row0 = g * p.group_rows + p.rank * p.group_part;
+            if (row0 >= p.m) continue;
+            const uint32_t units = min(p.group_part, p.m - row0) * p.n8;
+            for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < units; i += gridDim.x * blockDim.x) unit(g, row0, i);
         }
-        const uint32_t row0 = g * p.group_rows + p.rank * p.group_part;
-        if (row0 >= p.m) continue;
-        const uint32_t rows = min(p.group_part, p.m - row0);
-        const uint32_t units = rows * p.n8;
-        for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < units; i += gridDim.x * blockDim.x) {
-            const uint32_t j = i / p.n8, c = i - j * p.n8;
-            const size_t src = ((size_t)g * p.group_part + j) * p.n8 + c;
-            const size_t at = (size_t)(row0 + j) * p.n8 + c;
-            float4 part[TP_MAX_WORLD][2];
-#pragma unroll
-            for (uint32_t s = 0; s < TP_MAX_WORLD; ++s) {
-                if (s < p.world) {
-                    const float4* q = reinterpret_cast<const float4*>(p.staging) + (s * slot_units + src) * 2;
-                    part[s][0] = __ldcs(q);
-                    part[s][1] = __ldcs(q + 1);
+    } else {
+        if (p.sync == 2) {
+            // the barrier "every rank's partial has been pushed" inside the kernel (the GEMMs precede it on every
+            // rank's stream): block 0 says so for this rank, every block waits for all ranks
+            if (threadIdx.x < p.world) {
+                if (blockIdx.x == 0) {
+                    __threadfence_system();
+                    uint32_t* remote = reinterpret_cast<uint32_t*>(p.peers_done[threadIdx.x]) + TP_START_WORD + p.rank;
+                    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(step) : "memory");
+                }
+                if (!wait_for_step(reinterpret_cast<const uint32_t*>(p.peers_done[p.rank]) + TP_START_WORD + threadIdx.x, step, p.wait_cycles)) {
+                    if (blockIdx.x == 0) report(p.status, ST_WAIT_TIMEOUT, WHERE_PEER, 32u + threadIdx.x);
+                    ok_s = 0u;
                 }
             }
-            float v[8] = {part[0][0].x, part[0][0].y, part[0][0].z, part[0][0].w, part[0][1].x, part[0][1].y, part[0][1].z, part[0][1].w};
-#pragma unroll
-            for (uint32_t s = 1; s < TP_MAX_WORLD; ++s) {
-                if (s < p.world) {
-                    v[0] = __fadd_rn(v[0], part[s][0].x); v[1] = __fadd_rn(v[1], part[s][0].y);
-                    v[2] = __fadd_rn(v[2], part[s][0].z); v[3] = __fadd_rn(v[3], part[s][0].w);
-                    v[4] = __fadd_rn(v[4], part[s][1].x); v[5] = __fadd_rn(v[5], part[s][1].y);
-                    v[6] = __fadd_rn(v[6], part[s][1].z); v[7] = __fadd_rn(v[7], part[s][1].w);
-                }
-            }
-            uint32_t o[8];
-            if (OUT == HB_OUT_RESIDUAL) {
-                const uint4 old = reinterpret_cast<const uint4*>(y_s[p.rank])[at];
-                const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    o[2 * e] = f32_to_bf16(__fadd_rn(bf16_to_f32(ow[e] & 0xffffu), round_bf16(v[2 * e])));
-                    o[2 * e + 1] = f32_to_bf16(__fadd_rn(bf16_to_f32(ow[e] >> 16), round_bf16(v[2 * e + 1])));
-                }
-            } else {
-#pragma unroll
-                for (int e = 0; e < 8; ++e) o[e] = f32_to_bf16(v[e]);
-            }
-            const uint4 res = make_uint4(o[0] | (o[1] << 16), o[2] | (o[3] << 16), o[4] | (o[5] << 16), o[6] | (o[7] << 16));
-            for (uint32_t d = 0; d < p.world; ++d) reinterpret_cast<uint4*>(y_s[d])[at] = res;
+            __syncthreads();
+        }
+        // all groups as one index space (every thread has work whatever the group's size)
+        const uint32_t per_group = p.group_part * p.n8;
+        const size_t total = ok_s ? (size_t)p.groups * per_group : 0;
+        for (size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (size_t)gridDim.x * blockDim.x) {
+            const uint32_t g = (uint32_t)(t / per_group), i = (uint32_t)(t - (size_t)g * per_group);
+            const uint32_t row0 = g * p.group_rows + p.rank * p.group_part;
+            if (row0 < p.m && i < min(p.group_part, p.m - row0) * p.n8) unit(g, row0, i);
         }
     }
     // the closing handshake: this block's stores are out, the last block to get here speaks for the rank
@@ -209,14 +237,17 @@ struct TpSumStream : hb_kernel {
         p.sync = sync;
         p.wait_cycles = (long long)ctx->peer_wait_ms * TP_CYCLES_PER_MS;
         p.status = ctx->status_dev;
-        const size_t units = (size_t)part * p.n8;  // of one group
-        const uint32_t grid = (uint32_t)std::max<size_t>(1, std::min<size_t>((units + 127) / 128, (size_t)ctx->sm_count));
+        // sync = 1: the kernel shares the SMs with the GEMM it follows, one block per SM, a group at a time; otherwise
+        // all groups are one index space and four blocks per SM keep more loads in flight (all of them resident: they
+        // may wait for the other ranks at their start)
+        const size_t units = sync == 1 ? (size_t)part * p.n8 : (size_t)groups * part * p.n8;
+        const uint32_t grid = (uint32_t)std::max<size_t>(1, std::min<size_t>((units + 127) / 128, (size_t)ctx->sm_count * (sync == 1 ? 1 : 4)));
         cudaLaunchConfig_t cfg{};
         cfg.gridDim = dim3(grid);
         cfg.blockDim = dim3(128);
         cfg.stream = ctx->stream;
         cudaLaunchAttribute attr[1];
-        if (sync) {  // may start while the GEMM before it on the stream runs: it waits for the GEMMs' flags, not for their end
+        if (sync == 1) {  // may start while the GEMM before it on the stream runs: it waits for the GEMMs' flags, not for their end
             attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
             attr[0].val.programmaticStreamSerializationAllowed = 1;
             cfg.attrs = attr;
@@ -309,11 +340,12 @@ extern "C" int hb_tp_sum_stream_get(hb_ctx* ctx, uint32_t n, uint32_t out, uint3
         k->world = world;
         k->rank = rank;
         k->group_rows = group_rows;
-        k->sync = sync ? 1u : 0u;
+        if (sync > 2) return hb::fail(ctx, HB_INVALID, "tp_sum_stream: sync is 0, 1 or 2");
+        k->sync = sync;
         k->kind = 16;
         k->nargs = 5;
         k->name = "tp_sum_stream_" + std::to_string(n) + "_" + hb::out_tag(out) + "_g" + std::to_string(group_rows) + "_r" + std::to_string(rank) + "of" + std::to_string(world) +
-                  (sync ? "" : "_hostordered");
+                  (sync == 1 ? "" : sync == 2 ? "_barriers" : "_hostordered");
         *res = hb::intern(ctx, std::move(k));
         return HB_OK;
     } catch (const std::exception& e) {

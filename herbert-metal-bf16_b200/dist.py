@@ -646,17 +646,18 @@ class TpPeer:
             mode = ("push" if push else "pull") if push is not None else "push"
         if world == 1:
             mode = "pull"
-        assert mode in ("stream", "push", "pull")
+        assert mode in ("stream", "push", "pull", "pushsync")
         self.mode = mode
         self.push = mode == "push"
+        self.grouped = mode in ("stream", "pushsync")  # rows dealt in groups of 256, the streaming sum kernel
         self.rows_per = (m + world - 1) // world
         self.groups = (m + TP_GROUP_ROWS - 1) // TP_GROUP_ROWS
         self.group_part = TP_GROUP_ROWS // world
         # acc: the whole partial [m][h] (pull), the staging [world][rows_per][h] of the blocks this rank sums (push), or the
         # staging [world][groups][256 / world][h] of its slices of every group (stream)
-        acc_rows = {"pull": m, "push": max(m, world * self.rows_per), "stream": world * self.groups * self.group_part}[mode]
+        acc_rows = {"pull": m, "push": max(m, world * self.rows_per)}.get(mode, world * self.groups * self.group_part)
         sizes = {"acc": acc_rows * h * 4, "y": m * h * 2}
-        if mode == "stream":
+        if self.grouped:
             assert self.groups <= TP_MAX_GROUPS
             sizes.update(gflags=world * TP_MAX_GROUPS * 4, done=256)
             self.ctl = ctx.alloc(TP_CTL_WORDS * 4)  # zeroed: step 0
@@ -664,7 +665,7 @@ class TpPeer:
         self.acc, self.y = self.pb.local["acc"], self.pb.local["y"]
         self._yv = _view(self.y, (m, h), "<i2", dev).view(torch.bfloat16)
         self.token = torch.zeros(1, device=dev, dtype=torch.float32)
-        self.k_reduce = None if mode == "stream" else ctx.tp_sum(h, out, world, rank) if self.push else ctx.tp_reduce(h, out, world, rank)
+        self.k_reduce = None if self.grouped else ctx.tp_sum(h, out, world, rank) if self.push else ctx.tp_reduce(h, out, world, rank)
         self._k_stream = {}
         self.push_table = torch.zeros(world, device=dev, dtype=torch.int64)  # where this rank's block for owner d goes
         self.kernels = {}
@@ -678,6 +679,9 @@ class TpPeer:
                       "summing ranks' staging (NVLink, under the GEMM) and flags each finished group; tp_sum_stream runs beside the GEMM (programmatic launch), sums "
                       "the groups as they complete in rank order, rounds once, adds the residual, stores bf16 Y to every rank and ends with its own handshake "
                       "(3 kernels per step, no barrier kernel, no NCCL call)",
+            "pushsync": "rows dealt in groups of 256, each rank sums 256/P rows of every group: the down GEMM's epilogue stores its f32 partial tile by tile into "
+                        "the summing ranks' staging (NVLink, under the GEMM); tp_sum_stream with both barriers inside (its first block says that this rank's "
+                        "partial is out, every block waits for all ranks; the last block closes the step with a handshake): 3 kernels per step, no NCCL call",
             "push": "down GEMM epilogue stores its f32 partial block by block into the summing ranks' memory (NVLink, under the GEMM); tp_sum: rank-order sum, one "
                     "rounding, residual, peer stores of bf16 Y; 2 barrier kernels (no NCCL call in the step)",
             "pull": "f32 partial stays local; tp_reduce pulls the blocks it sums through NVLink loads, rank-order sum, one rounding, residual, peer stores of bf16 Y; "
@@ -693,7 +697,7 @@ class TpPeer:
 
     def _after_connect(self) -> None:
         # slot `rank` of every owner's staging buffer
-        slot = self.rank * (self.groups * self.group_part if self.mode == "stream" else self.rows_per) * self.h * 4
+        slot = self.rank * (self.groups * self.group_part if self.grouped else self.rows_per) * self.h * 4
         self.push_table.copy_(self.pb.tables["acc"] + slot)
 
     def close(self) -> None:
@@ -714,7 +718,8 @@ class TpPeer:
         key = (h, ip)
         if key not in self.kernels:
             hmid = torch.empty((self.m, ip), device=x.device, dtype=torch.bfloat16)
-            form = {"pull": {}, "push": dict(y_shards=self.world), "stream": dict(y_shards=self.world, y_group_rows=TP_GROUP_ROWS, y_signal=self.rank + 1)}[self.mode]
+            form = {"pull": {}, "push": dict(y_shards=self.world), "pushsync": dict(y_shards=self.world, y_group_rows=TP_GROUP_ROWS),
+                    "stream": dict(y_shards=self.world, y_group_rows=TP_GROUP_ROWS, y_signal=self.rank + 1)}[self.mode]
             # the tile width of each GEMM is chosen by timing both on these operands (plain local outputs: nothing of a
             # peer's is touched)
             tn_gu = pair_tile_n(self.ctx, self.m, h, 2 * ip, OUT_SWIGLU, wgu_local, x[: self.m], hmid) if self.tune_tiles else 256
@@ -729,15 +734,15 @@ class TpPeer:
         if self.mode == "stream":
             self.emit(k_down, m, self._w(wd_local), self._w(hmid), self._w(self.push_table), self.pb.table("gflags"), self.ctl)
         else:
-            self.emit(k_down, m, self._w(wd_local), self._w(hmid), self._w(self.push_table) if self.push else self.acc)
+            self.emit(k_down, m, self._w(wd_local), self._w(hmid), self._w(self.push_table) if self.mode != "pull" else self.acc)
 
     def phase_reduce(self, sync: bool = False) -> None:
-        """pull / push: every rank's partial is complete (push: has arrived). stream with sync: right behind this
-        rank's GEMMs, the kernel waits for the flags itself; without: as for push."""
-        if self.mode == "stream":
-            sync = bool(sync)
+        """pull / push: every rank's partial is complete (push: has arrived). stream / pushsync with sync: right behind
+        this rank's GEMMs, the kernel orders itself against the other ranks; without: as for push."""
+        if self.grouped:
+            sync = (1 if self.mode == "stream" else 2) if sync else 0
             if sync not in self._k_stream:
-                self._k_stream[sync] = self.ctx.tp_sum_stream(self.h, self.out, self.world, self.rank, TP_GROUP_ROWS, 1 if sync else 0)
+                self._k_stream[sync] = self.ctx.tp_sum_stream(self.h, self.out, self.world, self.rank, TP_GROUP_ROWS, sync)
             self.emit(self._k_stream[sync], self.m, self.acc, self.pb.table("y"), self.pb.local["gflags"], self.pb.table("done"), self.ctl)
         else:
             self.emit(self.k_reduce, self.m, self.acc if self.push else self.pb.table("acc"), self.pb.table("y"))
@@ -773,7 +778,7 @@ def _tp_step(state: TpPeer, x, wgu_local, wd_local, group, nccl_sync):
 def _tp_step_body(state: TpPeer, x, wgu_local, wd_local, group, nccl_sync):
     multi = state.world > 1
     state.phase_gemms(x, wgu_local, wd_local)
-    if state.mode == "stream" and multi and not nccl_sync and not state.pb.emulated:
+    if state.grouped and multi and not nccl_sync and not state.pb.emulated:
         state.phase_reduce(sync=True)  # the kernel orders itself against the other ranks: no barrier before or after
         return state.y_view()
     if multi:

@@ -383,6 +383,10 @@ int hb_tp_sum_get(hb_ctx* ctx, uint32_t n, uint32_t out, uint32_t world, uint32_
  * staging: this rank's f32 [world][groups][group_rows / world][n], groups = ceil(m / group_rows).
  * sync = 0: no flag is waited for and none is sent (the host orders the kernels: one process that holds every rank on
  * one GPU, or ranks ordered by a collective of the caller's).
+ * sync = 2: for a GEMM that deals its rows in groups but flags nothing (y_group_rows = 256, y_signal = 0): the kernel
+ * starts after the GEMM, its first block tells every rank that this rank's partial is out, every block waits for all
+ * ranks (words 16.. of the `done` arrays, which must hold 16 + world words), then all groups are summed at once and
+ * the kernel closes as with sync = 1: both barriers of the step inside the summing kernel.
  * Bindings: staging, peers_y, flags (this rank's u32[world][HB_TP_MAX_GROUPS]), peers_done (u64[world]: every rank's
  * u32[world], zeroed once), ctl (this rank's, the array the GEMM is bound to). No reference counterpart. */
 #define HB_TP_MAX_GROUPS 64u

@@ -212,7 +212,7 @@ def _two_process_worker(rank, world, port, repo, result):
         a, b = d.shard_gate_up(t16(wgu2), rank, world).cuda(), d.shard_down(t16(wd2), rank, world).cuda()
         be = d.GpuBackend(hb, ctx, rows_max=512)
         y_ref = d.tp_ffn(be, t16(x2).cuda(), a, b, t16(y0).cuda())
-        for mode in ("pull", "push", "stream"):  # pulled by the summing kernel; pushed by the GEMM; pushed and summed beside the GEMM
+        for mode in ("pull", "push", "stream", "pushsync"):  # pulled by the summing kernel; pushed by the GEMM; pushed and summed beside the GEMM
             tp = d.TpPeer(hb, ctx, rank, world, m, h, mode=mode)
             d.tp_peer_connect(tp)
             x2d = t16(x2).cuda()
@@ -256,7 +256,7 @@ def test_two_processes_over_nvlink():
 
 # ---------------------------------------------------------------- the tensor-parallel FFN through tp_reduce
 
-@pytest.mark.parametrize("mode", ["pull", "push", "stream"])
+@pytest.mark.parametrize("mode", ["pull", "push", "stream", "pushsync"])
 @pytest.mark.parametrize("world,m", [(1, 200), (2, 200), (4, 200), (8, 200), (4, 700), (8, 1024)])
 def test_tp_reduce_emulated_ranks(env, hb200, oracle, world, m, mode):
     # push: the down GEMM stores each block of rows of its partial into its owner's staging buffer (y_shards) and the

@@ -238,7 +238,7 @@ def env(hb200):
     c.close()
 
 
-@pytest.mark.parametrize("mode", ["stream", "push", "pull"])
+@pytest.mark.parametrize("mode", ["stream", "pushsync", "push", "pull"])
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_ffn_27b_tensor_parallel_emulated_ranks_real_shapes(env, hb200, oracle, ffn27, world, mode):
     """The sharded FFN at its real shapes, the ranks emulated on one GPU (no kernel of the step waits for another
