@@ -1048,8 +1048,10 @@ def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks)
                 # the other two forms of the exchange over the same kernels: the partial stays local and tp_reduce pulls the
                 # blocks it sums from the peers; the GEMM flags finished row groups and the sum runs beside it
                 other_forms = {}
-                for mode_ in (("pull", "stream", "pushsync") if world > 1 else ()):
-                    tpl = D.TpPeer(hb, ctx, rank, world, m, h, mode=mode_)
+                forms_ = (("pull", dict(mode="pull")), ("stream", dict(mode="stream")), ("pushsync", dict(mode="pushsync")),
+                          ("push, barrier kernels", dict(mode="push", fold_barriers=False))) if world > 1 else ()
+                for mode_, kw_ in forms_:
+                    tpl = D.TpPeer(hb, ctx, rank, world, m, h, **kw_)
                     D.tp_peer_connect(tpl)
                     tpl.set_y(y)
                     got_other = D.tp_ffn_peer(tpl, x, wgu_l, wd_l).clone()

@@ -106,6 +106,7 @@ def lib() -> C.CDLL:
         "hb_ep_plan_direct_get": (ci, [vp, u32, u32, u32, u32, u32, pvp]),
         "hb_tp_reduce_get": (ci, [vp, u32, u32, u32, u32, pvp]),
         "hb_tp_sum_get": (ci, [vp, u32, u32, u32, u32, pvp]),
+        "hb_tp_sum_sync_get": (ci, [vp, u32, u32, u32, u32, pvp]),
         "hb_tp_sum_stream_get": (ci, [vp, u32, u32, u32, u32, u32, u32, pvp]),
         "hb_dequant_q4_get": (ci, [vp, u32, u32, pvp]),
         "hb_matvec_q4_get": (ci, [vp, u32, u32, u32, u32, u32, pvp]),
@@ -179,7 +180,7 @@ EXPORTS = [
     "hb_open", "hb_close", "hb_last_error", "hb_describe", "hb_set_stream", "hb_alloc", "hb_set_alloc_limit", "hb_upload",
     "hb_download", "hb_memset", "hb_sync", "hb_launch_count", "hb_event_new", "hb_event_free", "hb_lane_record", "hb_lane_wait", "hb_event_sync",
     "hb_upload_async", "hb_download_async", "hb_host_alloc", "hb_host_free", "hb_ipc_export", "hb_ipc_open", "hb_ipc_close",
-    "hb_ep_dispatch_get", "hb_ep_plan_get", "hb_ep_return_get", "hb_ep_combine_get", "hb_ep_combine_sync_get", "hb_ep_dispatch_direct_get", "hb_ep_plan_direct_get", "hb_tp_reduce_get", "hb_tp_sum_get", "hb_tp_sum_stream_get", "hb_dequant_q4_get", "hb_matvec_q4_get", "hb_matvec_q4_split_get", "hb_matmul_q4_get", "hb_gemm_q4_get", "hb_select_gemm_q4", "hb_rmsnorm_get", "hb_argmax_get", "hb_moe_out_get", "hb_peer_sync_get", "hb_set_peer_wait_ms", "hb_gemm_get", "hb_matvec_get", "hb_swiglu_get", "hb_route_get",
+    "hb_ep_dispatch_get", "hb_ep_plan_get", "hb_ep_return_get", "hb_ep_combine_get", "hb_ep_combine_sync_get", "hb_ep_dispatch_direct_get", "hb_ep_plan_direct_get", "hb_tp_reduce_get", "hb_tp_sum_get", "hb_tp_sum_sync_get", "hb_tp_sum_stream_get", "hb_dequant_q4_get", "hb_matvec_q4_get", "hb_matvec_q4_split_get", "hb_matmul_q4_get", "hb_gemm_q4_get", "hb_select_gemm_q4", "hb_rmsnorm_get", "hb_argmax_get", "hb_moe_out_get", "hb_peer_sync_get", "hb_set_peer_wait_ms", "hb_gemm_get", "hb_matvec_get", "hb_swiglu_get", "hb_route_get",
     "hb_moe_sort_get", "hb_moe_tiles", "hb_moe_gather_get", "hb_moe_combine_get", "hb_experts_matvec_get", "hb_epilogue_get", "hb_gemm_static_scratch", "hb_kernel_name", "hb_launch", "hb_run", "hb_time", "hb_set_launch_overlap", "hb_graph_record", "hb_graph_launch", "hb_graph_time", "hb_graph_free",
     "hb_tune_new", "hb_tune_free", "hb_tune_apply", "hb_tune_get", "hb_tune_summary", "hb_tune_gemm_timed", "hb_selector_new",
     "hb_selector_free", "hb_selector_log", "hb_selector_buckets", "hb_fill_random16", "hb_select_gemm", "hb_select_gate_up",
@@ -411,8 +412,9 @@ class Context:
     def moe_out(self, d) -> "Kernel":
         return self._get(lib().hb_moe_out_get, d)
 
-    def tp_sum(self, n, out, world, rank) -> "Kernel":
-        return self._get(lib().hb_tp_sum_get, n, out, world, rank)
+    def tp_sum(self, n, out, world, rank, sync=False) -> "Kernel":
+        """sync: the form that carries the step's two barriers (hb_tp_sum_sync_get; bindings staging, peers_y, peers_flags, ctl)."""
+        return self._get(lib().hb_tp_sum_sync_get if sync else lib().hb_tp_sum_get, n, out, world, rank)
 
     def tp_sum_stream(self, n, out, world, rank, group_rows=256, sync=1) -> "Kernel":
         return self._get(lib().hb_tp_sum_stream_get, n, out, world, rank, group_rows, sync)

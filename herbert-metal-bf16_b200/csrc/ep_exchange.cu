@@ -118,10 +118,17 @@ __global__ void __launch_bounds__(256) ep_move_kernel(const EpParams p) {
             }
         }
         // this block's rows are out; the block that gets here last numbers the step and tells every rank
+        // A block's own fence is at device scope: it orders the block's stores before its count below. The block that
+        // counts last has synchronised with all the others through that counter, and its system-scope fence before the
+        // flags is cumulative: what the other blocks stored is visible to whoever acquires the flag. (A system-scope
+        // fence in every block waits for that block's remote stores to be acknowledged: 8 us of a 26 us dispatch.)
         __shared__ uint32_t last_s;
-        __threadfence_system();
+        __threadfence();
         __syncthreads();
-        if (threadIdx.x == 0) last_s = atomicAdd(p.ctl + 1, 1u) == gridDim.x - 1u ? 1u : 0u;
+        if (threadIdx.x == 0) {
+            last_s = atomicAdd(p.ctl + 1, 1u) == gridDim.x - 1u ? 1u : 0u;
+            __threadfence();  // (the count is read before anything below)
+        }
         __syncthreads();
         if (last_s && threadIdx.x < p.world) {
             __threadfence_system();

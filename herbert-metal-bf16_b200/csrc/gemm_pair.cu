@@ -324,7 +324,9 @@ gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
                 // This warp's rows of the tile are stored (the __syncwarp above orders the other lanes' stores before
                 // this fence). The tile's row group is complete when the eight epilogue warps of the pair have arrived
                 // for each of its column tiles; whoever arrives last tells every summing rank, with the step's number.
-                __threadfence_system();
+                // (device scope here; the last arriver's system-scope fence is cumulative over the warps it has
+                // synchronised with through the counter)
+                __threadfence();
                 uint32_t* cnt = p.ctl + TP_CTL_GROUP0 + tm;
                 if (atomicAdd(cnt, 1u) == 8u * tiles_n - 1u) {
                     *cnt = 0u;  // for the next launch

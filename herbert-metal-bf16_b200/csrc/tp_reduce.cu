@@ -23,11 +23,32 @@ struct TpParams {
     const uint64_t* peers_acc;  // [world] f32 [m][n] on every rank
     const uint64_t* peers_y;    // [world] bf16 [m][n] on every rank
     uint32_t m, n8, world, rank, rows_per;
+    // optional (hb_tp_sum_sync_get): the two barriers of the step inside this kernel. Its first block tells every rank
+    // that this rank's partial has been pushed (the GEMM precedes this kernel on the stream) and every block waits
+    // until all ranks have said so; the block that finishes last tells every rank that this rank's rows of Y are out
+    // and waits until all ranks have said that too. The step's number lives in ctl[0].
+    const uint64_t* peers_flags;  // [world] -> u32[32] on every rank: [0, world) Y is out, [16, 16 + world) partial is out
+    uint32_t* ctl;                // [0] steps completed, [1] blocks finished
+    long long wait_cycles;
+    uint32_t* status;
 };
 
 template <int OUT, bool STAGED>
 __global__ void __launch_bounds__(256) tp_reduce_kernel(const TpParams p) {
     __shared__ uint64_t acc_s[TP_MAX_WORLD], y_s[TP_MAX_WORLD];
+    uint32_t step = 0;
+    if (p.peers_flags) {
+        step = *reinterpret_cast<volatile uint32_t*>(p.ctl) + 1u;
+        if (threadIdx.x < p.world) {
+            if (blockIdx.x == 0) {
+                __threadfence_system();
+                uint32_t* remote = reinterpret_cast<uint32_t*>(p.peers_flags[threadIdx.x]) + TP_START_WORD + p.rank;
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(step) : "memory");
+            }
+            if (!wait_for_step(reinterpret_cast<const uint32_t*>(p.peers_flags[p.rank]) + TP_START_WORD + threadIdx.x, step, p.wait_cycles) && blockIdx.x == 0)
+                report(p.status, ST_WAIT_TIMEOUT, WHERE_PEER, 32u + threadIdx.x);
+        }
+    }
     if (threadIdx.x < p.world) {
         // STAGED: slot s of the local staging buffer, rebased so that the row index of the whole matrix applies
         acc_s[threadIdx.x] = STAGED ? reinterpret_cast<uint64_t>(p.staging + ((size_t)threadIdx.x * p.rows_per - (size_t)p.rank * p.rows_per) * p.n8 * 8)
@@ -35,8 +56,7 @@ __global__ void __launch_bounds__(256) tp_reduce_kernel(const TpParams p) {
         y_s[threadIdx.x] = p.peers_y[threadIdx.x];
     }
     __syncthreads();
-    const uint32_t r0 = p.rank * p.rows_per, r1 = min(p.m, r0 + p.rows_per);
-    if (r0 >= r1) return;
+    const uint32_t r0 = min(p.m, p.rank * p.rows_per), r1 = min(p.m, r0 + p.rows_per);
     const size_t first = (size_t)r0 * p.n8, total = (size_t)(r1 - r0) * p.n8;  // units of 8 elements
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
         const size_t at = first + i;
@@ -77,6 +97,29 @@ __global__ void __launch_bounds__(256) tp_reduce_kernel(const TpParams p) {
         }
         const uint4 res = make_uint4(o[0] | (o[1] << 16), o[2] | (o[3] << 16), o[4] | (o[5] << 16), o[6] | (o[7] << 16));
         for (uint32_t d = 0; d < p.world; ++d) reinterpret_cast<uint4*>(y_s[d])[at] = res;
+    }
+    if (p.peers_flags) {
+        // (a block's fence is at device scope; the last block's system-scope fence is cumulative over the blocks it has
+        // synchronised with through the counter)
+        __shared__ uint32_t last_s;
+        __threadfence();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            last_s = atomicAdd(p.ctl + 1, 1u) == gridDim.x - 1u ? 1u : 0u;
+            __threadfence();
+        }
+        __syncthreads();
+        if (!last_s) return;
+        if (threadIdx.x == 0) p.ctl[1] = 0u;
+        if (threadIdx.x < p.world) {
+            __threadfence_system();
+            uint32_t* remote = reinterpret_cast<uint32_t*>(p.peers_flags[threadIdx.x]) + p.rank;
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(remote), "r"(step) : "memory");
+            if (!wait_for_step(reinterpret_cast<const uint32_t*>(p.peers_flags[p.rank]) + threadIdx.x, step, p.wait_cycles))
+                report(p.status, ST_WAIT_TIMEOUT, WHERE_PEER, 16u + threadIdx.x);
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) *reinterpret_cast<volatile uint32_t*>(p.ctl) = step;
     }
 }
 
@@ -192,10 +235,14 @@ __global__ void __launch_bounds__(128) tp_sum_stream_kernel(const TpStreamParams
             if (row0 < p.m && i < min(p.group_part, p.m - row0) * p.n8) unit(g, row0, i);
         }
     }
-    // the closing handshake: this block's stores are out, the last block to get here speaks for the rank
-    __threadfence_system();
+    // the closing handshake: this block's stores are ordered before its count (device scope), the last block to get
+    // here speaks for the rank (its system-scope fence is cumulative over the blocks it has synchronised with)
+    __threadfence();
     __syncthreads();
-    if (threadIdx.x == 0) last_s = atomicAdd(p.ctl + TP_CTL_DONE, 1u) == gridDim.x - 1u ? 1u : 0u;
+    if (threadIdx.x == 0) {
+        last_s = atomicAdd(p.ctl + TP_CTL_DONE, 1u) == gridDim.x - 1u ? 1u : 0u;
+        __threadfence();
+    }
     __syncthreads();
     if (!last_s) return;
     if (threadIdx.x == 0) p.ctl[TP_CTL_DONE] = 0u;
@@ -262,9 +309,10 @@ struct TpSumStream : hb_kernel {
 
 struct TpReduce : hb_kernel {
     uint32_t n = 0, out = 0, world = 0, rank = 0;
-    bool staged = false;
+    bool staged = false, sync = false;
     int launch(hb_ctx* ctx, const hb_range* a, int na, uint32_t m) override {
-        if (na != 2) return fail(ctx, HB_INVALID, name + (staged ? ": bindings are staging, peers_y" : ": bindings are peers_acc, peers_y (device arrays of one address per rank)"));
+        if (na != (sync ? 4 : 2))
+            return fail(ctx, HB_INVALID, name + (sync ? ": bindings are staging, peers_y, peers_flags, ctl" : staged ? ": bindings are staging, peers_y" : ": bindings are peers_acc, peers_y (device arrays of one address per rank)"));
         if (m == 0) return fail(ctx, HB_INVALID, name + ": m = 0");
         const uint32_t rows_per = (m + world - 1) / world;
         if (!range_ok(a[0], staged ? (size_t)world * rows_per * n * 4 : (size_t)world * 8) || !range_ok(a[1], (size_t)world * 8))
@@ -278,8 +326,16 @@ struct TpReduce : hb_kernel {
         p.world = world;
         p.rank = rank;
         p.rows_per = rows_per;
+        if (sync) {
+            if (!range_ok(a[2], (size_t)world * 8) || !range_ok(a[3], 8)) return fail(ctx, HB_INVALID, name + ": a bound range is too small");
+            p.peers_flags = static_cast<const uint64_t*>(a[2].ptr);
+            p.ctl = static_cast<uint32_t*>(a[3].ptr);
+            p.wait_cycles = (long long)ctx->peer_wait_ms * TP_CYCLES_PER_MS;
+            p.status = ctx->status_dev;
+        }
         const size_t units = (size_t)p.rows_per * p.n8;
-        const uint32_t grid = (uint32_t)std::max<size_t>(1, std::min<size_t>((units + 255) / 256, (size_t)ctx->sm_count * 8));
+        // (with the barriers inside, every block starts with a round trip to the flags: fewer, longer-lived blocks)
+        const uint32_t grid = (uint32_t)std::max<size_t>(1, std::min<size_t>((units + 255) / 256, (size_t)ctx->sm_count * (sync ? 3 : 8)));
         if (staged) {
             if (out == HB_OUT_RESIDUAL) tp_reduce_kernel<HB_OUT_RESIDUAL, true><<<grid, 256, 0, ctx->stream>>>(p);
             else tp_reduce_kernel<HB_OUT_BF16, true><<<grid, 256, 0, ctx->stream>>>(p);
@@ -294,7 +350,7 @@ struct TpReduce : hb_kernel {
 };
 }  // namespace
 
-int make_tp_reduce(hb_ctx* ctx, uint32_t n, uint32_t out, uint32_t world, uint32_t rank, bool staged, hb_kernel** res) {
+int make_tp_reduce(hb_ctx* ctx, uint32_t n, uint32_t out, uint32_t world, uint32_t rank, bool staged, hb_kernel** res, bool sync = false) {
     *res = nullptr;
     if (n == 0 || n % 8 != 0) return fail(ctx, HB_UNSUPPORTED, "tp_reduce: n a positive multiple of 8");
     if (out != HB_OUT_BF16 && out != HB_OUT_RESIDUAL) return fail(ctx, HB_UNSUPPORTED, "tp_reduce: output Bf16 or Residual");
@@ -304,10 +360,12 @@ int make_tp_reduce(hb_ctx* ctx, uint32_t n, uint32_t out, uint32_t world, uint32
     k->out = out;
     k->world = world;
     k->rank = rank;
+    if (sync && (!staged || world < 2)) return fail(ctx, HB_UNSUPPORTED, "tp_sum (with its barriers): the staged form, 2..8 ranks, one GPU each");
     k->staged = staged;
+    k->sync = sync;
     k->kind = 14;
-    k->nargs = 2;
-    k->name = std::string(staged ? "tp_sum_" : "tp_reduce_") + std::to_string(n) + "_" + out_tag(out) + "_r" + std::to_string(rank) + "of" + std::to_string(world);
+    k->nargs = sync ? 4 : 2;
+    k->name = std::string(staged ? "tp_sum_" : "tp_reduce_") + std::to_string(n) + "_" + out_tag(out) + "_r" + std::to_string(rank) + "of" + std::to_string(world) + (sync ? "_barriers" : "");
     *res = intern(ctx, std::move(k));
     return HB_OK;
 }
@@ -348,6 +406,16 @@ extern "C" int hb_tp_sum_stream_get(hb_ctx* ctx, uint32_t n, uint32_t out, uint3
                   (sync == 1 ? "" : sync == 2 ? "_barriers" : "_hostordered");
         *res = hb::intern(ctx, std::move(k));
         return HB_OK;
+    } catch (const std::exception& e) {
+        return hb::fail(ctx, HB_BACKEND, e.what());
+    }
+}
+
+extern "C" int hb_tp_sum_sync_get(hb_ctx* ctx, uint32_t n, uint32_t out, uint32_t world, uint32_t rank, hb_kernel** res) {
+    if (!ctx || !res) return hb::fail(ctx, HB_INVALID, "hb_tp_sum_sync_get: bad argument");
+    try {
+        hb::bind(ctx);
+        return hb::make_tp_reduce(ctx, n, out, world, rank, true, res, true);
     } catch (const std::exception& e) {
         return hb::fail(ctx, HB_BACKEND, e.what());
     }

@@ -638,7 +638,7 @@ class TpPeer:
     on eight. (The pushed stores leave as whole 128-byte row segments: one 16-byte piece per lane took 537 and 437 us.)"""
 
     def __init__(self, hb, ctx, rank: int, world: int, m: int, h: int, out: int = OUT_RESIDUAL, device=None, push: bool | None = None, mode: str | None = None,
-                 tune_tiles: bool = True):
+                 tune_tiles: bool = True, fold_barriers: bool = True):
         self.hb, self.ctx, self.rank, self.world, self.m, self.h, self.out = hb, ctx, rank, world, m, h, out
         self.tune_tiles, self.tile_n = tune_tiles, (256, 256)
         dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
@@ -661,11 +661,17 @@ class TpPeer:
             assert self.groups <= TP_MAX_GROUPS
             sizes.update(gflags=world * TP_MAX_GROUPS * 4, done=256)
             self.ctl = ctx.alloc(TP_CTL_WORDS * 4)  # zeroed: step 0
+        # push: tp_sum can carry the step's two barriers itself (one process per GPU): flags on every rank, its own counters
+        self.fold_barriers = self.push and world > 1 and fold_barriers
+        if self.fold_barriers:
+            sizes.update(done=256)
+            self.ctl = ctx.alloc(TP_CTL_WORDS * 4)
         self.pb = PeerBuffers(ctx, rank, world, sizes, dev)
         self.acc, self.y = self.pb.local["acc"], self.pb.local["y"]
         self._yv = _view(self.y, (m, h), "<i2", dev).view(torch.bfloat16)
         self.token = torch.zeros(1, device=dev, dtype=torch.float32)
         self.k_reduce = None if self.grouped else ctx.tp_sum(h, out, world, rank) if self.push else ctx.tp_reduce(h, out, world, rank)
+        self.k_reduce_sync = ctx.tp_sum(h, out, world, rank, sync=True) if self.fold_barriers else None
         self._k_stream = {}
         self.push_table = torch.zeros(world, device=dev, dtype=torch.int64)  # where this rank's block for owner d goes
         self.kernels = {}
@@ -683,7 +689,8 @@ class TpPeer:
                         "the summing ranks' staging (NVLink, under the GEMM); tp_sum_stream with both barriers inside (its first block says that this rank's "
                         "partial is out, every block waits for all ranks; the last block closes the step with a handshake): 3 kernels per step, no NCCL call",
             "push": "down GEMM epilogue stores its f32 partial block by block into the summing ranks' memory (NVLink, under the GEMM); tp_sum: rank-order sum, one "
-                    "rounding, residual, peer stores of bf16 Y; 2 barrier kernels (no NCCL call in the step)",
+                    "rounding, residual, peer stores of bf16 Y; " + ("the step's two barriers inside tp_sum: 3 kernels" if self.fold_barriers else "2 barrier kernels") +
+                    " (no NCCL call in the step)",
             "pull": "f32 partial stays local; tp_reduce pulls the blocks it sums through NVLink loads, rank-order sum, one rounding, residual, peer stores of bf16 Y; "
                     "2 barrier kernels (no NCCL call in the step)",
         }[self.mode]
@@ -744,6 +751,8 @@ class TpPeer:
             if sync not in self._k_stream:
                 self._k_stream[sync] = self.ctx.tp_sum_stream(self.h, self.out, self.world, self.rank, TP_GROUP_ROWS, sync)
             self.emit(self._k_stream[sync], self.m, self.acc, self.pb.table("y"), self.pb.local["gflags"], self.pb.table("done"), self.ctl)
+        elif sync and self.fold_barriers:
+            self.emit(self.k_reduce_sync, self.m, self.acc, self.pb.table("y"), self.pb.table("done"), self.ctl)
         else:
             self.emit(self.k_reduce, self.m, self.acc if self.push else self.pb.table("acc"), self.pb.table("y"))
 
@@ -778,7 +787,7 @@ def _tp_step(state: TpPeer, x, wgu_local, wd_local, group, nccl_sync):
 def _tp_step_body(state: TpPeer, x, wgu_local, wd_local, group, nccl_sync):
     multi = state.world > 1
     state.phase_gemms(x, wgu_local, wd_local)
-    if state.grouped and multi and not nccl_sync and not state.pb.emulated:
+    if (state.grouped or state.fold_barriers) and multi and not nccl_sync and not state.pb.emulated:
         state.phase_reduce(sync=True)  # the kernel orders itself against the other ranks: no barrier before or after
         return state.y_view()
     if multi:

@@ -372,6 +372,14 @@ int hb_tp_reduce_get(hb_ctx* ctx, uint32_t n, uint32_t out, uint32_t world, uint
  * Sums the slots in rank order, rounds once, applies the output mode with its own old Y and stores the rows into
  * every rank's Y. Bindings: staging (local), peers_y. The host puts a barrier before and after. */
 int hb_tp_sum_get(hb_ctx* ctx, uint32_t n, uint32_t out, uint32_t world, uint32_t rank, hb_kernel** res);
+/* hb_tp_sum_get's kernel with the step's two barriers inside: bindings staging, peers_y, peers_flags (u64[world]: the
+ * addresses of every rank's u32[32] flags, zeroed once), ctl (this rank's u32[2], zeroed once). Its first block tells
+ * every rank that this rank's partial has been pushed (the GEMM precedes the kernel on the stream), every block waits
+ * (bounded, hb_set_peer_wait_ms) until all ranks have said so; the block that finishes last tells every rank that this
+ * rank's rows of Y are stored and waits until all ranks have said that: when the kernel ends Y is complete on every
+ * rank and the staging may be overwritten. The step's number is kept in ctl[0]. One process per GPU: never launched
+ * for several ranks on one GPU. No counterpart in the reference (one GPU). */
+int hb_tp_sum_sync_get(hb_ctx* ctx, uint32_t n, uint32_t out, uint32_t world, uint32_t rank, hb_kernel** res);
 /* The sum as a kernel that runs beside the GEMM whose partial it sums (hb_gemm_desc.y_group_rows = group_rows,
  * y_signal = 1 on every rank): for each group of rows in turn it waits until every rank's GEMM has flagged the group,
  * sums this rank's slice of it from the staging slots in rank order, rounds once, applies the output mode and stores

@@ -212,8 +212,10 @@ def _two_process_worker(rank, world, port, repo, result):
         a, b = d.shard_gate_up(t16(wgu2), rank, world).cuda(), d.shard_down(t16(wd2), rank, world).cuda()
         be = d.GpuBackend(hb, ctx, rows_max=512)
         y_ref = d.tp_ffn(be, t16(x2).cuda(), a, b, t16(y0).cuda())
-        for mode in ("pull", "push", "stream", "pushsync"):  # pulled by the summing kernel; pushed by the GEMM; pushed and summed beside the GEMM
-            tp = d.TpPeer(hb, ctx, rank, world, m, h, mode=mode)
+        # pulled by the summing kernel; pushed by the GEMM (the barriers inside tp_sum, or as kernels of their own); pushed and
+        # summed beside the GEMM; pushed in groups with the barriers inside the streaming sum
+        for mode, kw in (("pull", {}), ("push", {}), ("push", dict(fold_barriers=False)), ("stream", {}), ("pushsync", {})):
+            tp = d.TpPeer(hb, ctx, rank, world, m, h, mode=mode, **kw)
             d.tp_peer_connect(tp)
             x2d = t16(x2).cuda()
             for it in range(6):  # step by step, recorded then replayed (1..4), with NCCL barriers
