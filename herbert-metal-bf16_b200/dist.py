@@ -622,20 +622,21 @@ def pair_tile_n(ctx, m: int, k: int, n: int, out: int, w, x, y) -> int:
 class TpPeer:
     """One rank of the peer-memory FFN: the partial-product buffer, the output Y and their peer tables.
 
-    Three forms of the exchange, the same bits from each (the f32 partials are summed in rank order by one rank per row):
+    Forms of the exchange, the same bits from each (the f32 partials are summed in rank order by one rank per row):
 
-    "stream": the rows are dealt in groups of 256 (the down GEMM's row tile) and
-      every rank sums 256 / world rows of every group. The down GEMM stores each tile of its partial straight into the
-      staging buffers of the ranks that sum its rows and flags a group when its last tile is out; the summing kernel
-      (hb_tp_sum_stream_get) starts beside the GEMM, takes the groups as they complete, stores the bf16 rows into every
-      rank's Y and closes the step with a handshake of its own. Three kernels per step, none of them a barrier.
-      Slower than "push" as measured: a system-scope fence behind a tile's remote stores waits until they have all
-      been acknowledged, and with NVLink as the bound that wait is long (the down GEMM of the 27B-class FFN on eight
-      B200s: 188 us with the flags, 89 us without; the step 319 against 213 us; on two B200s 448 against 437 us).
-    "push" (the default): contiguous blocks of rows, one per rank; the down GEMM pushes, a barrier kernel, tp_sum, a barrier kernel.
+    "push" (the default): contiguous blocks of rows, one per rank; the down GEMM pushes its partial into the staging of
+      the rank that sums the block; tp_sum sums, rounds, stores Y to every rank and carries the step's two barriers itself
+      (hb_tp_sum_sync_get: three kernels per step), or, with fold_barriers=False, sits between two barrier kernels.
     "pull": the partial stays local; a barrier kernel, tp_reduce pulls the blocks it sums from the peers, a barrier.
-    Measured for the 27B-class FFN (2048 rows), push against pull: 449 against 483 us on two B200s, 220 against 259 us
-    on eight. (The pushed stores leave as whole 128-byte row segments: one 16-byte piece per lane took 537 and 437 us.)"""
+    "pushsync": the rows are dealt in groups of 256 (the down GEMM's row tile) and every rank sums 256 / world rows of
+      every group; the sum is hb_tp_sum_stream_get's kernel with both barriers inside (sync = 2). Three kernels.
+    "stream": as pushsync, and the down GEMM flags a group when its last tile is out; the summing kernel starts beside
+      the GEMM, takes the groups as they complete and closes the step with a handshake of its own. Three kernels.
+      The slowest as measured: a flag needs a fence behind a tile's remote stores, and with NVLink as the bound a
+      fence is expensive.
+    Measured for the 27B-class FFN (2048 rows), step replayed, on two / four / eight B200s: push 436-452 / 258-282 /
+    200-203 us, pushsync 445 / 263 / 207, pull 470 / 298 / 248, stream 465 / 317 / 279. (The pushed stores leave as whole
+    128-byte row segments: one 16-byte piece per lane took 537 us on two and 437 us on eight.)"""
 
     def __init__(self, hb, ctx, rank: int, world: int, m: int, h: int, out: int = OUT_RESIDUAL, device=None, push: bool | None = None, mode: str | None = None,
                  tune_tiles: bool = True, fold_barriers: bool = True):
