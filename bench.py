@@ -485,7 +485,7 @@ def summaries(extra: dict, pk: dict) -> dict:
     for key, name in (("tp_ffn_27b_m2048", "tp_ffn_27b"), ("moe_ep_2048tok", "moe_ep")):
         v = extra.get(key)
         if v:
-            sh[name] = {k_: v.get(k_) for k_ in ("n_gpus", "us", "t1_us", "efficiency", "kernels_per_step", "nccl_form_us", "parity") if k_ in v}
+            sh[name] = {k_: v.get(k_) for k_ in ("n_gpus", "us", "t1_us", "efficiency", "kernels_per_step", "kernels_us", "forms_us", "nccl_form_us", "parity") if k_ in v}
     weak = extra.get("moe_ep_weak_2048tok_per_gpu")
     if weak:
         sh["moe_ep_weak"] = {"n_gpus": weak["n_gpus"], "us": weak["us"], "tokens_per_s_total": weak["tokens_per_s_total"]}
@@ -1007,6 +1007,27 @@ def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks)
                 barrier()
                 return max_over_ranks(e0.elapsed_time(e1) * 1e-3 / reps)
 
+            def kernels_of(state, body):
+                """Every kernel of one step of `state` timed alone (20 launches each, all ranks in step, max over ranks):
+                the step's calls are taken down through the state's emitters instead of launched."""
+                ops = []
+                rec = lambda kern, mm, *ranges: ops.append((kern, mm, *ranges))
+                state.emit = rec
+                state.pb.emit = rec
+                try:
+                    body()
+                finally:
+                    state.emit = D._launch_now
+                    state.pb.emit = D._launch_now
+                res = []
+                for op in ops:
+                    stream.synchronize()
+                    barrier()
+                    ctx.time([op], 2)
+                    barrier()
+                    res.append({"kernel": op[0].name, "us": max_over_ranks(ctx.time([op], 20) / 20) * 1e6})
+                return res
+
             sample = torch.randperm(2048, generator=torch.Generator().manual_seed(5))[:16].sort().values.to(dev)
 
             # -- the 27B-class FFN: hidden 5120, intermediate 17408, M = 2048
@@ -1045,6 +1066,7 @@ def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks)
                 # (the step's kernels recorded once and replayed with one call; also launched one by one from the host)
                 sec = timed(lambda: D.tp_ffn_peer(tp, x, wgu_l, wd_l, recorded=True), 3, 10)
                 sec_loop = timed(lambda: D.tp_ffn_peer(tp, x, wgu_l, wd_l), 3, 10) if world > 1 else sec
+                tp_kernels = kernels_of(tp, lambda: D._tp_step_body(tp, x, wgu_l, wd_l, None, False))
                 # the other two forms of the exchange over the same kernels: the partial stays local and tp_reduce pulls the
                 # blocks it sums from the peers; the GEMM flags finished row groups and the sum runs beside it
                 other_forms = {}
@@ -1081,7 +1103,7 @@ def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks)
                 out["tp_ffn_27b_m2048"] = {"n_gpus": world, "us": sec * 1e6, "t1_us": t1 * 1e6, "efficiency": t1 / (world * sec), "tflops_total": flop / sec / 1e12,
                                            "tflops_per_gpu": flop / sec / 1e12 / world, "frac_of_measured_peak_per_gpu": flop / sec / 1e12 / world / pk["bf16_tflops"],
                                            "nvlink_bytes_per_gpu": (m * h * 4 + m * h * 2) * (world - 1) // world if world > 1 else 0, "scaling": "strong",
-                                           "kernels_per_step": tp.kernels_per_step, "parity": parity,
+                                           "kernels_per_step": tp.kernels_per_step, "parity": parity, "kernels_us": tp_kernels,
                                            "exchange": tp.describe(),
                                            "launched_one_by_one_us": sec_loop * 1e6, "pull_form_us": sec_pull * 1e6,
                                            "forms_us": {tp.mode: sec * 1e6, **{k_: v * 1e6 for k_, v in other_forms.items()}},
@@ -1126,6 +1148,12 @@ def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks)
                 if not torch.equal(got_rec, got):
                     raise RuntimeError("ep_moe: the replayed step differs from the step launched kernel by kernel")
                 sec_loop = timed(lambda: D.ep_moe_peer(st, xs, sc, wgu_l, wd_l), 3, 20) if world > 1 else sec
+
+                def ep_body():
+                    D._ep_step_body(st, xs, sc, wgu_l, wd_l, None, False)
+                    st.parity ^= 1  # taken down, not run: the two offset buffers keep their turn
+
+                ep_kernels = kernels_of(st, ep_body)
                 # ... and the same block with the rows exchanged by NCCL all-to-all, host-known counts (the baseline form)
                 ref = D.ep_moe(be, xs, sc, wgu_l, wd_l, E, top_k, mi, bm)
                 same = bool(torch.equal(ref, got))
@@ -1140,7 +1168,7 @@ def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks)
                     t1 = timed(lambda: D.ep_moe_peer(one, x_all, sc_all, wgu, wd), 3, 10)
                     one.close()
                 out["moe_ep_2048tok"] = {"n_gpus": world, "us": sec * 1e6, "t1_us": t1 * 1e6, "efficiency": t1 / (world * sec), "weight_gbs_total": wbytes / sec / 1e9,
-                                         "tokens_per_s": m / sec, "scaling": "strong", "tile_rows": bm, "kernels_per_step": kernels_per_step, "parity": parity,
+                                         "tokens_per_s": m / sec, "scaling": "strong", "tile_rows": bm, "kernels_per_step": kernels_per_step, "parity": parity, "kernels_us": ep_kernels,
                                          "exchange": "peer-memory stores and loads by the library's kernels, offsets all-gather and barriers as kernels (no NCCL call in the step); the step replayed as one recorded sequence",
                                          "launched_one_by_one_us": sec_loop * 1e6,
                                          "nccl_form_us": sec_nccl * 1e6, "equals_nccl_form_bitwise": same}
