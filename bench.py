@@ -232,6 +232,7 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--plain-launches", action="store_true", help="never launch the step's kernels overlapped")
     ap.add_argument("--no-extra", action="store_true", help="skip the matvec / MoE / tensor-parallel sections")
     ap.add_argument("--tune", default="", help="engine tune keys, e.g. gemm.auto=0 to skip the load-time timing")
     ap.add_argument("--form", default="", choices=["", "pair", "sk", "one"], help="with --case gate_up/down/layer: the GEMM form (one = one CTA per 128x256 tile)")
@@ -308,6 +309,29 @@ def main():
         ops += [(k_gu[0], ROWS, wrap(weights[2]), wrap(x), wrap(hmid))]
     ops += [(k_down, ROWS, wrap(weights[3]), wrap(hmid), wrap(resid))]
     picks = {"qkv": k_qkv.name, "o_proj": k_o.name, "gate_up": "+".join(k.name for k in k_gu), "down": k_down.name}
+
+    # Overlapped launches (each GEMM requests its first weight stages under the tail of the one before and waits for it
+    # inside): the same bits, checked here on one step from the same start; used for the timed region when faster.
+    resid0 = resid.clone()
+    outs_ = []
+    for on in (False, True):
+        resid.copy_(resid0)
+        torch.cuda.synchronize()
+        ctx.set_launch_overlap(on)
+        ctx.run(ops)
+        ctx.sync()
+        outs_.append((resid.clone(), qkv.clone(), hmid.clone()))
+    if not all(torch.equal(a_, b_) for a_, b_ in zip(*outs_)):
+        raise RuntimeError("overlapped launches changed the step's result")
+    del outs_
+    t_launch = {}
+    for on in (False, True):
+        ctx.set_launch_overlap(on)
+        ctx.time(ops, 3)
+        t_launch["overlapped" if on else "plain"] = max_over_ranks(ctx.time(ops, 5)) / 5
+    overlap = t_launch["overlapped"] < t_launch["plain"] and not args.plain_launches
+    ctx.set_launch_overlap(overlap)
+    resid.copy_(resid0)
 
     ctx.time(ops, args.warmup)
     barrier()
@@ -398,6 +422,8 @@ def main():
         "algorithmic_bytes_per_launch": sum(2.0 * (ROWS * k + n * k + ROWS * (n // 2 if o == 3 else n) * (2 if o == 2 else 1)) for _, k, n, o in LAYER) / 4,
     }
 
+    ctx.set_launch_overlap(False)  # (the sections below set it themselves where they use it)
+    roofline["launches"] = {"mode": "overlapped" if overlap else "plain", "us_per_step": {k_: v * 1e6 for k_, v in t_launch.items()}}
     extra = {"selection_seconds": t_sel, "picks": picks}
     if not args.no_extra:
         try:

@@ -124,34 +124,51 @@ gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
 
     if (warp == 0) {
         // ---------------------------------------------------------- producer (one per CTA)
+        // Overlapped launch (hb_set_launch_overlap): this kernel may have started while the kernel before it on the
+        // stream still runs. W is not that kernel's output, so the W halves of the first stages are requested at once;
+        // X may be, so its halves follow griddepcontrol.wait. In a plain launch the wait returns at once.
         if (lane == 0) {
             tma_prefetch_desc(&tm_x);
             tma_prefetch_desc(&tm_w);
-            uint32_t s = 0, ph = 0;
-            bool ok = true;
-            for (uint32_t item = pair; ok && item < num_items; item += npairs) {
-                const uint32_t tile = item % num_tiles, slice = item / num_tiles;
-                const uint32_t tm = p.m_first ? tile % tiles_m : tile / tiles_n;
-                const uint32_t tn = p.m_first ? tile / tiles_m : tile % tiles_n;
-                const int row_x = (int)(tm * 256 + rank * 128);
-                int row_w;
-                if constexpr (OUT == HB_OUT_SWIGLU) row_w = (int)(rank * p.n_out + tn * HALF);  // rank 0: gate rows, rank 1: up rows
-                else row_w = (int)(tn * BN + rank * HALF);
-                const uint32_t kb0 = slice * p.k_blocks / nsplit, kb1 = (slice + 1) * p.k_blocks / nsplit;
-                for (uint32_t kb = kb0; kb < kb1; ++kb) {
-                    if (!mbar_wait(smem_u32(&bars.empty[s]), ph ^ 1u)) {
-                        report(p.status, ST_WAIT_TIMEOUT, WHERE_EMPTY, s);
-                        ok = false;
-                        break;
+            uint32_t s = 0, ph = 0, fill = 0;
+            bool ok = true, waited = false;
+            for (int pass = 0; pass < 2 && ok; ++pass) {  // pass 0: the W halves of the first S fills; pass 1: everything else
+                s = 0; ph = 0; fill = 0;
+                for (uint32_t item = pair; ok && item < num_items; item += npairs) {
+                    const uint32_t tile = item % num_tiles, slice = item / num_tiles;
+                    const uint32_t tm = p.m_first ? tile % tiles_m : tile / tiles_n;
+                    const uint32_t tn = p.m_first ? tile / tiles_m : tile % tiles_n;
+                    const int row_x = (int)(tm * 256 + rank * 128);
+                    int row_w;
+                    if constexpr (OUT == HB_OUT_SWIGLU) row_w = (int)(rank * p.n_out + tn * HALF);  // rank 0: gate rows, rank 1: up rows
+                    else row_w = (int)(tn * BN + rank * HALF);
+                    const uint32_t kb0 = slice * p.k_blocks / nsplit, kb1 = (slice + 1) * p.k_blocks / nsplit;
+                    for (uint32_t kb = kb0; kb < kb1; ++kb, ++fill) {
+                        const bool early = fill < S;  // the stage is free: nothing to wait for
+                        if (pass == 0 && !early) { ok = false; break; }  // (ok is set again below: pass 0 just ends here)
+                        if (pass == 1 && !early && !mbar_wait(smem_u32(&bars.empty[s]), ph ^ 1u)) {
+                            report(p.status, ST_WAIT_TIMEOUT, WHERE_EMPTY, s);
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t full_leader = map_to_cta(smem_u32(&bars.full[s]), 0);
+                        const uint32_t a_dst = smem_base + s * PAIR_STAGE_BYTES;
+                        const bool do_w = pass == 0 || !early, do_x = pass == 1;
+                        if (do_w && rank == 0) mbar_arrive_expect_tx(smem_u32(&bars.full[s]), STAGE_TX);
+                        if (do_x) tma_load_2d_pair(a_dst, &tm_x, full_leader, (int)(kb * BK), row_x);
+                        if (do_w) tma_load_2d_pair(a_dst + A_BYTES, &tm_w, full_leader, (int)(kb * BK), row_w);
+                        if (++s == S) { s = 0; ph ^= 1u; }
                     }
-                    const uint32_t full_leader = map_to_cta(smem_u32(&bars.full[s]), 0);
-                    const uint32_t a_dst = smem_base + s * PAIR_STAGE_BYTES;
-                    if (rank == 0) mbar_arrive_expect_tx(smem_u32(&bars.full[s]), STAGE_TX);
-                    tma_load_2d_pair(a_dst, &tm_x, full_leader, (int)(kb * BK), row_x);
-                    tma_load_2d_pair(a_dst + A_BYTES, &tm_w, full_leader, (int)(kb * BK), row_w);
-                    if (++s == S) { s = 0; ph ^= 1u; }
+                }
+                if (pass == 0) {
+                    ok = true;
+                    griddep_wait();
+                    waited = true;
                 }
             }
+            (void)waited;
+            // every load of this CTA is requested: the kernel behind this one may take the SMs as they fall free
+            griddep_launch_dependents();
         }
     } else if (warp == 1) {
         // --------------------------------------------------------- MMA issuer (leader CTA only)
@@ -191,6 +208,7 @@ gemm_bf16_tn_pair_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_
         // ------------------------------------------------------------ epilogue (both CTAs: their own 128 rows)
         const uint32_t q = (uint32_t)warp & 3u;
         uint32_t it = 0;
+        griddep_wait();  // Y may be read (residual) or still be in use by the kernel before this one
         for (uint32_t item = pair; item < num_items; item += npairs, ++it) {
             const uint32_t tile = item % num_tiles, slice = item / num_tiles;
             const uint32_t tm = p.m_first ? tile % tiles_m : tile / tiles_n;
@@ -439,13 +457,18 @@ struct PairGemm : hb_kernel {
         cfg.blockDim = dim3(GEMM_THREADS);
         cfg.dynamicSmemBytes = smem;
         cfg.stream = ctx->stream;
-        cudaLaunchAttribute attr[1];
+        cudaLaunchAttribute attr[2];
         attr[0].id = cudaLaunchAttributeClusterDimension;
         attr[0].val.clusterDim.x = 2;
         attr[0].val.clusterDim.y = 1;
         attr[0].val.clusterDim.z = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
+        if (ctx->overlap_launches) {  // the kernel waits for its predecessor itself (griddepcontrol.wait before X and Y are touched)
+            attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[1].val.programmaticStreamSerializationAllowed = 1;
+            cfg.numAttrs = 2;
+        }
         HB_CUDA(ctx, cudaLaunchKernelEx(&cfg, fn, tm_x, tm_w, p));
         ctx->launches++;
         return HB_OK;

@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 
 from gpu_util import gemm_inputs, out_buffer, run_gemm, within_contract
-from oracle_lib import OUT_BF16, OUT_F32, OUT_RESIDUAL, OUT_SWIGLU
+from oracle_lib import OUT_BF16, OUT_F32, OUT_RESIDUAL, OUT_SWIGLU, SEED_W, SEED_X
 
 pytestmark = pytest.mark.gpu
 
@@ -131,6 +131,34 @@ def test_cta_pair_matches_single_cta_bits(ctx, oracle):
     b = run_gemm(ctx, oracle, m, k, n, OUT_BF16, tile_n=256)[2]
     c = run_gemm(ctx, oracle, m, k, n, OUT_BF16, cta_pair=1, tile_n=192)[2]
     assert np.array_equal(a, b) and np.array_equal(a, c)
+
+
+def test_cta_pair_chain_with_overlapped_launches(ctx, oracle):
+    """hb_set_launch_overlap: every GEMM of a chain starts under the tail of the one before (its first weight stages are
+    requested before it waits for its predecessor). A chain with true dependencies (each product is the next one's
+    input, the last adds into a residual twice): the same bits as with plain launches, several times over."""
+    m, dims = 600, (512, 1280, 768, 512)
+    x0 = oracle.normal((m, dims[0]), SEED_X, 1, 1.0)
+    ws = [oracle.normal((dims[i + 1], dims[i]), SEED_W, 2 + i, dims[i] ** -0.5) for i in range(3)]
+    d_ws = [ctx.to_device(w) for w in ws]
+    d_x = ctx.to_device(x0)
+    bufs = [d_x] + [ctx.alloc(m * dims[i + 1] * 2) for i in range(3)]
+    ops = [(ctx.gemm(dims[i], dims[i + 1], OUT_BF16 if i < 2 else OUT_RESIDUAL, rows_max=m, cta_pair=1), m, d_ws[i], bufs[i], bufs[i + 1]) for i in range(3)]
+    ops = ops + [ops[2]]  # the residual product twice in a row: read-modify-write of the same rows by neighbours
+
+    def once():
+        bufs[3].zero()
+        ctx.run(ops)
+        ctx.sync()
+        return bufs[3].download(np.uint16, (m, dims[3]))
+
+    plain = once()
+    ctx.set_launch_overlap(True)
+    try:
+        for _ in range(5):
+            assert np.array_equal(plain, once())
+    finally:
+        ctx.set_launch_overlap(False)
 
 
 def test_config1_dense_gemm(ctx, oracle):
