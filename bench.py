@@ -438,14 +438,19 @@ def main():
                 ops_s = [(ks[0], rows_s, wrap(weights[0]), wrap(xs_), wrap(qkv_)), (ks[1], rows_s, wrap(weights[1]), wrap(xs_), wrap(res_))]
                 ops_s += [(kg[0], rows_s, wrap(weights[2]), wrap(xs_), wrap(gu_)), (kg[1], rows_s, wrap(gu_), wrap(hm_))] if len(kg) == 2 else [(kg[0], rows_s, wrap(weights[2]), wrap(xs_), wrap(hm_))]
                 ops_s += [(kd, rows_s, wrap(weights[3]), wrap(hm_), wrap(res_))]
-                ctx.time(ops_s, 5)
-                barrier()
-                sec_s = max_over_ranks(ctx.time(ops_s, 50) / 50)
+                modes_s = {}
+                for on in (False, True):  # plain launches, then overlapped ones (the kernels that can wait for their predecessor themselves do)
+                    ctx.set_launch_overlap(on)
+                    ctx.time(ops_s, 5)
+                    barrier()
+                    modes_s["overlapped" if on else "plain"] = max_over_ranks(ctx.time(ops_s, 50) / 50)
+                ctx.set_launch_overlap(False)
+                sec_s = min(modes_s.values())
                 flop_s = STEP_FLOP * rows_s / ROWS
                 wbytes_s = sum(2.0 * n * k for _, k, n, _ in LAYER)
                 small[f"M{rows_s}"] = {"us": sec_s * 1e6, "tflops": flop_s / sec_s / 1e12, "weight_gbs": wbytes_s / sec_s / 1e9,
                                        "frac_hbm_weights": wbytes_s / sec_s / 1e9 / pk["hbm_gbs"], "frac_bf16_peak": flop_s / sec_s / 1e12 / pk["bf16_tflops"],
-                                       "picks": [o[0].name for o in ops_s]}
+                                       "picks": [o[0].name for o in ops_s], "launches_us": {k_: v * 1e6 for k_, v in modes_s.items()}}
             extra["layer_set_small_blocks"] = small
         except Exception as e:
             extra["small_error"] = repr(e)

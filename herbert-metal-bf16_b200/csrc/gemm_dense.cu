@@ -63,38 +63,54 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
 
     if (warp == 0) {
         // ---------------------------------------------------------- producer
+        // Overlapped launch (hb_set_launch_overlap): the kernel may have started while the kernel before it on the stream
+        // still runs. W is not that kernel's output, so the W boxes of the first stages are requested at once; X may be,
+        // so its boxes follow griddepcontrol.wait. In a plain launch the wait returns at once.
         if (lane == 0) {
             tma_prefetch_desc(&tm_x);
             tma_prefetch_desc(&tm_w);
-            uint32_t s = 0, ph = 0;
             bool ok = true;
-            for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
-                const uint32_t tm = p.m_first ? tile % p.tiles_m : tile / p.tiles_n;
-                const uint32_t tn = p.m_first ? tile / p.tiles_m : tile % p.tiles_n;
-                const int row_x = (int)(tm * BM);
-                int row_w0, row_w1;
-                if constexpr (OUT == HB_OUT_SWIGLU) {
-                    row_w0 = (int)(tn * HALF);
-                    row_w1 = (int)(p.n_out + tn * HALF);
-                } else {
-                    row_w0 = (int)(tn * BN);
-                    row_w1 = row_w0 + HALF;
-                }
-                for (uint32_t kb = 0; kb < p.k_blocks; ++kb) {
-                    if (!mbar_wait(smem_u32(&bars.empty[s]), ph ^ 1u)) {
-                        report(p.status, ST_WAIT_TIMEOUT, WHERE_EMPTY, s);
-                        ok = false;
-                        break;
+            for (int pass = 0; pass < 2 && ok; ++pass) {  // pass 0: the W boxes of the first S fills; pass 1: everything else
+                uint32_t s = 0, ph = 0, fill = 0;
+                for (uint32_t tile = blockIdx.x; ok && tile < p.num_tiles; tile += gridDim.x) {
+                    const uint32_t tm = p.m_first ? tile % p.tiles_m : tile / p.tiles_n;
+                    const uint32_t tn = p.m_first ? tile / p.tiles_m : tile % p.tiles_n;
+                    const int row_x = (int)(tm * BM);
+                    int row_w0, row_w1;
+                    if constexpr (OUT == HB_OUT_SWIGLU) {
+                        row_w0 = (int)(tn * HALF);
+                        row_w1 = (int)(p.n_out + tn * HALF);
+                    } else {
+                        row_w0 = (int)(tn * BN);
+                        row_w1 = row_w0 + HALF;
                     }
-                    const uint32_t full = smem_u32(&bars.full[s]);
-                    const uint32_t a_dst = smem_base + s * STAGE_BYTES;
-                    mbar_arrive_expect_tx(full, STAGE_BYTES);
-                    tma_load_2d(a_dst, &tm_x, full, (int)(kb * BK), row_x);
-                    tma_load_2d(a_dst + A_BYTES, &tm_w, full, (int)(kb * BK), row_w0);
-                    tma_load_2d(a_dst + A_BYTES + HALF * BK * 2, &tm_w, full, (int)(kb * BK), row_w1);
-                    if (++s == S) { s = 0; ph ^= 1u; }
+                    for (uint32_t kb = 0; kb < p.k_blocks; ++kb, ++fill) {
+                        const bool early = fill < S;  // the stage is free: nothing to wait for
+                        if (pass == 0 && !early) { ok = false; break; }  // (pass 0 ends here; ok is set again below)
+                        if (pass == 1 && !early && !mbar_wait(smem_u32(&bars.empty[s]), ph ^ 1u)) {
+                            report(p.status, ST_WAIT_TIMEOUT, WHERE_EMPTY, s);
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t full = smem_u32(&bars.full[s]);
+                        const uint32_t a_dst = smem_base + s * STAGE_BYTES;
+                        const bool do_w = pass == 0 || !early, do_x = pass == 1;
+                        if (do_w) mbar_arrive_expect_tx(full, STAGE_BYTES);
+                        if (do_x) tma_load_2d(a_dst, &tm_x, full, (int)(kb * BK), row_x);
+                        if (do_w) {
+                            tma_load_2d(a_dst + A_BYTES, &tm_w, full, (int)(kb * BK), row_w0);
+                            tma_load_2d(a_dst + A_BYTES + HALF * BK * 2, &tm_w, full, (int)(kb * BK), row_w1);
+                        }
+                        if (++s == S) { s = 0; ph ^= 1u; }
+                    }
+                }
+                if (pass == 0) {
+                    ok = true;
+                    griddep_wait();
                 }
             }
+            // every load of this CTA is requested: the kernel behind this one may take the SMs as they fall free
+            griddep_launch_dependents();
         }
     } else if (warp == 1) {
         // --------------------------------------------------------- MMA issuer
@@ -132,6 +148,7 @@ gemm_bf16_tn_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_const
         // ------------------------------------------------------------ epilogue
         const uint32_t q = (uint32_t)warp & 3u;  // the TMEM lane quarter this warp may read
         uint32_t it = 0;
+        griddep_wait();  // Y may be read (residual) or still be in use by the kernel before this one
         for (uint32_t tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++it) {
             const uint32_t tm = p.m_first ? tile % p.tiles_m : tile / p.tiles_n;
             const uint32_t tn = p.m_first ? tile / p.tiles_m : tile % p.tiles_n;
@@ -234,7 +251,7 @@ struct DenseGemm : hb_kernel {
         p.vec_ok = ((reinterpret_cast<uintptr_t>(a[2].ptr) & 15u) == 0 && ((size_t)n_out * elem) % 16 == 0) ? 1u : 0u;
         p.status = ctx->status_dev;
         const uint32_t grid = std::min<uint32_t>(p.num_tiles, (uint32_t)ctx->sm_count);
-        fn<<<grid, GEMM_THREADS, smem, ctx->stream>>>(tm_x, tm_w, p);
+        HB_CUDA(ctx, launch_kernel(ctx, true, fn, dim3(grid), dim3(GEMM_THREADS), smem, tm_x, tm_w, p));
         HB_CUDA(ctx, cudaGetLastError());
         ctx->launches++;
         return HB_OK;

@@ -133,7 +133,8 @@ def test_cta_pair_matches_single_cta_bits(ctx, oracle):
     assert np.array_equal(a, b) and np.array_equal(a, c)
 
 
-def test_cta_pair_chain_with_overlapped_launches(ctx, oracle):
+@pytest.mark.parametrize("form", [dict(cta_pair=1), dict(cta_pair=1, tile_n=192), dict(tile_n=256), dict(tile_n=128), dict(tile_n=64)], ids=str)
+def test_gemm_chain_with_overlapped_launches(ctx, oracle, form):
     """hb_set_launch_overlap: every GEMM of a chain starts under the tail of the one before (its first weight stages are
     requested before it waits for its predecessor). A chain with true dependencies (each product is the next one's
     input, the last adds into a residual twice): the same bits as with plain launches, several times over."""
@@ -143,7 +144,7 @@ def test_cta_pair_chain_with_overlapped_launches(ctx, oracle):
     d_ws = [ctx.to_device(w) for w in ws]
     d_x = ctx.to_device(x0)
     bufs = [d_x] + [ctx.alloc(m * dims[i + 1] * 2) for i in range(3)]
-    ops = [(ctx.gemm(dims[i], dims[i + 1], OUT_BF16 if i < 2 else OUT_RESIDUAL, rows_max=m, cta_pair=1), m, d_ws[i], bufs[i], bufs[i + 1]) for i in range(3)]
+    ops = [(ctx.gemm(dims[i], dims[i + 1], OUT_BF16 if i < 2 else OUT_RESIDUAL, rows_max=m, **form), m, d_ws[i], bufs[i], bufs[i + 1]) for i in range(3)]
     ops = ops + [ops[2]]  # the residual product twice in a row: read-modify-write of the same rows by neighbours
 
     def once():
