@@ -141,6 +141,11 @@ gemm_bf16_tn_streamk_kernel(const __grid_constant__ CUtensorMap tm_x, const __gr
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    // Overlapped launch: barriers and tensor memory were set up under the tail of the kernel before this one; from here
+    // on its outputs may be read, and the partial-tile scratch and flags (shared by all stream-K kernels of the context)
+    // are this kernel's alone. A plain launch passes straight through.
+    griddep_wait();
+    griddep_launch_dependents();
     const uint32_t tmem_base = bars.tmem_base;
     const uint32_t n_pieces = sk_pieces(sp, cta, grid, 0, nullptr);
     const uint32_t sk_units = (p.num_tiles - (p.num_tiles / grid) * grid) * p.k_blocks;  // units of the partial wave
@@ -442,8 +447,7 @@ struct StreamKGemm : hb_kernel {
         sp.flags = ctx->sk_flags;
         sp.epoch = 1;
         const uint32_t grid = (uint32_t)std::min<uint64_t>(units, (uint64_t)ctx->sm_count);  // a whole wave or more: every SM
-        fn<<<grid, GEMM_THREADS, smem, ctx->stream>>>(tm_x, tm_w, sp);
-        HB_CUDA(ctx, cudaGetLastError());
+        HB_CUDA(ctx, launch_kernel(ctx, true, fn, dim3(grid), dim3(GEMM_THREADS), smem, tm_x, tm_w, sp));
         ctx->launches++;
         return HB_OK;
     }

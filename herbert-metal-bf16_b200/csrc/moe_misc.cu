@@ -13,6 +13,8 @@ namespace hb {
 // h[r][c] = bf16(g*sigmoid(g)*u), g = gu[r][c], u = gu[r][n + c]
 // (reference src/metal/prefill.rs:2790-2818; src/metal/qwen_kernels.rs:2087 over expert rows).
 __global__ void swiglu_rows_kernel(const uint16_t* __restrict__ gu, uint16_t* __restrict__ h, uint32_t m, uint32_t n, uint32_t vec) {
+    griddep_wait();
+    griddep_launch_dependents();
     if (vec) {
         const uint32_t n8 = n / 8;
         const size_t total = (size_t)m * n8;
@@ -253,7 +255,7 @@ struct SwigluRows : hb_kernel {
         if (!range_ok(a[0], (size_t)m * 2 * n * 2) || !range_ok(a[1], (size_t)m * n * 2)) return fail(ctx, HB_INVALID, name + ": a bound range is too small");
         const uint32_t vec = (n % 8 == 0 && ((reinterpret_cast<uintptr_t>(a[0].ptr) | reinterpret_cast<uintptr_t>(a[1].ptr)) & 15u) == 0) ? 1u : 0u;
         const size_t items = vec ? (size_t)m * (n / 8) : (size_t)m * n;
-        swiglu_rows_kernel<<<grid_for(ctx, items, 256), 256, 0, ctx->stream>>>(static_cast<const uint16_t*>(a[0].ptr), static_cast<uint16_t*>(a[1].ptr), m, n, vec);
+        HB_CUDA(ctx, launch_kernel(ctx, true, swiglu_rows_kernel, dim3(grid_for(ctx, items, 256)), dim3(256), 0, static_cast<const uint16_t*>(a[0].ptr), static_cast<uint16_t*>(a[1].ptr), m, n, vec));
         HB_CUDA(ctx, cudaGetLastError());
         ctx->launches++;
         return HB_OK;

@@ -133,7 +133,7 @@ def test_cta_pair_matches_single_cta_bits(ctx, oracle):
     assert np.array_equal(a, b) and np.array_equal(a, c)
 
 
-@pytest.mark.parametrize("form", [dict(cta_pair=1), dict(cta_pair=1, tile_n=192), dict(tile_n=256), dict(tile_n=128), dict(tile_n=64)], ids=str)
+@pytest.mark.parametrize("form", [dict(cta_pair=1), dict(cta_pair=1, tile_n=192), dict(tile_n=256), dict(tile_n=128), dict(tile_n=64), dict(stream_k=1, tile_n=128), dict(stream_k=1, tile_n=64)], ids=str)
 def test_gemm_chain_with_overlapped_launches(ctx, oracle, form):
     """hb_set_launch_overlap: every GEMM of a chain starts under the tail of the one before (its first weight stages are
     requested before it waits for its predecessor). A chain with true dependencies (each product is the next one's

@@ -184,6 +184,8 @@ def test_moe_layer_with_overlapped_launches(ctx, hb200, oracle, shape):
         for _ in range(2):
             over = moe_layer(ctx, hb200, oracle, *shape, merge_runs=1)
             assert np.array_equal(plain, over)
+        # (the form with the SwiGLU as a kernel of its own between the expert GEMMs)
+        assert np.array_equal(plain, moe_layer(ctx, hb200, oracle, *shape, fused=False, merge_runs=1))
     finally:
         ctx.set_launch_overlap(False)
 
