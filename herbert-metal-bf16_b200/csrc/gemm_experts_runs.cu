@@ -175,7 +175,6 @@ gemm_expert_runs_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_c
     // (an overlapped launch: barriers and tensor memory are set up under the tail of the kernel before this one; the
     // table, the list and the token rows are its outputs)
     griddep_wait();
-    griddep_launch_dependents();
     const uint32_t ntiles = min(p.tiles[0], p.max_tiles);
     build_runs(p, ntiles, reinterpret_cast<uint32_t*>(smem_raw), run_first, run_end, runs, scratch, &bars.nruns);  // ends with __syncthreads
     tc_fence_before();
@@ -212,6 +211,9 @@ gemm_expert_runs_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_c
                     if (++s == S) { s = 0; ph ^= 1u; }
                 }
             }
+            // every weight load of this CTA is requested: the kernel behind this one may take the SMs as they fall free
+            // (let go at the kernel's start, its blocks sat on the SMs beside this kernel's for its whole length: slower)
+            griddep_launch_dependents();
         }
     } else if (warp == 1) {
         if (lane == 0) {

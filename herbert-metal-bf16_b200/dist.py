@@ -404,7 +404,7 @@ class EpPeer:
     def __init__(self, hb, ctx, rank: int, world: int, rows: int, h: int, mi: int, experts: int, top_k: int, bm: int = 64, cap: int | None = None,
                  device=None, fused: bool = True, plain_when_alone: bool = True, direct: bool | None = None, overlap: bool = False):
         # overlap: record the step with overlapped launches (its kernels wait for their predecessors themselves);
-        # measured slower than plain launches for this block on one B200 (334 against 328 us), so off unless asked for
+        # measured no faster than plain launches for this block on one B200 (326 us either way), so off unless asked for
         assert experts % world == 0
         self.hb, self.ctx, self.rank, self.world = hb, ctx, rank, world
         self.rows, self.h, self.mi, self.experts, self.top_k, self.bm = rows, h, mi, experts, top_k, bm
