@@ -1200,7 +1200,7 @@ def bench_sharded(hb, ctx, torch, dev, pk, rank, world, barrier, max_over_ranks)
                     one.close()
                 out["moe_ep_2048tok"] = {"n_gpus": world, "us": sec * 1e6, "t1_us": t1 * 1e6, "efficiency": t1 / (world * sec), "weight_gbs_total": wbytes / sec / 1e9,
                                          "tokens_per_s": m / sec, "scaling": "strong", "tile_rows": bm, "kernels_per_step": kernels_per_step, "parity": parity, "kernels_us": ep_kernels,
-                                         "exchange": "peer-memory stores and loads by the library's kernels, offsets all-gather and barriers as kernels (no NCCL call in the step); the step replayed as one recorded sequence",
+                                         "exchange": "peer-memory stores and loads by the library's kernels: every source owns a region of the owners' buffers (no counts exchanged first), the dispatch flags its landing and the plan waits for the flags, the combine carries the outputs-complete barrier and pulls the expert outputs (no NCCL call in the step); the step replayed as one recorded sequence" if world > 1 else "one GPU: the plain block",
                                          "launched_one_by_one_us": sec_loop * 1e6,
                                          "nccl_form_us": sec_nccl * 1e6, "equals_nccl_form_bitwise": same}
                 if world > 1:

@@ -214,9 +214,10 @@ class GpuBackend:
 #
 # The same block as ep_moe with the exchange done by the library's own kernels through NVLink (include/hb200.h,
 # "expert-parallel exchange over peer memory"): nothing is read back to the host, no variable-size collective.
-# Per rank and call: route, sort by global expert (+ offsets), all-gather of the offsets (1 KB per rank),
-# dispatch (stores into the owners' receive buffers), barrier, plan + gate/up + down on the received rows,
-# barrier, return (loads from the owners' output buffers), combine.
+# Per rank and call, in the plain form: route, sort by global expert (+ offsets), all-gather of the offsets (1 KB per
+# rank), dispatch (stores into the owners' receive buffers), barrier, plan + gate/up + down on the received rows,
+# barrier, return (loads from the owners' output buffers), combine. In the default form (EpPeer below) the all-gather
+# and both barrier kernels are gone: seven kernels.
 
 def ep_positions_np(offs_all, rank: int, epr: int, region: int = 0):
     """Host mirror of the dispatch / return index arithmetic: for every sorted position p of `rank`, the
@@ -394,7 +395,8 @@ class EpPeer:
     and the combine are one kernel that reads every slot's output row from its owner (no EY written and re-read).
     direct (the default with fused, when cap divides by the number of ranks): every source owns a fixed region of every
     receive buffer, so nobody needs anybody's counts to place rows and the all-gather of the offsets before the dispatch
-    falls away (the dispatch delivers the offsets itself): route, sort, dispatch, plan, two GEMMs, barrier, combine.
+    falls away (the dispatch delivers the offsets itself): route, sort, dispatch, plan, two GEMMs, and a combine that
+    carries the barrier "every rank's outputs are complete" itself when every rank is a process of its own.
     fused = False: all-gather, dispatch, barrier, plan, GEMMs, barrier, return into EY, combine.
     With one rank there is nothing to exchange and the step is the plain block (route, sort, the expert GEMMs gathering
     from X and scattering into EY, combine) unless plain_when_alone is False (the exchange kernels with one rank, as the
