@@ -149,36 +149,18 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     const int lane = threadIdx.x & 31;
     const uint32_t S = p.stages;
 
-    if (threadIdx.x == 0) {
-        for (uint32_t s = 0; s < S; ++s) {
-            mbar_init(smem_u32(&bars.full[s]), 1);
-            mbar_init(smem_u32(&bars.empty[s]), 1);
-        }
-        for (int a = 0; a < 2; ++a) {
-            mbar_init(smem_u32(&bars.tmem_full[a]), 1);
-            mbar_init(smem_u32(&bars.tmem_empty[a]), 4);
-        }
-        fence_mbar_init();
-        fence_proxy_async();
-    }
-    if (warp == 1) {
-        tmem_alloc(smem_u32(&bars.tmem_base), TMEM_COLS);
-        tmem_relinquish();
-    }
-    tc_fence_before();
-    __syncthreads();
-    tc_fence_after();
-    const uint32_t tmem_base = bars.tmem_base;
-
-    // this CTA's segments: the table was worked out on the host when the kernel object was made (it depends on n, k
-    // and the grid only); the first SK_SEG_CACHE of them are copied to shared memory for the three roles
+    // this CTA's segments. Whole feature blocks per CTA: block c, c + grid, ... over all of K, worked out here. Balanced
+    // units: the table made on the host when the kernel object was made (it depends on n, k and the grid only); the
+    // first SK_SEG_CACHE entries are copied to shared memory for the three roles.
     __shared__ SkinnySeg segs_s[SK_SEG_CACHE];
-    const uint32_t seg0 = p.seg_start[blockIdx.x], n_segs = p.seg_start[blockIdx.x + 1] - seg0;
-    if (threadIdx.x < min(n_segs, (uint32_t)SK_SEG_CACHE)) segs_s[threadIdx.x] = p.segs[seg0 + threadIdx.x];
-    __syncthreads();
-    auto seg_at = [&](uint32_t i, SkinnySeg* out) { *out = i < (uint32_t)SK_SEG_CACHE ? segs_s[i] : p.segs[seg0 + i]; };
-    griddep_launch_dependents();
-
+    const bool table = p.balanced != 0;
+    const uint32_t seg0 = table ? p.seg_start[blockIdx.x] : 0u;
+    const uint32_t n_segs = table ? p.seg_start[blockIdx.x + 1] - seg0
+                                  : (blockIdx.x < p.feat_blocks ? (p.feat_blocks - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u);
+    auto seg_at = [&](uint32_t i, SkinnySeg* out) {
+        if (!table) *out = SkinnySeg{blockIdx.x + i * gridDim.x, 0u, p.k_blocks, 0u, 1u};
+        else *out = i < (uint32_t)SK_SEG_CACHE ? segs_s[i] : p.segs[seg0 + i];
+    };
     // The stage fills of this CTA, in order. The first S of them find their stage free; their weight boxes do
     // not depend on the kernel before this one on the stream, so they are issued first (pass 0), then the
     // predecessor is waited for, then their activation boxes follow (pass 1) and the rest of the fills (pass 2).
@@ -219,6 +201,39 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         }
         return true;
     };
+    // Set-up. Thread 0 makes the barriers and, where nothing else is needed to know this CTA's work (whole blocks, no
+    // fused norm), requests the weight boxes of the first fills at once: before tensor memory is allocated and before
+    // the first block-wide barrier (a weight stream of 100 MB is 15 us long: every microsecond before its first byte counts).
+    bool early_w = false;
+    if (threadIdx.x == 0) {
+        for (uint32_t s = 0; s < S; ++s) {
+            mbar_init(smem_u32(&bars.full[s]), 1);
+            mbar_init(smem_u32(&bars.empty[s]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(smem_u32(&bars.tmem_full[a]), 1);
+            mbar_init(smem_u32(&bars.tmem_empty[a]), 4);
+        }
+        fence_mbar_init();
+        fence_proxy_async();
+        if (!table && !NORM) {
+            tma_prefetch_desc(&tm_w);
+            tma_prefetch_desc(&tm_x);
+            walk(0);
+            early_w = true;
+        }
+    }
+    if (warp == 1) {
+        tmem_alloc(smem_u32(&bars.tmem_base), TMEM_COLS);
+        tmem_relinquish();
+    }
+    if (table && threadIdx.x < min(n_segs, (uint32_t)SK_SEG_CACHE)) segs_s[threadIdx.x] = p.segs[seg0 + threadIdx.x];
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = bars.tmem_base;
+    griddep_launch_dependents();
+
     if constexpr (NORM) {
         if (warp == 0 && lane == 0) {
             tma_prefetch_desc(&tm_w);
@@ -236,9 +251,11 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     if (warp == 0) {
         if (lane == 0) {
             if constexpr (!NORM) {
-                tma_prefetch_desc(&tm_w);
-                tma_prefetch_desc(&tm_x);
-                walk(0);
+                if (!early_w) {
+                    tma_prefetch_desc(&tm_w);
+                    tma_prefetch_desc(&tm_x);
+                    walk(0);
+                }
                 griddep_wait();
             }
             walk(1);
