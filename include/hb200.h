@@ -418,7 +418,7 @@ int hb_tp_sum_stream_get(hb_ctx* ctx, uint32_t n, uint32_t out, uint32_t world, 
  * HB_STATIC_SCRATCH_MAX_ROWS rows, HB_STATIC_SCRATCH_MAX_K or HB_STATIC_SCRATCH_MAX_N are refused with
  * HB_UNSUPPORTED: use hb_gemm_get for those.
  * The first call on a device looks up the array's device address (cudaGetSymbolAddress) and raises the kernel's
- * shared-memory limit; make that first call before any stream capture begins.
+ * shared-memory limit.
  * All calls on a device share the one array: two calls whose kernels overlap on the GPU (different streams or
  * contexts) race on it. Calls on one stream are ordered and safe; nothing needs clearing between them. */
 #define HB_STATIC_SCRATCH_SLOTS 160u
@@ -441,7 +441,7 @@ int hb_time(hb_ctx* ctx, const hb_op* ops, int nops, int reps, double* gpu_secon
  * reference encodes its ops into one command buffer per step (src/metal/gpu.rs:151-221) for the same reason. The
  * bound ranges and m are fixed at recording. Every kernel of this library can be recorded (none of them carries a
  * host-side counter: the stream-K GEMM's flags are cleared by their reader, the peer barrier counts itself);
- * hb_gemm_static_scratch is a direct call, not an hb_kernel, and is not recordable. */
+ * hb_gemm_static_scratch is a direct call, not an hb_kernel: it is not an entry of an hb_op list. */
 /* Overlapped launches (off by default): the decode kernels (hb_matvec_get in all its forms, hb_rmsnorm_get) are then
  * launched with programmatic stream serialization: a kernel may start while the one before it on the stream is
  * still finishing, sets up, prefetches weights, and waits inside for its predecessor's completion before it reads
