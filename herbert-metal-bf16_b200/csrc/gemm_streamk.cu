@@ -141,11 +141,10 @@ gemm_bf16_tn_streamk_kernel(const __grid_constant__ CUtensorMap tm_x, const __gr
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    // Overlapped launch: barriers and tensor memory were set up under the tail of the kernel before this one; from here
-    // on its outputs may be read, and the partial-tile scratch and flags (shared by all stream-K kernels of the context)
-    // are this kernel's alone. A plain launch passes straight through.
-    griddep_wait();
-    griddep_launch_dependents();
+    // Overlapped launch: barriers and tensor memory were set up under the tail of the kernel before this one. The
+    // producer requests the W boxes of its first fills (weights are nobody's output) and then waits for that kernel;
+    // the epilogue warps wait before they touch Y or the partial-tile scratch and flags, which all stream-K kernels of
+    // the context share. A plain launch passes straight through the waits.
     const uint32_t tmem_base = bars.tmem_base;
     const uint32_t n_pieces = sk_pieces(sp, cta, grid, 0, nullptr);
     const uint32_t sk_units = (p.num_tiles - (p.num_tiles / grid) * grid) * p.k_blocks;  // units of the partial wave
@@ -159,37 +158,49 @@ gemm_bf16_tn_streamk_kernel(const __grid_constant__ CUtensorMap tm_x, const __gr
         if (lane == 0) {
             tma_prefetch_desc(&tm_x);
             tma_prefetch_desc(&tm_w);
-            uint32_t s = 0, ph = 0;
             bool ok = true;
-            for (uint32_t i = 0; ok && i < n_pieces; ++i) {
-                Piece pc;
-                sk_pieces(sp, cta, grid, i, &pc);
-                uint32_t tm, tn;
-                tile_mn(pc.tile, tm, tn);
-                const int row_x = (int)(tm * BM);
-                int row_w0, row_w1;
-                if constexpr (OUT == HB_OUT_SWIGLU) {
-                    row_w0 = (int)(tn * HALF);
-                    row_w1 = (int)(p.n_out + tn * HALF);
-                } else {
-                    row_w0 = (int)(tn * BN);
-                    row_w1 = row_w0 + HALF;
-                }
-                for (uint32_t kb = pc.kb0; kb < pc.kb1; ++kb) {
-                    if (!mbar_wait(smem_u32(&bars.empty[s]), ph ^ 1u)) {
-                        report(p.status, ST_WAIT_TIMEOUT, WHERE_EMPTY, s);
-                        ok = false;
-                        break;
+            for (int pass = 0; pass < 2 && ok; ++pass) {  // pass 0: the W boxes of the first S fills; pass 1: everything else
+                uint32_t s = 0, ph = 0, fill = 0;
+                for (uint32_t i = 0; ok && i < n_pieces; ++i) {
+                    Piece pc;
+                    sk_pieces(sp, cta, grid, i, &pc);
+                    uint32_t tm, tn;
+                    tile_mn(pc.tile, tm, tn);
+                    const int row_x = (int)(tm * BM);
+                    int row_w0, row_w1;
+                    if constexpr (OUT == HB_OUT_SWIGLU) {
+                        row_w0 = (int)(tn * HALF);
+                        row_w1 = (int)(p.n_out + tn * HALF);
+                    } else {
+                        row_w0 = (int)(tn * BN);
+                        row_w1 = row_w0 + HALF;
                     }
-                    const uint32_t full = smem_u32(&bars.full[s]);
-                    const uint32_t a_dst = smem_base + s * STAGE_BYTES;
-                    mbar_arrive_expect_tx(full, STAGE_BYTES);
-                    tma_load_2d(a_dst, &tm_x, full, (int)(kb * BK), row_x);
-                    tma_load_2d(a_dst + A_BYTES, &tm_w, full, (int)(kb * BK), row_w0);
-                    tma_load_2d(a_dst + A_BYTES + HALF * BK * 2, &tm_w, full, (int)(kb * BK), row_w1);
-                    if (++s == S) { s = 0; ph ^= 1u; }
+                    for (uint32_t kb = pc.kb0; kb < pc.kb1; ++kb, ++fill) {
+                        const bool early = fill < S;  // the stage is free: nothing to wait for
+                        if (pass == 0 && !early) { ok = false; break; }  // (pass 0 ends here; ok is set again below)
+                        if (pass == 1 && !early && !mbar_wait(smem_u32(&bars.empty[s]), ph ^ 1u)) {
+                            report(p.status, ST_WAIT_TIMEOUT, WHERE_EMPTY, s);
+                            ok = false;
+                            break;
+                        }
+                        const uint32_t full = smem_u32(&bars.full[s]);
+                        const uint32_t a_dst = smem_base + s * STAGE_BYTES;
+                        const bool do_w = pass == 0 || !early, do_x = pass == 1;
+                        if (do_w) mbar_arrive_expect_tx(full, STAGE_BYTES);
+                        if (do_x) tma_load_2d(a_dst, &tm_x, full, (int)(kb * BK), row_x);
+                        if (do_w) {
+                            tma_load_2d(a_dst + A_BYTES, &tm_w, full, (int)(kb * BK), row_w0);
+                            tma_load_2d(a_dst + A_BYTES + HALF * BK * 2, &tm_w, full, (int)(kb * BK), row_w1);
+                        }
+                        if (++s == S) { s = 0; ph ^= 1u; }
+                    }
+                }
+                if (pass == 0) {
+                    ok = true;
+                    griddep_wait();
                 }
             }
+            griddep_launch_dependents();  // every load of this CTA is requested
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -226,6 +237,7 @@ gemm_bf16_tn_streamk_kernel(const __grid_constant__ CUtensorMap tm_x, const __gr
         }
     } else {
         const uint32_t q = (uint32_t)warp & 3u;
+        griddep_wait();  // Y, the scratch and the flags may still be in use by the kernel before this one
         for (uint32_t i = 0; i < n_pieces; ++i) {
             Piece pc;
             sk_pieces(sp, cta, grid, i, &pc);
