@@ -542,7 +542,7 @@ def ep_moe_peer(state: EpPeer, x_local, scores_local, wgu_local, wd_local, group
     """The sparse block for this rank's token rows with the exchange through peer memory; returns out [rows][h].
     nccl_sync = True orders the steps with NCCL collectives (an all-gather and two one-word all-reduces) instead
     of the library's barrier kernel; the data path is the same. recorded = True (several ranks, the library's
-    barriers): the step's 13 kernels are recorded once per (buffers, parity) and replayed with one call."""
+    barriers): the step's kernels (7 in the default form) are recorded once per (buffers, parity) and replayed with one call."""
     multi = state.world > 1
     if recorded and multi and not nccl_sync and not state.pb.emulated:
         def step(replay=False):
